@@ -1,0 +1,245 @@
+/*
+ * moe_b200.h — C ABI of the B200 (sm_100a) quantized-MoE hot path.
+ *
+ * This is the boundary a host program (a Rust crate through `extern "C"`, a
+ * Python module through ctypes, C++) binds to replace the 4-bit MoE path of
+ * fbundle/moe_infer.  Each entry point names the reference interface it stands
+ * in for (paths are relative to the reference project root).
+ *
+ * Conventions
+ *  - Every function returns an int status: 0 (MOE_OK) on success, a negative
+ *    moe_status_t otherwise; moe_last_error() returns a thread-local message.
+ *    Nothing throws, aborts or exits across this boundary.
+ *  - Handles are opaque.  An engine is bound to one CUDA device and, like the
+ *    reference engine (`#[pyclass(unsendable)]`, &mut self), serves one caller
+ *    thread at a time; there is no internal locking.
+ *  - Pointers named *_host are host memory (pageable or pinned), pointers
+ *    named *_dev are device memory on the engine's device.  Inputs are borrowed
+ *    read-only for the duration of the call; outputs are caller-allocated.
+ *  - All work is issued on the engine's own CUDA stream.  Host-pointer entry
+ *    points return after the result is in the caller's buffer; *_dev entry
+ *    points return after enqueueing (call moe_engine_sync to wait).
+ *  - There is no CPU fallback: without a usable CUDA device every compute entry
+ *    point fails with MOE_ERR_CUDA.
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct moe_engine moe_engine_t;
+
+typedef enum {
+    MOE_OK = 0,
+    MOE_ERR_INVALID = -1,     /* bad argument / shape / config  (reference: MoEError::Config -> ValueError) */
+    MOE_ERR_CUDA = -2,        /* CUDA runtime failure           (reference: MoEError::Metal  -> RuntimeError) */
+    MOE_ERR_STATE = -3,       /* tensors not loaded yet, wrong call order */
+    MOE_ERR_INTERRUPTED = -4, /* the caller's check callback returned non-zero ("interrupted") */
+    MOE_ERR_DEVICE_WAIT = -5, /* a bounded device-side wait gave up; the context stays usable */
+    MOE_ERR_UNSUPPORTED = -6,
+    MOE_ERR_IO = -7           /* reference: MoEError::Io -> IOError */
+} moe_status_t;
+
+/* Tensor-selection scheme (src/quantize/qwen35_moe/bq4.rs:25-45, int4.rs:24-35):
+ * both use the same 4-bit codec for experts; they differ in the router dtype. */
+typedef enum { MOE_SCHEME_BQ4 = 0, MOE_SCHEME_INT4 = 1 } moe_scheme_t;
+
+typedef enum { MOE_DT_F32 = 0, MOE_DT_BF16 = 1, MOE_DT_INT4 = 2 } moe_dtype_t;
+
+/* Non-expert tensors of one MoE block, by role.  Names in the reference's
+ * weight manifest: `model.layers.{L}.post_attention_layernorm.weight`,
+ * `…mlp.gate`, `…mlp.shared_expert.{gate,up,down}_proj`, `…mlp.shared_expert_gate`
+ * (src/engine/qwen35_moe/cpu.rs:180-205, 453-463). */
+typedef enum {
+    MOE_T_POST_NORM = 0,   /* bf16 [hidden] */
+    MOE_T_ROUTER = 1,      /* bf16 [E, hidden] (BQ4) or INT4 triple (INT4 scheme) */
+    MOE_T_SHARED_GATE = 2, /* INT4 [shared_inter, hidden] */
+    MOE_T_SHARED_UP = 3,   /* INT4 [shared_inter, hidden] */
+    MOE_T_SHARED_DOWN = 4, /* INT4 [hidden, shared_inter] */
+    MOE_T_SHARED_SGATE = 5 /* INT4 [1, hidden]: the shared expert's sigmoid scalar gate */
+} moe_tensor_role_t;
+
+/* Replaces the compile-time ModelConfig constants
+ * (src/engine/qwen35_moe/constants.rs:146-241) and validate_config (:57-90). */
+typedef struct {
+    int32_t hidden;         /* 2048 */
+    int32_t inter;          /* moe_intermediate_size, 512 */
+    int32_t shared_inter;   /* shared_expert_intermediate_size, 512 */
+    int32_t num_experts;    /* 256 (stripped test model: 4) */
+    int32_t top_k;          /* num_active_experts, <= 8 (src/engine/qwen35_moe/metal_context.rs:564-577) */
+    int32_t num_layers;     /* 40 */
+    int32_t num_mtp_layers; /* 0 or 1; the MTP block's experts are layer index num_layers */
+    int32_t group;          /* 64 (src/constants.rs GROUP_SIZE) */
+    int32_t vocab;          /* carried for the caller; unused by the MoE path */
+    int32_t scheme;         /* moe_scheme_t */
+} moe_dims_t;
+
+/* Byte offsets inside one packed expert
+ * (src/engine/qwen35_moe/constants.rs:117-139 expert_layout). */
+typedef struct {
+    int64_t gate_w, gate_s, gate_b, up_w, up_s, up_b, down_w, down_s, down_b, expert_size;
+} moe_expert_layout_t;
+
+const char* moe_last_error(void);
+const char* moe_version(void);
+
+/* src/engine/qwen35_moe/constants.rs:117-139 */
+int moe_expert_layout(int32_t hidden, int32_t inter, int32_t group, moe_expert_layout_t* out);
+
+/* ── engine lifetime ─────────────────────────────────────────────────────────
+ * Replaces MetalContext::new (src/engine/qwen35_moe/metal_context.rs:558-600):
+ * device, stream, persistent workspace.  MOE_ERR_INVALID for top_k > 8 or
+ * dimensions the kernels do not cover. */
+int moe_engine_create(const moe_dims_t* dims, int device, moe_engine_t** out);
+void moe_engine_destroy(moe_engine_t* e);
+int moe_engine_sync(moe_engine_t* e);
+int moe_engine_dims(const moe_engine_t* e, moe_dims_t* out);
+
+/* ── resident expert store ───────────────────────────────────────────────────
+ * Replaces ExpertFile::read_expert (src/model/expert.rs:29-66), ExpertCache
+ * (src/engine/qwen35_moe/metal_context.rs:25-121) and the prefetch pool: every
+ * `packed_experts/layer_NN.bin` is copied once into device memory and stays.
+ * `bytes` must equal num_experts * expert_size. */
+int moe_store_load_layer(moe_engine_t* e, int layer, const void* blob_host, size_t bytes);
+/* Device address of a layer's resident blob, so that the GPU packer can write
+ * it in place (allocates the layer if needed). */
+int moe_store_layer_dev(moe_engine_t* e, int layer, void** blob_dev);
+/* Marks a layer whose blob was written on the device as loaded. */
+int moe_store_mark_loaded(moe_engine_t* e, int layer);
+/* Non-expert tensors by role; replaces WeightFile lookups by name
+ * (src/model/weights.rs:124-179).  dtype MOE_DT_BF16: `w` only; MOE_DT_INT4:
+ * `w` u32 words, `s` bf16 scales, `b` bf16 biases.  Host pointers. */
+int moe_store_load_tensor(moe_engine_t* e, int layer, int role, const void* w_host,
+                          const void* s_host, const void* b_host, int dtype);
+int moe_store_bytes(const moe_engine_t* e, size_t* resident_bytes);
+
+/* ── packer ──────────────────────────────────────────────────────────────────
+ * quant_f32_to_int4 (src/dtype.rs:102-135) with the reference's bf16 rounding
+ * (src/dtype.rs:85-89); bit-exact.  src is f32 or bf16 [rows, cols]; cols % 64
+ * == 0.  Device pointers. */
+int moe_pack_int4_dev(moe_engine_t* e, const void* src_dev, int src_dtype, int64_t rows, int32_t cols,
+                      void* w_dev, void* s_dev, void* b_dev);
+/* Same through host buffers (copies in, packs on the GPU, copies out). */
+int moe_pack_int4_host(moe_engine_t* e, const void* src_host, int src_dtype, int64_t rows, int32_t cols,
+                       void* w_host, void* s_host, void* b_host);
+/* process_experts_common (src/quantize/qwen35_moe/common.rs:300-345): HF
+ * gate_up [E, 2I, H] and down [E, H, I] -> E packed experts back to back.
+ * Device pointers; n_experts may be a sub-range (pointers pre-offset). */
+int moe_pack_experts_dev(moe_engine_t* e, const void* gate_up_dev, const void* down_dev, int src_dtype,
+                         int32_t n_experts, void* blob_dev);
+int moe_pack_experts_host(moe_engine_t* e, const void* gate_up_host, const void* down_host, int src_dtype,
+                          int32_t n_experts, void* blob_host);
+
+/* ── single dequant-matvec ───────────────────────────────────────────────────
+ * dequant_matvec_4bit (src/math_util.rs:14-54; Metal default
+ * dequant_matvec_4bit_v4_nr4, src/engine/shaders.metal:2949).  x f32 [cols],
+ * y f32 [rows]. */
+int moe_matvec_int4_dev(moe_engine_t* e, const void* w_dev, const void* s_dev, const void* b_dev,
+                        const float* x_dev, float* y_dev, int32_t rows, int32_t cols);
+int moe_matvec_int4_host(moe_engine_t* e, const void* w_host, const void* s_host, const void* b_host,
+                         const float* x_host, float* y_host, int32_t rows, int32_t cols);
+
+/* ── one MoE block ───────────────────────────────────────────────────────────
+ * post-attention RMS norm, router, top-k, routed experts, gated shared expert,
+ * combine with the residual: CpuEngine pre_expert (tail) + route_experts +
+ * post_expert (src/engine/qwen35_moe/cpu.rs:187-205, 78-85, 398-483);
+ * GPU engines: op1 tail + route_experts + encode_post_expert
+ * (src/engine/qwen35_moe/fused_exp1.rs:231-365, 734-856), batched:
+ * encode_post_expert_at (src/engine/qwen35_moe/batched.rs:334-447).
+ *   h_in, h_out   f32 [n_tokens, hidden]  (h_in is the reference's h_mid)
+ *   logit_bias    f32 [E] added to router logits before softmax, or NULL
+ *   forced_idx    int32 [n_tokens, top_k] replaces the top-k choice, or NULL
+ *   out_idx/out_w [n_tokens, top_k] chosen experts and renormalised weights
+ *                 (descending weight order), or NULL
+ * n_tokens == 1 runs the decode (matvec) path, n_tokens > 1 the grouped path
+ * (token-serial fallback inside the reference: fused_exp3.rs:169-171). */
+int moe_layer_forward_host(moe_engine_t* e, int layer, const float* h_in_host, int32_t n_tokens,
+                           float* h_out_host, const float* logit_bias_host,
+                           const int32_t* forced_idx_host, int32_t* out_idx_host, float* out_w_host);
+int moe_layer_forward_dev(moe_engine_t* e, int layer, const float* h_in_dev, int32_t n_tokens,
+                          float* h_out_dev, const float* logit_bias_dev, const int32_t* forced_idx_dev,
+                          int32_t* out_idx_dev, float* out_w_dev);
+
+/* ── the layer stack behind forward_hidden / forward_hidden_batched ──────────
+ * Engine::forward_hidden / forward_hidden_batched (src/engine.rs:45-63;
+ * src/engine/qwen35_moe/fused_exp1.rs:937-984, fused_exp3.rs:155-319) with the
+ * attention half of every block passed through (h_mid = h): for each layer
+ * h <- moe_block(h).  emb/out f32 [n_tokens, hidden]; out is the hidden state
+ * before the final norm (Engine::last_h_pre_norm).  batched == 0 walks the
+ * tokens one by one through the decode path (the reference's token-serial
+ * loop), batched != 0 runs all tokens per layer through the grouped path.
+ * mtp != 0 keeps the last token's hidden state for moe_mtp_forward.  `check`
+ * (nullable) is polled between tokens / layers like the reference's
+ * SignalCheckFn (src/engine.rs:10); non-zero aborts with MOE_ERR_INTERRUPTED. */
+typedef int (*moe_check_fn)(void* ctx);
+int moe_forward_hidden_host(moe_engine_t* e, const float* emb_host, int32_t n_tokens, int batched, int mtp,
+                            moe_check_fn check, void* check_ctx, float* out_host);
+int moe_forward_hidden_dev(moe_engine_t* e, const float* emb_dev, int32_t n_tokens, int batched,
+                           float* out_dev);
+/* Engine::last_h_pre_norm (src/engine.rs:66-68): f32 [hidden] of the last token. */
+int moe_last_h_pre_norm(moe_engine_t* e, float* out_host);
+
+/* ── MTP block ───────────────────────────────────────────────────────────────
+ * Engine::mtp_forward / mtp_reset / mtp_rollback (src/engine.rs:70-78;
+ * src/engine/qwen35_moe/mtp.rs:58-225).  Only the block's MoE half
+ * (mtp.rs:176-207, 381-517; experts = layer index num_layers) runs here; its
+ * attention half is passed through.  `h_in_host` is the block input the caller
+ * built from last_h_pre_norm and the token embedding (mtp.rs:85-110); out is
+ * f32 [hidden].  MOE_ERR_STATE when num_mtp_layers == 0. */
+int moe_mtp_forward_host(moe_engine_t* e, const float* h_in_host, float* h_out_host);
+int moe_mtp_reset(moe_engine_t* e);
+int moe_mtp_rollback(moe_engine_t* e, int64_t pos);
+int moe_mtp_pos(const moe_engine_t* e, int64_t* pos);
+
+/* ── telemetry ───────────────────────────────────────────────────────────────
+ * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys
+ * follow the reference (`engine.total_ms`, `phase.route_cpu_ms`, ...).  Fills up
+ * to *n entries; on return *n is the number available.  Key pointers stay
+ * valid until the next call on the same engine. */
+void moe_set_record_telemetry(int on);
+int moe_get_record_telemetry(void);
+int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n);
+
+/* ── expert parallelism over the GPUs of one box ─────────────────────────────
+ * No counterpart in the reference (single device).  Rank r keeps experts
+ * [r*E/P, (r+1)*E/P) of every layer.  Peers exchange token rows through
+ * device memory they map from one another: each rank exports one handle
+ * (moe_ep_export), the host program gathers all handles by any means it has,
+ * and gives the table to moe_ep_init. */
+#define MOE_EP_HANDLE_BYTES 64
+int moe_ep_export(moe_engine_t* e, int32_t max_tokens_per_rank, void* handle_out /* MOE_EP_HANDLE_BYTES */);
+int moe_ep_init(moe_engine_t* e, int rank, int world, const void* all_handles /* world * MOE_EP_HANDLE_BYTES */);
+int moe_ep_finalize(moe_engine_t* e);
+
+/* ── synthetic data ──────────────────────────────────────────────────────────
+ * No counterpart in the reference (it reads real checkpoints): fills a device
+ * buffer with seeded N(0, sigma^2) values, a fraction `outlier_frac` of them
+ * replaced by +-outlier_value; f32 or bf16.  Used to build synthetic
+ * checkpoints of the reference's shapes for benchmarks and full-size tests. */
+int moe_synth_normal_dev(moe_engine_t* e, void* dst_dev, int dtype, int64_t n, uint64_t seed, float sigma,
+                         float outlier_frac, float outlier_value);
+
+/* ── plain device-memory helpers for hosts without a CUDA binding ──────────── */
+int moe_dev_alloc(moe_engine_t* e, size_t bytes, void** out_dev);
+int moe_dev_free(moe_engine_t* e, void* p_dev);
+int moe_dev_upload(moe_engine_t* e, void* dst_dev, const void* src_host, size_t bytes);
+int moe_dev_download(moe_engine_t* e, void* dst_host, const void* src_dev, size_t bytes);
+int moe_dev_memset(moe_engine_t* e, void* dst_dev, int value, size_t bytes);
+int moe_host_alloc_pinned(size_t bytes, void** out_host);
+int moe_host_free_pinned(void* p_host);
+/* CUDA-event timing on the engine's stream: elapsed milliseconds between
+ * moe_timer_start and moe_timer_stop (stop waits for the stream). */
+int moe_timer_start(moe_engine_t* e);
+int moe_timer_stop(moe_engine_t* e, float* ms);
+/* Number of kernels this library has launched on the engine since creation. */
+int moe_launch_count(const moe_engine_t* e, int64_t* n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

@@ -1,0 +1,183 @@
+// Shared declarations of the sm_100a MoE library: engine state, error plumbing,
+// small device helpers.  Internal; the public surface is include/moe_b200.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+constexpr int kGroup = 64;  // weights per scale/bias pair (src/constants.rs GROUP_SIZE)
+constexpr int kMaxK = 8;    // MAX_K (src/engine/qwen35_moe/metal_context.rs:564-577)
+
+// ─── host-side error plumbing ───────────────────────────────────────────────
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t err, const char* what, const char* file, int line);
+
+#define MOE_CUDA(call)                                                            \
+    do {                                                                          \
+        cudaError_t _e = (call);                                                  \
+        if (_e != cudaSuccess) return moe::cuda_fail(_e, #call, __FILE__, __LINE__); \
+    } while (0)
+
+#define MOE_REQUIRE(cond, ...)              \
+    do {                                    \
+        if (!(cond)) {                      \
+            moe::set_error(__VA_ARGS__);    \
+            return MOE_ERR_INVALID;         \
+        }                                   \
+    } while (0)
+
+// One 4-bit tensor on the device: u32 words, bf16 scales, bf16 biases.
+struct Q4Dev {
+    const uint32_t* w = nullptr;
+    const uint16_t* s = nullptr;
+    const uint16_t* b = nullptr;
+};
+
+// Device pointers of one MoE block, passed to kernels by value (in an array in
+// device memory for the persistent decode kernel).
+struct LayerDev {
+    const uint8_t* experts;      // E * expert_size
+    const uint16_t* post_norm;   // bf16 [H]
+    const uint16_t* router_bf16; // bf16 [E, H] or nullptr
+    Q4Dev router_q4;             // INT4-scheme router
+    const uint8_t* shared;       // shared expert in expert-blob layout (hidden, shared_inter)
+    Q4Dev sgate;                 // [1, H]
+};
+
+struct LayerHost {
+    uint8_t* experts = nullptr;
+    uint8_t* aux = nullptr;   // one allocation holding every non-expert tensor
+    bool experts_loaded = false;
+    bool role_loaded[6] = {false, false, false, false, false, false};
+    bool router_is_bf16 = true;
+    LayerDev dev{};
+};
+
+// Work areas of the batched (grouped) path, sized for max_tokens.
+struct BatchWork {
+    int32_t capacity = 0;        // tokens
+    float* h_a = nullptr;        // [cap, H] ping
+    float* h_b = nullptr;        // [cap, H] pong
+    __nv_bfloat16* x = nullptr;  // [cap, H] normalised activations, bf16, K-permuted
+    float* logits = nullptr;     // [cap, E]
+    int32_t* topk_idx = nullptr; // [cap, K]
+    float* topk_w = nullptr;     // [cap, K]
+    float* sgate = nullptr;      // [cap] sigmoid(shared gate score)
+    int32_t* counts = nullptr;   // [E + 1] tokens per expert (+ shared)
+    int32_t* offsets = nullptr;  // [E + 2] exclusive scan
+    int32_t* cursor = nullptr;   // [E + 1]
+    int32_t* slot_token = nullptr; // [cap*K + cap] token of each expert-sorted slot
+    float* slot_w = nullptr;       // [cap*K + cap] combine weight of each slot
+    __nv_bfloat16* act = nullptr;  // [cap*K + cap, I] SwiGLU outputs, expert-sorted
+    int32_t* tile_list = nullptr;  // work list of (expert, token tile)
+    int32_t* n_tiles = nullptr;
+};
+
+}  // namespace moe
+
+struct moe_engine {
+    moe_dims_t dims{};
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    moe_expert_layout_t lay{};         // routed experts
+    moe_expert_layout_t shared_lay{};  // shared expert (hidden, shared_inter)
+    std::vector<moe::LayerHost> layers;  // num_layers + num_mtp_layers
+    moe::LayerDev* layers_dev = nullptr; // device copy of the LayerDev table
+    bool table_dirty = true;
+    size_t resident = 0;
+    int64_t launches = 0;
+
+    // decode (n = 1) work areas
+    float* dec_h[2] = {nullptr, nullptr};  // [H] ping-pong
+    float* dec_logits = nullptr;           // [E]
+    float* dec_act = nullptr;              // [(K + 1), I]
+    float* dec_misc = nullptr;             // [16] sgate score etc.
+    int32_t* dec_idx = nullptr;            // [K]
+    float* dec_w = nullptr;                // [K]
+    unsigned int* dec_sync = nullptr;      // grid barrier words + error flag
+    int dec_grid = 0;
+    float* stage_host = nullptr;           // pinned staging [H] x 2
+    std::vector<float> last_h;             // last_h_pre_norm
+    int64_t mtp_pos = 0;
+
+    moe::BatchWork bw;
+    uint8_t* io_dev = nullptr;  // staging of the host-pointer entry points
+    size_t io_cap = 0;
+
+    // telemetry
+    std::map<std::string, double> telemetry;
+    std::vector<std::string> tel_keys;
+
+    // expert parallelism
+    int ep_rank = 0, ep_world = 1;
+};
+
+namespace moe {
+
+// Kernel launchers implemented in the .cu files; all enqueue on e->stream.
+int launch_pack(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols,
+                int64_t src_row_stride, void* w, void* s, void* b);
+int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, int src_dtype,
+                        int32_t n_experts, void* blob);
+int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
+                  float* y, int32_t rows, int32_t cols);
+int decode_init(moe_engine* e);
+void decode_destroy(moe_engine* e);
+// Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
+int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
+                  const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);
+int batch_reserve(moe_engine* e, int32_t n_tokens);
+void batch_destroy(moe_engine* e);
+int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_out,
+                         const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx,
+                         float* out_w);
+int refresh_layer_table(moe_engine* e);
+int check_layer_ready(moe_engine* e, int layer);
+
+#ifdef __CUDACC__
+// ─── device helpers ─────────────────────────────────────────────────────────
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t v) {
+    return __uint_as_float(((uint32_t)v) << 16);
+}
+
+// The reference's f32 -> bf16 (src/dtype.rs:85-89): round_up = bit15 & (bit0 | bit16).
+// Not round-to-nearest-even; reproduced bit for bit.
+__device__ __forceinline__ uint16_t f32_to_bf16_ref(float v) {
+    uint32_t bits = __float_as_uint(v);
+    uint32_t round_up = ((bits >> 15) & 1u) & ((bits & 0x7FFFu) | ((bits >> 16) & 1u));
+    return (uint16_t)((bits + (round_up << 16)) >> 16);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 128-bit read-only streaming load (weights are read once per token).
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+#endif
+
+}  // namespace moe

@@ -1,0 +1,110 @@
+// Stand-alone 4-bit dequant-matvec: y[r] = sum_c (nib*scale + bias) * x[c].
+//
+// Replaces dequant_matvec_4bit (reference src/math_util.rs:14-54) and the Metal
+// kernel family dequant_matvec_4bit_* (reference src/engine/shaders.metal:74-3409).
+// HBM-bound: 0.5625 B of weights per multiply-add.  One warp per output row; each
+// lane issues 128-bit loads of 32 nibbles (half a group), dequantises in
+// registers and reduces with warp shuffles.  x is staged into shared memory
+// with one bulk (TMA) copy, then re-laid out chunk-transposed (see q4dot.cuh)
+// together with the per-chunk sums the affine dequant needs.
+#include "q4dot.cuh"
+#include "stage.cuh"
+
+namespace moe {
+
+constexpr int kMvWarps = 8;
+
+__global__ void __launch_bounds__(kMvWarps * 32)
+matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s,
+                   const uint16_t* __restrict__ b, const float* __restrict__ x,
+                   float* __restrict__ y, int rows, int cols, unsigned int* err_flag) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int nch = cols / 32;  // chunks per row
+    float* raw = reinterpret_cast<float*>(smem_raw);                 // [cols]
+    float4* xs = reinterpret_cast<float4*>(smem_raw + (size_t)cols * 4);  // [8][nch]
+    float* sumx = reinterpret_cast<float*>(smem_raw + (size_t)cols * 8);  // [nch]
+    __shared__ uint64_t bar;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        mbar_expect_tx(&bar, (uint32_t)cols * 4u);
+        bulk_g2s(raw, x, (uint32_t)cols * 4u, &bar);
+    }
+    // every thread observes the phase itself, so the copied bytes are visible to it
+    const int ok = __syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0);
+    if (!ok) {
+        if (tid == 0) atomicExch(err_flag, 1u);
+        return;
+    }
+    // chunk-transposed copy + per-chunk sums
+    for (int c = tid; c < nch; c += blockDim.x) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 v = reinterpret_cast<const float4*>(raw)[c * 8 + j];
+            xs[j * nch + c] = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+        sumx[c] = sum;
+    }
+    __syncthreads();
+
+    const int groups = cols / kGroup;
+    for (int row = blockIdx.x * kMvWarps + warp; row < rows; row += gridDim.x * kMvWarps) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (cols / 8));
+        const uint16_t* srow = s + (size_t)row * groups;
+        const uint16_t* brow = b + (size_t)row * groups;
+        float acc = 0.0f;
+        for (int c0 = 0; c0 < nch; c0 += 64) {
+            // two chunks per lane in flight
+            const int ca = c0 + lane, cb = c0 + 32 + lane;
+            const bool va = ca < nch, vb = cb < nch;
+            uint4 qa = make_uint4(0, 0, 0, 0), qb = qa;
+            uint16_t sa = 0, ba = 0, sb = 0, bb = 0;
+            if (va) { qa = ld_stream_u4(wrow + ca); sa = srow[ca >> 1]; ba = brow[ca >> 1]; }
+            if (vb) { qb = ld_stream_u4(wrow + cb); sb = srow[cb >> 1]; bb = brow[cb >> 1]; }
+            if (va) {
+                float4 xv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xv[j] = xs[j * nch + ca];
+                acc += chunk_term(qa, xv, sumx[ca], sa, ba);
+            }
+            if (vb) {
+                float4 xv[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) xv[j] = xs[j * nch + cb];
+                acc += chunk_term(qb, xv, sumx[cb], sb, bb);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = acc;
+    }
+}
+
+int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
+                  float* y, int32_t rows, int32_t cols) {
+    MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
+    MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
+    MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
+    const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
+    static bool attr_set = false;
+    if (!attr_set) {
+        MOE_CUDA(cudaFuncSetAttribute(matvec_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8 + 2048));
+        attr_set = true;
+    }
+    int blocks = (rows + kMvWarps - 1) / kMvWarps;
+    const int cap = e->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    matvec_int4_kernel<<<blocks, kMvWarps * 32, smem, e->stream>>>(
+        (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2);
+    e->launches++;
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
+}  // namespace moe

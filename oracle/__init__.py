@@ -1,0 +1,262 @@
+"""ctypes front end of the CPU oracle (``moe_oracle.c``).  TEST INFRASTRUCTURE ONLY.
+
+Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark
+may import this package; the product (``moe_infer_b200``) never does.
+
+Parity status: bf16 rounding, dequantiser and blob layout are pinned against the
+reference's own Python by the fixtures in ``tests/golden``; the packed nibbles of
+``quant_int4`` are pinned by source text only (the reference ships no
+known-answer vector for them).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libmoe_oracle.so")
+GROUP = 64
+
+
+def build(force: bool = False) -> str:
+    """Compile ``moe_oracle.c`` with gcc (see the Makefile) and return the .so path."""
+    src = os.path.join(_HERE, "moe_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "libmoe_oracle.so"])
+    return _SO
+
+
+_lib = None
+
+
+class _Layout(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in
+                ("gate_w", "gate_s", "gate_b", "up_w", "up_s", "up_b",
+                 "down_w", "down_s", "down_b", "expert_size")]
+
+
+class _Dims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "inter", "shared_inter", "num_experts", "top_k")]
+
+
+class _Q4(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("s", C.c_void_p), ("b", C.c_void_p)]
+
+
+class _Layer(C.Structure):
+    _fields_ = [("post_norm_w", C.c_void_p), ("router_bf16", C.c_void_p), ("router_q4", _Q4),
+                ("sh_gate", _Q4), ("sh_up", _Q4), ("sh_down", _Q4), ("sgate", _Q4),
+                ("experts", C.c_void_p)]
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.orc_f32_to_bf16.restype = C.c_uint16
+        _lib.orc_f32_to_bf16.argtypes = [C.c_float]
+        _lib.orc_sigmoid.restype = C.c_float
+        _lib.orc_sigmoid.argtypes = [C.c_float]
+        _lib.orc_num_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dtype):
+    a = np.ascontiguousarray(a, dtype=dtype)
+    return a
+
+
+# ─── bf16 ────────────────────────────────────────────────────────────────────
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().orc_f32_to_bf16_n(_p(x), _p(out), C.c_size_t(x.size))
+    return out
+
+
+def bf16_to_f32(x: np.ndarray) -> np.ndarray:
+    x = _c(x, np.uint16)
+    return (x.astype(np.uint32) << 16).view(np.float32)
+
+
+# ─── codec ───────────────────────────────────────────────────────────────────
+
+def quant_int4(vals: np.ndarray) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """f32 [out, in] -> (u32 [out, in/8], bf16 scales [out, in/64], bf16 biases)."""
+    vals = _c(vals, np.float32)
+    out_dim, in_dim = vals.shape
+    assert in_dim % GROUP == 0
+    w = np.empty((out_dim, in_dim // 8), np.uint32)
+    s = np.empty((out_dim, in_dim // GROUP), np.uint16)
+    b = np.empty((out_dim, in_dim // GROUP), np.uint16)
+    lib().orc_quant_int4(_p(vals), out_dim, in_dim, _p(w), _p(s), _p(b))
+    return w, s, b
+
+
+def quant_int4_bf16(vals_u16: np.ndarray):
+    """bf16 bit patterns [out, in] widened exactly to f32, then ``quant_int4``."""
+    return quant_int4(bf16_to_f32(vals_u16))
+
+
+def dequant_int4(w, s, b) -> np.ndarray:
+    w = _c(w, np.uint32)
+    s = _c(s, np.uint16)
+    b = _c(b, np.uint16)
+    out_dim, wpr = w.shape
+    in_dim = wpr * 8
+    out = np.empty((out_dim, in_dim), np.float32)
+    lib().orc_dequant_int4(_p(w), _p(s), _p(b), out_dim, in_dim, _p(out))
+    return out
+
+
+def expert_layout(hd: int, mi: int, gs: int = GROUP) -> dict:
+    L = _Layout()
+    lib().orc_expert_layout(hd, mi, gs, C.byref(L))
+    return {n: getattr(L, n) for n, _ in _Layout._fields_}
+
+
+def pack_experts_layer(gate_up: np.ndarray, down: np.ndarray) -> np.ndarray:
+    """gate_up f32 [E, 2I, H], down f32 [E, H, I] -> uint8 blob [E * expert_size]."""
+    gate_up = _c(gate_up, np.float32)
+    down = _c(down, np.float32)
+    E, two_i, H = gate_up.shape
+    inter = two_i // 2
+    assert down.shape == (E, H, inter)
+    size = expert_layout(H, inter)["expert_size"]
+    blob = np.empty(E * size, np.uint8)
+    lib().orc_pack_experts_layer(_p(gate_up), _p(down), E, inter, H, _p(blob))
+    return blob
+
+
+# ─── matvec and small math ───────────────────────────────────────────────────
+
+def matvec_int4(w, s, b, x, threads: int = 1) -> np.ndarray:
+    w = _c(w, np.uint32)
+    s = _c(s, np.uint16)
+    b = _c(b, np.uint16)
+    x = _c(x, np.float32)
+    out_dim, wpr = w.shape
+    out = np.empty(out_dim, np.float32)
+    fn = lib().orc_matvec_int4_mt if threads > 1 else lib().orc_matvec_int4
+    fn(_p(w), _p(s), _p(b), _p(x), _p(out), out_dim, wpr * 8)
+    return out
+
+
+def matvec_bf16(w_u16, x) -> np.ndarray:
+    w_u16 = _c(w_u16, np.uint16)
+    x = _c(x, np.float32)
+    out = np.empty(w_u16.shape[0], np.float32)
+    lib().orc_matvec_bf16(_p(w_u16), _p(x), _p(out), w_u16.shape[0], w_u16.shape[1])
+    return out
+
+
+def route_experts(scores: np.ndarray, k: int):
+    """Returns (indices int32 [k] in heap order, weights f32 [k], probabilities [E])."""
+    probs = _c(scores, np.float32).copy()
+    idx = np.zeros(k, np.int32)
+    wts = np.zeros(k, np.float32)
+    lib().orc_route_experts(_p(probs), probs.size, k, _p(idx), _p(wts))
+    return idx, wts, probs
+
+
+def swiglu(gate, up) -> np.ndarray:
+    gate = _c(gate, np.float32)
+    up = _c(up, np.float32)
+    out = np.empty_like(gate)
+    lib().orc_swiglu(_p(gate), _p(up), _p(out), gate.size)
+    return out
+
+
+def rms_norm_bf16(x, w_u16, eps: float = 1e-6) -> np.ndarray:
+    x = _c(x, np.float32)
+    w_u16 = _c(w_u16, np.uint16)
+    out = np.empty_like(x)
+    lib().orc_rms_norm_bf16(_p(x), _p(w_u16), _p(out), x.size, C.c_float(eps))
+    return out
+
+
+def sigmoid(x: float) -> float:
+    return float(lib().orc_sigmoid(C.c_float(x)))
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+# ─── one MoE block ───────────────────────────────────────────────────────────
+
+Q4 = Tuple[np.ndarray, np.ndarray, np.ndarray]
+
+
+@dataclass
+class LayerWeights:
+    """Host copy of one MoE block's tensors in the reference's byte layout."""
+    hidden: int
+    inter: int
+    shared_inter: int
+    num_experts: int
+    post_norm_w: np.ndarray            # bf16 bits [H]
+    router_bf16: Optional[np.ndarray]  # bf16 bits [E, H] (BQ4 scheme) or None
+    router_q4: Optional[Q4]            # INT4 scheme
+    sh_gate: Q4
+    sh_up: Q4
+    sh_down: Q4
+    sgate: Q4
+    experts: np.ndarray                # uint8 [E * expert_size]
+
+
+def _q4(t: Optional[Q4]) -> _Q4:
+    if t is None:
+        return _Q4(None, None, None)
+    return _Q4(_p(t[0]), _p(t[1]), _p(t[2]))
+
+
+def moe_layer(lw: LayerWeights, h_mid: np.ndarray, top_k: int, *, logit_bias=None,
+              forced_idx=None, threads: int = 1):
+    """h_mid f32 [n, H] -> (h_out [n, H], idx int32 [n, k] heap order, weights f32 [n, k])."""
+    h_mid = _c(h_mid, np.float32).reshape(-1, lw.hidden)
+    n = h_mid.shape[0]
+    d = _Dims(lw.hidden, lw.inter, lw.shared_inter, lw.num_experts, top_k)
+    ly = _Layer(_p(lw.post_norm_w), _p(lw.router_bf16), _q4(lw.router_q4), _q4(lw.sh_gate),
+                _q4(lw.sh_up), _q4(lw.sh_down), _q4(lw.sgate), _p(lw.experts))
+    h_out = np.empty_like(h_mid)
+    idx = np.empty((n, top_k), np.int32)
+    wts = np.empty((n, top_k), np.float32)
+    lb = None if logit_bias is None else _c(logit_bias, np.float32)
+    fi = None if forced_idx is None else _c(forced_idx, np.int32)
+    lib().orc_moe_layer(C.byref(d), C.byref(ly), _p(h_mid), n, _p(h_out), _p(idx), _p(wts),
+                        _p(lb), _p(fi), threads)
+    return h_out, idx, wts
+
+
+def moe_layer_decode_mt(lw: LayerWeights, h_mid: np.ndarray, top_k: int):
+    """One token, matvec rows split over all OpenMP threads; same result as ``moe_layer``."""
+    h_mid = _c(h_mid, np.float32).reshape(lw.hidden)
+    d = _Dims(lw.hidden, lw.inter, lw.shared_inter, lw.num_experts, top_k)
+    ly = _Layer(_p(lw.post_norm_w), _p(lw.router_bf16), _q4(lw.router_q4), _q4(lw.sh_gate),
+                _q4(lw.sh_up), _q4(lw.sh_down), _q4(lw.sgate), _p(lw.experts))
+    h_out = np.empty_like(h_mid)
+    idx = np.empty(top_k, np.int32)
+    wts = np.empty(top_k, np.float32)
+    lib().orc_moe_layer_decode_mt(C.byref(d), C.byref(ly), _p(h_mid), _p(h_out), _p(idx), _p(wts))
+    return h_out, idx, wts
+
+
+def moe_stack(layers, h: np.ndarray, top_k: int, threads: int = 1) -> np.ndarray:
+    """Residual stack with attention omitted: h <- moe_layer_l(h) for each layer."""
+    h = _c(h, np.float32).reshape(-1, layers[0].hidden)
+    for lw in layers:
+        h, _, _ = moe_layer(lw, h, top_k, threads=threads)
+    return h
