@@ -205,6 +205,17 @@ void moe_set_record_telemetry(int on);
 int moe_get_record_telemetry(void);
 int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n);
 
+/* Fine-grained phase timing of the decode kernel, the device-side counterpart of
+ * the reference's `phase.*` telemetry (src/engine/qwen35_moe/fused_exp5.rs:162-177).
+ * With stamps == NULL: switches recording on (enable != 0) or off.  Otherwise
+ * copies the SM-clock stamps of the last decode launch, [layer][*points_per_layer],
+ * taken by CTA 0 at: layer start, norm staged and phase-A weights landed, router
+ * and shared rows done, barrier 1 passed, next layer's phase-A copies issued,
+ * top-k done, gate/up/down copies issued, gate/up weights landed, gate/up rows
+ * done, barrier 2 passed, activations staged and down weights landed, down rows
+ * and combine done. */
+int moe_decode_profile(moe_engine_t* e, int enable, int64_t* stamps, int max_layers, int* points_per_layer);
+
 /* ── expert parallelism over the GPUs of one box ─────────────────────────────
  * No counterpart in the reference (single device).  Rank r keeps experts
  * [r*E/P, (r+1)*E/P) of every layer.  Peers exchange token rows through

@@ -70,6 +70,7 @@ SIGNATURES = {
     "moe_set_record_telemetry": (None, [_i]),
     "moe_get_record_telemetry": (_i, []),
     "moe_telemetry_get": (_i, [_vp, C.POINTER(C.c_char_p), C.POINTER(C.c_double), C.POINTER(_i)]),
+    "moe_decode_profile": (_i, [_vp, _i, C.POINTER(_i64), _i, C.POINTER(_i)]),
     "moe_ep_export": (_i, [_vp, _i32, _vp]),
     "moe_ep_init": (_i, [_vp, _i, _i, _vp]),
     "moe_ep_finalize": (_i, [_vp]),

@@ -106,6 +106,7 @@ struct moe_engine {
     int32_t* dec_idx = nullptr;            // [K]
     float* dec_w = nullptr;                // [K]
     unsigned int* dec_sync = nullptr;      // grid barrier words + error flag
+    long long* dec_prof = nullptr;         // per-phase clock stamps (off unless enabled)
     int dec_grid = 0;
     float* stage_host = nullptr;           // pinned staging [H] x 2
     std::vector<float> last_h;             // last_h_pre_norm
@@ -137,6 +138,8 @@ void decode_destroy(moe_engine* e);
 // Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
                   const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);
+int decode_profile_enable(moe_engine* e, bool on);
+int decode_profile_read(moe_engine* e, long long* out, int max_layers, int* points);
 int batch_reserve(moe_engine* e, int32_t n_tokens);
 void batch_destroy(moe_engine* e);
 int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_out,

@@ -1,6 +1,8 @@
 // Batch-1 decode of the MoE stack: one persistent cooperative kernel walks the
-// layers, three grid-wide phases per layer, weights streamed from the resident
-// HBM store with 128-bit loads and dequantised in registers.
+// layers; every CTA owns a fixed, contiguous slice of each weight matrix and
+// pulls it from the resident HBM store into shared memory with bulk (TMA)
+// copies issued as early as the data dependencies allow; nibbles are
+// dequantised in registers and reduced with warp shuffles.
 //
 // Replaces, per layer, the tail of op1 (post-attention norm, router matvec,
 // shared-expert gate/up, shared_expert_gate), the CPU route_experts round trip and
@@ -12,15 +14,19 @@
 // the device.
 //
 //   phase A  x = rmsnorm(h) (every CTA, redundantly); router logits, shared
-//            expert gate/up + SwiGLU, shared gate score          [~2.2 MB]
-//   phase B  softmax + top-k (every CTA, redundantly, one warp); gate/up/SwiGLU
-//            of the K chosen experts                               [~9.4 MB]
+//            expert gate/up + SwiGLU, shared gate score            [~2.2 MB]
+//            -- does not depend on routing: its weights are requested one
+//               layer ahead
+//   phase B  softmax + top-k (every CTA, redundantly); gate/up/SwiGLU of the K
+//            chosen experts                                         [~9.4 MB]
 //   phase C  down projections of the K experts and the shared expert, combine
-//            with the residual: one warp owns one output element   [~5.3 MB]
+//            with the residual: one warp owns one output element    [~5.3 MB]
+//            -- requested together with phase B's weights, right after top-k
 //
 // HBM-bound: 16,974,976 weight bytes per layer-token at the reference sizes.
 // Between phases the CTAs meet at a grid barrier built on one global counter;
-// the wait is bounded and a timeout raises an error word instead of hanging.
+// every wait (barrier, mbarrier) is bounded and a timeout raises an error word
+// instead of hanging.
 #include "q4dot.cuh"
 #include "stage.cuh"
 
@@ -30,9 +36,21 @@ constexpr int kH = 2048;        // hidden (both reference models)
 constexpr int kI = 512;         // moe_intermediate_size == shared_expert_intermediate_size
 constexpr int kDecWarps = 16;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kChH = kH / 32;   // 64 chunks per hidden row
+constexpr int kChH = kH / 32;   // 64 chunks (128-bit loads) per hidden row
 constexpr int kChI = kI / 32;   // 16 chunks per intermediate row
-constexpr int kMaxEPerLane = 16;  // top-k supports E <= 512
+constexpr int kMaxE = 512;      // routing supports up to 512 experts
+constexpr int kProfPoints = 12;
+
+// Per-CTA slice capacities; the host checks that the grid is large enough.
+constexpr int kMaxRouterRows = 4;   // ceil(E / grid)
+constexpr int kMaxSharedRows = 4;   // ceil(I / grid) gate/up row pairs of the shared expert
+constexpr int kMaxBItems = 28;      // ceil(K * I / grid) gate/up row pairs of routed experts
+constexpr int kMaxCRows = 14;       // ceil(H / grid) output elements
+
+#define PROF(idx)                                                                                  \
+    do {                                                                                           \
+        if (p.prof && cta == 0 && tid == 0) p.prof[(l - p.l0) * kProfPoints + (idx)] = clock64();  \
+    } while (0)
 
 struct DecodeParams {
     const LayerDev* layers;
@@ -49,23 +67,51 @@ struct DecodeParams {
     int32_t* out_idx;
     float* out_w;
     unsigned int* sync; // [0] arrivals, [1] exits, [2] error word
+    long long* prof;    // nullable: [layer][kProfPoints] SM-clock stamps taken by CTA 0
     int E, K;
     moe_expert_layout_t lay;
 };
 
-struct __align__(16) DecodeSmem {
+struct __align__(128) DecodeSmem {
+    // prefetched weight slices (destinations of bulk copies: 16-byte aligned offsets)
+    uint4 a_router[kMaxRouterRows * (kH * 2 / 16)];      // bf16 rows (4096 B each) or 4-bit rows (1024 B each)
+    uint4 a_shw[2][kMaxSharedRows][kChH];                // shared expert gate / up rows
+    uint4 a_sgw[kChH];                                   // shared_expert_gate row
+    uint4 b_w[2][kMaxBItems][kChH];                      // routed gate / up rows
+    uint4 c_w[kMaxK + 1][kMaxCRows][kChI];               // down rows of the K experts + shared expert
+    uint16_t a_router_s[kMaxRouterRows][kH / kGroup];
+    uint16_t a_router_b[kMaxRouterRows][kH / kGroup];
+    uint16_t a_shs[2][kMaxSharedRows][kH / kGroup];
+    uint16_t a_shb[2][kMaxSharedRows][kH / kGroup];
+    uint16_t a_sgs[kH / kGroup];
+    uint16_t a_sgb[kH / kGroup];
+    uint16_t b_s[2][kMaxBItems][kH / kGroup];
+    uint16_t b_b[2][kMaxBItems][kH / kGroup];
+    uint16_t c_s[kMaxK + 1][kMaxCRows][kI / kGroup];
+    uint16_t c_b[kMaxK + 1][kMaxCRows][kI / kGroup];
+    // activations
     float raw[kH];              // bulk-copy landing zone for h
     float xn[kH];               // normalised x, plain order (bf16 router rows)
     float4 xs[8 * kChH];        // normalised x, chunk-transposed
     float sumx[kChH];
     float4 acts[(kMaxK + 1) * 8 * kChI];  // SwiGLU outputs, chunk-transposed per expert
     float suma[(kMaxK + 1) * kChI];
+    float prob[kMaxE];
     float red[kDecWarps];
+    float red2[kDecWarps];
+    float cand_p[kMaxE];
+    int cand_i[kMaxE];
+    int ncand;
     float topw[kMaxK + 1];      // combine weights; [K] = sigmoid(shared gate)
+    float topp[kMaxK];
     int topi[kMaxK];
     int flag;
-    uint64_t bar;
+    uint64_t bar_h;
 };
+static_assert(sizeof(DecodeSmem) <= 227 * 1024, "decode staging exceeds shared memory");
+static_assert((sizeof(uint16_t) * (kMaxK + 1) * kMaxCRows * (kI / kGroup)) % 16 == 0, "bulk-copy destinations stay aligned");
+
+__device__ __forceinline__ int slice_lo(int c, int n, int G) { return (int)(((long long)c * n) / G); }
 
 // ─── grid barrier with a bounded wait ───────────────────────────────────────
 // Arrivals are counted on one monotonically increasing word; `target` is the
@@ -76,17 +122,18 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* sync, unsigned int ta
     asm volatile("fence.proxy.async;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(&sync[0], 1u);
+        // release: publishes this CTA's writes (ordered before it by the bar.sync above)
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(sync), "r"(1u) : "memory");
         int ok = 0;
-        for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        const long long t0 = clock64();
+        for (uint32_t i = 0;; ++i) {
             unsigned int v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sync) : "memory");
             if (v >= target) { ok = 1; break; }
-            if ((i & 255u) == 255u) {
+            if ((i & 63u) == 63u) {
                 unsigned int err;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(err) : "l"(sync + 2) : "memory");
-                if (err) break;
+                if (err || clock64() - t0 > kWaitCycles) break;
             }
         }
         if (!ok) atomicExch(&sync[2], 2u);
@@ -97,16 +144,120 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* sync, unsigned int ta
     return sm->flag != 0;
 }
 
+// ─── weight prefetch with per-thread 16-byte asynchronous copies ─────────────
+// Every thread of the CTA copies pieces p = tid, tid + 512, ... of a slice;
+// completion is tracked with cp.async groups (one group per slice), then a CTA
+// barrier makes the bytes visible to every warp.
+__device__ __forceinline__ void cp16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void copy_flat(void* dst, const void* src, int pieces, int tid) {
+    for (int q = tid; q < pieces; q += kDecThreads)
+        cp16(reinterpret_cast<uint8_t*>(dst) + (size_t)q * 16, reinterpret_cast<const uint8_t*>(src) + (size_t)q * 16);
+}
+
+// phase A slice: router rows [e0, e0+ne), shared gate/up pairs [p0, p0+np), shared gate (last CTA)
+__device__ __forceinline__ void prefetch_A(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& S,
+                                           int cta, int G, int E, int tid) {
+    const int e0 = slice_lo(cta, E, G), ne = slice_lo(cta + 1, E, G) - e0;
+    const int p0 = slice_lo(cta, kI, G), np = slice_lo(cta + 1, kI, G) - p0;
+    constexpr int kRowW = kH / 2, kRowS = (kH / kGroup) * 2;  // bytes of one 4-bit row / of its scales
+    if (ly.router_bf16) {
+        copy_flat(sm->a_router, ly.router_bf16 + (size_t)e0 * kH, ne * (kH * 2 / 16), tid);
+    } else {
+        copy_flat(sm->a_router, ly.router_q4.w + (size_t)e0 * (kH / 8), ne * (kRowW / 16), tid);
+        copy_flat(sm->a_router_s, ly.router_q4.s + (size_t)e0 * (kH / kGroup), ne * (kRowS / 16), tid);
+        copy_flat(sm->a_router_b, ly.router_q4.b + (size_t)e0 * (kH / kGroup), ne * (kRowS / 16), tid);
+    }
+    const uint8_t* sh = ly.shared;
+    copy_flat(sm->a_shw[0], sh + S.gate_w + (size_t)p0 * kRowW, np * (kRowW / 16), tid);
+    copy_flat(sm->a_shw[1], sh + S.up_w + (size_t)p0 * kRowW, np * (kRowW / 16), tid);
+    // the four small arrays: one piece per thread at most
+    {
+        const int per = np * (kRowS / 16);
+        if (tid < 4 * per) {
+            const int a = tid / per, q = tid - a * per;
+            const int64_t off = a == 0 ? S.gate_s : a == 1 ? S.up_s : a == 2 ? S.gate_b : S.up_b;
+            uint16_t* d = a == 0 ? sm->a_shs[0][0] : a == 1 ? sm->a_shs[1][0] : a == 2 ? sm->a_shb[0][0] : sm->a_shb[1][0];
+            cp16(reinterpret_cast<uint8_t*>(d) + q * 16, sh + off + (size_t)p0 * kRowS + q * 16);
+        }
+    }
+    if (cta == G - 1) {
+        copy_flat(sm->a_sgw, ly.sgate.w, kRowW / 16, tid);
+        if (tid < kRowS / 16) cp16(reinterpret_cast<uint8_t*>(sm->a_sgs) + tid * 16, reinterpret_cast<const uint8_t*>(ly.sgate.s) + tid * 16);
+        else if (tid < 2 * (kRowS / 16))
+            cp16(reinterpret_cast<uint8_t*>(sm->a_sgb) + (tid - kRowS / 16) * 16,
+                 reinterpret_cast<const uint8_t*>(ly.sgate.b) + (tid - kRowS / 16) * 16);
+    }
+    cp_commit();
+}
+
+// phase B slice: items (slot k, row r) flattened as k * I + r, this CTA owns [i0, i0 + nb)
+__device__ __forceinline__ void prefetch_B(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                           int i0, int nb, int tid) {
+    constexpr int kPW = kH / 2 / 16, kPS = (kH / kGroup) * 2 / 16;  // 16-byte pieces per row: 64 weights, 4 scales
+    // weights: piece -> (m, j, c)
+    const int pw = 2 * nb * kPW;
+    for (int q = tid; q < pw; q += kDecThreads) {
+        const int m = q >= nb * kPW;
+        const int rem = q - m * nb * kPW;
+        const int j = rem / kPW, c = rem % kPW;
+        const int i = i0 + j, k = i / kI, r = i - k * kI;
+        const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
+        cp16(&sm->b_w[m][j][c], ex + (m ? L.up_w : L.gate_w) + (size_t)r * (kH / 2) + c * 16);
+    }
+    // scales and biases: piece -> (a in {gate_s, up_s, gate_b, up_b}, j, c)
+    const int ps = 4 * nb * kPS;
+    for (int q = tid; q < ps; q += kDecThreads) {
+        const int a = q / (nb * kPS);
+        const int rem = q - a * nb * kPS;
+        const int j = rem / kPS, c = rem % kPS;
+        const int i = i0 + j, k = i / kI, r = i - k * kI;
+        const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
+        const int64_t off = a == 0 ? L.gate_s : a == 1 ? L.up_s : a == 2 ? L.gate_b : L.up_b;
+        uint16_t* d = a == 0 ? sm->b_s[0][j] : a == 1 ? sm->b_s[1][j] : a == 2 ? sm->b_b[0][j] : sm->b_b[1][j];
+        cp16(reinterpret_cast<uint8_t*>(d) + c * 16, ex + off + (size_t)r * (kH / kGroup) * 2 + c * 16);
+    }
+    cp_commit();
+}
+
+// phase C slice: down rows [r0, r0 + nc) of the K chosen experts and the shared expert
+__device__ __forceinline__ void prefetch_C(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                           int r0, int nc, int K, int tid) {
+    constexpr int kPW = kI / 2 / 16;  // 16 pieces per row; scales and biases are one piece per row
+    const int per_w = nc * kPW;
+    const int pw = (K + 1) * per_w;
+    for (int q = tid; q < pw; q += kDecThreads) {
+        const int m = q / per_w, rem = q - m * per_w;
+        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+        cp16(reinterpret_cast<uint8_t*>(sm->c_w[m]) + rem * 16, ex + L.down_w + (size_t)r0 * (kI / 2) + rem * 16);
+    }
+    const int ps = (K + 1) * 2 * nc;
+    for (int q = tid; q < ps; q += kDecThreads) {
+        const int m = q / (2 * nc), rem = q - m * 2 * nc;
+        const int a = rem >= nc, j = rem - a * nc;
+        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+        uint16_t* d = a ? sm->c_b[m][j] : sm->c_s[m][j];
+        cp16(d, ex + (a ? L.down_b : L.down_s) + (size_t)(r0 + j) * (kI / kGroup) * 2);
+    }
+    cp_commit();
+}
+
 // ─── x = rmsnorm(h) * w, staged three ways (plain, chunk-transposed, chunk sums) ──
 // rms_norm_bf16 (reference src/math_util.rs:282-288), eps 1e-6.
 __device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const uint16_t* norm_w,
                                            uint32_t parity) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        mbar_expect_tx(&sm->bar, kH * 4u);
-        bulk_g2s(sm->raw, h, kH * 4u, &sm->bar);
+        mbar_expect_tx(&sm->bar_h, kH * 4u);
+        bulk_g2s(sm->raw, h, kH * 4u, &sm->bar_h);
     }
-    if (!__syncthreads_and(mbar_wait(&sm->bar, parity) ? 1 : 0)) return false;
+    const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + tid);  // 4 bf16, in flight during the wait
+    if (!__syncthreads_and(mbar_wait(&sm->bar_h, parity) ? 1 : 0)) return false;
     static_assert(kH == kDecThreads * 4, "one float4 per thread");
     const float4 v = reinterpret_cast<const float4*>(sm->raw)[tid];
     float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
@@ -116,7 +267,6 @@ __device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const
 #pragma unroll
     for (int i = 0; i < kDecWarps; ++i) tot += sm->red[i];
     const float inv_rms = 1.0f / sqrtf(tot / (float)kH + 1e-6f);
-    const uint2 wb = reinterpret_cast<const uint2*>(norm_w)[tid];  // 4 bf16
     float4 o;
     o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
     o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
@@ -134,24 +284,11 @@ __device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const
     return true;
 }
 
-// Dot products of NR 4-bit rows of length kH with the staged x.  All loads are
-// issued before the first use so that NR*2 128-bit loads per lane are in flight.
+// Dot products of NR 4-bit rows of length kH (staged in shared memory) with the staged x.
 template <int NR>
-__device__ __forceinline__ void rows_dot_h(const DecodeSmem* sm, const uint32_t* const (&w)[NR],
-                                           const uint16_t* const (&s)[NR],
-                                           const uint16_t* const (&b)[NR], float (&out)[NR], int lane) {
-    uint4 q[NR][2];
-    uint16_t sc[NR][2], bi[NR][2];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-#pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const int c = lane + 32 * it;
-            q[r][it] = ld_stream_u4(reinterpret_cast<const uint4*>(w[r]) + c);
-            sc[r][it] = __ldg(s[r] + (c >> 1));
-            bi[r][it] = __ldg(b[r] + (c >> 1));
-        }
-    }
+__device__ __forceinline__ void rows_dot_h(const DecodeSmem* sm, const uint4* const (&w)[NR],
+                                           const uint16_t* const (&s)[NR], const uint16_t* const (&b)[NR],
+                                           float (&out)[NR], int lane) {
 #pragma unroll
     for (int r = 0; r < NR; ++r) out[r] = 0.0f;
 #pragma unroll
@@ -162,33 +299,30 @@ __device__ __forceinline__ void rows_dot_h(const DecodeSmem* sm, const uint32_t*
         for (int j = 0; j < 8; ++j) xv[j] = sm->xs[j * kChH + c];
         const float sx = sm->sumx[c];
 #pragma unroll
-        for (int r = 0; r < NR; ++r) out[r] += chunk_term(q[r][it], xv, sx, sc[r][it], bi[r][it]);
+        for (int r = 0; r < NR; ++r) out[r] += chunk_term(w[r][c], xv, sx, s[r][c >> 1], b[r][c >> 1]);
     }
 #pragma unroll
     for (int r = 0; r < NR; ++r) out[r] = warp_sum(out[r]);
 }
 
 // One bf16 row of length kH (BQ4-scheme router; reference matvec_bf16,
-// src/engine/shaders.metal:2392).
-__device__ __forceinline__ float row_dot_bf16(const DecodeSmem* sm, const uint16_t* wrow, int lane) {
-    uint4 q[kH / 8 / 32];
-#pragma unroll
-    for (int it = 0; it < kH / 256; ++it)
-        q[it] = ld_stream_u4(reinterpret_cast<const uint4*>(wrow) + lane + 32 * it);
+// src/engine/shaders.metal:2392), the row staged in shared memory.
+__device__ __forceinline__ float row_dot_bf16(const DecodeSmem* sm, const uint4* wrow, int lane) {
     float acc = 0.0f;
 #pragma unroll
     for (int it = 0; it < kH / 256; ++it) {
+        const uint4 q = wrow[lane + 32 * it];
         const int base = (lane + 32 * it) * 8;
         const float4 x0 = *reinterpret_cast<const float4*>(sm->xn + base);
         const float4 x1 = *reinterpret_cast<const float4*>(sm->xn + base + 4);
-        acc = fmaf(__uint_as_float(q[it].x << 16), x0.x, acc);
-        acc = fmaf(__uint_as_float(q[it].x & 0xFFFF0000u), x0.y, acc);
-        acc = fmaf(__uint_as_float(q[it].y << 16), x0.z, acc);
-        acc = fmaf(__uint_as_float(q[it].y & 0xFFFF0000u), x0.w, acc);
-        acc = fmaf(__uint_as_float(q[it].z << 16), x1.x, acc);
-        acc = fmaf(__uint_as_float(q[it].z & 0xFFFF0000u), x1.y, acc);
-        acc = fmaf(__uint_as_float(q[it].w << 16), x1.z, acc);
-        acc = fmaf(__uint_as_float(q[it].w & 0xFFFF0000u), x1.w, acc);
+        acc = fmaf(__uint_as_float(q.x << 16), x0.x, acc);
+        acc = fmaf(__uint_as_float(q.x & 0xFFFF0000u), x0.y, acc);
+        acc = fmaf(__uint_as_float(q.y << 16), x0.z, acc);
+        acc = fmaf(__uint_as_float(q.y & 0xFFFF0000u), x0.w, acc);
+        acc = fmaf(__uint_as_float(q.z << 16), x1.x, acc);
+        acc = fmaf(__uint_as_float(q.z & 0xFFFF0000u), x1.y, acc);
+        acc = fmaf(__uint_as_float(q.w << 16), x1.z, acc);
+        acc = fmaf(__uint_as_float(q.w & 0xFFFF0000u), x1.w, acc);
     }
     return warp_sum(acc);
 }
@@ -196,77 +330,91 @@ __device__ __forceinline__ float row_dot_bf16(const DecodeSmem* sm, const uint16
 // swiglu_fused (reference src/math_util.rs:254-259): silu(gate) * up.
 __device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
-// ─── softmax + top-k + renormalise, one warp ────────────────────────────────
+// ─── softmax + top-k + renormalise, whole CTA ───────────────────────────────
 // route_experts (reference src/engine/qwen35_moe/cpu.rs:78-85): softmax over all
 // E logits (src/math_util.rs:77-88), the K largest probabilities (ties: lower
 // index first, matching the strict `>` of src/math_util.rs:101), divided by their
-// sum (:120-126).  Results in descending order.
-__device__ __forceinline__ void route_warp(const float* logits, const float* bias, const int32_t* forced,
-                                           int E, int K, int* topi, float* topw, int lane) {
-    float p[kMaxEPerLane];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) {
-        const int e = lane + 32 * i;
-        float v = -INFINITY;
-        if (e < E) {
-            v = __ldcg(logits + e);  // written by other CTAs: read through L2
-            if (bias) v += bias[e];
-        }
-        p[i] = v;
-        mx = fmaxf(mx, v);
+// sum (:120-126).  Thread t owns expert t.  The K-th largest of the 16 per-warp
+// maxima is a lower bound of the K-th largest probability, so only experts at
+// or above it are candidates; each candidate finds its rank by counting the
+// candidates that beat it.  Results come out in descending order.
+__device__ __forceinline__ void route_cta(DecodeSmem* sm, const float* logits, const float* bias,
+                                          const int32_t* forced, int E, int K) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float v = -INFINITY;
+    if (tid < E) {
+        v = __ldcg(logits + tid);  // written by other CTAs: read through L2
+        if (bias) v += bias[tid];
     }
+    float mx = v;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) sm->red[warp] = mx;
+    if (tid == 0) sm->ncand = 0;
+    __syncthreads();
+    const float wmx = mx;  // this warp's max logit
+    mx = sm->red[0];
+#pragma unroll
+    for (int i = 1; i < kDecWarps; ++i) mx = fmaxf(mx, sm->red[i]);
+    const float ex = (tid < E) ? expf(v - mx) : 0.0f;
+    const float ws = warp_sum(ex);
+    __syncthreads();
+    if (lane == 0) { sm->red[warp] = ws; sm->red2[warp] = (warp * 32 < E) ? expf(wmx - mx) : -1.0f; }
+    __syncthreads();
     float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) {
-        const int e = lane + 32 * i;
-        p[i] = (e < E) ? expf(p[i] - mx) : 0.0f;
-        sum += p[i];
-    }
-    sum = warp_sum(sum);
+    for (int i = 0; i < kDecWarps; ++i) sum += sm->red[i];
     const float inv = 1.0f / sum;
-#pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) p[i] = (lane + 32 * i < E) ? p[i] * inv : -1.0f;
-
-    float myw = 0.0f;
-    int myi = 0;
+    const float pr = ex * inv;
+    static_assert(kMaxE == kDecThreads, "one thread per expert slot");
+    sm->prob[tid] = (tid < E) ? pr : -1.0f;
     if (forced) {
-        for (int k = 0; k < K; ++k) {
-            const int e = forced[k];
-            float v = 0.0f;
-#pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i)
-                if (lane + 32 * i == e) v = p[i];
-            v = __shfl_sync(0xffffffffu, v, e & 31);
-            if (lane == k) { myw = v; myi = e; }
-        }
+        __syncthreads();
+        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]]; }
     } else {
-        for (int k = 0; k < K; ++k) {
-            float bv = -2.0f;
-            int be = 0x7fffffff;
+        // threshold = K-th largest warp maximum (as a probability); -1 when fewer than K warps hold experts
+        float tau;
+        {
+            const int me = lane & (kDecWarps - 1);
+            const float mine = sm->red2[me] * inv;  // bit-identical to the owning thread's pr; negative for empty warps
+            int cnt = 0;
 #pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i) {
-                const int e = lane + 32 * i;
-                if (p[i] > bv) { bv = p[i]; be = e; }  // ascending e inside a lane: first max wins
+            for (int j = 0; j < kDecWarps; ++j) {
+                const float o = __shfl_sync(0xffffffffu, mine, j);
+                cnt += (o > mine) || (o == mine && j < me);
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            // exactly one of lanes 0..15 has K-1 warp maxima ahead of it
+            const unsigned hit = __ballot_sync(0xffffffffu, cnt == K - 1 && lane < kDecWarps);
+            tau = __shfl_sync(0xffffffffu, mine, __ffs(hit) - 1);
+            if (tau < 0.0f) tau = -1.0f;  // fewer than K warps hold experts: everything is a candidate
+        }
+        if (tid < E && pr >= tau) {
+            const int slot = atomicAdd(&sm->ncand, 1);
+            sm->cand_p[slot] = pr;
+            sm->cand_i[slot] = tid;
+        }
+        __syncthreads();
+        const int nc = sm->ncand;
+        if (tid < nc) {
+            const float cp = sm->cand_p[tid];
+            const int ci = sm->cand_i[tid];
+            int rank = 0;
+            for (int j = 0; j < nc; ++j) {
+                const float q = sm->cand_p[j];
+                rank += (q > cp) || (q == cp && sm->cand_i[j] < ci);
             }
-            if (lane == k) { myw = bv; myi = be; }
-#pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i)
-                if (lane + 32 * i == be) p[i] = -1.0f;  // taken
+            if (rank < K) { sm->topi[rank] = ci; sm->topp[rank] = cp; }
         }
     }
-    // normalize_weights: divide by the sum of the K selected probabilities
-    float ws = warp_sum(lane < K ? myw : 0.0f);
-    if (ws > 0.0f) myw *= (1.0f / ws);
-    if (lane < K) { topi[lane] = myi; topw[lane] = myw; }
+    __syncthreads();
+    if (tid == 0) {
+        // normalize_weights: divide by the sum of the K selected probabilities
+        float s = 0.0f;
+        for (int k = 0; k < K; ++k) s += sm->topp[k];
+        const float invs = s > 0.0f ? 1.0f / s : 1.0f;
+        for (int k = 0; k < K; ++k) sm->topw[k] = sm->topp[k] * invs;
+    }
+    __syncthreads();
 }
 
 // ─── the persistent kernel ──────────────────────────────────────────────────
@@ -280,14 +428,22 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
     const moe_expert_layout_t L = p.lay;
 
     if (tid == 0) {
-        mbar_init(&sm->bar, 1);
+        mbar_init(&sm->bar_h, 1);
         mbar_fence_init();
     }
     __syncthreads();
 
+    // this CTA's slices
+    const int e0 = slice_lo(cta, E, G), ne = slice_lo(cta + 1, E, G) - e0;
+    const int p0 = slice_lo(cta, kI, G), np = slice_lo(cta + 1, kI, G) - p0;
+    const int i0 = slice_lo(cta, K * kI, G), nb = slice_lo(cta + 1, K * kI, G) - i0;
+    const int r0 = slice_lo(cta, kH, G), nc = slice_lo(cta + 1, kH, G) - r0;
+
     unsigned int bar_target = 0;
     uint32_t parity = 0;
     bool alive = true;
+
+    prefetch_A(sm, p.layers[p.l0], L, cta, G, E, tid);
 
     for (int l = p.l0; l < p.l1 && alive; ++l) {
         const LayerDev ly = p.layers[l];
@@ -295,62 +451,62 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
         float* h_nxt = (l == p.l1 - 1) ? p.h_out : (((l - p.l0) & 1) ? p.h_buf1 : p.h_buf0);
 
         // ── phase A ────────────────────────────────────────────────────────
+        PROF(0);
         if (!stage_norm(sm, h_cur, ly.post_norm, parity)) {
             if (tid == 0) atomicExch(&p.sync[2], 3u);
             alive = false;
             break;
         }
-        parity ^= 1u;
+        cp_wait<0>();  // this layer's phase-A slice (requested one layer ago)
+        __syncthreads();
+        PROF(1);
         {
-            // items: [0, E) router rows, [E, E + I) shared gate/up row pairs, E + I: shared gate score
-            const int n_items = E + kI + 1;
-            for (int item = warp * G + cta; item < n_items; item += kDecWarps * G) {
-                if (item < E) {
-                    float v;
-                    if (ly.router_bf16) {
-                        v = row_dot_bf16(sm, ly.router_bf16 + (size_t)item * kH, lane);
-                    } else {
-                        const uint32_t* const w[1] = {ly.router_q4.w + (size_t)item * (kH / 8)};
-                        const uint16_t* const s[1] = {ly.router_q4.s + (size_t)item * (kH / kGroup)};
-                        const uint16_t* const b[1] = {ly.router_q4.b + (size_t)item * (kH / kGroup)};
-                        float o[1];
-                        rows_dot_h<1>(sm, w, s, b, o, lane);
-                        v = o[0];
-                    }
-                    if (lane == 0) p.logits[item] = v;
-                } else if (item < E + kI) {
-                    const int r = item - E;
-                    const moe_expert_layout_t& S = L;  // shared expert uses the same layout (kI rows)
-                    const uint8_t* ex = ly.shared;
-                    const uint32_t* const w[2] = {
-                        reinterpret_cast<const uint32_t*>(ex + S.gate_w) + (size_t)r * (kH / 8),
-                        reinterpret_cast<const uint32_t*>(ex + S.up_w) + (size_t)r * (kH / 8)};
-                    const uint16_t* const s[2] = {
-                        reinterpret_cast<const uint16_t*>(ex + S.gate_s) + (size_t)r * (kH / kGroup),
-                        reinterpret_cast<const uint16_t*>(ex + S.up_s) + (size_t)r * (kH / kGroup)};
-                    const uint16_t* const b[2] = {
-                        reinterpret_cast<const uint16_t*>(ex + S.gate_b) + (size_t)r * (kH / kGroup),
-                        reinterpret_cast<const uint16_t*>(ex + S.up_b) + (size_t)r * (kH / kGroup)};
-                    float o[2];
-                    rows_dot_h<2>(sm, w, s, b, o, lane);
-                    if (lane == 0) p.act[K * kI + r] = swiglu(o[0], o[1]);
+            // warps [0, ne): router rows; [4, 4 + np): shared gate/up pairs; 8: shared gate score
+            if (warp < ne) {
+                float v;
+                if (ly.router_bf16) {
+                    v = row_dot_bf16(sm, sm->a_router + warp * (kH * 2 / 16), lane);
                 } else {
-                    const uint32_t* const w[1] = {ly.sgate.w};
-                    const uint16_t* const s[1] = {ly.sgate.s};
-                    const uint16_t* const b[1] = {ly.sgate.b};
+                    const uint4* const w[1] = {sm->a_router + warp * kChH};
+                    const uint16_t* const s[1] = {sm->a_router_s[warp]};
+                    const uint16_t* const b[1] = {sm->a_router_b[warp]};
                     float o[1];
                     rows_dot_h<1>(sm, w, s, b, o, lane);
-                    if (lane == 0) p.misc[0] = o[0];
+                    v = o[0];
                 }
+                if (lane == 0) p.logits[e0 + warp] = v;
+            } else if (warp >= 4 && warp < 4 + np) {
+                const int j = warp - 4;
+                const uint4* const w[2] = {sm->a_shw[0][j], sm->a_shw[1][j]};
+                const uint16_t* const s[2] = {sm->a_shs[0][j], sm->a_shs[1][j]};
+                const uint16_t* const b[2] = {sm->a_shb[0][j], sm->a_shb[1][j]};
+                float o[2];
+                rows_dot_h<2>(sm, w, s, b, o, lane);
+                if (lane == 0) p.act[K * kI + p0 + j] = swiglu(o[0], o[1]);
+            } else if (warp == 8 && cta == G - 1) {
+                const uint4* const w[1] = {sm->a_sgw};
+                const uint16_t* const s[1] = {sm->a_sgs};
+                const uint16_t* const b[1] = {sm->a_sgb};
+                float o[1];
+                rows_dot_h<1>(sm, w, s, b, o, lane);
+                if (lane == 0) p.misc[0] = o[0];
             }
         }
+        PROF(2);
         bar_target += G;
         if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
+        PROF(3);
+        PROF(4);
 
         // ── phase B ────────────────────────────────────────────────────────
+        route_cta(sm, p.logits, p.logit_bias, p.forced_idx, E, K);
+        PROF(5);
+        // request everything that depends on the routing, then the next layer's phase-A slice
+        prefetch_B(sm, ly, L, i0, nb, tid);
+        prefetch_C(sm, ly, L, r0, nc, K, tid);
+        if (l + 1 < p.l1) prefetch_A(sm, p.layers[l + 1], L, cta, G, E, tid);
+        else cp_commit();  // keep the group count per layer fixed
         if (warp == 0) {
-            const int32_t* forced = p.forced_idx;
-            route_warp(p.logits, p.logit_bias, forced, E, K, sm->topi, sm->topw, lane);
             if (lane == 0) {
                 // sigmoid (reference src/math_util.rs:67-69) of the shared gate score
                 sm->topw[K] = 1.0f / (1.0f + expf(-__ldcg(p.misc)));
@@ -360,40 +516,31 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                 if (p.out_w) p.out_w[lane] = sm->topw[lane];
             }
         }
+        PROF(6);
+        cp_wait<2>();  // gate/up slice landed (down slice and next phase-A slice may still be in flight)
         __syncthreads();
+        PROF(7);
         {
-            const int n_items = K * kI;  // (expert slot k, row r): gate row r and up row r
-            for (int item0 = warp * G + cta; item0 < n_items; item0 += 2 * kDecWarps * G) {
-                const int item1 = item0 + kDecWarps * G;
-                const bool two = item1 < n_items;
-                const int it[2] = {item0, two ? item1 : item0};
-                const uint32_t* w[4];
-                const uint16_t* s[4];
-                const uint16_t* b[4];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int k = it[q] / kI, r = it[q] - k * kI;
-                    const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
-                    w[2 * q] = reinterpret_cast<const uint32_t*>(ex + L.gate_w) + (size_t)r * (kH / 8);
-                    w[2 * q + 1] = reinterpret_cast<const uint32_t*>(ex + L.up_w) + (size_t)r * (kH / 8);
-                    s[2 * q] = reinterpret_cast<const uint16_t*>(ex + L.gate_s) + (size_t)r * (kH / kGroup);
-                    s[2 * q + 1] = reinterpret_cast<const uint16_t*>(ex + L.up_s) + (size_t)r * (kH / kGroup);
-                    b[2 * q] = reinterpret_cast<const uint16_t*>(ex + L.gate_b) + (size_t)r * (kH / kGroup);
-                    b[2 * q + 1] = reinterpret_cast<const uint16_t*>(ex + L.up_b) + (size_t)r * (kH / kGroup);
-                }
-                const uint32_t* const wc[4] = {w[0], w[1], w[2], w[3]};
-                const uint16_t* const sc[4] = {s[0], s[1], s[2], s[3]};
-                const uint16_t* const bc[4] = {b[0], b[1], b[2], b[3]};
+            // item j of this CTA = (gate row, up row) pair; two items per warp pass
+            for (int j = warp; j < nb; j += 2 * kDecWarps) {
+                const int j2 = j + kDecWarps;
+                const bool two = j2 < nb;
+                const int jb = two ? j2 : j;
+                const uint4* const w[4] = {sm->b_w[0][j], sm->b_w[1][j], sm->b_w[0][jb], sm->b_w[1][jb]};
+                const uint16_t* const s[4] = {sm->b_s[0][j], sm->b_s[1][j], sm->b_s[0][jb], sm->b_s[1][jb]};
+                const uint16_t* const b[4] = {sm->b_b[0][j], sm->b_b[1][j], sm->b_b[0][jb], sm->b_b[1][jb]};
                 float o[4];
-                rows_dot_h<4>(sm, wc, sc, bc, o, lane);
+                rows_dot_h<4>(sm, w, s, b, o, lane);
                 if (lane == 0) {
-                    p.act[it[0]] = swiglu(o[0], o[1]);
-                    if (two) p.act[it[1]] = swiglu(o[2], o[3]);
+                    p.act[i0 + j] = swiglu(o[0], o[1]);
+                    if (two) p.act[i0 + j2] = swiglu(o[2], o[3]);
                 }
             }
         }
+        PROF(8);
         bar_target += G;
         if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
+        PROF(9);
 
         // ── phase C ────────────────────────────────────────────────────────
         {
@@ -410,27 +557,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                 sv += __shfl_xor_sync(0xffffffffu, sv, 4);
                 if (j == 0) sm->suma[m * kChI + c] = sv;
             }
+            cp_wait<1>();  // down slice landed
             __syncthreads();
-            // one warp per output element i: half-warp `sub` takes matrices sub, sub+2, ...
+            PROF(10);
+            // one warp per output element: half-warp `sub` takes matrices sub, sub+2, ...
             const int sub = lane >> 4, c = lane & 15;
             constexpr int kMats = (kMaxK + 2) / 2;  // 5 matrix slots per half-warp
-            for (int i = warp * G + cta; i < kH; i += kDecWarps * G) {
-                uint4 q[kMats];
-                uint16_t scv[kMats], biv[kMats];
-#pragma unroll
-                for (int jm = 0; jm < kMats; ++jm) {
-                    const int m = sub + 2 * jm;
-                    if (m <= K) {
-                        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-                        q[jm] = ld_stream_u4(reinterpret_cast<const uint4*>(ex + L.down_w) + (size_t)i * kChI + c);
-                        scv[jm] = __ldg(reinterpret_cast<const uint16_t*>(ex + L.down_s) + (size_t)i * (kI / kGroup) + (c >> 1));
-                        biv[jm] = __ldg(reinterpret_cast<const uint16_t*>(ex + L.down_b) + (size_t)i * (kI / kGroup) + (c >> 1));
-                    } else {
-                        q[jm] = make_uint4(0, 0, 0, 0);
-                        scv[jm] = 0;
-                        biv[jm] = 0;
-                    }
-                }
+            for (int j = warp; j < nc; j += kDecWarps) {
                 float acc = 0.0f;
 #pragma unroll
                 for (int jm = 0; jm < kMats; ++jm) {
@@ -438,15 +571,20 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                     if (m <= K) {
                         float4 xv[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) xv[j] = sm->acts[(m * 8 + j) * kChI + c];
-                        acc = fmaf(sm->topw[m], chunk_term(q[jm], xv, sm->suma[m * kChI + c], scv[jm], biv[jm]), acc);
+                        for (int q = 0; q < 8; ++q) xv[q] = sm->acts[(m * 8 + q) * kChI + c];
+                        acc = fmaf(sm->topw[m],
+                                   chunk_term(sm->c_w[m][j][c], xv, sm->suma[m * kChI + c], sm->c_s[m][j][c >> 1],
+                                              sm->c_b[m][j][c >> 1]),
+                                   acc);
                     }
                 }
                 acc = warp_sum(acc);
                 // moe_combine_residual (reference src/math_util.rs:599-612)
-                if (lane == 0) h_nxt[i] = sm->raw[i] + acc;
+                if (lane == 0) h_nxt[r0 + j] = sm->raw[r0 + j] + acc;
             }
         }
+        PROF(11);
+        parity ^= 1u;
         if (l + 1 < p.l1) {
             bar_target += G;
             if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
@@ -479,6 +617,7 @@ int decode_init(moe_engine* e) {
     MOE_CUDA(cudaMalloc(&e->dec_w, kMaxK * sizeof(float)));
     MOE_CUDA(cudaMalloc(&e->dec_sync, 16 * sizeof(unsigned int)));
     MOE_CUDA(cudaMemset(e->dec_sync, 0, 16 * sizeof(unsigned int)));
+    e->dec_prof = nullptr;
     MOE_CUDA(cudaMallocHost(&e->stage_host, (size_t)2 * d.hidden * sizeof(float)));
     MOE_CUDA(cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)sizeof(DecodeSmem)));
@@ -490,7 +629,31 @@ int decode_init(moe_engine* e) {
     return MOE_OK;
 }
 
+// Turns the per-phase clock stamps on or off (a device buffer of
+// layers x kProfPoints stamps, written by CTA 0 of the decode kernel).
+int decode_profile_enable(moe_engine* e, bool on) {
+    if (on && !e->dec_prof) {
+        MOE_CUDA(cudaMalloc(&e->dec_prof, e->layers.size() * kProfPoints * sizeof(long long)));
+        MOE_CUDA(cudaMemset(e->dec_prof, 0, e->layers.size() * kProfPoints * sizeof(long long)));
+    } else if (!on && e->dec_prof) {
+        MOE_CUDA(cudaStreamSynchronize(e->stream));
+        cudaFree(e->dec_prof);
+        e->dec_prof = nullptr;
+    }
+    return MOE_OK;
+}
+
+int decode_profile_read(moe_engine* e, long long* out, int max_layers, int* points) {
+    *points = kProfPoints;
+    if (!e->dec_prof) { set_error("decode profiling is off"); return MOE_ERR_STATE; }
+    int n = (int)e->layers.size() < max_layers ? (int)e->layers.size() : max_layers;
+    MOE_CUDA(cudaMemcpyAsync(out, e->dec_prof, (size_t)n * kProfPoints * sizeof(long long), cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    return MOE_OK;
+}
+
 void decode_destroy(moe_engine* e) {
+    if (e->dec_prof) cudaFree(e->dec_prof);
     cudaFree(e->dec_h[0]); cudaFree(e->dec_h[1]); cudaFree(e->dec_logits); cudaFree(e->dec_act);
     cudaFree(e->dec_misc); cudaFree(e->dec_idx); cudaFree(e->dec_w); cudaFree(e->dec_sync);
     if (e->stage_host) cudaFreeHost(e->stage_host);
@@ -502,7 +665,13 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     MOE_REQUIRE(d.hidden == kH && d.inter == kI && d.shared_inter == kI,
                 "decode path is built for hidden=%d, inter=shared_inter=%d (got %d/%d/%d)", kH, kI,
                 d.hidden, d.inter, d.shared_inter);
-    MOE_REQUIRE(d.num_experts <= 32 * kMaxEPerLane, "decode path supports at most %d experts", 32 * kMaxEPerLane);
+    MOE_REQUIRE(d.num_experts <= kMaxE, "decode path supports at most %d experts", kMaxE);
+    const int G = e->dec_grid;
+    auto cdiv = [](int a, int b) { return (a + b - 1) / b; };
+    // every CTA's weight slice must fit its shared-memory staging area
+    MOE_REQUIRE(cdiv(d.num_experts, G) <= kMaxRouterRows && cdiv(kI, G) <= kMaxSharedRows &&
+                    cdiv(d.top_k * kI, G) <= kMaxBItems && cdiv(kH, G) <= kMaxCRows,
+                "decode kernel needs at least 147 SMs for these dimensions (device has %d)", G);
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
     for (int l = l0; l < l1; ++l) {
@@ -520,6 +689,7 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     p.logit_bias = logit_bias; p.forced_idx = forced_idx;
     p.out_idx = out_idx; p.out_w = out_w;
     p.sync = e->dec_sync;
+    p.prof = e->dec_prof;
     p.E = d.num_experts; p.K = d.top_k;
     p.lay = e->lay;
     void* args[] = {&p};

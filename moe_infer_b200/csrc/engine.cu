@@ -705,6 +705,15 @@ int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n) 
     return MOE_OK;
 }
 
+// ── decode phase profile ─────────────────────────────────────────────────────
+
+int moe_decode_profile(moe_engine_t* e, int enable, int64_t* stamps, int max_layers, int* points_per_layer) {
+    MOE_REQUIRE(e, "null engine");
+    if (!stamps) return decode_profile_enable(e, enable != 0);
+    MOE_REQUIRE(points_per_layer && max_layers > 0, "null argument");
+    return decode_profile_read(e, (long long*)stamps, max_layers, points_per_layer);
+}
+
 // ── device-memory helpers ────────────────────────────────────────────────────
 
 int moe_dev_alloc(moe_engine_t* e, size_t bytes, void** out) {

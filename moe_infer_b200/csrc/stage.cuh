@@ -4,7 +4,8 @@
 
 namespace moe {
 
-constexpr uint32_t kWaitLimit = 4u * 1000u * 1000u;  // polls before a device-side wait gives up
+constexpr uint32_t kWaitLimit = 4u * 1000u * 1000u;  // polls before a device-side spin gives up
+constexpr long long kWaitCycles = 2000ll * 1000ll * 1000ll;  // SM cycles (about a second) before a wait gives up
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -29,9 +30,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: returns false if the phase never completed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > kWaitCycles) return false;
+    return true;
 }
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {

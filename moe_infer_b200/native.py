@@ -255,6 +255,18 @@ class NativeEngine:
         L.check(self.lib.moe_telemetry_get(self.h, keys, vals, C.byref(n)))
         return {keys[i].decode(): vals[i] for i in range(n.value)}
 
+    def decode_profile(self, enable: Optional[bool] = None) -> Optional[np.ndarray]:
+        """enable=True/False switches phase stamping; None returns stamps [layers, points]."""
+        if enable is not None:
+            L.check(self.lib.moe_decode_profile(self.h, int(enable), None, 0, None))
+            return None
+        n = self.dims.num_layers + self.dims.num_mtp_layers
+        buf = np.zeros((n, 16), np.int64)
+        pts = C.c_int(0)
+        tmp = np.zeros(n * 16, np.int64)
+        L.check(self.lib.moe_decode_profile(self.h, 1, tmp.ctypes.data_as(C.POINTER(C.c_int64)), n, C.byref(pts)))
+        return tmp[: n * pts.value].reshape(n, pts.value)
+
     # ── timing / accounting ──────────────────────────────────────────────
     def timer_start(self) -> None:
         L.check(self.lib.moe_timer_start(self.h))
