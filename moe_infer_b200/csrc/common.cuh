@@ -62,24 +62,28 @@ struct LayerHost {
     LayerDev dev{};
 };
 
-// Work areas of the batched (grouped) path, sized for max_tokens.
+// Work areas of the batched (grouped) path, sized for `capacity` tokens.
 struct BatchWork {
-    int32_t capacity = 0;        // tokens
-    float* h_a = nullptr;        // [cap, H] ping
-    float* h_b = nullptr;        // [cap, H] pong
-    __nv_bfloat16* x = nullptr;  // [cap, H] normalised activations, bf16, K-permuted
-    float* logits = nullptr;     // [cap, E]
-    int32_t* topk_idx = nullptr; // [cap, K]
-    float* topk_w = nullptr;     // [cap, K]
-    float* sgate = nullptr;      // [cap] sigmoid(shared gate score)
-    int32_t* counts = nullptr;   // [E + 1] tokens per expert (+ shared)
-    int32_t* offsets = nullptr;  // [E + 2] exclusive scan
-    int32_t* cursor = nullptr;   // [E + 1]
+    int32_t capacity = 0;          // tokens
+    uint8_t* base = nullptr;       // one allocation holding everything below
+    float* h_a = nullptr;          // [cap, H] ping (layer stack)
+    float* h_b = nullptr;          // [cap, H] pong
+    __nv_bfloat16* x = nullptr;    // [cap, H] normalised activations, bf16, K-interleaved
+    float* xf = nullptr;           // [cap, H] normalised activations, f32 (router)
+    float* logits = nullptr;       // [cap, E]
+    int32_t* topk_idx = nullptr;   // [cap, K]
+    float* topk_w = nullptr;       // [cap, K]
+    float* sgate = nullptr;        // [cap] sigmoid(shared gate score)
+    int32_t* counts = nullptr;     // [E + 1] tokens per expert (+ shared); zeroed every layer
+    int32_t* offsets = nullptr;    // [E + 2] exclusive scan
+    int32_t* cursor = nullptr;     // [E + 1]
     int32_t* slot_token = nullptr; // [cap*K + cap] token of each expert-sorted slot
-    float* slot_w = nullptr;       // [cap*K + cap] combine weight of each slot
-    __nv_bfloat16* act = nullptr;  // [cap*K + cap, I] SwiGLU outputs, expert-sorted
-    int32_t* tile_list = nullptr;  // work list of (expert, token tile)
+    int32_t* slot_of = nullptr;    // [cap*K] slot of (token, k)
+    __nv_bfloat16* act = nullptr;  // [cap*K + cap, I] SwiGLU outputs, expert-sorted, K-interleaved
+    __nv_bfloat16* o = nullptr;    // [cap*K + cap, H] down-projection outputs, expert-sorted
+    int32_t* tile_list = nullptr;  // (expert, first slot, slots) per token tile
     int32_t* n_tiles = nullptr;
+    int32_t max_tiles = 0;
 };
 
 }  // namespace moe

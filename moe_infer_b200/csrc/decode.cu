@@ -196,53 +196,53 @@ __device__ __forceinline__ void prefetch_A(DecodeSmem* sm, const LayerDev& ly, c
     cp_commit();
 }
 
-// phase B slice: items (slot k, row r) flattened as k * I + r, this CTA owns [i0, i0 + nb)
-__device__ __forceinline__ void prefetch_B(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
-                                           int i0, int nb, int tid) {
-    constexpr int kPW = kH / 2 / 16, kPS = (kH / kGroup) * 2 / 16;  // 16-byte pieces per row: 64 weights, 4 scales
-    // weights: piece -> (m, j, c)
-    const int pw = 2 * nb * kPW;
-    for (int q = tid; q < pw; q += kDecThreads) {
-        const int m = q >= nb * kPW;
-        const int rem = q - m * nb * kPW;
-        const int j = rem / kPW, c = rem % kPW;
-        const int i = i0 + j, k = i / kI, r = i - k * kI;
-        const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
-        cp16(&sm->b_w[m][j][c], ex + (m ? L.up_w : L.gate_w) + (size_t)r * (kH / 2) + c * 16);
+// phase B: a warp copies the items it will compute itself, j = warp and warp + 16
+// of this CTA's [i0, i0 + nb) (item = slot k * I + row r: gate row r and up row r of
+// the k-th chosen expert).  Warp-private, so only a __syncwarp is needed before use
+// and warps start computing as soon as their own bytes land.
+__device__ __forceinline__ void prefetch_B_warp(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                                int i0, int nb, int warp, int lane) {
+    constexpr int kPW = kH / 2 / 16;  // 64 pieces per weight row; scales/biases: 4 pieces per row
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int j = warp + t * kDecWarps;
+        if (j < nb) {
+            const int i = i0 + j, k = i / kI, r = i - k * kI;
+            const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
+            const uint8_t* gw = ex + L.gate_w + (size_t)r * (kH / 2);
+            const uint8_t* uw = ex + L.up_w + (size_t)r * (kH / 2);
+            cp16(&sm->b_w[0][j][lane], gw + lane * 16);
+            cp16(&sm->b_w[0][j][lane + 32], gw + (lane + 32) * 16);
+            cp16(&sm->b_w[1][j][lane], uw + lane * 16);
+            cp16(&sm->b_w[1][j][lane + 32], uw + (lane + 32) * 16);
+            if (lane < 16) {
+                const int a = lane >> 2, c = lane & 3;
+                const int64_t off = a == 0 ? L.gate_s : a == 1 ? L.up_s : a == 2 ? L.gate_b : L.up_b;
+                uint16_t* d = a == 0 ? sm->b_s[0][j] : a == 1 ? sm->b_s[1][j] : a == 2 ? sm->b_b[0][j] : sm->b_b[1][j];
+                cp16(reinterpret_cast<uint8_t*>(d) + c * 16, ex + off + (size_t)r * (kH / kGroup) * 2 + c * 16);
+            }
+        }
     }
-    // scales and biases: piece -> (a in {gate_s, up_s, gate_b, up_b}, j, c)
-    const int ps = 4 * nb * kPS;
-    for (int q = tid; q < ps; q += kDecThreads) {
-        const int a = q / (nb * kPS);
-        const int rem = q - a * nb * kPS;
-        const int j = rem / kPS, c = rem % kPS;
-        const int i = i0 + j, k = i / kI, r = i - k * kI;
-        const uint8_t* ex = ly.experts + (size_t)sm->topi[k] * L.expert_size;
-        const int64_t off = a == 0 ? L.gate_s : a == 1 ? L.up_s : a == 2 ? L.gate_b : L.up_b;
-        uint16_t* d = a == 0 ? sm->b_s[0][j] : a == 1 ? sm->b_s[1][j] : a == 2 ? sm->b_b[0][j] : sm->b_b[1][j];
-        cp16(reinterpret_cast<uint8_t*>(d) + c * 16, ex + off + (size_t)r * (kH / kGroup) * 2 + c * 16);
-    }
+    static_assert(kPW == 64, "two pieces per lane per row");
     cp_commit();
 }
 
-// phase C slice: down rows [r0, r0 + nc) of the K chosen experts and the shared expert
-__device__ __forceinline__ void prefetch_C(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
-                                           int r0, int nc, int K, int tid) {
-    constexpr int kPW = kI / 2 / 16;  // 16 pieces per row; scales and biases are one piece per row
-    const int per_w = nc * kPW;
-    const int pw = (K + 1) * per_w;
-    for (int q = tid; q < pw; q += kDecThreads) {
-        const int m = q / per_w, rem = q - m * per_w;
-        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-        cp16(reinterpret_cast<uint8_t*>(sm->c_w[m]) + rem * 16, ex + L.down_w + (size_t)r0 * (kI / 2) + rem * 16);
-    }
-    const int ps = (K + 1) * 2 * nc;
-    for (int q = tid; q < ps; q += kDecThreads) {
-        const int m = q / (2 * nc), rem = q - m * 2 * nc;
-        const int a = rem >= nc, j = rem - a * nc;
-        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-        uint16_t* d = a ? sm->c_b[m][j] : sm->c_s[m][j];
-        cp16(d, ex + (a ? L.down_b : L.down_s) + (size_t)(r0 + j) * (kI / kGroup) * 2);
+// phase C: a warp copies the down rows of the output element it owns (row r0 + warp)
+// for the K chosen experts and the shared expert.
+__device__ __forceinline__ void prefetch_C_warp(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                                int r0, int nc, int K, int warp, int lane) {
+    for (int j = warp; j < nc; j += kDecWarps) {
+        const int pw = (K + 1) * kChI;  // 16 pieces per row
+        for (int q = lane; q < pw; q += 32) {
+            const int m = q / kChI, c = q - m * kChI;
+            const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+            cp16(&sm->c_w[m][j][c], ex + L.down_w + (size_t)(r0 + j) * (kI / 2) + c * 16);
+        }
+        if (lane < 2 * (K + 1)) {
+            const int m = lane >> 1, a = lane & 1;
+            const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+            cp16(a ? sm->c_b[m][j] : sm->c_s[m][j], ex + (a ? L.down_b : L.down_s) + (size_t)(r0 + j) * (kI / kGroup) * 2);
+        }
     }
     cp_commit();
 }
@@ -501,11 +501,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
         // ── phase B ────────────────────────────────────────────────────────
         route_cta(sm, p.logits, p.logit_bias, p.forced_idx, E, K);
         PROF(5);
-        // request everything that depends on the routing, then the next layer's phase-A slice
-        prefetch_B(sm, ly, L, i0, nb, tid);
-        prefetch_C(sm, ly, L, r0, nc, K, tid);
-        if (l + 1 < p.l1) prefetch_A(sm, p.layers[l + 1], L, cta, G, E, tid);
-        else cp_commit();  // keep the group count per layer fixed
+        // request this warp's gate/up rows now; its down rows and the next layer's
+        // phase-A slice are requested after the gate/up arithmetic, so that their
+        // issue (which stalls while the load queues are full) overlaps barrier 2
+        prefetch_B_warp(sm, ly, L, i0, nb, warp, lane);
         if (warp == 0) {
             if (lane == 0) {
                 // sigmoid (reference src/math_util.rs:67-69) of the shared gate score
@@ -517,8 +516,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
             }
         }
         PROF(6);
-        cp_wait<2>();  // gate/up slice landed (down slice and next phase-A slice may still be in flight)
-        __syncthreads();
+        cp_wait<0>();  // this warp's gate/up rows landed
+        __syncwarp();
         PROF(7);
         {
             // item j of this CTA = (gate row, up row) pair; two items per warp pass
@@ -537,6 +536,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                 }
             }
         }
+        prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
+        if (l + 1 < p.l1) prefetch_A(sm, p.layers[l + 1], L, cta, G, E, tid);
+        else cp_commit();  // keep the group count per layer fixed
         PROF(8);
         bar_target += G;
         if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
@@ -557,8 +559,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                 sv += __shfl_xor_sync(0xffffffffu, sv, 4);
                 if (j == 0) sm->suma[m * kChI + c] = sv;
             }
-            cp_wait<1>();  // down slice landed
-            __syncthreads();
+            cp_wait<1>();  // this warp's down rows landed
+            __syncthreads();  // the staged activations above are shared by all warps
             PROF(10);
             // one warp per output element: half-warp `sub` takes matrices sub, sub+2, ...
             const int sub = lane >> 4, c = lane & 15;

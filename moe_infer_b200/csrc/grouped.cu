@@ -1,38 +1,646 @@
-// Batched (n > 1 tokens) path of one MoE block.
-#include "common.cuh"
+// Batched (n > 1 tokens) path of one MoE block: tokens are sorted by expert on the
+// device and each expert's tokens run through a grouped 4-bit GEMM on the
+// 5th-generation tensor cores.
+//
+// Replaces forward_hidden_batched's per-layer MoE half (reference
+// src/engine/qwen35_moe/fused_exp3.rs:216-276 and batched.rs:334-447), which
+// routes every token on the CPU and then issues 3 matvec dispatches per (token,
+// expert), re-reading the expert weights for each token.  Here every expert's
+// weights are read and dequantised once per tile of up to 128 of its tokens.
+//
+//   prep     per token: x = rmsnorm(h) (f32 for the router, bf16 for the GEMMs),
+//            sigmoid(shared_expert_gate . x)
+//   router   logits = x . Wr^T in f32
+//   route    per token softmax / top-k / renormalise (one warp), expert histogram
+//   plan     exclusive scan of the histogram, list of (expert, token tile) work items
+//   scatter  token -> expert-sorted slot
+//   gemm1    per (tile, 128-row block): D_gate, D_up [128 rows x N tokens] in TMEM =
+//            dequant(W_gate/up rows) . X_tile^T ; epilogue silu(g) * u -> act (bf16)
+//   gemm2    per (tile, 128-row block): D [128 rows x N tokens] = dequant(W_down rows)
+//            . act_tile^T ; epilogue -> O (bf16, one row per slot)
+//   combine  per token: h_out = h_in + sum_k w_k O[slot(t,k)] + sigmoid(sg) O[shared slot]
+//
+// GEMM operand staging: weights are dequantised by all 256 threads of the CTA
+// (128-bit nibble loads, bf16x2 arithmetic) straight into shared memory in the
+// K-major 128-byte-swizzled layout tcgen05.mma reads; one K step = one 64-column
+// quantisation group = one 128-byte swizzle row.  A 4-bit word holds columns
+// c..c+7; masking pairs (n, n+4) without shifting them into order yields the
+// column order [0,4,1,5,2,6,3,7] inside every 8-column block, so the activations
+// are stored with the same interleave (the dot product does not care about the
+// order of its terms).  One thread issues the MMAs; their completion frees the
+// stage through tcgen05.commit on an mbarrier.  Weights (A) take the M = 128
+// side, tokens (B) the N side, so ragged per-expert token counts only change N.
+#include "umma.cuh"
 
 namespace moe {
+
+constexpr int kBH = 2048;  // hidden
+constexpr int kBI = 512;   // moe_intermediate_size == shared_expert_intermediate_size
+constexpr int kNT = 128;   // tokens per tile (MMA N, padded to a multiple of 16)
+constexpr int kGemmThreads = 256;
+constexpr int kStages = 4;
+constexpr int kMaxEPerLane = 16;
+
+// position of logical column j (0..7) inside a K-interleaved 8-block
+__host__ __device__ __forceinline__ int ipos(int j) { return ((j & 3) << 1) | (j >> 2); }
+
+// ─── prep: norm, bf16/f32 activations, shared gate ──────────────────────────
+__global__ void __launch_bounds__(256) batch_prep_kernel(const float* __restrict__ h_in, int n, LayerDev ly,
+                                                         __nv_bfloat16* __restrict__ x_bf, float* __restrict__ x_f,
+                                                         float* __restrict__ sgate) {
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float red[8];
+    const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
+    const float4 a = hp[0], b = hp[1];
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    // rms_norm_bf16 (reference src/math_util.rs:282-288)
+    const float inv_rms = 1.0f / sqrtf(tot / (float)kBH + 1e-6f);
+    const uint4 nw = reinterpret_cast<const uint4*>(ly.post_norm)[tid];
+    const uint32_t nwr[4] = {nw.x, nw.y, nw.z, nw.w};
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i] = v[2 * i] * inv_rms * __uint_as_float(nwr[i] << 16);
+        x[2 * i + 1] = v[2 * i + 1] * inv_rms * __uint_as_float(nwr[i] & 0xFFFF0000u);
+    }
+    float4* xo = reinterpret_cast<float4*>(x_f + (size_t)t * kBH) + tid * 2;
+    xo[0] = make_float4(x[0], x[1], x[2], x[3]);
+    xo[1] = make_float4(x[4], x[5], x[6], x[7]);
+    // bf16, K-interleaved: stored order [0,4,1,5,2,6,3,7]
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(x[0], x[4]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(x[1], x[5]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(x[2], x[6]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(x[3], x[7]);
+    uint4 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&p0);
+    pk.y = *reinterpret_cast<uint32_t*>(&p1);
+    pk.z = *reinterpret_cast<uint32_t*>(&p2);
+    pk.w = *reinterpret_cast<uint32_t*>(&p3);
+    reinterpret_cast<uint4*>(x_bf + (size_t)t * kBH)[tid] = pk;
+    // shared_expert_gate . x : thread tid owns word tid of the single 4-bit row
+    const uint32_t w = ly.sgate.w[tid];
+    const float s = bf16_bits_to_f32(ly.sgate.s[tid >> 3]);
+    const float bb = bf16_bits_to_f32(ly.sgate.b[tid >> 3]);
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += ((float)((w >> (4 * i)) & 0xFu) * s + bb) * x[i];
+    acc = warp_sum(acc);
+    __syncthreads();
+    if (lane == 0) red[warp] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        float sc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc += red[i];
+        sgate[t] = 1.0f / (1.0f + expf(-sc));  // sigmoid (reference src/math_util.rs:67-69)
+    }
+}
+
+// ─── router logits in f32: logits[n, E] = X[n, H] . Wr[E, H]^T ──────────────
+// 64 tokens x 64 experts per block, 4 x 4 outputs per thread.
+__global__ void __launch_bounds__(256) batch_router_kernel(const float* __restrict__ x_f, int n, int E, LayerDev ly,
+                                                           float* __restrict__ logits) {
+    __shared__ float xs[16][65];
+    __shared__ float ws[16][65];
+    const int t0 = blockIdx.x * 64, e0 = blockIdx.y * 64;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < kBH; k0 += 16) {
+        // 64 rows x 16 columns each: thread -> (row = tid >> 2, 4 columns)
+        {
+            const int r = tid >> 2, c = (tid & 3) * 4;
+            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t0 + r < n) xv = *reinterpret_cast<const float4*>(x_f + (size_t)(t0 + r) * kBH + k0 + c);
+            xs[c][r] = xv.x; xs[c + 1][r] = xv.y; xs[c + 2][r] = xv.z; xs[c + 3][r] = xv.w;
+            float wv[4] = {0.f, 0.f, 0.f, 0.f};
+            const int e = e0 + r;
+            if (e < E) {
+                if (ly.router_bf16) {
+                    const uint2 q = *reinterpret_cast<const uint2*>(ly.router_bf16 + (size_t)e * kBH + k0 + c);
+                    wv[0] = __uint_as_float(q.x << 16); wv[1] = __uint_as_float(q.x & 0xFFFF0000u);
+                    wv[2] = __uint_as_float(q.y << 16); wv[3] = __uint_as_float(q.y & 0xFFFF0000u);
+                } else {
+                    const int col = k0 + c;
+                    const uint32_t word = ly.router_q4.w[(size_t)e * (kBH / 8) + (col >> 3)];
+                    const float s = bf16_bits_to_f32(ly.router_q4.s[(size_t)e * (kBH / kGroup) + (col >> 6)]);
+                    const float b = bf16_bits_to_f32(ly.router_q4.b[(size_t)e * (kBH / kGroup) + (col >> 6)]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) wv[i] = (float)((word >> (4 * ((col & 7) + i))) & 0xFu) * s + b;
+                }
+            }
+            ws[c][r] = wv[0]; ws[c + 1][r] = wv[1]; ws[c + 2][r] = wv[2]; ws[c + 3][r] = wv[3];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float xa[4], wb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xa[i] = xs[k][ty * 4 + i]; wb[i] = ws[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= n) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e0 + tx * 4 + j;
+            if (e < E) logits[(size_t)t * E + e] = acc[i][j];
+        }
+    }
+}
+
+// ─── route: one warp per token ──────────────────────────────────────────────
+// route_experts (reference src/engine/qwen35_moe/cpu.rs:78-85; softmax, top-k and
+// renormalise of src/math_util.rs:77-126).  Ties go to the lower index.  Results in
+// descending order.  Also counts tokens per expert.
+__global__ void __launch_bounds__(256) batch_route_kernel(const float* __restrict__ logits, int n, int E, int K,
+                                                          const float* __restrict__ bias,
+                                                          const int32_t* __restrict__ forced,
+                                                          int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                          int32_t* __restrict__ counts) {
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n) return;
+    const float* lg = logits + (size_t)t * E;
+    float p[kMaxEPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxEPerLane; ++i) {
+        const int e = lane + 32 * i;
+        float v = -INFINITY;
+        if (e < E) {
+            v = lg[e];
+            if (bias) v += bias[e];
+        }
+        p[i] = v;
+        mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxEPerLane; ++i) {
+        p[i] = (lane + 32 * i < E) ? expf(p[i] - mx) : 0.0f;
+        sum += p[i];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int i = 0; i < kMaxEPerLane; ++i) p[i] = (lane + 32 * i < E) ? p[i] * inv : -1.0f;
+    float myw = 0.0f;
+    int myi = 0;
+    if (forced) {
+        for (int k = 0; k < K; ++k) {
+            const int e = forced[(size_t)t * K + k];
+            float v = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kMaxEPerLane; ++i)
+                if (lane + 32 * i == e) v = p[i];
+            v = __shfl_sync(0xffffffffu, v, e & 31);
+            if (lane == k) { myw = v; myi = e; }
+        }
+    } else {
+        for (int k = 0; k < K; ++k) {
+            float bv = -2.0f;
+            int be = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < kMaxEPerLane; ++i)
+                if (p[i] > bv) { bv = p[i]; be = lane + 32 * i; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            if (lane == k) { myw = bv; myi = be; }
+#pragma unroll
+            for (int i = 0; i < kMaxEPerLane; ++i)
+                if (lane + 32 * i == be) p[i] = -1.0f;
+        }
+    }
+    const float ws = warp_sum(lane < K ? myw : 0.0f);
+    if (ws > 0.0f) myw *= (1.0f / ws);
+    if (lane < K) {
+        topk_idx[(size_t)t * K + lane] = myi;
+        topk_w[(size_t)t * K + lane] = myw;
+        atomicAdd(&counts[myi], 1);
+    }
+}
+
+// ─── plan: scan of the histogram and the tile list; one block ───────────────
+__global__ void __launch_bounds__(1024) batch_plan_kernel(int32_t* counts, int32_t* offsets, int32_t* cursor, int E,
+                                                          int n, int32_t* tile_list, int32_t* n_tiles, int max_tiles) {
+    __shared__ int s_off[1024 + 1];
+    __shared__ int s_tile[1024 + 1];
+    const int tid = threadIdx.x;
+    if (tid == 0) counts[E] = n;  // the shared expert sees every token
+    __syncthreads();
+    const int c = (tid <= E) ? counts[tid] : 0;
+    const int nt = (c + kNT - 1) / kNT;
+    s_off[tid] = c;
+    s_tile[tid] = nt;
+    __syncthreads();
+    if (tid == 0) {  // E + 1 <= 513 entries: a serial scan is a few microseconds
+        int a = 0, b = 0;
+        for (int i = 0; i <= E; ++i) {
+            const int ca = s_off[i], cb = s_tile[i];
+            s_off[i] = a; s_tile[i] = b;
+            a += ca; b += cb;
+        }
+        s_off[E + 1] = a;
+        s_tile[E + 1] = b;
+        *n_tiles = b < max_tiles ? b : max_tiles;
+    }
+    __syncthreads();
+    if (tid <= E + 1) offsets[tid] = s_off[tid];
+    if (tid <= E) {
+        cursor[tid] = 0;
+        for (int i = 0; i < nt; ++i) {
+            const int k = s_tile[tid] + i;
+            if (k < max_tiles) {
+                tile_list[3 * k] = tid;
+                tile_list[3 * k + 1] = s_off[tid] + i * kNT;
+                tile_list[3 * k + 2] = min(kNT, c - i * kNT);
+            }
+        }
+    }
+}
+
+// ─── scatter: (token, k) -> expert-sorted slot ──────────────────────────────
+__global__ void __launch_bounds__(256) batch_scatter_kernel(const int32_t* __restrict__ topk_idx, int n, int K, int E,
+                                                            const int32_t* __restrict__ offsets, int32_t* cursor,
+                                                            int32_t* __restrict__ slot_token,
+                                                            int32_t* __restrict__ slot_of) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * K) {
+        const int t = i / K;
+        const int e = topk_idx[i];
+        const int slot = offsets[e] + atomicAdd(&cursor[e], 1);
+        slot_token[slot] = t;
+        slot_of[i] = slot;
+    }
+    if (i < n) slot_token[offsets[E] + i] = i;
+}
+
+// ─── grouped GEMM ───────────────────────────────────────────────────────────
+struct GemmParams {
+    const uint8_t* experts;       // E packed experts of this layer
+    const uint8_t* shared;        // shared expert, same layout
+    moe_expert_layout_t lay;
+    int E;
+    const __nv_bfloat16* x;       // [n, H] bf16 K-interleaved           (gemm1 B operand)
+    __nv_bfloat16* act;           // [slots, I] bf16 K-interleaved         (gemm1 out, gemm2 B operand)
+    __nv_bfloat16* o;             // [slots, H] bf16                       (gemm2 out)
+    const int32_t* tile_list;
+    const int32_t* n_tiles;
+    const int32_t* slot_token;
+    unsigned int* err;
+};
+
+// 8 nibbles of one word -> 8 bf16 (n * s + b) in the order [0,4,1,5,2,6,3,7]
+__device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 s2, __nv_bfloat162 b2) {
+    const uint32_t kMask = 0x000F000Fu, kMagic = 0x43004300u;  // bf16 128.0 in both halves
+    const __nv_bfloat162 c128 = __floats2bfloat162_rn(128.0f, 128.0f);
+    uint32_t t[4];
+    t[0] = (w & kMask) | kMagic;
+    t[1] = ((w >> 4) & kMask) | kMagic;
+    t[2] = ((w >> 8) & kMask) | kMagic;
+    t[3] = ((w >> 12) & kMask) | kMagic;
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // (128 + n) - 128 = n exactly; n * s + b rounded once to bf16
+        const __nv_bfloat162 nn = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&t[i]), c128);
+        const __nv_bfloat162 v = __hfma2(nn, s2, b2);
+        r[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+template <int MODE>  // 1: gate/up + SwiGLU -> act ; 2: down -> o
+__global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParams p) {
+    constexpr int kIn = (MODE == 1) ? kBH : kBI;            // contraction length
+    constexpr int kKC = kIn / 64;                           // K steps (one quantisation group each)
+    constexpr int kRB = (MODE == 1) ? kBI / 128 : kBH / 128;  // 128-row blocks per expert matrix
+    constexpr int kARows = (MODE == 1) ? 256 : 128;         // gate + up rows, or down rows
+    constexpr int kABytes = kARows * 128;
+    constexpr int kBBytes = kNT * 128;
+    constexpr int kStage = kABytes + kBBytes;
+    constexpr int kTasks = kARows * 2 / kGemmThreads;       // (row, half-group) dequant tasks per thread per K step
+    constexpr uint32_t kTmemCols = 256;
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t bar_empty[kStages];
+    __shared__ uint64_t bar_acc;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_tok[kNT];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int i = 0; i < kStages; ++i) mbar_init(&bar_empty[i], 1);
+        mbar_init(&bar_acc, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+
+    const int n_items = *p.n_tiles * kRB;
+    uint32_t it = 0;       // K steps issued so far by this CTA (drives stage ring and parities)
+    uint32_t n_done = 0;   // items finished by this CTA
+    bool alive = true;
+
+    for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+        const int tile = item / kRB, rb = item - tile * kRB;
+        const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
+        const int N = (nt + 15) & ~15;
+        const uint8_t* ex = (e < p.E) ? p.experts + (size_t)e * p.lay.expert_size : p.shared;
+        if (MODE == 1 && tid < kNT) s_tok[tid] = (tid < nt) ? p.slot_token[s0 + tid] : 0;
+
+        // this thread's dequant tasks: (row of the A tile, half of the 64-column group)
+        const uint32_t* wp[kTasks];
+        const uint16_t* sp[kTasks];
+        const uint16_t* bp[kTasks];
+        int arow[kTasks], ahalf[kTasks];
+#pragma unroll
+        for (int q = 0; q < kTasks; ++q) {
+            const int task = tid + q * kGemmThreads;
+            const int r = task >> 1;
+            arow[q] = r;
+            ahalf[q] = task & 1;
+            if (MODE == 1) {
+                const int up = r >> 7, row = rb * 128 + (r & 127);
+                wp[q] = reinterpret_cast<const uint32_t*>(ex + (up ? p.lay.up_w : p.lay.gate_w)) + (size_t)row * (kBH / 8) + ahalf[q] * 4;
+                sp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_s : p.lay.gate_s)) + (size_t)row * (kBH / kGroup);
+                bp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_b : p.lay.gate_b)) + (size_t)row * (kBH / kGroup);
+            } else {
+                const int row = rb * 128 + r;
+                wp[q] = reinterpret_cast<const uint32_t*>(ex + p.lay.down_w) + (size_t)row * (kBI / 8) + ahalf[q] * 4;
+                sp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_s) + (size_t)row * (kBI / kGroup);
+                bp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_b) + (size_t)row * (kBI / kGroup);
+            }
+        }
+        __syncthreads();  // s_tok visible
+
+        // software prefetch of K step 0
+        uint4 wq[kTasks];
+        uint16_t sq[kTasks], bq[kTasks];
+#pragma unroll
+        for (int q = 0; q < kTasks; ++q) {
+            wq[q] = ld_stream_u4(wp[q]);
+            sq[q] = __ldg(sp[q]);
+            bq[q] = __ldg(bp[q]);
+        }
+
+        const uint32_t idesc = umma::make_idesc_bf16(128, (uint32_t)N);
+        for (int kc = 0; kc < kKC; ++kc, ++it) {
+            const uint32_t st = it % kStages, use = it / kStages;
+            unsigned char* a_tile = stages + st * kStage;
+            unsigned char* b_tile = a_tile + kABytes;
+            bool ok = true;
+            if (use > 0) ok = mbar_wait(&bar_empty[st], (use - 1) & 1);  // the MMAs that read this stage are done
+
+            // ---- A: dequantise this K step's 64 columns of every row of the tile ----
+            uint4 wc[kTasks];
+            uint16_t sc[kTasks], bc[kTasks];
+#pragma unroll
+            for (int q = 0; q < kTasks; ++q) { wc[q] = wq[q]; sc[q] = sq[q]; bc[q] = bq[q]; }
+            if (kc + 1 < kKC) {
+#pragma unroll
+                for (int q = 0; q < kTasks; ++q) {
+                    wq[q] = ld_stream_u4(wp[q] + (kc + 1) * 8);
+                    sq[q] = __ldg(sp[q] + kc + 1);
+                    bq[q] = __ldg(bp[q] + kc + 1);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < kTasks; ++q) {
+                const uint32_t s32 = (uint32_t)sc[q] | ((uint32_t)sc[q] << 16);
+                const uint32_t b32 = (uint32_t)bc[q] | ((uint32_t)bc[q] << 16);
+                const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s32);
+                const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&b32);
+                const uint32_t words[4] = {wc[q].x, wc[q].y, wc[q].z, wc[q].w};
+                unsigned char* sub = a_tile + ((MODE == 1 && arow[q] >= 128) ? 128 * 128 : 0);
+                const uint32_t r = (uint32_t)(arow[q] & 127);
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    const uint4 v = dequant_word(words[wi], s2, b2);
+                    *reinterpret_cast<uint4*>(sub + umma::sw128_offset(r, (uint32_t)(ahalf[q] * 4 + wi))) = v;
+                }
+            }
+            // ---- B: this K step's 64 columns of every token row of the tile ----
+            for (int q = tid; q < N * 8; q += kGemmThreads) {
+                const int j = q >> 3, c = q & 7;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (j < nt) {
+                    const __nv_bfloat16* src = (MODE == 1) ? p.x + (size_t)s_tok[j] * kBH : p.act + (size_t)(s0 + j) * kBI;
+                    v = __ldg(reinterpret_cast<const uint4*>(src + kc * 64) + c);
+                }
+                *reinterpret_cast<uint4*>(b_tile + umma::sw128_offset((uint32_t)j, (uint32_t)c)) = v;
+            }
+            umma::fence_smem_to_async();
+            if (!__syncthreads_and(ok ? 1 : 0)) { alive = false; break; }
+            if (tid == 0) {
+                umma::fence_after_sync();
+                const uint32_t a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) {
+                    const uint64_t db = umma::make_desc_sw128_kmajor(b_addr + k16 * 32);
+                    const uint32_t acc = (kc > 0 || k16 > 0) ? 1u : 0u;
+                    umma::mma_bf16(tmem, umma::make_desc_sw128_kmajor(a_addr + k16 * 32), db, idesc, acc);
+                    if (MODE == 1)
+                        umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
+                }
+                umma::commit(&bar_empty[st]);
+                if (kc == kKC - 1) umma::commit(&bar_acc);
+            }
+        }
+        if (!alive) break;
+
+        // ---- epilogue: TMEM -> registers -> global ----
+        const bool acc_ok = mbar_wait(&bar_acc, n_done & 1);
+        if (!__syncthreads_and(acc_ok ? 1 : 0)) { alive = false; break; }
+        umma::fence_after_sync();
+        {
+            const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 belong to this warp
+            const int row = rb * 128 + quad * 32 + lane;  // output row inside the expert matrix
+            for (int cb = (warp >> 2); cb * 32 < N; cb += 2) {
+                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32);
+                float g[32];
+                umma::ld_32x32(taddr, g);
+                if (MODE == 1) {
+                    float u[32];
+                    umma::ld_32x32(taddr + kNT, u);
+                    const int pos = (row & ~7) | ipos(row & 7);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int col = cb * 32 + c;
+                        if (col < nt) {
+                            // swiglu_fused (reference src/math_util.rs:254-259)
+                            const float a = g[c] / (1.0f + expf(-g[c])) * u[c];
+                            p.act[(size_t)(s0 + col) * kBI + pos] = __float2bfloat16_rn(a);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int col = cb * 32 + c;
+                        if (col < nt) p.o[(size_t)(s0 + col) * kBH + row] = __float2bfloat16_rn(g[c]);
+                    }
+                }
+            }
+        }
+        ++n_done;
+        umma::fence_before_sync();
+        __syncthreads();  // every warp has read its accumulators before the next item overwrites them
+    }
+
+    if (!alive && tid == 0) atomicExch(p.err, 7u);
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, kTmemCols);
+}
+
+// ─── combine ────────────────────────────────────────────────────────────────
+// moe_combine_residual (reference src/math_util.rs:599-612) per token, reading the
+// expert outputs through the token's slots.
+__global__ void __launch_bounds__(256) batch_combine_kernel(const float* __restrict__ h_in, float* __restrict__ h_out,
+                                                            int n, int K, int E, const __nv_bfloat16* __restrict__ o,
+                                                            const int32_t* __restrict__ slot_of,
+                                                            const float* __restrict__ topk_w,
+                                                            const float* __restrict__ sgate,
+                                                            const int32_t* __restrict__ offsets) {
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
+    const float4 a = hp[0], b = hp[1];
+    float moe[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto add = [&](int slot, float w, float (&dst)[8]) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(o + (size_t)slot * kBH) + tid);
+        const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            dst[2 * i] += w * __uint_as_float(r[i] << 16);
+            dst[2 * i + 1] += w * __uint_as_float(r[i] & 0xFFFF0000u);
+        }
+    };
+    for (int k = 0; k < K; ++k) add(slot_of[(size_t)t * K + k], topk_w[(size_t)t * K + k], moe);
+    float sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    add(offsets[E] + t, sgate[t], sh);
+    const float hin[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float out[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = hin[i] + moe[i] + sh[i];
+    float4* op = reinterpret_cast<float4*>(h_out + (size_t)t * kBH) + tid * 2;
+    op[0] = make_float4(out[0], out[1], out[2], out[3]);
+    op[1] = make_float4(out[4], out[5], out[6], out[7]);
+}
+
+// ─── host side ──────────────────────────────────────────────────────────────
+
+static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
+
+template <int MODE>
+static constexpr size_t gemm_smem_bytes() {
+    return (size_t)kStages * (((MODE == 1) ? 256 : 128) * 128 + kNT * 128) + 1024;
+}
 
 int batch_reserve(moe_engine* e, int32_t n_tokens) {
     BatchWork& bw = e->bw;
     if (n_tokens <= bw.capacity) return MOE_OK;
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     batch_destroy(e);
-    const size_t hb = (size_t)n_tokens * e->dims.hidden * sizeof(float);
-    MOE_CUDA(cudaMalloc(&bw.h_a, hb));
-    MOE_CUDA(cudaMalloc(&bw.h_b, hb));
+    const moe_dims_t& d = e->dims;
+    const size_t n = (size_t)n_tokens, H = d.hidden, I = d.inter, E = d.num_experts, K = d.top_k;
+    const size_t slots = n * K + n;
+    const int max_tiles = (int)(slots / kNT + E + 2);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
+    const size_t o_ha = take(n * H * 4), o_hb = take(n * H * 4), o_x = take(n * H * 2), o_xf = take(n * H * 4);
+    const size_t o_lg = take(n * E * 4), o_ti = take(n * K * 4), o_tw = take(n * K * 4), o_sg = take(n * 4);
+    const size_t o_cnt = take((E + 1) * 4), o_off = take((E + 2) * 4), o_cur = take((E + 1) * 4);
+    const size_t o_st = take(slots * 4), o_so = take(n * K * 4), o_act = take(slots * I * 2), o_o = take(slots * H * 2);
+    const size_t o_tl = take((size_t)max_tiles * 3 * 4), o_nt = take(4);
+    MOE_CUDA(cudaMalloc(&bw.base, off));
+    uint8_t* b = bw.base;
+    bw.h_a = (float*)(b + o_ha); bw.h_b = (float*)(b + o_hb);
+    bw.x = (__nv_bfloat16*)(b + o_x); bw.xf = (float*)(b + o_xf);
+    bw.logits = (float*)(b + o_lg); bw.topk_idx = (int32_t*)(b + o_ti); bw.topk_w = (float*)(b + o_tw);
+    bw.sgate = (float*)(b + o_sg);
+    bw.counts = (int32_t*)(b + o_cnt); bw.offsets = (int32_t*)(b + o_off); bw.cursor = (int32_t*)(b + o_cur);
+    bw.slot_token = (int32_t*)(b + o_st); bw.slot_of = (int32_t*)(b + o_so);
+    bw.act = (__nv_bfloat16*)(b + o_act); bw.o = (__nv_bfloat16*)(b + o_o);
+    bw.tile_list = (int32_t*)(b + o_tl); bw.n_tiles = (int32_t*)(b + o_nt);
+    bw.max_tiles = max_tiles;
     bw.capacity = n_tokens;
+    MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<1>()));
+    MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<2>()));
     return MOE_OK;
 }
 
 void batch_destroy(moe_engine* e) {
     BatchWork& bw = e->bw;
-    cudaFree(bw.h_a);
-    cudaFree(bw.h_b);
+    if (bw.base) cudaFree(bw.base);
     bw = BatchWork{};
 }
 
-// Token-serial walk: every token goes through the decode kernel on its own
-// (what the reference does for N tokens, src/engine/qwen35_moe/batched.rs:334-447).
 int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_out,
                          const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
-    const int H = e->dims.hidden, K = e->dims.top_k;
-    for (int t = 0; t < n; ++t) {
-        int rc = launch_decode(e, layer, layer + 1, h_in + (size_t)t * H, h_out + (size_t)t * H, logit_bias,
-                               forced_idx ? forced_idx + (size_t)t * K : nullptr,
-                               out_idx ? out_idx + (size_t)t * K : nullptr, out_w ? out_w + (size_t)t * K : nullptr);
-        if (rc) return rc;
-    }
+    const moe_dims_t& d = e->dims;
+    MOE_REQUIRE(d.hidden == kBH && d.inter == kBI && d.shared_inter == kBI,
+                "batched path is built for hidden=%d, inter=shared_inter=%d (got %d/%d/%d)", kBH, kBI, d.hidden,
+                d.inter, d.shared_inter);
+    MOE_REQUIRE(d.num_experts <= 32 * kMaxEPerLane, "batched path supports at most %d experts", 32 * kMaxEPerLane);
+    MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "batched: h must be 16-byte aligned");
+    int rc = check_layer_ready(e, layer);
+    if (rc) return rc;
+    rc = refresh_layer_table(e);
+    if (rc) return rc;
+    rc = batch_reserve(e, n);
+    if (rc) return rc;
+    BatchWork& bw = e->bw;
+    const LayerDev ly = e->layers[layer].dev;
+    const int E = d.num_experts, K = d.top_k;
+    cudaStream_t st = e->stream;
+    int32_t* idx = out_idx ? out_idx : bw.topk_idx;
+    float* wts = out_w ? out_w : bw.topk_w;
+
+    MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.xf, bw.sgate);
+    batch_router_kernel<<<dim3((n + 63) / 64, (E + 63) / 64), 256, 0, st>>>(bw.xf, n, E, ly, bw.logits);
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts);
+    batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
+    batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
+    GemmParams gp{};
+    gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
+    gp.x = bw.x; gp.act = bw.act; gp.o = bw.o;
+    gp.tile_list = bw.tile_list; gp.n_tiles = bw.n_tiles; gp.slot_token = bw.slot_token;
+    gp.err = e->dec_sync + 2;
+    grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
+    grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
+    batch_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, E, bw.o, bw.slot_of, wts, bw.sgate, bw.offsets);
+    e->launches += 8;
+    MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
 
