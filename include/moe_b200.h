@@ -227,6 +227,50 @@ int moe_ep_export(moe_engine_t* e, int32_t max_tokens_per_rank, void* handle_out
 int moe_ep_init(moe_engine_t* e, int rank, int world, const void* all_handles /* world * MOE_EP_HANDLE_BYTES */);
 int moe_ep_finalize(moe_engine_t* e);
 
+/* ── decode of one MoE block without any allocation ─────────────────────────
+ * This entry point has no counterpart in the reference.  It exists for hosts
+ * that must not let a library allocate device memory: a serving process whose
+ * HBM is partitioned once at start-up and owned by its own pool, a plug-in inside
+ * such a process, or a loop in which cudaMalloc / cudaFree (they synchronise the
+ * device and can fail under fragmentation) are banned after initialisation.
+ *
+ * It needs no engine.  It computes what moe_layer_forward_dev computes for one
+ * token (n_tokens == 1, no logit bias, no forced indices) from tensor pointers
+ * the caller owns (all device memory, in the reference's byte layout), and
+ * keeps its work areas (router logits, SwiGLU outputs, barrier words, one layer
+ * descriptor) in a 40 KiB array that is part of the library image; every GPU
+ * that loads the library holds that array until the process exits.
+ *
+ *  - Limits: hidden 2048, inter = shared_inter = 512, group 64, top_k <= 8,
+ *    num_experts <= 512 (the array has room for 512 router logits); anything
+ *    else is rejected with MOE_ERR_INVALID and a message.
+ *  - It calls no cudaMalloc, cudaFree or other allocating routine.
+ *  - The first call on a device looks up the array's device address and sets the
+ *    kernel's shared-memory attribute; make that first call before any stream
+ *    capture begins.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents; the words that must start at zero are cleared on the given stream
+ *    at every call.  Two calls that overlap on the same GPU (different streams,
+ *    or different threads) race on the array: serialise them.
+ *  - `cuda_stream` is a cudaStream_t (NULL = the default stream).  With wait == 0
+ *    the call returns after enqueueing; with wait != 0 it waits for the stream
+ *    and reports a device-side bounded-wait failure as MOE_ERR_DEVICE_WAIT. */
+typedef struct {
+    const void* experts;     /* num_experts packed experts (moe_expert_layout), back to back */
+    const void* post_norm;   /* bf16 [hidden] */
+    const void* router_bf16; /* bf16 [E, hidden], or NULL to use the 4-bit router below */
+    const void* router_w;    /* u32 [E, hidden/8] */
+    const void* router_s;    /* bf16 [E, hidden/64] */
+    const void* router_b;    /* bf16 [E, hidden/64] */
+    const void* shared;      /* shared expert, same byte layout as one packed expert */
+    const void* sgate_w;     /* shared_expert_gate: u32 [1, hidden/8] */
+    const void* sgate_s;     /* bf16 [1, hidden/64] */
+    const void* sgate_b;     /* bf16 [1, hidden/64] */
+} moe_layer_ptrs_t;
+int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, const moe_layer_ptrs_t* layer_ptrs_dev,
+                             const float* h_in_dev, float* h_out_dev, int32_t* out_idx_dev /* nullable */,
+                             float* out_w_dev /* nullable */, void* cuda_stream, int wait);
+
 /* ── synthetic data ──────────────────────────────────────────────────────────
  * No counterpart in the reference (it reads real checkpoints): fills a device
  * buffer with seeded N(0, sigma^2) values, a fraction `outlier_frac` of them

@@ -33,6 +33,11 @@ class ExpertLayout(C.Structure):
                                          "down_w", "down_s", "down_b", "expert_size")]
 
 
+class LayerPtrs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("experts", "post_norm", "router_bf16", "router_w", "router_s", "router_b",
+                                          "shared", "sgate_w", "sgate_s", "sgate_b")]
+
+
 CHECK_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
 
 _vp, _i, _i32, _i64, _sz = C.c_void_p, C.c_int, C.c_int32, C.c_int64, C.c_size_t
@@ -74,6 +79,7 @@ SIGNATURES = {
     "moe_ep_export": (_i, [_vp, _i32, _vp]),
     "moe_ep_init": (_i, [_vp, _i, _i, _vp]),
     "moe_ep_finalize": (_i, [_vp]),
+    "moe_layer_decode_noalloc": (_i, [C.POINTER(MoeDims), _i, C.POINTER(LayerPtrs), _vp, _vp, _vp, _vp, _vp, _i]),
     "moe_synth_normal_dev": (_i, [_vp, _vp, _i, _i64, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "moe_dev_alloc": (_i, [_vp, _sz, _pp]),
     "moe_dev_free": (_i, [_vp, _vp]),

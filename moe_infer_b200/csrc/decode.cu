@@ -701,4 +701,131 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     return MOE_OK;
 }
 
+// ─── decode of one block for callers that must not allocate ─────────────────
+//
+// Some hosts cannot let a library call cudaMalloc: a serving process whose device
+// memory is carved up once at start-up and owned by its own pool, a plug-in
+// running inside such a process, or a latency-critical loop in which cudaMalloc /
+// cudaFree (which synchronise the device and can fail when memory is fragmented)
+// are banned after initialisation.  For them the decode kernel's work areas (the
+// router logits, the SwiGLU outputs, the grid-barrier words, one layer
+// descriptor) live in the fixed array below instead of in engine-owned
+// allocations.  The array is part of the library image: every GPU that loads
+// the library holds these 40 KiB until the process exits.
+constexpr size_t kNaSync = 0;        // 16 barrier / error words
+constexpr size_t kNaLayer = 256;     // one LayerDev
+constexpr size_t kNaMisc = 512;      // float[16]
+constexpr size_t kNaLogits = 1024;   // float[kMaxE + 4]
+constexpr size_t kNaAct = 3328;      // float[(kMaxK + 1) * kI]
+constexpr size_t kNaH0 = kNaAct + sizeof(float) * (kMaxK + 1) * kI;
+constexpr size_t kNaH1 = kNaH0 + sizeof(float) * kH;
+constexpr size_t kNoAllocScratchBytes = 40960;
+static_assert(kNaH1 + sizeof(float) * kH <= kNoAllocScratchBytes, "scratch layout exceeds the array");
+static_assert(kNaLogits + sizeof(float) * (kMaxE + 4) <= kNaAct && sizeof(LayerDev) <= kNaMisc - kNaLayer, "scratch layout overlaps");
+static_assert(kNaAct % 256 == 0 && kNaH0 % 256 == 0 && kNaH1 % 256 == 0, "scratch parts stay 256-byte aligned");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNaMaxDevices = 64;
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is looked up once per device and kept here.
+static unsigned char* g_noalloc_dev_ptr[kNaMaxDevices] = {};
+static int g_noalloc_grid[kNaMaxDevices] = {};
+
 }  // namespace moe
+
+using namespace moe;
+
+extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, const moe_layer_ptrs_t* lp,
+                                        const float* h_in_dev, float* h_out_dev, int32_t* out_idx_dev,
+                                        float* out_w_dev, void* cuda_stream, int wait) {
+    MOE_REQUIRE(dims && lp && h_in_dev && h_out_dev, "null argument");
+    const moe_dims_t& d = *dims;
+    MOE_REQUIRE(d.hidden == kH && d.inter == kI && d.shared_inter == kI && d.group == kGroup,
+                "no-alloc decode is built for hidden=%d, inter=shared_inter=%d, group=%d", kH, kI, kGroup);
+    MOE_REQUIRE(d.top_k >= 1 && d.top_k <= kMaxK && d.top_k <= d.num_experts, "num_active_experts (%d) must be in 1..%d",
+                d.top_k, kMaxK);
+    // the fixed scratch array holds the logits of at most kMaxE experts
+    MOE_REQUIRE(d.num_experts >= 1 && d.num_experts <= kMaxE,
+                "num_experts (%d) exceeds the static scratch of the no-alloc entry point (at most %d experts)",
+                d.num_experts, kMaxE);
+    MOE_REQUIRE(lp->experts && lp->post_norm && lp->shared && lp->sgate_w && lp->sgate_s && lp->sgate_b &&
+                    (lp->router_bf16 || (lp->router_w && lp->router_s && lp->router_b)),
+                "no-alloc decode: a tensor pointer is missing");
+    MOE_REQUIRE(device >= 0 && device < kNaMaxDevices, "device %d out of range", device);
+    MOE_REQUIRE((((uintptr_t)h_in_dev) & 15) == 0 && (((uintptr_t)h_out_dev) & 15) == 0, "h must be 16-byte aligned");
+    int prev = 0;
+    MOE_CUDA(cudaGetDevice(&prev));
+    MOE_CUDA(cudaSetDevice(device));
+    int rc = MOE_OK;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    do {
+        if (!g_noalloc_dev_ptr[device]) {
+            // one-time set-up on this device (with the device current): device address of the array
+            unsigned char* ptr = nullptr;
+            cudaError_t ce = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+            if (ce != cudaSuccess || !ptr) { rc = cuda_fail(ce, "cudaGetSymbolAddress(g_noalloc_scratch)", __FILE__, __LINE__); break; }
+            ce = cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem));
+            int sms = 0;
+            if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+            if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode set-up", __FILE__, __LINE__); break; }
+            g_noalloc_grid[device] = sms;
+            g_noalloc_dev_ptr[device] = ptr;
+        }
+        unsigned char* base = g_noalloc_dev_ptr[device];
+        const int G = g_noalloc_grid[device];
+        auto cdiv = [](int a, int b) { return (a + b - 1) / b; };
+        if (!(cdiv(d.num_experts, G) <= kMaxRouterRows && cdiv(kI, G) <= kMaxSharedRows &&
+              cdiv(d.top_k * kI, G) <= kMaxBItems && cdiv(kH, G) <= kMaxCRows)) {
+            set_error("decode kernel needs at least 147 SMs for these dimensions (device has %d)", G);
+            rc = MOE_ERR_INVALID;
+            break;
+        }
+        LayerDev ld{};
+        ld.experts = (const uint8_t*)lp->experts;
+        ld.post_norm = (const uint16_t*)lp->post_norm;
+        ld.router_bf16 = (const uint16_t*)lp->router_bf16;
+        ld.router_q4.w = (const uint32_t*)lp->router_w;
+        ld.router_q4.s = (const uint16_t*)lp->router_s;
+        ld.router_q4.b = (const uint16_t*)lp->router_b;
+        ld.shared = (const uint8_t*)lp->shared;
+        ld.sgate.w = (const uint32_t*)lp->sgate_w;
+        ld.sgate.s = (const uint16_t*)lp->sgate_s;
+        ld.sgate.b = (const uint16_t*)lp->sgate_b;
+        // the array keeps whatever the previous call left: the barrier and error words must start at zero
+        cudaError_t ce = cudaMemsetAsync(base + kNaSync, 0, 64, st);
+        if (ce == cudaSuccess) ce = cudaMemcpyAsync(base + kNaLayer, &ld, sizeof(ld), cudaMemcpyHostToDevice, st);
+        if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode: scratch set-up", __FILE__, __LINE__); break; }
+        DecodeParams p{};
+        p.layers = reinterpret_cast<const LayerDev*>(base + kNaLayer);
+        p.l0 = 0; p.l1 = 1;
+        p.h_in = h_in_dev; p.h_out = h_out_dev;
+        p.h_buf0 = reinterpret_cast<float*>(base + kNaH0);
+        p.h_buf1 = reinterpret_cast<float*>(base + kNaH1);
+        p.logits = reinterpret_cast<float*>(base + kNaLogits);
+        p.act = reinterpret_cast<float*>(base + kNaAct);
+        p.misc = reinterpret_cast<float*>(base + kNaMisc);
+        p.logit_bias = nullptr; p.forced_idx = nullptr;
+        p.out_idx = out_idx_dev; p.out_w = out_w_dev;
+        p.sync = reinterpret_cast<unsigned int*>(base + kNaSync);
+        p.prof = nullptr;
+        p.E = d.num_experts; p.K = d.top_k;
+        if (moe_expert_layout(d.hidden, d.inter, d.group, &p.lay) != MOE_OK) { rc = MOE_ERR_INVALID; break; }
+        void* args[] = {&p};
+        ce = cudaLaunchCooperativeKernel((const void*)decode_stack_kernel, dim3(G), dim3(kDecThreads), args,
+                                         sizeof(DecodeSmem), st);
+        if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode launch", __FILE__, __LINE__); break; }
+        if (wait) {
+            unsigned int flag = 0;
+            ce = cudaMemcpyAsync(&flag, base + kNaSync + 8, sizeof(flag), cudaMemcpyDeviceToHost, st);
+            if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+            if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode wait", __FILE__, __LINE__); break; }
+            if (flag) {
+                set_error("a bounded device-side wait gave up (code %u); the result of this call is invalid", flag);
+                rc = MOE_ERR_DEVICE_WAIT;
+            }
+        }
+    } while (0);
+    cudaSetDevice(prev);
+    return rc;
+}
