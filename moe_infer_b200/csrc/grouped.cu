@@ -6,11 +6,11 @@
 // src/engine/qwen35_moe/fused_exp3.rs:216-276 and batched.rs:334-447), which
 // routes every token on the CPU and then issues 3 matvec dispatches per (token,
 // expert), re-reading the expert weights for each token.  Here every expert's
-// weights are read and dequantised once per tile of up to 128 of its tokens.
+// weights are read and dequantised once per tile of up to 256 of its tokens.
 //
 //   prep     per token: x = rmsnorm(h) (f32 for the router, bf16 for the GEMMs),
 //            sigmoid(shared_expert_gate . x)
-//   router   logits = x . Wr^T in f32
+//   router   logits = x . Wr^T on the tensor cores with three-way bf16 splits (f32 accuracy)
 //   route    per token softmax / top-k / renormalise (one warp), expert histogram
 //   plan     exclusive scan of the histogram, list of (expert, token tile) work items
 //   scatter  token -> expert-sorted slot
@@ -36,9 +36,9 @@ namespace moe {
 
 constexpr int kBH = 2048;  // hidden
 constexpr int kBI = 512;   // moe_intermediate_size == shared_expert_intermediate_size
-constexpr int kNT = 128;   // tokens per tile (MMA N, padded to a multiple of 16)
-constexpr int kGemmThreads = 256;
-constexpr int kStages = 4;
+constexpr int kNT = 256;   // tokens per tile (MMA N, padded to a multiple of 16)
+constexpr int kGemmThreads = 512;
+constexpr int kStages = 3;
 constexpr int kMaxEPerLane = 16;
 
 // position of logical column j (0..7) inside a K-interleaved 8-block
@@ -166,6 +166,180 @@ __global__ void __launch_bounds__(256) batch_router_kernel(const float* __restri
             if (e < E) logits[(size_t)t * E + e] = acc[i][j];
         }
     }
+}
+
+// ─── router logits on the tensor cores, to f32 accuracy ─────────────────────
+// logits[n, E] = X[n, H] . Wr[E, H]^T.  The expert choice must match an f32
+// evaluation, so neither operand may simply be rounded to bf16: every f32 value
+// v is split into three bf16 terms hi + mid + lo (24 significant bits) and the
+// products of total order <= 2 are accumulated in f32 by tcgen05.mma:
+//   bf16 router (BQ4):  W . (x_hi + x_mid + x_lo)                         3 MMAs per K block
+//   4-bit router (INT4): W_hi.x_hi + W_hi.x_mid + W_mid.x_hi + W_hi.x_lo + W_lo.x_hi + W_mid.x_mid   6 MMAs
+// One CTA = 128 experts x 64 tokens; both operand tiles are produced by the CTA's
+// 256 threads in natural column order, two stages.
+constexpr int kRtTok = 64;
+constexpr int kRtATile = 128 * 128;  // 128 rows x 64 bf16
+constexpr int kRtBTile = kRtTok * 128;
+constexpr int kRtStage = 3 * kRtATile + 3 * kRtBTile;
+
+__device__ __forceinline__ void split3(float v, uint16_t& hi, uint16_t& mid, uint16_t& lo) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(m);
+    const __nv_bfloat16 l = __float2bfloat16_rn(r2);
+    hi = __bfloat16_as_ushort(h); mid = __bfloat16_as_ushort(m); lo = __bfloat16_as_ushort(l);
+}
+
+__global__ void __launch_bounds__(256, 1) router_gemm_kernel(const float* __restrict__ x_f, int n, int E, LayerDev ly,
+                                                             float* __restrict__ logits, unsigned int* err) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t bar_empty[2];
+    __shared__ uint64_t bar_acc;
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t0 = blockIdx.x * kRtTok, e0 = blockIdx.y * 128;
+    const bool q4 = ly.router_bf16 == nullptr;
+    if (tid == 0) {
+        mbar_init(&bar_empty[0], 1);
+        mbar_init(&bar_empty[1], 1);
+        mbar_init(&bar_acc, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, 64);
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t idesc = umma::make_idesc_bf16(128, kRtTok);
+    bool alive = true;
+    constexpr int kSteps = kBH / 64;
+    for (int kc = 0; kc < kSteps; ++kc) {
+        const int st = kc & 1, use = kc >> 1;
+        bool ok = true;
+        if (use > 0) ok = mbar_wait(&bar_empty[st], (use - 1) & 1);
+        unsigned char* a_hi = stages + st * kRtStage;
+        unsigned char* b_hi = a_hi + 3 * kRtATile;
+        // ---- B: 64 tokens x 64 columns of x, split three ways; thread -> (token, 16 columns) ----
+        {
+            const int j = tid >> 2, cq = tid & 3;  // 4 threads per token row, 16 columns each
+            const int t = t0 + j;
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t < n) q = __ldg(reinterpret_cast<const float4*>(x_f + (size_t)t * kBH + kc * 64 + cq * 16) + i);
+                v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t ph[4], pm[4], pl[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint16_t h0, m0, l0, h1, m1, l1;
+                    split3(v[half * 8 + 2 * i], h0, m0, l0);
+                    split3(v[half * 8 + 2 * i + 1], h1, m1, l1);
+                    ph[i] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                    pm[i] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+                    pl[i] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+                }
+                const uint32_t off = umma::sw128_offset((uint32_t)j, (uint32_t)(cq * 2 + half));
+                *reinterpret_cast<uint4*>(b_hi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                *reinterpret_cast<uint4*>(b_hi + kRtBTile + off) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
+                *reinterpret_cast<uint4*>(b_hi + 2 * kRtBTile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+            }
+        }
+        // ---- A: 128 router rows x 64 columns; thread -> (row, 32 columns) ----
+        {
+            const int r = tid >> 1, half = tid & 1;
+            const int e = e0 + r;
+            if (!q4) {
+                uint4 q[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    q[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (e < E) q[i] = __ldg(reinterpret_cast<const uint4*>(ly.router_bf16 + (size_t)e * kBH + kc * 64 + half * 32) + i);
+                    *reinterpret_cast<uint4*>(a_hi + umma::sw128_offset((uint32_t)r, (uint32_t)(half * 4 + i))) = q[i];
+                }
+            } else {
+                uint4 w = make_uint4(0u, 0u, 0u, 0u);
+                float s = 0.f, b = 0.f;
+                if (e < E) {
+                    w = __ldg(reinterpret_cast<const uint4*>(ly.router_q4.w + (size_t)e * (kBH / 8) + kc * 8) + half);
+                    s = bf16_bits_to_f32(ly.router_q4.s[(size_t)e * (kBH / kGroup) + kc]);
+                    b = bf16_bits_to_f32(ly.router_q4.b[(size_t)e * (kBH / kGroup) + kc]);
+                }
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                    uint32_t ph[4], pm[4], pl[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint16_t h0, m0, l0, h1, m1, l1;
+                        // (nibble as f32) * scale + bias: the reference's dequantised weight (src/math_util.rs:47)
+                        split3((float)((words[wi] >> (8 * i)) & 0xFu) * s + b, h0, m0, l0);
+                        split3((float)((words[wi] >> (8 * i + 4)) & 0xFu) * s + b, h1, m1, l1);
+                        ph[i] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                        pm[i] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+                        pl[i] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+                    }
+                    const uint32_t off = umma::sw128_offset((uint32_t)r, (uint32_t)(half * 4 + wi));
+                    *reinterpret_cast<uint4*>(a_hi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    *reinterpret_cast<uint4*>(a_hi + kRtATile + off) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
+                    *reinterpret_cast<uint4*>(a_hi + 2 * kRtATile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                }
+            }
+        }
+        umma::fence_smem_to_async();
+        if (!__syncthreads_and(ok ? 1 : 0)) { alive = false; break; }
+        if (tid == 0) {
+            umma::fence_after_sync();
+            const uint32_t a0 = smem_u32(a_hi), b0 = smem_u32(b_hi);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16) {
+                const uint32_t o = k16 * 32;
+                const uint64_t ah = umma::make_desc_sw128_kmajor(a0 + o);
+                const uint64_t bh = umma::make_desc_sw128_kmajor(b0 + o);
+                const uint64_t bm = umma::make_desc_sw128_kmajor(b0 + kRtBTile + o);
+                const uint64_t bl = umma::make_desc_sw128_kmajor(b0 + 2 * kRtBTile + o);
+                umma::mma_bf16(tmem, ah, bh, idesc, (kc > 0 || k16 > 0) ? 1u : 0u);
+                umma::mma_bf16(tmem, ah, bm, idesc, 1u);
+                umma::mma_bf16(tmem, ah, bl, idesc, 1u);
+                if (q4) {
+                    const uint64_t am = umma::make_desc_sw128_kmajor(a0 + kRtATile + o);
+                    const uint64_t al = umma::make_desc_sw128_kmajor(a0 + 2 * kRtATile + o);
+                    umma::mma_bf16(tmem, am, bh, idesc, 1u);
+                    umma::mma_bf16(tmem, al, bh, idesc, 1u);
+                    umma::mma_bf16(tmem, am, bm, idesc, 1u);
+                }
+            }
+            umma::commit(&bar_empty[st]);
+            if (kc == kSteps - 1) umma::commit(&bar_acc);
+        }
+    }
+    if (alive) {
+        const bool acc_ok = mbar_wait(&bar_acc, 0);
+        alive = __syncthreads_and(acc_ok ? 1 : 0) != 0;
+    }
+    if (alive) {
+        umma::fence_after_sync();
+        const int quad = warp & 3;
+        const int e = e0 + quad * 32 + lane;
+        const int cb = warp >> 2;  // warps 0-3: tokens 0..31, warps 4-7: tokens 32..63
+        float g[32];
+        umma::ld_32x32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), g);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const int t = t0 + cb * 32 + c;
+            if (t < n && e < E) logits[(size_t)t * E + e] = g[c];
+        }
+    } else if (tid == 0) {
+        atomicExch(err, 8u);
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 64);
 }
 
 // ─── route: one warp per token ──────────────────────────────────────────────
@@ -335,17 +509,28 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 s2, __n
     return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp16_zfill(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int MODE>  // 1: gate/up + SwiGLU -> act ; 2: down -> o
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParams p) {
     constexpr int kIn = (MODE == 1) ? kBH : kBI;            // contraction length
     constexpr int kKC = kIn / 64;                           // K steps (one quantisation group each)
-    constexpr int kRB = (MODE == 1) ? kBI / 128 : kBH / 128;  // 128-row blocks per expert matrix
-    constexpr int kARows = (MODE == 1) ? 256 : 128;         // gate + up rows, or down rows
+    // work item = (token tile, row block): 128 gate rows + the same 128 up rows, or 256 down rows;
+    // either way two M = 128 accumulators share one activation tile
+    constexpr int kRB = (MODE == 1) ? kBI / 128 : kBH / 256;
+    constexpr int kARows = 256;
     constexpr int kABytes = kARows * 128;
     constexpr int kBBytes = kNT * 128;
     constexpr int kStage = kABytes + kBBytes;
     constexpr int kTasks = kARows * 2 / kGemmThreads;       // (row, half-group) dequant tasks per thread per K step
-    constexpr uint32_t kTmemCols = 256;
+    constexpr uint32_t kTmemCols = 512;
+    static_assert(kKC % 2 == 0, "the weight prefetch ring alternates between two register sets");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -365,7 +550,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = tmem_slot;
+    const uint32_t stages_addr = smem_u32(stages);
 
+#ifdef MOE_GEMM_PROF
+    long long pf[6] = {0, 0, 0, 0, 0, 0};
+    long long pt = clock64();
+#define GPROF(i) do { if (tid == 0) { const long long _n = clock64(); pf[i] += _n - pt; pt = _n; } } while (0)
+#else
+#define GPROF(i) do { } while (0)
+#endif
     const int n_items = *p.n_tiles * kRB;
     uint32_t it = 0;       // K steps issued so far by this CTA (drives stage ring and parities)
     uint32_t n_done = 0;   // items finished by this CTA
@@ -376,106 +569,122 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
         const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
         const int N = (nt + 15) & ~15;
         const uint8_t* ex = (e < p.E) ? p.experts + (size_t)e * p.lay.expert_size : p.shared;
-        if (MODE == 1 && tid < kNT) s_tok[tid] = (tid < nt) ? p.slot_token[s0 + tid] : 0;
+        if (MODE == 1)
+            for (int j = tid; j < kNT; j += kGemmThreads) s_tok[j] = (j < nt) ? p.slot_token[s0 + j] : 0;
 
         // this thread's dequant tasks: (row of the A tile, half of the 64-column group)
         const uint32_t* wp[kTasks];
         const uint16_t* sp[kTasks];
         const uint16_t* bp[kTasks];
-        int arow[kTasks], ahalf[kTasks];
+        uint32_t aoff[kTasks][4];  // swizzled byte offsets of the task's four 16-byte outputs inside a stage
 #pragma unroll
         for (int q = 0; q < kTasks; ++q) {
             const int task = tid + q * kGemmThreads;
-            const int r = task >> 1;
-            arow[q] = r;
-            ahalf[q] = task & 1;
+            const int r = task >> 1, half = task & 1;
             if (MODE == 1) {
                 const int up = r >> 7, row = rb * 128 + (r & 127);
-                wp[q] = reinterpret_cast<const uint32_t*>(ex + (up ? p.lay.up_w : p.lay.gate_w)) + (size_t)row * (kBH / 8) + ahalf[q] * 4;
+                wp[q] = reinterpret_cast<const uint32_t*>(ex + (up ? p.lay.up_w : p.lay.gate_w)) + (size_t)row * (kBH / 8) + half * 4;
                 sp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_s : p.lay.gate_s)) + (size_t)row * (kBH / kGroup);
                 bp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_b : p.lay.gate_b)) + (size_t)row * (kBH / kGroup);
             } else {
-                const int row = rb * 128 + r;
-                wp[q] = reinterpret_cast<const uint32_t*>(ex + p.lay.down_w) + (size_t)row * (kBI / 8) + ahalf[q] * 4;
+                const int row = rb * 256 + r;
+                wp[q] = reinterpret_cast<const uint32_t*>(ex + p.lay.down_w) + (size_t)row * (kBI / 8) + half * 4;
                 sp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_s) + (size_t)row * (kBI / kGroup);
                 bp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_b) + (size_t)row * (kBI / kGroup);
             }
+            const uint32_t sub = (r >= 128) ? 128u * 128u : 0u;
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) aoff[q][wi] = sub + umma::sw128_offset((uint32_t)(r & 127), (uint32_t)(half * 4 + wi));
         }
         __syncthreads();  // s_tok visible
 
-        // software prefetch of K step 0
-        uint4 wq[kTasks];
-        uint16_t sq[kTasks], bq[kTasks];
+        // Asynchronous copy of the activation tile of K step `kc` into stage `st`: N rows of 128 bytes,
+        // rows beyond the tile's tokens are zero-filled.
+        auto issue_b = [&](int kc, uint32_t st) {
+            const uint32_t b_base = stages_addr + st * kStage + kABytes;
+            for (int q = tid; q < N * 8; q += kGemmThreads) {
+                const int j = q >> 3, c = q & 7;
+                const __nv_bfloat16* src = (MODE == 1) ? p.x + (size_t)s_tok[j] * kBH : p.act + (size_t)(s0 + (j < nt ? j : 0)) * kBI;
+                cp16_zfill(b_base + umma::sw128_offset((uint32_t)j, (uint32_t)c), src + kc * 64 + c * 8, j < nt ? 16u : 0u);
+            }
+        };
+
+        // weight words, scales and biases of two K steps in flight in registers
+        uint4 wq[2][kTasks];
+        uint16_t sq[2][kTasks], bq[2][kTasks];
+        auto load_a = [&](int kc, uint4 (&w)[kTasks], uint16_t (&sc)[kTasks], uint16_t (&bi)[kTasks]) {
 #pragma unroll
-        for (int q = 0; q < kTasks; ++q) {
-            wq[q] = ld_stream_u4(wp[q]);
-            sq[q] = __ldg(sp[q]);
-            bq[q] = __ldg(bp[q]);
+            for (int q = 0; q < kTasks; ++q) {
+                w[q] = ld_stream_u4(wp[q] + kc * 8);
+                sc[q] = __ldg(sp[q] + kc);
+                bi[q] = __ldg(bp[q] + kc);
+            }
+        };
+
+        bool ok = true;
+        {   // prologue: activations of K step 0, weights of K steps 0 and 1
+            const uint32_t st0 = it % kStages, use0 = it / kStages;
+            if (use0 > 0) ok = mbar_wait(&bar_empty[st0], (use0 - 1) & 1);
+            issue_b(0, st0);
+            cp_commit_group();
+            load_a(0, wq[0], sq[0], bq[0]);
+            load_a(1, wq[1], sq[1], bq[1]);
         }
 
         const uint32_t idesc = umma::make_idesc_bf16(128, (uint32_t)N);
-        for (int kc = 0; kc < kKC; ++kc, ++it) {
-            const uint32_t st = it % kStages, use = it / kStages;
-            unsigned char* a_tile = stages + st * kStage;
-            unsigned char* b_tile = a_tile + kABytes;
-            bool ok = true;
-            if (use > 0) ok = mbar_wait(&bar_empty[st], (use - 1) & 1);  // the MMAs that read this stage are done
-
-            // ---- A: dequantise this K step's 64 columns of every row of the tile ----
-            uint4 wc[kTasks];
-            uint16_t sc[kTasks], bc[kTasks];
-#pragma unroll
-            for (int q = 0; q < kTasks; ++q) { wc[q] = wq[q]; sc[q] = sq[q]; bc[q] = bq[q]; }
+        auto k_step = [&](int kc, uint4 (&w)[kTasks], uint16_t (&sc)[kTasks], uint16_t (&bi)[kTasks]) -> bool {
+            const uint32_t st = it % kStages;
+            GPROF(5);
+            // next K step's activations go into the next stage once the MMAs that read it are done
             if (kc + 1 < kKC) {
-#pragma unroll
-                for (int q = 0; q < kTasks; ++q) {
-                    wq[q] = ld_stream_u4(wp[q] + (kc + 1) * 8);
-                    sq[q] = __ldg(sp[q] + kc + 1);
-                    bq[q] = __ldg(bp[q] + kc + 1);
-                }
+                const uint32_t nst = (it + 1) % kStages, nuse = (it + 1) / kStages;
+                if (nuse > 0) ok = mbar_wait(&bar_empty[nst], (nuse - 1) & 1) && ok;
+                issue_b(kc + 1, nst);
             }
+            cp_commit_group();
+            GPROF(0);
+            // ---- A: dequantise this K step's 64 columns of every row of the tile ----
+            unsigned char* a_tile = stages + st * kStage;
 #pragma unroll
             for (int q = 0; q < kTasks; ++q) {
                 const uint32_t s32 = (uint32_t)sc[q] | ((uint32_t)sc[q] << 16);
-                const uint32_t b32 = (uint32_t)bc[q] | ((uint32_t)bc[q] << 16);
+                const uint32_t b32 = (uint32_t)bi[q] | ((uint32_t)bi[q] << 16);
                 const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s32);
                 const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&b32);
-                const uint32_t words[4] = {wc[q].x, wc[q].y, wc[q].z, wc[q].w};
-                unsigned char* sub = a_tile + ((MODE == 1 && arow[q] >= 128) ? 128 * 128 : 0);
-                const uint32_t r = (uint32_t)(arow[q] & 127);
+                const uint32_t words[4] = {w[q].x, w[q].y, w[q].z, w[q].w};
 #pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const uint4 v = dequant_word(words[wi], s2, b2);
-                    *reinterpret_cast<uint4*>(sub + umma::sw128_offset(r, (uint32_t)(ahalf[q] * 4 + wi))) = v;
-                }
+                for (int wi = 0; wi < 4; ++wi)
+                    *reinterpret_cast<uint4*>(a_tile + aoff[q][wi]) = dequant_word(words[wi], s2, b2);
             }
-            // ---- B: this K step's 64 columns of every token row of the tile ----
-            for (int q = tid; q < N * 8; q += kGemmThreads) {
-                const int j = q >> 3, c = q & 7;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (j < nt) {
-                    const __nv_bfloat16* src = (MODE == 1) ? p.x + (size_t)s_tok[j] * kBH : p.act + (size_t)(s0 + j) * kBI;
-                    v = __ldg(reinterpret_cast<const uint4*>(src + kc * 64) + c);
-                }
-                *reinterpret_cast<uint4*>(b_tile + umma::sw128_offset((uint32_t)j, (uint32_t)c)) = v;
-            }
+            if (kc + 2 < kKC) load_a(kc + 2, w, sc, bi);  // refill this register set
+            GPROF(1);
+            cp_wait_group<1>();  // this K step's activation tile has landed (the next one may be in flight)
             umma::fence_smem_to_async();
-            if (!__syncthreads_and(ok ? 1 : 0)) { alive = false; break; }
+            GPROF(2);
+            if (!__syncthreads_and(ok ? 1 : 0)) return false;
+            GPROF(3);
             if (tid == 0) {
                 umma::fence_after_sync();
-                const uint32_t a_addr = smem_u32(a_tile), b_addr = smem_u32(b_tile);
+                const uint32_t a_addr = stages_addr + st * kStage, b_addr = a_addr + kABytes;
 #pragma unroll
                 for (int k16 = 0; k16 < 4; ++k16) {
                     const uint64_t db = umma::make_desc_sw128_kmajor(b_addr + k16 * 32);
                     const uint32_t acc = (kc > 0 || k16 > 0) ? 1u : 0u;
                     umma::mma_bf16(tmem, umma::make_desc_sw128_kmajor(a_addr + k16 * 32), db, idesc, acc);
-                    if (MODE == 1)
-                        umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
+                    umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
                 }
                 umma::commit(&bar_empty[st]);
                 if (kc == kKC - 1) umma::commit(&bar_acc);
             }
+            GPROF(4);
+            ++it;
+            return true;
+        };
+        for (int kc = 0; kc < kKC && alive; kc += 2) {
+            alive = k_step(kc, wq[0], sq[0], bq[0]);
+            if (alive) alive = k_step(kc + 1, wq[1], sq[1], bq[1]);
         }
+        cp_wait_group<0>();
         if (!alive) break;
 
         // ---- epilogue: TMEM -> registers -> global ----
@@ -484,29 +693,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
         umma::fence_after_sync();
         {
             const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 belong to this warp
-            const int row = rb * 128 + quad * 32 + lane;  // output row inside the expert matrix
-            for (int cb = (warp >> 2); cb * 32 < N; cb += 2) {
+            constexpr int kColGroups = kGemmThreads / 128;  // warps sharing a lane quadrant split the columns
+            for (int cb = (warp >> 2); cb * 32 < N; cb += kColGroups) {
                 const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32);
-                float g[32];
+                float g[32], u[32];
                 umma::ld_32x32(taddr, g);
+                umma::ld_32x32(taddr + kNT, u);
                 if (MODE == 1) {
-                    float u[32];
-                    umma::ld_32x32(taddr + kNT, u);
+                    const int row = rb * 128 + quad * 32 + lane;  // gate/up row inside the expert matrix
                     const int pos = (row & ~7) | ipos(row & 7);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int col = cb * 32 + c;
                         if (col < nt) {
                             // swiglu_fused (reference src/math_util.rs:254-259)
-                            const float a = g[c] / (1.0f + expf(-g[c])) * u[c];
+                            const float a = g[c] / (1.0f + __expf(-g[c])) * u[c];
                             p.act[(size_t)(s0 + col) * kBI + pos] = __float2bfloat16_rn(a);
                         }
                     }
                 } else {
+                    const int row = rb * 256 + quad * 32 + lane;  // first accumulator: rows +0, second: rows +128
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int col = cb * 32 + c;
-                        if (col < nt) p.o[(size_t)(s0 + col) * kBH + row] = __float2bfloat16_rn(g[c]);
+                        if (col < nt) {
+                            p.o[(size_t)(s0 + col) * kBH + row] = __float2bfloat16_rn(g[c]);
+                            p.o[(size_t)(s0 + col) * kBH + row + 128] = __float2bfloat16_rn(u[c]);
+                        }
                     }
                 }
             }
@@ -517,6 +730,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     }
 
     if (!alive && tid == 0) atomicExch(p.err, 7u);
+#ifdef MOE_GEMM_PROF
+    if (tid == 0 && blockIdx.x == 0)
+        printf("gemm<%d> cta0: steps %u  issueB %lld  dequant %lld  cpwait+fence %lld  sync %lld  mma-issue %lld  other(epilogue etc) %lld\n",
+               MODE, it, pf[0], pf[1], pf[2], pf[3], pf[4], pf[5]);
+#endif
+    cp_wait_group<0>();
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, kTmemCols);
@@ -562,7 +781,7 @@ static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
 
 template <int MODE>
 static constexpr size_t gemm_smem_bytes() {
-    return (size_t)kStages * (((MODE == 1) ? 256 : 128) * 128 + kNT * 128) + 1024;
+    return (size_t)kStages * (256 * 128 + kNT * 128) + 1024;
 }
 
 int batch_reserve(moe_engine* e, int32_t n_tokens) {
@@ -595,6 +814,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     bw.capacity = n_tokens;
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<1>()));
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<2>()));
+    MOE_CUDA(cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRtStage + 1024));
     return MOE_OK;
 }
 
@@ -627,7 +847,8 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
 
     MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.xf, bw.sgate);
-    batch_router_kernel<<<dim3((n + 63) / 64, (E + 63) / 64), 256, 0, st>>>(bw.xf, n, E, ly, bw.logits);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, 2 * kRtStage + 1024, st>>>(
+        bw.xf, n, E, ly, bw.logits, e->dec_sync + 2);
     batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts);
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
