@@ -20,15 +20,15 @@
 //            . act_tile^T ; epilogue -> O (bf16, one row per slot)
 //   combine  per token: h_out = h_in + sum_k w_k O[slot(t,k)] + sigmoid(sg) O[shared slot]
 //
-// GEMM operand staging: weights are dequantised by all 256 threads of the CTA
+// GEMM operand staging: weights are dequantised by the 512 producer threads of the CTA
 // (128-bit nibble loads, bf16x2 arithmetic) straight into shared memory in the
 // K-major 128-byte-swizzled layout tcgen05.mma reads; one K step = one 64-column
 // quantisation group = one 128-byte swizzle row.  A 4-bit word holds columns
 // c..c+7; masking pairs (n, n+4) without shifting them into order yields the
 // column order [0,4,1,5,2,6,3,7] inside every 8-column block, so the activations
 // are stored with the same interleave (the dot product does not care about the
-// order of its terms).  One thread issues the MMAs; their completion frees the
-// stage through tcgen05.commit on an mbarrier.  Weights (A) take the M = 128
+// order of its terms).  A dedicated warp issues the MMAs (hand-off through "full"
+// mbarriers); their completion frees the stage through tcgen05.commit on an mbarrier.  Weights (A) take the M = 128
 // side, tokens (B) the N side, so ragged per-expert token counts only change N.
 #include "umma.cuh"
 
@@ -37,7 +37,9 @@ namespace moe {
 constexpr int kBH = 2048;  // hidden
 constexpr int kBI = 512;   // moe_intermediate_size == shared_expert_intermediate_size
 constexpr int kNT = 256;   // tokens per tile (MMA N, padded to a multiple of 16)
-constexpr int kGemmThreads = 512;
+constexpr int kProdWarps = 16;                  // operand producers / epilogue
+constexpr int kProdThreads = kProdWarps * 32;
+constexpr int kGemmThreads = kProdThreads + 32;  // + one MMA-issuing warp
 constexpr int kStages = 3;
 constexpr int kMaxEPerLane = 16;
 
@@ -517,6 +519,27 @@ __device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Bounded, abort-aware mbarrier wait: gives up after about a second of SM clocks or as
+// soon as another warp of the CTA has given up (s_abort), so that a broken pipeline
+// drains instead of hanging.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* s_abort) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0u && (*s_abort || clock64() - t0 > kWaitCycles)) {
+            *s_abort = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Warp roles: warps 0..15 produce the operand tiles (dequantised weights, copied
+// activations) and run the epilogue; warp 16 only issues the MMAs, because a
+// tcgen05.mma issue blocks its thread for about as long as the MMA runs.
 template <int MODE>  // 1: gate/up + SwiGLU -> act ; 2: down -> o
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParams p) {
     constexpr int kIn = (MODE == 1) ? kBH : kBI;            // contraction length
@@ -528,21 +551,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     constexpr int kABytes = kARows * 128;
     constexpr int kBBytes = kNT * 128;
     constexpr int kStage = kABytes + kBBytes;
-    constexpr int kTasks = kARows * 2 / kGemmThreads;       // (row, half-group) dequant tasks per thread per K step
     constexpr uint32_t kTmemCols = 512;
+    static_assert(kARows * 2 == kProdThreads, "one (row, half-group) dequant task per producer thread");
     static_assert(kKC % 2 == 0, "the weight prefetch ring alternates between two register sets");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t bar_empty[kStages];
-    __shared__ uint64_t bar_acc;
+    __shared__ uint64_t bar_full[kStages];   // producers -> MMA warp: operands of a stage are in place
+    __shared__ uint64_t bar_empty[kStages];  // MMA completion -> producers: stage may be overwritten
+    __shared__ uint64_t bar_acc;             // MMA completion -> epilogue: accumulators are final
+    __shared__ uint64_t bar_tfree;           // epilogue -> MMA warp: accumulators have been read
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_tok[kNT];
+    __shared__ int s_abort_mem;
+    volatile int* s_abort = &s_abort_mem;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) mbar_init(&bar_empty[i], 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&bar_full[i], kProdWarps);
+            mbar_init(&bar_empty[i], 1);
+        }
         mbar_init(&bar_acc, 1);
+        mbar_init(&bar_tfree, kProdWarps);
+        s_abort_mem = 0;
         mbar_fence_init();
     }
     if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
@@ -552,192 +583,191 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     const uint32_t tmem = tmem_slot;
     const uint32_t stages_addr = smem_u32(stages);
 
-#ifdef MOE_GEMM_PROF
-    long long pf[6] = {0, 0, 0, 0, 0, 0};
-    long long pt = clock64();
-#define GPROF(i) do { if (tid == 0) { const long long _n = clock64(); pf[i] += _n - pt; pt = _n; } } while (0)
-#else
-#define GPROF(i) do { } while (0)
-#endif
     const int n_items = *p.n_tiles * kRB;
-    uint32_t it = 0;       // K steps issued so far by this CTA (drives stage ring and parities)
+    uint32_t it = 0;       // K steps so far (drives the stage ring and the mbarrier parities)
     uint32_t n_done = 0;   // items finished by this CTA
     bool alive = true;
 
-    for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
-        const int tile = item / kRB, rb = item - tile * kRB;
-        const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
-        const int N = (nt + 15) & ~15;
-        const uint8_t* ex = (e < p.E) ? p.experts + (size_t)e * p.lay.expert_size : p.shared;
-        if (MODE == 1)
-            for (int j = tid; j < kNT; j += kGemmThreads) s_tok[j] = (j < nt) ? p.slot_token[s0 + j] : 0;
-
-        // this thread's dequant tasks: (row of the A tile, half of the 64-column group)
-        const uint32_t* wp[kTasks];
-        const uint16_t* sp[kTasks];
-        const uint16_t* bp[kTasks];
-        uint32_t aoff[kTasks][4];  // swizzled byte offsets of the task's four 16-byte outputs inside a stage
+    if (warp == kProdWarps) {
+        // ─── MMA issuer ───────────────────────────────────────────────────────
+        for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+            const int tile = item / kRB;
+            const int nt = p.tile_list[3 * tile + 2];
+            const uint32_t idesc = umma::make_idesc_bf16(128, (uint32_t)((nt + 15) & ~15));
+            for (int kc = 0; kc < kKC && alive; ++kc, ++it) {
+                const uint32_t st = it % kStages, use = it / kStages;
+                bool ok = wait_or_abort(&bar_full[st], use & 1, s_abort);
+                // the previous item's accumulators must have been read before they are overwritten
+                if (kc == 0 && n_done > 0) ok = wait_or_abort(&bar_tfree, (n_done - 1) & 1, s_abort) && ok;
+                alive = __all_sync(0xffffffffu, ok);
+                if (!alive) break;
+                if (lane == 0) {
+                    umma::fence_after_sync();
+                    const uint32_t a_addr = stages_addr + st * kStage, b_addr = a_addr + kABytes;
 #pragma unroll
-        for (int q = 0; q < kTasks; ++q) {
-            const int task = tid + q * kGemmThreads;
-            const int r = task >> 1, half = task & 1;
+                    for (int k16 = 0; k16 < 4; ++k16) {
+                        const uint64_t db = umma::make_desc_sw128_kmajor(b_addr + k16 * 32);
+                        const uint32_t acc = (kc > 0 || k16 > 0) ? 1u : 0u;
+                        umma::mma_bf16(tmem, umma::make_desc_sw128_kmajor(a_addr + k16 * 32), db, idesc, acc);
+                        umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
+                    }
+                    umma::commit(&bar_empty[st]);
+                    if (kc == kKC - 1) umma::commit(&bar_acc);
+                }
+                __syncwarp();
+            }
+            ++n_done;
+        }
+    } else {
+        // ─── producers + epilogue ─────────────────────────────────────────────
+        for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+            const int tile = item / kRB, rb = item - tile * kRB;
+            const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
+            const int N = (nt + 15) & ~15;
+            const uint8_t* ex = (e < p.E) ? p.experts + (size_t)e * p.lay.expert_size : p.shared;
+
+            // this thread's dequant task: (row of the A tile, half of the 64-column group)
+            const int r = tid >> 1, half = tid & 1;
+            const uint32_t* wp;
+            const uint16_t* sp;
+            const uint16_t* bp;
             if (MODE == 1) {
                 const int up = r >> 7, row = rb * 128 + (r & 127);
-                wp[q] = reinterpret_cast<const uint32_t*>(ex + (up ? p.lay.up_w : p.lay.gate_w)) + (size_t)row * (kBH / 8) + half * 4;
-                sp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_s : p.lay.gate_s)) + (size_t)row * (kBH / kGroup);
-                bp[q] = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_b : p.lay.gate_b)) + (size_t)row * (kBH / kGroup);
+                wp = reinterpret_cast<const uint32_t*>(ex + (up ? p.lay.up_w : p.lay.gate_w)) + (size_t)row * (kBH / 8) + half * 4;
+                sp = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_s : p.lay.gate_s)) + (size_t)row * (kBH / kGroup);
+                bp = reinterpret_cast<const uint16_t*>(ex + (up ? p.lay.up_b : p.lay.gate_b)) + (size_t)row * (kBH / kGroup);
             } else {
                 const int row = rb * 256 + r;
-                wp[q] = reinterpret_cast<const uint32_t*>(ex + p.lay.down_w) + (size_t)row * (kBI / 8) + half * 4;
-                sp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_s) + (size_t)row * (kBI / kGroup);
-                bp[q] = reinterpret_cast<const uint16_t*>(ex + p.lay.down_b) + (size_t)row * (kBI / kGroup);
+                wp = reinterpret_cast<const uint32_t*>(ex + p.lay.down_w) + (size_t)row * (kBI / 8) + half * 4;
+                sp = reinterpret_cast<const uint16_t*>(ex + p.lay.down_s) + (size_t)row * (kBI / kGroup);
+                bp = reinterpret_cast<const uint16_t*>(ex + p.lay.down_b) + (size_t)row * (kBI / kGroup);
             }
-            const uint32_t sub = (r >= 128) ? 128u * 128u : 0u;
+            uint32_t aoff[4];  // swizzled byte offsets of the task's four 16-byte outputs inside a stage
+            {
+                const uint32_t sub = (r >= 128) ? 128u * 128u : 0u;
 #pragma unroll
-            for (int wi = 0; wi < 4; ++wi) aoff[q][wi] = sub + umma::sw128_offset((uint32_t)(r & 127), (uint32_t)(half * 4 + wi));
-        }
-        __syncthreads();  // s_tok visible
-
-        // Asynchronous copy of the activation tile of K step `kc` into stage `st`: N rows of 128 bytes,
-        // rows beyond the tile's tokens are zero-filled.
-        auto issue_b = [&](int kc, uint32_t st) {
-            const uint32_t b_base = stages_addr + st * kStage + kABytes;
-            for (int q = tid; q < N * 8; q += kGemmThreads) {
+                for (int wi = 0; wi < 4; ++wi) aoff[wi] = sub + umma::sw128_offset((uint32_t)(r & 127), (uint32_t)(half * 4 + wi));
+            }
+            // this thread's pieces of the activation tile: piece q = tid + 512 * i -> (token row q >> 3, chunk q & 7)
+            constexpr int kBPieces = kNT * 8 / kProdThreads;  // 4
+            const __nv_bfloat16* bsrc[kBPieces];
+            uint32_t boff[kBPieces];
+#pragma unroll
+            for (int i = 0; i < kBPieces; ++i) {
+                const int q = tid + i * kProdThreads;
                 const int j = q >> 3, c = q & 7;
-                const __nv_bfloat16* src = (MODE == 1) ? p.x + (size_t)s_tok[j] * kBH : p.act + (size_t)(s0 + (j < nt ? j : 0)) * kBI;
-                cp16_zfill(b_base + umma::sw128_offset((uint32_t)j, (uint32_t)c), src + kc * 64 + c * 8, j < nt ? 16u : 0u);
+                const int jj = j < nt ? j : 0;
+                bsrc[i] = ((MODE == 1) ? p.x + (size_t)__ldg(p.slot_token + s0 + jj) * kBH : p.act + (size_t)(s0 + jj) * kBI) + c * 8;
+                boff[i] = kABytes + umma::sw128_offset((uint32_t)j, (uint32_t)c);
             }
-        };
-
-        // weight words, scales and biases of two K steps in flight in registers
-        uint4 wq[2][kTasks];
-        uint16_t sq[2][kTasks], bq[2][kTasks];
-        auto load_a = [&](int kc, uint4 (&w)[kTasks], uint16_t (&sc)[kTasks], uint16_t (&bi)[kTasks]) {
+            // asynchronous copy of the activation tile of K step kc into stage st (rows >= nt zero-filled)
+            auto issue_b = [&](int kc, uint32_t st) {
+                const uint32_t base = stages_addr + st * kStage;
 #pragma unroll
-            for (int q = 0; q < kTasks; ++q) {
-                w[q] = ld_stream_u4(wp[q] + kc * 8);
-                sc[q] = __ldg(sp[q] + kc);
-                bi[q] = __ldg(bp[q] + kc);
-            }
-        };
+                for (int i = 0; i < kBPieces; ++i) {
+                    const int j = (tid + i * kProdThreads) >> 3;
+                    if (j < N) cp16_zfill(base + boff[i], bsrc[i] + kc * 64, j < nt ? 16u : 0u);
+                }
+            };
+            // weight words, scales and biases of two K steps in flight in registers
+            uint4 wq[2];
+            uint16_t sq[2], bq[2];
+            auto load_a = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
+                w = ld_stream_u4(wp + kc * 8);
+                sc = __ldg(sp + kc);
+                bi = __ldg(bp + kc);
+            };
 
-        bool ok = true;
-        {   // prologue: activations of K step 0, weights of K steps 0 and 1
-            const uint32_t st0 = it % kStages, use0 = it / kStages;
-            if (use0 > 0) ok = mbar_wait(&bar_empty[st0], (use0 - 1) & 1);
-            issue_b(0, st0);
-            cp_commit_group();
-            load_a(0, wq[0], sq[0], bq[0]);
-            load_a(1, wq[1], sq[1], bq[1]);
-        }
-
-        const uint32_t idesc = umma::make_idesc_bf16(128, (uint32_t)N);
-        auto k_step = [&](int kc, uint4 (&w)[kTasks], uint16_t (&sc)[kTasks], uint16_t (&bi)[kTasks]) -> bool {
-            const uint32_t st = it % kStages;
-            GPROF(5);
-            // next K step's activations go into the next stage once the MMAs that read it are done
-            if (kc + 1 < kKC) {
-                const uint32_t nst = (it + 1) % kStages, nuse = (it + 1) / kStages;
-                if (nuse > 0) ok = mbar_wait(&bar_empty[nst], (nuse - 1) & 1) && ok;
-                issue_b(kc + 1, nst);
+            bool ok = true;
+            {   // prologue: activations of K step 0, weights of K steps 0 and 1
+                const uint32_t st0 = it % kStages, use0 = it / kStages;
+                if (use0 > 0) ok = wait_or_abort(&bar_empty[st0], (use0 - 1) & 1, s_abort);
+                issue_b(0, st0);
+                cp_commit_group();
+                load_a(0, wq[0], sq[0], bq[0]);
+                load_a(1, wq[1], sq[1], bq[1]);
             }
-            cp_commit_group();
-            GPROF(0);
-            // ---- A: dequantise this K step's 64 columns of every row of the tile ----
-            unsigned char* a_tile = stages + st * kStage;
-#pragma unroll
-            for (int q = 0; q < kTasks; ++q) {
-                const uint32_t s32 = (uint32_t)sc[q] | ((uint32_t)sc[q] << 16);
-                const uint32_t b32 = (uint32_t)bi[q] | ((uint32_t)bi[q] << 16);
+            auto k_step = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
+                const uint32_t st = it % kStages;
+                // next K step's activations go into the next stage once the MMAs that read it are done
+                if (kc + 1 < kKC) {
+                    const uint32_t nst = (it + 1) % kStages, nuse = (it + 1) / kStages;
+                    if (nuse > 0) ok = wait_or_abort(&bar_empty[nst], (nuse - 1) & 1, s_abort) && ok;
+                    issue_b(kc + 1, nst);
+                }
+                cp_commit_group();
+                // dequantise this K step's 64 columns of this thread's row half
+                unsigned char* a_tile = stages + st * kStage;
+                const uint32_t s32 = (uint32_t)sc | ((uint32_t)sc << 16);
+                const uint32_t b32 = (uint32_t)bi | ((uint32_t)bi << 16);
                 const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s32);
                 const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&b32);
-                const uint32_t words[4] = {w[q].x, w[q].y, w[q].z, w[q].w};
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi)
-                    *reinterpret_cast<uint4*>(a_tile + aoff[q][wi]) = dequant_word(words[wi], s2, b2);
+                    *reinterpret_cast<uint4*>(a_tile + aoff[wi]) = dequant_word(words[wi], s2, b2);
+                if (kc + 2 < kKC) load_a(kc + 2, w, sc, bi);  // refill this register set
+                cp_wait_group<1>();  // this K step's activation pieces have landed (the next ones may be in flight)
+                umma::fence_smem_to_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_full[st]);
+                ++it;
+            };
+            for (int kc = 0; kc < kKC; kc += 2) {
+                k_step(kc, wq[0], sq[0], bq[0]);
+                k_step(kc + 1, wq[1], sq[1], bq[1]);
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             }
-            if (kc + 2 < kKC) load_a(kc + 2, w, sc, bi);  // refill this register set
-            GPROF(1);
-            cp_wait_group<1>();  // this K step's activation tile has landed (the next one may be in flight)
-            umma::fence_smem_to_async();
-            GPROF(2);
-            if (!__syncthreads_and(ok ? 1 : 0)) return false;
-            GPROF(3);
-            if (tid == 0) {
-                umma::fence_after_sync();
-                const uint32_t a_addr = stages_addr + st * kStage, b_addr = a_addr + kABytes;
+            if (!alive) break;
+
+            // ---- epilogue: TMEM -> registers -> global ----
+            alive = __all_sync(0xffffffffu, wait_or_abort(&bar_acc, n_done & 1, s_abort));
+            if (!alive) break;
+            umma::fence_after_sync();
+            {
+                const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 belong to this warp
+                constexpr int kColGroups = kProdWarps / 4;  // warps sharing a lane quadrant split the columns
+                for (int cb = (warp >> 2); cb * 32 < N; cb += kColGroups) {
+                    const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32);
+                    float g[32], u[32];
+                    umma::ld_32x32(taddr, g);
+                    umma::ld_32x32(taddr + kNT, u);
+                    if (MODE == 1) {
+                        const int row = rb * 128 + quad * 32 + lane;  // gate/up row inside the expert matrix
+                        const int pos = (row & ~7) | ipos(row & 7);
 #pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16) {
-                    const uint64_t db = umma::make_desc_sw128_kmajor(b_addr + k16 * 32);
-                    const uint32_t acc = (kc > 0 || k16 > 0) ? 1u : 0u;
-                    umma::mma_bf16(tmem, umma::make_desc_sw128_kmajor(a_addr + k16 * 32), db, idesc, acc);
-                    umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
+                        for (int c = 0; c < 32; ++c) {
+                            const int col = cb * 32 + c;
+                            if (col < nt) {
+                                // swiglu_fused (reference src/math_util.rs:254-259)
+                                const float a = __fdividef(g[c], 1.0f + __expf(-g[c])) * u[c];
+                                p.act[(size_t)(s0 + col) * kBI + pos] = __float2bfloat16_rn(a);
+                            }
+                        }
+                    } else {
+                        const int row = rb * 256 + quad * 32 + lane;  // first accumulator: rows +0, second: rows +128
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const int col = cb * 32 + c;
+                            if (col < nt) {
+                                p.o[(size_t)(s0 + col) * kBH + row] = __float2bfloat16_rn(g[c]);
+                                p.o[(size_t)(s0 + col) * kBH + row + 128] = __float2bfloat16_rn(u[c]);
+                            }
+                        }
+                    }
                 }
-                umma::commit(&bar_empty[st]);
-                if (kc == kKC - 1) umma::commit(&bar_acc);
             }
-            GPROF(4);
-            ++it;
-            return true;
-        };
-        for (int kc = 0; kc < kKC && alive; kc += 2) {
-            alive = k_step(kc, wq[0], sq[0], bq[0]);
-            if (alive) alive = k_step(kc + 1, wq[1], sq[1], bq[1]);
+            ++n_done;
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_tfree);  // this warp has read its part of the accumulators
         }
         cp_wait_group<0>();
-        if (!alive) break;
-
-        // ---- epilogue: TMEM -> registers -> global ----
-        const bool acc_ok = mbar_wait(&bar_acc, n_done & 1);
-        if (!__syncthreads_and(acc_ok ? 1 : 0)) { alive = false; break; }
-        umma::fence_after_sync();
-        {
-            const int quad = warp & 3;                 // TMEM lanes 32*quad .. +31 belong to this warp
-            constexpr int kColGroups = kGemmThreads / 128;  // warps sharing a lane quadrant split the columns
-            for (int cb = (warp >> 2); cb * 32 < N; cb += kColGroups) {
-                const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32);
-                float g[32], u[32];
-                umma::ld_32x32(taddr, g);
-                umma::ld_32x32(taddr + kNT, u);
-                if (MODE == 1) {
-                    const int row = rb * 128 + quad * 32 + lane;  // gate/up row inside the expert matrix
-                    const int pos = (row & ~7) | ipos(row & 7);
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int col = cb * 32 + c;
-                        if (col < nt) {
-                            // swiglu_fused (reference src/math_util.rs:254-259)
-                            const float a = g[c] / (1.0f + __expf(-g[c])) * u[c];
-                            p.act[(size_t)(s0 + col) * kBI + pos] = __float2bfloat16_rn(a);
-                        }
-                    }
-                } else {
-                    const int row = rb * 256 + quad * 32 + lane;  // first accumulator: rows +0, second: rows +128
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int col = cb * 32 + c;
-                        if (col < nt) {
-                            p.o[(size_t)(s0 + col) * kBH + row] = __float2bfloat16_rn(g[c]);
-                            p.o[(size_t)(s0 + col) * kBH + row + 128] = __float2bfloat16_rn(u[c]);
-                        }
-                    }
-                }
-            }
-        }
-        ++n_done;
-        umma::fence_before_sync();
-        __syncthreads();  // every warp has read its accumulators before the next item overwrites them
     }
 
-    if (!alive && tid == 0) atomicExch(p.err, 7u);
-#ifdef MOE_GEMM_PROF
-    if (tid == 0 && blockIdx.x == 0)
-        printf("gemm<%d> cta0: steps %u  issueB %lld  dequant %lld  cpwait+fence %lld  sync %lld  mma-issue %lld  other(epilogue etc) %lld\n",
-               MODE, it, pf[0], pf[1], pf[2], pf[3], pf[4], pf[5]);
-#endif
-    cp_wait_group<0>();
+    if (!alive && lane == 0) atomicExch(p.err, 7u);
     umma::fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // the only CTA-wide barrier after set-up: every role has left its loop
     if (warp == 0) umma::tmem_dealloc(tmem, kTmemCols);
 }
 
