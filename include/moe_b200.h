@@ -217,15 +217,27 @@ int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n);
 int moe_decode_profile(moe_engine_t* e, int enable, int64_t* stamps, int max_layers, int* points_per_layer);
 
 /* ── expert parallelism over the GPUs of one box ─────────────────────────────
- * No counterpart in the reference (single device).  Rank r keeps experts
- * [r*E/P, (r+1)*E/P) of every layer.  Peers exchange token rows through
- * device memory they map from one another: each rank exports one handle
- * (moe_ep_export), the host program gathers all handles by any means it has,
- * and gives the table to moe_ep_init. */
+ * No counterpart in the reference (single device).  One process per GPU; rank r
+ * keeps experts [r*E/P, (r+1)*E/P) of every layer, the router, the shared expert
+ * and the norms are replicated, and every rank brings its own tokens.  Token rows
+ * travel through device buffers the ranks map from one another (CUDA IPC) with
+ * plain peer stores; ranks meet through epoch flags with bounded waits.
+ *   1. every rank: moe_ep_export -> one 64-byte handle
+ *   2. the host program gathers the handles of all ranks, in rank order, by any
+ *      means it has (MPI, torch.distributed, a pipe)
+ *   3. every rank: moe_ep_init with the table of world * 64 bytes
+ *   4. every rank calls moe_ep_layer_forward_dev / moe_ep_forward_hidden_dev for the
+ *      same layer at the same point of its program (collective calls)
+ * h_in/h_out are f32 [n_local, hidden] on the device; n_local <= max_tokens_per_rank
+ * and may differ between ranks.  The expert store keeps the full-size allocation
+ * per layer; a rank only needs valid bytes for the experts it owns. */
 #define MOE_EP_HANDLE_BYTES 64
-int moe_ep_export(moe_engine_t* e, int32_t max_tokens_per_rank, void* handle_out /* MOE_EP_HANDLE_BYTES */);
-int moe_ep_init(moe_engine_t* e, int rank, int world, const void* all_handles /* world * MOE_EP_HANDLE_BYTES */);
+int moe_ep_export(moe_engine_t* e, int rank, int world, int32_t max_tokens_per_rank,
+                  void* handle_out /* MOE_EP_HANDLE_BYTES */);
+int moe_ep_init(moe_engine_t* e, const void* all_handles /* world * MOE_EP_HANDLE_BYTES */);
 int moe_ep_finalize(moe_engine_t* e);
+int moe_ep_layer_forward_dev(moe_engine_t* e, int layer, const float* h_in_dev, int32_t n_local, float* h_out_dev);
+int moe_ep_forward_hidden_dev(moe_engine_t* e, const float* emb_dev, int32_t n_local, float* out_dev);
 
 /* ── decode of one MoE block without any allocation ─────────────────────────
  * This entry point has no counterpart in the reference.  It exists for hosts

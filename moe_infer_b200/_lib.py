@@ -76,9 +76,11 @@ SIGNATURES = {
     "moe_get_record_telemetry": (_i, []),
     "moe_telemetry_get": (_i, [_vp, C.POINTER(C.c_char_p), C.POINTER(C.c_double), C.POINTER(_i)]),
     "moe_decode_profile": (_i, [_vp, _i, C.POINTER(_i64), _i, C.POINTER(_i)]),
-    "moe_ep_export": (_i, [_vp, _i32, _vp]),
-    "moe_ep_init": (_i, [_vp, _i, _i, _vp]),
+    "moe_ep_export": (_i, [_vp, _i, _i, _i32, _vp]),
+    "moe_ep_init": (_i, [_vp, _vp]),
     "moe_ep_finalize": (_i, [_vp]),
+    "moe_ep_layer_forward_dev": (_i, [_vp, _i, _vp, _i32, _vp]),
+    "moe_ep_forward_hidden_dev": (_i, [_vp, _vp, _i32, _vp]),
     "moe_layer_decode_noalloc": (_i, [C.POINTER(MoeDims), _i, C.POINTER(LayerPtrs), _vp, _vp, _vp, _vp, _vp, _i]),
     "moe_synth_normal_dev": (_i, [_vp, _vp, _i, _i64, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "moe_dev_alloc": (_i, [_vp, _sz, _pp]),

@@ -1,0 +1,279 @@
+"""Mirror of the reference's PyO3 module ``_moe_infer_rs`` (src/python_bindings.rs, src/lib.rs:33-49)
+for the Qwen3.5/3.6 MoE path, on top of the C ABI of ``libmoe_b200.so``.
+
+Same class and function names, argument meaning and exception classes as the
+reference binding: ``Model``, ``Cache``, ``Engine``, ``PyEngineSnapshot``,
+``record_engine_telemetry``, ``qwen35_moe_quantize``.  Every forward goes through the
+CUDA library; nothing here computes the MoE path on the CPU.
+
+What is NOT behind this surface yet, and how the calls behave:
+  * attention / DeltaNet are passed through (each block is h <- h + moe(rmsnorm(h)));
+  * the final norm and ``lm_head`` are not built: ``forward*`` return the hidden states
+    before the final norm, float32 [n, hidden], instead of logits [n, vocab];
+  * ``embed_lookup`` dequantises rows of the 4-bit embedding table on the host (as the
+    reference does, src/math_util.rs:205-236) and returns zeros when the table is absent;
+  * ``mtp_forward`` runs the MoE half of the MTP block on ``last_h_pre_norm`` and returns
+    float32 [hidden] (an empty array when the model has no MTP block, like the reference).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from typing import Optional
+
+import numpy as np
+
+from . import _lib as L
+from .modeldir import ARCHS, ModelDir, ModelDirWriter
+from .native import Dims, NativeEngine
+
+_MODES = tuple(f"Qwen35MoEFusedExp{i}" for i in range(1, 7))
+
+
+def record_engine_telemetry(on: bool) -> None:
+    """src/python_bindings.rs:29-32"""
+    L.load().moe_set_record_telemetry(1 if on else 0)
+
+
+class Model:
+    """src/python_bindings.rs:41-55: loads a converted model directory; RuntimeError on failure."""
+
+    def __init__(self, model_path: str):
+        try:
+            self.inner = ModelDir(model_path)
+        except (OSError, KeyError, ValueError) as e:
+            raise RuntimeError(str(e)) from e
+
+    def __repr__(self) -> str:
+        return f"Model({self.inner.get('num_hidden_layers', 0)} layers, hidden={self.inner.get('hidden_size', 0)})"
+
+
+class Cache:
+    """src/python_bindings.rs:64-100.  The MoE path is stateless; only the position and the
+    dirty flags of the reference's cache (src/cache.rs:32-42) are kept."""
+
+    def __init__(self, model: Model):
+        self.pos = 0
+        self.cpu_dirty = False
+        self.gpu_dirty = False
+
+    def reset(self) -> None:
+        self.pos = 0
+        self.cpu_dirty = False
+        self.gpu_dirty = False
+
+    def save(self, bin_path: str, json_path: str) -> None:
+        if self.gpu_dirty:
+            print("[cache] WARNING: saving cache with gpu_dirty=true", file=sys.stderr)
+        try:
+            with open(bin_path, "wb"):
+                pass
+            with open(json_path, "w") as f:
+                json.dump({"pos": self.pos}, f)
+        except OSError as e:
+            raise IOError(str(e)) from e
+
+    @staticmethod
+    def load(bin_path: str, json_path: str) -> "Cache":
+        try:
+            with open(json_path) as f:
+                meta = json.load(f)
+            os.stat(bin_path)
+        except (OSError, ValueError) as e:
+            raise IOError(str(e)) from e
+        c = Cache.__new__(Cache)
+        c.pos, c.cpu_dirty, c.gpu_dirty = int(meta.get("pos", 0)), True, False
+        return c
+
+    def __repr__(self) -> str:
+        return f"Cache(pos={self.pos})"
+
+
+class PyEngineSnapshot:
+    """src/python_bindings.rs:21-24, src/engine.rs:98-109"""
+
+    def __init__(self, pos: int, mtp_pos: int, last_h: np.ndarray):
+        self.pos, self.mtp_pos, self.last_h_pre_norm = pos, mtp_pos, last_h.copy()
+
+
+class Engine:
+    """src/python_bindings.rs:104-311.  All six ``Qwen35MoEFusedExp*`` modes map to the one B200 engine."""
+
+    def __init__(self, model: Model, pipeline_mode: str = "Qwen35MoEFusedExp2", num_active_experts: int = 0, *,
+                 expert_cache_count: int = 0, device: int = 0):
+        m = model.inner
+        arch = m.architecture
+        if pipeline_mode not in _MODES or arch not in ARCHS:
+            # reference src/engine.rs:233-235
+            raise ValueError(f"Config error: Unknown engine: engine_type={pipeline_mode!r}, arch={arch!r}")
+        per_tok = m.get_usize("num_experts_per_tok", 8)
+        k = num_active_experts or per_tok
+        if k > per_tok or k > 8:
+            raise ValueError(f"Config error: num_active_experts ({k}) exceeds num_experts_per_tok ({per_tok}) or MAX_K (8)")
+        self.model = model
+        self.pos = 0
+        self._telemetry = {}
+        self._last_h = np.zeros(m.get_usize("hidden_size"), np.float32)
+        layers = m.get_usize("num_hidden_layers")
+        mtp = m.get_usize("mtp_num_hidden_layers", 0)
+        router_probe = m.tensor("model.layers.0.mlp.gate.weight")
+        scheme = L.SCHEME_BQ4 if (router_probe is not None and router_probe.dtype == np.uint16) else L.SCHEME_INT4
+        self.dims = Dims(hidden=m.get_usize("hidden_size"), inter=m.get_usize("moe_intermediate_size", 512),
+                         shared_inter=m.get_usize("shared_expert_intermediate_size", 512),
+                         num_experts=m.get_usize("num_experts", 256), top_k=k, num_layers=layers,
+                         num_mtp_layers=mtp, vocab=m.get_usize("vocab_size"), scheme=scheme)
+        self.native = NativeEngine(self.dims, device=device)  # ValueError for unsupported dimensions
+        try:
+            for l in range(layers + mtp):
+                self._load_layer(l, f"model.layers.{l}" if l < layers else f"mtp.layers.{l - layers}")
+        except Exception:
+            self.native.close()
+            raise
+
+    def _load_layer(self, layer: int, prefix: str) -> None:
+        m, d, eng = self.model.inner, self.dims, self.native
+        path = m.expert_file(layer)
+        want = d.num_experts * eng.layout["expert_size"]
+        if not os.path.exists(path) or os.path.getsize(path) != want:
+            raise RuntimeError(f"I/O error: {path}: expected {want} bytes of packed experts")
+        eng.load_layer(layer, np.memmap(path, dtype=np.uint8, mode="r"))
+        norm = m.tensor(prefix + ".post_attention_layernorm.weight")
+        if norm is None:
+            raise RuntimeError(f"Config error: tensor {prefix}.post_attention_layernorm.weight missing")
+        eng.load_bf16(layer, L.T_POST_NORM, norm)
+        router = m.tensor(prefix + ".mlp.gate.weight")
+        if router is not None and router.dtype == np.uint16:
+            eng.load_bf16(layer, L.T_ROUTER, router.reshape(d.num_experts, d.hidden))
+        else:
+            eng.load_q4(layer, L.T_ROUTER, self._need_q4(prefix + ".mlp.gate"))
+        eng.load_q4(layer, L.T_SHARED_GATE, self._need_q4(prefix + ".mlp.shared_expert.gate_proj"))
+        eng.load_q4(layer, L.T_SHARED_UP, self._need_q4(prefix + ".mlp.shared_expert.up_proj"))
+        eng.load_q4(layer, L.T_SHARED_DOWN, self._need_q4(prefix + ".mlp.shared_expert.down_proj"))
+        eng.load_q4(layer, L.T_SHARED_SGATE, self._need_q4(prefix + ".mlp.shared_expert_gate"))
+
+    def _need_q4(self, base: str):
+        t = self.model.inner.q4(base)
+        if t is None:
+            raise RuntimeError(f"Config error: tensor {base}.weight/.scales/.biases missing")
+        return t
+
+    # ── reference surface ────────────────────────────────────────────────
+    def embed_lookup(self, input_ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(input_ids, np.int64).reshape(-1)
+        H = self.dims.hidden
+        out = np.zeros((ids.size, H), np.float32)
+        t = self.model.inner.q4("model.embed_tokens")
+        if t is None:
+            return out
+        w, s, b = t
+        for i, tok in enumerate(ids):
+            nib = np.stack([(w[tok] >> (4 * n)) & 0xF for n in range(8)], axis=-1).reshape(H).astype(np.float32)
+            sc = (s[tok].astype(np.uint32) << 16).view(np.float32).repeat(64)
+            bi = (b[tok].astype(np.uint32) << 16).view(np.float32).repeat(64)
+            out[i] = nib * sc + bi
+        return out
+
+    def _run(self, emb: np.ndarray, cache: Cache, batched: bool, mtp: bool) -> np.ndarray:
+        emb = np.ascontiguousarray(emb, np.float32).reshape(-1, self.dims.hidden)
+        if cache.cpu_dirty:
+            self.upload_cache(cache)
+        try:
+            out = self.native.forward_hidden(emb, batched=batched, mtp=mtp, check=_interrupt_pending)
+        except L.MoeError as e:
+            raise RuntimeError(str(e)) from e
+        self.pos += emb.shape[0]
+        cache.pos = self.pos
+        cache.gpu_dirty = True
+        self._last_h = out[-1].copy()
+        self._telemetry = self.native.telemetry()
+        return out
+
+    def forward_hidden(self, embeddings: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
+        return self._run(embeddings, cache, False, mtp)
+
+    def forward(self, tokens: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
+        toks = np.ascontiguousarray(tokens, np.int64).reshape(-1)
+        if toks.size == 0:
+            return np.zeros((0, self.dims.hidden), np.float32)
+        return self._run(self.embed_lookup(toks), cache, False, mtp)
+
+    def forward_batched(self, tokens: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
+        toks = np.ascontiguousarray(tokens, np.int64).reshape(-1)
+        if toks.size == 0:
+            return np.zeros((0, self.dims.hidden), np.float32)
+        return self._run(self.embed_lookup(toks), cache, True, mtp)
+
+    def upload_cache(self, cache: Cache) -> None:
+        self.pos = cache.pos
+        cache.cpu_dirty = False
+
+    def download_cache(self, cache: Cache) -> None:
+        cache.pos = self.pos
+        cache.gpu_dirty = False
+
+    def telemetry(self) -> dict:
+        return dict(self._telemetry)
+
+    def last_h_pre_norm(self) -> np.ndarray:
+        return self._last_h.copy()
+
+    def mtp_forward(self, token_id: int) -> np.ndarray:
+        if self.dims.num_mtp_layers == 0:
+            return np.zeros(0, np.float32)
+        return self.native.mtp_forward(self._last_h)
+
+    def mtp_reset(self) -> None:
+        self.native.mtp_reset()
+
+    def mtp_rollback(self, pos: int) -> None:
+        self.native.mtp_rollback(pos)
+
+    def snapshot_state(self) -> PyEngineSnapshot:
+        return PyEngineSnapshot(self.pos, self.native.mtp_pos(), self._last_h)
+
+    def restore_snapshot(self, snap: PyEngineSnapshot) -> None:
+        self.pos = snap.pos
+        self._last_h = snap.last_h_pre_norm.copy()
+        self.native.mtp_rollback(snap.mtp_pos)
+
+    def __repr__(self) -> str:
+        return f"Engine(loaded: {self.dims.num_layers} layers, hidden={self.dims.hidden})"
+
+
+def _interrupt_pending() -> bool:
+    """The reference polls ``py.check_signals()`` (src/python_bindings.rs:152); ctypes delivers
+    KeyboardInterrupt after the call returns, so nothing is pending inside the callback."""
+    return False
+
+
+def qwen35_moe_quantize(model_path: str, output_dir: str, *, version: str, scheme: str = "bq4", device: int = 0) -> None:
+    """src/python_bindings.rs:327-387: HF safetensors -> model_weights.{bin,json} + packed_experts/.
+
+    Converts the tensors of the MoE path (experts, router, shared expert, shared gate,
+    post-attention norms) with the GPU packer; attention, embedding and lm_head tensors
+    are not converted yet.
+    """
+    if version not in ("3.5", "3.6"):
+        raise ValueError(f"unknown Qwen version {version!r} (expected '3.5' or '3.6')")
+    if scheme not in ("bq4", "int4"):
+        raise ValueError(f"unknown scheme {scheme!r} (expected 'bq4' or 'int4')")
+    from .quantize import quantize_moe_checkpoint
+    quantize_moe_checkpoint(model_path, output_dir, version=version, scheme=scheme, device=device)
+
+
+def _not_built(name: str):
+    def f(*a, **k):
+        raise NotImplementedError(f"{name} is outside the Qwen3.5/3.6 MoE path this library covers")
+    f.__name__ = name
+    return f
+
+
+qwen35_dense_quantize = _not_built("qwen35_dense_quantize")
+gemma4_moe_quantize = _not_built("gemma4_moe_quantize")
+gemma4_dense_quantize = _not_built("gemma4_dense_quantize")
+
+
+class PyHfRepo:
+    def __init__(self, *a, **k):
+        raise NotImplementedError("PyHfRepo (HF download) is outside the path this library covers; there is no network here")

@@ -154,6 +154,62 @@ def run_batched(args, rank, world, local, dist, n_tokens, n_layers, scheme, zipf
     eng.close()
 
 
+def run_prefill_ep(args, rank, world, local, dist):
+    """Config 4 across `world` GPUs: experts sharded 256/P, tokens T/P per rank, dispatch/combine over peer memory."""
+    from . import ep as ephost
+    T = args.tokens or 4096
+    n_local = T // world
+    dims = Dims(num_layers=args.layers, scheme=L.SCHEME_INT4)
+    eng = NativeEngine(dims, device=local)
+    benchlib.populate_synthetic(eng, base_seed=args.seed, config_id=4)  # same seed on every rank: replicated tensors agree
+    H, E, K, I = dims.hidden, dims.num_experts, dims.top_k, dims.inter
+    emb = synth.hidden_states(args.seed, 3, T, H)[rank * n_local:(rank + 1) * n_local]
+    d_in = eng.alloc(emb.nbytes).upload(emb)
+    d_out = eng.alloc(emb.nbytes)
+    eng.ep_init(ephost.exchange_handles(eng.ep_export(rank, world, n_local)))
+    dist.barrier()
+
+    def step(i):
+        eng.ep_forward_hidden_dev(d_in.ptr, n_local, d_out.ptr)
+
+    for i in range(args.warmup):
+        step(i)
+    eng.sync()
+    dist.barrier()
+    n0 = eng.launch_count()
+    with benchlib.ClockSampler(local) as clk:
+        eng.timer_start()
+        for i in range(args.steps):
+            step(i)
+        ms = eng.timer_stop()
+        eng.sync()
+    launches = eng.launch_count() - n0
+    dist.barrier()
+    ms = dist.max(ms)
+    out = d_out.download(np.float32, (n_local, H))
+    finite = bool(np.isfinite(out).all())
+    ms_step = ms / args.steps
+    flops_layer = T * K * 6 * H * I + T * 6 * H * I + T * 2 * E * H + T * 2 * H
+    tf = flops_layer * args.layers / (ms_step / 1e3) / 1e12
+    peaks = benchlib.measured_peaks()
+    roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<1>+<2> (per GPU)", "achieved": tf / world,
+            "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
+            "frac": tf / world / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
+            "aggregate_tflops": tf, "traffic": None}
+    dist.barrier()
+    if rank == 0:
+        line = _line(args, world, "moe_prefill_tokens_per_s", "tok/s", T / (ms_step / 1e3), ms_step,
+                     f"config 4: {T}-token prefill through {args.layers} MoE layers, INT4 scheme, experts sharded "
+                     f"{E}/{world} per GPU, token dispatch/combine over NVLink peer memory", roof,
+                     {"value": None, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, launches,
+                     clk.summary(), {"tokens_per_step": T, "tokens_per_rank": n_local, "finite": finite,
+                                     "parallelism": f"ep{world}"})
+        line["scaling"] = "strong"
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    eng.close()
+
+
 def run_pack(args, rank, world, local, dist):
     dims = Dims(num_layers=1)
     eng = NativeEngine(dims, device=local)
@@ -244,6 +300,8 @@ def run(args, rank, world, local, dist):
         run_batched(args, rank, world, local, dist, args.tokens or 64, 8, L.SCHEME_BQ4, True,
                     "config 3: 64 tokens through one MoE layer, top-8 of 256, Zipf(1.1) routing, BQ4",
                     "moe_batched_decode_tokens_per_s")
+    elif args.workload == "prefill" and world > 1:
+        run_prefill_ep(args, rank, world, local, dist)
     elif args.workload == "prefill":
         run_batched(args, rank, world, local, dist, args.tokens or 4096, args.layers, L.SCHEME_INT4, False,
                     f"config 4: {args.tokens or 4096}-token prefill through {args.layers} MoE layers, INT4 scheme, "

@@ -86,6 +86,32 @@ struct BatchWork {
     int32_t max_tiles = 0;
 };
 
+// Expert-parallel state: experts of every layer are split over `world` GPUs of one box;
+// token rows travel through buffers the ranks map from one another (CUDA IPC).
+constexpr int kEpMaxWorld = 8;
+struct EpSym {                    // layout of the buffer every rank exports (byte offsets)
+    size_t flags, counts, meta, xrecv, oback, total;
+};
+struct EpState {
+    bool ready = false;
+    int rank = 0, world = 1, cap = 0;       // cap = max tokens per rank
+    int slots_cap = 0;                      // world * cap * top_k rows a rank can receive
+    EpSym sym{};
+    uint8_t* local = nullptr;               // this rank's exported buffer
+    uint8_t* peer[kEpMaxWorld] = {};        // every rank's buffer as mapped here (peer[rank] == local)
+    unsigned int epoch = 0;
+    uint8_t* work = nullptr;                // private work areas (one allocation)
+    __nv_bfloat16* act = nullptr;           // [slots_cap + cap, I]
+    __nv_bfloat16* o = nullptr;             // [slots_cap + cap, H]
+    int32_t* tile_list = nullptr;
+    int32_t* n_tiles = nullptr;
+    int32_t* base_send = nullptr;           // [E] first slot of my rows of expert e at its owner
+    int32_t* cursor = nullptr;              // [E]
+    int32_t* ident = nullptr;               // [slots_cap + cap] identity map
+    int32_t* total_recv = nullptr;          // rows received this layer
+    int max_tiles = 0;
+};
+
 }  // namespace moe
 
 struct moe_engine {
@@ -125,7 +151,7 @@ struct moe_engine {
     std::vector<std::string> tel_keys;
 
     // expert parallelism
-    int ep_rank = 0, ep_world = 1;
+    moe::EpState ep;
 };
 
 namespace moe {
@@ -149,6 +175,8 @@ void batch_destroy(moe_engine* e);
 int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_out,
                          const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx,
                          float* out_w);
+int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n_local, float* h_out);
+int ep_alloc_work(moe_engine* e);
 int refresh_layer_table(moe_engine* e);
 int check_layer_ready(moe_engine* e, int layer);
 

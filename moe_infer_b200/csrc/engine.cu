@@ -256,6 +256,7 @@ void moe_engine_destroy(moe_engine_t* e) {
         if (lh.experts) cudaFree(lh.experts);
         if (lh.aux) cudaFree(lh.aux);
     }
+    moe_ep_finalize(e);
     decode_destroy(e);
     batch_destroy(e);
     if (e->layers_dev) cudaFree(e->layers_dev);

@@ -805,6 +805,206 @@ __global__ void __launch_bounds__(256) batch_combine_kernel(const float* __restr
     op[1] = make_float4(out[4], out[5], out[6], out[7]);
 }
 
+// ─── expert parallelism: dispatch / combine over peer memory ────────────────
+// No counterpart in the reference (one device).  Rank r owns experts
+// [r*E/P, (r+1)*E/P) of every layer; router, shared expert and norms are
+// replicated; each rank brings its own tokens.  Per layer:
+//   counts   every rank writes its expert histogram into every peer's table
+//   plan     from the full table each rank derives (a) where its rows go inside the
+//            owner's receive buffer and (b) the tile list over the rows it receives
+//   scatter  each (token, k) row of bf16 activations is written straight into the
+//            owner's buffer with 16-byte peer stores, with a return address
+//   gemm     the owner runs the grouped GEMMs over what it received (+ the shared
+//            expert over its own tokens)
+//   return   the owner writes each output row back into the sender's buffer
+//   combine  the sender adds residual, weighted expert rows and the shared expert
+// Ranks meet through per-source epoch flags in the mapped buffers; every wait
+// is bounded and raises the engine's error word instead of hanging.
+struct EpPeers {
+    uint8_t* base[kEpMaxWorld];
+};
+
+__global__ void ep_push_counts_kernel(EpPeers peers, EpSym sym, int me, int P, int E, const int32_t* counts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < P * E) {
+        const int d = i / E, e = i - d * E;
+        reinterpret_cast<int32_t*>(peers.base[d] + sym.counts)[(size_t)me * E + e] = counts[e];
+    }
+}
+
+// One warp: lane s publishes this rank's epoch to peer s (after a system-scope fence:
+// the rows written by earlier kernels of this stream are visible before the flag).
+__global__ void ep_signal_kernel(EpPeers peers, EpSym sym, int me, int P, unsigned int epoch) {
+    __threadfence_system();
+    const int s = threadIdx.x;
+    if (s < P) {
+        unsigned int* f = reinterpret_cast<unsigned int*>(peers.base[s] + sym.flags) + me * 16;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    }
+}
+
+// One warp: lane s waits until peer s has published `epoch`; bounded.
+__global__ void ep_wait_kernel(uint8_t* local, EpSym sym, int P, unsigned int epoch, unsigned int* err) {
+    const int s = threadIdx.x;
+    if (s < P) {
+        const unsigned int* f = reinterpret_cast<const unsigned int*>(local + sym.flags) + s * 16;
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - epoch) >= 0) break;
+            if (clock64() - t0 > kWaitCycles) { atomicExch(err, 9u); break; }
+        }
+    }
+    __threadfence_system();
+}
+
+// plan: one block.  counts_all[s][e] = rows rank s sends to expert e.
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* counts_all, int me, int P, int E, int n_local,
+                                                       int32_t* base_send, int32_t* cursor, int32_t* tile_list,
+                                                       int32_t* n_tiles, int max_tiles, int32_t* total_recv) {
+    __shared__ int tot[1024];      // rows expert e receives from everybody
+    __shared__ int before[1024];   // ... from ranks below me
+    __shared__ int estart[1024];   // first slot of expert e inside its owner's buffer
+    __shared__ int tstart[1024];   // first tile of my local expert
+    __shared__ int s_total, s_tiles;
+    const int tid = threadIdx.x, Eloc = E / P;
+    if (tid < E) {
+        int t = 0, b = 0;
+        for (int s = 0; s < P; ++s) {
+            const int c = counts_all[(size_t)s * E + tid];
+            if (s < me) b += c;
+            t += c;
+        }
+        tot[tid] = t;
+        before[tid] = b;
+    }
+    __syncthreads();
+    if (tid < P) {  // exclusive scan of each owner's experts
+        int a = 0;
+        for (int i = 0; i < Eloc; ++i) { estart[tid * Eloc + i] = a; a += tot[tid * Eloc + i]; }
+        if (tid == me) s_total = a;
+    }
+    __syncthreads();
+    if (tid < E) {
+        base_send[tid] = estart[tid] + before[tid];
+        cursor[tid] = 0;
+    }
+    if (tid == 0) {
+        int b = 0;
+        for (int i = 0; i < Eloc; ++i) { tstart[i] = b; b += (tot[me * Eloc + i] + kNT - 1) / kNT; }
+        tstart[Eloc] = b;
+        const int sh = (n_local + kNT - 1) / kNT;
+        s_tiles = b + sh;
+        *n_tiles = s_tiles < max_tiles ? s_tiles : max_tiles;
+        *total_recv = s_total;
+    }
+    __syncthreads();
+    if (tid < Eloc) {
+        const int e = me * Eloc + tid, c = tot[e];
+        for (int i = 0; i * kNT < c; ++i) {
+            const int k = tstart[tid] + i;
+            if (k < max_tiles) {
+                tile_list[3 * k] = e;
+                tile_list[3 * k + 1] = estart[e] + i * kNT;
+                tile_list[3 * k + 2] = min(kNT, c - i * kNT);
+            }
+        }
+    }
+    if (tid == 0) {  // shared expert over this rank's own tokens, stored after the received rows
+        for (int i = 0; i * kNT < n_local; ++i) {
+            const int k = tstart[Eloc] + i;
+            if (k < max_tiles) {
+                tile_list[3 * k] = E;
+                tile_list[3 * k + 1] = s_total + i * kNT;
+                tile_list[3 * k + 2] = min(kNT, n_local - i * kNT);
+            }
+        }
+    }
+}
+
+// scatter: one warp per (token, k) row, plus one warp per token for the shared expert's local copy.
+__global__ void __launch_bounds__(256) ep_scatter_kernel(EpPeers peers, EpSym sym, int me, int P, int E, int K, int n,
+                                                         const __nv_bfloat16* __restrict__ x,
+                                                         const int32_t* __restrict__ topk_idx,
+                                                         const int32_t* __restrict__ base_send, int32_t* cursor,
+                                                         const int32_t* __restrict__ total_recv) {
+    const int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int Eloc = E / P;
+    if (w < n * K) {
+        const int t = w / K;
+        const int e = topk_idx[w];
+        const int d = e / Eloc;
+        int slot = 0;
+        if (lane == 0) slot = base_send[e] + atomicAdd(&cursor[e], 1);
+        slot = __shfl_sync(0xffffffffu, slot, 0);
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * kBH);
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[d] + sym.xrecv + (size_t)slot * kBH * 2);
+#pragma unroll
+        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
+        if (lane == 0) {
+            int2* meta = reinterpret_cast<int2*>(peers.base[d] + sym.meta);
+            meta[slot] = make_int2(me, w);  // return address: rank and (token * K + k)
+        }
+    } else if (w < n * K + n) {
+        const int t = w - n * K;
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * kBH);
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[me] + sym.xrecv + (size_t)(*total_recv + t) * kBH * 2);
+#pragma unroll
+        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
+    }
+}
+
+// return: one warp per received row; the output row goes back to the rank that sent the input row.
+__global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, EpSym sym, int me,
+                                                        const __nv_bfloat16* __restrict__ o,
+                                                        const int32_t* __restrict__ total_recv) {
+    const int lane = threadIdx.x & 31;
+    const int total = *total_recv;
+    const int2* meta = reinterpret_cast<const int2*>(peers.base[me] + sym.meta);
+    for (int s = blockIdx.x * 8 + (threadIdx.x >> 5); s < total; s += gridDim.x * 8) {
+        const int2 m = meta[s];
+        const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)s * kBH);
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[m.x] + sym.oback + (size_t)m.y * kBH * 2);
+#pragma unroll
+        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
+    }
+}
+
+// combine: moe_combine_residual (reference src/math_util.rs:599-612); routed rows come from the
+// returned buffer in (token, k) order, the shared expert's row from this rank's own output.
+__global__ void __launch_bounds__(256) ep_combine_kernel(const float* __restrict__ h_in, float* __restrict__ h_out,
+                                                         int n, int K, const __nv_bfloat16* __restrict__ oback,
+                                                         const __nv_bfloat16* __restrict__ o_local,
+                                                         const int32_t* __restrict__ total_recv,
+                                                         const float* __restrict__ topk_w,
+                                                         const float* __restrict__ sgate) {
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
+    const float4 a = hp[0], b = hp[1];
+    float moe[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto add = [&](const __nv_bfloat16* row, float w, float (&dst)[8]) {
+        const uint4 q = *(reinterpret_cast<const uint4*>(row) + tid);  // plain load: written by peers during this launch sequence
+        const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            dst[2 * i] += w * __uint_as_float(r[i] << 16);
+            dst[2 * i + 1] += w * __uint_as_float(r[i] & 0xFFFF0000u);
+        }
+    };
+    for (int k = 0; k < K; ++k) add(oback + ((size_t)t * K + k) * kBH, topk_w[(size_t)t * K + k], moe);
+    add(o_local + (size_t)(*total_recv + t) * kBH, sgate[t], sh);
+    const float hin[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float4* op = reinterpret_cast<float4*>(h_out + (size_t)t * kBH) + tid * 2;
+    op[0] = make_float4(hin[0] + moe[0] + sh[0], hin[1] + moe[1] + sh[1], hin[2] + moe[2] + sh[2], hin[3] + moe[3] + sh[3]);
+    op[1] = make_float4(hin[4] + moe[4] + sh[4], hin[5] + moe[5] + sh[5], hin[6] + moe[6] + sh[6], hin[7] + moe[7] + sh[7]);
+}
+
+__global__ void ep_iota_kernel(int32_t* p, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = i;
+}
+
 // ─── host side ──────────────────────────────────────────────────────────────
 
 static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
@@ -891,6 +1091,85 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
     batch_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, E, bw.o, bw.slot_of, wts, bw.sgate, bw.offsets);
     e->launches += 8;
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
+
+// Private work areas of the expert-parallel path (sized at moe_ep_export time).
+int ep_alloc_work(moe_engine* e) {
+    EpState& ep = e->ep;
+    const moe_dims_t& d = e->dims;
+    const size_t rows = (size_t)ep.slots_cap + ep.cap;
+    ep.max_tiles = (int)(rows / kNT + d.num_experts + 2);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
+    const size_t o_act = take(rows * d.inter * 2), o_o = take(rows * d.hidden * 2), o_tl = take((size_t)ep.max_tiles * 12);
+    const size_t o_nt = take(4), o_bs = take((size_t)d.num_experts * 4), o_cu = take((size_t)d.num_experts * 4);
+    const size_t o_id = take(rows * 4), o_tr = take(4);
+    MOE_CUDA(cudaMalloc(&ep.work, off));
+    ep.act = (__nv_bfloat16*)(ep.work + o_act); ep.o = (__nv_bfloat16*)(ep.work + o_o);
+    ep.tile_list = (int32_t*)(ep.work + o_tl); ep.n_tiles = (int32_t*)(ep.work + o_nt);
+    ep.base_send = (int32_t*)(ep.work + o_bs); ep.cursor = (int32_t*)(ep.work + o_cu);
+    ep.ident = (int32_t*)(ep.work + o_id); ep.total_recv = (int32_t*)(ep.work + o_tr);
+    ep_iota_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, e->stream>>>(ep.ident, (int)rows);
+    MOE_CUDA(cudaGetLastError());
+    return batch_reserve(e, ep.cap);
+}
+
+// One MoE block, expert-parallel; every rank of the group must call it for the same layer.
+int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_out) {
+    EpState& ep = e->ep;
+    const moe_dims_t& d = e->dims;
+    MOE_REQUIRE(ep.ready, "expert parallelism is not initialised (moe_ep_export + moe_ep_init)");
+    MOE_REQUIRE(n >= 1 && n <= ep.cap, "token count %d outside 1..%d (max_tokens_per_rank)", n, ep.cap);
+    MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "h must be 16-byte aligned");
+    int rc = check_layer_ready(e, layer);
+    if (rc) return rc;
+    rc = refresh_layer_table(e);
+    if (rc) return rc;
+    BatchWork& bw = e->bw;
+    const LayerDev ly = e->layers[layer].dev;
+    const int E = d.num_experts, K = d.top_k, P = ep.world, me = ep.rank;
+    cudaStream_t st = e->stream;
+    unsigned int* err = e->dec_sync + 2;
+    EpPeers peers{};
+    for (int i = 0; i < P; ++i) peers.base[i] = ep.peer[i];
+    const int32_t* counts_all = reinterpret_cast<const int32_t*>(ep.local + ep.sym.counts);
+
+    MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.xf, bw.sgate);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, 2 * kRtStage + 1024, st>>>(
+        bw.xf, n, E, ly, bw.logits, err);
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts);
+    // 1. histogram exchange
+    ep_push_counts_kernel<<<(P * E + 255) / 256, 256, 0, st>>>(peers, ep.sym, me, P, E, bw.counts);
+    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
+                                       ep.max_tiles, ep.total_recv);
+    // 2. dispatch
+    ep_scatter_kernel<<<(n * K + n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, ep.base_send,
+                                                          ep.cursor, ep.total_recv);
+    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    // 3. grouped GEMMs over the received rows (+ shared expert over the local ones)
+    GemmParams gp{};
+    gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
+    gp.x = reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.xrecv);
+    gp.act = ep.act; gp.o = ep.o;
+    gp.tile_list = ep.tile_list; gp.n_tiles = ep.n_tiles; gp.slot_token = ep.ident;
+    gp.err = err;
+    grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
+    grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
+    // 4. return
+    ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, ep.o, ep.total_recv);
+    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    // 5. combine
+    ep_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.oback),
+                                         ep.o, ep.total_recv, bw.topk_w, bw.sgate);
+    e->launches += 17;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }

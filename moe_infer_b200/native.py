@@ -255,6 +255,24 @@ class NativeEngine:
         L.check(self.lib.moe_telemetry_get(self.h, keys, vals, C.byref(n)))
         return {keys[i].decode(): vals[i] for i in range(n.value)}
 
+    # ── expert parallelism ───────────────────────────────────────────────
+    def ep_export(self, rank: int, world: int, max_tokens_per_rank: int) -> bytes:
+        buf = C.create_string_buffer(L.EP_HANDLE_BYTES)
+        L.check(self.lib.moe_ep_export(self.h, rank, world, max_tokens_per_rank, buf))
+        return buf.raw
+
+    def ep_init(self, all_handles: bytes) -> None:
+        L.check(self.lib.moe_ep_init(self.h, C.create_string_buffer(all_handles, len(all_handles))))
+
+    def ep_finalize(self) -> None:
+        L.check(self.lib.moe_ep_finalize(self.h))
+
+    def ep_layer_forward_dev(self, layer: int, h_in: int, n_local: int, h_out: int) -> None:
+        L.check(self.lib.moe_ep_layer_forward_dev(self.h, layer, C.c_void_p(h_in), n_local, C.c_void_p(h_out)))
+
+    def ep_forward_hidden_dev(self, emb: int, n_local: int, out: int) -> None:
+        L.check(self.lib.moe_ep_forward_hidden_dev(self.h, C.c_void_p(emb), n_local, C.c_void_p(out)))
+
     def decode_profile(self, enable: Optional[bool] = None) -> Optional[np.ndarray]:
         """enable=True/False switches phase stamping; None returns stamps [layers, points]."""
         if enable is not None:

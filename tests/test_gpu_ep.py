@@ -1,0 +1,101 @@
+"""Expert-parallel path on 2 GPUs (one process per GPU), parity against the CPU oracle.
+
+Each rank uploads the layer with the experts it does NOT own zeroed out, brings its
+own tokens (different counts per rank) and runs the collective layer call; the
+result must match the oracle evaluated with the full weights.
+"""
+import ctypes as C
+import multiprocessing as mp
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORLD = 2
+N_TOK = [37, 50]
+E, K, LAYERS = 16, 8, 2
+
+
+def _gpu_count():
+    try:
+        n = C.c_int(0)
+        cudart = C.CDLL("libcudart.so")
+        return n.value if cudart.cudaGetDeviceCount(C.byref(n)) == 0 else 0
+    except OSError:
+        return len([d for d in os.listdir("/dev") if d.startswith("nvidia") and d[6:].isdigit()])
+
+
+def _worker(rank, conn, ret_q):
+    try:
+        sys.path.insert(0, ROOT)
+        import oracle
+        from moe_infer_b200 import synth
+        from moe_infer_b200.native import Dims, NativeEngine
+        from tests.util import make_layer, rel_l2, upload_layer
+        layers = [make_layer(41, l, num_experts=E) for l in range(LAYERS)]
+        eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=LAYERS), device=rank)
+        size = eng.layout["expert_size"]
+        eloc = E // WORLD
+        for l, lw in enumerate(layers):
+            blob = lw.experts.copy().reshape(E, size)
+            blob[:rank * eloc] = 0
+            blob[(rank + 1) * eloc:] = 0  # only the owned experts hold valid bytes on this rank
+            upload_layer(eng, l, lw)
+            eng.load_layer(l, blob.reshape(-1))
+        conn.send(eng.ep_export(rank, WORLD, 64))
+        eng.ep_init(conn.recv())
+        n = N_TOK[rank]
+        h = synth.hidden_states(500 + rank, 3, n, 2048)
+        d_in = eng.alloc(h.nbytes).upload(h)
+        d_out = eng.alloc(h.nbytes)
+        eng.ep_layer_forward_dev(0, d_in.ptr, n, d_out.ptr)
+        eng.sync()
+        out1 = d_out.download(np.float32, (n, 2048))
+        ref1, _, _ = oracle.moe_layer(layers[0], h, K, threads=4)
+        eng.ep_forward_hidden_dev(d_in.ptr, n, d_out.ptr)
+        eng.sync()
+        out2 = d_out.download(np.float32, (n, 2048))
+        ref2 = oracle.moe_stack(layers, h, K, threads=4)
+        conn.send("done")
+        conn.recv()  # leave only after every rank has finished using peer memory
+        ret_q.put((rank, rel_l2(out1 - h, ref1 - h), rel_l2(out2, ref2), None))
+        eng.close()
+    except Exception as ex:  # surface the failure in the parent
+        ret_q.put((rank, None, None, repr(ex)))
+
+
+def test_ep_two_gpus_matches_oracle():
+    if _gpu_count() < WORLD:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    ret_q = ctx.Queue()
+    pipes = [ctx.Pipe() for _ in range(WORLD)]
+    procs = [ctx.Process(target=_worker, args=(r, pipes[r][1], ret_q)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    try:
+        handles = []
+        for r in range(WORLD):
+            assert pipes[r][0].poll(300), "rank did not export a handle"
+            handles.append(pipes[r][0].recv())
+        table = b"".join(handles)
+        for r in range(WORLD):
+            pipes[r][0].send(table)
+        for r in range(WORLD):
+            if pipes[r][0].poll(300):
+                pipes[r][0].recv()
+        for r in range(WORLD):
+            pipes[r][0].send("bye")
+        results = [ret_q.get(timeout=300) for _ in range(WORLD)]
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    for rank, e1, e2, err in sorted(results):
+        assert err is None, f"rank {rank}: {err}"
+        assert e1 < 1e-2, (rank, e1)   # one block, MoE update only
+        assert e2 < 1e-2, (rank, e2)   # two-block stack
