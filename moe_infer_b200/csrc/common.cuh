@@ -51,6 +51,8 @@ struct LayerDev {
     Q4Dev router_q4;             // INT4-scheme router
     const uint8_t* shared;       // shared expert in expert-blob layout (hidden, shared_inter)
     Q4Dev sgate;                 // [1, H]
+    const uint16_t* router_planes;  // batched path: router weights split into bf16 planes (see grouped.cu), or nullptr
+    int router_nplanes;             // 1 (bf16 router) or 3 (4-bit router)
 };
 
 struct LayerHost {
@@ -59,6 +61,8 @@ struct LayerHost {
     bool experts_loaded = false;
     bool role_loaded[6] = {false, false, false, false, false, false};
     bool router_is_bf16 = true;
+    uint8_t* planes = nullptr;   // router planes of the batched path, built on first use
+    bool planes_valid = false;
     LayerDev dev{};
 };
 
@@ -69,7 +73,8 @@ struct BatchWork {
     float* h_a = nullptr;          // [cap, H] ping (layer stack)
     float* h_b = nullptr;          // [cap, H] pong
     __nv_bfloat16* x = nullptr;    // [cap, H] normalised activations, bf16, K-interleaved
-    float* xf = nullptr;           // [cap, H] normalised activations, f32 (router)
+    __nv_bfloat16* x_mid = nullptr;  // [cap, H] second and third bf16 terms of x (x = x + x_mid + x_lo to 24 bits),
+    __nv_bfloat16* x_lo = nullptr;   //          same order, for the f32-accurate router
     float* logits = nullptr;       // [cap, E]
     int32_t* topk_idx = nullptr;   // [cap, K]
     float* topk_w = nullptr;       // [cap, K]

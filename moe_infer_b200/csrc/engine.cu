@@ -116,6 +116,8 @@ int refresh_layer_table(moe_engine* e) {
             dv.sgate.s = (const uint16_t*)(lh.aux + a.sgate_s);
             dv.sgate.b = (const uint16_t*)(lh.aux + a.sgate_b);
         }
+        dv.router_planes = lh.planes_valid ? (const uint16_t*)lh.planes : nullptr;
+        dv.router_nplanes = lh.router_is_bf16 ? 1 : 3;
         lh.dev = dv;
         tab[l] = dv;
     }
@@ -255,6 +257,7 @@ void moe_engine_destroy(moe_engine_t* e) {
     for (auto& lh : e->layers) {
         if (lh.experts) cudaFree(lh.experts);
         if (lh.aux) cudaFree(lh.aux);
+        if (lh.planes) cudaFree(lh.planes);
     }
     moe_ep_finalize(e);
     decode_destroy(e);
@@ -345,6 +348,7 @@ int moe_store_load_tensor(moe_engine_t* e, int layer, int role, const void* w, c
                 lh.router_is_bf16 = false;
             }
             e->table_dirty = true;
+            lh.planes_valid = false;  // rebuilt from the new router on the next batched call
             break;
         case MOE_T_SHARED_GATE:
             rc = up_q4(a.shared + S.gate_w, a.shared + S.gate_s, a.shared + S.gate_b, d.shared_inter, d.hidden);

@@ -8,7 +8,7 @@
 // expert), re-reading the expert weights for each token.  Here every expert's
 // weights are read and dequantised once per tile of up to 256 of its tokens.
 //
-//   prep     per token: x = rmsnorm(h) (f32 for the router, bf16 for the GEMMs),
+//   prep     per token: x = rmsnorm(h) as three bf16 terms (hi for the GEMMs, all three for the router),
 //            sigmoid(shared_expert_gate . x)
 //   router   logits = x . Wr^T on the tensor cores with three-way bf16 splits (f32 accuracy)
 //   route    per token softmax / top-k / renormalise (one warp), expert histogram
@@ -48,8 +48,9 @@ __host__ __device__ __forceinline__ int ipos(int j) { return ((j & 3) << 1) | (j
 
 // ─── prep: norm, bf16/f32 activations, shared gate ──────────────────────────
 __global__ void __launch_bounds__(256) batch_prep_kernel(const float* __restrict__ h_in, int n, LayerDev ly,
-                                                         __nv_bfloat16* __restrict__ x_bf, float* __restrict__ x_f,
-                                                         float* __restrict__ sgate) {
+                                                         __nv_bfloat16* __restrict__ x_bf,
+                                                         __nv_bfloat16* __restrict__ x_mid,
+                                                         __nv_bfloat16* __restrict__ x_lo, float* __restrict__ sgate) {
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float red[8];
     const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
@@ -74,20 +75,25 @@ __global__ void __launch_bounds__(256) batch_prep_kernel(const float* __restrict
         x[2 * i] = v[2 * i] * inv_rms * __uint_as_float(nwr[i] << 16);
         x[2 * i + 1] = v[2 * i + 1] * inv_rms * __uint_as_float(nwr[i] & 0xFFFF0000u);
     }
-    float4* xo = reinterpret_cast<float4*>(x_f + (size_t)t * kBH) + tid * 2;
-    xo[0] = make_float4(x[0], x[1], x[2], x[3]);
-    xo[1] = make_float4(x[4], x[5], x[6], x[7]);
-    // bf16, K-interleaved: stored order [0,4,1,5,2,6,3,7]
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(x[0], x[4]);
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(x[1], x[5]);
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(x[2], x[6]);
-    __nv_bfloat162 p3 = __floats2bfloat162_rn(x[3], x[7]);
-    uint4 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&p0);
-    pk.y = *reinterpret_cast<uint32_t*>(&p1);
-    pk.z = *reinterpret_cast<uint32_t*>(&p2);
-    pk.w = *reinterpret_cast<uint32_t*>(&p3);
-    reinterpret_cast<uint4*>(x_bf + (size_t)t * kBH)[tid] = pk;
+    // bf16, K-interleaved: stored order [0,4,1,5,2,6,3,7]; x = hi + mid + lo to 24 significant bits
+    // (hi feeds the expert GEMMs, all three the f32-accurate router)
+    uint16_t ph[8], pm[8], pl[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int q = ((i & 3) << 1) | (i >> 2);
+        const __nv_bfloat16 hb = __float2bfloat16_rn(x[i]);
+        const float r1 = x[i] - __bfloat162float(hb);
+        const __nv_bfloat16 mb = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 lb = __float2bfloat16_rn(r1 - __bfloat162float(mb));
+        ph[q] = __bfloat16_as_ushort(hb); pm[q] = __bfloat16_as_ushort(mb); pl[q] = __bfloat16_as_ushort(lb);
+    }
+    auto pack8 = [](const uint16_t (&v)[8]) {
+        return make_uint4(v[0] | ((uint32_t)v[1] << 16), v[2] | ((uint32_t)v[3] << 16), v[4] | ((uint32_t)v[5] << 16),
+                          v[6] | ((uint32_t)v[7] << 16));
+    };
+    reinterpret_cast<uint4*>(x_bf + (size_t)t * kBH)[tid] = pack8(ph);
+    reinterpret_cast<uint4*>(x_mid + (size_t)t * kBH)[tid] = pack8(pm);
+    reinterpret_cast<uint4*>(x_lo + (size_t)t * kBH)[tid] = pack8(pl);
     // shared_expert_gate . x : thread tid owns word tid of the single 4-bit row
     const uint32_t w = ly.sgate.w[tid];
     const float s = bf16_bits_to_f32(ly.sgate.s[tid >> 3]);
@@ -107,68 +113,13 @@ __global__ void __launch_bounds__(256) batch_prep_kernel(const float* __restrict
     }
 }
 
-// ─── router logits in f32: logits[n, E] = X[n, H] . Wr[E, H]^T ──────────────
-// 64 tokens x 64 experts per block, 4 x 4 outputs per thread.
-__global__ void __launch_bounds__(256) batch_router_kernel(const float* __restrict__ x_f, int n, int E, LayerDev ly,
-                                                           float* __restrict__ logits) {
-    __shared__ float xs[16][65];
-    __shared__ float ws[16][65];
-    const int t0 = blockIdx.x * 64, e0 = blockIdx.y * 64;
-    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
-    for (int k0 = 0; k0 < kBH; k0 += 16) {
-        // 64 rows x 16 columns each: thread -> (row = tid >> 2, 4 columns)
-        {
-            const int r = tid >> 2, c = (tid & 3) * 4;
-            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t0 + r < n) xv = *reinterpret_cast<const float4*>(x_f + (size_t)(t0 + r) * kBH + k0 + c);
-            xs[c][r] = xv.x; xs[c + 1][r] = xv.y; xs[c + 2][r] = xv.z; xs[c + 3][r] = xv.w;
-            float wv[4] = {0.f, 0.f, 0.f, 0.f};
-            const int e = e0 + r;
-            if (e < E) {
-                if (ly.router_bf16) {
-                    const uint2 q = *reinterpret_cast<const uint2*>(ly.router_bf16 + (size_t)e * kBH + k0 + c);
-                    wv[0] = __uint_as_float(q.x << 16); wv[1] = __uint_as_float(q.x & 0xFFFF0000u);
-                    wv[2] = __uint_as_float(q.y << 16); wv[3] = __uint_as_float(q.y & 0xFFFF0000u);
-                } else {
-                    const int col = k0 + c;
-                    const uint32_t word = ly.router_q4.w[(size_t)e * (kBH / 8) + (col >> 3)];
-                    const float s = bf16_bits_to_f32(ly.router_q4.s[(size_t)e * (kBH / kGroup) + (col >> 6)]);
-                    const float b = bf16_bits_to_f32(ly.router_q4.b[(size_t)e * (kBH / kGroup) + (col >> 6)]);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) wv[i] = (float)((word >> (4 * ((col & 7) + i))) & 0xFu) * s + b;
-                }
-            }
-            ws[c][r] = wv[0]; ws[c + 1][r] = wv[1]; ws[c + 2][r] = wv[2]; ws[c + 3][r] = wv[3];
-        }
-        __syncthreads();
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            float xa[4], wb[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { xa[i] = xs[k][ty * 4 + i]; wb[i] = ws[k][tx * 4 + i]; }
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
-        }
-        __syncthreads();
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int t = t0 + ty * 4 + i;
-        if (t >= n) continue;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = e0 + tx * 4 + j;
-            if (e < E) logits[(size_t)t * E + e] = acc[i][j];
-        }
-    }
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp16_zfill(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ─── router logits on the tensor cores, to f32 accuracy ─────────────────────
 // logits[n, E] = X[n, H] . Wr[E, H]^T.  The expert choice must match an f32
@@ -177,12 +128,16 @@ __global__ void __launch_bounds__(256) batch_router_kernel(const float* __restri
 // products of total order <= 2 are accumulated in f32 by tcgen05.mma:
 //   bf16 router (BQ4):  W . (x_hi + x_mid + x_lo)                         3 MMAs per K block
 //   4-bit router (INT4): W_hi.x_hi + W_hi.x_mid + W_mid.x_hi + W_hi.x_lo + W_lo.x_hi + W_mid.x_mid   6 MMAs
-// One CTA = 128 experts x 64 tokens; both operand tiles are produced by the CTA's
-// 256 threads in natural column order, two stages.
-constexpr int kRtTok = 64;
-constexpr int kRtATile = 128 * 128;  // 128 rows x 64 bf16
+// The weight planes are built once per layer (router_planes_kernel), the
+// activation planes by the prep kernel, both K-interleaved; the GEMM kernel only
+// copies tiles (16-byte asynchronous copies, three stages) and issues MMAs.
+// One CTA = 128 experts x 32 tokens.
+constexpr int kRtTok = 32;
+constexpr int kRtStages = 3;
+constexpr int kRtATile = 128 * 128;   // 128 rows x 64 bf16
 constexpr int kRtBTile = kRtTok * 128;
 constexpr int kRtStage = 3 * kRtATile + 3 * kRtBTile;
+constexpr int kRtSmem = kRtStages * kRtStage + 1024;
 
 __device__ __forceinline__ void split3(float v, uint16_t& hi, uint16_t& mid, uint16_t& lo) {
     const __nv_bfloat16 h = __float2bfloat16_rn(v);
@@ -193,111 +148,103 @@ __device__ __forceinline__ void split3(float v, uint16_t& hi, uint16_t& mid, uin
     hi = __bfloat16_as_ushort(h); mid = __bfloat16_as_ushort(m); lo = __bfloat16_as_ushort(l);
 }
 
-__global__ void __launch_bounds__(256, 1) router_gemm_kernel(const float* __restrict__ x_f, int n, int E, LayerDev ly,
-                                                             float* __restrict__ logits, unsigned int* err) {
+// planes[p][row][H] (bf16, K-interleaved, rows padded to a multiple of 128 with zeros);
+// one thread per 8-column block.  4-bit weights are dequantised as the reference does,
+// (nibble as f32) * scale + bias (src/math_util.rs:47), before the split.
+__global__ void __launch_bounds__(256) router_planes_kernel(LayerDev ly, int E, int rows_padded, uint16_t* planes) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = kBH / 8;
+    if (i >= rows_padded * per_row) return;
+    const int row = i / per_row, blk = i - row * per_row;
+    const bool q4 = ly.router_bf16 == nullptr;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (row < E) {
+        if (!q4) {
+            const uint4 q = *reinterpret_cast<const uint4*>(ly.router_bf16 + (size_t)row * kBH + blk * 8);
+            const uint32_t r[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { v[2 * k] = __uint_as_float(r[k] << 16); v[2 * k + 1] = __uint_as_float(r[k] & 0xFFFF0000u); }
+        } else {
+            const uint32_t w = ly.router_q4.w[(size_t)row * per_row + blk];
+            const float s = bf16_bits_to_f32(ly.router_q4.s[(size_t)row * (kBH / kGroup) + (blk >> 3)]);
+            const float b = bf16_bits_to_f32(ly.router_q4.b[(size_t)row * (kBH / kGroup) + (blk >> 3)]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = (float)((w >> (4 * k)) & 0xFu) * s + b;
+        }
+    }
+    const int np = q4 ? 3 : 1;
+    uint16_t pl[3][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) split3(v[k], pl[0][ipos(k)], pl[1][ipos(k)], pl[2][ipos(k)]);
+    for (int p = 0; p < np; ++p) {
+        uint4 o;
+        o.x = pl[p][0] | ((uint32_t)pl[p][1] << 16); o.y = pl[p][2] | ((uint32_t)pl[p][3] << 16);
+        o.z = pl[p][4] | ((uint32_t)pl[p][5] << 16); o.w = pl[p][6] | ((uint32_t)pl[p][7] << 16);
+        *reinterpret_cast<uint4*>(planes + ((size_t)p * rows_padded + row) * kBH + blk * 8) = o;
+    }
+}
+
+__global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16* __restrict__ x_hi,
+                                                             const __nv_bfloat16* __restrict__ x_mid,
+                                                             const __nv_bfloat16* __restrict__ x_lo, int n, int E,
+                                                             const uint16_t* __restrict__ planes, int nplanes,
+                                                             int rows_padded, float* __restrict__ logits,
+                                                             unsigned int* err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t bar_empty[2];
+    __shared__ uint64_t bar_empty[kRtStages];
     __shared__ uint64_t bar_acc;
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t0 = blockIdx.x * kRtTok, e0 = blockIdx.y * 128;
-    const bool q4 = ly.router_bf16 == nullptr;
     if (tid == 0) {
-        mbar_init(&bar_empty[0], 1);
-        mbar_init(&bar_empty[1], 1);
+        for (int i = 0; i < kRtStages; ++i) mbar_init(&bar_empty[i], 1);
         mbar_init(&bar_acc, 1);
         mbar_fence_init();
     }
-    if (warp == 0) umma::tmem_alloc(&tmem_slot, 64);
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, 32);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = tmem_slot;
+    const uint32_t stages_addr = smem_u32(stages);
     const uint32_t idesc = umma::make_idesc_bf16(128, kRtTok);
-    bool alive = true;
     constexpr int kSteps = kBH / 64;
-    for (int kc = 0; kc < kSteps; ++kc) {
-        const int st = kc & 1, use = kc >> 1;
-        bool ok = true;
-        if (use > 0) ok = mbar_wait(&bar_empty[st], (use - 1) & 1);
-        unsigned char* a_hi = stages + st * kRtStage;
-        unsigned char* b_hi = a_hi + 3 * kRtATile;
-        // ---- B: 64 tokens x 64 columns of x, split three ways; thread -> (token, 16 columns) ----
-        {
-            const int j = tid >> 2, cq = tid & 3;  // 4 threads per token row, 16 columns each
+    const __nv_bfloat16* xs[3] = {x_hi, x_mid, x_lo};
+
+    // copies of K step kc into stage st: nplanes x (128 rows x 8 chunks) weights, 3 x (32 tokens x 8 chunks) activations
+    auto issue = [&](int kc, int st) {
+        const uint32_t base = stages_addr + st * kRtStage;
+        for (int q = tid; q < nplanes * 1024; q += 256) {
+            const int p = q >> 10, r = (q >> 3) & 127, c = q & 7;
+            cp16_zfill(base + p * kRtATile + umma::sw128_offset((uint32_t)r, (uint32_t)c),
+                       planes + ((size_t)p * rows_padded + e0 + r) * kBH + kc * 64 + c * 8, 16u);
+        }
+        for (int q = tid; q < 3 * kRtTok * 8; q += 256) {
+            const int p = q / (kRtTok * 8), rem = q - p * (kRtTok * 8), j = rem >> 3, c = rem & 7;
             const int t = t0 + j;
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (t < n) q = __ldg(reinterpret_cast<const float4*>(x_f + (size_t)t * kBH + kc * 64 + cq * 16) + i);
-                v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
-            }
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t ph[4], pm[4], pl[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint16_t h0, m0, l0, h1, m1, l1;
-                    split3(v[half * 8 + 2 * i], h0, m0, l0);
-                    split3(v[half * 8 + 2 * i + 1], h1, m1, l1);
-                    ph[i] = (uint32_t)h0 | ((uint32_t)h1 << 16);
-                    pm[i] = (uint32_t)m0 | ((uint32_t)m1 << 16);
-                    pl[i] = (uint32_t)l0 | ((uint32_t)l1 << 16);
-                }
-                const uint32_t off = umma::sw128_offset((uint32_t)j, (uint32_t)(cq * 2 + half));
-                *reinterpret_cast<uint4*>(b_hi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                *reinterpret_cast<uint4*>(b_hi + kRtBTile + off) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
-                *reinterpret_cast<uint4*>(b_hi + 2 * kRtBTile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-            }
+            cp16_zfill(base + 3 * kRtATile + p * kRtBTile + umma::sw128_offset((uint32_t)j, (uint32_t)c),
+                       xs[p] + (size_t)(t < n ? t : 0) * kBH + kc * 64 + c * 8, t < n ? 16u : 0u);
         }
-        // ---- A: 128 router rows x 64 columns; thread -> (row, 32 columns) ----
-        {
-            const int r = tid >> 1, half = tid & 1;
-            const int e = e0 + r;
-            if (!q4) {
-                uint4 q[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    q[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (e < E) q[i] = __ldg(reinterpret_cast<const uint4*>(ly.router_bf16 + (size_t)e * kBH + kc * 64 + half * 32) + i);
-                    *reinterpret_cast<uint4*>(a_hi + umma::sw128_offset((uint32_t)r, (uint32_t)(half * 4 + i))) = q[i];
-                }
-            } else {
-                uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                float s = 0.f, b = 0.f;
-                if (e < E) {
-                    w = __ldg(reinterpret_cast<const uint4*>(ly.router_q4.w + (size_t)e * (kBH / 8) + kc * 8) + half);
-                    s = bf16_bits_to_f32(ly.router_q4.s[(size_t)e * (kBH / kGroup) + kc]);
-                    b = bf16_bits_to_f32(ly.router_q4.b[(size_t)e * (kBH / kGroup) + kc]);
-                }
-                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    uint32_t ph[4], pm[4], pl[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint16_t h0, m0, l0, h1, m1, l1;
-                        // (nibble as f32) * scale + bias: the reference's dequantised weight (src/math_util.rs:47)
-                        split3((float)((words[wi] >> (8 * i)) & 0xFu) * s + b, h0, m0, l0);
-                        split3((float)((words[wi] >> (8 * i + 4)) & 0xFu) * s + b, h1, m1, l1);
-                        ph[i] = (uint32_t)h0 | ((uint32_t)h1 << 16);
-                        pm[i] = (uint32_t)m0 | ((uint32_t)m1 << 16);
-                        pl[i] = (uint32_t)l0 | ((uint32_t)l1 << 16);
-                    }
-                    const uint32_t off = umma::sw128_offset((uint32_t)r, (uint32_t)(half * 4 + wi));
-                    *reinterpret_cast<uint4*>(a_hi + off) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    *reinterpret_cast<uint4*>(a_hi + kRtATile + off) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
-                    *reinterpret_cast<uint4*>(a_hi + 2 * kRtATile + off) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                }
-            }
+    };
+    bool alive = true;
+    issue(0, 0); cp_commit_group();
+    issue(1, 1); cp_commit_group();
+    for (int kc = 0; kc < kSteps; ++kc) {
+        const int st = kc % kRtStages;
+        bool ok = true;
+        if (kc + 2 < kSteps) {
+            const int nst = (kc + 2) % kRtStages, nuse = (kc + 2) / kRtStages;
+            if (nuse > 0) ok = mbar_wait(&bar_empty[nst], (nuse - 1) & 1);
+            issue(kc + 2, nst);
         }
+        cp_commit_group();
+        cp_wait_group<2>();  // this K step's tiles have landed
         umma::fence_smem_to_async();
         if (!__syncthreads_and(ok ? 1 : 0)) { alive = false; break; }
         if (tid == 0) {
             umma::fence_after_sync();
-            const uint32_t a0 = smem_u32(a_hi), b0 = smem_u32(b_hi);
+            const uint32_t a0 = stages_addr + st * kRtStage, b0 = a0 + 3 * kRtATile;
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
                 const uint32_t o = k16 * 32;
@@ -308,7 +255,7 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const float* __rest
                 umma::mma_bf16(tmem, ah, bh, idesc, (kc > 0 || k16 > 0) ? 1u : 0u);
                 umma::mma_bf16(tmem, ah, bm, idesc, 1u);
                 umma::mma_bf16(tmem, ah, bl, idesc, 1u);
-                if (q4) {
+                if (nplanes == 3) {
                     const uint64_t am = umma::make_desc_sw128_kmajor(a0 + kRtATile + o);
                     const uint64_t al = umma::make_desc_sw128_kmajor(a0 + 2 * kRtATile + o);
                     umma::mma_bf16(tmem, am, bh, idesc, 1u);
@@ -320,28 +267,29 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const float* __rest
             if (kc == kSteps - 1) umma::commit(&bar_acc);
         }
     }
+    cp_wait_group<0>();
     if (alive) {
         const bool acc_ok = mbar_wait(&bar_acc, 0);
         alive = __syncthreads_and(acc_ok ? 1 : 0) != 0;
     }
     if (alive) {
         umma::fence_after_sync();
-        const int quad = warp & 3;
-        const int e = e0 + quad * 32 + lane;
-        const int cb = warp >> 2;  // warps 0-3: tokens 0..31, warps 4-7: tokens 32..63
-        float g[32];
-        umma::ld_32x32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), g);
+        if (warp < 4) {
+            const int e = e0 + warp * 32 + lane;
+            float g[32];
+            umma::ld_32x32(tmem + ((uint32_t)(warp * 32) << 16), g);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            const int t = t0 + cb * 32 + c;
-            if (t < n && e < E) logits[(size_t)t * E + e] = g[c];
+            for (int c = 0; c < 32; ++c) {
+                const int t = t0 + c;
+                if (t < n && e < E) logits[(size_t)t * E + e] = g[c];
+            }
         }
     } else if (tid == 0) {
         atomicExch(err, 8u);
     }
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tmem, 64);
+    if (warp == 0) umma::tmem_dealloc(tmem, 32);
 }
 
 // ─── route: one warp per token ──────────────────────────────────────────────
@@ -510,14 +458,6 @@ __device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 s2, __n
     }
     return make_uint4(r[0], r[1], r[2], r[3]);
 }
-
-// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
-__device__ __forceinline__ void cp16_zfill(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Bounded, abort-aware mbarrier wait: gives up after about a second of SM clocks or as
 // soon as another warp of the CTA has given up (s_abort), so that a broken pipeline
@@ -1014,6 +954,25 @@ static constexpr size_t gemm_smem_bytes() {
     return (size_t)kStages * (256 * 128 + kNT * 128) + 1024;
 }
 
+// Builds the router's bf16 planes of a layer on first batched use (and after the router is reloaded).
+static int ensure_router_planes(moe_engine* e, int layer) {
+    LayerHost& lh = e->layers[layer];
+    if (lh.planes_valid) return MOE_OK;
+    const int E = e->dims.num_experts, rows = (E + 127) / 128 * 128;
+    if (!lh.planes) {
+        MOE_CUDA(cudaMalloc(&lh.planes, (size_t)3 * rows * kBH * 2));
+        e->resident += (size_t)3 * rows * kBH * 2;
+    }
+    int rc = refresh_layer_table(e);
+    if (rc) return rc;
+    router_planes_kernel<<<(rows * (kBH / 8) + 255) / 256, 256, 0, e->stream>>>(lh.dev, E, rows, (uint16_t*)lh.planes);
+    MOE_CUDA(cudaGetLastError());
+    e->launches++;
+    lh.planes_valid = true;
+    e->table_dirty = true;
+    return refresh_layer_table(e);
+}
+
 int batch_reserve(moe_engine* e, int32_t n_tokens) {
     BatchWork& bw = e->bw;
     if (n_tokens <= bw.capacity) return MOE_OK;
@@ -1025,7 +984,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     const int max_tiles = (int)(slots / kNT + E + 2);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
-    const size_t o_ha = take(n * H * 4), o_hb = take(n * H * 4), o_x = take(n * H * 2), o_xf = take(n * H * 4);
+    const size_t o_ha = take(n * H * 4), o_hb = take(n * H * 4), o_x = take(n * H * 2), o_xm = take(n * H * 2), o_xl = take(n * H * 2);
     const size_t o_lg = take(n * E * 4), o_ti = take(n * K * 4), o_tw = take(n * K * 4), o_sg = take(n * 4);
     const size_t o_cnt = take((E + 1) * 4), o_off = take((E + 2) * 4), o_cur = take((E + 1) * 4);
     const size_t o_st = take(slots * 4), o_so = take(n * K * 4), o_act = take(slots * I * 2), o_o = take(slots * H * 2);
@@ -1033,7 +992,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     MOE_CUDA(cudaMalloc(&bw.base, off));
     uint8_t* b = bw.base;
     bw.h_a = (float*)(b + o_ha); bw.h_b = (float*)(b + o_hb);
-    bw.x = (__nv_bfloat16*)(b + o_x); bw.xf = (float*)(b + o_xf);
+    bw.x = (__nv_bfloat16*)(b + o_x); bw.x_mid = (__nv_bfloat16*)(b + o_xm); bw.x_lo = (__nv_bfloat16*)(b + o_xl);
     bw.logits = (float*)(b + o_lg); bw.topk_idx = (int32_t*)(b + o_ti); bw.topk_w = (float*)(b + o_tw);
     bw.sgate = (float*)(b + o_sg);
     bw.counts = (int32_t*)(b + o_cnt); bw.offsets = (int32_t*)(b + o_off); bw.cursor = (int32_t*)(b + o_cur);
@@ -1044,7 +1003,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     bw.capacity = n_tokens;
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<1>()));
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<2>()));
-    MOE_CUDA(cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRtStage + 1024));
+    MOE_CUDA(cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem));
     return MOE_OK;
 }
 
@@ -1068,6 +1027,8 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     if (rc) return rc;
     rc = batch_reserve(e, n);
     if (rc) return rc;
+    rc = ensure_router_planes(e, layer);
+    if (rc) return rc;
     BatchWork& bw = e->bw;
     const LayerDev ly = e->layers[layer].dev;
     const int E = d.num_experts, K = d.top_k;
@@ -1076,9 +1037,10 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     float* wts = out_w ? out_w : bw.topk_w;
 
     MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
-    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.xf, bw.sgate);
-    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, 2 * kRtStage + 1024, st>>>(
-        bw.xf, n, E, ly, bw.logits, e->dec_sync + 2);
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, kRtSmem, st>>>(
+        bw.x, bw.x_mid, bw.x_lo, n, E, ly.router_planes, ly.router_nplanes, (E + 127) / 128 * 128, bw.logits,
+        e->dec_sync + 2);
     batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts);
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
@@ -1128,6 +1090,8 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     if (rc) return rc;
     rc = refresh_layer_table(e);
     if (rc) return rc;
+    rc = ensure_router_planes(e, layer);
+    if (rc) return rc;
     BatchWork& bw = e->bw;
     const LayerDev ly = e->layers[layer].dev;
     const int E = d.num_experts, K = d.top_k, P = ep.world, me = ep.rank;
@@ -1138,9 +1102,9 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     const int32_t* counts_all = reinterpret_cast<const int32_t*>(ep.local + ep.sym.counts);
 
     MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
-    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.xf, bw.sgate);
-    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, 2 * kRtStage + 1024, st>>>(
-        bw.xf, n, E, ly, bw.logits, err);
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, kRtSmem, st>>>(
+        bw.x, bw.x_mid, bw.x_lo, n, E, ly.router_planes, ly.router_nplanes, (E + 127) / 128 * 128, bw.logits, err);
     batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts);
     // 1. histogram exchange
     ep_push_counts_kernel<<<(P * E + 255) / 256, 256, 0, st>>>(peers, ep.sym, me, P, E, bw.counts);

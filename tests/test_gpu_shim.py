@@ -1,0 +1,101 @@
+"""GPU: the `_moe_infer_rs` mirror end to end — quantise a synthetic HF-style checkpoint,
+load it through Model/Engine and compare the forward with the CPU oracle."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+from moe_infer_b200 import _moe_infer_rs as rs
+from moe_infer_b200 import synth
+from tests.util import rel_l2
+
+pytestmark = pytest.mark.gpu
+E, K, H, I = 4, 4, 2048, 512
+
+
+def _write_safetensors(path, tensors):
+    hdr, blobs, off = {}, [], 0
+    for name, arr in tensors.items():
+        raw = np.ascontiguousarray(arr).tobytes()
+        hdr[name] = {"dtype": "BF16", "shape": list(arr.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    h = json.dumps(hdr).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)))
+        f.write(h)
+        for b in blobs:
+            f.write(b)
+
+
+def _hf_checkpoint(tmp, layers, mtp):
+    cfg = {"architectures": ["Qwen3_5MoeForConditionalGeneration_Stripped"],
+           "text_config": {"hidden_size": H, "num_hidden_layers": layers, "mtp_num_hidden_layers": mtp, "vocab_size": 100,
+                           "num_experts": E, "num_experts_per_tok": K, "moe_intermediate_size": I,
+                           "shared_expert_intermediate_size": I, "num_key_value_heads": 2, "head_dim": 256}}
+    os.makedirs(tmp, exist_ok=True)
+    json.dump(cfg, open(os.path.join(tmp, "config.json"), "w"))
+    raw, ts = [], {}
+    for l in range(layers + mtp):
+        t = synth.layer_tensors(7, 5, l, hidden=H, inter=I, shared_inter=I, num_experts=E, bf16_source=True)
+        t["post_norm"] = synth.bf16_to_f32(synth.to_bf16_rne(
+            np.random.default_rng(l).uniform(-0.1, 0.1, H).astype(np.float32)))  # zero-centred, as in Qwen3.6
+        raw.append(t)
+        p = f"model.language_model.layers.{l}." if l < layers else f"mtp.layers.{l - layers}."
+        b = synth.to_bf16_rne
+        ts.update({p + "mlp.experts.gate_up_proj": b(t["gate_up"]), p + "mlp.experts.down_proj": b(t["down"]),
+                   p + "mlp.gate.weight": b(t["router"]), p + "mlp.shared_expert.gate_proj.weight": b(t["shared_gate"]),
+                   p + "mlp.shared_expert.up_proj.weight": b(t["shared_up"]),
+                   p + "mlp.shared_expert.down_proj.weight": b(t["shared_down"]),
+                   p + "mlp.shared_expert_gate.weight": b(t["shared_sgate"]),
+                   p + "post_attention_layernorm.weight": b(t["post_norm"])})
+    _write_safetensors(os.path.join(tmp, "model-00001-of-00001.safetensors"), ts)
+    return raw
+
+
+def _oracle_layers(raw, scheme):
+    out = []
+    for t in raw:
+        out.append(oracle.LayerWeights(
+            hidden=H, inter=I, shared_inter=I, num_experts=E, post_norm_w=oracle.f32_to_bf16(t["post_norm"] + np.float32(1.0)),
+            router_bf16=oracle.f32_to_bf16(t["router"]) if scheme == "bq4" else None,
+            router_q4=None if scheme == "bq4" else oracle.quant_int4(t["router"]),
+            sh_gate=oracle.quant_int4(t["shared_gate"]), sh_up=oracle.quant_int4(t["shared_up"]),
+            sh_down=oracle.quant_int4(t["shared_down"]), sgate=oracle.quant_int4(t["shared_sgate"]),
+            experts=oracle.pack_experts_layer(t["gate_up"], t["down"])))
+    return out
+
+
+@pytest.mark.parametrize("scheme", ["bq4", "int4"])
+def test_quantize_load_forward(tmp_path, scheme):
+    src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
+    raw = _hf_checkpoint(src, layers=2, mtp=1)
+    rs.qwen35_moe_quantize(src, dst, version="3.6", scheme=scheme)
+    ref_layers = _oracle_layers(raw, scheme)
+    for l, lw in enumerate(ref_layers):  # packed bytes identical to the reference packer's
+        assert np.array_equal(np.fromfile(os.path.join(dst, "packed_experts", f"layer_{l:02d}.bin"), np.uint8), lw.experts)
+    model = rs.Model(dst)
+    eng = rs.Engine(model, "Qwen35MoEFusedExp3")
+    cache = rs.Cache(model)
+    emb = synth.hidden_states(3, 2, 5, H)
+    rs.record_engine_telemetry(True)
+    out = eng.forward_hidden(emb, cache)
+    rs.record_engine_telemetry(False)
+    ref = oracle.moe_stack(ref_layers[:2], emb, K)
+    assert out.shape == (5, H) and rel_l2(out, ref) < 1e-2
+    assert cache.pos == 5 and cache.gpu_dirty and eng.telemetry()["engine.total_ms"] > 0
+    assert np.array_equal(eng.last_h_pre_norm(), out[-1])
+    out_b = eng.forward_batched(np.arange(3, dtype=np.int64), cache)       # no embedding table: zeros in, finite out
+    assert out_b.shape == (3, H) and cache.pos == 8
+    assert eng.forward(np.zeros(0, np.int64), cache).shape == (0, H)
+    snap = eng.snapshot_state()
+    m = eng.mtp_forward(0)                                                 # MoE half of the MTP block (layer index 2)
+    ref_m, _, _ = oracle.moe_layer(ref_layers[2], eng.last_h_pre_norm(), K)
+    assert rel_l2(m, ref_m[0]) < 1e-2
+    eng.forward_hidden(emb[:1], cache)
+    eng.restore_snapshot(snap)
+    assert eng.pos == 8
+    eng.native.close()
