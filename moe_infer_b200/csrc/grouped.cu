@@ -131,8 +131,8 @@ __device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_gr
 // The weight planes are built once per layer (router_planes_kernel), the
 // activation planes by the prep kernel, both K-interleaved; the GEMM kernel only
 // copies tiles (16-byte asynchronous copies, three stages) and issues MMAs.
-// One CTA = 128 experts x 32 tokens.
-constexpr int kRtTok = 32;
+// One CTA = 128 experts x 64 tokens.
+constexpr int kRtTok = 64;
 constexpr int kRtStages = 3;
 constexpr int kRtATile = 128 * 128;   // 128 rows x 64 bf16
 constexpr int kRtBTile = kRtTok * 128;
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16
         mbar_init(&bar_acc, 1);
         mbar_fence_init();
     }
-    if (warp == 0) umma::tmem_alloc(&tmem_slot, 32);
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, kRtTok);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -274,13 +274,14 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16
     }
     if (alive) {
         umma::fence_after_sync();
-        if (warp < 4) {
-            const int e = e0 + warp * 32 + lane;
+        {
+            const int quad = warp & 3, cb = warp >> 2;  // 8 warps: 4 lane quadrants x 2 column blocks of 32 tokens
+            const int e = e0 + quad * 32 + lane;
             float g[32];
-            umma::ld_32x32(tmem + ((uint32_t)(warp * 32) << 16), g);
+            umma::ld_32x32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), g);
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-                const int t = t0 + c;
+                const int t = t0 + cb * 32 + c;
                 if (t < n && e < E) logits[(size_t)t * E + e] = g[c];
             }
         }
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16
     }
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tmem, 32);
+    if (warp == 0) umma::tmem_dealloc(tmem, kRtTok);
 }
 
 // ─── route: one warp per token ──────────────────────────────────────────────
@@ -493,7 +494,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     constexpr int kStage = kABytes + kBBytes;
     constexpr uint32_t kTmemCols = 512;
     static_assert(kARows * 2 == kProdThreads, "one (row, half-group) dequant task per producer thread");
-    static_assert(kKC % 2 == 0, "the weight prefetch ring alternates between two register sets");
+    constexpr int kWRing = 4;  // K steps of weight words in flight in registers
+    static_assert(kKC % kWRing == 0, "the weight prefetch ring cycles through kWRing register sets");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -609,9 +611,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                     if (j < N) cp16_zfill(base + boff[i], bsrc[i] + kc * 64, j < nt ? 16u : 0u);
                 }
             };
-            // weight words, scales and biases of two K steps in flight in registers
-            uint4 wq[2];
-            uint16_t sq[2], bq[2];
+            // weight words, scales and biases of kWRing K steps in flight in registers
+            uint4 wq[kWRing];
+            uint16_t sq[kWRing], bq[kWRing];
             auto load_a = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
                 w = ld_stream_u4(wp + kc * 8);
                 sc = __ldg(sp + kc);
@@ -619,13 +621,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             };
 
             bool ok = true;
-            {   // prologue: activations of K step 0, weights of K steps 0 and 1
+            {   // prologue: weights of the first kWRing K steps, activations of K step 0
+#pragma unroll
+                for (int i = 0; i < kWRing; ++i) load_a(i, wq[i], sq[i], bq[i]);
                 const uint32_t st0 = it % kStages, use0 = it / kStages;
                 if (use0 > 0) ok = wait_or_abort(&bar_empty[st0], (use0 - 1) & 1, s_abort);
                 issue_b(0, st0);
                 cp_commit_group();
-                load_a(0, wq[0], sq[0], bq[0]);
-                load_a(1, wq[1], sq[1], bq[1]);
             }
             auto k_step = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
                 const uint32_t st = it % kStages;
@@ -646,16 +648,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi)
                     *reinterpret_cast<uint4*>(a_tile + aoff[wi]) = dequant_word(words[wi], s2, b2);
-                if (kc + 2 < kKC) load_a(kc + 2, w, sc, bi);  // refill this register set
+                if (kc + kWRing < kKC) load_a(kc + kWRing, w, sc, bi);  // refill this register set
                 cp_wait_group<1>();  // this K step's activation pieces have landed (the next ones may be in flight)
                 umma::fence_smem_to_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_full[st]);
                 ++it;
             };
-            for (int kc = 0; kc < kKC; kc += 2) {
-                k_step(kc, wq[0], sq[0], bq[0]);
-                k_step(kc + 1, wq[1], sq[1], bq[1]);
+            for (int kc = 0; kc < kKC; kc += kWRing) {
+#pragma unroll
+                for (int i = 0; i < kWRing; ++i) k_step(kc + i, wq[i], sq[i], bq[i]);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             }
             if (!alive) break;

@@ -26,84 +26,138 @@ struct PackJob {
     uint8_t* b_base[2];
 };
 
+constexpr int kPackUnroll = 4;  // groups per 8-lane team: their loads are all issued before the first use
+
 template <bool kSrcBf16>
 __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
-    const int groups_per_row = job.cols / kGroup;
-    const int64_t total_groups = job.n_rows * groups_per_row;
-    const int64_t gi = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    // 32-bit index arithmetic: the host splits jobs so that a launch covers fewer than 2^31 groups
+    const uint32_t groups_per_row = (uint32_t)(job.cols / kGroup);
+    const uint32_t total_groups = (uint32_t)job.n_rows * groups_per_row;
+    const uint32_t teams = gridDim.x * (blockDim.x >> 3);
+    const uint32_t team = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
     const int p = threadIdx.x & 7;
-    if (gi >= total_groups) return;  // whole 8-lane groups leave together
-    const int64_t row = gi / groups_per_row;
-    const int g = (int)(gi - row * groups_per_row);
-
-    float v[8];
-    if (kSrcBf16) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(
-            reinterpret_cast<const uint16_t*>(job.src) + row * job.cols + g * kGroup + p * 8);
-        const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[2 * i] = __uint_as_float(r[i] << 16);            // bf16 -> f32 is exact
-            v[2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
-        }
-    } else {
-        const float4* sp = reinterpret_cast<const float4*>(
-            reinterpret_cast<const float*>(job.src) + row * job.cols + g * kGroup + p * 8);
-        const float4 a = sp[0], b = sp[1];
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-
-    float vmin = v[0], vmax = v[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) {
-        vmin = fminf(vmin, v[i]);
-        vmax = fmaxf(vmax, v[i]);
-    }
-    // Lanes of one group are 8-aligned inside the warp; all 32 lanes of a warp
-    // are either all in range or leave together only per 8-lane group, so the
-    // shuffle mask names just this group's lanes.
+    // Lanes of one team are 8-aligned inside the warp and take the same branches,
+    // so the shuffle mask names just this team's lanes.
     const unsigned gmask = 0xFFu << (threadIdx.x & 24);
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        vmin = fminf(vmin, __shfl_xor_sync(gmask, vmin, o));
-        vmax = fmaxf(vmax, __shfl_xor_sync(gmask, vmax, o));
-    }
-    if (vmax == vmin) vmax = __fadd_rn(vmin, 1.0f);
-    const float fscale = __fdiv_rn(__fsub_rn(vmax, vmin), 15.0f);
-    const float fbias = vmin;
-    const float inv_scale = __fdiv_rn(1.0f, fscale);
 
-    uint32_t word = 0;
+    uint4 raw[kPackUnroll][kSrcBf16 ? 1 : 2];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        const float t = __fadd_rn(__fmul_rn(__fsub_rn(v[n], fbias), inv_scale), 0.5f);
-        int q = __float2int_rz(t);  // truncates, saturates, NaN -> 0: Rust `as i32`
-        q = min(max(q, 0), 15);
-        word |= ((uint32_t)q) << (n * 4);
+    for (int u = 0; u < kPackUnroll; ++u) {
+        const uint32_t gi = team + u * teams;
+        if (gi < total_groups) {
+            const uint32_t row = gi / groups_per_row, g = gi - row * groups_per_row;
+            if (kSrcBf16) {
+                raw[u][0] = ld_stream_u4(reinterpret_cast<const uint16_t*>(job.src) + (size_t)row * job.cols + g * kGroup + p * 8);
+            } else {
+                const float* sp = reinterpret_cast<const float*>(job.src) + (size_t)row * job.cols + g * kGroup + p * 8;
+                raw[u][0] = ld_stream_u4(sp);
+                raw[u][kSrcBf16 ? 0 : 1] = ld_stream_u4(sp + 4);
+            }
+        }
     }
-
-    const int64_t unit = row / job.rows_per_unit;
-    const int64_t rr = row - unit * job.rows_per_unit;
-    const int m = (int)(rr / job.rows_per_mat);
-    const int64_t r = rr - m * job.rows_per_mat;
-    const int64_t uoff = unit * job.unit_stride;
-    // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
-    uint8_t* const wb = m ? job.w_base[1] : job.w_base[0];
-    uint8_t* const sb = m ? job.s_base[1] : job.s_base[0];
-    uint8_t* const bb = m ? job.b_base[1] : job.b_base[0];
-    uint32_t* wp = reinterpret_cast<uint32_t*>(wb + uoff) + r * (job.cols / 8) + g * 8 + p;
-    *wp = word;
-    if (p == 0)
-        reinterpret_cast<uint16_t*>(sb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fscale);
-    if (p == 1)
-        reinterpret_cast<uint16_t*>(bb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fbias);
+#pragma unroll
+    for (int u = 0; u < kPackUnroll; ++u) {
+        const uint32_t gi = team + u * teams;
+        if (gi >= total_groups) continue;
+        const uint32_t row = gi / groups_per_row;
+        const int g = (int)(gi - row * groups_per_row);
+        float v[8];
+        if (kSrcBf16) {
+            const uint32_t r[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(r[i] << 16);            // bf16 -> f32 is exact
+                v[2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
+            }
+        } else {
+            const uint4 a = raw[u][0], b = raw[u][kSrcBf16 ? 0 : 1];
+            v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+            v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+        }
+        float vmin = v[0], vmax = v[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            vmin = fminf(vmin, v[i]);
+            vmax = fmaxf(vmax, v[i]);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            vmin = fminf(vmin, __shfl_xor_sync(gmask, vmin, o));
+            vmax = fmaxf(vmax, __shfl_xor_sync(gmask, vmax, o));
+        }
+        if (vmax == vmin) vmax = __fadd_rn(vmin, 1.0f);
+        const float fscale = __fdiv_rn(__fsub_rn(vmax, vmin), 15.0f);
+        const float fbias = vmin;
+        const float inv_scale = __fdiv_rn(1.0f, fscale);
+        uint32_t word = 0;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const float t = __fadd_rn(__fmul_rn(__fsub_rn(v[n], fbias), inv_scale), 0.5f);
+            int q = __float2int_rz(t);  // truncates, saturates, NaN -> 0: Rust `as i32`
+            q = min(max(q, 0), 15);
+            word |= ((uint32_t)q) << (n * 4);
+        }
+        const uint32_t unit = row / (uint32_t)job.rows_per_unit;
+        const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
+        const int m = (int)(rr / (uint32_t)job.rows_per_mat);
+        const int64_t r = rr - (uint32_t)m * (uint32_t)job.rows_per_mat;
+        const int64_t uoff = (int64_t)unit * job.unit_stride;
+        // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
+        uint8_t* const wb = m ? job.w_base[1] : job.w_base[0];
+        uint8_t* const sb = m ? job.s_base[1] : job.s_base[0];
+        uint8_t* const bb = m ? job.b_base[1] : job.b_base[0];
+        reinterpret_cast<uint32_t*>(wb + uoff)[r * (job.cols / 8) + g * 8 + p] = word;
+        if (p == 0) reinterpret_cast<uint16_t*>(sb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fscale);
+        if (p == 1) reinterpret_cast<uint16_t*>(bb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fbias);
+    }
 }
 
+static int run_pack_one(moe_engine* e, const PackJob& job, int src_dtype);
+
+// Splits a job at unit boundaries so that every launch covers fewer than 2^30 groups.
 static int run_pack(moe_engine* e, const PackJob& job, int src_dtype) {
+    const int64_t gpr = job.cols / kGroup;
+    const int64_t limit_rows = ((int64_t)1 << 30) / gpr;
+    if (job.n_rows <= limit_rows) return run_pack_one(e, job, src_dtype);
+    const size_t esz = src_dtype == MOE_DT_BF16 ? 2 : 4;
+    if (job.unit_stride == 0) {  // plain matrix: split by rows, advancing the three outputs
+        for (int64_t r0 = 0; r0 < job.n_rows; r0 += limit_rows) {
+            PackJob j = job;
+            j.n_rows = job.n_rows - r0 < limit_rows ? job.n_rows - r0 : limit_rows;
+            j.rows_per_unit = j.rows_per_mat = j.n_rows;
+            j.src = (const uint8_t*)job.src + (size_t)r0 * job.cols * esz;
+            for (int m = 0; m < 2; ++m) {
+                j.w_base[m] = job.w_base[m] + (size_t)r0 * (job.cols / 2);
+                j.s_base[m] = job.s_base[m] + (size_t)r0 * gpr * 2;
+                j.b_base[m] = job.b_base[m] + (size_t)r0 * gpr * 2;
+            }
+            int rc = run_pack_one(e, j, src_dtype);
+            if (rc) return rc;
+        }
+        return MOE_OK;
+    }
+    const int64_t units_per = limit_rows / job.rows_per_unit > 0 ? limit_rows / job.rows_per_unit : 1;
+    const int64_t n_units = job.n_rows / job.rows_per_unit;
+    for (int64_t u0 = 0; u0 < n_units; u0 += units_per) {
+        PackJob j = job;
+        const int64_t nu = n_units - u0 < units_per ? n_units - u0 : units_per;
+        j.n_rows = nu * job.rows_per_unit;
+        j.src = (const uint8_t*)job.src + (size_t)u0 * job.rows_per_unit * job.cols * esz;
+        for (int m = 0; m < 2; ++m) {
+            j.w_base[m] = job.w_base[m] + u0 * job.unit_stride;
+            j.s_base[m] = job.s_base[m] + u0 * job.unit_stride;
+            j.b_base[m] = job.b_base[m] + u0 * job.unit_stride;
+        }
+        int rc = run_pack_one(e, j, src_dtype);
+        if (rc) return rc;
+    }
+    return MOE_OK;
+}
+
+static int run_pack_one(moe_engine* e, const PackJob& job, int src_dtype) {
     const int64_t total_groups = job.n_rows * (job.cols / kGroup);
     if (total_groups == 0) return MOE_OK;
-    const int64_t threads = total_groups * 8;
+    const int64_t threads = (total_groups + kPackUnroll - 1) / kPackUnroll * 8;
     const int64_t blocks = (threads + 255) / 256;
     MOE_REQUIRE(blocks < (1ll << 31), "pack: too many rows for one launch (%lld blocks)", (long long)blocks);
     if (src_dtype == MOE_DT_BF16)
