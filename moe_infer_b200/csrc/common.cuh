@@ -53,6 +53,7 @@ struct LayerDev {
     Q4Dev sgate;                 // [1, H]
     const uint16_t* router_planes;  // batched path: router weights split into bf16 planes (see grouped.cu), or nullptr
     int router_nplanes;             // 1 (bf16 router) or 3 (4-bit router)
+    const void* router_t;           // decode path: router transposed to [H][E] (bf16 bits, or f32 for a 4-bit router), or nullptr
 };
 
 struct LayerHost {
@@ -63,6 +64,8 @@ struct LayerHost {
     bool router_is_bf16 = true;
     uint8_t* planes = nullptr;   // router planes of the batched path, built on first use
     bool planes_valid = false;
+    uint8_t* router_t = nullptr; // transposed router of the decode path, built on first use
+    bool router_t_valid = false;
     LayerDev dev{};
 };
 
@@ -141,6 +144,9 @@ struct moe_engine {
     int32_t* dec_idx = nullptr;            // [K]
     float* dec_w = nullptr;                // [K]
     unsigned int* dec_sync = nullptr;      // grid barrier words + error flag
+    unsigned long long* dec_act_ll = nullptr;  // fused decode kernel: tagged SwiGLU outputs
+    long long* dec_acc = nullptr;          // fused decode kernel: fixed-point router accumulators, two sets
+    unsigned int dec_epoch = 0;            // tags consumed so far (one per layer pass)
     long long* dec_prof = nullptr;         // per-phase clock stamps (off unless enabled)
     int dec_grid = 0;
     float* stage_host = nullptr;           // pinned staging [H] x 2
@@ -170,6 +176,7 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);
 void decode_destroy(moe_engine* e);
+int decode_reset_after_error(moe_engine* e);
 // Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
                   const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);

@@ -99,6 +99,7 @@ struct __align__(128) DecodeSmem {
     float prob[kMaxE];
     float red[kDecWarps];
     float red2[kDecWarps];
+    float inv_rms;
     float cand_p[kMaxE];
     int cand_i[kMaxE];
     int ncand;
@@ -117,7 +118,8 @@ __device__ __forceinline__ int slice_lo(int c, int n, int G) { return (int)(((lo
 // Arrivals are counted on one monotonically increasing word; `target` is the
 // count that completes this barrier.  Returns false (for the whole CTA) when
 // the wait gave up or another CTA already raised the error word.
-__device__ __forceinline__ bool grid_barrier(unsigned int* sync, unsigned int target, DecodeSmem* sm) {
+template <class SM>
+__device__ __forceinline__ bool grid_barrier(unsigned int* sync, unsigned int target, SM* sm) {
     // h is written with generic stores and read back by bulk (async-proxy) copies
     asm volatile("fence.proxy.async;" ::: "memory");
     __syncthreads();
@@ -200,7 +202,8 @@ __device__ __forceinline__ void prefetch_A(DecodeSmem* sm, const LayerDev& ly, c
 // of this CTA's [i0, i0 + nb) (item = slot k * I + row r: gate row r and up row r of
 // the k-th chosen expert).  Warp-private, so only a __syncwarp is needed before use
 // and warps start computing as soon as their own bytes land.
-__device__ __forceinline__ void prefetch_B_warp(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+template <class SM>
+__device__ __forceinline__ void prefetch_B_warp(SM* sm, const LayerDev& ly, const moe_expert_layout_t& L,
                                                 int i0, int nb, int warp, int lane) {
     constexpr int kPW = kH / 2 / 16;  // 64 pieces per weight row; scales/biases: 4 pieces per row
 #pragma unroll
@@ -229,7 +232,8 @@ __device__ __forceinline__ void prefetch_B_warp(DecodeSmem* sm, const LayerDev& 
 
 // phase C: a warp copies the down rows of the output element it owns (row r0 + warp)
 // for the K chosen experts and the shared expert.
-__device__ __forceinline__ void prefetch_C_warp(DecodeSmem* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+template <class SM>
+__device__ __forceinline__ void prefetch_C_warp(SM* sm, const LayerDev& ly, const moe_expert_layout_t& L,
                                                 int r0, int nc, int K, int warp, int lane) {
     for (int j = warp; j < nc; j += kDecWarps) {
         const int pw = (K + 1) * kChI;  // 16 pieces per row
@@ -249,7 +253,8 @@ __device__ __forceinline__ void prefetch_C_warp(DecodeSmem* sm, const LayerDev& 
 
 // ─── x = rmsnorm(h) * w, staged three ways (plain, chunk-transposed, chunk sums) ──
 // rms_norm_bf16 (reference src/math_util.rs:282-288), eps 1e-6.
-__device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const uint16_t* norm_w,
+template <class SM>
+__device__ __forceinline__ bool stage_norm(SM* sm, const float* h, const uint16_t* norm_w,
                                            uint32_t parity) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -267,6 +272,7 @@ __device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const
 #pragma unroll
     for (int i = 0; i < kDecWarps; ++i) tot += sm->red[i];
     const float inv_rms = 1.0f / sqrtf(tot / (float)kH + 1e-6f);
+    if (tid == 0) sm->inv_rms = inv_rms;
     float4 o;
     o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
     o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
@@ -285,8 +291,8 @@ __device__ __forceinline__ bool stage_norm(DecodeSmem* sm, const float* h, const
 }
 
 // Dot products of NR 4-bit rows of length kH (staged in shared memory) with the staged x.
-template <int NR>
-__device__ __forceinline__ void rows_dot_h(const DecodeSmem* sm, const uint4* const (&w)[NR],
+template <int NR, class SM>
+__device__ __forceinline__ void rows_dot_h(const SM* sm, const uint4* const (&w)[NR],
                                            const uint16_t* const (&s)[NR], const uint16_t* const (&b)[NR],
                                            float (&out)[NR], int lane) {
 #pragma unroll
@@ -338,14 +344,10 @@ __device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + e
 // maxima is a lower bound of the K-th largest probability, so only experts at
 // or above it are candidates; each candidate finds its rank by counting the
 // candidates that beat it.  Results come out in descending order.
-__device__ __forceinline__ void route_cta(DecodeSmem* sm, const float* logits, const float* bias,
-                                          const int32_t* forced, int E, int K) {
+template <class SM>
+__device__ __forceinline__ void route_cta(SM* sm, float v, const int32_t* forced, int E, int K) {
+    // v: this thread's router logit (thread t owns expert t; -INFINITY for t >= E)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float v = -INFINITY;
-    if (tid < E) {
-        v = __ldcg(logits + tid);  // written by other CTAs: read through L2
-        if (bias) v += bias[tid];
-    }
     float mx = v;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -499,7 +501,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
         PROF(4);
 
         // ── phase B ────────────────────────────────────────────────────────
-        route_cta(sm, p.logits, p.logit_bias, p.forced_idx, E, K);
+        {
+            float v = -INFINITY;
+            if (tid < E) {
+                v = __ldcg(p.logits + tid);  // written by other CTAs: read through L2
+                if (p.logit_bias) v += p.logit_bias[tid];
+            }
+            route_cta(sm, v, p.forced_idx, E, K);
+        }
         PROF(5);
         // request this warp's gate/up rows now; its down rows and the next layer's
         // phase-A slice are requested after the gate/up arithmetic, so that their
@@ -606,6 +615,636 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
     }
 }
 
+// ════════════════════════════════════════════════════════════════════════════
+// Fused variant: the next layer's router is folded into the down phase.
+//
+// logits_{l+1}[e] = inv_rms * sum_i Wr[e][i] * nw[i] * h_{l+1}[i] is linear in h, and after
+// the down phase every CTA owns ~14 finished elements of h_{l+1}: it multiplies them
+// with its slice of the transposed, norm-weighted router (built once per layer) and adds
+// the 256 partial sums into a global accumulator.  Partial sums are added as 64-bit
+// fixed point (2^-32 units), so the total does not depend on the order of arrival and
+// repeated runs give identical bits.  The logits are complete at the same barrier as
+// h itself, and so is the sum of squares the norm needs (one more accumulator), so routing
+// starts straight after the barrier while h is still being staged.  The shared expert's
+// gate/up rows ride along with the routed experts' as a ninth "slot".
+// The SwiGLU outputs cross from the CTAs that compute them to all CTAs without a barrier:
+// each value travels in one 8-byte word together with a tag (the layer's epoch number),
+// 8-byte stores are single-copy atomic, and a reader simply re-reads until every tag it
+// needs is current.  That leaves one counting barrier per layer (after the down phase).
+// ════════════════════════════════════════════════════════════════════════════
+constexpr size_t kActLLWords = (size_t)(kMaxK + 1) * kI + 8;
+constexpr int kMaxB3Items = 32;   // ceil((K + 1) * I / grid) gate/up row pairs incl. the shared expert
+constexpr float kFix = 4294967296.0f;  // 2^32
+constexpr int kAccStride = kMaxE + 8;
+constexpr int kLLGroups = ((kMaxK + 1) * (kI / 4) + kDecThreads - 1) / kDecThreads;  // 4-value groups per thread
+
+struct Decode3Params {
+    const LayerDev* layers;
+    int l0, l1;
+    const float* h_in;
+    float* h_out;
+    float* h_buf0;
+    float* h_buf1;
+    long long* acc;     // [2][kAccStride] fixed-point accumulators (router logits; [kMaxE] = sum of squares), zero at launch
+    unsigned long long* act_ll;  // [(K + 1) * I + 1] (tag << 32 | float bits): SwiGLU outputs, then the shared gate score
+    unsigned int epoch_base;     // tags in act_ll are <= epoch_base when the kernel starts
+    const float* logit_bias;
+    const int32_t* forced_idx;
+    int32_t* out_idx;
+    float* out_w;
+    unsigned int* sync;      // [0] arrivals, [1] exits, [2] error word
+    unsigned int* err;
+    long long* prof;
+    int E, K;
+    moe_expert_layout_t lay;
+};
+
+struct __align__(128) DecodeSmem3 {
+    uint4 b_w[2][kMaxB3Items][kChH];
+    uint4 c_w[kMaxK + 1][kMaxCRows][kChI];
+    float wt[kMaxCRows * kMaxE];          // slice of the next layer's transposed router (bf16 or f32 rows of E)
+    uint4 sg_w[kChH];                     // shared_expert_gate row (CTA 0 only)
+    uint16_t sg_s[kH / kGroup];
+    uint16_t sg_b[kH / kGroup];
+    uint16_t b_s[2][kMaxB3Items][kH / kGroup];
+    uint16_t b_b[2][kMaxB3Items][kH / kGroup];
+    uint16_t c_s[kMaxK + 1][kMaxCRows][kI / kGroup];
+    uint16_t c_b[kMaxK + 1][kMaxCRows][kI / kGroup];
+    float raw[kH];
+    float xn[kH];
+    float4 xs[8 * kChH];
+    float sumx[kChH];
+    float4 acts[(kMaxK + 1) * 8 * kChI];
+    float suma[(kMaxK + 1) * kChI];
+    float prob[kMaxE];
+    float red[kDecWarps];
+    float red2[kDecWarps];
+    float inv_rms;
+    float cand_p[kMaxE];
+    int cand_i[kMaxE];
+    int ncand;
+    float topw[kMaxK + 1];
+    float topp[kMaxK];
+    int topi[kMaxK];
+    float hn[kMaxCRows + 2];              // this CTA's finished elements of the next h, times the next norm weight
+    float hraw[kMaxCRows + 2];            // the same elements as they are
+    float hmax[32];                       // routing: maxima of 16-expert groups
+    int flag;
+    uint64_t bar_h;
+};
+static_assert(sizeof(DecodeSmem3) <= 227 * 1024, "decode staging exceeds shared memory");
+
+// Grid barrier on per-CTA flag words.  Every CTA publishes `value`; warp 0 polls until all
+// flags have reached it (wrap-safe signed comparison).  Bounded: gives up after about a second.
+__device__ __forceinline__ bool flag_barrier(unsigned int* flags, unsigned int value, int G, unsigned int* err,
+                                             DecodeSmem3* sm) {
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(value) : "memory");
+        const long long t0 = clock64();
+        int ok = 1;
+        for (uint32_t it = 0;; ++it) {
+            int done = 1;
+            for (int i = lane; i < G; i += 32) {
+                unsigned int v;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+                done &= ((int)(v - value) >= 0);
+            }
+            if (__all_sync(0xffffffffu, done)) break;
+            if ((it & 31u) == 31u) {
+                unsigned int e;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(err) : "memory");
+                if (__any_sync(0xffffffffu, e != 0u || clock64() - t0 > kWaitCycles)) { ok = 0; break; }
+            }
+        }
+        // acquire side: orders the relaxed flag reads before everything after the barrier
+        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+        if (lane == 0) {
+            if (!ok) atomicExch(err, 2u);
+            sm->flag = ok;
+            asm volatile("fence.proxy.async;" ::: "memory");
+        }
+    }
+    __syncthreads();
+    return sm->flag != 0;
+}
+
+// gate/up rows of item j (slot m = item / I: the m-th chosen expert, or the shared expert for m == K)
+__device__ __forceinline__ void prefetch_B3_warp(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                                 int i0, int nb, int K, bool with_sgate, int warp, int lane) {
+    if (with_sgate) {
+        cp16(&sm->sg_w[lane], reinterpret_cast<const uint8_t*>(ly.sgate.w) + lane * 16);
+        cp16(&sm->sg_w[lane + 32], reinterpret_cast<const uint8_t*>(ly.sgate.w) + (lane + 32) * 16);
+        if (lane < 4) cp16(reinterpret_cast<uint8_t*>(sm->sg_s) + lane * 16, reinterpret_cast<const uint8_t*>(ly.sgate.s) + lane * 16);
+        else if (lane < 8) cp16(reinterpret_cast<uint8_t*>(sm->sg_b) + (lane - 4) * 16, reinterpret_cast<const uint8_t*>(ly.sgate.b) + (lane - 4) * 16);
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int j = warp + t * kDecWarps;
+        if (j < nb) {
+            const int i = i0 + j, m = i / kI, r = i - m * kI;
+            const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+            const uint8_t* gw = ex + L.gate_w + (size_t)r * (kH / 2);
+            const uint8_t* uw = ex + L.up_w + (size_t)r * (kH / 2);
+            cp16(&sm->b_w[0][j][lane], gw + lane * 16);
+            cp16(&sm->b_w[0][j][lane + 32], gw + (lane + 32) * 16);
+            cp16(&sm->b_w[1][j][lane], uw + lane * 16);
+            cp16(&sm->b_w[1][j][lane + 32], uw + (lane + 32) * 16);
+            if (lane < 16) {
+                const int a = lane >> 2, c = lane & 3;
+                const int64_t off = a == 0 ? L.gate_s : a == 1 ? L.up_s : a == 2 ? L.gate_b : L.up_b;
+                uint16_t* d = a == 0 ? sm->b_s[0][j] : a == 1 ? sm->b_s[1][j] : a == 2 ? sm->b_b[0][j] : sm->b_b[1][j];
+                cp16(reinterpret_cast<uint8_t*>(d) + c * 16, ex + off + (size_t)r * (kH / kGroup) * 2 + c * 16);
+            }
+        }
+    }
+    cp_commit();
+}
+
+// rows [r0, r0 + nc) of a layer's transposed router (contiguous: nc * E elements), all threads
+__device__ __forceinline__ int router_t_stride(int E) { return (E + 7) & ~7; }  // elements per row: 16-byte multiples
+
+__device__ __forceinline__ void prefetch_wt(DecodeSmem3* sm, const void* router_t, bool bf16, int r0, int nc, int E, int tid) {
+    const size_t row_bytes = (size_t)router_t_stride(E) * (bf16 ? 2 : 4);
+    copy_flat(sm->wt, reinterpret_cast<const uint8_t*>(router_t) + (size_t)r0 * row_bytes, (int)(nc * row_bytes / 16), tid);
+    cp_commit();
+}
+
+// This CTA's contribution to the router logits of a layer: sum over its rows j of
+// Wr[e][r0 + j] * (h[r0 + j] * norm_w[r0 + j]), times `scale` (the caller's estimate of
+// 1 / rms(h), which keeps the fixed-point value near the size of a finished logit).
+__device__ __forceinline__ void push_partial_logits(const DecodeSmem3* sm, bool bf16, long long* acc, int nc, int E,
+                                                    float scale, int tid) {
+    if (tid < E) {
+        const int Ep = router_t_stride(E);
+        float part = 0.0f;
+        if (bf16) {
+            const uint16_t* w = reinterpret_cast<const uint16_t*>(sm->wt);
+            for (int j = 0; j < nc; ++j) part = fmaf(__uint_as_float((uint32_t)w[j * Ep + tid] << 16), sm->hn[j], part);
+        } else {
+            for (int j = 0; j < nc; ++j) part = fmaf(sm->wt[j * Ep + tid], sm->hn[j], part);
+        }
+        const long long fx = __float2ll_rn(part * scale * kFix);
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + tid, (unsigned long long)fx);
+    }
+    if (tid == kDecThreads - 1) {
+        // this CTA's share of sum((h * scale)^2)
+        float q = 0.0f;
+        for (int j = 0; j < nc; ++j) {
+            const float t = sm->hraw[j] * scale;
+            q = fmaf(t, t, q);
+        }
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + kMaxE, (unsigned long long)__float2ll_rn(q * kFix));
+    }
+}
+
+__device__ __forceinline__ void st_ll(unsigned long long* ptr, unsigned int tag, float v) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(ptr), "l"(w) : "memory");
+}
+__device__ __forceinline__ void ld_ll2(const unsigned long long* ptr, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
+}
+
+// stage_norm in two halves, so that other work can run while h is in flight
+__device__ __forceinline__ void stage_issue(DecodeSmem3* sm, const float* h) {
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(&sm->bar_h, kH * 4u);
+        bulk_g2s(sm->raw, h, kH * 4u, &sm->bar_h);
+    }
+}
+__device__ __forceinline__ bool stage_finish(DecodeSmem3* sm, const uint16_t* norm_w, uint32_t parity) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + tid);
+    if (!__syncthreads_and(mbar_wait(&sm->bar_h, parity) ? 1 : 0)) return false;
+    const float4 v = reinterpret_cast<const float4*>(sm->raw)[tid];
+    float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    if (lane == 0) sm->red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kDecWarps; ++i) tot += sm->red[i];
+    const float inv_rms = 1.0f / sqrtf(tot / (float)kH + 1e-6f);
+    if (tid == 0) sm->inv_rms = inv_rms;
+    float4 o;
+    o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
+    o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
+    o.z = v.z * inv_rms * __uint_as_float(wb.y << 16);
+    o.w = v.w * inv_rms * __uint_as_float(wb.y & 0xFFFF0000u);
+    const int c = tid >> 3, j = tid & 7;
+    sm->xs[j * kChH + c] = o;
+    float s = (o.x + o.y) + (o.z + o.w);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (j == 0) sm->sumx[c] = s;
+    __syncthreads();
+    return true;
+}
+
+// route_cta with fewer CTA-wide barriers: the threshold comes from the maxima of 16-expert
+// groups (32 of them, one per lane, ranked with shuffles), candidates are collected with one
+// shared-memory atomic per warp, and probabilities are only formed for the candidates.
+// Same arithmetic as route_cta for the values it returns: p = exp(v - max) * (1 / sum), ties to
+// the lower index, weights p_k * (1 / sum_k p_k).
+__device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32_t* forced, int E, int K) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float m = v;
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+    if ((lane & 15) == 0) sm->hmax[tid >> 4] = m;
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+    if (lane == 0) sm->red[warp] = m;
+    if (tid == 0) sm->ncand = 0;
+    __syncthreads();
+    float mx = sm->red[0];
+#pragma unroll
+    for (int i = 1; i < kDecWarps; ++i) mx = fmaxf(mx, sm->red[i]);
+    const float ex = (tid < E) ? expf(v - mx) : 0.0f;
+    const float ws = warp_sum(ex);
+    if (lane == 0) sm->red2[warp] = ws;
+    if (forced) {
+        sm->prob[tid] = ex;
+    } else {
+        // tau = K-th largest group maximum (as exp(v - max), bit-identical to its owner's value),
+        // lowered by a hair so that values which round to the same probability stay candidates
+        const float mine = (lane * 16 < E) ? expf(sm->hmax[lane] - mx) : -1.0f;
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float o = __shfl_sync(0xffffffffu, mine, j);
+            cnt += (o > mine) || (o == mine && j < lane);
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, cnt == K - 1);
+        float tau = __shfl_sync(0xffffffffu, mine, __ffs(hit) - 1);
+        tau = tau < 0.0f ? -1.0f : tau * 0.999999f;
+        const bool is_c = tid < E && ex >= tau;
+        const unsigned bal = __ballot_sync(0xffffffffu, is_c);
+        int base = 0;
+        if (lane == 0 && bal) base = atomicAdd(&sm->ncand, __popc(bal));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (is_c) {
+            const int slot = base + __popc(bal & ((1u << lane) - 1u));
+            sm->cand_p[slot] = ex;
+            sm->cand_i[slot] = tid;
+        }
+    }
+    __syncthreads();
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kDecWarps; ++i) sum += sm->red2[i];
+    const float inv = 1.0f / sum;
+    if (forced) {
+        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]] * inv; }
+    } else {
+        const int nc = sm->ncand;
+        if (tid < nc) {
+            const float cp = sm->cand_p[tid] * inv;
+            const int ci = sm->cand_i[tid];
+            int rank = 0;
+            for (int j = 0; j < nc; ++j) {
+                const float q = sm->cand_p[j] * inv;
+                rank += (q > cp) || (q == cp && sm->cand_i[j] < ci);
+            }
+            if (rank < K) { sm->topi[rank] = ci; sm->topp[rank] = cp; }
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // normalize_weights: divide by the sum of the K selected probabilities
+        float s = 0.0f;
+        for (int k = 0; k < K; ++k) s += sm->topp[k];
+        const float invs = s > 0.0f ? 1.0f / s : 1.0f;
+        if (lane < K) sm->topw[lane] = sm->topp[lane] * invs;
+    }
+    __syncthreads();
+}
+
+#ifdef MOE_DEC_SKEW
+// build-time diagnostic: wall-clock stamps of every CTA at a few points of one layer
+__device__ long long g_dbg[8 * 1024];
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define DBG(k) do { if (p.prof && l == p.l0 + 4 && tid == 0) g_dbg[(k) * 1024 + cta] = gtime(); } while (0)
+#else
+#define DBG(k) do { } while (0)
+#endif
+#define PROF3(idx)                                                                                 \
+    do {                                                                                           \
+        if (p.prof && cta == 0 && tid == 0) p.prof[(l - p.l0) * kProfPoints + (idx)] = clock64();  \
+    } while (0)
+
+static_assert(kMaxCRows <= kDecWarps, "one finished element of h per warp");
+
+__global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Params p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    DecodeSmem3* sm = reinterpret_cast<DecodeSmem3*>(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = gridDim.x;
+    const int cta = blockIdx.x;
+    const int E = p.E, K = p.K;
+    const moe_expert_layout_t L = p.lay;
+
+    if (tid == 0) {
+        mbar_init(&sm->bar_h, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int n_items = (K + 1) * kI;
+    const int i0 = slice_lo(cta, n_items, G), nb = slice_lo(cta + 1, n_items, G) - i0;
+    const int r0 = slice_lo(cta, kH, G), nc = slice_lo(cta + 1, kH, G) - r0;
+    // the shared expert's gate score is one more row: CTA 0's last warp takes it
+    const bool sg_here = (cta == 0 && warp == kDecWarps - 1);
+
+    unsigned int bar_target = 0;
+    uint32_t parity = 0;
+    bool alive = true;
+    float pscale = 1.0f;  // scale the pending accumulators were pushed with
+
+    // ── prologue: router logits and sum of squares of the first layer from h_in ──
+    {
+        const LayerDev ly = p.layers[p.l0];
+        prefetch_wt(sm, ly.router_t, ly.router_bf16 != nullptr, r0, nc, E, tid);
+        if (!stage_norm(sm, p.h_in, ly.post_norm, parity)) {
+            if (tid == 0) atomicExch(p.err, 3u);
+            alive = false;
+        }
+        parity ^= 1u;
+        if (alive) {
+            pscale = sm->inv_rms;
+            if (tid < nc) {
+                const float hv = sm->raw[r0 + tid];
+                sm->hraw[tid] = hv;
+                sm->hn[tid] = hv * __uint_as_float((uint32_t)ly.post_norm[r0 + tid] << 16);
+            }
+            cp_wait<0>();
+            __syncthreads();
+            push_partial_logits(sm, ly.router_bf16 != nullptr, p.acc, nc, E, pscale, tid);
+            bar_target += G;
+            if (!grid_barrier(p.sync, bar_target, sm)) alive = false;
+        }
+    }
+
+    for (int l = p.l0; l < p.l1 && alive; ++l) {
+        const LayerDev ly = p.layers[l];
+        const int rel = l - p.l0;
+        const bool has_next = l + 1 < p.l1;
+        const float* h_cur = (rel == 0) ? p.h_in : ((rel & 1) ? p.h_buf0 : p.h_buf1);
+        float* h_nxt = !has_next ? p.h_out : ((rel & 1) ? p.h_buf1 : p.h_buf0);
+        long long* acc_cur = p.acc + (rel & 1) * kAccStride;
+        long long* acc_nxt = p.acc + ((rel + 1) & 1) * kAccStride;
+        const unsigned int epoch = p.epoch_base + (unsigned int)rel + 1u;
+
+        // ── route (from the accumulators) while h is being staged ──────────
+        PROF3(0);
+        DBG(4);
+        stage_issue(sm, h_cur);
+        {
+            float v = -INFINITY;
+            const long long aq = __ldcg(acc_cur + kMaxE);
+            long long a = 0;
+            if (tid < E) a = __ldcg(acc_cur + tid);
+            // mean of (h * pscale)^2 -> 1 / rms(h); the logits were accumulated times pscale
+            const float r = 1.0f / pscale;
+            const float msq = __ll2float_rn(aq) * (1.0f / kFix) * (1.0f / (float)kH);
+            const float inv_rms_acc = 1.0f / sqrtf(msq * r * r + 1e-6f);
+            if (tid < E) {
+                v = __ll2float_rn(a) * (1.0f / kFix) * r * inv_rms_acc;
+                if (p.logit_bias) v += p.logit_bias[tid];
+            }
+            route_fast(sm, v, p.forced_idx, E, K);
+        }
+        PROF3(1);
+        prefetch_B3_warp(sm, ly, L, i0, nb, K, sg_here, warp, lane);
+        if (cta == 0 && warp == 0 && lane < K) {
+            if (p.out_idx) p.out_idx[lane] = sm->topi[lane];
+            if (p.out_w) p.out_w[lane] = sm->topw[lane];
+        }
+        // next layer's norm weight of the element of h this warp will finish
+        float nwn = 0.0f;
+        if (has_next && warp < nc && lane == 0)
+            nwn = __uint_as_float((uint32_t)__ldg(p.layers[l + 1].post_norm + r0 + warp) << 16);
+        PROF3(2);
+        if (!stage_finish(sm, ly.post_norm, parity)) {
+            if (tid == 0) atomicExch(p.err, 3u);
+            alive = false;
+            break;
+        }
+        parity ^= 1u;
+        const float inv_rms = sm->inv_rms;
+        PROF3(3);
+        cp_wait<0>();  // this warp's gate/up rows landed
+        __syncwarp();
+        PROF3(4);
+        {
+            bool sg_done = !sg_here;
+            for (int j = warp; j < nb; j += 2 * kDecWarps) {
+                const int j2 = j + kDecWarps;
+                const bool two = j2 < nb;
+                const bool sg_now = !two && !sg_done;  // the spare half of the pass takes the gate-score row
+                const int jb = two ? j2 : j;
+                const uint4* const w[4] = {sm->b_w[0][j], sm->b_w[1][j], sg_now ? sm->sg_w : sm->b_w[0][jb], sm->b_w[1][jb]};
+                const uint16_t* const s[4] = {sm->b_s[0][j], sm->b_s[1][j], sg_now ? sm->sg_s : sm->b_s[0][jb], sm->b_s[1][jb]};
+                const uint16_t* const b[4] = {sm->b_b[0][j], sm->b_b[1][j], sg_now ? sm->sg_b : sm->b_b[0][jb], sm->b_b[1][jb]};
+                float o[4];
+                rows_dot_h<4>(sm, w, s, b, o, lane);
+                if (lane == 0) {
+                    st_ll(p.act_ll + i0 + j, epoch, swiglu(o[0], o[1]));
+                    if (two) st_ll(p.act_ll + i0 + j2, epoch, swiglu(o[2], o[3]));
+                    if (sg_now) st_ll(p.act_ll + n_items, epoch, o[2]);
+                }
+                sg_done |= sg_now;
+            }
+            if (!sg_done) {
+                const uint4* const w[1] = {sm->sg_w};
+                const uint16_t* const s[1] = {sm->sg_s};
+                const uint16_t* const b[1] = {sm->sg_b};
+                float o[1];
+                rows_dot_h<1>(sm, w, s, b, o, lane);
+                if (lane == 0) st_ll(p.act_ll + n_items, epoch, o[0]);
+            }
+        }
+        prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
+        if (has_next) {
+            const LayerDev& nx = p.layers[l + 1];
+            prefetch_wt(sm, nx.router_t, nx.router_bf16 != nullptr, r0, nc, E, tid);
+        } else {
+            cp_commit();  // keep the group count per layer fixed
+        }
+        PROF3(5);
+        DBG(0);
+
+        // ── gather every CTA's SwiGLU outputs: re-read until all tags are current ──
+        {
+            const int n_g = (K + 1) * (kI / 4);  // groups of 4 values
+            unsigned long long q[kLLGroups][4];
+            unsigned long long qs = 0;
+            unsigned int pending = 0;
+#pragma unroll
+            for (int t = 0; t < kLLGroups; ++t)
+                if (tid + t * kDecThreads < n_g) pending |= 1u << t;
+            const bool sg_reader = (tid == kDecThreads - 1);
+            if (sg_reader) pending |= 1u << kLLGroups;
+            const long long t0 = clock64();
+            int ok = 1;
+            for (uint32_t it = 0; pending; ++it) {
+#pragma unroll
+                for (int t = 0; t < kLLGroups; ++t)
+                    if (pending >> t & 1u) {
+                        const unsigned long long* src = p.act_ll + 4 * (size_t)(tid + t * kDecThreads);
+                        ld_ll2(src, q[t][0], q[t][1]);
+                        ld_ll2(src + 2, q[t][2], q[t][3]);
+                    }
+                if (pending >> kLLGroups & 1u)
+                    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(qs) : "l"(p.act_ll + n_items) : "memory");
+#pragma unroll
+                for (int t = 0; t < kLLGroups; ++t)
+                    if (pending >> t & 1u) {
+                        const bool cur = (unsigned int)(q[t][0] >> 32) == epoch && (unsigned int)(q[t][1] >> 32) == epoch &&
+                                         (unsigned int)(q[t][2] >> 32) == epoch && (unsigned int)(q[t][3] >> 32) == epoch;
+                        if (cur) pending &= ~(1u << t);
+                    }
+                if ((pending >> kLLGroups & 1u) && (unsigned int)(qs >> 32) == epoch) pending &= ~(1u << kLLGroups);
+                if (pending && (it & 15u) == 15u) {
+                    unsigned int e;
+                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(p.err) : "memory");
+                    if (e != 0u || clock64() - t0 > kWaitCycles) { ok = 0; break; }
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int t = 0; t < kLLGroups; ++t) {
+                const int i = tid + t * kDecThreads;
+                if (i < n_g) {  // uniform per warp: n_g and the stride are multiples of 32
+                    float4 v;
+                    v.x = __uint_as_float((unsigned int)q[t][0]);
+                    v.y = __uint_as_float((unsigned int)q[t][1]);
+                    v.z = __uint_as_float((unsigned int)q[t][2]);
+                    v.w = __uint_as_float((unsigned int)q[t][3]);
+                    const int m = i / (kI / 4), f = i - m * (kI / 4);
+                    const int c = f >> 3, j = f & 7;
+                    sm->acts[(m * 8 + j) * kChI + c] = v;
+                    float sv = (v.x + v.y) + (v.z + v.w);
+                    sv += __shfl_xor_sync(0xffffffffu, sv, 1);
+                    sv += __shfl_xor_sync(0xffffffffu, sv, 2);
+                    sv += __shfl_xor_sync(0xffffffffu, sv, 4);
+                    if (j == 0) sm->suma[m * kChI + c] = sv;
+                }
+            }
+            // sigmoid (reference src/math_util.rs:67-69) of the shared gate score
+            if (sg_reader) sm->topw[K] = 1.0f / (1.0f + expf(-__uint_as_float((unsigned int)qs)));
+            DBG(1);
+            PROF3(6);
+            cp_wait<1>();  // this warp's down rows landed
+            if (!__syncthreads_and(ok)) {
+                if (tid == 0) atomicExch(p.err, 4u);
+                alive = false;
+                break;
+            }
+            // Every CTA routed (and so read these accumulators) before it produced the outputs
+            // that this CTA has now seen in full: safe to clear them for the layer after next.
+            if (cta == 0) {
+                if (tid < E) acc_cur[tid] = 0;
+                if (tid == kDecThreads - 1) acc_cur[kMaxE] = 0;
+            }
+        }
+        PROF3(7);
+        DBG(5);
+        {
+            const int sub = lane >> 4, c = lane & 15;
+            constexpr int kMats = (kMaxK + 2) / 2;
+            if (warp < nc) {
+                const int j = warp;
+                float acc = 0.0f;
+#pragma unroll
+                for (int jm = 0; jm < kMats; ++jm) {
+                    const int m = sub + 2 * jm;
+                    if (m <= K) {
+                        float4 xv[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) xv[q] = sm->acts[(m * 8 + q) * kChI + c];
+                        acc = fmaf(sm->topw[m],
+                                   chunk_term(sm->c_w[m][j][c], xv, sm->suma[m * kChI + c], sm->c_s[m][j][c >> 1],
+                                              sm->c_b[m][j][c >> 1]),
+                                   acc);
+                    }
+                }
+                acc = warp_sum(acc);
+                // moe_combine_residual (reference src/math_util.rs:599-612)
+                if (lane == 0) {
+                    const float hv = sm->raw[r0 + j] + acc;
+                    h_nxt[r0 + j] = hv;
+                    sm->hraw[j] = hv;
+                    sm->hn[j] = hv * nwn;
+                }
+            }
+            PROF3(8);
+            if (has_next) {
+                cp_wait<0>();  // the next router's slice landed
+                __syncthreads();
+                push_partial_logits(sm, p.layers[l + 1].router_bf16 != nullptr, acc_nxt, nc, E, inv_rms, tid);
+                pscale = inv_rms;
+                PROF3(9);
+                DBG(2);
+                bar_target += G;
+                if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
+                DBG(3);
+                PROF3(10);
+            }
+        }
+    }
+
+    // Last CTA out rewinds the barrier words for the next launch.
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&p.sync[1], 1u) + 1u;
+        if (done == (unsigned int)G) {
+            p.sync[0] = 0u;
+            p.sync[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+// Transposed router of a layer for the fused decode kernel: out[i][e] = Wr[e][i], as bf16
+// bit patterns when the router is bf16 and as dequantised f32 when it is 4-bit; rows are
+// padded with zeros to router_t_stride(E) elements.
+__global__ void __launch_bounds__(256) router_transpose_kernel(LayerDev ly, int E, void* out) {
+    const int Ep = router_t_stride(E);
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int i_blk = blockIdx.x * 32, e_blk = blockIdx.y * 32;
+    for (int r = ty; r < 32; r += 8) {
+        const int e = e_blk + r, i = i_blk + tx;
+        float v = 0.0f;
+        if (e < E) {
+            if (ly.router_bf16) {
+                v = __uint_as_float((uint32_t)ly.router_bf16[(size_t)e * kH + i] << 16);
+            } else {
+                const uint32_t word = ly.router_q4.w[(size_t)e * (kH / 8) + (i >> 3)];
+                const float q = (float)((word >> (4 * (i & 7))) & 15u);
+                const size_t g = (size_t)e * (kH / kGroup) + i / kGroup;
+                v = fmaf(q, __uint_as_float((uint32_t)ly.router_q4.s[g] << 16), __uint_as_float((uint32_t)ly.router_q4.b[g] << 16));
+            }
+        }
+        tile[r][tx] = v;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int i = i_blk + r, e = e_blk + tx;
+        if (e < Ep) {
+            const float v = tile[tx][r];  // zero beyond E
+            if (ly.router_bf16) reinterpret_cast<uint16_t*>(out)[(size_t)i * Ep + e] = (uint16_t)(__float_as_uint(v) >> 16);
+            else reinterpret_cast<float*>(out)[(size_t)i * Ep + e] = v;
+        }
+    }
+}
+
 // ─── host side ──────────────────────────────────────────────────────────────
 
 int decode_init(moe_engine* e) {
@@ -621,9 +1260,19 @@ int decode_init(moe_engine* e) {
     MOE_CUDA(cudaMemset(e->dec_sync, 0, 16 * sizeof(unsigned int)));
     e->dec_prof = nullptr;
     MOE_CUDA(cudaMallocHost(&e->stage_host, (size_t)2 * d.hidden * sizeof(float)));
+    MOE_CUDA(cudaMalloc(&e->dec_act_ll, kActLLWords * sizeof(unsigned long long)));
+    MOE_CUDA(cudaMemset(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long)));
+    MOE_CUDA(cudaMalloc(&e->dec_acc, 2 * kAccStride * sizeof(long long)));
+    MOE_CUDA(cudaMemset(e->dec_acc, 0, 2 * kAccStride * sizeof(long long)));
+    e->dec_epoch = 0;
     MOE_CUDA(cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)sizeof(DecodeSmem)));
+    MOE_CUDA(cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)sizeof(DecodeSmem3)));
     int per_sm = 0;
+    MOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_fused_kernel, kDecThreads,
+                                                           sizeof(DecodeSmem3)));
+    MOE_REQUIRE(per_sm >= 1, "fused decode kernel does not fit on an SM");
     MOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_kernel, kDecThreads,
                                                            sizeof(DecodeSmem)));
     MOE_REQUIRE(per_sm >= 1, "decode kernel does not fit on an SM");
@@ -658,7 +1307,35 @@ void decode_destroy(moe_engine* e) {
     if (e->dec_prof) cudaFree(e->dec_prof);
     cudaFree(e->dec_h[0]); cudaFree(e->dec_h[1]); cudaFree(e->dec_logits); cudaFree(e->dec_act);
     cudaFree(e->dec_misc); cudaFree(e->dec_idx); cudaFree(e->dec_w); cudaFree(e->dec_sync);
+    cudaFree(e->dec_act_ll); cudaFree(e->dec_acc);
     if (e->stage_host) cudaFreeHost(e->stage_host);
+}
+
+// After a failed device-side wait (and before the epoch counter would wrap) the tagged
+// exchange buffer and the router accumulators are in an unknown state: put them back to the state a launch expects.
+int decode_reset_after_error(moe_engine* e) {
+    MOE_CUDA(cudaMemsetAsync(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long), e->stream));
+    MOE_CUDA(cudaMemsetAsync(e->dec_acc, 0, 2 * kAccStride * sizeof(long long), e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    e->dec_epoch = 0;
+    return MOE_OK;
+}
+
+// Builds the transposed router of a layer on first decode use (and after the router is reloaded).
+static int ensure_router_t(moe_engine* e, int layer) {
+    LayerHost& lh = e->layers[layer];
+    if (lh.router_t_valid) return MOE_OK;
+    const int E = e->dims.num_experts;
+    const int Ep = (E + 7) & ~7;
+    if (!lh.router_t) MOE_CUDA(cudaMalloc(&lh.router_t, (size_t)kH * Ep * sizeof(float)));
+    int rc = refresh_layer_table(e);  // lh.dev must point at the current router
+    if (rc != MOE_OK) return rc;
+    router_transpose_kernel<<<dim3(kH / 32, (Ep + 31) / 32), 256, 0, e->stream>>>(lh.dev, E, lh.router_t);
+    MOE_CUDA(cudaGetLastError());
+    e->launches++;
+    lh.router_t_valid = true;
+    e->table_dirty = true;
+    return MOE_OK;
 }
 
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
@@ -671,32 +1348,40 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     const int G = e->dec_grid;
     auto cdiv = [](int a, int b) { return (a + b - 1) / b; };
     // every CTA's weight slice must fit its shared-memory staging area
-    MOE_REQUIRE(cdiv(d.num_experts, G) <= kMaxRouterRows && cdiv(kI, G) <= kMaxSharedRows &&
-                    cdiv(d.top_k * kI, G) <= kMaxBItems && cdiv(kH, G) <= kMaxCRows,
+    MOE_REQUIRE(cdiv((d.top_k + 1) * kI, G) <= kMaxB3Items && cdiv(kH, G) <= kMaxCRows,
                 "decode kernel needs at least 147 SMs for these dimensions (device has %d)", G);
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
     for (int l = l0; l < l1; ++l) {
         int rc = check_layer_ready(e, l);
         if (rc != MOE_OK) return rc;
+        rc = ensure_router_t(e, l);
+        if (rc != MOE_OK) return rc;
     }
     int rc = refresh_layer_table(e);
     if (rc != MOE_OK) return rc;
-    DecodeParams p{};
+    Decode3Params p{};
     p.layers = e->layers_dev;
     p.l0 = l0; p.l1 = l1;
     p.h_in = h_in; p.h_out = h_out;
     p.h_buf0 = e->dec_h[0]; p.h_buf1 = e->dec_h[1];
-    p.logits = e->dec_logits; p.act = e->dec_act; p.misc = e->dec_misc;
+    if (e->dec_epoch > 0xFFFF0000u - (unsigned int)(l1 - l0)) {
+        rc = decode_reset_after_error(e);  // tags must never repeat: start the epochs over on a cleared buffer
+        if (rc != MOE_OK) return rc;
+    }
+    p.acc = e->dec_acc; p.act_ll = e->dec_act_ll;
+    p.epoch_base = e->dec_epoch;
+    e->dec_epoch += (unsigned int)(l1 - l0);
     p.logit_bias = logit_bias; p.forced_idx = forced_idx;
     p.out_idx = out_idx; p.out_w = out_w;
     p.sync = e->dec_sync;
+    p.err = e->dec_sync + 2;
     p.prof = e->dec_prof;
     p.E = d.num_experts; p.K = d.top_k;
     p.lay = e->lay;
     void* args[] = {&p};
-    MOE_CUDA(cudaLaunchCooperativeKernel((const void*)decode_stack_kernel, dim3(e->dec_grid), dim3(kDecThreads),
-                                         args, sizeof(DecodeSmem), e->stream));
+    MOE_CUDA(cudaLaunchCooperativeKernel((const void*)decode_fused_kernel, dim3(e->dec_grid), dim3(kDecThreads),
+                                         args, sizeof(DecodeSmem3), e->stream));
     e->launches++;
     return MOE_OK;
 }
@@ -829,3 +1514,9 @@ extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, cons
     cudaSetDevice(prev);
     return rc;
 }
+
+#ifdef MOE_DEC_SKEW
+extern "C" int moe_debug_read(long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, moe::g_dbg, (size_t)n * sizeof(long long));
+}
+#endif

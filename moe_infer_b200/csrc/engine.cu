@@ -118,6 +118,7 @@ int refresh_layer_table(moe_engine* e) {
         }
         dv.router_planes = lh.planes_valid ? (const uint16_t*)lh.planes : nullptr;
         dv.router_nplanes = lh.router_is_bf16 ? 1 : 3;
+        dv.router_t = lh.router_t_valid ? lh.router_t : nullptr;
         lh.dev = dv;
         tab[l] = dv;
     }
@@ -157,6 +158,7 @@ static int poll_device_error(moe_engine* e) {
     if (flag != 0) {
         cudaMemsetAsync(e->dec_sync, 0, 16 * sizeof(unsigned int), e->stream);
         cudaStreamSynchronize(e->stream);
+        decode_reset_after_error(e);
         set_error("a bounded device-side wait gave up (code %u); the result of the last call is invalid", flag);
         return MOE_ERR_DEVICE_WAIT;
     }
@@ -258,6 +260,7 @@ void moe_engine_destroy(moe_engine_t* e) {
         if (lh.experts) cudaFree(lh.experts);
         if (lh.aux) cudaFree(lh.aux);
         if (lh.planes) cudaFree(lh.planes);
+        if (lh.router_t) cudaFree(lh.router_t);
     }
     moe_ep_finalize(e);
     decode_destroy(e);
@@ -349,6 +352,7 @@ int moe_store_load_tensor(moe_engine_t* e, int layer, int role, const void* w, c
             }
             e->table_dirty = true;
             lh.planes_valid = false;  // rebuilt from the new router on the next batched call
+            lh.router_t_valid = false;
             break;
         case MOE_T_SHARED_GATE:
             rc = up_q4(a.shared + S.gate_w, a.shared + S.gate_s, a.shared + S.gate_b, d.shared_inter, d.hidden);
