@@ -635,6 +635,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
 constexpr size_t kActLLWords = (size_t)(kMaxK + 1) * kI + 8;
 constexpr int kMaxB3Items = 32;   // ceil((K + 1) * I / grid) gate/up row pairs incl. the shared expert
 constexpr float kFix = 4294967296.0f;  // 2^32
+constexpr int kMaxDecLayers = 64;  // layer table rows staged in shared memory per launch
 constexpr int kAccStride = kMaxE + 8;
 constexpr int kLLGroups = ((kMaxK + 1) * (kI / 4) + kDecThreads - 1) / kDecThreads;  // 4-value groups per thread
 
@@ -648,6 +649,8 @@ struct Decode3Params {
     long long* acc;     // [2][kAccStride] fixed-point accumulators (router logits; [kMaxE] = sum of squares), zero at launch
     unsigned long long* act_ll;  // [(K + 1) * I + 1] (tag << 32 | float bits): SwiGLU outputs, then the shared gate score
     unsigned int epoch_base;     // tags in act_ll are <= epoch_base when the kernel starts
+    unsigned long long* hint;    // counts CTAs that have written their outputs (a hint: the tags decide)
+    unsigned long long hint_base;
     const float* logit_bias;
     const int32_t* forced_idx;
     int32_t* out_idx;
@@ -691,6 +694,9 @@ struct __align__(128) DecodeSmem3 {
     float hmax[32];                       // routing: maxima of 16-expert groups
     int flag;
     uint64_t bar_h;
+    uint64_t bar_b;   // gate/up slices landed
+    uint64_t bar_c;   // down slices and the next router's slice landed
+    LayerDev tab[kMaxDecLayers];  // this launch's rows of the layer table
 };
 static_assert(sizeof(DecodeSmem3) <= 227 * 1024, "decode staging exceeds shared memory");
 
@@ -763,9 +769,68 @@ __device__ __forceinline__ void prefetch_B3_warp(DecodeSmem3* sm, const LayerDev
     cp_commit();
 }
 
-// rows [r0, r0 + nc) of a layer's transposed router (contiguous: nc * E elements), all threads
 __device__ __forceinline__ int router_t_stride(int E) { return (E + 7) & ~7; }  // elements per row: 16-byte multiples
 
+// ─── weight slices by bulk copy ─────────────────────────────────────────────
+// A CTA's gate/up items are consecutive (slot, row) pairs, so each of the six arrays it needs
+// (gate/up weights, scales, biases) is at most two contiguous byte ranges (one per slot
+// touched): twelve bulk copies, issued by twelve different threads, each announcing its own
+// bytes on the mbarrier (which counts kBCopies arrivals per phase).
+constexpr bool kBulk = false;   // gate/up slices by bulk copy
+constexpr bool kBulkC = false;  // down slices by bulk copy as well (measured slower: many small copies)
+constexpr int kBCopies = 12;
+constexpr int kCCopies = 3 * (kMaxK + 1) + 1;
+
+__device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                            int i0, int nb, int K, int q) {
+    const int a = q >> 1, sg = q & 1;
+    const int m0 = i0 / kI, ra = i0 - m0 * kI;
+    const int n0 = min(nb, kI - ra), n1 = nb - n0;
+    const int m = m0 + sg, row = sg ? 0 : ra, n = sg ? n1 : n0, j0 = sg ? n0 : 0;
+    uint32_t bytes = 0;
+    if (n > 0) {
+        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+        const bool is_w = a < 2;
+        const int64_t off = a == 0 ? L.gate_w : a == 1 ? L.up_w : a == 2 ? L.gate_s : a == 3 ? L.up_s : a == 4 ? L.gate_b : L.up_b;
+        const uint32_t row_bytes = is_w ? kH / 2 : (kH / kGroup) * 2;
+        void* dst = a == 0 ? (void*)sm->b_w[0][j0] : a == 1 ? (void*)sm->b_w[1][j0] : a == 2 ? (void*)sm->b_s[0][j0]
+                  : a == 3 ? (void*)sm->b_s[1][j0] : a == 4 ? (void*)sm->b_b[0][j0] : (void*)sm->b_b[1][j0];
+        bytes = (uint32_t)n * row_bytes;
+        mbar_expect_tx(&sm->bar_b, bytes);
+        bulk_g2s(dst, ex + off + (size_t)row * row_bytes, bytes, &sm->bar_b);
+    } else {
+        mbar_expect_tx(&sm->bar_b, 0u);
+    }
+}
+
+// Down rows [r0, r0 + nc) of matrix m (weights, scales, biases: q = 3 m + kind) and, as copy
+// number kCCopies - 1, the next layer's slice of the transposed router.
+__device__ __forceinline__ void bulk_C_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                            const void* next_router_t, bool next_bf16, int r0, int nc, int E, int K, int q) {
+    const void* src = nullptr;
+    void* dst = nullptr;
+    uint32_t bytes = 0;
+    if (q == kCCopies - 1) {
+        if (next_router_t) {
+            const size_t row_bytes = (size_t)router_t_stride(E) * (next_bf16 ? 2 : 4);
+            src = reinterpret_cast<const uint8_t*>(next_router_t) + (size_t)r0 * row_bytes;
+            dst = sm->wt;
+            bytes = (uint32_t)(nc * row_bytes);
+        }
+    } else {
+        const int m = q / 3, kind = q - 3 * m;
+        if (m <= K) {
+            const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+            if (kind == 0) { src = ex + L.down_w + (size_t)r0 * (kI / 2); dst = sm->c_w[m][0]; bytes = (uint32_t)nc * (kI / 2); }
+            else if (kind == 1) { src = ex + L.down_s + (size_t)r0 * (kI / kGroup) * 2; dst = sm->c_s[m][0]; bytes = (uint32_t)nc * (kI / kGroup) * 2; }
+            else { src = ex + L.down_b + (size_t)r0 * (kI / kGroup) * 2; dst = sm->c_b[m][0]; bytes = (uint32_t)nc * (kI / kGroup) * 2; }
+        }
+    }
+    mbar_expect_tx(&sm->bar_c, bytes);
+    if (bytes) bulk_g2s(dst, src, bytes, &sm->bar_c);
+}
+
+// rows [r0, r0 + nc) of a layer's transposed router (contiguous: nc * E elements), all threads
 __device__ __forceinline__ void prefetch_wt(DecodeSmem3* sm, const void* router_t, bool bf16, int r0, int nc, int E, int tid) {
     const size_t row_bytes = (size_t)router_t_stride(E) * (bf16 ? 2 : 4);
     copy_flat(sm->wt, reinterpret_cast<const uint8_t*>(router_t) + (size_t)r0 * row_bytes, (int)(nc * row_bytes / 16), tid);
@@ -929,8 +994,10 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
 __device__ long long g_dbg[8 * 1024];
 __device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define DBG(k) do { if (p.prof && l == p.l0 + 4 && tid == 0) g_dbg[(k) * 1024 + cta] = gtime(); } while (0)
+#define DBGW(k) do { if (p.prof && l == p.l0 + 4 && lane == 0) atomicMax((unsigned long long*)&g_dbg[(k) * 1024 + cta], (unsigned long long)gtime()); } while (0)
 #else
 #define DBG(k) do { } while (0)
+#define DBGW(k) do { } while (0)
 #endif
 #define PROF3(idx)                                                                                 \
     do {                                                                                           \
@@ -950,7 +1017,17 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
 
     if (tid == 0) {
         mbar_init(&sm->bar_h, 1);
+        mbar_init(&sm->bar_b, kBCopies);
+        mbar_init(&sm->bar_c, kCCopies);
         mbar_fence_init();
+    }
+    {
+        // pointer loads from shared memory instead of dependent global loads on the critical path
+        static_assert(sizeof(LayerDev) % 4 == 0, "table rows are copied as words");
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.layers + p.l0);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(sm->tab);
+        const int words = (p.l1 - p.l0) * (int)(sizeof(LayerDev) / 4);
+        for (int i = tid; i < words; i += kDecThreads) dst[i] = __ldg(src + i);
     }
     __syncthreads();
 
@@ -961,13 +1038,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
     const bool sg_here = (cta == 0 && warp == kDecWarps - 1);
 
     unsigned int bar_target = 0;
-    uint32_t parity = 0;
+    uint32_t parity = 0, wpar = 0;
     bool alive = true;
     float pscale = 1.0f;  // scale the pending accumulators were pushed with
 
     // ── prologue: router logits and sum of squares of the first layer from h_in ──
     {
-        const LayerDev ly = p.layers[p.l0];
+        const LayerDev& ly = sm->tab[0];
         prefetch_wt(sm, ly.router_t, ly.router_bf16 != nullptr, r0, nc, E, tid);
         if (!stage_norm(sm, p.h_in, ly.post_norm, parity)) {
             if (tid == 0) atomicExch(p.err, 3u);
@@ -990,7 +1067,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
     }
 
     for (int l = p.l0; l < p.l1 && alive; ++l) {
-        const LayerDev ly = p.layers[l];
+        const LayerDev& ly = sm->tab[l - p.l0];
         const int rel = l - p.l0;
         const bool has_next = l + 1 < p.l1;
         const float* h_cur = (rel == 0) ? p.h_in : ((rel & 1) ? p.h_buf0 : p.h_buf1);
@@ -1019,7 +1096,19 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             route_fast(sm, v, p.forced_idx, E, K);
         }
         PROF3(1);
-        prefetch_B3_warp(sm, ly, L, i0, nb, K, sg_here, warp, lane);
+        if (kBulk) {
+            // one copy per thread: gate/up slices first, then everything the down phase needs
+            if (lane == 0 && warp < kBCopies) bulk_B_copy(sm, ly, L, i0, nb, K, warp);
+            if (kBulkC && (lane == 1 || lane == 2) && 2 * warp + lane - 1 < kCCopies) {
+                const LayerDev& nx = sm->tab[has_next ? rel + 1 : rel];
+                bulk_C_copy(sm, ly, L, has_next ? nx.router_t : nullptr, nx.router_bf16 != nullptr, r0, nc, E, K,
+                            2 * warp + lane - 1);
+            }
+            if (sg_here) prefetch_B3_warp(sm, ly, L, i0, 0, K, true, warp, lane);  // the gate-score row only
+            else cp_commit();
+        } else {
+            prefetch_B3_warp(sm, ly, L, i0, nb, K, sg_here, warp, lane);
+        }
         if (cta == 0 && warp == 0 && lane < K) {
             if (p.out_idx) p.out_idx[lane] = sm->topi[lane];
             if (p.out_w) p.out_w[lane] = sm->topw[lane];
@@ -1027,7 +1116,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         // next layer's norm weight of the element of h this warp will finish
         float nwn = 0.0f;
         if (has_next && warp < nc && lane == 0)
-            nwn = __uint_as_float((uint32_t)__ldg(p.layers[l + 1].post_norm + r0 + warp) << 16);
+            nwn = __uint_as_float((uint32_t)__ldg(sm->tab[rel + 1].post_norm + r0 + warp) << 16);
         PROF3(2);
         if (!stage_finish(sm, ly.post_norm, parity)) {
             if (tid == 0) atomicExch(p.err, 3u);
@@ -1037,7 +1126,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         parity ^= 1u;
         const float inv_rms = sm->inv_rms;
         PROF3(3);
-        cp_wait<0>();  // this warp's gate/up rows landed
+        int landed = 1;
+        cp_wait<0>();  // this warp's gate/up rows (and the gate-score row) landed
+        if (kBulk) landed = mbar_wait(&sm->bar_b, wpar) ? 1 : 0;
         __syncwarp();
         PROF3(4);
         {
@@ -1068,12 +1159,21 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 if (lane == 0) st_ll(p.act_ll + n_items, epoch, o[0]);
             }
         }
-        prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
-        if (has_next) {
-            const LayerDev& nx = p.layers[l + 1];
-            prefetch_wt(sm, nx.router_t, nx.router_bf16 != nullptr, r0, nc, E, tid);
-        } else {
-            cp_commit();  // keep the group count per layer fixed
+        DBGW(6);
+        // Tell the others that this CTA's outputs are on their way.  Not ordered against the
+        // stores above (no fence): readers use it only to decide when to start reading.
+        __syncthreads();
+        if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.hint), "l"(1ull) : "memory");
+        // down rows and the next router's slice: requested after the gate/up arithmetic, so that their
+        // issue (which stalls while the load queues are full) does not delay it
+        if (!kBulkC) {
+            prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
+            if (has_next) {
+                const LayerDev& nx = sm->tab[rel + 1];
+                prefetch_wt(sm, nx.router_t, nx.router_bf16 != nullptr, r0, nc, E, tid);
+            } else {
+                cp_commit();  // keep the group count per layer fixed
+            }
         }
         PROF3(5);
         DBG(0);
@@ -1090,12 +1190,31 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             const bool sg_reader = (tid == kDecThreads - 1);
             if (sg_reader) pending |= 1u << kLLGroups;
             const long long t0 = clock64();
-            int ok = 1;
+            int ok = landed;
+            if (tid == 0) {
+                const unsigned long long want_n = p.hint_base + (unsigned long long)G * (unsigned long long)(rel + 1);
+                for (uint32_t it = 0;; ++it) {
+                    unsigned long long n;
+                    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(n) : "l"(p.hint) : "memory");
+                    if (n >= want_n) break;
+                    if ((it & 63u) == 63u && clock64() - t0 > kWaitCycles) { ok = 0; break; }
+                }
+            }
+            __syncthreads();
+            // the groups are taken in an order rotated by the CTA index, so that the CTAs do not
+            // all ask for the same lines at the same moment
+            const int n_wg = n_g / 32;
+            int gidx[kLLGroups];
+#pragma unroll
+            for (int t = 0; t < kLLGroups; ++t) {
+                const int wg = warp + t * kDecWarps;
+                gidx[t] = ((wg + cta) % n_wg) * 32 + lane;
+            }
             for (uint32_t it = 0; pending; ++it) {
 #pragma unroll
                 for (int t = 0; t < kLLGroups; ++t)
                     if (pending >> t & 1u) {
-                        const unsigned long long* src = p.act_ll + 4 * (size_t)(tid + t * kDecThreads);
+                        const unsigned long long* src = p.act_ll + 4 * (size_t)gidx[t];
                         ld_ll2(src, q[t][0], q[t][1]);
                         ld_ll2(src + 2, q[t][2], q[t][3]);
                     }
@@ -1116,10 +1235,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 }
             }
             __syncwarp();
+            DBGW(7);
 #pragma unroll
             for (int t = 0; t < kLLGroups; ++t) {
-                const int i = tid + t * kDecThreads;
-                if (i < n_g) {  // uniform per warp: n_g and the stride are multiples of 32
+                const int i = gidx[t];
+                if (tid + t * kDecThreads < n_g) {  // uniform per warp: n_g and the stride are multiples of 32
                     float4 v;
                     v.x = __uint_as_float((unsigned int)q[t][0]);
                     v.y = __uint_as_float((unsigned int)q[t][1]);
@@ -1139,7 +1259,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             if (sg_reader) sm->topw[K] = 1.0f / (1.0f + expf(-__uint_as_float((unsigned int)qs)));
             DBG(1);
             PROF3(6);
-            cp_wait<1>();  // this warp's down rows landed
+            if (kBulkC) ok &= mbar_wait(&sm->bar_c, wpar) ? 1 : 0;  // down rows and the next router's slice landed
+            else cp_wait<1>();                                       // this warp's down rows landed
+            wpar ^= 1u;
             if (!__syncthreads_and(ok)) {
                 if (tid == 0) atomicExch(p.err, 4u);
                 alive = false;
@@ -1186,7 +1308,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             if (has_next) {
                 cp_wait<0>();  // the next router's slice landed
                 __syncthreads();
-                push_partial_logits(sm, p.layers[l + 1].router_bf16 != nullptr, acc_nxt, nc, E, inv_rms, tid);
+                push_partial_logits(sm, sm->tab[rel + 1].router_bf16 != nullptr, acc_nxt, nc, E, inv_rms, tid);
                 pscale = inv_rms;
                 PROF3(9);
                 DBG(2);
@@ -1262,6 +1384,9 @@ int decode_init(moe_engine* e) {
     MOE_CUDA(cudaMallocHost(&e->stage_host, (size_t)2 * d.hidden * sizeof(float)));
     MOE_CUDA(cudaMalloc(&e->dec_act_ll, kActLLWords * sizeof(unsigned long long)));
     MOE_CUDA(cudaMemset(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long)));
+    MOE_CUDA(cudaMalloc(&e->dec_hint, 128));
+    MOE_CUDA(cudaMemset(e->dec_hint, 0, 128));
+    e->dec_hint_base = 0;
     MOE_CUDA(cudaMalloc(&e->dec_acc, 2 * kAccStride * sizeof(long long)));
     MOE_CUDA(cudaMemset(e->dec_acc, 0, 2 * kAccStride * sizeof(long long)));
     e->dec_epoch = 0;
@@ -1307,7 +1432,7 @@ void decode_destroy(moe_engine* e) {
     if (e->dec_prof) cudaFree(e->dec_prof);
     cudaFree(e->dec_h[0]); cudaFree(e->dec_h[1]); cudaFree(e->dec_logits); cudaFree(e->dec_act);
     cudaFree(e->dec_misc); cudaFree(e->dec_idx); cudaFree(e->dec_w); cudaFree(e->dec_sync);
-    cudaFree(e->dec_act_ll); cudaFree(e->dec_acc);
+    cudaFree(e->dec_act_ll); cudaFree(e->dec_acc); cudaFree(e->dec_hint);
     if (e->stage_host) cudaFreeHost(e->stage_host);
 }
 
@@ -1316,6 +1441,8 @@ void decode_destroy(moe_engine* e) {
 int decode_reset_after_error(moe_engine* e) {
     MOE_CUDA(cudaMemsetAsync(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long), e->stream));
     MOE_CUDA(cudaMemsetAsync(e->dec_acc, 0, 2 * kAccStride * sizeof(long long), e->stream));
+    MOE_CUDA(cudaMemsetAsync(e->dec_hint, 0, 128, e->stream));
+    e->dec_hint_base = 0;
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     e->dec_epoch = 0;
     return MOE_OK;
@@ -1338,8 +1465,25 @@ static int ensure_router_t(moe_engine* e, int layer) {
     return MOE_OK;
 }
 
+static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
+                               const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);
+
+// Layers [l0, l1) for one token.  Long stacks run as several launches of at most kMaxDecLayers
+// layers; a later launch reads its input from h_out (a CTA writes its part of the output
+// only after every CTA has staged the input, so the two may be the same buffer).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
                   const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
+    MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
+    for (int a = l0; a < l1; a += kMaxDecLayers) {
+        const int b = a + kMaxDecLayers < l1 ? a + kMaxDecLayers : l1;
+        int rc = launch_decode_chunk(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w);
+        if (rc != MOE_OK) return rc;
+    }
+    return MOE_OK;
+}
+
+static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
+                               const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
     const moe_dims_t& d = e->dims;
     MOE_REQUIRE(d.hidden == kH && d.inter == kI && d.shared_inter == kI,
                 "decode path is built for hidden=%d, inter=shared_inter=%d (got %d/%d/%d)", kH, kI,
@@ -1351,6 +1495,7 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     MOE_REQUIRE(cdiv((d.top_k + 1) * kI, G) <= kMaxB3Items && cdiv(kH, G) <= kMaxCRows,
                 "decode kernel needs at least 147 SMs for these dimensions (device has %d)", G);
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
+    MOE_REQUIRE(l1 - l0 <= kMaxDecLayers, "decode: at most %d layers per launch", kMaxDecLayers);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
     for (int l = l0; l < l1; ++l) {
         int rc = check_layer_ready(e, l);
@@ -1372,6 +1517,9 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     p.acc = e->dec_acc; p.act_ll = e->dec_act_ll;
     p.epoch_base = e->dec_epoch;
     e->dec_epoch += (unsigned int)(l1 - l0);
+    p.hint = e->dec_hint;
+    p.hint_base = e->dec_hint_base;
+    e->dec_hint_base += (unsigned long long)G * (unsigned long long)(l1 - l0);
     p.logit_bias = logit_bias; p.forced_idx = forced_idx;
     p.out_idx = out_idx; p.out_w = out_w;
     p.sync = e->dec_sync;
