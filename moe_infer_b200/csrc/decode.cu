@@ -639,6 +639,19 @@ constexpr int kMaxDecLayers = 64;  // layer table rows staged in shared memory p
 constexpr int kAccStride = kMaxE + 8;
 constexpr int kLLGroups = ((kMaxK + 1) * (kI / 4) + kDecThreads - 1) / kDecThreads;  // 4-value groups per thread
 
+#ifdef MOE_DEC_SKEW
+// build-time diagnostic: wall-clock stamps of every CTA at a few points of one layer
+__device__ long long g_dbg[8 * 1024];
+__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define DBG(k) do { if (p.prof && l == p.l0 + 4 && tid == 0) g_dbg[(k) * 1024 + cta] = gtime(); } while (0)
+#define RT(k) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_dbg[7 * 1024 + 512 + (k)] = clock64(); } while (0)
+#define DBGW(k) do { if (p.prof && l == p.l0 + 4 && lane == 0) atomicMax((unsigned long long*)&g_dbg[(k) * 1024 + cta], (unsigned long long)gtime()); } while (0)
+#else
+#define DBG(k) do { } while (0)
+#define DBGW(k) do { } while (0)
+#define RT(k) do { } while (0)
+#endif
+
 struct Decode3Params {
     const LayerDev* layers;
     int l0, l1;
@@ -689,9 +702,14 @@ struct __align__(128) DecodeSmem3 {
     float topw[kMaxK + 1];
     float topp[kMaxK];
     int topi[kMaxK];
+    uint4 xq[6 * kChH];                   // x as three signed-byte digit planes, [plane * 2 + odd][chunk] (see stage_digits)
+    float xdl[kChH];                      // value of one unit of a chunk's digits
+    uint4 aq[(kMaxK + 1) * 6 * kChI];     // SwiGLU outputs as digit planes, per matrix [plane * 2 + odd][chunk]
+    float adl[(kMaxK + 1) * kChI];
     float hn[kMaxCRows + 2];              // this CTA's finished elements of the next h, times the next norm weight
     float hraw[kMaxCRows + 2];            // the same elements as they are
     float hmax[32];                       // routing: maxima of 16-expert groups
+    float tau;                            // routing: candidate threshold
     int flag;
     uint64_t bar_h;
     uint64_t bar_b;   // gate/up slices landed
@@ -873,6 +891,101 @@ __device__ __forceinline__ void ld_ll2(const unsigned long long* ptr, unsigned l
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
 }
 
+// ─── integer dot products ───────────────────────────────────────────────────
+// The 4-bit weights are small integers, so the dot product of a row with a vector is done in
+// integer arithmetic: every 32-element chunk of the vector is written as X * delta with
+// integers |X| <= 2^22 (delta = chunk maximum / 2^22), X is split into three signed base-256
+// digits, and dp4a (four byte products summed into 32 bits) multiplies them with the nibbles,
+// four at a time.  Sums are exact; the only rounding is that of x to 23 bits relative to its
+// chunk's maximum, the same order as the f32 mantissa the reference multiplies with.
+// Byte order: the nibbles of a weight word are split as (w & 0x0F0F0F0F) = columns 0,2,4,6 and
+// ((w >> 4) & 0x0F0F0F0F) = columns 1,3,5,7, so digit words are stored "even" and "odd".
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// One thread's float4 (elements 4 j .. 4 j + 3 of chunk c; the 8 threads of a chunk are
+// consecutive lanes): writes its digits into planes[(p * 2 + odd) * n_chunks + c] and, from
+// lane j == 0, the chunk's delta.
+__device__ __forceinline__ void stage_digits(uint4* planes, float* deltas, int n_chunks, int c, int j, const float4& o) {
+    float mx = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    const float inv = mx > 0.0f ? 4194304.0f / mx : 0.0f;
+    if (j == 0) deltas[c] = mx * (1.0f / 4194304.0f);
+    const int X[4] = {__float2int_rn(o.x * inv), __float2int_rn(o.y * inv), __float2int_rn(o.z * inv), __float2int_rn(o.w * inv)};
+    uint32_t d[3][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int d0 = (X[i] << 24) >> 24;
+        const int X1 = (X[i] - d0) >> 8;
+        const int d1 = (X1 << 24) >> 24;
+        const int d2 = (X1 - d1) >> 8;
+        d[0][i] = (uint32_t)d0 & 0xFFu;
+        d[1][i] = (uint32_t)d1 & 0xFFu;
+        d[2][i] = (uint32_t)d2 & 0xFFu;
+    }
+    // this thread holds columns (4 half .. 4 half + 3) of word k: two even and two odd bytes
+    const int k = j >> 1, half = j & 1;
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+        const uint16_t ev = (uint16_t)(d[p][0] | (d[p][2] << 8));
+        const uint16_t od = (uint16_t)(d[p][1] | (d[p][3] << 8));
+        uint16_t* e16 = reinterpret_cast<uint16_t*>(planes + (size_t)(p * 2 + 0) * n_chunks + c);
+        uint16_t* o16 = reinterpret_cast<uint16_t*>(planes + (size_t)(p * 2 + 1) * n_chunks + c);
+        e16[k * 2 + half] = ev;
+        o16[k * 2 + half] = od;
+    }
+}
+
+// sum over the 32 nibbles of q of nibble * X, as a float (X = the chunk's integers)
+__device__ __forceinline__ float dot32_int(const uint4& q, const uint4 (&xe)[3], const uint4 (&xo)[3]) {
+    int a[3] = {0, 0, 0};
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = w[k] & 0x0F0F0F0Fu, hi = (w[k] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            const uint32_t e = k == 0 ? xe[p].x : k == 1 ? xe[p].y : k == 2 ? xe[p].z : xe[p].w;
+            const uint32_t o = k == 0 ? xo[p].x : k == 1 ? xo[p].y : k == 2 ? xo[p].z : xo[p].w;
+            a[p] = dp4a_us(lo, e, a[p]);
+            a[p] = dp4a_us(hi, o, a[p]);
+        }
+    }
+    return fmaf((float)a[2], 65536.0f, fmaf((float)a[1], 256.0f, (float)a[0]));
+}
+
+// Dot products of NR 4-bit rows of length kH with the staged x (integer path).
+template <int NR>
+__device__ __forceinline__ void rows_dot_q(const DecodeSmem3* sm, const uint4* const (&w)[NR],
+                                           const uint16_t* const (&s)[NR], const uint16_t* const (&b)[NR],
+                                           float (&out)[NR], int lane) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) out[r] = 0.0f;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int c = lane + 32 * it;
+        uint4 xe[3], xo[3];
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            xe[p] = sm->xq[(p * 2 + 0) * kChH + c];
+            xo[p] = sm->xq[(p * 2 + 1) * kChH + c];
+        }
+        const float sx = sm->sumx[c], dl = sm->xdl[c];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const float sc = bf16_bits_to_f32(s[r][c >> 1]), bi = bf16_bits_to_f32(b[r][c >> 1]);
+            out[r] += fmaf(sc * dl, dot32_int(w[r][c], xe, xo), bi * sx);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) out[r] = warp_sum(out[r]);
+}
+
 // stage_norm in two halves, so that other work can run while h is in flight
 __device__ __forceinline__ void stage_issue(DecodeSmem3* sm, const float* h) {
     if (threadIdx.x == 0) {
@@ -899,7 +1012,7 @@ __device__ __forceinline__ bool stage_finish(DecodeSmem3* sm, const uint16_t* no
     o.z = v.z * inv_rms * __uint_as_float(wb.y << 16);
     o.w = v.w * inv_rms * __uint_as_float(wb.y & 0xFFFF0000u);
     const int c = tid >> 3, j = tid & 7;
-    sm->xs[j * kChH + c] = o;
+    stage_digits(sm->xq, sm->xdl, kChH, c, j, o);
     float s = (o.x + o.y) + (o.z + o.w);
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -909,9 +1022,10 @@ __device__ __forceinline__ bool stage_finish(DecodeSmem3* sm, const uint16_t* no
     return true;
 }
 
-// route_cta with fewer CTA-wide barriers: the threshold comes from the maxima of 16-expert
-// groups (32 of them, one per lane, ranked with shuffles), candidates are collected with one
-// shared-memory atomic per warp, and probabilities are only formed for the candidates.
+// route_cta rearranged for latency.  Ranks are found with warp votes instead of per-thread
+// loops: the rank of a value among 32 is the population count of one ballot.  The candidate
+// threshold comes from the maxima of 16-expert groups (32 of them, one per lane): warp w ranks
+// group maxima 2w and 2w+1, and whichever has K-1 maxima ahead of it is the threshold.
 // Same arithmetic as route_cta for the values it returns: p = exp(v - max) * (1 / sum), ties to
 // the lower index, weights p_k * (1 / sum_k p_k).
 __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32_t* forced, int E, int K) {
@@ -924,7 +1038,7 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
     if ((lane & 15) == 0) sm->hmax[tid >> 4] = m;
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
     if (lane == 0) sm->red[warp] = m;
-    if (tid == 0) sm->ncand = 0;
+    if (tid == 0) { sm->ncand = 0; sm->tau = -1.0f; }
     __syncthreads();
     float mx = sm->red[0];
 #pragma unroll
@@ -935,27 +1049,16 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
     if (forced) {
         sm->prob[tid] = ex;
     } else {
-        // tau = K-th largest group maximum (as exp(v - max), bit-identical to its owner's value),
-        // lowered by a hair so that values which round to the same probability stay candidates
+        // group maxima as exp(v - max): bit-identical to the owning thread's value; -1 for empty groups
         const float mine = (lane * 16 < E) ? expf(sm->hmax[lane] - mx) : -1.0f;
-        int cnt = 0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float o = __shfl_sync(0xffffffffu, mine, j);
-            cnt += (o > mine) || (o == mine && j < lane);
-        }
-        const unsigned hit = __ballot_sync(0xffffffffu, cnt == K - 1);
-        float tau = __shfl_sync(0xffffffffu, mine, __ffs(hit) - 1);
-        tau = tau < 0.0f ? -1.0f : tau * 0.999999f;
-        const bool is_c = tid < E && ex >= tau;
-        const unsigned bal = __ballot_sync(0xffffffffu, is_c);
-        int base = 0;
-        if (lane == 0 && bal) base = atomicAdd(&sm->ncand, __popc(bal));
-        base = __shfl_sync(0xffffffffu, base, 0);
-        if (is_c) {
-            const int slot = base + __popc(bal & ((1u << lane) - 1u));
-            sm->cand_p[slot] = ex;
-            sm->cand_i[slot] = tid;
+        for (int t = 0; t < 2; ++t) {
+            const int iu = 2 * warp + t;
+            const float u = __shfl_sync(0xffffffffu, mine, iu);
+            const int ahead = __popc(__ballot_sync(0xffffffffu, (mine > u) || (mine == u && lane < iu)));
+            // exactly one group has K-1 ahead of it; lowered by a hair so that values which
+            // round to the same probability stay candidates (an empty group: everything is one)
+            if (ahead == K - 1 && lane == 0) sm->tau = u < 0.0f ? -1.0f : u * 0.999999f;
         }
     }
     __syncthreads();
@@ -966,16 +1069,35 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
     if (forced) {
         if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]] * inv; }
     } else {
+        const bool is_c = tid < E && ex >= sm->tau;
+        const unsigned bal = __ballot_sync(0xffffffffu, is_c);
+        int base = 0;
+        if (lane == 0 && bal) base = atomicAdd(&sm->ncand, __popc(bal));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (is_c) {
+            const int slot = base + __popc(bal & ((1u << lane) - 1u));
+            sm->cand_p[slot] = ex * inv;
+            sm->cand_i[slot] = tid;
+        }
+    }
+    __syncthreads();
+    if (!forced) {
+        // warp w ranks candidates w, w + 16, ...: every lane compares one other candidate per vote
         const int nc = sm->ncand;
-        if (tid < nc) {
-            const float cp = sm->cand_p[tid] * inv;
-            const int ci = sm->cand_i[tid];
+        for (int c = warp; c < nc; c += kDecWarps) {
+            const float cp = sm->cand_p[c];
+            const int ci = sm->cand_i[c];
             int rank = 0;
-            for (int j = 0; j < nc; ++j) {
-                const float q = sm->cand_p[j] * inv;
-                rank += (q > cp) || (q == cp && sm->cand_i[j] < ci);
+            for (int j0 = 0; j0 < nc; j0 += 32) {
+                const int j = j0 + lane;
+                bool beats = false;
+                if (j < nc) {
+                    const float q = sm->cand_p[j];
+                    beats = (q > cp) || (q == cp && sm->cand_i[j] < ci);
+                }
+                rank += __popc(__ballot_sync(0xffffffffu, beats));
             }
-            if (rank < K) { sm->topi[rank] = ci; sm->topp[rank] = cp; }
+            if (rank < K && lane == 0) { sm->topi[rank] = ci; sm->topp[rank] = cp; }
         }
     }
     __syncthreads();
@@ -989,16 +1111,6 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
     __syncthreads();
 }
 
-#ifdef MOE_DEC_SKEW
-// build-time diagnostic: wall-clock stamps of every CTA at a few points of one layer
-__device__ long long g_dbg[8 * 1024];
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define DBG(k) do { if (p.prof && l == p.l0 + 4 && tid == 0) g_dbg[(k) * 1024 + cta] = gtime(); } while (0)
-#define DBGW(k) do { if (p.prof && l == p.l0 + 4 && lane == 0) atomicMax((unsigned long long*)&g_dbg[(k) * 1024 + cta], (unsigned long long)gtime()); } while (0)
-#else
-#define DBG(k) do { } while (0)
-#define DBGW(k) do { } while (0)
-#endif
 #define PROF3(idx)                                                                                 \
     do {                                                                                           \
         if (p.prof && cta == 0 && tid == 0) p.prof[(l - p.l0) * kProfPoints + (idx)] = clock64();  \
@@ -1142,7 +1254,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 const uint16_t* const s[4] = {sm->b_s[0][j], sm->b_s[1][j], sg_now ? sm->sg_s : sm->b_s[0][jb], sm->b_s[1][jb]};
                 const uint16_t* const b[4] = {sm->b_b[0][j], sm->b_b[1][j], sg_now ? sm->sg_b : sm->b_b[0][jb], sm->b_b[1][jb]};
                 float o[4];
-                rows_dot_h<4>(sm, w, s, b, o, lane);
+                rows_dot_q<4>(sm, w, s, b, o, lane);
                 if (lane == 0) {
                     st_ll(p.act_ll + i0 + j, epoch, swiglu(o[0], o[1]));
                     if (two) st_ll(p.act_ll + i0 + j2, epoch, swiglu(o[2], o[3]));
@@ -1155,7 +1267,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 const uint16_t* const s[1] = {sm->sg_s};
                 const uint16_t* const b[1] = {sm->sg_b};
                 float o[1];
-                rows_dot_h<1>(sm, w, s, b, o, lane);
+                rows_dot_q<1>(sm, w, s, b, o, lane);
                 if (lane == 0) st_ll(p.act_ll + n_items, epoch, o[0]);
             }
         }
@@ -1247,7 +1359,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                     v.w = __uint_as_float((unsigned int)q[t][3]);
                     const int m = i / (kI / 4), f = i - m * (kI / 4);
                     const int c = f >> 3, j = f & 7;
-                    sm->acts[(m * 8 + j) * kChI + c] = v;
+                    stage_digits(sm->aq + m * 6 * kChI, sm->adl + m * kChI, kChI, c, j, v);
                     float sv = (v.x + v.y) + (v.z + v.w);
                     sv += __shfl_xor_sync(0xffffffffu, sv, 1);
                     sv += __shfl_xor_sync(0xffffffffu, sv, 2);
@@ -1286,13 +1398,16 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 for (int jm = 0; jm < kMats; ++jm) {
                     const int m = sub + 2 * jm;
                     if (m <= K) {
-                        float4 xv[8];
+                        uint4 xe[3], xo[3];
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) xv[q] = sm->acts[(m * 8 + q) * kChI + c];
-                        acc = fmaf(sm->topw[m],
-                                   chunk_term(sm->c_w[m][j][c], xv, sm->suma[m * kChI + c], sm->c_s[m][j][c >> 1],
-                                              sm->c_b[m][j][c >> 1]),
-                                   acc);
+                        for (int q = 0; q < 3; ++q) {
+                            xe[q] = sm->aq[(m * 6 + q * 2 + 0) * kChI + c];
+                            xo[q] = sm->aq[(m * 6 + q * 2 + 1) * kChI + c];
+                        }
+                        const float sc = bf16_bits_to_f32(sm->c_s[m][j][c >> 1]), bi = bf16_bits_to_f32(sm->c_b[m][j][c >> 1]);
+                        const float term = fmaf(sc * sm->adl[m * kChI + c], dot32_int(sm->c_w[m][j][c], xe, xo),
+                                                bi * sm->suma[m * kChI + c]);
+                        acc = fmaf(sm->topw[m], term, acc);
                     }
                 }
                 acc = warp_sum(acc);
