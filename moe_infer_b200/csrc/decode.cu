@@ -636,7 +636,8 @@ constexpr size_t kActLLWords = (size_t)(kMaxK + 1) * kI + 8;
 constexpr int kMaxB3Items = 32;   // ceil((K + 1) * I / grid) gate/up row pairs incl. the shared expert
 constexpr float kFix = 4294967296.0f;  // 2^32
 constexpr int kMaxDecLayers = 64;  // layer table rows staged in shared memory per launch
-constexpr int kAccStride = kMaxE + 8;
+constexpr int kAccPitch = 1;  // distance between accumulators in words (spreading them over sectors measured no faster)
+constexpr int kAccStride = (kMaxE + 8) * kAccPitch;
 constexpr int kLLGroups = ((kMaxK + 1) * (kI / 4) + kDecThreads - 1) / kDecThreads;  // 4-value groups per thread
 
 #ifdef MOE_DEC_SKEW
@@ -794,10 +795,10 @@ __device__ __forceinline__ int router_t_stride(int E) { return (E + 7) & ~7; }  
 // (gate/up weights, scales, biases) is at most two contiguous byte ranges (one per slot
 // touched): twelve bulk copies, issued by twelve different threads, each announcing its own
 // bytes on the mbarrier (which counts kBCopies arrivals per phase).
-constexpr bool kBulk = false;   // gate/up slices by bulk copy
-constexpr bool kBulkC = false;  // down slices by bulk copy as well (measured slower: many small copies)
+constexpr bool kBulk = true;    // gate/up slices by bulk copy
+constexpr bool kBulkC = false;  // down weight slices and the router slice by bulk copy as well
 constexpr int kBCopies = 12;
-constexpr int kCCopies = 3 * (kMaxK + 1) + 1;
+constexpr int kCCopies = (kMaxK + 1) + 1;
 
 __device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
                                             int i0, int nb, int K, int q) {
@@ -821,8 +822,9 @@ __device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly,
     }
 }
 
-// Down rows [r0, r0 + nc) of matrix m (weights, scales, biases: q = 3 m + kind) and, as copy
-// number kCCopies - 1, the next layer's slice of the transposed router.
+// Down rows [r0, r0 + nc) of matrix q (weights only: the scale and bias rows are 16 bytes each
+// and go through per-thread copies, bulk copies that small cost more than they move) and, as
+// copy number kCCopies - 1, the next layer's slice of the transposed router.
 __device__ __forceinline__ void bulk_C_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
                                             const void* next_router_t, bool next_bf16, int r0, int nc, int E, int K, int q) {
     const void* src = nullptr;
@@ -836,16 +838,28 @@ __device__ __forceinline__ void bulk_C_copy(DecodeSmem3* sm, const LayerDev& ly,
             bytes = (uint32_t)(nc * row_bytes);
         }
     } else {
-        const int m = q / 3, kind = q - 3 * m;
+        const int m = q;
         if (m <= K) {
             const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-            if (kind == 0) { src = ex + L.down_w + (size_t)r0 * (kI / 2); dst = sm->c_w[m][0]; bytes = (uint32_t)nc * (kI / 2); }
-            else if (kind == 1) { src = ex + L.down_s + (size_t)r0 * (kI / kGroup) * 2; dst = sm->c_s[m][0]; bytes = (uint32_t)nc * (kI / kGroup) * 2; }
-            else { src = ex + L.down_b + (size_t)r0 * (kI / kGroup) * 2; dst = sm->c_b[m][0]; bytes = (uint32_t)nc * (kI / kGroup) * 2; }
+            src = ex + L.down_w + (size_t)r0 * (kI / 2);
+            dst = sm->c_w[m][0];
+            bytes = (uint32_t)nc * (kI / 2);
         }
     }
     mbar_expect_tx(&sm->bar_c, bytes);
     if (bytes) bulk_g2s(dst, src, bytes, &sm->bar_c);
+}
+
+// scale and bias rows of the down slices: one 16-byte piece per thread
+__device__ __forceinline__ void prefetch_C_scales(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
+                                                  int r0, int nc, int K, int tid) {
+    const int n = (K + 1) * nc * 2;
+    for (int q = tid; q < n; q += kDecThreads) {
+        const int a = q & 1, mj = q >> 1, m = mj / nc, j = mj - m * nc;
+        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
+        cp16(a ? sm->c_b[m][j] : sm->c_s[m][j], ex + (a ? L.down_b : L.down_s) + (size_t)(r0 + j) * (kI / kGroup) * 2);
+    }
+    cp_commit();
 }
 
 // rows [r0, r0 + nc) of a layer's transposed router (contiguous: nc * E elements), all threads
@@ -870,7 +884,7 @@ __device__ __forceinline__ void push_partial_logits(const DecodeSmem3* sm, bool 
             for (int j = 0; j < nc; ++j) part = fmaf(sm->wt[j * Ep + tid], sm->hn[j], part);
         }
         const long long fx = __float2ll_rn(part * scale * kFix);
-        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + tid, (unsigned long long)fx);
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + tid * kAccPitch, (unsigned long long)fx);
     }
     if (tid == kDecThreads - 1) {
         // this CTA's share of sum((h * scale)^2)
@@ -879,7 +893,7 @@ __device__ __forceinline__ void push_partial_logits(const DecodeSmem3* sm, bool 
             const float t = sm->hraw[j] * scale;
             q = fmaf(t, t, q);
         }
-        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + kMaxE, (unsigned long long)__float2ll_rn(q * kFix));
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + kMaxE * kAccPitch, (unsigned long long)__float2ll_rn(q * kFix));
     }
 }
 
@@ -1194,9 +1208,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         stage_issue(sm, h_cur);
         {
             float v = -INFINITY;
-            const long long aq = __ldcg(acc_cur + kMaxE);
+            const long long aq = __ldcg(acc_cur + kMaxE * kAccPitch);
             long long a = 0;
-            if (tid < E) a = __ldcg(acc_cur + tid);
+            if (tid < E) a = __ldcg(acc_cur + tid * kAccPitch);
             // mean of (h * pscale)^2 -> 1 / rms(h); the logits were accumulated times pscale
             const float r = 1.0f / pscale;
             const float msq = __ll2float_rn(aq) * (1.0f / kFix) * (1.0f / (float)kH);
@@ -1211,11 +1225,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         if (kBulk) {
             // one copy per thread: gate/up slices first, then everything the down phase needs
             if (lane == 0 && warp < kBCopies) bulk_B_copy(sm, ly, L, i0, nb, K, warp);
-            if (kBulkC && (lane == 1 || lane == 2) && 2 * warp + lane - 1 < kCCopies) {
-                const LayerDev& nx = sm->tab[has_next ? rel + 1 : rel];
-                bulk_C_copy(sm, ly, L, has_next ? nx.router_t : nullptr, nx.router_bf16 != nullptr, r0, nc, E, K,
-                            2 * warp + lane - 1);
-            }
             if (sg_here) prefetch_B3_warp(sm, ly, L, i0, 0, K, true, warp, lane);  // the gate-score row only
             else cp_commit();
         } else {
@@ -1242,6 +1251,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         cp_wait<0>();  // this warp's gate/up rows (and the gate-score row) landed
         if (kBulk) landed = mbar_wait(&sm->bar_b, wpar) ? 1 : 0;
         __syncwarp();
+        // the gate/up slices are in: now request what the down phase needs, to stream in during the arithmetic
+        if (kBulk && kBulkC) {
+            if (lane == 1 && warp < kCCopies) {
+                const LayerDev& nx = sm->tab[has_next ? rel + 1 : rel];
+                bulk_C_copy(sm, ly, L, has_next ? nx.router_t : nullptr, nx.router_bf16 != nullptr, r0, nc, E, K, warp);
+            }
+            prefetch_C_scales(sm, ly, L, r0, nc, K, tid);
+        }
         PROF3(4);
         {
             bool sg_done = !sg_here;
@@ -1382,8 +1399,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             // Every CTA routed (and so read these accumulators) before it produced the outputs
             // that this CTA has now seen in full: safe to clear them for the layer after next.
             if (cta == 0) {
-                if (tid < E) acc_cur[tid] = 0;
-                if (tid == kDecThreads - 1) acc_cur[kMaxE] = 0;
+                if (tid < E) acc_cur[tid * kAccPitch] = 0;
+                if (tid == kDecThreads - 1) acc_cur[kMaxE * kAccPitch] = 0;
             }
         }
         PROF3(7);
