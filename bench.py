@@ -24,6 +24,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+NCU_DRAM_BYTES_PER_LAYER = 17.32e6  # (68.00 MB read + 1.26 MB written) / 4 layers
 N_ROTATE = 64  # distinct input tokens cycled through, so routing differs from step to step
 
 
@@ -228,6 +229,12 @@ def run_decode(args, rank, world, local, dist):
     bytes_per_launch = benchlib.layer_token_bytes(dims) * dims.num_layers
     achieved = bytes_per_launch / (ms / K / 1e3) / 1e9
 
+    # DRAM bytes (read + write) per layer from the ncu capture of a 4-layer launch of this kernel; every layer's
+    # weights are read once, so a launch's traffic is that figure times the layer count.
+    default_shape = (dims.hidden, dims.inter, dims.num_experts, dims.top_k) == (2048, 512, 256, 8)
+    traffic = NCU_DRAM_BYTES_PER_LAYER * dims.num_layers if default_shape else None
+    traffic_src = "ncu dram__bytes_read+write of a 4-layer launch, per layer, x layers" if default_shape else None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         v, desc = cpu_decode_sample(dims, 2, 1, target_s=10.0, seed=args.seed)
@@ -247,10 +254,10 @@ def run_decode(args, rank, world, local, dist):
             "clocks": clk.summary(),
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": H * 4, "d2h_bytes_per_step": H * 4},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": "decode_stack_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": "decode_fused_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8TBs": achieved / 8000.0, "bytes_per_launch": bytes_per_launch,
-                         "traffic": None},
+                         "traffic": traffic, "traffic_source": traffic_src},
         }
         if cpu:
             line["cpu_baseline"] = cpu

@@ -73,7 +73,7 @@ def run_layer(args, rank, world, local, dist):
     peaks = benchlib.measured_peaks()
     b = benchlib.layer_token_bytes(dims)
     ach = b / (ms / args.steps / 1e3) / 1e9
-    roof = {"bound": "hbm", "kernel": "decode_stack_kernel (1 layer)", "achieved": ach, "peak": peaks["hbm_gbs"],
+    roof = {"bound": "hbm", "kernel": "decode_fused_kernel (1 layer)", "achieved": ach, "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"],
             "frac_of_nominal_8TBs": ach / 8000.0, "bytes_per_launch": b, "traffic": None}
     if rank == 0:

@@ -179,6 +179,7 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
 int decode_init(moe_engine* e);
 void decode_destroy(moe_engine* e);
 int decode_reset_after_error(moe_engine* e);
+int ensure_router_t(moe_engine* e, int layer);
 // Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
                   const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);

@@ -1580,10 +1580,11 @@ int decode_reset_after_error(moe_engine* e) {
     return MOE_OK;
 }
 
-// Builds the transposed router of a layer on first decode use (and after the router is reloaded).
-static int ensure_router_t(moe_engine* e, int layer) {
+// Builds the transposed router of a layer: when the router tensor is loaded, and again on first
+// decode use if it is missing.
+int ensure_router_t(moe_engine* e, int layer) {
     LayerHost& lh = e->layers[layer];
-    if (lh.router_t_valid) return MOE_OK;
+    if (lh.router_t_valid || e->dims.hidden != kH) return MOE_OK;  // other widths never reach the decode kernel
     const int E = e->dims.num_experts;
     const int Ep = (E + 7) & ~7;
     if (!lh.router_t) MOE_CUDA(cudaMalloc(&lh.router_t, (size_t)kH * Ep * sizeof(float)));

@@ -370,6 +370,8 @@ int moe_store_load_tensor(moe_engine_t* e, int layer, int role, const void* w, c
     if (rc != MOE_OK) return rc;
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     lh.role_loaded[role] = true;
+    // the decode kernel reads the router transposed: build that copy now, off the first token's path
+    if (role == MOE_T_ROUTER) return ensure_router_t(e, layer);
     return MOE_OK;
 }
 
