@@ -13,20 +13,23 @@
 // GPU->CPU wait each, this is one launch for the whole stack; top-k runs on
 // the device.
 //
+// Two kernels live here.  decode_stack_kernel is the three-phase form (serves the
+// allocation-free single-block entry point):
+//
 //   phase A  x = rmsnorm(h) (every CTA, redundantly); router logits, shared
 //            expert gate/up + SwiGLU, shared gate score            [~2.2 MB]
-//            -- does not depend on routing: its weights are requested one
-//               layer ahead
 //   phase B  softmax + top-k (every CTA, redundantly); gate/up/SwiGLU of the K
 //            chosen experts                                         [~9.4 MB]
 //   phase C  down projections of the K experts and the shared expert, combine
 //            with the residual: one warp owns one output element    [~5.3 MB]
-//            -- requested together with phase B's weights, right after top-k
+//
+// with a counting grid barrier after each phase.  decode_fused_kernel (further down,
+// used by the engine) folds phase A into the neighbouring phases and needs two
+// grid-wide exchanges per layer, one of them without a barrier.
 //
 // HBM-bound: 16,974,976 weight bytes per layer-token at the reference sizes.
-// Between phases the CTAs meet at a grid barrier built on one global counter;
-// every wait (barrier, mbarrier) is bounded and a timeout raises an error word
-// instead of hanging.
+// Every wait (grid barrier, mbarrier, tag poll) is bounded and a timeout raises an
+// error word instead of hanging.
 #include "q4dot.cuh"
 #include "stage.cuh"
 

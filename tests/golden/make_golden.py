@@ -75,7 +75,9 @@ def packer_cases():
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
+    ref = sys.argv[1]
     deq = _load(os.path.join(ref, "moe_infer", "dequantize.py"), "ref_dequantize")
     qhf = _load(os.path.join(ref, "moe_infer", "helpers", "quantize_from_hf.py"), "ref_quantize_from_hf")
     rng = np.random.Generator(np.random.PCG64(7))
