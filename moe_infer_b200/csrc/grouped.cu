@@ -40,7 +40,9 @@ constexpr int kNT = 256;   // tokens per tile (MMA N, padded to a multiple of 16
 constexpr int kProdWarps = 16;                  // operand producers / epilogue
 constexpr int kProdThreads = kProdWarps * 32;
 constexpr int kGemmThreads = kProdThreads + 32;  // + one MMA-issuing warp
-constexpr int kStages = 3;
+constexpr int kAStages = 2;   // dequantised weight tiles (produced locally: shallow ring)
+constexpr int kBStages = 4;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
+constexpr int kFullRing = 4;  // "operands in place" barriers (producers run at most kAStages steps ahead of the MMAs)
 constexpr int kMaxEPerLane = 16;
 
 // position of logical column j (0..7) inside a K-interleaved 8-block
@@ -478,6 +480,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+#ifdef MOE_GEMM_PROF
+__device__ long long g_gprof[2][256][8];
+#define GP_DECL long long gp_t = clock64(), gp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long gp_t0 = gp_t
+#define GP(k) do { const long long n_ = clock64(); gp_acc[k] += n_ - gp_t; gp_t = n_; } while (0)
+#define GP_FLUSH(role) do { if (lane == 0) { gp_acc[7] = clock64() - gp_t0; for (int i_ = 0; i_ < 8; ++i_) g_gprof[role][blockIdx.x][i_] = gp_acc[i_]; } } while (0)
+#else
+#define GP_DECL
+#define GP(k) do { } while (0)
+#define GP_FLUSH(role) do { } while (0)
+#endif
+
 // Warp roles: warps 0..15 produce the operand tiles (dequantised weights, copied
 // activations) and run the epilogue; warp 16 only issues the MMAs, because a
 // tcgen05.mma issue blocks its thread for about as long as the MMA runs.
@@ -491,16 +504,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     constexpr int kARows = 256;
     constexpr int kABytes = kARows * 128;
     constexpr int kBBytes = kNT * 128;
-    constexpr int kStage = kABytes + kBBytes;
+    constexpr int kLook = kBStages - 1;  // K steps between requesting an activation tile and using it
     constexpr uint32_t kTmemCols = 512;
+    static_assert(kKC > kLook, "the prologue requests the first kLook activation tiles");
     static_assert(kARows * 2 == kProdThreads, "one (row, half-group) dequant task per producer thread");
     constexpr int kWRing = 4;  // K steps of weight words in flight in registers
     static_assert(kKC % kWRing == 0, "the weight prefetch ring cycles through kWRing register sets");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t bar_full[kStages];   // producers -> MMA warp: operands of a stage are in place
-    __shared__ uint64_t bar_empty[kStages];  // MMA completion -> producers: stage may be overwritten
+    __shared__ uint64_t bar_full[kFullRing];    // producers -> MMA warp: operands of a K step are in place
+    __shared__ uint64_t bar_empty_a[kAStages];  // MMA completion -> producers: weight stage may be overwritten
+    __shared__ uint64_t bar_empty_b[kBStages];  // MMA completion -> producers: activation stage may be overwritten
     __shared__ uint64_t bar_acc;             // MMA completion -> epilogue: accumulators are final
     __shared__ uint64_t bar_tfree;           // epilogue -> MMA warp: accumulators have been read
     __shared__ uint32_t tmem_slot;
@@ -509,10 +524,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
-            mbar_init(&bar_full[i], kProdWarps);
-            mbar_init(&bar_empty[i], 1);
-        }
+        for (int i = 0; i < kFullRing; ++i) mbar_init(&bar_full[i], kProdWarps);
+        for (int i = 0; i < kAStages; ++i) mbar_init(&bar_empty_a[i], 1);
+        for (int i = 0; i < kBStages; ++i) mbar_init(&bar_empty_b[i], 1);
         mbar_init(&bar_acc, 1);
         mbar_init(&bar_tfree, kProdWarps);
         s_abort_mem = 0;
@@ -524,6 +538,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
     umma::fence_after_sync();
     const uint32_t tmem = tmem_slot;
     const uint32_t stages_addr = smem_u32(stages);
+    const uint32_t b_ring_addr = stages_addr + kAStages * kABytes;  // activation stages follow the weight stages
 
     const int n_items = *p.n_tiles * kRB;
     uint32_t it = 0;       // K steps so far (drives the stage ring and the mbarrier parities)
@@ -532,20 +547,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
 
     if (warp == kProdWarps) {
         // ─── MMA issuer ───────────────────────────────────────────────────────
+        GP_DECL;
         for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
             const int tile = item / kRB;
             const int nt = p.tile_list[3 * tile + 2];
             const uint32_t idesc = umma::make_idesc_bf16(128, (uint32_t)((nt + 15) & ~15));
             for (int kc = 0; kc < kKC && alive; ++kc, ++it) {
-                const uint32_t st = it % kStages, use = it / kStages;
-                bool ok = wait_or_abort(&bar_full[st], use & 1, s_abort);
+                const uint32_t sa = it % kAStages, sb = it % kBStages, sf = it % kFullRing;
+                bool ok = wait_or_abort(&bar_full[sf], (it / kFullRing) & 1, s_abort);
                 // the previous item's accumulators must have been read before they are overwritten
                 if (kc == 0 && n_done > 0) ok = wait_or_abort(&bar_tfree, (n_done - 1) & 1, s_abort) && ok;
                 alive = __all_sync(0xffffffffu, ok);
                 if (!alive) break;
+                GP(0);
                 if (lane == 0) {
                     umma::fence_after_sync();
-                    const uint32_t a_addr = stages_addr + st * kStage, b_addr = a_addr + kABytes;
+                    const uint32_t a_addr = stages_addr + sa * kABytes, b_addr = b_ring_addr + sb * kBBytes;
 #pragma unroll
                     for (int k16 = 0; k16 < 4; ++k16) {
                         const uint64_t db = umma::make_desc_sw128_kmajor(b_addr + k16 * 32);
@@ -553,15 +570,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                         umma::mma_bf16(tmem, umma::make_desc_sw128_kmajor(a_addr + k16 * 32), db, idesc, acc);
                         umma::mma_bf16(tmem + kNT, umma::make_desc_sw128_kmajor(a_addr + 128 * 128 + k16 * 32), db, idesc, acc);
                     }
-                    umma::commit(&bar_empty[st]);
+                    umma::commit(&bar_empty_a[sa]);
+                    umma::commit(&bar_empty_b[sb]);
                     if (kc == kKC - 1) umma::commit(&bar_acc);
                 }
                 __syncwarp();
+                GP(1);
             }
             ++n_done;
         }
+        GP_FLUSH(0);
     } else {
         // ─── producers + epilogue ─────────────────────────────────────────────
+        GP_DECL;
         for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
             const int tile = item / kRB, rb = item - tile * kRB;
             const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
@@ -600,11 +621,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                 const int j = q >> 3, c = q & 7;
                 const int jj = j < nt ? j : 0;
                 bsrc[i] = ((MODE == 1) ? p.x + (size_t)__ldg(p.slot_token + s0 + jj) * kBH : p.act + (size_t)(s0 + jj) * kBI) + c * 8;
-                boff[i] = kABytes + umma::sw128_offset((uint32_t)j, (uint32_t)c);
+                boff[i] = umma::sw128_offset((uint32_t)j, (uint32_t)c);
             }
-            // asynchronous copy of the activation tile of K step kc into stage st (rows >= nt zero-filled)
+            // asynchronous copy of the activation tile of K step kc into activation stage st (rows >= nt zero-filled)
             auto issue_b = [&](int kc, uint32_t st) {
-                const uint32_t base = stages_addr + st * kStage;
+                const uint32_t base = b_ring_addr + st * kBBytes;
 #pragma unroll
                 for (int i = 0; i < kBPieces; ++i) {
                     const int j = (tid + i * kProdThreads) >> 3;
@@ -621,25 +642,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             };
 
             bool ok = true;
-            {   // prologue: weights of the first kWRing K steps, activations of K step 0
+            GP(0);
+            {   // prologue: weights of the first kWRing K steps, activations of the first kLook K steps
 #pragma unroll
                 for (int i = 0; i < kWRing; ++i) load_a(i, wq[i], sq[i], bq[i]);
-                const uint32_t st0 = it % kStages, use0 = it / kStages;
-                if (use0 > 0) ok = wait_or_abort(&bar_empty[st0], (use0 - 1) & 1, s_abort);
-                issue_b(0, st0);
-                cp_commit_group();
+#pragma unroll
+                for (int j = 0; j < kLook; ++j) {
+                    const uint32_t g = it + j, sb = g % kBStages, use = g / kBStages;
+                    if (use > 0) ok = wait_or_abort(&bar_empty_b[sb], (use - 1) & 1, s_abort) && ok;
+                    issue_b(j, sb);
+                    cp_commit_group();
+                }
             }
             auto k_step = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
-                const uint32_t st = it % kStages;
-                // next K step's activations go into the next stage once the MMAs that read it are done
-                if (kc + 1 < kKC) {
-                    const uint32_t nst = (it + 1) % kStages, nuse = (it + 1) / kStages;
-                    if (nuse > 0) ok = wait_or_abort(&bar_empty[nst], (nuse - 1) & 1, s_abort) && ok;
-                    issue_b(kc + 1, nst);
+                const uint32_t sa = it % kAStages;
+                GP(1);
+                // dequantise this K step's 64 columns of this thread's row half, once the MMAs that read
+                // this weight stage kAStages K steps ago are done
+                {
+                    const uint32_t use = it / kAStages;
+                    if (use > 0) ok = wait_or_abort(&bar_empty_a[sa], (use - 1) & 1, s_abort) && ok;
                 }
-                cp_commit_group();
-                // dequantise this K step's 64 columns of this thread's row half
-                unsigned char* a_tile = stages + st * kStage;
+                GP(2);
+                unsigned char* a_tile = stages + sa * kABytes;
                 const uint32_t s32 = (uint32_t)sc | ((uint32_t)sc << 16);
                 const uint32_t b32 = (uint32_t)bi | ((uint32_t)bi << 16);
                 const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s32);
@@ -649,10 +674,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                 for (int wi = 0; wi < 4; ++wi)
                     *reinterpret_cast<uint4*>(a_tile + aoff[wi]) = dequant_word(words[wi], s2, b2);
                 if (kc + kWRing < kKC) load_a(kc + kWRing, w, sc, bi);  // refill this register set
-                cp_wait_group<1>();  // this K step's activation pieces have landed (the next ones may be in flight)
+                GP(3);
+                cp_wait_group<kLook - 1>();  // this K step's activation pieces have landed (later ones may be in flight)
+                GP(4);
                 umma::fence_smem_to_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_full[st]);
+                if (lane == 0) mbar_arrive(&bar_full[it % kFullRing]);
+                // The activations of K step kc + kLook go into the stage that K step kc - 1 used: its MMAs
+                // were issued a whole dequantisation ago, so this wait is short, and it sits after this
+                // step's hand-off so that it never delays the tensor pipe.
+                if (kc + kLook < kKC) {
+                    const uint32_t g = it + kLook, sb = g % kBStages, use = g / kBStages;
+                    if (use > 0) ok = wait_or_abort(&bar_empty_b[sb], (use - 1) & 1, s_abort) && ok;
+                    issue_b(kc + kLook, sb);
+                }
+                cp_commit_group();
+                GP(5);
                 ++it;
             };
             for (int kc = 0; kc < kKC; kc += kWRing) {
@@ -703,8 +740,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             umma::fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_tfree);  // this warp has read its part of the accumulators
+            GP(6);
         }
         cp_wait_group<0>();
+        if (warp == 0) GP_FLUSH(1);
     }
 
     if (!alive && lane == 0) atomicExch(p.err, 7u);
@@ -953,7 +992,7 @@ static size_t al256(size_t v) { return (v + 255) / 256 * 256; }
 
 template <int MODE>
 static constexpr size_t gemm_smem_bytes() {
-    return (size_t)kStages * (256 * 128 + kNT * 128) + 1024;
+    return (size_t)kAStages * (256 * 128) + (size_t)kBStages * (kNT * 128) + 1024;
 }
 
 // Builds the router's bf16 planes of a layer on first batched use (and after the router is reloaded).
@@ -1141,3 +1180,9 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
 }
 
 }  // namespace moe
+
+#ifdef MOE_GEMM_PROF
+extern "C" int moe_gemm_prof_read(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, moe::g_gprof, sizeof(long long) * 2 * 256 * 8);
+}
+#endif
