@@ -64,6 +64,7 @@ struct LayerHost {
     bool router_is_bf16 = true;
     uint8_t* planes = nullptr;   // router planes of the batched path, built on first use
     bool planes_valid = false;
+    alignas(64) unsigned char planes_map[128] = {};  // tensor map (TMA descriptor) over the planes
     uint8_t* router_t = nullptr; // transposed router of the decode path, built on first use
     bool router_t_valid = false;
     LayerDev dev{};
@@ -92,6 +93,7 @@ struct BatchWork {
     int32_t* tile_list = nullptr;  // (expert, first slot, slots) per token tile
     int32_t* n_tiles = nullptr;
     int32_t max_tiles = 0;
+    alignas(64) unsigned char x_map[128] = {};  // tensor map (TMA descriptor) over x, x_mid, x_lo as one [3 * cap, H] tensor
 };
 
 // Expert-parallel state: experts of every layer are split over `world` GPUs of one box;

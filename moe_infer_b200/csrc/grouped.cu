@@ -31,6 +31,11 @@
 // mbarriers); their completion frees the stage through tcgen05.commit on an mbarrier.  Weights (A) take the M = 128
 // side, tokens (B) the N side, so ragged per-expert token counts only change N.
 #include "umma.cuh"
+#include <cuda.h>
+#include <vector>
+#include <utility>
+#include <cstdlib>
+#include <cstdio>
 
 namespace moe {
 
@@ -135,11 +140,21 @@ __device__ __forceinline__ void cp_wait_group() { asm volatile("cp.async.wait_gr
 // copies tiles (16-byte asynchronous copies, three stages) and issues MMAs.
 // One CTA = 128 experts x 64 tokens.
 constexpr int kRtTok = 64;
-constexpr int kRtStages = 3;
+constexpr int kRtMaxStages = 5;
 constexpr int kRtATile = 128 * 128;   // 128 rows x 64 bf16
 constexpr int kRtBTile = kRtTok * 128;
-constexpr int kRtStage = 3 * kRtATile + 3 * kRtBTile;
-constexpr int kRtSmem = kRtStages * kRtStage + 1024;
+constexpr int kRtRing = 216 * 1024;   // bytes of operand stages: 3 for a bf16 router (256 rows per CTA), 3 for a 4-bit one (128 rows)
+constexpr int kRtMaxSplit = 8;        // the contraction may be split over up to this many CTAs; batch_route_kernel adds the partial sums
+// how many ways to split so that a small token count still fills the machine
+static int router_split(int n, int E, int nplanes) {
+    const int ctas = ((n + kRtTok - 1) / kRtTok) * (nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128);
+    int s = 1;
+    while (s < kRtMaxSplit && ctas * s < 100) s *= 2;
+    return s;
+}
+constexpr int kRtSmem = kRtRing + 1024;
+constexpr int kRtAccCols = 256;       // TMEM columns per accumulator (3 x 64 used)
+constexpr int kRtTmemCols = 512;
 
 __device__ __forceinline__ void split3(float v, uint16_t& hi, uint16_t& mid, uint16_t& lo) {
     const __nv_bfloat16 h = __float2bfloat16_rn(v);
@@ -186,105 +201,121 @@ __global__ void __launch_bounds__(256) router_planes_kernel(LayerDev ly, int E, 
     }
 }
 
-__global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16* __restrict__ x_hi,
-                                                             const __nv_bfloat16* __restrict__ x_mid,
-                                                             const __nv_bfloat16* __restrict__ x_lo, int n, int E,
-                                                             const uint16_t* __restrict__ planes, int nplanes,
-                                                             int rows_padded, float* __restrict__ logits,
-                                                             unsigned int* err) {
+// Operands arrive by tiled TMA loads (one instruction per 128 x 64 or 64 x 64 bf16 box, 128-byte
+// swizzle applied by the copy engine): a thread-issued cp.async costs its warp about 130 cycles
+// per instruction, which made this short, latency-bound kernel several times slower.
+// Warp 0 lane 0 requests tiles, warp 1 lane 0 issues the MMAs, all 8 warps run the epilogue.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* s_abort);
+
+// map_w: the layer's router planes as one [nplanes * rows_padded][H] bf16 tensor;
+// map_x: the activation planes hi/mid/lo as one [3 * x_rows][H] bf16 tensor.
+__global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                             const __grid_constant__ CUtensorMap map_x, int n, int E,
+                                                             int nplanes, int rows_padded, int x_rows,
+                                                             float* __restrict__ logits, unsigned int* err) {
+    // A CTA computes logits for 64 tokens x (256 experts when the router is bf16, 128 when it is three
+    // planes of a 4-bit one) over one kRtSplit-th of the contraction, into its own partial-sum slab.
+    const int nacc = (nplanes == 1) ? 2 : 1;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t bar_empty[kRtStages];
+    __shared__ uint64_t bar_full[kRtMaxStages];
+    __shared__ uint64_t bar_empty[kRtMaxStages];
     __shared__ uint64_t bar_acc;
     __shared__ uint32_t tmem_slot;
+    __shared__ int s_abort_mem;
+    volatile int* s_abort = &s_abort_mem;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t0 = blockIdx.x * kRtTok, e0 = blockIdx.y * 128;
+    const int t0 = blockIdx.x * kRtTok, e0 = blockIdx.y * 128 * nacc;
+    logits += (size_t)blockIdx.z * n * E;
+    // a stage holds nacc * nplanes weight tiles and the three activation tiles
+    const int na = nacc * nplanes;
+    const uint32_t stage_bytes = (uint32_t)na * kRtATile + 3u * kRtBTile;
+    const int S = min(kRtMaxStages, (int)(kRtRing / stage_bytes));
     if (tid == 0) {
-        for (int i = 0; i < kRtStages; ++i) mbar_init(&bar_empty[i], 1);
+        for (int i = 0; i < kRtMaxStages; ++i) { mbar_init(&bar_full[i], 1); mbar_init(&bar_empty[i], 1); }
         mbar_init(&bar_acc, 1);
+        s_abort_mem = 0;
         mbar_fence_init();
     }
-    if (warp == 0) umma::tmem_alloc(&tmem_slot, kRtTok);
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, kRtTmemCols);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = tmem_slot;
     const uint32_t stages_addr = smem_u32(stages);
-    const uint32_t idesc = umma::make_idesc_bf16(128, kRtTok);
-    constexpr int kSteps = kBH / 64;
-    const __nv_bfloat16* xs[3] = {x_hi, x_mid, x_lo};
+    const int kSteps = kBH / 64 / (int)gridDim.z;
+    const int kc0 = blockIdx.z * kSteps;  // first K step of this CTA's share
 
-    // copies of K step kc into stage st: nplanes x (128 rows x 8 chunks) weights, 3 x (32 tokens x 8 chunks) activations
-    auto issue = [&](int kc, int st) {
-        const uint32_t base = stages_addr + st * kRtStage;
-        for (int q = tid; q < nplanes * 1024; q += 256) {
-            const int p = q >> 10, r = (q >> 3) & 127, c = q & 7;
-            cp16_zfill(base + p * kRtATile + umma::sw128_offset((uint32_t)r, (uint32_t)c),
-                       planes + ((size_t)p * rows_padded + e0 + r) * kBH + kc * 64 + c * 8, 16u);
+    if (tid == 0) {
+        // ─── tile requests ────────────────────────────────────────────────────
+        for (int kc = 0; kc < kSteps; ++kc) {
+            const int st = kc % S, use = kc / S;
+            if (use > 0 && !wait_or_abort(&bar_empty[st], (uint32_t)(use - 1) & 1u, s_abort)) break;
+            const uint32_t base = stages_addr + (uint32_t)st * stage_bytes;
+            mbar_expect_tx(&bar_full[st], stage_bytes);
+            // weight tile i = a * nplanes + p: plane p of expert rows e0 + 128 a ..
+            for (int i = 0; i < na; ++i) {
+                const int a = i / nplanes, p = i - a * nplanes;
+                tma_load_2d(base + i * kRtATile, &map_w, (kc0 + kc) * 64, p * rows_padded + e0 + 128 * a, &bar_full[st]);
+            }
+            for (int p = 0; p < 3; ++p)
+                tma_load_2d(base + na * kRtATile + p * kRtBTile, &map_x, (kc0 + kc) * 64, p * x_rows + t0, &bar_full[st]);
         }
-        for (int q = tid; q < 3 * kRtTok * 8; q += 256) {
-            const int p = q / (kRtTok * 8), rem = q - p * (kRtTok * 8), j = rem >> 3, c = rem & 7;
-            const int t = t0 + j;
-            cp16_zfill(base + 3 * kRtATile + p * kRtBTile + umma::sw128_offset((uint32_t)j, (uint32_t)c),
-                       xs[p] + (size_t)(t < n ? t : 0) * kBH + kc * 64 + c * 8, t < n ? 16u : 0u);
-        }
-    };
-    bool alive = true;
-    issue(0, 0); cp_commit_group();
-    issue(1, 1); cp_commit_group();
-    for (int kc = 0; kc < kSteps; ++kc) {
-        const int st = kc % kRtStages;
-        bool ok = true;
-        if (kc + 2 < kSteps) {
-            const int nst = (kc + 2) % kRtStages, nuse = (kc + 2) / kRtStages;
-            if (nuse > 0) ok = mbar_wait(&bar_empty[nst], (nuse - 1) & 1);
-            issue(kc + 2, nst);
-        }
-        cp_commit_group();
-        cp_wait_group<2>();  // this K step's tiles have landed
-        umma::fence_smem_to_async();
-        if (!__syncthreads_and(ok ? 1 : 0)) { alive = false; break; }
-        if (tid == 0) {
+    } else if (tid == 32) {
+        // ─── MMA issue ────────────────────────────────────────────────────────
+        // The three activation tiles (hi, mid, lo; 64 token rows each) are stacked in shared memory, so one MMA
+        // with N = 192 multiplies a weight tile with all three (N = 128, 64 for the smaller weight terms); the
+        // three column groups of the accumulator are added in the epilogue.
+        const uint32_t idesc3 = umma::make_idesc_bf16(128, 3 * kRtTok), idesc2 = umma::make_idesc_bf16(128, 2 * kRtTok),
+                       idesc1 = umma::make_idesc_bf16(128, kRtTok);
+        for (int kc = 0; kc < kSteps; ++kc) {
+            const int st = kc % S, use = kc / S;
+            if (!wait_or_abort(&bar_full[st], (uint32_t)use & 1u, s_abort)) break;
             umma::fence_after_sync();
-            const uint32_t a0 = stages_addr + st * kRtStage, b0 = a0 + 3 * kRtATile;
+            const uint32_t a0 = stages_addr + (uint32_t)st * stage_bytes, b0 = a0 + na * kRtATile;
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16) {
                 const uint32_t o = k16 * 32;
-                const uint64_t ah = umma::make_desc_sw128_kmajor(a0 + o);
-                const uint64_t bh = umma::make_desc_sw128_kmajor(b0 + o);
-                const uint64_t bm = umma::make_desc_sw128_kmajor(b0 + kRtBTile + o);
-                const uint64_t bl = umma::make_desc_sw128_kmajor(b0 + 2 * kRtBTile + o);
-                umma::mma_bf16(tmem, ah, bh, idesc, (kc > 0 || k16 > 0) ? 1u : 0u);
-                umma::mma_bf16(tmem, ah, bm, idesc, 1u);
-                umma::mma_bf16(tmem, ah, bl, idesc, 1u);
-                if (nplanes == 3) {
-                    const uint64_t am = umma::make_desc_sw128_kmajor(a0 + kRtATile + o);
-                    const uint64_t al = umma::make_desc_sw128_kmajor(a0 + 2 * kRtATile + o);
-                    umma::mma_bf16(tmem, am, bh, idesc, 1u);
-                    umma::mma_bf16(tmem, al, bh, idesc, 1u);
-                    umma::mma_bf16(tmem, am, bm, idesc, 1u);
+                const uint64_t bx = umma::make_desc_sw128_kmajor(b0 + o);
+                const uint32_t first = (kc > 0 || k16 > 0) ? 1u : 0u;
+                for (int a = 0; a < nacc; ++a) {
+                    const uint32_t d = tmem + a * kRtAccCols, aa = a0 + a * nplanes * kRtATile + o;
+                    umma::mma_bf16(d, umma::make_desc_sw128_kmajor(aa), bx, idesc3, first);  // W_hi . {x_hi, x_mid, x_lo}
+                    if (nplanes == 3) {
+                        umma::mma_bf16(d, umma::make_desc_sw128_kmajor(aa + kRtATile), bx, idesc2, 1u);      // W_mid . {x_hi, x_mid}
+                        umma::mma_bf16(d, umma::make_desc_sw128_kmajor(aa + 2 * kRtATile), bx, idesc1, 1u);  // W_lo . x_hi
+                    }
                 }
             }
             umma::commit(&bar_empty[st]);
             if (kc == kSteps - 1) umma::commit(&bar_acc);
         }
     }
-    cp_wait_group<0>();
-    if (alive) {
-        const bool acc_ok = mbar_wait(&bar_acc, 0);
-        alive = __syncthreads_and(acc_ok ? 1 : 0) != 0;
-    }
+    __syncwarp();
+    const bool acc_ok = wait_or_abort(&bar_acc, 0, s_abort);
+    const bool alive = __syncthreads_and(acc_ok ? 1 : 0) != 0;
     if (alive) {
         umma::fence_after_sync();
         {
             const int quad = warp & 3, cb = warp >> 2;  // 8 warps: 4 lane quadrants x 2 column blocks of 32 tokens
-            const int e = e0 + quad * 32 + lane;
-            float g[32];
-            umma::ld_32x32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(cb * 32), g);
+            for (int a = 0; a < nacc; ++a) {
+                const int e = e0 + 128 * a + quad * 32 + lane;
+                float g[32], gm[32], gl[32];
+                const uint32_t ta = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * kRtAccCols + cb * 32);
+                umma::ld_32x32(ta, g);
+                umma::ld_32x32(ta + kRtTok, gm);
+                umma::ld_32x32(ta + 2 * kRtTok, gl);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const int t = t0 + cb * 32 + c;
-                if (t < n && e < E) logits[(size_t)t * E + e] = g[c];
+                for (int c = 0; c < 32; ++c) {
+                    const int t = t0 + cb * 32 + c;
+                    if (t < n && e < E) logits[(size_t)t * E + e] = (g[c] + gm[c]) + gl[c];
+                }
             }
         }
     } else if (tid == 0) {
@@ -292,7 +323,7 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __nv_bfloat16
     }
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tmem, kRtTok);
+    if (warp == 0) umma::tmem_dealloc(tmem, kRtTmemCols);
 }
 
 // ─── route: one warp per token ──────────────────────────────────────────────
@@ -303,10 +334,11 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
                                                           const float* __restrict__ bias,
                                                           const int32_t* __restrict__ forced,
                                                           int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
-                                                          int32_t* __restrict__ counts) {
+                                                          int32_t* __restrict__ counts, int nsplit) {
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= n) return;
     const float* lg = logits + (size_t)t * E;
+    const size_t slab = (size_t)n * E;  // the router GEMM leaves kRtSplit partial sums, added here in a fixed order
     float p[kMaxEPerLane];
     float mx = -INFINITY;
 #pragma unroll
@@ -314,7 +346,14 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
         const int e = lane + 32 * i;
         float v = -INFINITY;
         if (e < E) {
-            v = lg[e];
+            // all partial sums are requested before the first is used; they are added in slab order
+            float part[kRtMaxSplit];
+#pragma unroll
+            for (int z = 0; z < kRtMaxSplit; ++z) part[z] = (z < nsplit) ? __ldg(lg + e + z * slab) : 0.0f;
+            v = part[0];
+#pragma unroll
+            for (int z = 1; z < kRtMaxSplit; ++z)
+                if (z < nsplit) v += part[z];
             if (bias) v += bias[e];
         }
         p[i] = v;
@@ -995,6 +1034,33 @@ static constexpr size_t gemm_smem_bytes() {
     return (size_t)kAStages * (256 * 128) + (size_t)kBStages * (kNT * 128) + 1024;
 }
 
+// Tensor map of a row-major [rows][H] bf16 tensor read in boxes of box_rows x 64 columns with the
+// 128-byte swizzle the MMA descriptors expect.  The encoder lives in the driver library; its entry
+// point is looked up through the runtime so that nothing links against the driver directly.
+typedef CUresult (*tmap_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int encode_rows_map(void* out128, const void* base, uint64_t rows, uint32_t box_rows) {
+    static tmap_encode_fn fn = nullptr;
+    if (!fn) {
+        void* pfn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        MOE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pfn, cudaEnableDefault, &q));
+        MOE_REQUIRE(pfn && q == cudaDriverEntryPointSuccess, "the driver does not provide cuTensorMapEncodeTiled");
+        fn = reinterpret_cast<tmap_encode_fn>(pfn);
+    }
+    static_assert(sizeof(CUtensorMap) == 128, "tensor maps are stored in 128-byte fields");
+    const cuuint64_t gdim[2] = {(cuuint64_t)kBH, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)kBH * 2};
+    const cuuint32_t box[2] = {64u, box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(reinterpret_cast<CUtensorMap*>(out128), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim,
+                          gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MOE_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with driver status %d", (int)r);
+    return MOE_OK;
+}
+
 // Builds the router's bf16 planes of a layer on first batched use (and after the router is reloaded).
 static int ensure_router_planes(moe_engine* e, int layer) {
     LayerHost& lh = e->layers[layer];
@@ -1002,6 +1068,8 @@ static int ensure_router_planes(moe_engine* e, int layer) {
     const int E = e->dims.num_experts, rows = (E + 127) / 128 * 128;
     if (!lh.planes) {
         MOE_CUDA(cudaMalloc(&lh.planes, (size_t)3 * rows * kBH * 2));
+        int rcm = encode_rows_map(lh.planes_map, lh.planes, (uint64_t)3 * rows, 128);
+        if (rcm) return rcm;
         e->resident += (size_t)3 * rows * kBH * 2;
     }
     int rc = refresh_layer_table(e);
@@ -1026,7 +1094,8 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
     const size_t o_ha = take(n * H * 4), o_hb = take(n * H * 4), o_x = take(n * H * 2), o_xm = take(n * H * 2), o_xl = take(n * H * 2);
-    const size_t o_lg = take(n * E * 4), o_ti = take(n * K * 4), o_tw = take(n * K * 4), o_sg = take(n * 4);
+    const size_t o_lg = take((n > 8192 ? n : (size_t)8192) * E * 4);  // up to kRtMaxSplit partial sums for small token counts
+    const size_t o_ti = take(n * K * 4), o_tw = take(n * K * 4), o_sg = take(n * 4);
     const size_t o_cnt = take((E + 1) * 4), o_off = take((E + 2) * 4), o_cur = take((E + 1) * 4);
     const size_t o_st = take(slots * 4), o_so = take(n * K * 4), o_act = take(slots * I * 2), o_o = take(slots * H * 2);
     const size_t o_tl = take((size_t)max_tiles * 3 * 4), o_nt = take(4);
@@ -1042,6 +1111,10 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     bw.tile_list = (int32_t*)(b + o_tl); bw.n_tiles = (int32_t*)(b + o_nt);
     bw.max_tiles = max_tiles;
     bw.capacity = n_tokens;
+    {
+        int rcm = encode_rows_map(bw.x_map, bw.x, (uint64_t)3 * n, kRtTok);
+        if (rcm) return rcm;
+    }
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<1>()));
     MOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<2>()));
     MOE_CUDA(cudaFuncSetAttribute(router_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem));
@@ -1079,10 +1152,11 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
 
     MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
-    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, kRtSmem, st>>>(
-        bw.x, bw.x_mid, bw.x_lo, n, E, ly.router_planes, ly.router_nplanes, (E + 127) / 128 * 128, bw.logits,
-        e->dec_sync + 2);
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts);
+    const int rsplit = router_split(n, E, ly.router_nplanes);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
+        *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
+        ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, e->dec_sync + 2);
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit);
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
     GemmParams gp{};
@@ -1142,22 +1216,49 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     for (int i = 0; i < P; ++i) peers.base[i] = ep.peer[i];
     const int32_t* counts_all = reinterpret_cast<const int32_t*>(ep.local + ep.sym.counts);
 
+    // optional timeline of one layer (environment variable MOE_EP_TRACE = layer index): an event after every
+    // launch, printed by rank 0 once the layer has finished
+    static const int trace_layer = getenv("MOE_EP_TRACE") ? atoi(getenv("MOE_EP_TRACE")) : -1;
+    const bool tracing = (layer == trace_layer);
+    std::vector<std::pair<const char*, cudaEvent_t>> marks;
+    auto ep_mark = [&](const char* name) {
+        if (!tracing) return;
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        cudaEventRecord(ev, st);
+        marks.emplace_back(name, ev);
+    };
+#define EP_MARK(name) ep_mark(name)
+    EP_MARK("start");
     MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
+    EP_MARK("memset");
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
-    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, (E + 127) / 128), 256, kRtSmem, st>>>(
-        bw.x, bw.x_mid, bw.x_lo, n, E, ly.router_planes, ly.router_nplanes, (E + 127) / 128 * 128, bw.logits, err);
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts);
+    EP_MARK("batch_prep_kernel");
+    const int rsplit = router_split(n, E, ly.router_nplanes);
+    router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
+        *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
+        ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, err);
+    EP_MARK("router_gemm_kernel");
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit);
+    EP_MARK("batch_route_kernel");
     // 1. histogram exchange
     ep_push_counts_kernel<<<(P * E + 255) / 256, 256, 0, st>>>(peers, ep.sym, me, P, E, bw.counts);
+    EP_MARK("ep_push_counts_kernel");
     ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    EP_MARK("ep_signal_kernel");
     ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    EP_MARK("ep_wait_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
                                        ep.max_tiles, ep.total_recv);
+    EP_MARK("ep_plan_kernel");
     // 2. dispatch
     ep_scatter_kernel<<<(n * K + n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, ep.base_send,
                                                           ep.cursor, ep.total_recv);
+    EP_MARK("ep_scatter_kernel");
     ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    EP_MARK("ep_signal_kernel");
     ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    EP_MARK("ep_wait_kernel");
     // 3. grouped GEMMs over the received rows (+ shared expert over the local ones)
     GemmParams gp{};
     gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
@@ -1166,14 +1267,36 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     gp.tile_list = ep.tile_list; gp.n_tiles = ep.n_tiles; gp.slot_token = ep.ident;
     gp.err = err;
     grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
+    EP_MARK("grouped_gemm_kernel<1>");
     grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
+    EP_MARK("grouped_gemm_kernel<2>");
     // 4. return
     ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, ep.o, ep.total_recv);
+    EP_MARK("ep_return_kernel");
     ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
+    EP_MARK("ep_signal_kernel");
     ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
+    EP_MARK("ep_wait_kernel");
     // 5. combine
     ep_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.oback),
                                          ep.o, ep.total_recv, bw.topk_w, bw.sgate);
+    EP_MARK("ep_combine_kernel");
+    if (tracing) {
+        cudaStreamSynchronize(st);
+        if (me == 0) {
+            fprintf(stderr, "[ep trace] layer %d, %d tokens on this rank, %d ranks\n", layer, n, P);
+            for (size_t i = 1; i < marks.size(); ++i) {
+                float ms = 0.0f;
+                cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
+                fprintf(stderr, "[ep trace] %-28s %8.1f us\n", marks[i].first, ms * 1e3f);
+            }
+            float tot = 0.0f;
+            cudaEventElapsedTime(&tot, marks.front().second, marks.back().second);
+            fprintf(stderr, "[ep trace] %-28s %8.1f us\n", "total", tot * 1e3f);
+        }
+        for (auto& m : marks) cudaEventDestroy(m.second);
+    }
+#undef EP_MARK
     e->launches += 17;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
