@@ -119,6 +119,7 @@ struct EpState {
     int32_t* cursor = nullptr;              // [E]
     int32_t* ident = nullptr;               // [slots_cap + cap] identity map
     int32_t* total_recv = nullptr;          // rows received this layer
+    unsigned int* done = nullptr;           // blocks finished (scatter / return kernels), rewound by the last one
     int max_tiles = 0;
 };
 

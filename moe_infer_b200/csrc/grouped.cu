@@ -479,7 +479,31 @@ struct GemmParams {
     const int32_t* n_tiles;
     const int32_t* slot_token;
     unsigned int* err;
+    // expert-parallel use: before touching x, wait until every peer has published `ep_epoch` (ep_world = 0: no wait)
+    const uint8_t* ep_local;
+    size_t ep_flags;
+    int ep_world;
+    unsigned int ep_epoch;
 };
+
+// Hand-offs between the GPUs of an expert-parallel group are epoch numbers in a flag word per
+// (receiver, sender).  Lanes 0..P-1 of the calling warp wait until every sender has published
+// `epoch` to this rank; bounded (an error word is raised and the caller goes on).
+__device__ __forceinline__ void ep_wait_warp(const uint8_t* local, size_t flags_off, int P, unsigned int epoch,
+                                             unsigned int* err, int lane) {
+    if (lane < P) {
+        const unsigned int* f = reinterpret_cast<const unsigned int*>(local + flags_off) + lane * 16;
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - epoch) >= 0) break;
+            if (clock64() - t0 > kWaitCycles) { atomicExch(err, 9u); break; }
+        }
+    }
+    __threadfence_system();
+    __syncwarp();
+}
 
 // 8 nibbles of one word -> 8 bf16 (n * s + b) in the order [0,4,1,5,2,6,3,7]
 __device__ __forceinline__ uint4 dequant_word(uint32_t w, __nv_bfloat162 s2, __nv_bfloat162 b2) {
@@ -572,6 +596,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
         mbar_fence_init();
     }
     if (warp == 0) umma::tmem_alloc(&tmem_slot, kTmemCols);
+    if (warp == 1 && p.ep_world > 0) ep_wait_warp(p.ep_local, p.ep_flags, p.ep_world, p.ep_epoch, p.err, lane);
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
@@ -844,45 +869,52 @@ struct EpPeers {
     uint8_t* base[kEpMaxWorld];
 };
 
-__global__ void ep_push_counts_kernel(EpPeers peers, EpSym sym, int me, int P, int E, const int32_t* counts) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < P * E) {
-        const int d = i / E, e = i - d * E;
-        reinterpret_cast<int32_t*>(peers.base[d] + sym.counts)[(size_t)me * E + e] = counts[e];
-    }
-}
-
-// One warp: lane s publishes this rank's epoch to peer s (after a system-scope fence:
-// the rows written by earlier kernels of this stream are visible before the flag).
-__global__ void ep_signal_kernel(EpPeers peers, EpSym sym, int me, int P, unsigned int epoch) {
+// Lanes 0..P-1 of the calling warp publish this rank's epoch to every peer, after a system-scope
+// fence: whatever this thread has observed as written is visible before the flag.
+__device__ __forceinline__ void ep_signal_warp(const EpPeers& peers, const EpSym& sym, int me, int P, unsigned int epoch, int lane) {
     __threadfence_system();
-    const int s = threadIdx.x;
-    if (s < P) {
-        unsigned int* f = reinterpret_cast<unsigned int*>(peers.base[s] + sym.flags) + me * 16;
+    if (lane < P) {
+        unsigned int* f = reinterpret_cast<unsigned int*>(peers.base[lane] + sym.flags) + me * 16;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
     }
 }
 
-// One warp: lane s waits until peer s has published `epoch`; bounded.
-__global__ void ep_wait_kernel(uint8_t* local, EpSym sym, int P, unsigned int epoch, unsigned int* err) {
-    const int s = threadIdx.x;
-    if (s < P) {
-        const unsigned int* f = reinterpret_cast<const unsigned int*>(local + sym.flags) + s * 16;
-        const long long t0 = clock64();
-        for (;;) {
-            unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if ((int)(v - epoch) >= 0) break;
-            if (clock64() - t0 > kWaitCycles) { atomicExch(err, 9u); break; }
-        }
+// True in exactly one block of the grid: the last one whose threads have all finished their stores
+// (each thread fences at system scope before its block is counted).  That block resets the counter.
+__device__ __forceinline__ bool ep_last_block(unsigned int* counter) {
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(counter, 1u);
+        s_last = (prev == gridDim.x - 1) ? 1 : 0;
+        if (s_last) *counter = 0u;
+    }
+    __syncthreads();
+    return s_last != 0;
+}
+
+// One block: this rank's histogram goes to every peer, then the epoch flag.
+__global__ void __launch_bounds__(1024) ep_push_counts_kernel(EpPeers peers, EpSym sym, int me, int P, int E,
+                                                              const int32_t* counts, unsigned int epoch) {
+    for (int i = threadIdx.x; i < P * E; i += blockDim.x) {
+        const int d = i / E, e = i - d * E;
+        reinterpret_cast<int32_t*>(peers.base[d] + sym.counts)[(size_t)me * E + e] = counts[e];
     }
     __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
 // plan: one block.  counts_all[s][e] = rows rank s sends to expert e.
 __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* counts_all, int me, int P, int E, int n_local,
                                                        int32_t* base_send, int32_t* cursor, int32_t* tile_list,
-                                                       int32_t* n_tiles, int max_tiles, int32_t* total_recv) {
+                                                       int32_t* n_tiles, int max_tiles, int32_t* total_recv,
+                                                       const uint8_t* local, size_t flags_off, unsigned int epoch,
+                                                       unsigned int* err) {
+    // every peer's histogram must have arrived
+    if (threadIdx.x < 32) ep_wait_warp(local, flags_off, P, epoch, err, threadIdx.x);
+    __syncthreads();
     __shared__ int tot[1024];      // rows expert e receives from everybody
     __shared__ int before[1024];   // ... from ranks below me
     __shared__ int estart[1024];   // first slot of expert e inside its owner's buffer
@@ -948,7 +980,8 @@ __global__ void __launch_bounds__(256) ep_scatter_kernel(EpPeers peers, EpSym sy
                                                          const __nv_bfloat16* __restrict__ x,
                                                          const int32_t* __restrict__ topk_idx,
                                                          const int32_t* __restrict__ base_send, int32_t* cursor,
-                                                         const int32_t* __restrict__ total_recv) {
+                                                         const int32_t* __restrict__ total_recv, unsigned int* done,
+                                                         unsigned int epoch) {
     const int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int Eloc = E / P;
     if (w < n * K) {
@@ -973,12 +1006,15 @@ __global__ void __launch_bounds__(256) ep_scatter_kernel(EpPeers peers, EpSym sy
 #pragma unroll
         for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
     }
+    // the last block to finish tells every peer that this rank's rows are in place
+    if (ep_last_block(done) && threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
 // return: one warp per received row; the output row goes back to the rank that sent the input row.
-__global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, EpSym sym, int me,
+__global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, EpSym sym, int me, int P,
                                                         const __nv_bfloat16* __restrict__ o,
-                                                        const int32_t* __restrict__ total_recv) {
+                                                        const int32_t* __restrict__ total_recv, unsigned int* done,
+                                                        unsigned int epoch) {
     const int lane = threadIdx.x & 31;
     const int total = *total_recv;
     const int2* meta = reinterpret_cast<const int2*>(peers.base[me] + sym.meta);
@@ -989,6 +1025,7 @@ __global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, EpSym sym
 #pragma unroll
         for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
     }
+    if (ep_last_block(done) && threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
 // combine: moe_combine_residual (reference src/math_util.rs:599-612); routed rows come from the
@@ -998,8 +1035,12 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const float* __restrict
                                                          const __nv_bfloat16* __restrict__ o_local,
                                                          const int32_t* __restrict__ total_recv,
                                                          const float* __restrict__ topk_w,
-                                                         const float* __restrict__ sgate) {
+                                                         const float* __restrict__ sgate, const uint8_t* local,
+                                                         size_t flags_off, int P, unsigned int epoch, unsigned int* err) {
     const int t = blockIdx.x, tid = threadIdx.x;
+    // every peer's output rows must have arrived
+    if (tid < 32) ep_wait_warp(local, flags_off, P, epoch, err, tid);
+    __syncthreads();
     const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
     const float4 a = hp[0], b = hp[1];
     float moe[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, sh[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -1183,8 +1224,10 @@ int ep_alloc_work(moe_engine* e) {
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
     const size_t o_act = take(rows * d.inter * 2), o_o = take(rows * d.hidden * 2), o_tl = take((size_t)ep.max_tiles * 12);
     const size_t o_nt = take(4), o_bs = take((size_t)d.num_experts * 4), o_cu = take((size_t)d.num_experts * 4);
-    const size_t o_id = take(rows * 4), o_tr = take(4);
+    const size_t o_id = take(rows * 4), o_tr = take(4), o_dn = take(4);
     MOE_CUDA(cudaMalloc(&ep.work, off));
+    ep.done = (unsigned int*)(ep.work + o_dn);
+    MOE_CUDA(cudaMemsetAsync(ep.done, 0, 4, e->stream));
     ep.act = (__nv_bfloat16*)(ep.work + o_act); ep.o = (__nv_bfloat16*)(ep.work + o_o);
     ep.tile_list = (int32_t*)(ep.work + o_tl); ep.n_tiles = (int32_t*)(ep.work + o_nt);
     ep.base_send = (int32_t*)(ep.work + o_bs); ep.cursor = (int32_t*)(ep.work + o_cu);
@@ -1241,45 +1284,34 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     EP_MARK("router_gemm_kernel");
     batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit);
     EP_MARK("batch_route_kernel");
-    // 1. histogram exchange
-    ep_push_counts_kernel<<<(P * E + 255) / 256, 256, 0, st>>>(peers, ep.sym, me, P, E, bw.counts);
+    // 1. histogram exchange (the push publishes the epoch; the plan waits for everybody's)
+    ep_push_counts_kernel<<<1, 1024, 0, st>>>(peers, ep.sym, me, P, E, bw.counts, ++ep.epoch);
     EP_MARK("ep_push_counts_kernel");
-    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
-    EP_MARK("ep_signal_kernel");
-    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
-    EP_MARK("ep_wait_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
-                                       ep.max_tiles, ep.total_recv);
+                                       ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);
     EP_MARK("ep_plan_kernel");
-    // 2. dispatch
+    // 2. dispatch (the last block of the scatter publishes the epoch)
     ep_scatter_kernel<<<(n * K + n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, ep.base_send,
-                                                          ep.cursor, ep.total_recv);
+                                                          ep.cursor, ep.total_recv, ep.done, ++ep.epoch);
     EP_MARK("ep_scatter_kernel");
-    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
-    EP_MARK("ep_signal_kernel");
-    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
-    EP_MARK("ep_wait_kernel");
-    // 3. grouped GEMMs over the received rows (+ shared expert over the local ones)
+    // 3. grouped GEMMs over the received rows (+ shared expert over the local ones); the first one waits for the rows
     GemmParams gp{};
     gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
     gp.x = reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.xrecv);
     gp.act = ep.act; gp.o = ep.o;
     gp.tile_list = ep.tile_list; gp.n_tiles = ep.n_tiles; gp.slot_token = ep.ident;
     gp.err = err;
+    gp.ep_local = ep.local; gp.ep_flags = ep.sym.flags; gp.ep_world = P; gp.ep_epoch = ep.epoch;
     grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
     EP_MARK("grouped_gemm_kernel<1>");
+    gp.ep_world = 0;
     grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
     EP_MARK("grouped_gemm_kernel<2>");
-    // 4. return
-    ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, ep.o, ep.total_recv);
+    // 4. return (the last block publishes the epoch), 5. combine (waits for everybody's rows)
+    ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, P, ep.o, ep.total_recv, ep.done, ++ep.epoch);
     EP_MARK("ep_return_kernel");
-    ep_signal_kernel<<<1, 32, 0, st>>>(peers, ep.sym, me, P, ++ep.epoch);
-    EP_MARK("ep_signal_kernel");
-    ep_wait_kernel<<<1, 32, 0, st>>>(ep.local, ep.sym, P, ep.epoch, err);
-    EP_MARK("ep_wait_kernel");
-    // 5. combine
     ep_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.oback),
-                                         ep.o, ep.total_recv, bw.topk_w, bw.sgate);
+                                         ep.o, ep.total_recv, bw.topk_w, bw.sgate, ep.local, ep.sym.flags, P, ep.epoch, err);
     EP_MARK("ep_combine_kernel");
     if (tracing) {
         cudaStreamSynchronize(st);
@@ -1297,7 +1329,7 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
         for (auto& m : marks) cudaEventDestroy(m.second);
     }
 #undef EP_MARK
-    e->launches += 17;
+    e->launches += 11;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
