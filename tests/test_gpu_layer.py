@@ -77,6 +77,34 @@ def test_forced_indices_and_logit_bias(full_layer):
     assert rel_l2(out - h, ref - h) < TIGHT
 
 
+@pytest.mark.parametrize("scale", [1e-3, 1.0, 1e3])
+def test_decode_layer_activation_scale(full_layer, scale):
+    """The decode router sums exact products in fixed point, scaled by the running 1/rms: expert choices
+    and outputs must not depend on the magnitude of the residual stream."""
+    eng, lw = full_layer
+    h = (synth.hidden_states(4, 2, 1, 2048) * np.float32(scale)).astype(np.float32)
+    out, idx, wts = eng.layer_forward(0, h)
+    ref, idx_r, wts_r = oracle.moe_layer(lw, h, 8)
+    _check_routing(idx, wts, idx_r, wts_r)
+    # out = h + update is rounded to f32 at the magnitude of h: that rounding bounds how well the update
+    # can be recovered by subtracting h again
+    floor = np.finfo(np.float32).eps * np.linalg.norm(h) / np.linalg.norm(ref - h)
+    assert rel_l2(out - h, ref - h) < TIGHT + 2.0 * floor
+    assert rel_l2(out, ref) < TIGHT
+
+
+def test_decode_layer_outlier_activations(full_layer):
+    """A few elements hundreds of times the rms (as in real residual streams): the integer dot products keep
+    23 bits relative to each 32-element chunk's maximum, so the rest of the chunk must not lose accuracy."""
+    eng, lw = full_layer
+    h = synth.hidden_states(5, 2, 1, 2048).copy()
+    h[0, [7, 300, 1029, 2047]] *= np.float32(300.0)
+    out, idx, wts = eng.layer_forward(0, h)
+    ref, idx_r, wts_r = oracle.moe_layer(lw, h, 8)
+    _check_routing(idx, wts, idx_r, wts_r)
+    assert rel_l2(out - h, ref - h) < TIGHT
+
+
 def test_stripped_model_shape_int4_router():
     """The reference's test model: 4 experts, top-4; INT4 scheme (4-bit router)."""
     lw = make_layer(5, 0, num_experts=4, scheme="int4")
@@ -123,6 +151,18 @@ def test_stack_decode(small_stack):
     # batched flag gives the same hidden states (tolerance: the grouped path computes in bf16)
     out_b = eng.forward_hidden(emb, batched=True)
     assert rel_l2(out_b, ref) < TOL
+
+
+def test_stack_decode_growing_residual(small_stack):
+    """Inside a stack the next layer's logits are accumulated with the previous layer's 1/rms as scale: a
+    residual stream that starts tiny and one that starts huge must both route like the oracle."""
+    eng, layers = small_stack
+    for scale in (1e-4, 50.0):
+        emb = (synth.hidden_states(11, 2, 2, 2048) * np.float32(scale)).astype(np.float32)
+        out = eng.forward_hidden(emb)
+        ref = oracle.moe_stack(layers[:4], emb, 8)
+        floor = np.finfo(np.float32).eps * np.linalg.norm(emb) / np.linalg.norm(ref - emb)
+        assert rel_l2(out - emb, ref - emb) < 1e-3 + 2.0 * floor
 
 
 def test_stack_interrupt(small_stack):
