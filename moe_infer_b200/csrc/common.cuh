@@ -152,6 +152,7 @@ struct moe_engine {
     unsigned int dec_epoch = 0;            // tags consumed so far (one per layer pass)
     unsigned long long* dec_hint = nullptr;    // fused decode kernel: count of CTAs whose outputs are written
     unsigned long long dec_hint_base = 0;
+    unsigned long long* dec_h_ll = nullptr;    // fused decode kernel: tagged hidden state between layers
     long long* dec_prof = nullptr;         // per-phase clock stamps (off unless enabled)
     int dec_grid = 0;
     float* stage_host = nullptr;           // pinned staging [H] x 2

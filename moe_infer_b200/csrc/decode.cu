@@ -661,18 +661,17 @@ struct Decode3Params {
     int l0, l1;
     const float* h_in;
     float* h_out;
-    float* h_buf0;
-    float* h_buf1;
     long long* acc;     // [2][kAccStride] fixed-point accumulators (router logits; [kMaxE] = sum of squares), zero at launch
     unsigned long long* act_ll;  // [(K + 1) * I + 1] (tag << 32 | float bits): SwiGLU outputs, then the shared gate score
     unsigned int epoch_base;     // tags in act_ll are <= epoch_base when the kernel starts
-    unsigned long long* hint;    // counts CTAs that have written their outputs (a hint: the tags decide)
+    unsigned long long* hint;    // counts CTAs that have written their SwiGLU outputs (a hint: the tags decide)
+    unsigned long long* hint2;   // counts CTAs that have finished a layer (h stored, partial logits added); same base
     unsigned long long hint_base;
+    unsigned long long* h_ll;    // [H] (tag << 32 | float bits): the hidden state between layers
     const float* logit_bias;
     const int32_t* forced_idx;
     int32_t* out_idx;
     float* out_w;
-    unsigned int* sync;      // [0] arrivals, [1] exits, [2] error word
     unsigned int* err;
     long long* prof;
     int E, K;
@@ -886,8 +885,10 @@ __device__ __forceinline__ void push_partial_logits(const DecodeSmem3* sm, bool 
         } else {
             for (int j = 0; j < nc; ++j) part = fmaf(sm->wt[j * Ep + tid], sm->hn[j], part);
         }
+        // value in the upper 56 bits, a contribution count in the low 8: a reader knows the sum is complete
+        // when the count has advanced by the number of CTAs (fewer than 256)
         const long long fx = __float2ll_rn(part * scale * kFix);
-        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + tid * kAccPitch, (unsigned long long)fx);
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + tid * kAccPitch, ((unsigned long long)fx << 8) + 1ull);
     }
     if (tid == kDecThreads - 1) {
         // this CTA's share of sum((h * scale)^2)
@@ -896,7 +897,8 @@ __device__ __forceinline__ void push_partial_logits(const DecodeSmem3* sm, bool 
             const float t = sm->hraw[j] * scale;
             q = fmaf(t, t, q);
         }
-        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + kMaxE * kAccPitch, (unsigned long long)__float2ll_rn(q * kFix));
+        atomicAdd(reinterpret_cast<unsigned long long*>(acc) + kMaxE * kAccPitch,
+                  ((unsigned long long)__float2ll_rn(q * kFix) << 8) + 1ull);
     }
 }
 
@@ -1001,6 +1003,50 @@ __device__ __forceinline__ void rows_dot_q(const DecodeSmem3* sm, const uint4* c
     }
 #pragma unroll
     for (int r = 0; r < NR; ++r) out[r] = warp_sum(out[r]);
+}
+
+// Reads an accumulator until the contributions of all G CTAs are in: the word is never reset, the reader
+// subtracts what it read two layers ago (`prev`, updated).  Returns the sum (2^-32 units); bounded.
+__device__ __forceinline__ long long read_counted(const long long* word, unsigned long long& prev, int G, int* ok) {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        unsigned long long raw;
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(raw) : "l"(word) : "memory");
+        const unsigned long long d = raw - prev;
+        if ((int)(d & 0xFFull) == G) {
+            prev = raw;
+            return (long long)d >> 8;
+        }
+        if ((it & 15u) == 15u && clock64() - t0 > kWaitCycles) { *ok = 0; return 0; }
+    }
+}
+
+// x = rmsnorm(h) * w staged as digit planes, h given as this thread's float4 (elements 4 tid ..)
+__device__ __forceinline__ void stage_from_regs(DecodeSmem3* sm, const uint16_t* norm_w, const float4 v) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + tid);
+    reinterpret_cast<float4*>(sm->raw)[tid] = v;  // the down phase adds the residual from here
+    float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    if (lane == 0) sm->red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kDecWarps; ++i) tot += sm->red[i];
+    const float inv_rms = 1.0f / sqrtf(tot / (float)kH + 1e-6f);
+    if (tid == 0) sm->inv_rms = inv_rms;
+    float4 o;
+    o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
+    o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
+    o.z = v.z * inv_rms * __uint_as_float(wb.y << 16);
+    o.w = v.w * inv_rms * __uint_as_float(wb.y & 0xFFFF0000u);
+    const int c = tid >> 3, j = tid & 7;
+    stage_digits(sm->xq, sm->xdl, kChH, c, j, o);
+    float s = (o.x + o.y) + (o.z + o.w);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (j == 0) sm->sumx[c] = s;
+    __syncthreads();
 }
 
 // stage_norm in two halves, so that other work can run while h is in flight
@@ -1166,10 +1212,16 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
     // the shared expert's gate score is one more row: CTA 0's last warp takes it
     const bool sg_here = (cta == 0 && warp == kDecWarps - 1);
 
-    unsigned int bar_target = 0;
     uint32_t parity = 0, wpar = 0;
     bool alive = true;
     float pscale = 1.0f;  // scale the pending accumulators were pushed with
+    // what this thread read from its accumulator words the last time each of the two sets was used
+    unsigned long long pa_cur = 0, pa_oth = 0, pq_cur = 0, pq_oth = 0;
+    // "this CTA has finished": a relaxed count, no fence; the data it announces validates itself
+    auto announce = [&]() {
+        __syncthreads();
+        if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.hint2), "l"(1ull) : "memory");
+    };
 
     // ── prologue: router logits and sum of squares of the first layer from h_in ──
     {
@@ -1190,8 +1242,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             cp_wait<0>();
             __syncthreads();
             push_partial_logits(sm, ly.router_bf16 != nullptr, p.acc, nc, E, pscale, tid);
-            bar_target += G;
-            if (!grid_barrier(p.sync, bar_target, sm)) alive = false;
+            announce();
         }
     }
 
@@ -1199,8 +1250,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         const LayerDev& ly = sm->tab[l - p.l0];
         const int rel = l - p.l0;
         const bool has_next = l + 1 < p.l1;
-        const float* h_cur = (rel == 0) ? p.h_in : ((rel & 1) ? p.h_buf0 : p.h_buf1);
-        float* h_nxt = !has_next ? p.h_out : ((rel & 1) ? p.h_buf1 : p.h_buf0);
         long long* acc_cur = p.acc + (rel & 1) * kAccStride;
         long long* acc_nxt = p.acc + ((rel + 1) & 1) * kAccStride;
         const unsigned int epoch = p.epoch_base + (unsigned int)rel + 1u;
@@ -1208,12 +1257,32 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         // ── route (from the accumulators) while h is being staged ──────────
         PROF3(0);
         DBG(4);
-        stage_issue(sm, h_cur);
         {
+            // every CTA has announced the end of the previous phase (a hint: the words below validate themselves)
+            if (tid == 0) {
+                const unsigned long long want_n = p.hint_base + (unsigned long long)G * (unsigned long long)(rel + 1);
+                const long long t0 = clock64();
+                int okh = 1;
+                for (uint32_t it = 0;; ++it) {
+                    unsigned long long nn;
+                    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(nn) : "l"(p.hint2) : "memory");
+                    if (nn >= want_n) break;
+                    if ((it & 63u) == 63u && clock64() - t0 > kWaitCycles) { okh = 0; break; }
+                }
+                sm->flag = okh;
+            }
+            __syncthreads();
+            int okr = sm->flag;
             float v = -INFINITY;
-            const long long aq = __ldcg(acc_cur + kMaxE * kAccPitch);
+            const long long aq = read_counted(acc_cur + kMaxE * kAccPitch, pq_cur, G, &okr);
             long long a = 0;
-            if (tid < E) a = __ldcg(acc_cur + tid * kAccPitch);
+            if (tid < E) a = read_counted(acc_cur + tid * kAccPitch, pa_cur, G, &okr);
+            { unsigned long long t = pa_cur; pa_cur = pa_oth; pa_oth = t; t = pq_cur; pq_cur = pq_oth; pq_oth = t; }
+            if (!__syncthreads_and(okr)) {
+                if (tid == 0) atomicExch(p.err, 5u);
+                alive = false;
+                break;
+            }
             // mean of (h * pscale)^2 -> 1 / rms(h); the logits were accumulated times pscale
             const float r = 1.0f / pscale;
             const float msq = __ll2float_rn(aq) * (1.0f / kFix) * (1.0f / (float)kH);
@@ -1242,12 +1311,35 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         if (has_next && warp < nc && lane == 0)
             nwn = __uint_as_float((uint32_t)__ldg(sm->tab[rel + 1].post_norm + r0 + warp) << 16);
         PROF3(2);
-        if (!stage_finish(sm, ly.post_norm, parity)) {
-            if (tid == 0) atomicExch(p.err, 3u);
-            alive = false;
-            break;
+        {
+            // this thread's four elements of h: plain floats for the first layer, tagged words afterwards
+            float4 hv4;
+            int okh = 1;
+            if (rel == 0) {
+                hv4 = __ldg(reinterpret_cast<const float4*>(p.h_in) + tid);
+            } else {
+                const unsigned int want_tag = p.epoch_base + (unsigned int)rel;  // the producing layer's epoch
+                const unsigned long long* src = p.h_ll + 4 * tid;
+                unsigned long long q0, q1, q2, q3;
+                const long long t0 = clock64();
+                for (uint32_t it = 0;; ++it) {
+                    ld_ll2(src, q0, q1);
+                    ld_ll2(src + 2, q2, q3);
+                    if ((unsigned int)(q0 >> 32) == want_tag && (unsigned int)(q1 >> 32) == want_tag &&
+                        (unsigned int)(q2 >> 32) == want_tag && (unsigned int)(q3 >> 32) == want_tag)
+                        break;
+                    if ((it & 15u) == 15u && clock64() - t0 > kWaitCycles) { okh = 0; break; }
+                }
+                hv4 = make_float4(__uint_as_float((unsigned int)q0), __uint_as_float((unsigned int)q1),
+                                  __uint_as_float((unsigned int)q2), __uint_as_float((unsigned int)q3));
+            }
+            if (!__syncthreads_and(okh)) {
+                if (tid == 0) atomicExch(p.err, 3u);
+                alive = false;
+                break;
+            }
+            stage_from_regs(sm, ly.post_norm, hv4);
         }
-        parity ^= 1u;
         const float inv_rms = sm->inv_rms;
         PROF3(3);
         int landed = 1;
@@ -1399,12 +1491,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 alive = false;
                 break;
             }
-            // Every CTA routed (and so read these accumulators) before it produced the outputs
-            // that this CTA has now seen in full: safe to clear them for the layer after next.
-            if (cta == 0) {
-                if (tid < E) acc_cur[tid * kAccPitch] = 0;
-                if (tid == kDecThreads - 1) acc_cur[kMaxE * kAccPitch] = 0;
-            }
         }
         PROF3(7);
         DBG(5);
@@ -1434,7 +1520,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 // moe_combine_residual (reference src/math_util.rs:599-612)
                 if (lane == 0) {
                     const float hv = sm->raw[r0 + j] + acc;
-                    h_nxt[r0 + j] = hv;
+                    if (has_next) st_ll(p.h_ll + r0 + j, epoch, hv);
+                    else p.h_out[r0 + j] = hv;
                     sm->hraw[j] = hv;
                     sm->hn[j] = hv * nwn;
                 }
@@ -1447,23 +1534,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 pscale = inv_rms;
                 PROF3(9);
                 DBG(2);
-                bar_target += G;
-                if (!grid_barrier(p.sync, bar_target, sm)) { alive = false; break; }
+                announce();
                 DBG(3);
                 PROF3(10);
             }
-        }
-    }
-
-    // Last CTA out rewinds the barrier words for the next launch.
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        const unsigned int done = atomicAdd(&p.sync[1], 1u) + 1u;
-        if (done == (unsigned int)G) {
-            p.sync[0] = 0u;
-            p.sync[1] = 0u;
-            __threadfence();
         }
     }
 }
@@ -1519,9 +1593,11 @@ int decode_init(moe_engine* e) {
     MOE_CUDA(cudaMallocHost(&e->stage_host, (size_t)2 * d.hidden * sizeof(float)));
     MOE_CUDA(cudaMalloc(&e->dec_act_ll, kActLLWords * sizeof(unsigned long long)));
     MOE_CUDA(cudaMemset(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long)));
-    MOE_CUDA(cudaMalloc(&e->dec_hint, 128));
-    MOE_CUDA(cudaMemset(e->dec_hint, 0, 128));
+    MOE_CUDA(cudaMalloc(&e->dec_hint, 256));  // two counters, a cache line apart
+    MOE_CUDA(cudaMemset(e->dec_hint, 0, 256));
     e->dec_hint_base = 0;
+    MOE_CUDA(cudaMalloc(&e->dec_h_ll, kH * sizeof(unsigned long long)));
+    MOE_CUDA(cudaMemset(e->dec_h_ll, 0, kH * sizeof(unsigned long long)));
     MOE_CUDA(cudaMalloc(&e->dec_acc, 2 * kAccStride * sizeof(long long)));
     MOE_CUDA(cudaMemset(e->dec_acc, 0, 2 * kAccStride * sizeof(long long)));
     e->dec_epoch = 0;
@@ -1567,7 +1643,7 @@ void decode_destroy(moe_engine* e) {
     if (e->dec_prof) cudaFree(e->dec_prof);
     cudaFree(e->dec_h[0]); cudaFree(e->dec_h[1]); cudaFree(e->dec_logits); cudaFree(e->dec_act);
     cudaFree(e->dec_misc); cudaFree(e->dec_idx); cudaFree(e->dec_w); cudaFree(e->dec_sync);
-    cudaFree(e->dec_act_ll); cudaFree(e->dec_acc); cudaFree(e->dec_hint);
+    cudaFree(e->dec_act_ll); cudaFree(e->dec_acc); cudaFree(e->dec_hint); cudaFree(e->dec_h_ll);
     if (e->stage_host) cudaFreeHost(e->stage_host);
 }
 
@@ -1576,7 +1652,8 @@ void decode_destroy(moe_engine* e) {
 int decode_reset_after_error(moe_engine* e) {
     MOE_CUDA(cudaMemsetAsync(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long), e->stream));
     MOE_CUDA(cudaMemsetAsync(e->dec_acc, 0, 2 * kAccStride * sizeof(long long), e->stream));
-    MOE_CUDA(cudaMemsetAsync(e->dec_hint, 0, 128, e->stream));
+    MOE_CUDA(cudaMemsetAsync(e->dec_hint, 0, 256, e->stream));
+    MOE_CUDA(cudaMemsetAsync(e->dec_h_ll, 0, kH * sizeof(unsigned long long), e->stream));
     e->dec_hint_base = 0;
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     e->dec_epoch = 0;
@@ -1645,7 +1722,6 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
     p.layers = e->layers_dev;
     p.l0 = l0; p.l1 = l1;
     p.h_in = h_in; p.h_out = h_out;
-    p.h_buf0 = e->dec_h[0]; p.h_buf1 = e->dec_h[1];
     if (e->dec_epoch > 0xFFFF0000u - (unsigned int)(l1 - l0)) {
         rc = decode_reset_after_error(e);  // tags must never repeat: start the epochs over on a cleared buffer
         if (rc != MOE_OK) return rc;
@@ -1654,15 +1730,19 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
     p.epoch_base = e->dec_epoch;
     e->dec_epoch += (unsigned int)(l1 - l0);
     p.hint = e->dec_hint;
+    p.hint2 = e->dec_hint + 16;  // 128 bytes further
+    p.h_ll = e->dec_h_ll;
     p.hint_base = e->dec_hint_base;
+    // the accumulators are never cleared by the kernel (readers subtract what they saw before): start from zero
+    MOE_CUDA(cudaMemsetAsync(e->dec_acc, 0, 2 * kAccStride * sizeof(long long), e->stream));
     e->dec_hint_base += (unsigned long long)G * (unsigned long long)(l1 - l0);
     p.logit_bias = logit_bias; p.forced_idx = forced_idx;
     p.out_idx = out_idx; p.out_w = out_w;
-    p.sync = e->dec_sync;
     p.err = e->dec_sync + 2;
     p.prof = e->dec_prof;
     p.E = d.num_experts; p.K = d.top_k;
     p.lay = e->lay;
+    MOE_REQUIRE(G < 256, "decode kernel counts CTAs in 8 bits (grid of %d)", G);
     void* args[] = {&p};
     MOE_CUDA(cudaLaunchCooperativeKernel((const void*)decode_fused_kernel, dim3(e->dec_grid), dim3(kDecThreads),
                                          args, sizeof(DecodeSmem3), e->stream));
