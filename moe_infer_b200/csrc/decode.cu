@@ -623,17 +623,25 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
 //
 // logits_{l+1}[e] = inv_rms * sum_i Wr[e][i] * nw[i] * h_{l+1}[i] is linear in h, and after
 // the down phase every CTA owns ~14 finished elements of h_{l+1}: it multiplies them
-// with its slice of the transposed, norm-weighted router (built once per layer) and adds
-// the 256 partial sums into a global accumulator.  Partial sums are added as 64-bit
-// fixed point (2^-32 units), so the total does not depend on the order of arrival and
-// repeated runs give identical bits.  The logits are complete at the same barrier as
-// h itself, and so is the sum of squares the norm needs (one more accumulator), so routing
-// starts straight after the barrier while h is still being staged.  The shared expert's
-// gate/up rows ride along with the routed experts' as a ninth "slot".
-// The SwiGLU outputs cross from the CTAs that compute them to all CTAs without a barrier:
-// each value travels in one 8-byte word together with a tag (the layer's epoch number),
-// 8-byte stores are single-copy atomic, and a reader simply re-reads until every tag it
-// needs is current.  That leaves one counting barrier per layer (after the down phase).
+// with its slice of the transposed router (built once per layer) and adds the 256 partial
+// sums into a global accumulator.  Partial sums are added as 64-bit fixed point (2^-32
+// units, scaled by the current 1/rms so magnitudes stay near a finished logit): integer
+// addition is associative, so the total does not depend on the order of arrival and
+// repeated runs give identical bits.  The sum of squares the next norm needs travels the
+// same way, so routing starts from 2 KB of accumulators.  The shared expert's gate/up rows
+// ride along with the routed experts' as a ninth "slot".
+//
+// Nothing that crosses CTAs waits for a fence:
+//  * SwiGLU outputs and the hidden state travel as 8-byte words (tag, value), tag = the
+//    producing layer's epoch.  8-byte accesses are single-copy atomic: a reader that sees
+//    the current tag sees the value, and re-reads a word whose tag is stale.
+//  * Accumulator words carry a contribution count in their low 8 bits (value in the upper
+//    56); they are never cleared, a reader subtracts what it read two layers earlier and
+//    knows the sum is complete when the count has advanced by the number of CTAs.
+//  * "This CTA is done" is a relaxed increment of a counter that readers watch before they
+//    read at all: a hint that keeps 148 CTAs from hammering lines that are still being
+//    written (polling the data itself was 2-3x slower), never a proof of visibility.
+// Every wait is bounded (about a second of SM clocks) and ends in an error word.
 // ════════════════════════════════════════════════════════════════════════════
 constexpr size_t kActLLWords = (size_t)(kMaxK + 1) * kI + 8;
 constexpr int kMaxB3Items = 32;   // ceil((K + 1) * I / grid) gate/up row pairs incl. the shared expert
@@ -716,47 +724,9 @@ struct __align__(128) DecodeSmem3 {
     int flag;
     uint64_t bar_h;
     uint64_t bar_b;   // gate/up slices landed
-    uint64_t bar_c;   // down slices and the next router's slice landed
     LayerDev tab[kMaxDecLayers];  // this launch's rows of the layer table
 };
 static_assert(sizeof(DecodeSmem3) <= 227 * 1024, "decode staging exceeds shared memory");
-
-// Grid barrier on per-CTA flag words.  Every CTA publishes `value`; warp 0 polls until all
-// flags have reached it (wrap-safe signed comparison).  Bounded: gives up after about a second.
-__device__ __forceinline__ bool flag_barrier(unsigned int* flags, unsigned int value, int G, unsigned int* err,
-                                             DecodeSmem3* sm) {
-    asm volatile("fence.proxy.async;" ::: "memory");
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
-        if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(value) : "memory");
-        const long long t0 = clock64();
-        int ok = 1;
-        for (uint32_t it = 0;; ++it) {
-            int done = 1;
-            for (int i = lane; i < G; i += 32) {
-                unsigned int v;
-                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
-                done &= ((int)(v - value) >= 0);
-            }
-            if (__all_sync(0xffffffffu, done)) break;
-            if ((it & 31u) == 31u) {
-                unsigned int e;
-                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(e) : "l"(err) : "memory");
-                if (__any_sync(0xffffffffu, e != 0u || clock64() - t0 > kWaitCycles)) { ok = 0; break; }
-            }
-        }
-        // acquire side: orders the relaxed flag reads before everything after the barrier
-        asm volatile("fence.acq_rel.gpu;" ::: "memory");
-        if (lane == 0) {
-            if (!ok) atomicExch(err, 2u);
-            sm->flag = ok;
-            asm volatile("fence.proxy.async;" ::: "memory");
-        }
-    }
-    __syncthreads();
-    return sm->flag != 0;
-}
 
 // gate/up rows of item j (slot m = item / I: the m-th chosen expert, or the shared expert for m == K)
 __device__ __forceinline__ void prefetch_B3_warp(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
@@ -798,9 +768,7 @@ __device__ __forceinline__ int router_t_stride(int E) { return (E + 7) & ~7; }  
 // touched): twelve bulk copies, issued by twelve different threads, each announcing its own
 // bytes on the mbarrier (which counts kBCopies arrivals per phase).
 constexpr bool kBulk = true;    // gate/up slices by bulk copy
-constexpr bool kBulkC = false;  // down weight slices and the router slice by bulk copy as well
 constexpr int kBCopies = 12;
-constexpr int kCCopies = (kMaxK + 1) + 1;
 
 __device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
                                             int i0, int nb, int K, int q) {
@@ -822,46 +790,6 @@ __device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly,
     } else {
         mbar_expect_tx(&sm->bar_b, 0u);
     }
-}
-
-// Down rows [r0, r0 + nc) of matrix q (weights only: the scale and bias rows are 16 bytes each
-// and go through per-thread copies, bulk copies that small cost more than they move) and, as
-// copy number kCCopies - 1, the next layer's slice of the transposed router.
-__device__ __forceinline__ void bulk_C_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
-                                            const void* next_router_t, bool next_bf16, int r0, int nc, int E, int K, int q) {
-    const void* src = nullptr;
-    void* dst = nullptr;
-    uint32_t bytes = 0;
-    if (q == kCCopies - 1) {
-        if (next_router_t) {
-            const size_t row_bytes = (size_t)router_t_stride(E) * (next_bf16 ? 2 : 4);
-            src = reinterpret_cast<const uint8_t*>(next_router_t) + (size_t)r0 * row_bytes;
-            dst = sm->wt;
-            bytes = (uint32_t)(nc * row_bytes);
-        }
-    } else {
-        const int m = q;
-        if (m <= K) {
-            const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-            src = ex + L.down_w + (size_t)r0 * (kI / 2);
-            dst = sm->c_w[m][0];
-            bytes = (uint32_t)nc * (kI / 2);
-        }
-    }
-    mbar_expect_tx(&sm->bar_c, bytes);
-    if (bytes) bulk_g2s(dst, src, bytes, &sm->bar_c);
-}
-
-// scale and bias rows of the down slices: one 16-byte piece per thread
-__device__ __forceinline__ void prefetch_C_scales(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
-                                                  int r0, int nc, int K, int tid) {
-    const int n = (K + 1) * nc * 2;
-    for (int q = tid; q < n; q += kDecThreads) {
-        const int a = q & 1, mj = q >> 1, m = mj / nc, j = mj - m * nc;
-        const uint8_t* ex = (m < K) ? ly.experts + (size_t)sm->topi[m] * L.expert_size : ly.shared;
-        cp16(a ? sm->c_b[m][j] : sm->c_s[m][j], ex + (a ? L.down_b : L.down_s) + (size_t)(r0 + j) * (kI / kGroup) * 2);
-    }
-    cp_commit();
 }
 
 // rows [r0, r0 + nc) of a layer's transposed router (contiguous: nc * E elements), all threads
@@ -1049,42 +977,6 @@ __device__ __forceinline__ void stage_from_regs(DecodeSmem3* sm, const uint16_t*
     __syncthreads();
 }
 
-// stage_norm in two halves, so that other work can run while h is in flight
-__device__ __forceinline__ void stage_issue(DecodeSmem3* sm, const float* h) {
-    if (threadIdx.x == 0) {
-        mbar_expect_tx(&sm->bar_h, kH * 4u);
-        bulk_g2s(sm->raw, h, kH * 4u, &sm->bar_h);
-    }
-}
-__device__ __forceinline__ bool stage_finish(DecodeSmem3* sm, const uint16_t* norm_w, uint32_t parity) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + tid);
-    if (!__syncthreads_and(mbar_wait(&sm->bar_h, parity) ? 1 : 0)) return false;
-    const float4 v = reinterpret_cast<const float4*>(sm->raw)[tid];
-    float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-    if (lane == 0) sm->red[warp] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kDecWarps; ++i) tot += sm->red[i];
-    const float inv_rms = 1.0f / sqrtf(tot / (float)kH + 1e-6f);
-    if (tid == 0) sm->inv_rms = inv_rms;
-    float4 o;
-    o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
-    o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
-    o.z = v.z * inv_rms * __uint_as_float(wb.y << 16);
-    o.w = v.w * inv_rms * __uint_as_float(wb.y & 0xFFFF0000u);
-    const int c = tid >> 3, j = tid & 7;
-    stage_digits(sm->xq, sm->xdl, kChH, c, j, o);
-    float s = (o.x + o.y) + (o.z + o.w);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    if (j == 0) sm->sumx[c] = s;
-    __syncthreads();
-    return true;
-}
-
 // route_cta rearranged for latency.  Ranks are found with warp votes instead of per-thread
 // loops: the rank of a value among 32 is the population count of one ballot.  The candidate
 // threshold comes from the maxima of 16-expert groups (32 of them, one per lane): warp w ranks
@@ -1193,7 +1085,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
     if (tid == 0) {
         mbar_init(&sm->bar_h, 1);
         mbar_init(&sm->bar_b, kBCopies);
-        mbar_init(&sm->bar_c, kCCopies);
         mbar_fence_init();
     }
     {
@@ -1346,14 +1237,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         cp_wait<0>();  // this warp's gate/up rows (and the gate-score row) landed
         if (kBulk) landed = mbar_wait(&sm->bar_b, wpar) ? 1 : 0;
         __syncwarp();
-        // the gate/up slices are in: now request what the down phase needs, to stream in during the arithmetic
-        if (kBulk && kBulkC) {
-            if (lane == 1 && warp < kCCopies) {
-                const LayerDev& nx = sm->tab[has_next ? rel + 1 : rel];
-                bulk_C_copy(sm, ly, L, has_next ? nx.router_t : nullptr, nx.router_bf16 != nullptr, r0, nc, E, K, warp);
-            }
-            prefetch_C_scales(sm, ly, L, r0, nc, K, tid);
-        }
         PROF3(4);
         {
             bool sg_done = !sg_here;
@@ -1390,14 +1273,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.hint), "l"(1ull) : "memory");
         // down rows and the next router's slice: requested after the gate/up arithmetic, so that their
         // issue (which stalls while the load queues are full) does not delay it
-        if (!kBulkC) {
-            prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
-            if (has_next) {
-                const LayerDev& nx = sm->tab[rel + 1];
-                prefetch_wt(sm, nx.router_t, nx.router_bf16 != nullptr, r0, nc, E, tid);
-            } else {
-                cp_commit();  // keep the group count per layer fixed
-            }
+        prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
+        if (has_next) {
+            const LayerDev& nx = sm->tab[rel + 1];
+            prefetch_wt(sm, nx.router_t, nx.router_bf16 != nullptr, r0, nc, E, tid);
+        } else {
+            cp_commit();  // keep the group count per layer fixed
         }
         PROF3(5);
         DBG(0);
@@ -1483,8 +1364,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             if (sg_reader) sm->topw[K] = 1.0f / (1.0f + expf(-__uint_as_float((unsigned int)qs)));
             DBG(1);
             PROF3(6);
-            if (kBulkC) ok &= mbar_wait(&sm->bar_c, wpar) ? 1 : 0;  // down rows and the next router's slice landed
-            else cp_wait<1>();                                       // this warp's down rows landed
+            cp_wait<1>();  // this warp's down rows landed (the next router's slice may still be in flight)
             wpar ^= 1u;
             if (!__syncthreads_and(ok)) {
                 if (tid == 0) atomicExch(p.err, 4u);
