@@ -24,7 +24,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-NCU_DRAM_BYTES_PER_LAYER = 17.32e6  # (68.00 MB read + 1.26 MB written) / 4 layers
+NCU_DRAM_BYTES_PER_LAYER = 17.24e6  # (68.00 MB read + 0.97 MB written) / 4 layers
 N_ROTATE = 64  # distinct input tokens cycled through, so routing differs from step to step
 
 
