@@ -14,6 +14,23 @@
 
 namespace moe {
 
+// Division of a 31-bit unsigned number by a run-time constant without a divide:
+// q = (umulhi(n, mul) + n) >> shift, with shift = ceil(log2 d) and mul = floor(2^32 (2^shift - d) / d) + 1
+// (Granlund-Montgomery; exact for n < 2^31, where the sum cannot overflow).
+struct FastDiv {
+    uint32_t mul, shift, d;
+};
+static FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f{};
+    f.d = d;
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    f.shift = s;
+    f.mul = (uint32_t)((((1ull << s) - d) << 32) / d) + 1u;
+    return f;
+}
+__device__ __forceinline__ uint32_t fdiv(uint32_t n, const FastDiv& f) { return (__umulhi(n, f.mul) + n) >> f.shift; }
+
 struct PackJob {
     const void* src;         // [n_rows, cols], rows contiguous
     int64_t n_rows;          // total source rows
@@ -24,6 +41,7 @@ struct PackJob {
     uint8_t* w_base[2];      // destination of matrix m of unit 0
     uint8_t* s_base[2];
     uint8_t* b_base[2];
+    FastDiv div_gpr, div_unit, div_mat;  // by groups per row, rows per unit, rows per matrix (filled at launch)
 };
 
 constexpr int kPackUnroll = 4;  // groups per 8-lane team: their loads are all issued before the first use
@@ -45,7 +63,7 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
     for (int u = 0; u < kPackUnroll; ++u) {
         const uint32_t gi = team + u * teams;
         if (gi < total_groups) {
-            const uint32_t row = gi / groups_per_row, g = gi - row * groups_per_row;
+            const uint32_t row = fdiv(gi, job.div_gpr), g = gi - row * groups_per_row;
             if (kSrcBf16) {
                 raw[u][0] = ld_stream_u4(reinterpret_cast<const uint16_t*>(job.src) + (size_t)row * job.cols + g * kGroup + p * 8);
             } else {
@@ -55,51 +73,69 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
             }
         }
     }
+    // pass 1: widen, and reduce min / max over each group (8 lanes, three xor-shuffles)
+    float v[kPackUnroll][8], gmin[kPackUnroll], gmax[kPackUnroll];
 #pragma unroll
     for (int u = 0; u < kPackUnroll; ++u) {
-        const uint32_t gi = team + u * teams;
-        if (gi >= total_groups) continue;
-        const uint32_t row = gi / groups_per_row;
-        const int g = (int)(gi - row * groups_per_row);
-        float v[8];
         if (kSrcBf16) {
             const uint32_t r[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                v[2 * i] = __uint_as_float(r[i] << 16);            // bf16 -> f32 is exact
-                v[2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
+                v[u][2 * i] = __uint_as_float(r[i] << 16);            // bf16 -> f32 is exact
+                v[u][2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
             }
         } else {
             const uint4 a = raw[u][0], b = raw[u][kSrcBf16 ? 0 : 1];
-            v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
-            v[4] = __uint_as_float(b.x); v[5] = __uint_as_float(b.y); v[6] = __uint_as_float(b.z); v[7] = __uint_as_float(b.w);
+            v[u][0] = __uint_as_float(a.x); v[u][1] = __uint_as_float(a.y); v[u][2] = __uint_as_float(a.z); v[u][3] = __uint_as_float(a.w);
+            v[u][4] = __uint_as_float(b.x); v[u][5] = __uint_as_float(b.y); v[u][6] = __uint_as_float(b.z); v[u][7] = __uint_as_float(b.w);
         }
-        float vmin = v[0], vmax = v[0];
+        float vmin = v[u][0], vmax = v[u][0];
 #pragma unroll
         for (int i = 1; i < 8; ++i) {
-            vmin = fminf(vmin, v[i]);
-            vmax = fmaxf(vmax, v[i]);
+            vmin = fminf(vmin, v[u][i]);
+            vmax = fmaxf(vmax, v[u][i]);
         }
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
             vmin = fminf(vmin, __shfl_xor_sync(gmask, vmin, o));
             vmax = fmaxf(vmax, __shfl_xor_sync(gmask, vmax, o));
         }
-        if (vmax == vmin) vmax = __fadd_rn(vmin, 1.0f);
-        const float fscale = __fdiv_rn(__fsub_rn(vmax, vmin), 15.0f);
-        const float fbias = vmin;
-        const float inv_scale = __fdiv_rn(1.0f, fscale);
+        gmin[u] = vmin;
+        gmax[u] = vmax;
+    }
+    // pass 2: the two IEEE divisions of a group are done once, by lane u of its team (lane u takes group u),
+    // and handed to the other seven lanes by shuffle: a division costs a dozen instructions
+    static_assert(kPackUnroll <= 8, "one lane of the team per unrolled group");
+    float my_min = gmin[0], my_max = gmax[0];
+#pragma unroll
+    for (int u = 1; u < kPackUnroll; ++u)
+        if (p == u) { my_min = gmin[u]; my_max = gmax[u]; }
+    if (my_max == my_min) my_max = __fadd_rn(my_min, 1.0f);
+    const float my_scale = __fdiv_rn(__fsub_rn(my_max, my_min), 15.0f);
+    const float my_inv = __fdiv_rn(1.0f, my_scale);
+    const int team_lane0 = threadIdx.x & 24;  // first lane of this team inside the warp
+    // pass 3: quantise and store
+#pragma unroll
+    for (int u = 0; u < kPackUnroll; ++u) {
+        const float fscale = __shfl_sync(gmask, my_scale, team_lane0 + u);
+        const float inv_scale = __shfl_sync(gmask, my_inv, team_lane0 + u);
+        const uint32_t gi = team + u * teams;
+        if (gi >= total_groups) continue;
+        const uint32_t row = fdiv(gi, job.div_gpr);
+        const int g = (int)(gi - row * groups_per_row);
+        const float fbias = gmin[u];
         uint32_t word = 0;
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
-            const float t = __fadd_rn(__fmul_rn(__fsub_rn(v[n], fbias), inv_scale), 0.5f);
-            int q = __float2int_rz(t);  // truncates, saturates, NaN -> 0: Rust `as i32`
-            q = min(max(q, 0), 15);
-            word |= ((uint32_t)q) << (n * 4);
+            const float t = __fadd_rn(__fmul_rn(__fsub_rn(v[u][n], fbias), inv_scale), 0.5f);
+            // Rust `as i32` truncates, saturates and maps NaN to 0, then clamp(0, 15): the unsigned conversion
+            // already sends everything below zero (and NaN) to 0, so one minimum remains
+            const uint32_t q = min(__float2uint_rz(t), 15u);
+            word |= q << (n * 4);
         }
-        const uint32_t unit = row / (uint32_t)job.rows_per_unit;
+        const uint32_t unit = fdiv(row, job.div_unit);
         const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
-        const int m = (int)(rr / (uint32_t)job.rows_per_mat);
+        const int m = (int)fdiv(rr, job.div_mat);
         const int64_t r = rr - (uint32_t)m * (uint32_t)job.rows_per_mat;
         const int64_t uoff = (int64_t)unit * job.unit_stride;
         // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
@@ -154,9 +190,15 @@ static int run_pack(moe_engine* e, const PackJob& job, int src_dtype) {
     return MOE_OK;
 }
 
-static int run_pack_one(moe_engine* e, const PackJob& job, int src_dtype) {
+static int run_pack_one(moe_engine* e, const PackJob& job_in, int src_dtype) {
+    PackJob job = job_in;
     const int64_t total_groups = job.n_rows * (job.cols / kGroup);
     if (total_groups == 0) return MOE_OK;
+    MOE_REQUIRE(job.rows_per_unit < (1ll << 31) && job.rows_per_mat < (1ll << 31) && job.rows_per_unit > 0 && job.rows_per_mat > 0,
+                "pack: unit of %lld rows is too large", (long long)job.rows_per_unit);
+    job.div_gpr = make_fastdiv((uint32_t)(job.cols / kGroup));
+    job.div_unit = make_fastdiv((uint32_t)job.rows_per_unit);
+    job.div_mat = make_fastdiv((uint32_t)job.rows_per_mat);
     const int64_t threads = (total_groups + kPackUnroll - 1) / kPackUnroll * 8;
     const int64_t blocks = (threads + 255) / 256;
     MOE_REQUIRE(blocks < (1ll << 31), "pack: too many rows for one launch (%lld blocks)", (long long)blocks);
