@@ -51,8 +51,9 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
     // 32-bit index arithmetic: the host splits jobs so that a launch covers fewer than 2^31 groups
     const uint32_t groups_per_row = (uint32_t)(job.cols / kGroup);
     const uint32_t total_groups = (uint32_t)job.n_rows * groups_per_row;
-    const uint32_t teams = gridDim.x * (blockDim.x >> 3);
+    // a team of 8 lanes takes kPackUnroll consecutive groups: gi0 .. gi0 + kPackUnroll - 1
     const uint32_t team = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    const uint32_t gi0 = team * kPackUnroll;
     const int p = threadIdx.x & 7;
     // Lanes of one team are 8-aligned inside the warp and take the same branches,
     // so the shuffle mask names just this team's lanes.
@@ -61,13 +62,13 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
     uint4 raw[kPackUnroll][kSrcBf16 ? 1 : 2];
 #pragma unroll
     for (int u = 0; u < kPackUnroll; ++u) {
-        const uint32_t gi = team + u * teams;
+        const uint32_t gi = gi0 + u;
         if (gi < total_groups) {
-            const uint32_t row = fdiv(gi, job.div_gpr), g = gi - row * groups_per_row;
+            // source rows are contiguous, so group gi starts at element gi * 64
             if (kSrcBf16) {
-                raw[u][0] = ld_stream_u4(reinterpret_cast<const uint16_t*>(job.src) + (size_t)row * job.cols + g * kGroup + p * 8);
+                raw[u][0] = ld_stream_u4(reinterpret_cast<const uint16_t*>(job.src) + (size_t)gi * kGroup + p * 8);
             } else {
-                const float* sp = reinterpret_cast<const float*>(job.src) + (size_t)row * job.cols + g * kGroup + p * 8;
+                const float* sp = reinterpret_cast<const float*>(job.src) + (size_t)gi * kGroup + p * 8;
                 raw[u][0] = ld_stream_u4(sp);
                 raw[u][kSrcBf16 ? 0 : 1] = ld_stream_u4(sp + 4);
             }
@@ -114,15 +115,16 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
     const float my_scale = __fdiv_rn(__fsub_rn(my_max, my_min), 15.0f);
     const float my_inv = __fdiv_rn(1.0f, my_scale);
     const int team_lane0 = threadIdx.x & 24;  // first lane of this team inside the warp
-    // pass 3: quantise and store
+    // pass 3: quantise and store.  (row, group in row) of the first group by division, of the others by stepping.
+    uint32_t row = fdiv(gi0, job.div_gpr);
+    uint32_t g = gi0 - row * groups_per_row;
 #pragma unroll
     for (int u = 0; u < kPackUnroll; ++u) {
         const float fscale = __shfl_sync(gmask, my_scale, team_lane0 + u);
         const float inv_scale = __shfl_sync(gmask, my_inv, team_lane0 + u);
-        const uint32_t gi = team + u * teams;
+        if (u > 0 && ++g == groups_per_row) { g = 0; ++row; }
+        const uint32_t gi = gi0 + u;
         if (gi >= total_groups) continue;
-        const uint32_t row = fdiv(gi, job.div_gpr);
-        const int g = (int)(gi - row * groups_per_row);
         const float fbias = gmin[u];
         uint32_t word = 0;
 #pragma unroll
@@ -136,15 +138,18 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
         const uint32_t unit = fdiv(row, job.div_unit);
         const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
         const int m = (int)fdiv(rr, job.div_mat);
-        const int64_t r = rr - (uint32_t)m * (uint32_t)job.rows_per_mat;
+        const uint32_t r = rr - (uint32_t)m * (uint32_t)job.rows_per_mat;
         const int64_t uoff = (int64_t)unit * job.unit_stride;
         // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
         uint8_t* const wb = m ? job.w_base[1] : job.w_base[0];
         uint8_t* const sb = m ? job.s_base[1] : job.s_base[0];
         uint8_t* const bb = m ? job.b_base[1] : job.b_base[0];
-        reinterpret_cast<uint32_t*>(wb + uoff)[r * (job.cols / 8) + g * 8 + p] = word;
-        if (p == 0) reinterpret_cast<uint16_t*>(sb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fscale);
-        if (p == 1) reinterpret_cast<uint16_t*>(bb + uoff)[r * groups_per_row + g] = f32_to_bf16_ref(fbias);
+        const uint64_t gq = (uint64_t)r * groups_per_row + g;  // group index inside the destination matrix
+        reinterpret_cast<uint32_t*>(wb + uoff)[gq * 8 + p] = word;
+        // lane 0 writes the scale, lane 1 the bias: one conversion and one store per lane
+        const float sv = p == 0 ? fscale : fbias;
+        uint8_t* const dst = p == 0 ? sb : bb;
+        if (p < 2) reinterpret_cast<uint16_t*>(dst + uoff)[gq] = f32_to_bf16_ref(sv);
     }
 }
 
