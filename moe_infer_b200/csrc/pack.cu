@@ -118,11 +118,27 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
     // pass 3: quantise and store.  (row, group in row) of the first group by division, of the others by stepping.
     uint32_t row = fdiv(gi0, job.div_gpr);
     uint32_t g = gi0 - row * groups_per_row;
+    // where a row's groups go: recomputed only when the row changes
+    uint8_t *wdst = nullptr, *sdst = nullptr, *bdst = nullptr;  // destination matrices of this row, at its unit
+    uint64_t gq0 = 0;                                            // index of the row's first group inside them
+    auto locate = [&]() {
+        const uint32_t unit = fdiv(row, job.div_unit);
+        const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
+        const uint32_t m = fdiv(rr, job.div_mat);
+        const uint32_t r = rr - m * (uint32_t)job.rows_per_mat;
+        const int64_t uoff = (int64_t)unit * job.unit_stride;
+        // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
+        wdst = (m ? job.w_base[1] : job.w_base[0]) + uoff;
+        sdst = (m ? job.s_base[1] : job.s_base[0]) + uoff;
+        bdst = (m ? job.b_base[1] : job.b_base[0]) + uoff;
+        gq0 = (uint64_t)r * groups_per_row;
+    };
+    locate();
 #pragma unroll
     for (int u = 0; u < kPackUnroll; ++u) {
         const float fscale = __shfl_sync(gmask, my_scale, team_lane0 + u);
         const float inv_scale = __shfl_sync(gmask, my_inv, team_lane0 + u);
-        if (u > 0 && ++g == groups_per_row) { g = 0; ++row; }
+        if (u > 0 && ++g == groups_per_row) { g = 0; ++row; locate(); }
         const uint32_t gi = gi0 + u;
         if (gi >= total_groups) continue;
         const float fbias = gmin[u];
@@ -133,23 +149,14 @@ __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
             // Rust `as i32` truncates, saturates and maps NaN to 0, then clamp(0, 15): the unsigned conversion
             // already sends everything below zero (and NaN) to 0, so one minimum remains
             const uint32_t q = min(__float2uint_rz(t), 15u);
-            word |= q << (n * 4);
+            word = q * (1u << (n * 4)) + word;  // multiply-add (the nibbles do not overlap): one instruction, off the ALU pipe
         }
-        const uint32_t unit = fdiv(row, job.div_unit);
-        const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
-        const int m = (int)fdiv(rr, job.div_mat);
-        const uint32_t r = rr - (uint32_t)m * (uint32_t)job.rows_per_mat;
-        const int64_t uoff = (int64_t)unit * job.unit_stride;
-        // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
-        uint8_t* const wb = m ? job.w_base[1] : job.w_base[0];
-        uint8_t* const sb = m ? job.s_base[1] : job.s_base[0];
-        uint8_t* const bb = m ? job.b_base[1] : job.b_base[0];
-        const uint64_t gq = (uint64_t)r * groups_per_row + g;  // group index inside the destination matrix
-        reinterpret_cast<uint32_t*>(wb + uoff)[gq * 8 + p] = word;
+        const uint64_t gq = gq0 + g;  // group index inside the destination matrix
+        reinterpret_cast<uint32_t*>(wdst)[gq * 8 + p] = word;
         // lane 0 writes the scale, lane 1 the bias: one conversion and one store per lane
         const float sv = p == 0 ? fscale : fbias;
-        uint8_t* const dst = p == 0 ? sb : bb;
-        if (p < 2) reinterpret_cast<uint16_t*>(dst + uoff)[gq] = f32_to_bf16_ref(sv);
+        uint8_t* const dst = p == 0 ? sdst : bdst;
+        if (p < 2) reinterpret_cast<uint16_t*>(dst)[gq] = f32_to_bf16_ref(sv);
     }
 }
 
