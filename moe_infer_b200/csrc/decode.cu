@@ -838,74 +838,6 @@ __device__ __forceinline__ void ld_ll2(const unsigned long long* ptr, unsigned l
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
 }
 
-// ─── integer dot products ───────────────────────────────────────────────────
-// The 4-bit weights are small integers, so the dot product of a row with a vector is done in
-// integer arithmetic: every 32-element chunk of the vector is written as X * delta with
-// integers |X| <= 2^22 (delta = chunk maximum / 2^22), X is split into three signed base-256
-// digits, and dp4a (four byte products summed into 32 bits) multiplies them with the nibbles,
-// four at a time.  Sums are exact; the only rounding is that of x to 23 bits relative to its
-// chunk's maximum, the same order as the f32 mantissa the reference multiplies with.
-// Byte order: the nibbles of a weight word are split as (w & 0x0F0F0F0F) = columns 0,2,4,6 and
-// ((w >> 4) & 0x0F0F0F0F) = columns 1,3,5,7, so digit words are stored "even" and "odd".
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-// One thread's float4 (elements 4 j .. 4 j + 3 of chunk c; the 8 threads of a chunk are
-// consecutive lanes): writes its digits into planes[(p * 2 + odd) * n_chunks + c] and, from
-// lane j == 0, the chunk's delta.
-__device__ __forceinline__ void stage_digits(uint4* planes, float* deltas, int n_chunks, int c, int j, const float4& o) {
-    float mx = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-    const float inv = mx > 0.0f ? 4194304.0f / mx : 0.0f;
-    if (j == 0) deltas[c] = mx * (1.0f / 4194304.0f);
-    const int X[4] = {__float2int_rn(o.x * inv), __float2int_rn(o.y * inv), __float2int_rn(o.z * inv), __float2int_rn(o.w * inv)};
-    uint32_t d[3][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int d0 = (X[i] << 24) >> 24;
-        const int X1 = (X[i] - d0) >> 8;
-        const int d1 = (X1 << 24) >> 24;
-        const int d2 = (X1 - d1) >> 8;
-        d[0][i] = (uint32_t)d0 & 0xFFu;
-        d[1][i] = (uint32_t)d1 & 0xFFu;
-        d[2][i] = (uint32_t)d2 & 0xFFu;
-    }
-    // this thread holds columns (4 half .. 4 half + 3) of word k: two even and two odd bytes
-    const int k = j >> 1, half = j & 1;
-#pragma unroll
-    for (int p = 0; p < 3; ++p) {
-        const uint16_t ev = (uint16_t)(d[p][0] | (d[p][2] << 8));
-        const uint16_t od = (uint16_t)(d[p][1] | (d[p][3] << 8));
-        uint16_t* e16 = reinterpret_cast<uint16_t*>(planes + (size_t)(p * 2 + 0) * n_chunks + c);
-        uint16_t* o16 = reinterpret_cast<uint16_t*>(planes + (size_t)(p * 2 + 1) * n_chunks + c);
-        e16[k * 2 + half] = ev;
-        o16[k * 2 + half] = od;
-    }
-}
-
-// sum over the 32 nibbles of q of nibble * X, as a float (X = the chunk's integers)
-__device__ __forceinline__ float dot32_int(const uint4& q, const uint4 (&xe)[3], const uint4 (&xo)[3]) {
-    int a[3] = {0, 0, 0};
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const uint32_t lo = w[k] & 0x0F0F0F0Fu, hi = (w[k] >> 4) & 0x0F0F0F0Fu;
-#pragma unroll
-        for (int p = 0; p < 3; ++p) {
-            const uint32_t e = k == 0 ? xe[p].x : k == 1 ? xe[p].y : k == 2 ? xe[p].z : xe[p].w;
-            const uint32_t o = k == 0 ? xo[p].x : k == 1 ? xo[p].y : k == 2 ? xo[p].z : xo[p].w;
-            a[p] = dp4a_us(lo, e, a[p]);
-            a[p] = dp4a_us(hi, o, a[p]);
-        }
-    }
-    return fmaf((float)a[2], 65536.0f, fmaf((float)a[1], 256.0f, (float)a[0]));
-}
-
 // Dot products of NR 4-bit rows of length kH with the staged x (integer path).
 template <int NR>
 __device__ __forceinline__ void rows_dot_q(const DecodeSmem3* sm, const uint4* const (&w)[NR],
