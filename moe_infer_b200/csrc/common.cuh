@@ -100,7 +100,7 @@ struct BatchWork {
 // token rows travel through buffers the ranks map from one another (CUDA IPC).
 constexpr int kEpMaxWorld = 8;
 struct EpSym {                    // layout of the buffer every rank exports (byte offsets)
-    size_t flags, counts, meta, xrecv, oback, total;
+    size_t flags, counts, meta, xmap, memb, mwt, xrecv, oback, total;
 };
 struct EpState {
     bool ready = false;
@@ -117,9 +117,9 @@ struct EpState {
     int32_t* n_tiles = nullptr;
     int32_t* base_send = nullptr;           // [E] first slot of my rows of expert e at its owner
     int32_t* cursor = nullptr;              // [E]
-    int32_t* ident = nullptr;               // [slots_cap + cap] identity map
     int32_t* total_recv = nullptr;          // rows received this layer
     unsigned int* done = nullptr;           // blocks finished (scatter / return kernels), rewound by the last one
+    uint8_t* lead_mask = nullptr;           // [cap] bit k: (token, k) is the first of the token's experts on its GPU
     int max_tiles = 0;
 };
 

@@ -29,7 +29,13 @@ int moe_ep_export(moe_engine_t* e, int rank, int world, int32_t max_tokens_per_r
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
     ep.sym.flags = take(kEpMaxWorld * 64);
     ep.sym.counts = take((size_t)world * d.num_experts * 4);
-    ep.sym.meta = take((size_t)ep.slots_cap * 8);
+    // per received row: who sent it and where its result goes (16 B); which received row holds its
+    // activations (a token is sent once per GPU, its experts there share the row); and, for the first
+    // ("leader") row of a (token, GPU) pair, the rows and weights to combine before returning
+    ep.sym.meta = take((size_t)ep.slots_cap * 16);
+    ep.sym.xmap = take(((size_t)ep.slots_cap + ep.cap) * 4);
+    ep.sym.memb = take((size_t)ep.slots_cap * 8 * 4);
+    ep.sym.mwt = take((size_t)ep.slots_cap * 8 * 4);
     ep.sym.xrecv = take(((size_t)ep.slots_cap + ep.cap) * d.hidden * 2);
     ep.sym.oback = take((size_t)ep.cap * d.top_k * d.hidden * 2);
     ep.sym.total = off;

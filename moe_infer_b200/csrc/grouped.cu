@@ -684,7 +684,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                 const int q = tid + i * kProdThreads;
                 const int j = q >> 3, c = q & 7;
                 const int jj = j < nt ? j : 0;
-                bsrc[i] = ((MODE == 1) ? p.x + (size_t)__ldg(p.slot_token + s0 + jj) * kBH : p.act + (size_t)(s0 + jj) * kBI) + c * 8;
+                // (the map may have been written by a peer GPU after this kernel started: read it through L2)
+                bsrc[i] = ((MODE == 1) ? p.x + (size_t)__ldcg(p.slot_token + s0 + jj) * kBH : p.act + (size_t)(s0 + jj) * kBI) + c * 8;
                 boff[i] = umma::sw128_offset((uint32_t)j, (uint32_t)c);
             }
             // asynchronous copy of the activation tile of K step kc into activation stage st (rows >= nt zero-filled)
@@ -975,66 +976,128 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* counts_all
     }
 }
 
-// scatter: one warp per (token, k) row, plus one warp per token for the shared expert's local copy.
+// scatter: one warp per token.  A token's activations go once to every GPU that owns at least one of its
+// experts (into the slot of the first such expert, the "leader"); the other experts' slots on that GPU are
+// mapped to the same row.  The leader slot also receives the list of its members and their routing weights,
+// so that the owner can add up the token's expert outputs and send back one row.
 __global__ void __launch_bounds__(256) ep_scatter_kernel(EpPeers peers, EpSym sym, int me, int P, int E, int K, int n,
                                                          const __nv_bfloat16* __restrict__ x,
                                                          const int32_t* __restrict__ topk_idx,
+                                                         const float* __restrict__ topk_w,
                                                          const int32_t* __restrict__ base_send, int32_t* cursor,
-                                                         const int32_t* __restrict__ total_recv, unsigned int* done,
-                                                         unsigned int epoch) {
-    const int w = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+                                                         const int32_t* __restrict__ total_recv, uint8_t* lead_mask,
+                                                         unsigned int* done, unsigned int epoch) {
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int Eloc = E / P;
-    if (w < n * K) {
-        const int t = w / K;
-        const int e = topk_idx[w];
-        const int d = e / Eloc;
-        int slot = 0;
-        if (lane == 0) slot = base_send[e] + atomicAdd(&cursor[e], 1);
-        slot = __shfl_sync(0xffffffffu, slot, 0);
-        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * kBH);
-        uint4* dst = reinterpret_cast<uint4*>(peers.base[d] + sym.xrecv + (size_t)slot * kBH * 2);
-#pragma unroll
-        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
-        if (lane == 0) {
-            int2* meta = reinterpret_cast<int2*>(peers.base[d] + sym.meta);
-            meta[slot] = make_int2(me, w);  // return address: rank and (token * K + k)
+    if (t < n) {
+        int d = -1 - lane, slot = 0;  // lanes beyond K: destinations that match nobody
+        float w = 0.0f;
+        if (lane < K) {
+            const int e = topk_idx[(size_t)t * K + lane];
+            d = e / Eloc;
+            slot = base_send[e] + atomicAdd(&cursor[e], 1);
+            w = topk_w[(size_t)t * K + lane];
         }
-    } else if (w < n * K + n) {
-        const int t = w - n * K;
+        // leader = lowest k with the same destination; rank = position among that destination's experts
+        int leader = lane, rank = 0, cnt = 0;
+        for (int k2 = 0; k2 < K; ++k2) {
+            const int d2 = __shfl_sync(0xffffffffu, d, k2);
+            if (d2 == d) {
+                if (k2 < leader) leader = k2;
+                if (k2 < lane) ++rank;
+                ++cnt;
+            }
+        }
+        const int lslot = __shfl_sync(0xffffffffu, slot, leader);
+        const bool is_leader = lane < K && leader == lane;
+        if (lane < K) {
+            uint8_t* pb = peers.base[d];
+            reinterpret_cast<int32_t*>(pb + sym.xmap)[slot] = lslot;
+            // return address: rank and (token * K + leader's k); member count for leaders, 0 otherwise
+            reinterpret_cast<int4*>(pb + sym.meta)[slot] = make_int4(me, t * K + leader, is_leader ? cnt : 0, 0);
+            reinterpret_cast<int32_t*>(pb + sym.memb)[(size_t)lslot * kMaxK + rank] = slot;
+            reinterpret_cast<float*>(pb + sym.mwt)[(size_t)lslot * kMaxK + rank] = w;
+        }
+        const unsigned lmask = __ballot_sync(0xffffffffu, is_leader);
+        if (lane == 0) lead_mask[t] = (uint8_t)lmask;
+        // the row: read once, stored once per destination and once locally for the shared expert
+        uint4 r[kBH * 2 / 16 / 32];
         const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * kBH);
-        uint4* dst = reinterpret_cast<uint4*>(peers.base[me] + sym.xrecv + (size_t)(*total_recv + t) * kBH * 2);
 #pragma unroll
-        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
+        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) r[i] = src[lane + 32 * i];
+        for (unsigned m = lmask; m; m &= m - 1) {
+            const int k = __ffs(m) - 1;
+            const int dk = __shfl_sync(0xffffffffu, d, k), sk = __shfl_sync(0xffffffffu, slot, k);
+            uint4* dst = reinterpret_cast<uint4*>(peers.base[dk] + sym.xrecv + (size_t)sk * kBH * 2);
+#pragma unroll
+            for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = r[i];
+        }
+        const int ls = *total_recv + t;
+        uint4* dst = reinterpret_cast<uint4*>(peers.base[me] + sym.xrecv + (size_t)ls * kBH * 2);
+#pragma unroll
+        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = r[i];
+        if (lane == 0) reinterpret_cast<int32_t*>(peers.base[me] + sym.xmap)[ls] = ls;
     }
     // the last block to finish tells every peer that this rank's rows are in place
     if (ep_last_block(done) && threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
-// return: one warp per received row; the output row goes back to the rank that sent the input row.
+// return: one warp per received row; a leader row adds up the weighted outputs of its members (in the order
+// of the sender's expert list) and sends the sum to the rank the token came from.
 __global__ void __launch_bounds__(256) ep_return_kernel(EpPeers peers, EpSym sym, int me, int P,
                                                         const __nv_bfloat16* __restrict__ o,
                                                         const int32_t* __restrict__ total_recv, unsigned int* done,
                                                         unsigned int epoch) {
     const int lane = threadIdx.x & 31;
     const int total = *total_recv;
-    const int2* meta = reinterpret_cast<const int2*>(peers.base[me] + sym.meta);
+    const int4* meta = reinterpret_cast<const int4*>(peers.base[me] + sym.meta);
+    const int32_t* memb = reinterpret_cast<const int32_t*>(peers.base[me] + sym.memb);
+    const float* mwt = reinterpret_cast<const float*>(peers.base[me] + sym.mwt);
+    constexpr int kPer = kBH * 2 / 16 / 32;  // 16-byte pieces of a row per lane
     for (int s = blockIdx.x * 8 + (threadIdx.x >> 5); s < total; s += gridDim.x * 8) {
-        const int2 m = meta[s];
-        const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)s * kBH);
+        const int4 m = __ldcg(meta + s);
+        if (m.z <= 0) continue;  // not a leader: its output travels inside its leader's sum
+        float acc[kPer * 8];
+#pragma unroll
+        for (int i = 0; i < kPer * 8; ++i) acc[i] = 0.0f;
+        for (int j = 0; j < m.z; ++j) {
+            const int sj = __ldcg(memb + (size_t)s * kMaxK + j);
+            const float wj = __ldcg(mwt + (size_t)s * kMaxK + j);
+            const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)sj * kBH);
+#pragma unroll
+            for (int i = 0; i < kPer; ++i) {
+                const uint4 q = src[lane + 32 * i];
+                const uint32_t rr[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    acc[i * 8 + 2 * c] = fmaf(wj, __uint_as_float(rr[c] << 16), acc[i * 8 + 2 * c]);
+                    acc[i * 8 + 2 * c + 1] = fmaf(wj, __uint_as_float(rr[c] & 0xFFFF0000u), acc[i * 8 + 2 * c + 1]);
+                }
+            }
+        }
         uint4* dst = reinterpret_cast<uint4*>(peers.base[m.x] + sym.oback + (size_t)m.y * kBH * 2);
 #pragma unroll
-        for (int i = 0; i < kBH * 2 / 16 / 32; ++i) dst[lane + 32 * i] = src[lane + 32 * i];
+        for (int i = 0; i < kPer; ++i) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(acc[i * 8 + 2 * c], acc[i * 8 + 2 * c + 1]);
+                pk[c] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            dst[lane + 32 * i] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
     }
     if (ep_last_block(done) && threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
-// combine: moe_combine_residual (reference src/math_util.rs:599-612); routed rows come from the
+// combine: moe_combine_residual (reference src/math_util.rs:599-612); the routed experts' outputs arrive already
+// weighted and summed per owning GPU (one row per leader, see the scatter kernel); routed rows come from the
 // returned buffer in (token, k) order, the shared expert's row from this rank's own output.
 __global__ void __launch_bounds__(256) ep_combine_kernel(const float* __restrict__ h_in, float* __restrict__ h_out,
                                                          int n, int K, const __nv_bfloat16* __restrict__ oback,
                                                          const __nv_bfloat16* __restrict__ o_local,
                                                          const int32_t* __restrict__ total_recv,
-                                                         const float* __restrict__ topk_w,
+                                                         const uint8_t* __restrict__ lead_mask,
                                                          const float* __restrict__ sgate, const uint8_t* local,
                                                          size_t flags_off, int P, unsigned int epoch, unsigned int* err) {
     const int t = blockIdx.x, tid = threadIdx.x;
@@ -1053,17 +1116,14 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const float* __restrict
             dst[2 * i + 1] += w * __uint_as_float(r[i] & 0xFFFF0000u);
         }
     };
-    for (int k = 0; k < K; ++k) add(oback + ((size_t)t * K + k) * kBH, topk_w[(size_t)t * K + k], moe);
+    const unsigned lm = lead_mask[t];
+    for (int k = 0; k < K; ++k)
+        if (lm >> k & 1u) add(oback + ((size_t)t * K + k) * kBH, 1.0f, moe);
     add(o_local + (size_t)(*total_recv + t) * kBH, sgate[t], sh);
     const float hin[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     float4* op = reinterpret_cast<float4*>(h_out + (size_t)t * kBH) + tid * 2;
     op[0] = make_float4(hin[0] + moe[0] + sh[0], hin[1] + moe[1] + sh[1], hin[2] + moe[2] + sh[2], hin[3] + moe[3] + sh[3]);
     op[1] = make_float4(hin[4] + moe[4] + sh[4], hin[5] + moe[5] + sh[5], hin[6] + moe[6] + sh[6], hin[7] + moe[7] + sh[7]);
-}
-
-__global__ void ep_iota_kernel(int32_t* p, int n) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = i;
 }
 
 // ─── host side ──────────────────────────────────────────────────────────────
@@ -1224,16 +1284,15 @@ int ep_alloc_work(moe_engine* e) {
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
     const size_t o_act = take(rows * d.inter * 2), o_o = take(rows * d.hidden * 2), o_tl = take((size_t)ep.max_tiles * 12);
     const size_t o_nt = take(4), o_bs = take((size_t)d.num_experts * 4), o_cu = take((size_t)d.num_experts * 4);
-    const size_t o_id = take(rows * 4), o_tr = take(4), o_dn = take(4);
+    const size_t o_tr = take(4), o_dn = take(4), o_lm = take((size_t)ep.cap);
     MOE_CUDA(cudaMalloc(&ep.work, off));
     ep.done = (unsigned int*)(ep.work + o_dn);
+    ep.lead_mask = ep.work + o_lm;
     MOE_CUDA(cudaMemsetAsync(ep.done, 0, 4, e->stream));
     ep.act = (__nv_bfloat16*)(ep.work + o_act); ep.o = (__nv_bfloat16*)(ep.work + o_o);
     ep.tile_list = (int32_t*)(ep.work + o_tl); ep.n_tiles = (int32_t*)(ep.work + o_nt);
     ep.base_send = (int32_t*)(ep.work + o_bs); ep.cursor = (int32_t*)(ep.work + o_cu);
-    ep.ident = (int32_t*)(ep.work + o_id); ep.total_recv = (int32_t*)(ep.work + o_tr);
-    ep_iota_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, e->stream>>>(ep.ident, (int)rows);
-    MOE_CUDA(cudaGetLastError());
+    ep.total_recv = (int32_t*)(ep.work + o_tr);
     return batch_reserve(e, ep.cap);
 }
 
@@ -1291,15 +1350,15 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
                                        ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);
     EP_MARK("ep_plan_kernel");
     // 2. dispatch (the last block of the scatter publishes the epoch)
-    ep_scatter_kernel<<<(n * K + n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, ep.base_send,
-                                                          ep.cursor, ep.total_recv, ep.done, ++ep.epoch);
+    ep_scatter_kernel<<<(n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, bw.topk_w, ep.base_send,
+                                                  ep.cursor, ep.total_recv, ep.lead_mask, ep.done, ++ep.epoch);
     EP_MARK("ep_scatter_kernel");
     // 3. grouped GEMMs over the received rows (+ shared expert over the local ones); the first one waits for the rows
     GemmParams gp{};
     gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
     gp.x = reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.xrecv);
     gp.act = ep.act; gp.o = ep.o;
-    gp.tile_list = ep.tile_list; gp.n_tiles = ep.n_tiles; gp.slot_token = ep.ident;
+    gp.tile_list = ep.tile_list; gp.n_tiles = ep.n_tiles; gp.slot_token = reinterpret_cast<const int32_t*>(ep.local + ep.sym.xmap);
     gp.err = err;
     gp.ep_local = ep.local; gp.ep_flags = ep.sym.flags; gp.ep_world = P; gp.ep_epoch = ep.epoch;
     grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
@@ -1311,7 +1370,7 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, P, ep.o, ep.total_recv, ep.done, ++ep.epoch);
     EP_MARK("ep_return_kernel");
     ep_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.oback),
-                                         ep.o, ep.total_recv, bw.topk_w, bw.sgate, ep.local, ep.sym.flags, P, ep.epoch, err);
+                                         ep.o, ep.total_recv, ep.lead_mask, bw.sgate, ep.local, ep.sym.flags, P, ep.epoch, err);
     EP_MARK("ep_combine_kernel");
     if (tracing) {
         cudaStreamSynchronize(st);
