@@ -57,9 +57,13 @@ __host__ __device__ __forceinline__ int ipos(int j) { return ((j & 3) << 1) | (j
 __global__ void __launch_bounds__(256) batch_prep_kernel(const float* __restrict__ h_in, int n, LayerDev ly,
                                                          __nv_bfloat16* __restrict__ x_bf,
                                                          __nv_bfloat16* __restrict__ x_mid,
-                                                         __nv_bfloat16* __restrict__ x_lo, float* __restrict__ sgate) {
+                                                         __nv_bfloat16* __restrict__ x_lo, float* __restrict__ sgate,
+                                                         int32_t* __restrict__ counts, int n_counts) {
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float red[8];
+    // the expert histogram of this layer starts from zero (it is filled two kernels later)
+    if (t == 0)
+        for (int i = tid; i < n_counts; i += 256) counts[i] = 0;
     const float4* hp = reinterpret_cast<const float4*>(h_in + (size_t)t * kBH) + tid * 2;
     const float4 a = hp[0], b = hp[1];
     float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -326,6 +330,19 @@ __global__ void __launch_bounds__(256, 1) router_gemm_kernel(const __grid_consta
     if (warp == 0) umma::tmem_dealloc(tmem, kRtTmemCols);
 }
 
+// every rank's exported buffer as mapped into this process (expert parallelism)
+struct EpPeers {
+    uint8_t* base[kEpMaxWorld];
+};
+// what the route kernel needs to send the histogram to the peers (world = 0: single GPU, nothing is sent)
+struct EpPush {
+    EpPeers peers;
+    size_t counts_off, flags_off;
+    int me, world;
+    unsigned int epoch;
+    unsigned int* done;
+};
+
 // ─── route: one warp per token ──────────────────────────────────────────────
 // route_experts (reference src/engine/qwen35_moe/cpu.rs:78-85; softmax, top-k and
 // renormalise of src/math_util.rs:77-126).  Ties go to the lower index.  Results in
@@ -334,9 +351,9 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
                                                           const float* __restrict__ bias,
                                                           const int32_t* __restrict__ forced,
                                                           int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
-                                                          int32_t* __restrict__ counts, int nsplit) {
+                                                          int32_t* __restrict__ counts, int nsplit, EpPush ep) {
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= n) return;
+    if (t < n) {
     const float* lg = logits + (size_t)t * E;
     const size_t slab = (size_t)n * E;  // the router GEMM leaves kRtSplit partial sums, added here in a fixed order
     float p[kMaxEPerLane];
@@ -408,6 +425,33 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
         topk_idx[(size_t)t * K + lane] = myi;
         topk_w[(size_t)t * K + lane] = myw;
         atomicAdd(&counts[myi], 1);
+    }
+    }
+    // expert parallelism: the last block to finish sends this rank's histogram to every peer and
+    // publishes the epoch (the plan kernel of every rank waits for it)
+    if (ep.world > 0) {
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(ep.done, 1u);
+            s_last = (prev == gridDim.x - 1) ? 1 : 0;
+            if (s_last) *ep.done = 0u;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int i = threadIdx.x; i < ep.world * E; i += blockDim.x) {
+                const int d = i / E, e = i - d * E;
+                reinterpret_cast<int32_t*>(ep.peers.base[d] + ep.counts_off)[(size_t)ep.me * E + e] = __ldcg(counts + e);
+            }
+            __threadfence_system();
+            __syncthreads();
+            if (threadIdx.x < 32 && (int)threadIdx.x < ep.world) {
+                unsigned int* f = reinterpret_cast<unsigned int*>(ep.peers.base[threadIdx.x] + ep.flags_off) + ep.me * 16;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(ep.epoch) : "memory");
+            }
+        }
     }
 }
 
@@ -866,10 +910,6 @@ __global__ void __launch_bounds__(256) batch_combine_kernel(const float* __restr
 //   combine  the sender adds residual, weighted expert rows and the shared expert
 // Ranks meet through per-source epoch flags in the mapped buffers; every wait
 // is bounded and raises the engine's error word instead of hanging.
-struct EpPeers {
-    uint8_t* base[kEpMaxWorld];
-};
-
 // Lanes 0..P-1 of the calling warp publish this rank's epoch to every peer, after a system-scope
 // fence: whatever this thread has observed as written is visible before the flag.
 __device__ __forceinline__ void ep_signal_warp(const EpPeers& peers, const EpSym& sym, int me, int P, unsigned int epoch, int lane) {
@@ -893,18 +933,6 @@ __device__ __forceinline__ bool ep_last_block(unsigned int* counter) {
     }
     __syncthreads();
     return s_last != 0;
-}
-
-// One block: this rank's histogram goes to every peer, then the epoch flag.
-__global__ void __launch_bounds__(1024) ep_push_counts_kernel(EpPeers peers, EpSym sym, int me, int P, int E,
-                                                              const int32_t* counts, unsigned int epoch) {
-    for (int i = threadIdx.x; i < P * E; i += blockDim.x) {
-        const int d = i / E, e = i - d * E;
-        reinterpret_cast<int32_t*>(peers.base[d] + sym.counts)[(size_t)me * E + e] = counts[e];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < 32) ep_signal_warp(peers, sym, me, P, epoch, threadIdx.x);
 }
 
 // plan: one block.  counts_all[s][e] = rows rank s sends to expert e.
@@ -1251,13 +1279,12 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     int32_t* idx = out_idx ? out_idx : bw.topk_idx;
     float* wts = out_w ? out_w : bw.topk_w;
 
-    MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
-    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate, bw.counts, E + 1);
     const int rsplit = router_split(n, E, ly.router_nplanes);
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, e->dec_sync + 2);
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit);
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
     GemmParams gp{};
@@ -1332,20 +1359,19 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     };
 #define EP_MARK(name) ep_mark(name)
     EP_MARK("start");
-    MOE_CUDA(cudaMemsetAsync(bw.counts, 0, (size_t)(E + 1) * 4, st));
-    EP_MARK("memset");
-    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate);
+    batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate, bw.counts, E + 1);
     EP_MARK("batch_prep_kernel");
     const int rsplit = router_split(n, E, ly.router_nplanes);
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, err);
     EP_MARK("router_gemm_kernel");
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit);
+    // 1. histogram exchange: the last block of the route kernel pushes it and publishes the epoch; the plan waits for everybody's
+    EpPush push{};
+    push.peers = peers; push.counts_off = ep.sym.counts; push.flags_off = ep.sym.flags;
+    push.me = me; push.world = P; push.epoch = ++ep.epoch; push.done = ep.done;
+    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
     EP_MARK("batch_route_kernel");
-    // 1. histogram exchange (the push publishes the epoch; the plan waits for everybody's)
-    ep_push_counts_kernel<<<1, 1024, 0, st>>>(peers, ep.sym, me, P, E, bw.counts, ++ep.epoch);
-    EP_MARK("ep_push_counts_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
                                        ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);
     EP_MARK("ep_plan_kernel");
@@ -1388,7 +1414,7 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
         for (auto& m : marks) cudaEventDestroy(m.second);
     }
 #undef EP_MARK
-    e->launches += 11;
+    e->launches += 9;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
