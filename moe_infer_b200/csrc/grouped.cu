@@ -347,6 +347,7 @@ struct EpPush {
 // route_experts (reference src/engine/qwen35_moe/cpu.rs:78-85; softmax, top-k and
 // renormalise of src/math_util.rs:77-126).  Ties go to the lower index.  Results in
 // descending order.  Also counts tokens per expert.
+template <int NPER>  // experts per lane: 8 covers 256 experts, 16 covers 512
 __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restrict__ logits, int n, int E, int K,
                                                           const float* __restrict__ bias,
                                                           const int32_t* __restrict__ forced,
@@ -356,10 +357,10 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
     if (t < n) {
     const float* lg = logits + (size_t)t * E;
     const size_t slab = (size_t)n * E;  // the router GEMM leaves kRtSplit partial sums, added here in a fixed order
-    float p[kMaxEPerLane];
+    float p[NPER];
     float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) {
+    for (int i = 0; i < NPER; ++i) {
         const int e = lane + 32 * i;
         float v = -INFINITY;
         if (e < E) {
@@ -380,14 +381,14 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) {
+    for (int i = 0; i < NPER; ++i) {
         p[i] = (lane + 32 * i < E) ? expf(p[i] - mx) : 0.0f;
         sum += p[i];
     }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
 #pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) p[i] = (lane + 32 * i < E) ? p[i] * inv : -1.0f;
+    for (int i = 0; i < NPER; ++i) p[i] = (lane + 32 * i < E) ? p[i] * inv : -1.0f;
     float myw = 0.0f;
     int myi = 0;
     if (forced) {
@@ -395,7 +396,7 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
             const int e = forced[(size_t)t * K + k];
             float v = 0.0f;
 #pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i)
+            for (int i = 0; i < NPER; ++i)
                 if (lane + 32 * i == e) v = p[i];
             v = __shfl_sync(0xffffffffu, v, e & 31);
             if (lane == k) { myw = v; myi = e; }
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
             float bv = -2.0f;
             int be = 0x7fffffff;
 #pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i)
+            for (int i = 0; i < NPER; ++i)
                 if (p[i] > bv) { bv = p[i]; be = lane + 32 * i; }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -415,7 +416,7 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
             }
             if (lane == k) { myw = bv; myi = be; }
 #pragma unroll
-            for (int i = 0; i < kMaxEPerLane; ++i)
+            for (int i = 0; i < NPER; ++i)
                 if (lane + 32 * i == be) p[i] = -1.0f;
         }
     }
@@ -1284,7 +1285,8 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, e->dec_sync + 2);
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
+    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
+    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
     GemmParams gp{};
@@ -1370,7 +1372,8 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     EpPush push{};
     push.peers = peers; push.counts_off = ep.sym.counts; push.flags_off = ep.sym.flags;
     push.me = me; push.world = P; push.epoch = ++ep.epoch; push.done = ep.done;
-    batch_route_kernel<<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
+    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
+    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
     EP_MARK("batch_route_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
                                        ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);
