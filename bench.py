@@ -244,7 +244,7 @@ def run_decode(args, rank, world, local, dist):
         line = {
             "metric": "moe_decode_tokens_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32 accumulate over 4-bit weights", "data": "synthetic",
+            "dtype": "u4 weights x 24-bit fixed-point activations (three s8 digits), exact s32 dp4a sums, f32 scales", "data": "synthetic",
             "config": {"workload": f"decode 1 token x {dims.num_layers} MoE layers, 256 experts top-8, hidden 2048, "
                                    "inter 512, BQ4 (bf16 router), attention passed through",
                        "replicas": world, "resident_store_GB": round(eng.resident_bytes() / 1e9, 2),
