@@ -81,7 +81,8 @@ def run_layer(args, rank, world, local, dist):
                                ms / args.steps, "config 2: one MoE layer, batch-1 decode, 256 experts top-8, BQ4; "
                                f"rotating over {n_copies} layer copies (L2 cannot hold them)", roof,
                                {"value": args.steps / e2e_s, "unit": "layer-tok/s", "h2d_bytes_per_step": H * 4,
-                                "d2h_bytes_per_step": H * 4 + 64}, launches, clocks, dtype="f32 accumulate over 4-bit weights")),
+                                "d2h_bytes_per_step": H * 4 + 64}, launches, clocks,
+                               dtype="u4 weights x 24-bit fixed-point activations (three s8 digits), exact s32 dp4a sums, f32 scales")),
               flush=True)
     eng.close()
 
