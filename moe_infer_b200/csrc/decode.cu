@@ -909,13 +909,17 @@ __device__ __forceinline__ void stage_from_regs(DecodeSmem3* sm, const uint16_t*
     __syncthreads();
 }
 
-// route_cta rearranged for latency.  Ranks are found with warp votes instead of per-thread
-// loops: the rank of a value among 32 is the population count of one ballot.  The candidate
-// threshold comes from the maxima of 16-expert groups (32 of them, one per lane): warp w ranks
-// group maxima 2w and 2w+1, and whichever has K-1 maxima ahead of it is the threshold.
-// Same arithmetic as route_cta for the values it returns: p = exp(v - max) * (1 / sum), ties to
-// the lower index, weights p_k * (1 / sum_k p_k).
-__device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32_t* forced, int E, int K) {
+// route_cta rearranged for latency, in two halves.  route_select picks the K experts from the raw logits
+// (softmax is monotonic, so the K largest logits are the K largest probabilities) and is all that the
+// weight copies wait for; route_weights forms the probabilities of the chosen experts afterwards, while the
+// copies are in flight.  Ranks are found with warp votes instead of per-thread loops: the rank of a value
+// among 32 is the population count of one ballot.  The candidate threshold comes from the maxima of
+// 16-expert groups (32 of them, one per lane): warp w ranks group maxima 2w and 2w+1, and whichever has K-1
+// maxima ahead of it is the threshold.  Values: p = exp(v - max) * (1 / sum), weights p_k * (1 / sum_k p_k),
+// as route_cta; ties between equal logits go to the lower index.  (Two different logits whose probabilities
+// round to the same float are ordered by logit here and by index in the reference: a difference below the
+// rounding of the logits themselves.)
+__device__ __forceinline__ void route_select(DecodeSmem3* sm, float v, const int32_t* forced, int E, int K) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float m = v;
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
@@ -924,51 +928,42 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
     if ((lane & 15) == 0) sm->hmax[tid >> 4] = m;
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
-    if (lane == 0) sm->red[warp] = m;
-    if (tid == 0) { sm->ncand = 0; sm->tau = -1.0f; }
+    if (lane == 0) sm->red[warp] = m;  // per-warp maxima: kept for route_weights
+    if (tid == 0) { sm->ncand = 0; sm->tau = -INFINITY; }
+    if (forced) sm->prob[tid] = v;
     __syncthreads();
-    float mx = sm->red[0];
-#pragma unroll
-    for (int i = 1; i < kDecWarps; ++i) mx = fmaxf(mx, sm->red[i]);
-    const float ex = (tid < E) ? expf(v - mx) : 0.0f;
-    const float ws = warp_sum(ex);
-    if (lane == 0) sm->red2[warp] = ws;
     if (forced) {
-        sm->prob[tid] = ex;
-    } else {
-        // group maxima as exp(v - max): bit-identical to the owning thread's value; -1 for empty groups
-        const float mine = (lane * 16 < E) ? expf(sm->hmax[lane] - mx) : -1.0f;
+        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]]; }
+        __syncthreads();
+        return;
+    }
+    {
+        // group maxima; -inf for groups beyond E (then everything is a candidate)
+        const float mine = (lane * 16 < E) ? sm->hmax[lane] : -INFINITY;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             const int iu = 2 * warp + t;
             const float u = __shfl_sync(0xffffffffu, mine, iu);
             const int ahead = __popc(__ballot_sync(0xffffffffu, (mine > u) || (mine == u && lane < iu)));
-            // exactly one group has K-1 ahead of it; lowered by a hair so that values which
-            // round to the same probability stay candidates (an empty group: everything is one)
-            if (ahead == K - 1 && lane == 0) sm->tau = u < 0.0f ? -1.0f : u * 0.999999f;
+            // exactly one group has K-1 ahead of it; lowered by a hair (harmless: it only adds candidates)
+            if (ahead == K - 1 && lane == 0) sm->tau = u - 1e-6f * fmaxf(1.0f, fabsf(u));
         }
     }
     __syncthreads();
-    float sum = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kDecWarps; ++i) sum += sm->red2[i];
-    const float inv = 1.0f / sum;
-    if (forced) {
-        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]] * inv; }
-    } else {
-        const bool is_c = tid < E && ex >= sm->tau;
+    {
+        const bool is_c = tid < E && v >= sm->tau;
         const unsigned bal = __ballot_sync(0xffffffffu, is_c);
         int base = 0;
         if (lane == 0 && bal) base = atomicAdd(&sm->ncand, __popc(bal));
         base = __shfl_sync(0xffffffffu, base, 0);
         if (is_c) {
             const int slot = base + __popc(bal & ((1u << lane) - 1u));
-            sm->cand_p[slot] = ex * inv;
+            sm->cand_p[slot] = v;
             sm->cand_i[slot] = tid;
         }
     }
     __syncthreads();
-    if (!forced) {
+    {
         // warp w ranks candidates w, w + 16, ...: every lane compares one other candidate per vote
         const int nc = sm->ncand;
         for (int c = warp; c < nc; c += kDecWarps) {
@@ -984,16 +979,34 @@ __device__ __forceinline__ void route_fast(DecodeSmem3* sm, float v, const int32
                 }
                 rank += __popc(__ballot_sync(0xffffffffu, beats));
             }
-            if (rank < K && lane == 0) { sm->topi[rank] = ci; sm->topp[rank] = cp; }
+            if (rank < K && lane == 0) { sm->topi[rank] = ci; sm->topp[rank] = cp; }  // topp: the logit, for now
         }
     }
     __syncthreads();
+}
+
+// Probabilities and renormalised weights of the experts route_select chose (their logits are in topp).
+__device__ __forceinline__ void route_weights(DecodeSmem3* sm, float v, int E, int K) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float mx = sm->red[0];
+#pragma unroll
+    for (int i = 1; i < kDecWarps; ++i) mx = fmaxf(mx, sm->red[i]);
+    const float ex = (tid < E) ? expf(v - mx) : 0.0f;
+    const float ws = warp_sum(ex);
+    if (lane == 0) sm->red2[warp] = ws;
+    __syncthreads();
     if (warp == 0) {
-        // normalize_weights: divide by the sum of the K selected probabilities
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kDecWarps; ++i) sum += sm->red2[i];
+        const float inv = 1.0f / sum;
+        // same expression as the owning thread's exp(v - max) * inv
+        const float pk = (lane < K) ? expf(sm->topp[lane] - mx) * inv : 0.0f;
+        // normalize_weights: divide by the sum of the K selected probabilities, added in order
         float s = 0.0f;
-        for (int k = 0; k < K; ++k) s += sm->topp[k];
+        for (int k = 0; k < K; ++k) s += __shfl_sync(0xffffffffu, pk, k);
         const float invs = s > 0.0f ? 1.0f / s : 1.0f;
-        if (lane < K) sm->topw[lane] = sm->topp[lane] * invs;
+        if (lane < K) sm->topw[lane] = pk * invs;
     }
     __syncthreads();
 }
@@ -1080,6 +1093,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         // ── route (from the accumulators) while h is being staged ──────────
         PROF3(0);
         DBG(4);
+        float vlogit = -INFINITY;  // this thread's router logit (thread t owns expert t)
         {
             // every CTA has announced the end of the previous phase (a hint: the words below validate themselves)
             if (tid == 0) {
@@ -1114,7 +1128,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 v = __ll2float_rn(a) * (1.0f / kFix) * r * inv_rms_acc;
                 if (p.logit_bias) v += p.logit_bias[tid];
             }
-            route_fast(sm, v, p.forced_idx, E, K);
+            route_select(sm, v, p.forced_idx, E, K);
+            vlogit = v;
         }
         PROF3(1);
         if (kBulk) {
@@ -1125,6 +1140,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         } else {
             prefetch_B3_warp(sm, ly, L, i0, nb, K, sg_here, warp, lane);
         }
+        // the copies are on their way: now the softmax weights of the chosen experts
+        route_weights(sm, vlogit, E, K);
         if (cta == 0 && warp == 0 && lane < K) {
             if (p.out_idx) p.out_idx[lane] = sm->topi[lane];
             if (p.out_w) p.out_w[lane] = sm->topw[lane];
