@@ -140,12 +140,6 @@ struct moe_engine {
     int64_t launches = 0;
 
     // decode (n = 1) work areas
-    float* dec_h[2] = {nullptr, nullptr};  // [H] ping-pong
-    float* dec_logits = nullptr;           // [E]
-    float* dec_act = nullptr;              // [(K + 1), I]
-    float* dec_misc = nullptr;             // [16] sgate score etc.
-    int32_t* dec_idx = nullptr;            // [K]
-    float* dec_w = nullptr;                // [K]
     unsigned int* dec_sync = nullptr;      // grid barrier words + error flag
     unsigned long long* dec_act_ll = nullptr;  // fused decode kernel: tagged SwiGLU outputs
     long long* dec_acc = nullptr;          // fused decode kernel: fixed-point router accumulators, two sets

@@ -1409,13 +1409,6 @@ __global__ void __launch_bounds__(256) router_transpose_kernel(LayerDev ly, int 
 
 int decode_init(moe_engine* e) {
     const moe_dims_t& d = e->dims;
-    MOE_CUDA(cudaMalloc(&e->dec_h[0], d.hidden * sizeof(float)));
-    MOE_CUDA(cudaMalloc(&e->dec_h[1], d.hidden * sizeof(float)));
-    MOE_CUDA(cudaMalloc(&e->dec_logits, d.num_experts * sizeof(float)));
-    MOE_CUDA(cudaMalloc(&e->dec_act, (size_t)(kMaxK + 1) * d.inter * sizeof(float)));
-    MOE_CUDA(cudaMalloc(&e->dec_misc, 16 * sizeof(float)));
-    MOE_CUDA(cudaMalloc(&e->dec_idx, kMaxK * sizeof(int32_t)));
-    MOE_CUDA(cudaMalloc(&e->dec_w, kMaxK * sizeof(float)));
     MOE_CUDA(cudaMalloc(&e->dec_sync, 16 * sizeof(unsigned int)));
     MOE_CUDA(cudaMemset(e->dec_sync, 0, 16 * sizeof(unsigned int)));
     e->dec_prof = nullptr;
@@ -1470,8 +1463,7 @@ int decode_profile_read(moe_engine* e, long long* out, int max_layers, int* poin
 
 void decode_destroy(moe_engine* e) {
     if (e->dec_prof) cudaFree(e->dec_prof);
-    cudaFree(e->dec_h[0]); cudaFree(e->dec_h[1]); cudaFree(e->dec_logits); cudaFree(e->dec_act);
-    cudaFree(e->dec_misc); cudaFree(e->dec_idx); cudaFree(e->dec_w); cudaFree(e->dec_sync);
+    cudaFree(e->dec_sync);
     cudaFree(e->dec_act_ll); cudaFree(e->dec_acc); cudaFree(e->dec_hint); cudaFree(e->dec_h_ll);
     if (e->stage_host) cudaFreeHost(e->stage_host);
 }
