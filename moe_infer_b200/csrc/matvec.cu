@@ -35,6 +35,18 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
         mbar_expect_tx(&bar, (uint32_t)cols * 4u);
         bulk_g2s(raw, x, (uint32_t)cols * 4u, &bar);
     }
+    // the first two chunks of this warp's first row do not depend on x: request them before waiting for it
+    const int groups = cols / kGroup;
+    const int row_first = blockIdx.x * kMvWarps + warp;
+    uint4 pqa = make_uint4(0, 0, 0, 0), pqb = pqa;
+    uint16_t psa = 0, pba = 0, psb = 0, pbb = 0;
+    if (row_first < rows) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row_first * (cols / 8));
+        const uint16_t* srow = s + (size_t)row_first * groups;
+        const uint16_t* brow = b + (size_t)row_first * groups;
+        if (lane < nch) { pqa = ld_stream_u4(wrow + lane); psa = srow[lane >> 1]; pba = brow[lane >> 1]; }
+        if (32 + lane < nch) { pqb = ld_stream_u4(wrow + 32 + lane); psb = srow[(32 + lane) >> 1]; pbb = brow[(32 + lane) >> 1]; }
+    }
     // every thread observes the phase itself, so the copied bytes are visible to it
     const int ok = __syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0);
     if (!ok) {
@@ -54,8 +66,7 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
     }
     __syncthreads();
 
-    const int groups = cols / kGroup;
-    for (int row = blockIdx.x * kMvWarps + warp; row < rows; row += gridDim.x * kMvWarps) {
+    for (int row = row_first; row < rows; row += gridDim.x * kMvWarps) {
         const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (cols / 8));
         const uint16_t* srow = s + (size_t)row * groups;
         const uint16_t* brow = b + (size_t)row * groups;
@@ -66,8 +77,13 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
             const bool va = ca < nch, vb = cb < nch;
             uint4 qa = make_uint4(0, 0, 0, 0), qb = qa;
             uint16_t sa = 0, ba = 0, sb = 0, bb = 0;
-            if (va) { qa = ld_stream_u4(wrow + ca); sa = srow[ca >> 1]; ba = brow[ca >> 1]; }
-            if (vb) { qb = ld_stream_u4(wrow + cb); sb = srow[cb >> 1]; bb = brow[cb >> 1]; }
+            if (row == row_first && c0 == 0) {
+                qa = pqa; sa = psa; ba = pba;
+                qb = pqb; sb = psb; bb = pbb;
+            } else {
+                if (va) { qa = ld_stream_u4(wrow + ca); sa = srow[ca >> 1]; ba = brow[ca >> 1]; }
+                if (vb) { qb = ld_stream_u4(wrow + cb); sb = srow[cb >> 1]; bb = brow[cb >> 1]; }
+            }
             if (va) {
                 float4 xv[8];
 #pragma unroll
