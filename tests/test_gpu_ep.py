@@ -99,3 +99,75 @@ def test_ep_two_gpus_matches_oracle():
         assert err is None, f"rank {rank}: {err}"
         assert e1 < 1e-2, (rank, e1)   # one block, MoE update only
         assert e2 < 1e-2, (rank, e2)   # two-block stack
+
+
+def _worker_absent_peer(rank, conn, ret_q):
+    """Rank 1 joins the group but never makes the collective call; rank 0's waits must run out."""
+    try:
+        sys.path.insert(0, ROOT)
+        from moe_infer_b200 import _lib, synth
+        from moe_infer_b200.native import Dims, NativeEngine
+        from tests.util import make_layer, upload_layer
+        lw = make_layer(43, 0, num_experts=E)
+        eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=1), device=rank)
+        upload_layer(eng, 0, lw)
+        conn.send(eng.ep_export(rank, WORLD, 64))
+        eng.ep_init(conn.recv())
+        outcome = "idle"
+        if rank == 0:
+            h = synth.hidden_states(600, 3, 8, 2048)
+            d_in = eng.alloc(h.nbytes).upload(h)
+            d_out = eng.alloc(h.nbytes)
+            try:
+                eng.ep_layer_forward_dev(0, d_in.ptr, 8, d_out.ptr)
+                eng.sync()
+                outcome = "no error"
+            except _lib.MoeError as ex:
+                outcome = "error: " + str(ex)
+            # the context is still usable: the same engine runs an ordinary layer afterwards
+            out, _, _ = eng.layer_forward(0, h[:1])
+            if not np.isfinite(out).all():
+                outcome += " / follow-up call produced non-finite values"
+        conn.send("done")
+        conn.recv()  # the idle rank keeps its buffers mapped until rank 0 has finished
+        ret_q.put((rank, outcome, None))
+        eng.close()
+    except Exception as ex:
+        ret_q.put((rank, None, repr(ex)))
+
+
+def test_ep_absent_peer_ends_in_an_error_not_a_hang():
+    """Failure detection without a GPU fault: every device-side wait is bounded (about a second), so a peer
+    that never arrives turns into MOE_ERR_DEVICE_WAIT on the host and the context stays usable."""
+    if _gpu_count() < WORLD:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    ret_q = ctx.Queue()
+    pipes = [ctx.Pipe() for _ in range(WORLD)]
+    procs = [ctx.Process(target=_worker_absent_peer, args=(r, pipes[r][1], ret_q)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    try:
+        handles = []
+        for r in range(WORLD):
+            assert pipes[r][0].poll(300), "rank did not export a handle"
+            handles.append(pipes[r][0].recv())
+        table = b"".join(handles)
+        for r in range(WORLD):
+            pipes[r][0].send(table)
+        for r in range(WORLD):
+            if pipes[r][0].poll(300):
+                pipes[r][0].recv()
+        for r in range(WORLD):
+            pipes[r][0].send("bye")
+        results = [ret_q.get(timeout=300) for _ in range(WORLD)]
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    by_rank = {r: (o, e) for r, o, e in results}
+    assert by_rank[1] == ("idle", None), by_rank[1]
+    outcome, err = by_rank[0]
+    assert err is None, err
+    assert outcome.startswith("error: ") and "wait" in outcome and "non-finite" not in outcome, outcome
