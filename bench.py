@@ -31,15 +31,23 @@ N_ROTATE = 64  # distinct input tokens cycled through, so routing differs from s
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default 2000; 20 for --impl reference and the prefill workload)")
+    ap.add_argument("--warmup", type=int, default=None,
+                    help="untimed steps (default 20; 3 for --impl reference and the prefill workload)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "layer", "pack", "matvec", "batched64", "prefill"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--tokens", type=int, default=0, help="tokens per step for the batched workloads")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    return ap.parse_args()
+    args = ap.parse_args()
+    slow = args.impl == "reference" or args.workload == "prefill"
+    if args.steps is None:
+        args.steps = 20 if slow else 2000
+    if args.warmup is None:
+        args.warmup = 3 if slow else 20
+    return args
 
 
 def dist_env():
