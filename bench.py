@@ -106,7 +106,7 @@ def cpu_decode_sample(dims, n_layers_sample: int, threads: int, target_s: float 
     full stack, description).
     """
     import oracle
-    from moe_infer_b200 import synth
+    from benchmarks import synth
     oracle.build()
     rng = np.random.default_rng(seed)
     H, I, E, K = dims.hidden, dims.inter, dims.num_experts, dims.top_k
@@ -186,7 +186,7 @@ def run_reference(args, rank, world):
 
 def run_decode(args, rank, world, local, dist):
     from moe_infer_b200 import _lib as L
-    from moe_infer_b200 import benchlib, synth
+    from benchmarks import benchlib, synth
     from moe_infer_b200.native import Dims, NativeEngine, PinnedArray
 
     dims = Dims(num_layers=args.layers)
@@ -288,7 +288,7 @@ def main():
         if args.workload == "decode":
             run_decode(args, rank, world, local, dist)
         else:
-            from moe_infer_b200 import bench_extra
+            from benchmarks import workloads as bench_extra
             bench_extra.run(args, rank, world, local, dist)
     finally:
         dist.close()

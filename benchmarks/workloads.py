@@ -15,9 +15,10 @@ import time
 
 import numpy as np
 
-from . import _lib as L
+from moe_infer_b200 import _lib as L
+from moe_infer_b200.native import Dims, NativeEngine, PinnedArray
+
 from . import benchlib, synth
-from .native import Dims, NativeEngine, PinnedArray
 
 
 # Router logits of random weights have a spread of about +-2.5; the Zipf(1.1) popularity prior ln p_e spans 6.1.
@@ -162,7 +163,7 @@ def run_batched(args, rank, world, local, dist, n_tokens, n_layers, scheme, zipf
 
 def run_prefill_ep(args, rank, world, local, dist):
     """Config 4 across `world` GPUs: experts sharded 256/P, tokens T/P per rank, dispatch/combine over peer memory."""
-    from . import ep as ephost
+    from moe_infer_b200 import ep as ephost
     T = args.tokens or 4096
     n_local = T // world
     dims = Dims(num_layers=args.layers, scheme=L.SCHEME_INT4)

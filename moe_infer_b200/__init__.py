@@ -6,4 +6,4 @@
 
 The compute path is the CUDA library only; there is no CPU fallback.
 """
-__all__ = ["native", "build", "synth"]
+__all__ = ["native", "build"]

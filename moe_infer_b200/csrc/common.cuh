@@ -79,7 +79,8 @@ struct BatchWork {
     __nv_bfloat16* x = nullptr;    // [cap, H] normalised activations, bf16, K-interleaved
     __nv_bfloat16* x_mid = nullptr;  // [cap, H] second and third bf16 terms of x (x = x + x_mid + x_lo to 24 bits),
     __nv_bfloat16* x_lo = nullptr;   //          same order, for the f32-accurate router
-    float* logits = nullptr;       // [cap, E]
+    float* logits = nullptr;       // [logit_rows, E]: up to kRtMaxSplit slabs of partial sums
+    int64_t logit_rows = 0;
     int32_t* topk_idx = nullptr;   // [cap, K]
     float* topk_w = nullptr;       // [cap, K]
     float* sgate = nullptr;        // [cap] sigmoid(shared gate score)
@@ -149,6 +150,7 @@ struct moe_engine {
     unsigned long long* dec_h_ll = nullptr;    // fused decode kernel: tagged hidden state between layers
     long long* dec_prof = nullptr;         // per-phase clock stamps (off unless enabled)
     int dec_grid = 0;
+    bool matvec_attr_set = false;          // matvec kernel's shared-memory attribute set on this engine's device
     float* stage_host = nullptr;           // pinned staging [H] x 2
     std::vector<float> last_h;             // last_h_pre_norm
     int64_t mtp_pos = 0;

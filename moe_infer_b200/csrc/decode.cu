@@ -30,18 +30,10 @@
 // HBM-bound: 16,974,976 weight bytes per layer-token at the reference sizes.
 // Every wait (grid barrier, mbarrier, tag poll) is bounded and a timeout raises an
 // error word instead of hanging.
-#include "q4dot.cuh"
-#include "stage.cuh"
+#include "decode_common.cuh"
 
 namespace moe {
 
-constexpr int kH = 2048;        // hidden (both reference models)
-constexpr int kI = 512;         // moe_intermediate_size == shared_expert_intermediate_size
-constexpr int kDecWarps = 16;
-constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kChH = kH / 32;   // 64 chunks (128-bit loads) per hidden row
-constexpr int kChI = kI / 32;   // 16 chunks per intermediate row
-constexpr int kMaxE = 512;      // routing supports up to 512 experts
 constexpr int kProfPoints = 12;
 
 // Per-CTA slice capacities; the host checks that the grid is large enough.
@@ -147,22 +139,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* sync, unsigned int ta
     }
     __syncthreads();
     return sm->flag != 0;
-}
-
-// ─── weight prefetch with per-thread 16-byte asynchronous copies ─────────────
-// Every thread of the CTA copies pieces p = tid, tid + 512, ... of a slice;
-// completion is tracked with cp.async groups (one group per slice), then a CTA
-// barrier makes the bytes visible to every warp.
-__device__ __forceinline__ void cp16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void copy_flat(void* dst, const void* src, int pieces, int tid) {
-    for (int q = tid; q < pieces; q += kDecThreads)
-        cp16(reinterpret_cast<uint8_t*>(dst) + (size_t)q * 16, reinterpret_cast<const uint8_t*>(src) + (size_t)q * 16);
 }
 
 // phase A slice: router rows [e0, e0+ne), shared gate/up pairs [p0, p0+np), shared gate (last CTA)
@@ -336,9 +312,6 @@ __device__ __forceinline__ float row_dot_bf16(const DecodeSmem* sm, const uint4*
     return warp_sum(acc);
 }
 
-// swiglu_fused (reference src/math_util.rs:254-259): silu(gate) * up.
-__device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + expf(-g)) * u; }
-
 // ─── softmax + top-k + renormalise, whole CTA ───────────────────────────────
 // route_experts (reference src/engine/qwen35_moe/cpu.rs:78-85): softmax over all
 // E logits (src/math_util.rs:77-88), the K largest probabilities (ties: lower
@@ -348,7 +321,7 @@ __device__ __forceinline__ float swiglu(float g, float u) { return g / (1.0f + e
 // or above it are candidates; each candidate finds its rank by counting the
 // candidates that beat it.  Results come out in descending order.
 template <class SM>
-__device__ __forceinline__ void route_cta(SM* sm, float v, const int32_t* forced, int E, int K) {
+__device__ __forceinline__ void route_cta(SM* sm, float v, const int32_t* forced, int E, int K, unsigned int* err) {
     // v: this thread's router logit (thread t owns expert t; -INFINITY for t >= E)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float mx = v;
@@ -375,7 +348,12 @@ __device__ __forceinline__ void route_cta(SM* sm, float v, const int32_t* forced
     sm->prob[tid] = (tid < E) ? pr : -1.0f;
     if (forced) {
         __syncthreads();
-        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]]; }
+        if (tid < K) {
+            int fe = forced[tid];
+            if ((unsigned)fe >= (unsigned)E) { atomicExch(err, 10u); fe = 0; }  // reported, never dereferenced
+            sm->topi[tid] = fe;
+            sm->topp[tid] = sm->prob[fe];
+        }
     } else {
         // threshold = K-th largest warp maximum (as a probability); -1 when fewer than K warps hold experts
         float tau;
@@ -510,7 +488,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
                 v = __ldcg(p.logits + tid);  // written by other CTAs: read through L2
                 if (p.logit_bias) v += p.logit_bias[tid];
             }
-            route_cta(sm, v, p.forced_idx, E, K);
+            route_cta(sm, v, p.forced_idx, E, K, p.sync + 2);
         }
         PROF(5);
         // request this warp's gate/up rows now; its down rows and the next layer's
@@ -838,33 +816,6 @@ __device__ __forceinline__ void ld_ll2(const unsigned long long* ptr, unsigned l
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(ptr) : "memory");
 }
 
-// Dot products of NR 4-bit rows of length kH with the staged x (integer path).
-template <int NR>
-__device__ __forceinline__ void rows_dot_q(const DecodeSmem3* sm, const uint4* const (&w)[NR],
-                                           const uint16_t* const (&s)[NR], const uint16_t* const (&b)[NR],
-                                           float (&out)[NR], int lane) {
-#pragma unroll
-    for (int r = 0; r < NR; ++r) out[r] = 0.0f;
-#pragma unroll
-    for (int it = 0; it < 2; ++it) {
-        const int c = lane + 32 * it;
-        uint4 xe[3], xo[3];
-#pragma unroll
-        for (int p = 0; p < 3; ++p) {
-            xe[p] = sm->xq[(p * 2 + 0) * kChH + c];
-            xo[p] = sm->xq[(p * 2 + 1) * kChH + c];
-        }
-        const float sx = sm->sumx[c], dl = sm->xdl[c];
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-            const float sc = bf16_bits_to_f32(s[r][c >> 1]), bi = bf16_bits_to_f32(b[r][c >> 1]);
-            out[r] += fmaf(sc * dl, dot32_int(w[r][c], xe, xo), bi * sx);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < NR; ++r) out[r] = warp_sum(out[r]);
-}
-
 // Reads an accumulator until the contributions of all G CTAs are in: the word is never reset, the reader
 // subtracts what it read two layers ago (`prev`, updated).  Returns the sum (2^-32 units); bounded.
 __device__ __forceinline__ long long read_counted(const long long* word, unsigned long long& prev, int G, int* ok) {
@@ -906,108 +857,6 @@ __device__ __forceinline__ void stage_from_regs(DecodeSmem3* sm, const uint16_t*
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     s += __shfl_xor_sync(0xffffffffu, s, 4);
     if (j == 0) sm->sumx[c] = s;
-    __syncthreads();
-}
-
-// route_cta rearranged for latency, in two halves.  route_select picks the K experts from the raw logits
-// (softmax is monotonic, so the K largest logits are the K largest probabilities) and is all that the
-// weight copies wait for; route_weights forms the probabilities of the chosen experts afterwards, while the
-// copies are in flight.  Ranks are found with warp votes instead of per-thread loops: the rank of a value
-// among 32 is the population count of one ballot.  The candidate threshold comes from the maxima of
-// 16-expert groups (32 of them, one per lane): warp w ranks group maxima 2w and 2w+1, and whichever has K-1
-// maxima ahead of it is the threshold.  Values: p = exp(v - max) * (1 / sum), weights p_k * (1 / sum_k p_k),
-// as route_cta; ties between equal logits go to the lower index.  (Two different logits whose probabilities
-// round to the same float are ordered by logit here and by index in the reference: a difference below the
-// rounding of the logits themselves.)
-__device__ __forceinline__ void route_select(DecodeSmem3* sm, float v, const int32_t* forced, int E, int K) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float m = v;
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
-    if ((lane & 15) == 0) sm->hmax[tid >> 4] = m;
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
-    if (lane == 0) sm->red[warp] = m;  // per-warp maxima: kept for route_weights
-    if (tid == 0) { sm->ncand = 0; sm->tau = -INFINITY; }
-    if (forced) sm->prob[tid] = v;
-    __syncthreads();
-    if (forced) {
-        if (tid < K) { sm->topi[tid] = forced[tid]; sm->topp[tid] = sm->prob[forced[tid]]; }
-        __syncthreads();
-        return;
-    }
-    {
-        // group maxima; -inf for groups beyond E (then everything is a candidate)
-        const float mine = (lane * 16 < E) ? sm->hmax[lane] : -INFINITY;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const int iu = 2 * warp + t;
-            const float u = __shfl_sync(0xffffffffu, mine, iu);
-            const int ahead = __popc(__ballot_sync(0xffffffffu, (mine > u) || (mine == u && lane < iu)));
-            // exactly one group has K-1 ahead of it; lowered by a hair (harmless: it only adds candidates)
-            if (ahead == K - 1 && lane == 0) sm->tau = u - 1e-6f * fmaxf(1.0f, fabsf(u));
-        }
-    }
-    __syncthreads();
-    {
-        const bool is_c = tid < E && v >= sm->tau;
-        const unsigned bal = __ballot_sync(0xffffffffu, is_c);
-        int base = 0;
-        if (lane == 0 && bal) base = atomicAdd(&sm->ncand, __popc(bal));
-        base = __shfl_sync(0xffffffffu, base, 0);
-        if (is_c) {
-            const int slot = base + __popc(bal & ((1u << lane) - 1u));
-            sm->cand_p[slot] = v;
-            sm->cand_i[slot] = tid;
-        }
-    }
-    __syncthreads();
-    {
-        // warp w ranks candidates w, w + 16, ...: every lane compares one other candidate per vote
-        const int nc = sm->ncand;
-        for (int c = warp; c < nc; c += kDecWarps) {
-            const float cp = sm->cand_p[c];
-            const int ci = sm->cand_i[c];
-            int rank = 0;
-            for (int j0 = 0; j0 < nc; j0 += 32) {
-                const int j = j0 + lane;
-                bool beats = false;
-                if (j < nc) {
-                    const float q = sm->cand_p[j];
-                    beats = (q > cp) || (q == cp && sm->cand_i[j] < ci);
-                }
-                rank += __popc(__ballot_sync(0xffffffffu, beats));
-            }
-            if (rank < K && lane == 0) { sm->topi[rank] = ci; sm->topp[rank] = cp; }  // topp: the logit, for now
-        }
-    }
-    __syncthreads();
-}
-
-// Probabilities and renormalised weights of the experts route_select chose (their logits are in topp).
-__device__ __forceinline__ void route_weights(DecodeSmem3* sm, float v, int E, int K) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float mx = sm->red[0];
-#pragma unroll
-    for (int i = 1; i < kDecWarps; ++i) mx = fmaxf(mx, sm->red[i]);
-    const float ex = (tid < E) ? expf(v - mx) : 0.0f;
-    const float ws = warp_sum(ex);
-    if (lane == 0) sm->red2[warp] = ws;
-    __syncthreads();
-    if (warp == 0) {
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kDecWarps; ++i) sum += sm->red2[i];
-        const float inv = 1.0f / sum;
-        // same expression as the owning thread's exp(v - max) * inv
-        const float pk = (lane < K) ? expf(sm->topp[lane] - mx) * inv : 0.0f;
-        // normalize_weights: divide by the sum of the K selected probabilities, added in order
-        float s = 0.0f;
-        for (int k = 0; k < K; ++k) s += __shfl_sync(0xffffffffu, pk, k);
-        const float invs = s > 0.0f ? 1.0f / s : 1.0f;
-        if (lane < K) sm->topw[lane] = pk * invs;
-    }
     __syncthreads();
 }
 
@@ -1128,7 +977,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 v = __ll2float_rn(a) * (1.0f / kFix) * r * inv_rms_acc;
                 if (p.logit_bias) v += p.logit_bias[tid];
             }
-            route_select(sm, v, p.forced_idx, E, K);
+            route_select(sm, v, p.forced_idx, E, K, p.err);
             vlogit = v;
         }
         PROF3(1);
@@ -1530,6 +1379,7 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
                 "decode kernel needs at least 147 SMs for these dimensions (device has %d)", G);
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
     MOE_REQUIRE(l1 - l0 <= kMaxDecLayers, "decode: at most %d layers per launch", kMaxDecLayers);
+    MOE_REQUIRE(G < 256, "decode kernel counts CTAs in 8 bits (grid of %d)", G);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
     for (int l = l0; l < l1; ++l) {
         int rc = check_layer_ready(e, l);
@@ -1563,7 +1413,6 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
     p.prof = e->dec_prof;
     p.E = d.num_experts; p.K = d.top_k;
     p.lay = e->lay;
-    MOE_REQUIRE(G < 256, "decode kernel counts CTAs in 8 bits (grid of %d)", G);
     void* args[] = {&p};
     MOE_CUDA(cudaLaunchCooperativeKernel((const void*)decode_fused_kernel, dim3(e->dec_grid), dim3(kDecThreads),
                                          args, sizeof(DecodeSmem3), e->stream));

@@ -159,6 +159,11 @@ static int poll_device_error(moe_engine* e) {
         cudaMemsetAsync(e->dec_sync, 0, 16 * sizeof(unsigned int), e->stream);
         cudaStreamSynchronize(e->stream);
         decode_reset_after_error(e);
+        if (flag == 10u) {
+            set_error("forced_idx holds an expert index outside [0, %d); the result of the last call is invalid",
+                      e->dims.num_experts);
+            return MOE_ERR_INVALID;
+        }
         set_error("a bounded device-side wait gave up (code %u); the result of the last call is invalid", flag);
         return MOE_ERR_DEVICE_WAIT;
     }
@@ -529,6 +534,10 @@ int moe_layer_forward_host(moe_engine_t* e, int layer, const float* h_in, int32_
     MOE_REQUIRE(n >= 0, "negative token count");
     if (n == 0) return MOE_OK;
     const moe_dims_t& d = e->dims;
+    if (forced_idx)
+        for (size_t i = 0; i < (size_t)n * d.top_k; ++i)
+            MOE_REQUIRE(forced_idx[i] >= 0 && forced_idx[i] < d.num_experts,
+                        "forced_idx[%zu] = %d is outside [0, %d)", i, forced_idx[i], d.num_experts);
     const size_t hb = (size_t)n * d.hidden * 4;
     const size_t hb_al = align_up(hb, 256);
     const size_t lb = align_up((size_t)d.num_experts * 4, 256);

@@ -352,7 +352,8 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
                                                           const float* __restrict__ bias,
                                                           const int32_t* __restrict__ forced,
                                                           int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
-                                                          int32_t* __restrict__ counts, int nsplit, EpPush ep) {
+                                                          int32_t* __restrict__ counts, int nsplit, EpPush ep,
+                                                          unsigned int* err) {
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t < n) {
     const float* lg = logits + (size_t)t * E;
@@ -393,7 +394,11 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
     int myi = 0;
     if (forced) {
         for (int k = 0; k < K; ++k) {
-            const int e = forced[(size_t)t * K + k];
+            int e = forced[(size_t)t * K + k];
+            if ((unsigned)e >= (unsigned)E) {  // a caller's index outside [0, E): reported, never dereferenced
+                if (lane == 0) atomicExch(err, 10u);
+                e = 0;
+            }
             float v = 0.0f;
 #pragma unroll
             for (int i = 0; i < NPER; ++i)
@@ -1224,7 +1229,14 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += al256(bytes); return o; };
     const size_t o_ha = take(n * H * 4), o_hb = take(n * H * 4), o_x = take(n * H * 2), o_xm = take(n * H * 2), o_xl = take(n * H * 2);
-    const size_t o_lg = take((n > 8192 ? n : (size_t)8192) * E * 4);  // up to kRtMaxSplit partial sums for small token counts
+    // the router GEMM leaves router_split(n') slabs of n' x E partial sums for any n' up to the capacity
+    size_t lg_rows = n;
+    for (int np = 1; np <= n_tokens; ++np) {
+        const int s = router_split(np, (int)E, 1) > router_split(np, (int)E, 3) ? router_split(np, (int)E, 1) : router_split(np, (int)E, 3);
+        if ((size_t)s * np > lg_rows) lg_rows = (size_t)s * np;
+        if (s == 1) break;  // the split only shrinks as the token count grows
+    }
+    const size_t o_lg = take(lg_rows * E * 4);
     const size_t o_ti = take(n * K * 4), o_tw = take(n * K * 4), o_sg = take(n * 4);
     const size_t o_cnt = take((E + 1) * 4), o_off = take((E + 2) * 4), o_cur = take((E + 1) * 4);
     const size_t o_st = take(slots * 4), o_so = take(n * K * 4), o_act = take(slots * I * 2), o_o = take(slots * H * 2);
@@ -1241,6 +1253,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     bw.tile_list = (int32_t*)(b + o_tl); bw.n_tiles = (int32_t*)(b + o_nt);
     bw.max_tiles = max_tiles;
     bw.capacity = n_tokens;
+    bw.logit_rows = (int64_t)lg_rows;
     {
         int rcm = encode_rows_map(bw.x_map, bw.x, (uint64_t)3 * n, kRtTok);
         if (rcm) return rcm;
@@ -1282,11 +1295,13 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
 
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate, bw.counts, E + 1);
     const int rsplit = router_split(n, E, ly.router_nplanes);
+    MOE_REQUIRE((int64_t)rsplit * n <= bw.logit_rows, "router partial sums (%d x %d rows) exceed the logits work area (%lld rows)",
+                rsplit, n, (long long)bw.logit_rows);
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, e->dec_sync + 2);
-    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
-    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{});
+    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{}, e->dec_sync + 2);
+    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{}, e->dec_sync + 2);
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
     batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
     GemmParams gp{};
@@ -1364,6 +1379,8 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate, bw.counts, E + 1);
     EP_MARK("batch_prep_kernel");
     const int rsplit = router_split(n, E, ly.router_nplanes);
+    MOE_REQUIRE((int64_t)rsplit * n <= bw.logit_rows, "router partial sums (%d x %d rows) exceed the logits work area (%lld rows)",
+                rsplit, n, (long long)bw.logit_rows);
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, err);
@@ -1372,8 +1389,8 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     EpPush push{};
     push.peers = peers; push.counts_off = ep.sym.counts; push.flags_off = ep.sym.flags;
     push.me = me; push.world = P; push.epoch = ++ep.epoch; push.done = ep.done;
-    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
-    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push);
+    if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push, err);
+    else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push, err);
     EP_MARK("batch_route_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
                                        ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);

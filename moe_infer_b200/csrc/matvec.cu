@@ -108,10 +108,9 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
     const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
-    static bool attr_set = false;
-    if (!attr_set) {
+    if (!e->matvec_attr_set) {  // a per-device function attribute: set once per engine
         MOE_CUDA(cudaFuncSetAttribute(matvec_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8 + 2048));
-        attr_set = true;
+        e->matvec_attr_set = true;
     }
     int blocks = (rows + kMvWarps - 1) / kMvWarps;
     const int cap = e->sm_count * 8;

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 import oracle
-from moe_infer_b200 import synth
+from benchmarks import synth
 from moe_infer_b200.native import Dims, NativeEngine
 from tests.util import rel_l2
 

@@ -32,7 +32,7 @@ def _worker(rank, conn, ret_q):
     try:
         sys.path.insert(0, ROOT)
         import oracle
-        from moe_infer_b200 import synth
+        from benchmarks import synth
         from moe_infer_b200.native import Dims, NativeEngine
         from tests.util import make_layer, rel_l2, upload_layer
         layers = [make_layer(41, l, num_experts=E) for l in range(LAYERS)]
@@ -105,7 +105,8 @@ def _worker_absent_peer(rank, conn, ret_q):
     """Rank 1 joins the group but never makes the collective call; rank 0's waits must run out."""
     try:
         sys.path.insert(0, ROOT)
-        from moe_infer_b200 import _lib, synth
+        from moe_infer_b200 import _lib
+        from benchmarks import synth
         from moe_infer_b200.native import Dims, NativeEngine
         from tests.util import make_layer, upload_layer
         lw = make_layer(43, 0, num_experts=E)

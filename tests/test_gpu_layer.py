@@ -9,7 +9,8 @@ import numpy as np
 import pytest
 
 import oracle
-from moe_infer_b200 import _lib, synth
+from moe_infer_b200 import _lib
+from benchmarks import synth
 from moe_infer_b200.native import Dims, NativeEngine
 from tests.util import make_layer, rel_l2, routing_maps, upload_layer
 

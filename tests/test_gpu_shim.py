@@ -9,7 +9,7 @@ import pytest
 
 import oracle
 from moe_infer_b200 import _moe_infer_rs as rs
-from moe_infer_b200 import synth
+from benchmarks import synth
 from tests.util import rel_l2
 
 pytestmark = pytest.mark.gpu

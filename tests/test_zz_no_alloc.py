@@ -14,7 +14,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from moe_infer_b200 import _lib, synth
+from moe_infer_b200 import _lib
+from benchmarks import synth
 from moe_infer_b200.native import Dims, NativeEngine
 from tests.util import make_layer, rel_l2, upload_layer
 

@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 
 import oracle
-from moe_infer_b200 import synth
+from benchmarks import synth
 
 
 def rel_l2(a: np.ndarray, b: np.ndarray) -> float:
