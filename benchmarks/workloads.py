@@ -1,17 +1,21 @@
-"""Secondary benchmark workloads (selected with ``bench.py --workload``).
+"""Timed workloads behind ``bench.py``.
 
+decode     config 2 x 40 layers: one token through the MoE stack (the headline, in ``bench.py``)
 layer      config 2: one MoE block, batch-1 decode, rotating over distinct layer copies
 batched64  config 3: 64 tokens through one block, Zipf(1.1)-skewed routing
-prefill    config 4: T tokens through the 40-block stack (INT4 scheme), grouped tensor-core path
-pack       config 5: GPU quantisation of expert tensors into the packed blob layout
-matvec     config 1 on the GPU: one 512x2048 dequant-matvec
+prefill    config 4: T tokens through the 40-block stack (INT4 scheme); one GPU = grouped tensor-core path,
+           several GPUs = experts sharded over the ranks, token dispatch/combine over NVLink peer memory
+pack       config 5: GPU quantisation of expert tensors into the packed blob layout; several GPUs = layers
+           split over the ranks, no communication
+matvec     config 1 on the GPU (512 x 2048, launch-bound) and an HBM-sized matrix of the lm_head shape
 
-Each prints one JSON line with the same keys as the default workload.
+Every function returns a dict (one JSON line's worth).  A timed figure is the median over several repeats of its
+timed region (CUDA events on the engine's stream, max over ranks per repeat), so that short regions give steady numbers.
 """
 from __future__ import annotations
 
-import json
 import time
+from typing import Callable, List, Optional
 
 import numpy as np
 
@@ -20,42 +24,81 @@ from moe_infer_b200.native import Dims, NativeEngine, PinnedArray
 
 from . import benchlib, synth
 
-
 # Router logits of random weights have a spread of about +-2.5; the Zipf(1.1) popularity prior ln p_e spans 6.1.
 # Scaling the prior by this factor gives the hottest expert about 40 of 64 tokens, as config 3 asks.
 ZIPF_STRENGTH = 0.5
+MIN_REPEATS = 5
 
 
-def _line(args, world, metric, unit, value, ms_per_step, workload, roofline, e2e, launches, clocks, extra=None,
-          dtype="bf16 x 4-bit -> f32"):
-    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": {"workload": workload},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline}
-    if extra:
-        line["config"].update(extra)
-    return line
-
-
-def _time_loop(eng, fn, warmup, steps, local):
+def timed_repeats(eng: NativeEngine, fn: Callable[[int], None], warmup: int, steps: int, dist=None,
+                  min_repeats: int = MIN_REPEATS, fill_s: float = 0.0, max_repeats: int = 400) -> dict:
+    """Runs `warmup` untimed steps, then repeats a region of exactly `steps` steps at least `min_repeats` times (and
+    until `fill_s` seconds of device time have passed); every region is bracketed by a barrier + synchronize and timed
+    with CUDA events, max over ranks.  Returns the median region and the launch count of one region."""
     for i in range(warmup):
         fn(i)
     eng.sync()
-    n0 = eng.launch_count()
-    with benchlib.ClockSampler(local) as clk:
-        eng.timer_start()
+    regions: List[float] = []
+    launches = 0
+    i0 = warmup
+    while len(regions) < min_repeats or (sum(regions) / 1e3 < fill_s and len(regions) < max_repeats):
+        if dist is not None:
+            dist.barrier()
+        n0 = benchlib.launch_count(eng)
+        benchlib.timer_start(eng)
         for i in range(steps):
-            fn(warmup + i)
-        ms = eng.timer_stop()
+            fn(i0 + i)
+        ms = benchlib.timer_stop(eng)
         eng.sync()
-    return ms, eng.launch_count() - n0, clk.summary()
+        launches = benchlib.launch_count(eng) - n0
+        if dist is not None:
+            dist.barrier()
+            ms = dist.max(ms)
+        regions.append(ms)
+        i0 += steps
+    med = float(np.median(regions))
+    return {"ms": med, "ms_per_step": med / steps, "repeats": len(regions), "min_ms": float(min(regions)),
+            "max_ms": float(max(regions)), "launches": int(launches)}
 
 
-def run_layer(args, rank, world, local, dist):
-    n_copies = 12  # 12 x 453 MB of experts: the weights a step touches were evicted from L2 long ago
-    dims = Dims(num_layers=n_copies)
-    eng = NativeEngine(dims, device=local)
-    benchlib.populate_synthetic(eng, base_seed=args.seed)
+def hbm_roofline(kernel: str, bytes_per_step: float, ms_per_step: float, traffic=None, **extra) -> dict:
+    peaks = benchlib.measured_peaks()
+    ach = bytes_per_step / (ms_per_step / 1e3) / 1e9
+    r = {"bound": "hbm", "kernel": kernel, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+         "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"], "frac_of_nominal_8TBs": ach / 8000.0,
+         "bytes_per_step": bytes_per_step, "traffic": traffic}
+    r.update(extra)
+    return r
+
+
+def tensor_roofline(kernel: str, flops_per_step: float, ms_per_step: float, n_gpus: int = 1, **extra) -> dict:
+    peaks = benchlib.measured_peaks()
+    tf = flops_per_step / (ms_per_step / 1e3) / 1e12
+    r = {"bound": "tensor", "kernel": kernel, "achieved": tf / n_gpus, "peak": peaks["bf16_tflops_sustained"],
+         "unit": "TFLOP/s per GPU", "frac": tf / n_gpus / peaks["bf16_tflops_sustained"],
+         "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "flops_per_step": flops_per_step,
+         "aggregate_tflops": tf, "traffic": None}
+    r.update(extra)
+    return r
+
+
+def layer_flops(d: Dims, n_tokens: int) -> float:
+    """Useful flops of one MoE block over n tokens: routed experts, shared expert, router, gate score."""
+    H, I, E, K = d.hidden, d.inter, d.num_experts, d.top_k
+    return float(n_tokens) * (K * 6 * H * I + 6 * H * d.shared_inter + 2 * E * H + 2 * H)
+
+
+def rel_l2(a, b) -> float:
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+# ─── config 2: one block, one token ───────────────────────────────────────────
+
+def run_layer(args, eng: NativeEngine, local: int) -> dict:
+    dims = eng.dims
+    n_copies = dims.num_layers  # distinct layer copies: the weights a step touches were evicted from L2 long ago
     H = dims.hidden
     emb = synth.hidden_states(args.seed, 2, 64, H)
     d_in = eng.alloc(emb.nbytes).upload(emb)
@@ -64,258 +107,206 @@ def run_layer(args, rank, world, local, dist):
     def step(i):
         eng.layer_forward_dev(i % n_copies, d_in.ptr + (i % 64) * H * 4, 1, d_out.ptr + (i % 64) * H * 4)
 
-    ms, launches, clocks = _time_loop(eng, step, args.warmup, args.steps, local)
-    pin = PinnedArray((1, H), np.float32)
-    pin.array[:] = emb[:1]
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        eng.layer_forward(i % n_copies, pin.array)
-    e2e_s = time.perf_counter() - t0
-    peaks = benchlib.measured_peaks()
+    t = timed_repeats(eng, step, args.warmup, args.steps)
     b = benchlib.layer_token_bytes(dims)
-    ach = b / (ms / args.steps / 1e3) / 1e9
-    roof = {"bound": "hbm", "kernel": "decode_fused_kernel (1 layer)", "achieved": ach, "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            "frac_of_nominal_8TBs": ach / 8000.0, "bytes_per_launch": b, "traffic": None}
-    if rank == 0:
-        print(json.dumps(_line(args, world, "moe_layer_decode_tokens_per_s", "layer-tok/s", args.steps / (ms / 1e3),
-                               ms / args.steps, "config 2: one MoE layer, batch-1 decode, 256 experts top-8, BQ4; "
-                               f"rotating over {n_copies} layer copies (L2 cannot hold them)", roof,
-                               {"value": args.steps / e2e_s, "unit": "layer-tok/s", "h2d_bytes_per_step": H * 4,
-                                "d2h_bytes_per_step": H * 4 + 64}, launches, clocks,
-                               dtype="u4 weights x 24-bit fixed-point activations (three s8 digits), exact s32 dp4a sums, f32 scales")),
-              flush=True)
-    eng.close()
+    out = {"workload": f"config 2: one MoE layer, batch-1 decode, {dims.num_experts} experts top-{dims.top_k}, BQ4; "
+                       f"rotating over {n_copies} layer copies (L2 cannot hold them)",
+           "us_per_layer": t["ms_per_step"] * 1e3, "repeats": t["repeats"], "gpu_launches": t["launches"],
+           "roofline": hbm_roofline("decode_fused_kernel (1 layer)", b, t["ms_per_step"])}
+    d_in.free()
+    d_out.free()
+    return out
 
 
-def run_batched(args, rank, world, local, dist, n_tokens, n_layers, scheme, zipf, workload, metric):
-    dims = Dims(num_layers=n_layers, scheme=scheme)
-    eng = NativeEngine(dims, device=local)
-    benchlib.populate_synthetic(eng, base_seed=args.seed, config_id=4 if scheme == L.SCHEME_INT4 else 3)
-    H, E, K, I = dims.hidden, dims.num_experts, dims.top_k, dims.inter
+# ─── config 3: 64 tokens, Zipf routing ────────────────────────────────────────
+
+def run_batched64(args, eng: NativeEngine, local: int, n_tokens: int = 64) -> dict:
+    dims = eng.dims
+    H, E, K = dims.hidden, dims.num_experts, dims.top_k
+    n_layers = dims.num_layers
     emb = synth.hidden_states(args.seed, 3, n_tokens, H)
     d_in = eng.alloc(emb.nbytes).upload(emb)
     d_out = eng.alloc(emb.nbytes)
     d_idx = eng.alloc(n_tokens * K * 4)
     d_w = eng.alloc(n_tokens * K * 4)
-    d_bias = None
-    if zipf:
-        bias = synth.zipf_logit_bias(args.seed, E, alpha=1.1, strength=ZIPF_STRENGTH)
-        d_bias = eng.alloc(bias.nbytes).upload(bias)
-    single = n_layers if zipf else 0  # zipf workload: one block per step, rotating over the copies
+    bias = synth.zipf_logit_bias(args.seed, E, alpha=1.1, strength=ZIPF_STRENGTH)
+    d_bias = eng.alloc(bias.nbytes).upload(bias)
 
     def step(i):
-        if single:
-            eng.layer_forward_dev(i % n_layers, d_in.ptr, n_tokens, d_out.ptr, out_idx=d_idx.ptr, out_w=d_w.ptr,
-                                  logit_bias=d_bias.ptr if d_bias else 0)
-        else:
-            eng.forward_hidden_dev(d_in.ptr, n_tokens, True, d_out.ptr)
+        eng.layer_forward_dev(i % n_layers, d_in.ptr, n_tokens, d_out.ptr, out_idx=d_idx.ptr, out_w=d_w.ptr,
+                              logit_bias=d_bias.ptr)
 
-    ms, launches, clocks = _time_loop(eng, step, args.warmup, args.steps, local)
-    ms_step = ms / args.steps
-    # end to end through the host-pointer entry point
-    pin_in = PinnedArray((n_tokens, H), np.float32)
-    pin_in.array[:] = emb
-    pin_out = PinnedArray((n_tokens, H), np.float32)
-    reps = max(1, min(args.steps, 20))
-    if single:
-        eng.layer_forward(0, pin_in.array, logit_bias=None if not zipf else bias)
-        t0 = time.perf_counter()
-        for i in range(reps):
-            eng.layer_forward(i % n_layers, pin_in.array, logit_bias=None if not zipf else bias)
-    else:
-        eng.forward_hidden(pin_in.array, batched=True, out=pin_out.array)
-        t0 = time.perf_counter()
-        for i in range(reps):
-            eng.forward_hidden(pin_in.array, batched=True, out=pin_out.array)
-    e2e_s = (time.perf_counter() - t0) / reps
-    peaks = benchlib.measured_peaks()
+    t = timed_repeats(eng, step, args.warmup, args.steps)
+    idx = d_idx.download(np.int32, (n_tokens, K))
+    counts = np.bincount(idx.ravel(), minlength=E)
+    U = int((counts > 0).sum())
     lay = eng.layout["expert_size"]
-    layers_per_step = 1 if single else n_layers
-    flops_layer = n_tokens * K * 6 * H * I + n_tokens * 6 * H * I + n_tokens * 2 * E * H + n_tokens * 2 * H
-    extra = {"tokens_per_step": n_tokens, "layers_per_step": layers_per_step}
-    if zipf:
-        idx = d_idx.download(np.int32, (n_tokens, K))
-        counts = np.bincount(idx.ravel(), minlength=E)
-        U = int((counts > 0).sum())
-        router_b = E * H * 2 if scheme == L.SCHEME_BQ4 else E * H // 2 + 2 * E * (H // 64) * 2
-        b = U * lay + lay + 1152 + router_b + n_tokens * H * (2 + 4)
-        ach = b / (ms_step / 1e3) / 1e9
-        roof = {"bound": "hbm", "kernel": "grouped_gemm_kernel<1>+<2>", "achieved": ach, "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                "bytes_per_step": b, "tflops": flops_layer / (ms_step / 1e3) / 1e12, "traffic": None}
-        extra.update({"distinct_experts_hit": U, "max_tokens_per_expert": int(counts.max()),
-                      "l2": f"rotating over {n_layers} layer copies"})
-    else:
-        tf = flops_layer * layers_per_step / (ms_step / 1e3) / 1e12
-        roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<1>+<2>", "achieved": tf,
-                "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops_sustained"],
-                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "flops_per_step": flops_layer * layers_per_step,
-                "traffic": None}
-        extra.update({"l2": "each layer reads 455 MB of unique weights (> 126 MB L2)"})
-    tok_s = n_tokens / (ms_step / 1e3)
-    if rank == 0:
-        print(json.dumps(_line(args, world, metric, "tok/s", tok_s, ms_step, workload, roof,
-                               {"value": n_tokens / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": n_tokens * H * 4,
-                                "d2h_bytes_per_step": n_tokens * H * 4}, launches, clocks, extra)), flush=True)
-    eng.close()
+    router_b = E * H * 2 if dims.scheme == L.SCHEME_BQ4 else E * H // 2 + 2 * E * (H // 64) * 2
+    b = U * lay + lay + 1152 + router_b + n_tokens * H * (2 + 4)
+    # parity of the grouped path (bf16 operands) against the decode path (f32-class) on the same tokens and layer
+    last = (args.warmup + t["repeats"] * args.steps - 1) % n_layers
+    got = d_out.download(np.float32, (n_tokens, H))
+    errs = []
+    for tok in range(min(8, n_tokens)):
+        ref, _, _ = eng.layer_forward(last, emb[tok], logit_bias=bias)
+        errs.append(rel_l2(got[tok] - emb[tok], ref[0] - emb[tok]))
+    out = {"workload": f"config 3: {n_tokens} tokens through one MoE layer, top-{K} of {E}, Zipf(1.1) routing, BQ4; "
+                       f"rotating over {n_layers} layer copies",
+           "ms_per_step": t["ms_per_step"], "tok_per_s": n_tokens / (t["ms_per_step"] / 1e3), "repeats": t["repeats"],
+           "gpu_launches": t["launches"], "distinct_experts_hit": U, "max_tokens_per_expert": int(counts.max()),
+           "parity_rel_l2_vs_decode_path": float(max(errs)),
+           "roofline": hbm_roofline("grouped_gemm_kernel<1>+<2>", b, t["ms_per_step"],
+                                    tflops=layer_flops(dims, n_tokens) / (t["ms_per_step"] / 1e3) / 1e12)}
+    for buf in (d_in, d_out, d_idx, d_w, d_bias):
+        buf.free()
+    return out
 
 
-def run_prefill_ep(args, rank, world, local, dist):
-    """Config 4 across `world` GPUs: experts sharded 256/P, tokens T/P per rank, dispatch/combine over peer memory."""
-    from moe_infer_b200 import ep as ephost
-    T = args.tokens or 4096
-    n_local = T // world
-    dims = Dims(num_layers=args.layers, scheme=L.SCHEME_INT4)
+# ─── config 4: prefill ────────────────────────────────────────────────────────
+
+def run_prefill(args, rank: int, world: int, local: int, dist, n_tokens: int = 4096, layers: Optional[int] = None) -> dict:
+    """T tokens through the INT4-scheme stack.  world == 1: the grouped path on one GPU.  world > 1: experts sharded
+    E / world per rank, tokens T / world per rank, dispatch and combine over peer memory (strong scaling)."""
+    layers = layers or args.layers
+    dims = Dims(num_layers=layers, scheme=L.SCHEME_INT4)
     eng = NativeEngine(dims, device=local)
     benchlib.populate_synthetic(eng, base_seed=args.seed, config_id=4)  # same seed on every rank: replicated tensors agree
-    H, E, K, I = dims.hidden, dims.num_experts, dims.top_k, dims.inter
-    emb = synth.hidden_states(args.seed, 3, T, H)[rank * n_local:(rank + 1) * n_local]
+    H, E, K = dims.hidden, dims.num_experts, dims.top_k
+    n_local = n_tokens // world
+    emb_all = synth.hidden_states(args.seed, 3, n_tokens, H)
+    emb = emb_all[rank * n_local:(rank + 1) * n_local]
     d_in = eng.alloc(emb.nbytes).upload(emb)
     d_out = eng.alloc(emb.nbytes)
-    eng.ep_init(ephost.exchange_handles(eng.ep_export(rank, world, n_local)))
-    dist.barrier()
+    steps = max(1, min(args.steps, 5))
+    warm = max(3, min(args.warmup, 5))
+    if world > 1:
+        from moe_infer_b200 import ep as ephost
+        eng.ep_init(ephost.exchange_handles(eng.ep_export(rank, world, n_local)))
+        dist.barrier()
 
-    def step(i):
-        eng.ep_forward_hidden_dev(d_in.ptr, n_local, d_out.ptr)
+        def step(i):
+            eng.ep_forward_hidden_dev(d_in.ptr, n_local, d_out.ptr)
+    else:
+        def step(i):
+            eng.forward_hidden_dev(d_in.ptr, n_local, True, d_out.ptr)
 
-    for i in range(args.warmup):
-        step(i)
+    t = timed_repeats(eng, step, warm, steps, dist if world > 1 else None)
+    finite = bool(np.isfinite(d_out.download(np.float32, (n_local, H))).all())
+    # parity, outside the timed region: layer 0 over this rank's tokens as the timed path computes it, against the
+    # single-GPU entry point on the first 64 of them (every rank holds all experts of this synthetic store), and
+    # against the decode path (f32-class arithmetic) on the first 8
+    n_chk = min(64, n_local)
+    if world > 1:
+        eng.ep_layer_forward_dev(0, d_in.ptr, n_local, d_out.ptr)
+    else:
+        eng.layer_forward_dev(0, d_in.ptr, n_local, d_out.ptr)
     eng.sync()
-    dist.barrier()
-    n0 = eng.launch_count()
-    with benchlib.ClockSampler(local) as clk:
-        eng.timer_start()
-        for i in range(args.steps):
-            step(i)
-        ms = eng.timer_stop()
-        eng.sync()
-    launches = eng.launch_count() - n0
-    dist.barrier()
-    ms = dist.max(ms)
-    out = d_out.download(np.float32, (n_local, H))
-    finite = bool(np.isfinite(out).all())
-    ms_step = ms / args.steps
-    flops_layer = T * K * 6 * H * I + T * 6 * H * I + T * 2 * E * H + T * 2 * H
-    tf = flops_layer * args.layers / (ms_step / 1e3) / 1e12
-    peaks = benchlib.measured_peaks()
-    roof = {"bound": "tensor", "kernel": "grouped_gemm_kernel<1>+<2> (per GPU)", "achieved": tf / world,
-            "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
-            "frac": tf / world / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
-            "aggregate_tflops": tf, "traffic": None}
-    dist.barrier()
+    got = d_out.download(np.float32, (n_local, H))[:n_chk]
+    parity_single = None
+    if world > 1:
+        if rank == 0:
+            single, _, _ = eng.layer_forward(0, emb[:n_chk])
+            parity_single = rel_l2(got - emb[:n_chk], single - emb[:n_chk])
+        dist.barrier()
+    errs = []
     if rank == 0:
-        line = _line(args, world, "moe_prefill_tokens_per_s", "tok/s", T / (ms_step / 1e3), ms_step,
-                     f"config 4: {T}-token prefill through {args.layers} MoE layers, INT4 scheme, experts sharded "
-                     f"{E}/{world} per GPU, token dispatch/combine over NVLink peer memory", roof,
-                     {"value": None, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, launches,
-                     clk.summary(), {"tokens_per_step": T, "tokens_per_rank": n_local, "finite": finite,
-                                     "parallelism": f"ep{world}"})
-        line["scaling"] = "strong"
-        print(json.dumps(line), flush=True)
-    dist.barrier()
+        for tok in range(min(8, n_chk)):
+            ref, _, _ = eng.layer_forward(0, emb[tok])
+            errs.append(rel_l2(got[tok] - emb[tok], ref[0] - emb[tok]))
+    fl = layer_flops(dims, n_tokens) * layers
+    ms_step = t["ms_per_step"]
+    out = {"workload": f"config 4: {n_tokens}-token prefill through {layers} MoE layers, INT4 scheme, attention passed through; "
+                       + (f"experts sharded {E}/{world} per GPU, tokens {n_local} per GPU, dispatch/combine over NVLink peer memory"
+                          if world > 1 else "1 GPU"),
+           "n_gpus": world, "parallelism": f"ep{world}" if world > 1 else "single", "scaling": "strong",
+           "ms_per_step": ms_step, "tok_per_s": n_tokens / (ms_step / 1e3), "tflops": fl / (ms_step / 1e3) / 1e12,
+           "repeats": t["repeats"], "steps_per_repeat": steps, "gpu_launches": t["launches"], "finite": finite,
+           "parity_rel_l2_vs_decode_path": float(max(errs)) if errs else None,
+           "parity_rel_l2_vs_single_gpu": parity_single,
+           "l2": "each layer reads 455 MB of unique weights (> 126 MB L2)",
+           "roofline": tensor_roofline("grouped_gemm_kernel<1>+<2>", fl, ms_step, world)}
+    d_in.free()
+    d_out.free()
+    if world > 1:
+        dist.barrier()
     eng.close()
+    return out
 
 
-def run_pack(args, rank, world, local, dist):
+# ─── config 5: packer ─────────────────────────────────────────────────────────
+
+def run_pack(args, rank: int, world: int, local: int, dist) -> dict:
+    """One step = this rank's share of a 40-layer checkpoint's expert tensors (40 / world layers) packed into the blob
+    layout; ranks work on disjoint layers with no communication, the figure is the aggregate."""
     dims = Dims(num_layers=1)
     eng = NativeEngine(dims, device=local)
     H, I, E = dims.hidden, dims.inter, dims.num_experts
+    total_layers = 40
+    my_layers = len(range(rank, total_layers, world))
     n_src = 3  # three distinct 1.6 GB source sets, rotated: 4.8 GB >> L2
     gus, dns = [], []
     for s in range(n_src):
         gu = eng.alloc(E * 2 * I * H * 2)
         dn = eng.alloc(E * H * I * 2)
-        eng.synth_normal(gu.ptr, L.DT_BF16, E * 2 * I * H, 100 + s, 0.02, 0.001, 0.4)
-        eng.synth_normal(dn.ptr, L.DT_BF16, E * H * I, 200 + s, 0.02, 0.001, 0.4)
+        benchlib.synth_normal(eng, gu.ptr, L.DT_BF16, E * 2 * I * H, 100 + s + 10 * rank, 0.02, 0.001, 0.4)
+        benchlib.synth_normal(eng, dn.ptr, L.DT_BF16, E * H * I, 200 + s + 10 * rank, 0.02, 0.001, 0.4)
         gus.append(gu)
         dns.append(dn)
     blob = eng.layer_dev(0)
 
     def step(i):
-        eng.pack_experts_dev(gus[i % n_src].ptr, dns[i % n_src].ptr, L.DT_BF16, E, blob)
+        for l in range(my_layers):
+            k = (i * my_layers + l) % n_src
+            eng.pack_experts_dev(gus[k].ptr, dns[k].ptr, L.DT_BF16, E, blob)
 
-    ms, launches, clocks = _time_loop(eng, step, args.warmup, args.steps, local)
-    elems = E * 3 * I * H
+    steps = max(1, min(args.steps, 3))
+    t = timed_repeats(eng, step, 3, steps, dist if world > 1 else None)
+    elems = float(E * 3 * I * H) * total_layers
     b = elems * 2 + elems * 0.5625
-    peaks = benchlib.measured_peaks()
-    ach = b / (ms / args.steps / 1e3) / 1e9
-    roof = {"bound": "hbm", "kernel": "pack_int4_kernel<bf16>", "achieved": ach, "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"], "bytes_per_step": b,
-            "traffic": None}
-    # end to end: 8 experts from pinned host memory and back
-    n_e = 8
-    gu_h = PinnedArray((n_e, 2 * I, H), np.uint16)
-    dn_h = PinnedArray((n_e, H, I), np.uint16)
-    gu_h.array[:] = 0x3C00
-    dn_h.array[:] = 0x3C00
-    eng.pack_experts(gu_h.array, dn_h.array)
-    t0 = time.perf_counter()
-    for _ in range(3):
-        eng.pack_experts(gu_h.array, dn_h.array)
-    e2e_s = (time.perf_counter() - t0) / 3
-    if rank == 0:
-        print(json.dumps(_line(args, world, "quantize_GB_per_s", "GB/s", ach, ms / args.steps,
-                               "config 5: one layer's experts (256 x 3 matrices of 1,048,576 bf16, 0.1% outliers) -> packed blob",
-                               roof, {"value": n_e * 3 * I * H * 2.5625 / e2e_s / 1e9, "unit": "GB/s",
-                                      "h2d_bytes_per_step": n_e * 3 * I * H * 2,
-                                      "d2h_bytes_per_step": n_e * eng.layout["expert_size"]},
-                               launches, clocks, {"full_checkpoint_ms_extrapolated": ms / args.steps * 40.1},
-                               dtype="f32 (exactly rounded), u8 nibbles")), flush=True)
+    ms_step = t["ms_per_step"]
+    per_gpu_b = (float(E * 3 * I * H) * my_layers) * 2.5625
+    out = {"workload": f"config 5: the experts of a 40-layer checkpoint (40 x 256 x 3 matrices of 1,048,576 bf16, 0.1% outliers) "
+                       f"-> packed blobs; layers split over {world} GPU(s), no communication",
+           "n_gpus": world, "ms_per_checkpoint": ms_step, "GB_per_s": b / (ms_step / 1e3) / 1e9, "repeats": t["repeats"],
+           "gpu_launches": t["launches"], "layers_per_gpu": my_layers,
+           "roofline": hbm_roofline("pack_int4_kernel<bf16> (per GPU)", per_gpu_b, ms_step)}
+    for buf in gus + dns:
+        buf.free()
     eng.close()
+    return out
 
 
-def run_matvec(args, rank, world, local, dist):
-    dims = Dims(num_experts=4, top_k=4, num_layers=1)
-    eng = NativeEngine(dims, device=local)
-    rows, cols = 512, 2048
-    n_copies = 512  # 512 x 0.59 MB = 302 MB of distinct matrices, rotated
+# ─── config 1 on the GPU, and the matvec at HBM size ──────────────────────────
+
+def run_matvec(args, eng: NativeEngine, local: int, rows: int = 512, cols: int = 2048, copies: int = 512) -> dict:
     wb, sb = rows * cols // 2, rows * (cols // 64) * 2
-    w = eng.alloc(n_copies * wb)
-    s = eng.alloc(n_copies * sb)
-    b = eng.alloc(n_copies * sb)
-    src = eng.alloc(n_copies * rows * cols * 2)
-    eng.synth_normal(src.ptr, L.DT_BF16, n_copies * rows * cols, 7, 0.02)
-    eng.pack_int4_dev(src.ptr, L.DT_BF16, n_copies * rows, cols, w.ptr, s.ptr, b.ptr)
+    w = eng.alloc(copies * wb)
+    s = eng.alloc(copies * sb)
+    b = eng.alloc(copies * sb)
+    chunk_rows = min(copies * rows, 65536)
+    src = eng.alloc(chunk_rows * cols * 2)
+    done = 0
+    while done < copies * rows:  # pack in chunks so the bf16 source stays small
+        n = min(chunk_rows, copies * rows - done)
+        benchlib.synth_normal(eng, src.ptr, L.DT_BF16, n * cols, 7 + done, 0.02)
+        eng.pack_int4_dev(src.ptr, L.DT_BF16, n, cols, w.ptr + done * (cols // 2), s.ptr + done * (cols // 64) * 2,
+                          b.ptr + done * (cols // 64) * 2)
+        done += n
     x = synth.hidden_states(0, 1, 1, cols)
     dx = eng.alloc(x.nbytes).upload(x)
     dy = eng.alloc(rows * 4)
 
     def step(i):
-        c = i % n_copies
+        c = i % copies
         eng.matvec_int4_dev(w.ptr + c * wb, s.ptr + c * sb, b.ptr + c * sb, dx.ptr, dy.ptr, rows, cols)
 
-    ms, launches, clocks = _time_loop(eng, step, args.warmup, args.steps, local)
-    by = 595968
-    peaks = benchlib.measured_peaks()
-    ach = by / (ms / args.steps / 1e3) / 1e9
-    roof = {"bound": "hbm (launch-latency dominated at this size)", "kernel": "matvec_int4_kernel", "achieved": ach,
-            "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            "bytes_per_launch": by, "traffic": None}
-    if rank == 0:
-        print(json.dumps(_line(args, world, "matvec_GB_per_s", "GB/s", ach, ms / args.steps,
-                               "config 1 on the GPU: one 512x2048 4-bit dequant-matvec per launch", roof,
-                               {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                               launches, clocks, dtype="f32 accumulate over 4-bit weights")), flush=True)
-    eng.close()
-
-
-def run(args, rank, world, local, dist):
-    if args.workload == "layer":
-        run_layer(args, rank, world, local, dist)
-    elif args.workload == "batched64":
-        run_batched(args, rank, world, local, dist, args.tokens or 64, 8, L.SCHEME_BQ4, True,
-                    "config 3: 64 tokens through one MoE layer, top-8 of 256, Zipf(1.1) routing, BQ4",
-                    "moe_batched_decode_tokens_per_s")
-    elif args.workload == "prefill" and world > 1:
-        run_prefill_ep(args, rank, world, local, dist)
-    elif args.workload == "prefill":
-        run_batched(args, rank, world, local, dist, args.tokens or 4096, args.layers, L.SCHEME_INT4, False,
-                    f"config 4: {args.tokens or 4096}-token prefill through {args.layers} MoE layers, INT4 scheme, "
-                    "attention passed through, 1 GPU", "moe_prefill_tokens_per_s")
-    elif args.workload == "pack":
-        run_pack(args, rank, world, local, dist)
-    elif args.workload == "matvec":
-        run_matvec(args, rank, world, local, dist)
-    else:
-        raise SystemExit(f"unknown workload {args.workload}")
+    steps = args.steps if rows <= 4096 else max(1, min(args.steps, 20))
+    t = timed_repeats(eng, step, max(3, min(args.warmup, 10)), steps)
+    by = wb + 2 * sb + cols * 4 + rows * 4
+    out = {"workload": f"{rows} x {cols} 4-bit dequant-matvec per launch, rotating over {copies} distinct matrices "
+                       f"({copies * (wb + 2 * sb) / 1e6:.0f} MB)",
+           "us_per_call": t["ms_per_step"] * 1e3, "repeats": t["repeats"], "gpu_launches": t["launches"],
+           "roofline": hbm_roofline("matvec_int4_kernel", by, t["ms_per_step"])}
+    for buf in (w, s, b, src, dx, dy):
+        buf.free()
+    return out

@@ -249,24 +249,30 @@ int moe_ep_forward_hidden_dev(moe_engine_t* e, const float* emb_dev, int32_t n_l
  * It needs no engine.  It computes what moe_layer_forward_dev computes for one
  * token (n_tokens == 1, no logit bias, no forced indices) from tensor pointers
  * the caller owns (all device memory, in the reference's byte layout), and
- * keeps its work areas (router logits, SwiGLU outputs, barrier words, one layer
- * descriptor) in a 40 KiB array that is part of the library image; every GPU
- * that loads the library holds that array until the process exits.
+ * keeps its work areas (router logits, SwiGLU outputs, barrier words) in a
+ * 40 KiB array that is part of the library image; every GPU that loads the
+ * library holds that array until the process exits.
  *
  *  - Limits: hidden 2048, inter = shared_inter = 512, group 64, top_k <= 8,
  *    num_experts <= 512 (the array has room for 512 router logits); anything
  *    else is rejected with MOE_ERR_INVALID and a message.
  *  - It calls no cudaMalloc, cudaFree or other allocating routine.
  *  - The first call on a device looks up the array's device address and sets the
- *    kernel's shared-memory attribute; make that first call before any stream
- *    capture begins.
+ *    kernel's shared-memory attribute (under a lock: two host threads may race
+ *    on a device's first call); make that first call before any stream capture
+ *    begins.
  *  - All calls on a device share the one array and it keeps the previous call's
  *    contents; the words that must start at zero are cleared on the given stream
  *    at every call.  Two calls that overlap on the same GPU (different streams,
  *    or different threads) race on the array: serialise them.
  *  - `cuda_stream` is a cudaStream_t (NULL = the default stream).  With wait == 0
- *    the call returns after enqueueing; with wait != 0 it waits for the stream
- *    and reports a device-side bounded-wait failure as MOE_ERR_DEVICE_WAIT. */
+ *    the call returns after enqueueing and NEVER reports a device-side
+ *    bounded-wait failure: the error word stays in the array until the next call
+ *    on that device clears it, so a caller that enqueues must ask
+ *    moe_layer_decode_noalloc_status (below) before its next call if it wants to
+ *    know.  With wait != 0 the call waits for the stream and reports such a
+ *    failure as MOE_ERR_DEVICE_WAIT.
+ *  - h_out_dev may be the same buffer as h_in_dev. */
 typedef struct {
     const void* experts;     /* num_experts packed experts (moe_expert_layout), back to back */
     const void* post_norm;   /* bf16 [hidden] */
@@ -282,14 +288,11 @@ typedef struct {
 int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, const moe_layer_ptrs_t* layer_ptrs_dev,
                              const float* h_in_dev, float* h_out_dev, int32_t* out_idx_dev /* nullable */,
                              float* out_w_dev /* nullable */, void* cuda_stream, int wait);
-
-/* ── synthetic data ──────────────────────────────────────────────────────────
- * No counterpart in the reference (it reads real checkpoints): fills a device
- * buffer with seeded N(0, sigma^2) values, a fraction `outlier_frac` of them
- * replaced by +-outlier_value; f32 or bf16.  Used to build synthetic
- * checkpoints of the reference's shapes for benchmarks and full-size tests. */
-int moe_synth_normal_dev(moe_engine_t* e, void* dst_dev, int dtype, int64_t n, uint64_t seed, float sigma,
-                         float outlier_frac, float outlier_value);
+/* No counterpart in the reference.  Waits for `cuda_stream` on `device` and reads the error word the last
+ * moe_layer_decode_noalloc call on that device left in the array: *code == 0 and MOE_OK when every device-side
+ * wait completed, the code and MOE_ERR_DEVICE_WAIT otherwise.  Allocates nothing.  For callers that enqueue
+ * with wait == 0. */
+int moe_layer_decode_noalloc_status(int device, void* cuda_stream, unsigned int* code);
 
 /* ── plain device-memory helpers for hosts without a CUDA binding ──────────── */
 int moe_dev_alloc(moe_engine_t* e, size_t bytes, void** out_dev);
@@ -299,13 +302,6 @@ int moe_dev_download(moe_engine_t* e, void* dst_host, const void* src_dev, size_
 int moe_dev_memset(moe_engine_t* e, void* dst_dev, int value, size_t bytes);
 int moe_host_alloc_pinned(size_t bytes, void** out_host);
 int moe_host_free_pinned(void* p_host);
-/* CUDA-event timing on the engine's stream: elapsed milliseconds between
- * moe_timer_start and moe_timer_stop (stop waits for the stream). */
-int moe_timer_start(moe_engine_t* e);
-int moe_timer_stop(moe_engine_t* e, float* ms);
-/* Number of kernels this library has launched on the engine since creation. */
-int moe_launch_count(const moe_engine_t* e, int64_t* n);
-
 #ifdef __cplusplus
 }
 #endif

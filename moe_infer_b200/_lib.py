@@ -43,7 +43,7 @@ CHECK_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
 _vp, _i, _i32, _i64, _sz = C.c_void_p, C.c_int, C.c_int32, C.c_int64, C.c_size_t
 _pp = C.POINTER(C.c_void_p)
 
-# name -> (restype, argtypes); must list every function of include/moe_b200.h
+# name -> (restype, argtypes); must list every function the headers under include/ declare
 SIGNATURES = {
     "moe_last_error": (C.c_char_p, []),
     "moe_version": (C.c_char_p, []),
@@ -82,6 +82,7 @@ SIGNATURES = {
     "moe_ep_layer_forward_dev": (_i, [_vp, _i, _vp, _i32, _vp]),
     "moe_ep_forward_hidden_dev": (_i, [_vp, _vp, _i32, _vp]),
     "moe_layer_decode_noalloc": (_i, [C.POINTER(MoeDims), _i, C.POINTER(LayerPtrs), _vp, _vp, _vp, _vp, _vp, _i]),
+    "moe_layer_decode_noalloc_status": (_i, [_i, _vp, C.POINTER(C.c_uint)]),
     "moe_synth_normal_dev": (_i, [_vp, _vp, _i, _i64, C.c_uint64, C.c_float, C.c_float, C.c_float]),
     "moe_dev_alloc": (_i, [_vp, _sz, _pp]),
     "moe_dev_free": (_i, [_vp, _vp]),

@@ -31,6 +31,7 @@
 // Every wait (grid barrier, mbarrier, tag poll) is bounded and a timeout raises an
 // error word instead of hanging.
 #include "decode_common.cuh"
+#include <mutex>
 
 namespace moe {
 
@@ -48,7 +49,8 @@ constexpr int kMaxCRows = 14;       // ceil(H / grid) output elements
     } while (0)
 
 struct DecodeParams {
-    const LayerDev* layers;
+    const LayerDev* layers;  // table in device memory, or nullptr: then `one` is the only layer
+    LayerDev one;
     int l0, l1;
     const float* h_in;
     float* h_out;
@@ -426,10 +428,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
     uint32_t parity = 0;
     bool alive = true;
 
-    prefetch_A(sm, p.layers[p.l0], L, cta, G, E, tid);
+    prefetch_A(sm, p.layers ? p.layers[p.l0] : p.one, L, cta, G, E, tid);
 
     for (int l = p.l0; l < p.l1 && alive; ++l) {
-        const LayerDev ly = p.layers[l];
+        const LayerDev ly = p.layers ? p.layers[l] : p.one;
         const float* h_cur = (l == p.l0) ? p.h_in : (((l - p.l0) & 1) ? p.h_buf0 : p.h_buf1);
         float* h_nxt = (l == p.l1 - 1) ? p.h_out : (((l - p.l0) & 1) ? p.h_buf1 : p.h_buf0);
 
@@ -527,7 +529,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_stack_kernel(DecodePara
             }
         }
         prefetch_C_warp(sm, ly, L, r0, nc, K, warp, lane);
-        if (l + 1 < p.l1) prefetch_A(sm, p.layers[l + 1], L, cta, G, E, tid);
+        if (l + 1 < p.l1) prefetch_A(sm, p.layers ? p.layers[l + 1] : p.one, L, cta, G, E, tid);
         else cp_commit();  // keep the group count per layer fixed
         PROF(8);
         bar_target += G;
@@ -1427,8 +1429,8 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
 // running inside such a process, or a latency-critical loop in which cudaMalloc /
 // cudaFree (which synchronise the device and can fail when memory is fragmented)
 // are banned after initialisation.  For them the decode kernel's work areas (the
-// router logits, the SwiGLU outputs, the grid-barrier words, one layer
-// descriptor) live in the fixed array below instead of in engine-owned
+// router logits, the SwiGLU outputs, the grid-barrier words) live in the
+// fixed array below instead of in engine-owned
 // allocations.  The array is part of the library image: every GPU that loads
 // the library holds these 40 KiB until the process exits.
 constexpr size_t kNaSync = 0;        // 16 barrier / error words
@@ -1450,6 +1452,7 @@ constexpr int kNaMaxDevices = 64;
 // kernel can use; the device address is looked up once per device and kept here.
 static unsigned char* g_noalloc_dev_ptr[kNaMaxDevices] = {};
 static int g_noalloc_grid[kNaMaxDevices] = {};
+static std::mutex g_noalloc_mutex;  // two host threads may make a device's first call at the same time
 
 }  // namespace moe
 
@@ -1479,20 +1482,25 @@ extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, cons
     int rc = MOE_OK;
     cudaStream_t st = (cudaStream_t)cuda_stream;
     do {
-        if (!g_noalloc_dev_ptr[device]) {
-            // one-time set-up on this device (with the device current): device address of the array
-            unsigned char* ptr = nullptr;
-            cudaError_t ce = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
-            if (ce != cudaSuccess || !ptr) { rc = cuda_fail(ce, "cudaGetSymbolAddress(g_noalloc_scratch)", __FILE__, __LINE__); break; }
-            ce = cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem));
-            int sms = 0;
-            if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-            if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode set-up", __FILE__, __LINE__); break; }
-            g_noalloc_grid[device] = sms;
-            g_noalloc_dev_ptr[device] = ptr;
+        unsigned char* base = nullptr;
+        int G = 0;
+        {
+            std::lock_guard<std::mutex> lock(g_noalloc_mutex);  // held for the set-up only
+            if (!g_noalloc_dev_ptr[device]) {
+                // one-time set-up on this device (with the device current): device address of the array
+                unsigned char* ptr = nullptr;
+                cudaError_t ce = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+                if (ce != cudaSuccess || !ptr) { rc = cuda_fail(ce, "cudaGetSymbolAddress(g_noalloc_scratch)", __FILE__, __LINE__); break; }
+                ce = cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem));
+                int sms = 0;
+                if (ce == cudaSuccess) ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+                if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode set-up", __FILE__, __LINE__); break; }
+                g_noalloc_grid[device] = sms;
+                g_noalloc_dev_ptr[device] = ptr;
+            }
+            base = g_noalloc_dev_ptr[device];
+            G = g_noalloc_grid[device];
         }
-        unsigned char* base = g_noalloc_dev_ptr[device];
-        const int G = g_noalloc_grid[device];
         auto cdiv = [](int a, int b) { return (a + b - 1) / b; };
         if (!(cdiv(d.num_experts, G) <= kMaxRouterRows && cdiv(kI, G) <= kMaxSharedRows &&
               cdiv(d.top_k * kI, G) <= kMaxBItems && cdiv(kH, G) <= kMaxCRows)) {
@@ -1500,7 +1508,9 @@ extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, cons
             rc = MOE_ERR_INVALID;
             break;
         }
-        LayerDev ld{};
+        DecodeParams p{};
+        p.layers = nullptr;  // the layer travels inside the kernel parameters: no host copy is queued on the stream
+        LayerDev& ld = p.one;
         ld.experts = (const uint8_t*)lp->experts;
         ld.post_norm = (const uint16_t*)lp->post_norm;
         ld.router_bf16 = (const uint16_t*)lp->router_bf16;
@@ -1513,10 +1523,7 @@ extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, cons
         ld.sgate.b = (const uint16_t*)lp->sgate_b;
         // the array keeps whatever the previous call left: the barrier and error words must start at zero
         cudaError_t ce = cudaMemsetAsync(base + kNaSync, 0, 64, st);
-        if (ce == cudaSuccess) ce = cudaMemcpyAsync(base + kNaLayer, &ld, sizeof(ld), cudaMemcpyHostToDevice, st);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "no-alloc decode: scratch set-up", __FILE__, __LINE__); break; }
-        DecodeParams p{};
-        p.layers = reinterpret_cast<const LayerDev*>(base + kNaLayer);
         p.l0 = 0; p.l1 = 1;
         p.h_in = h_in_dev; p.h_out = h_out_dev;
         p.h_buf0 = reinterpret_cast<float*>(base + kNaH0);
@@ -1547,6 +1554,33 @@ extern "C" int moe_layer_decode_noalloc(const moe_dims_t* dims, int device, cons
     } while (0);
     cudaSetDevice(prev);
     return rc;
+}
+
+extern "C" int moe_layer_decode_noalloc_status(int device, void* cuda_stream, unsigned int* code) {
+    MOE_REQUIRE(code, "null argument");
+    MOE_REQUIRE(device >= 0 && device < kNaMaxDevices, "device %d out of range", device);
+    *code = 0;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        base = g_noalloc_dev_ptr[device];
+    }
+    if (!base) return MOE_OK;  // no call has run on this device yet
+    int prev = 0;
+    MOE_CUDA(cudaGetDevice(&prev));
+    MOE_CUDA(cudaSetDevice(device));
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    unsigned int flag = 0;
+    cudaError_t ce = cudaMemcpyAsync(&flag, base + kNaSync + 8, sizeof(flag), cudaMemcpyDeviceToHost, st);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+    cudaSetDevice(prev);
+    if (ce != cudaSuccess) return cuda_fail(ce, "no-alloc decode status", __FILE__, __LINE__);
+    *code = flag;
+    if (flag) {
+        set_error("a bounded device-side wait gave up (code %u); the result of the last no-alloc call is invalid", flag);
+        return MOE_ERR_DEVICE_WAIT;
+    }
+    return MOE_OK;
 }
 
 #ifdef MOE_DEC_SKEW

@@ -285,25 +285,6 @@ class NativeEngine:
         L.check(self.lib.moe_decode_profile(self.h, 1, tmp.ctypes.data_as(C.POINTER(C.c_int64)), n, C.byref(pts)))
         return tmp[: n * pts.value].reshape(n, pts.value)
 
-    # ── timing / accounting ──────────────────────────────────────────────
-    def timer_start(self) -> None:
-        L.check(self.lib.moe_timer_start(self.h))
-
-    def timer_stop(self) -> float:
-        ms = C.c_float()
-        L.check(self.lib.moe_timer_stop(self.h, C.byref(ms)))
-        return ms.value
-
-    def launch_count(self) -> int:
-        n = C.c_int64()
-        L.check(self.lib.moe_launch_count(self.h, C.byref(n)))
-        return n.value
-
-    def synth_normal(self, dst_dev: int, dtype: int, n: int, seed: int, sigma: float = 0.02,
-                     outlier_frac: float = 0.0, outlier_value: float = 0.4) -> None:
-        L.check(self.lib.moe_synth_normal_dev(self.h, C.c_void_p(dst_dev), dtype, n, seed, sigma, outlier_frac,
-                                              outlier_value))
-
     def alloc(self, nbytes: int) -> DevBuf:
         return DevBuf(self, nbytes)
 

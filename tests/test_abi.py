@@ -8,14 +8,20 @@ import pytest
 
 from moe_infer_b200 import _lib
 
-HEADER = os.path.join(os.path.dirname(__file__), "..", "include", "moe_b200.h")
+INCLUDE = os.path.join(os.path.dirname(__file__), "..", "include")
+HEADER = os.path.join(INCLUDE, "moe_b200.h")
 
 
 def declared_functions():
-    src = open(HEADER).read()
-    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    names = re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", src)
-    return sorted(set(n for n in names if not n.endswith("_fn")))
+    """Every function any header under include/ declares (the product ABI and the bench tooling header)."""
+    names = set()
+    for f in sorted(os.listdir(INCLUDE)):
+        if not f.endswith(".h"):
+            continue
+        src = open(os.path.join(INCLUDE, f)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        names.update(re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", src))
+    return sorted(n for n in names if not n.endswith("_fn"))
 
 
 def test_header_functions_are_exported(native_lib):

@@ -2,8 +2,8 @@
 
 The grouped path rounds activations and dequantised weights to bf16 before the
 tensor-core contraction (f32 accumulate), so it is held to the contract's
-tolerance, 1e-2 relative L2 against the CPU oracle, not to the tighter bound of
-the f32 decode path.  The router runs in f32, so the expert choices must match
+tolerance, 1e-2 relative L2 against the CPU oracle (over the batch and for every
+single token), not to the tighter bound of the decode path.  The router runs in f32, so the expert choices must match
 the oracle's exactly (no ties occur with these seeds).
 """
 import numpy as np
@@ -29,7 +29,7 @@ def _check(eng, lw, h, k, **kw):
     upd = rel_l2(out - h, ref - h)
     assert upd < TOL, upd
     per_token = np.linalg.norm((out - ref), axis=1) / np.linalg.norm(ref - h, axis=1)
-    assert per_token.max() < 3 * TOL, per_token.max()
+    assert per_token.max() < TOL, per_token.max()  # measured: about 6e-3 for the worst token, 4.5e-3 over a batch
     return upd
 
 

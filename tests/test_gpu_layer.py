@@ -1,8 +1,9 @@
 """GPU parity of the MoE block and the layer stack (decode path), through the C ABI.
 
 Tolerance: <= 1e-2 relative L2 against the CPU oracle (f32 accumulate), as the
-contract states; the decode path is f32 end to end, so the tests also hold a
-much tighter bound.  Expert choices must match exactly except where two
+contract states; the decode path keeps activations to 23 bits relative to each
+32-element chunk's maximum and sums exactly, so the tests also hold a much
+tighter bound.  Expert choices must match exactly except where two
 probabilities tie to the last bit (none occur with these seeds).
 """
 import numpy as np
