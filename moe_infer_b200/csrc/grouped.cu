@@ -45,8 +45,14 @@ constexpr int kNT = 256;   // tokens per tile (MMA N, padded to a multiple of 16
 constexpr int kProdWarps = 16;                  // operand producers / epilogue
 constexpr int kProdThreads = kProdWarps * 32;
 constexpr int kGemmThreads = kProdThreads + 32;  // + one MMA-issuing warp
-constexpr int kAStages = 2;   // dequantised weight tiles (produced locally: shallow ring)
-constexpr int kBStages = 4;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
+#ifndef MOE_AST
+#define MOE_AST 2
+#endif
+#ifndef MOE_BST
+#define MOE_BST 4
+#endif
+constexpr int kAStages = MOE_AST;   // dequantised weight tiles (produced locally: shallow ring)
+constexpr int kBStages = MOE_BST;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
 constexpr int kFullRing = 4;  // "operands in place" barriers (producers run at most kAStages steps ahead of the MMAs)
 constexpr int kMaxEPerLane = 16;
 

@@ -102,11 +102,108 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
     }
 }
 
+// ─── streaming variant for rows of 2,048 columns ────────────────────────────
+// The hidden width of both reference models: gate/up rows, router rows, lm_head rows.  x is staged once per
+// CTA (bulk copy, then three signed-byte digit planes per 32-element chunk as in the decode kernel: exact
+// integer sums, activations kept to 23 bits relative to their chunk's maximum); every lane then keeps the
+// planes of its own two chunks (one 64-column group) in registers for the whole kernel, so the row loop reads
+// nothing but weights: two 128-bit loads and one scale/bias pair per lane and row, four rows in flight per warp.
+constexpr int kSvCols = 2048;
+constexpr int kSvWarps = 8;
+constexpr int kSvUnroll = 4;
+
+__global__ void __launch_bounds__(kSvWarps * 32, 2)
+matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s, const uint16_t* __restrict__ b,
+                          const float* __restrict__ x, float* __restrict__ y, int rows, unsigned int* err_flag) {
+    constexpr int nch = kSvCols / 32;
+    __shared__ __align__(128) float raw[kSvCols];
+    __shared__ __align__(16) uint4 xq[6 * nch];
+    __shared__ float xdl[nch];
+    __shared__ float sumx[nch];
+    __shared__ uint64_t bar;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        mbar_expect_tx(&bar, kSvCols * 4u);
+        bulk_g2s(raw, x, kSvCols * 4u, &bar);
+    }
+    const int ok = __syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0);
+    if (!ok) {
+        if (tid == 0) atomicExch(err_flag, 1u);
+        return;
+    }
+#pragma unroll
+    for (int it = 0; it < kSvCols / 4 / (kSvWarps * 32); ++it) {
+        const int f = tid + it * kSvWarps * 32;  // float4 index: chunk f >> 3, part f & 7 (eight consecutive lanes per chunk)
+        const float4 v = reinterpret_cast<const float4*>(raw)[f];
+        stage_digits(xq, xdl, nch, f >> 3, f & 7, v);
+        float sv = (v.x + v.y) + (v.z + v.w);
+        sv += __shfl_xor_sync(0xffffffffu, sv, 1);
+        sv += __shfl_xor_sync(0xffffffffu, sv, 2);
+        sv += __shfl_xor_sync(0xffffffffu, sv, 4);
+        if ((f & 7) == 0) sumx[f >> 3] = sv;
+    }
+    __syncthreads();
+    // this lane's group: chunks 2 lane and 2 lane + 1
+    uint4 xe[2][3], xo[2][3];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            xe[h][p] = xq[(p * 2 + 0) * nch + 2 * lane + h];
+            xo[h][p] = xq[(p * 2 + 1) * nch + 2 * lane + h];
+        }
+    const float dl0 = xdl[2 * lane], dl1 = xdl[2 * lane + 1];
+    const float sx = sumx[2 * lane] + sumx[2 * lane + 1];
+
+    const int stride = gridDim.x * kSvWarps;
+    for (int row0 = blockIdx.x * kSvWarps + warp; row0 < rows; row0 += stride * kSvUnroll) {
+        uint4 q[kSvUnroll][2];
+        uint16_t sc[kSvUnroll], bi[kSvUnroll];
+#pragma unroll
+        for (int u = 0; u < kSvUnroll; ++u) {
+            const int row = row0 + u * stride;
+            if (row < rows) {
+                const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (kSvCols / 8)) + 2 * lane;
+                q[u][0] = ld_stream_u4(wrow);
+                q[u][1] = ld_stream_u4(wrow + 1);
+                sc[u] = __ldg(s + (size_t)row * (kSvCols / kGroup) + lane);
+                bi[u] = __ldg(b + (size_t)row * (kSvCols / kGroup) + lane);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kSvUnroll; ++u) {
+            const int row = row0 + u * stride;
+            if (row < rows) {  // uniform per warp
+                const float d = fmaf(dl0, dot32_regs(q[u][0], xe[0], xo[0]), dl1 * dot32_regs(q[u][1], xe[1], xo[1]));
+                float acc = fmaf(bf16_bits_to_f32(sc[u]), d, bf16_bits_to_f32(bi[u]) * sx);
+                acc = warp_sum(acc);
+                if (lane == 0) y[row] = acc;
+            }
+        }
+    }
+}
+
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
+    if (cols == kSvCols && rows >= 4096) {
+        // enough rows to stream: the register-resident variant
+        int blocks = (rows + kSvWarps * kSvUnroll - 1) / (kSvWarps * kSvUnroll);
+        const int cap = e->sm_count * 2;
+        if (blocks > cap) blocks = cap;
+        matvec_int4_stream_kernel<<<blocks, kSvWarps * 32, 0, e->stream>>>(
+            (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2);
+        e->launches++;
+        MOE_CUDA(cudaGetLastError());
+        return MOE_OK;
+    }
     const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
     if (!e->matvec_attr_set) {  // a per-device function attribute: set once per engine
         MOE_CUDA(cudaFuncSetAttribute(matvec_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8 + 2048));

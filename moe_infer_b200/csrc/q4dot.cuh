@@ -122,4 +122,26 @@ __device__ __forceinline__ float dot32_int(const uint4& q, const uint4 (&xe)[3],
     return fmaf((float)a[2], 65536.0f, fmaf((float)a[1], 256.0f, (float)a[0]));
 }
 
+// int -> float for |v| < 2^22 with one integer and one floating-point add (both full-rate pipes)
+__device__ __forceinline__ float small_int_to_float(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
+
+// dot32_int for digit planes that already sit in registers, converting through small_int_to_float
+// (|sum of a plane| <= 8 * 4 * 15 * 128 < 2^22)
+__device__ __forceinline__ float dot32_regs(const uint4& q, const uint4 (&xe)[3], const uint4 (&xo)[3]) {
+    int a[3] = {0, 0, 0};
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lo = w[k] & 0x0F0F0F0Fu, hi = (w[k] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+            const uint32_t e = k == 0 ? xe[p].x : k == 1 ? xe[p].y : k == 2 ? xe[p].z : xe[p].w;
+            const uint32_t o = k == 0 ? xo[p].x : k == 1 ? xo[p].y : k == 2 ? xo[p].z : xo[p].w;
+            a[p] = dp4a_us(lo, e, a[p]);
+            a[p] = dp4a_us(hi, o, a[p]);
+        }
+    }
+    return fmaf(small_int_to_float(a[2]), 65536.0f, fmaf(small_int_to_float(a[1]), 256.0f, small_int_to_float(a[0])));
+}
+
 }  // namespace moe

@@ -97,7 +97,7 @@ def test_matvec_config1(eng):
     assert _same(eng.pack_int4(W), (w, s, b))
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 2048), (2048, 512), (5, 64), (300, 4096), (64, 16384)])
+@pytest.mark.parametrize("rows,cols", [(1, 2048), (2048, 512), (5, 64), (300, 4096), (64, 16384), (4099, 2048), (9000, 2048)])
 def test_matvec_shapes(eng, rows, cols):
     rng = np.random.default_rng(rows + cols)
     w, s, b = oracle.quant_int4(synth.normal_weights(rng, (rows, cols)))
