@@ -49,7 +49,7 @@ typedef enum {
  * both use the same 4-bit codec for experts; they differ in the router dtype. */
 typedef enum { MOE_SCHEME_BQ4 = 0, MOE_SCHEME_INT4 = 1 } moe_scheme_t;
 
-typedef enum { MOE_DT_F32 = 0, MOE_DT_BF16 = 1, MOE_DT_INT4 = 2 } moe_dtype_t;
+typedef enum { MOE_DT_F32 = 0, MOE_DT_BF16 = 1, MOE_DT_INT4 = 2, MOE_DT_INT8 = 3 } moe_dtype_t;
 
 /* Non-expert tensors of one MoE block, by role.  Names in the reference's
  * weight manifest: `model.layers.{L}.post_attention_layernorm.weight`,
@@ -127,6 +127,12 @@ int moe_pack_int4_dev(moe_engine_t* e, const void* src_dev, int src_dtype, int64
 /* Same through host buffers (copies in, packs on the GPU, copies out). */
 int moe_pack_int4_host(moe_engine_t* e, const void* src_host, int src_dtype, int64_t rows, int32_t cols,
                        void* w_host, void* s_host, void* b_host);
+/* quant_f32_to_int8 (src/dtype.rs:164-179; encode_int8 src/dtype.rs:466-475): per-row symmetric INT8, the
+ * BQ4 scheme's lm_head codec.  src f32/bf16 [rows, cols] -> q int8 [rows, cols] + scales f32 [rows]; bit-exact
+ * with the reference (scale = max|v| / 127, round half away from zero, clamp to +-127). */
+int moe_pack_int8_host(moe_engine_t* e, const void* src_host, int src_dtype, int64_t rows, int32_t cols,
+                       void* q_host, void* scales_host);
+
 /* process_experts_common (src/quantize/qwen35_moe/common.rs:300-345): HF
  * gate_up [E, 2I, H] and down [E, H, I] -> E packed experts back to back.
  * Device pointers; n_experts may be a sub-range (pointers pre-offset). */
@@ -183,6 +189,30 @@ int moe_forward_hidden_dev(moe_engine_t* e, const float* emb_dev, int32_t n_toke
                            float* out_dev);
 /* Engine::last_h_pre_norm (src/engine.rs:66-68): f32 [hidden] of the last token. */
 int moe_last_h_pre_norm(moe_engine_t* e, float* out_host);
+
+/* ── the model head: embedding rows, final norm, lm_head ─────────────────────
+ * What surrounds the stack inside Engine::forward (src/python_bindings.rs:172-202):
+ * embed_lookup (src/math_util.rs:205-236: one row of the 4-bit table model.embed_tokens per token),
+ * final_norm (src/math_util.rs:240-247, model.norm.weight) and the lm_head matvec
+ * (src/engine/qwen35_moe/fused_exp1.rs:390-393, 860-879): INT8 rows with one f32 scale per row in the BQ4
+ * scheme (src/dtype.rs:164-179, src/engine/shaders.metal:2435-2471), a 4-bit triple in the INT4 scheme.
+ * moe_head_load_tensor copies a host tensor into HBM:
+ *   MOE_H_EMBED       INT4 [vocab, hidden]: w = u32 words, s/b = bf16 [vocab, hidden/64]
+ *   MOE_H_FINAL_NORM  bf16 [hidden] (w only)
+ *   MOE_H_LM_HEAD     MOE_DT_INT8: w = int8 [vocab, hidden], s = f32 [vocab];  MOE_DT_INT4: triple as above
+ * moe_embed_lookup_*: ids int64 [n] -> f32 [n, hidden]; an id outside [0, vocab) is MOE_ERR_INVALID.
+ * moe_logits_*: hidden f32 [n, hidden] (before the final norm) -> logits f32 [n, vocab].
+ * moe_forward_host: Engine::forward / forward_batched: ids -> logits [n, vocab] through embedding, stack and head
+ * (`batched`, `mtp`, `check` as for moe_forward_hidden_host); keeps the last token's pre-norm hidden state.
+ * MOE_ERR_STATE when a tensor the call needs has not been loaded. */
+typedef enum { MOE_H_EMBED = 0, MOE_H_FINAL_NORM = 1, MOE_H_LM_HEAD = 2 } moe_head_tensor_t;
+int moe_head_load_tensor(moe_engine_t* e, int which, const void* w_host, const void* s_host, const void* b_host, int dtype);
+int moe_embed_lookup_host(moe_engine_t* e, const int64_t* ids_host, int32_t n_tokens, float* out_host);
+int moe_embed_lookup_dev(moe_engine_t* e, const int64_t* ids_dev, int32_t n_tokens, float* out_dev);
+int moe_logits_host(moe_engine_t* e, const float* hidden_host, int32_t n_tokens, float* logits_host);
+int moe_logits_dev(moe_engine_t* e, const float* hidden_dev, int32_t n_tokens, float* logits_dev);
+int moe_forward_host(moe_engine_t* e, const int64_t* ids_host, int32_t n_tokens, int batched, int mtp,
+                     moe_check_fn check, void* check_ctx, float* logits_host);
 
 /* ── MTP block ───────────────────────────────────────────────────────────────
  * Engine::mtp_forward / mtp_reset / mtp_rollback (src/engine.rs:70-78;

@@ -18,7 +18,8 @@ HEADER_PATH = os.path.join(_HERE, "..", "include", "moe_b200.h")
 MOE_OK = 0
 ERR_INVALID, ERR_CUDA, ERR_STATE, ERR_INTERRUPTED, ERR_DEVICE_WAIT, ERR_UNSUPPORTED, ERR_IO = -1, -2, -3, -4, -5, -6, -7
 SCHEME_BQ4, SCHEME_INT4 = 0, 1
-DT_F32, DT_BF16, DT_INT4 = 0, 1, 2
+DT_F32, DT_BF16, DT_INT4, DT_INT8 = 0, 1, 2, 3
+H_EMBED, H_FINAL_NORM, H_LM_HEAD = 0, 1, 2
 T_POST_NORM, T_ROUTER, T_SHARED_GATE, T_SHARED_UP, T_SHARED_DOWN, T_SHARED_SGATE = range(6)
 EP_HANDLE_BYTES = 64
 
@@ -59,6 +60,7 @@ SIGNATURES = {
     "moe_store_bytes": (_i, [_vp, C.POINTER(_sz)]),
     "moe_pack_int4_dev": (_i, [_vp, _vp, _i, _i64, _i32, _vp, _vp, _vp]),
     "moe_pack_int4_host": (_i, [_vp, _vp, _i, _i64, _i32, _vp, _vp, _vp]),
+    "moe_pack_int8_host": (_i, [_vp, _vp, _i, _i64, _i32, _vp, _vp]),
     "moe_pack_experts_dev": (_i, [_vp, _vp, _vp, _i, _i32, _vp]),
     "moe_pack_experts_host": (_i, [_vp, _vp, _vp, _i, _i32, _vp]),
     "moe_matvec_int4_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32]),
@@ -68,6 +70,12 @@ SIGNATURES = {
     "moe_forward_hidden_host": (_i, [_vp, _vp, _i32, _i, _i, CHECK_FN, _vp, _vp]),
     "moe_forward_hidden_dev": (_i, [_vp, _vp, _i32, _i, _vp]),
     "moe_last_h_pre_norm": (_i, [_vp, _vp]),
+    "moe_head_load_tensor": (_i, [_vp, _i, _vp, _vp, _vp, _i]),
+    "moe_embed_lookup_host": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_embed_lookup_dev": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_logits_host": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_logits_dev": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_forward_host": (_i, [_vp, _vp, _i32, _i, _i, CHECK_FN, _vp, _vp]),
     "moe_mtp_forward_host": (_i, [_vp, _vp, _vp]),
     "moe_mtp_reset": (_i, [_vp]),
     "moe_mtp_rollback": (_i, [_vp, _i64]),

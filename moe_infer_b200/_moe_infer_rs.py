@@ -6,14 +6,18 @@ reference binding: ``Model``, ``Cache``, ``Engine``, ``PyEngineSnapshot``,
 ``record_engine_telemetry``, ``qwen35_moe_quantize``.  Every forward goes through the
 CUDA library; nothing here computes the MoE path on the CPU.
 
-What is NOT behind this surface yet, and how the calls behave:
+Where this surface departs from the reference, and how the calls behave:
   * attention / DeltaNet are passed through (each block is h <- h + moe(rmsnorm(h)));
-  * the final norm and ``lm_head`` are not built: ``forward*`` return the hidden states
-    before the final norm, float32 [n, hidden], instead of logits [n, vocab];
-  * ``embed_lookup`` dequantises rows of the 4-bit embedding table on the host (as the
-    reference does, src/math_util.rs:205-236) and returns zeros when the table is absent;
-  * ``mtp_forward`` runs the MoE half of the MTP block on ``last_h_pre_norm`` and returns
-    float32 [hidden] (an empty array when the model has no MTP block, like the reference).
+  * ``forward`` / ``forward_batched`` / ``forward_hidden`` return logits float32 [n, vocab] like the reference
+    (embedding rows, stack, final norm and lm_head all on the GPU).  They raise ``RuntimeError`` naming the missing
+    tensor when the model directory has no embedding table, final norm or lm_head, instead of returning zeros
+    (the reference's ``embed_lookup`` silently fills zeros, src/math_util.rs:211-214);
+  * ``forward_hidden_states`` (not in the reference) returns the hidden states before the final norm,
+    float32 [n, hidden], and needs no head tensors;
+  * ``mtp_forward(token_id)`` runs the MoE half of the MTP block on ``last_h_pre_norm`` and returns
+    float32 [hidden], not logits: the block's embedding / fc / attention half is not built, so the token id is
+    only range-checked (an empty array when the model has no MTP block, like the reference);
+  * ``Cache.save`` writes an empty state file: the MoE path keeps no per-sequence state (only ``pos``).
 """
 from __future__ import annotations
 
@@ -127,9 +131,33 @@ class Engine:
         try:
             for l in range(layers + mtp):
                 self._load_layer(l, f"model.layers.{l}" if l < layers else f"mtp.layers.{l - layers}")
+            self._missing_head = self._load_head()
         except Exception:
             self.native.close()
             raise
+
+    def _load_head(self):
+        """Embedding table, final norm and lm_head, when the directory has them; returns the names that are missing."""
+        m, eng = self.model.inner, self.native
+        missing = []
+        emb = m.q4("model.embed_tokens")
+        if emb is not None:
+            eng.load_embed(emb)
+        else:
+            missing.append("model.embed_tokens")
+        norm = m.tensor("model.norm.weight")
+        if norm is not None:
+            eng.load_final_norm(norm)
+        else:
+            missing.append("model.norm.weight")
+        w = m.tensor("lm_head.weight")
+        if w is not None and w.dtype == np.uint8:       # INT8 rows + f32 scale per row (BQ4 scheme)
+            eng.load_lm_head_int8(w, m.tensor("lm_head.scales"))
+        elif w is not None and m.q4("lm_head") is not None:  # 4-bit triple (INT4 scheme)
+            eng.load_lm_head_q4(m.q4("lm_head"))
+        else:
+            missing.append("lm_head")
+        return missing
 
     def _load_layer(self, layer: int, prefix: str) -> None:
         m, d, eng = self.model.inner, self.dims, self.native
@@ -159,50 +187,67 @@ class Engine:
         return t
 
     # ── reference surface ────────────────────────────────────────────────
-    def embed_lookup(self, input_ids: np.ndarray) -> np.ndarray:
-        ids = np.ascontiguousarray(input_ids, np.int64).reshape(-1)
-        H = self.dims.hidden
-        out = np.zeros((ids.size, H), np.float32)
-        t = self.model.inner.q4("model.embed_tokens")
-        if t is None:
-            return out
-        w, s, b = t
-        for i, tok in enumerate(ids):
-            nib = np.stack([(w[tok] >> (4 * n)) & 0xF for n in range(8)], axis=-1).reshape(H).astype(np.float32)
-            sc = (s[tok].astype(np.uint32) << 16).view(np.float32).repeat(64)
-            bi = (b[tok].astype(np.uint32) << 16).view(np.float32).repeat(64)
-            out[i] = nib * sc + bi
-        return out
+    def _need_head(self, *names: str) -> None:
+        miss = [n for n in names if n in self._missing_head]
+        if miss:
+            raise RuntimeError(f"Config error: tensor(s) {', '.join(miss)} missing from the model directory")
 
-    def _run(self, emb: np.ndarray, cache: Cache, batched: bool, mtp: bool) -> np.ndarray:
-        emb = np.ascontiguousarray(emb, np.float32).reshape(-1, self.dims.hidden)
+    def embed_lookup(self, input_ids: np.ndarray) -> np.ndarray:
+        self._need_head("model.embed_tokens")
+        try:
+            return self.native.embed_lookup(np.ascontiguousarray(input_ids, np.int64).reshape(-1))
+        except L.MoeError as e:
+            raise RuntimeError(str(e)) from e
+
+    def _after(self, n: int, cache: Cache) -> None:
+        self.pos += n
+        cache.pos = self.pos
+        cache.gpu_dirty = True
+        self._last_h = self.native.last_h_pre_norm()
+        self._telemetry = self.native.telemetry()
+
+    def forward_hidden_states(self, embeddings: np.ndarray, cache: Cache, *, batched: bool = False, mtp: bool = False) -> np.ndarray:
+        """Not in the reference: the hidden states before the final norm, float32 [n, hidden]."""
+        emb = np.ascontiguousarray(embeddings, np.float32).reshape(-1, self.dims.hidden)
         if cache.cpu_dirty:
             self.upload_cache(cache)
         try:
             out = self.native.forward_hidden(emb, batched=batched, mtp=mtp, check=_interrupt_pending)
         except L.MoeError as e:
             raise RuntimeError(str(e)) from e
-        self.pos += emb.shape[0]
-        cache.pos = self.pos
-        cache.gpu_dirty = True
-        self._last_h = out[-1].copy()
-        self._telemetry = self.native.telemetry()
+        self._after(emb.shape[0], cache)
         return out
 
     def forward_hidden(self, embeddings: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
-        return self._run(embeddings, cache, False, mtp)
+        """src/python_bindings.rs:141-160: embeddings [n, hidden] -> logits [n, vocab]."""
+        self._need_head("model.norm.weight", "lm_head")
+        hidden = self.forward_hidden_states(embeddings, cache, mtp=mtp)
+        try:
+            return self.native.logits(hidden)
+        except L.MoeError as e:
+            raise RuntimeError(str(e)) from e
+
+    def _forward_ids(self, tokens: np.ndarray, cache: Cache, batched: bool, mtp: bool) -> np.ndarray:
+        toks = np.ascontiguousarray(tokens, np.int64).reshape(-1)
+        if toks.size == 0:
+            return np.zeros((0, self.dims.vocab), np.float32)
+        self._need_head("model.embed_tokens", "model.norm.weight", "lm_head")
+        if cache.cpu_dirty:
+            self.upload_cache(cache)
+        try:
+            out = self.native.forward(toks, batched=batched, mtp=mtp, check=_interrupt_pending)
+        except L.MoeError as e:
+            raise RuntimeError(str(e)) from e
+        self._after(toks.size, cache)
+        return out
 
     def forward(self, tokens: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
-        toks = np.ascontiguousarray(tokens, np.int64).reshape(-1)
-        if toks.size == 0:
-            return np.zeros((0, self.dims.hidden), np.float32)
-        return self._run(self.embed_lookup(toks), cache, False, mtp)
+        """src/python_bindings.rs:172-202: token ids -> logits [n, vocab]; n = 0 gives [0, vocab]."""
+        return self._forward_ids(tokens, cache, False, mtp)
 
     def forward_batched(self, tokens: np.ndarray, cache: Cache, *, mtp: bool = False) -> np.ndarray:
-        toks = np.ascontiguousarray(tokens, np.int64).reshape(-1)
-        if toks.size == 0:
-            return np.zeros((0, self.dims.hidden), np.float32)
-        return self._run(self.embed_lookup(toks), cache, True, mtp)
+        """src/python_bindings.rs:208-244: same result, batched internals."""
+        return self._forward_ids(tokens, cache, True, mtp)
 
     def upload_cache(self, cache: Cache) -> None:
         self.pos = cache.pos
@@ -221,6 +266,8 @@ class Engine:
     def mtp_forward(self, token_id: int) -> np.ndarray:
         if self.dims.num_mtp_layers == 0:
             return np.zeros(0, np.float32)
+        if not 0 <= int(token_id) < self.dims.vocab:
+            raise ValueError(f"token id {token_id} outside [0, {self.dims.vocab})")
         return self.native.mtp_forward(self._last_h)
 
     def mtp_reset(self) -> None:

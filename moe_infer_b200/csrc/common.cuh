@@ -124,6 +124,21 @@ struct EpState {
     int max_tiles = 0;
 };
 
+// The model head: token embedding table, final norm weight, lm_head (head.cu).
+struct HeadState {
+    uint8_t* embed = nullptr;      // 4-bit table [vocab, hidden]: words, then scales at embed_s, biases at embed_b
+    size_t embed_s = 0, embed_b = 0;
+    uint16_t* final_norm = nullptr;  // bf16 [hidden]
+    uint8_t* lm_head = nullptr;    // INT8 rows + f32 scales at lm_s, or 4-bit words + bf16 scales at lm_s + biases at lm_b
+    size_t lm_s = 0, lm_b = 0, lm_bytes = 0;
+    int lm_dtype = 0;
+    bool embed_loaded = false, norm_loaded = false, lm_loaded = false, i8_attr_set = false;
+    uint8_t* work = nullptr;       // normalised hidden states and token ids of a call, grown on demand
+    float* x = nullptr;
+    int64_t* ids = nullptr;
+    int32_t cap = 0;
+};
+
 }  // namespace moe
 
 struct moe_engine {
@@ -165,6 +180,8 @@ struct moe_engine {
 
     // expert parallelism
     moe::EpState ep;
+
+    moe::HeadState head;
 };
 
 namespace moe {
@@ -172,6 +189,7 @@ namespace moe {
 // Kernel launchers implemented in the .cu files; all enqueue on e->stream.
 int launch_pack(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols,
                 int64_t src_row_stride, void* w, void* s, void* b);
+int launch_pack_int8(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols, void* q, void* scales);
 int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, int src_dtype,
                         int32_t n_experts, void* blob);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
@@ -192,6 +210,11 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
                          float* out_w);
 int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n_local, float* h_out);
 int ep_alloc_work(moe_engine* e);
+int head_load_tensor(moe_engine* e, int which, const void* w, const void* s, const void* b, int dtype);
+int launch_embed(moe_engine* e, const int64_t* ids_dev, int32_t n, float* out_dev);
+int launch_logits(moe_engine* e, const float* hidden_dev, int32_t n, float* logits_dev);
+int head_reserve(moe_engine* e, int32_t n);
+void head_destroy(moe_engine* e);
 int refresh_layer_table(moe_engine* e);
 int check_layer_ready(moe_engine* e, int layer);
 

@@ -159,6 +159,10 @@ static int poll_device_error(moe_engine* e) {
         cudaMemsetAsync(e->dec_sync, 0, 16 * sizeof(unsigned int), e->stream);
         cudaStreamSynchronize(e->stream);
         decode_reset_after_error(e);
+        if (flag == 11u) {
+            set_error("a token id is outside [0, %d); the result of the last call is invalid", e->dims.vocab);
+            return MOE_ERR_INVALID;
+        }
         if (flag == 10u) {
             set_error("forced_idx holds an expert index outside [0, %d); the result of the last call is invalid",
                       e->dims.num_experts);
@@ -270,6 +274,7 @@ void moe_engine_destroy(moe_engine_t* e) {
     moe_ep_finalize(e);
     decode_destroy(e);
     batch_destroy(e);
+    head_destroy(e);
     if (e->layers_dev) cudaFree(e->layers_dev);
     if (e->io_dev) cudaFree(e->io_dev);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -437,6 +442,30 @@ int moe_pack_int4_host(moe_engine_t* e, const void* src, int src_dtype, int64_t 
     return rc;
 }
 
+int moe_pack_int8_host(moe_engine_t* e, const void* src, int src_dtype, int64_t rows, int32_t cols, void* q, void* scales) {
+    MOE_REQUIRE(e && src && q && scales, "null argument");
+    MOE_REQUIRE(src_dtype == MOE_DT_F32 || src_dtype == MOE_DT_BF16, "pack: source dtype must be f32 or bf16");
+    MOE_REQUIRE(rows >= 0 && cols > 0, "pack_int8: bad shape");
+    if (rows == 0) return MOE_OK;
+    const size_t esz = src_dtype == MOE_DT_F32 ? 4 : 2, n = (size_t)rows * cols;
+    uint8_t* d = nullptr;
+    const size_t so = align_up(n * esz, 256), qo = so + align_up(n, 256);
+    MOE_CUDA(cudaMalloc(&d, qo + (size_t)rows * 4));
+    int rc = MOE_OK;
+    do {
+        if (cudaMemcpyAsync(d, src, n * esz, cudaMemcpyHostToDevice, e->stream) != cudaSuccess) { rc = MOE_ERR_CUDA; break; }
+        rc = launch_pack_int8(e, d, src_dtype, rows, cols, d + so, d + qo);
+        if (rc) break;
+        if (cudaMemcpyAsync(q, d + so, n, cudaMemcpyDeviceToHost, e->stream) != cudaSuccess ||
+            cudaMemcpyAsync(scales, d + qo, (size_t)rows * 4, cudaMemcpyDeviceToHost, e->stream) != cudaSuccess ||
+            cudaStreamSynchronize(e->stream) != cudaSuccess)
+            rc = MOE_ERR_CUDA;
+    } while (0);
+    if (rc == MOE_ERR_CUDA) cuda_fail(cudaGetLastError(), "pack_int8_host", __FILE__, __LINE__);
+    cudaFree(d);
+    return rc;
+}
+
 int moe_pack_experts_dev(moe_engine_t* e, const void* gate_up, const void* down, int src_dtype, int32_t n_experts,
                          void* blob) {
     MOE_REQUIRE(e && gate_up && down && blob, "null argument");
@@ -601,6 +630,34 @@ int moe_forward_hidden_dev(moe_engine_t* e, const float* emb, int32_t n, int bat
     return MOE_OK;
 }
 
+// The stack over device buffers, polling the caller between tokens (decode path) or layers (grouped path):
+// the reference polls once per layer (fused_exp1.rs:966-968).
+static int run_stack_checked(moe_engine* e, const float* d_in, int32_t n, int batched, moe_check_fn check, void* check_ctx,
+                             float* d_out) {
+    const moe_dims_t& d = e->dims;
+    if (!check) return moe_forward_hidden_dev(e, d_in, n, batched, d_out);
+    int rc = MOE_OK;
+    if (!batched || n == 1) {
+        for (int t = 0; t < n && rc == MOE_OK; ++t) {
+            if (check(check_ctx)) { set_error("interrupted"); return MOE_ERR_INTERRUPTED; }
+            rc = launch_decode(e, 0, d.num_layers, d_in + (size_t)t * d.hidden, d_out + (size_t)t * d.hidden, nullptr, nullptr,
+                               nullptr, nullptr);
+        }
+        return rc;
+    }
+    rc = batch_reserve(e, n);
+    if (rc) return rc;
+    const float* cur = d_in;
+    for (int l = 0; l < d.num_layers; ++l) {
+        if (check(check_ctx)) { set_error("interrupted"); return MOE_ERR_INTERRUPTED; }
+        float* nxt = (l == d.num_layers - 1) ? d_out : ((l & 1) ? e->bw.h_b : e->bw.h_a);
+        rc = launch_batched_layer(e, l, cur, n, nxt, nullptr, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+        cur = nxt;
+    }
+    return MOE_OK;
+}
+
 int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int batched, int mtp, moe_check_fn check,
                             void* check_ctx, float* out) {
     (void)mtp;
@@ -619,30 +676,8 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
         if (rec) cudaEventRecord(t0, e->stream);
         cudaError_t ce = cudaMemcpyAsync(d_in, emb, hb, cudaMemcpyHostToDevice, e->stream);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward_hidden upload", __FILE__, __LINE__); break; }
-        if (!check) {
-            rc = moe_forward_hidden_dev(e, d_in, n, batched, d_out);
-            if (rc) break;
-        } else if (!batched || n == 1) {
-            // poll the caller between tokens (reference polls once per layer: fused_exp1.rs:966-968)
-            for (int t = 0; t < n && rc == MOE_OK; ++t) {
-                if (check(check_ctx)) { set_error("interrupted"); rc = MOE_ERR_INTERRUPTED; break; }
-                rc = launch_decode(e, 0, d.num_layers, d_in + (size_t)t * d.hidden, d_out + (size_t)t * d.hidden,
-                                   nullptr, nullptr, nullptr, nullptr);
-            }
-            if (rc) break;
-        } else {
-            rc = batch_reserve(e, n);
-            if (rc) break;
-            const float* cur = d_in;
-            for (int l = 0; l < d.num_layers; ++l) {
-                if (check(check_ctx)) { set_error("interrupted"); rc = MOE_ERR_INTERRUPTED; break; }
-                float* nxt = (l == d.num_layers - 1) ? d_out : ((l & 1) ? e->bw.h_b : e->bw.h_a);
-                rc = launch_batched_layer(e, l, cur, n, nxt, nullptr, nullptr, nullptr, nullptr);
-                if (rc) break;
-                cur = nxt;
-            }
-            if (rc) break;
-        }
+        rc = run_stack_checked(e, d_in, n, batched, check, check_ctx, d_out);
+        if (rc) break;
         ce = cudaMemcpyAsync(out, d_out, hb, cudaMemcpyDeviceToHost, e->stream);
         if (rec && ce == cudaSuccess) ce = cudaEventRecord(t1, e->stream);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
@@ -656,6 +691,111 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
             tel_add(e, "engine.total_ms", ms);
             tel_add(e, "engine.tokens", n);
             // keys the reference fills with CPU-side costs that no longer exist here
+            tel_add(e, "engine.expert_io_ms", 0.0);
+            tel_add(e, "engine.routing_cpu_ms", 0.0);
+            tel_add(e, "phase.route_cpu_ms", 0.0);
+        }
+    } while (0);
+    if (rc == MOE_ERR_INTERRUPTED) cudaStreamSynchronize(e->stream);
+    return rc;
+}
+
+// ── the model head ───────────────────────────────────────────────────────────
+
+int moe_head_load_tensor(moe_engine_t* e, int which, const void* w, const void* s, const void* b, int dtype) {
+    MOE_REQUIRE(e, "null engine");
+    return head_load_tensor(e, which, w, s, b, dtype);
+}
+
+int moe_embed_lookup_dev(moe_engine_t* e, const int64_t* ids_dev, int32_t n, float* out_dev) {
+    MOE_REQUIRE(e && ids_dev && out_dev, "null argument");
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    return launch_embed(e, ids_dev, n, out_dev);
+}
+
+int moe_embed_lookup_host(moe_engine_t* e, const int64_t* ids, int32_t n, float* out) {
+    MOE_REQUIRE(e && ids && out, "null argument");
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    const size_t hb = (size_t)n * e->dims.hidden * 4;
+    int rc = io_reserve(e, align_up(hb, 256));
+    if (rc) return rc;
+    rc = head_reserve(e, n);
+    if (rc) return rc;
+    MOE_CUDA(cudaMemcpyAsync(e->head.ids, ids, (size_t)n * 8, cudaMemcpyHostToDevice, e->stream));
+    rc = launch_embed(e, e->head.ids, n, (float*)e->io_dev);
+    if (rc) return rc;
+    MOE_CUDA(cudaMemcpyAsync(out, e->io_dev, hb, cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    return poll_device_error(e);
+}
+
+int moe_logits_dev(moe_engine_t* e, const float* hidden_dev, int32_t n, float* logits_dev) {
+    MOE_REQUIRE(e && hidden_dev && logits_dev, "null argument");
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    return launch_logits(e, hidden_dev, n, logits_dev);
+}
+
+int moe_logits_host(moe_engine_t* e, const float* hidden, int32_t n, float* logits) {
+    MOE_REQUIRE(e && hidden && logits, "null argument");
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    const moe_dims_t& d = e->dims;
+    const size_t hb = align_up((size_t)n * d.hidden * 4, 256), lb = (size_t)n * d.vocab * 4;
+    int rc = io_reserve(e, hb + align_up(lb, 256));
+    if (rc) return rc;
+    float* d_h = (float*)e->io_dev;
+    float* d_l = (float*)(e->io_dev + hb);
+    MOE_CUDA(cudaMemcpyAsync(d_h, hidden, (size_t)n * d.hidden * 4, cudaMemcpyHostToDevice, e->stream));
+    rc = launch_logits(e, d_h, n, d_l);
+    if (rc) return rc;
+    MOE_CUDA(cudaMemcpyAsync(logits, d_l, lb, cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    return poll_device_error(e);
+}
+
+int moe_forward_host(moe_engine_t* e, const int64_t* ids, int32_t n, int batched, int mtp, moe_check_fn check, void* check_ctx,
+                     float* logits) {
+    (void)mtp;
+    MOE_REQUIRE(e && ids && logits, "null argument");
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    const moe_dims_t& d = e->dims;
+    const bool rec = g_record_telemetry.load(std::memory_order_relaxed) != 0;
+    const size_t hb = align_up((size_t)n * d.hidden * 4, 256), lb = (size_t)n * d.vocab * 4;
+    int rc = io_reserve(e, 2 * hb + align_up(lb, 256));
+    if (rc) return rc;
+    rc = head_reserve(e, n);
+    if (rc) return rc;
+    float* d_in = (float*)e->io_dev;
+    float* d_out = (float*)(e->io_dev + hb);
+    float* d_l = (float*)(e->io_dev + 2 * hb);
+    do {
+        if (rec) cudaEventRecord(e->ev0, e->stream);
+        cudaError_t ce = cudaMemcpyAsync(e->head.ids, ids, (size_t)n * 8, cudaMemcpyHostToDevice, e->stream);
+        if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward upload", __FILE__, __LINE__); break; }
+        rc = launch_embed(e, e->head.ids, n, d_in);
+        if (rc) break;
+        rc = run_stack_checked(e, d_in, n, batched, check, check_ctx, d_out);
+        if (rc) break;
+        rc = launch_logits(e, d_out, n, d_l);
+        if (rc) break;
+        ce = cudaMemcpyAsync(logits, d_l, lb, cudaMemcpyDeviceToHost, e->stream);
+        if (ce == cudaSuccess)
+            ce = cudaMemcpyAsync(e->stage_host, d_out + (size_t)(n - 1) * d.hidden, (size_t)d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
+        if (rec && ce == cudaSuccess) ce = cudaEventRecord(e->ev1, e->stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+        if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward download", __FILE__, __LINE__); break; }
+        rc = poll_device_error(e);
+        if (rc) break;
+        memcpy(e->last_h.data(), e->stage_host, (size_t)d.hidden * 4);
+        if (rec) {
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, e->ev0, e->ev1);
+            tel_add(e, "engine.total_ms", ms);
+            tel_add(e, "engine.tokens", n);
             tel_add(e, "engine.expert_io_ms", 0.0);
             tel_add(e, "engine.routing_cpu_ms", 0.0);
             tel_add(e, "phase.route_cpu_ms", 0.0);

@@ -268,4 +268,44 @@ int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, in
     return run_pack(e, dn, src_dtype);
 }
 
+// ─── INT8 per-row codec (lm_head of the BQ4 scheme) ─────────────────────────
+// quant_f32_to_int8 (reference src/dtype.rs:164-179), bit for bit: scale = max|v| / 127 (1/127 for an all-zero
+// row), q = clamp(round(v * (1 / scale)), -127, 127) with round-half-away-from-zero; one warp per row, two passes.
+template <bool kSrcBf16>
+__global__ void __launch_bounds__(256) pack_int8_kernel(const void* __restrict__ src, int64_t rows, int32_t cols,
+                                                        int8_t* __restrict__ q, float* __restrict__ scales) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    auto load = [&](int c) -> float {
+        if (kSrcBf16) return bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(src)[row * cols + c]);
+        return reinterpret_cast<const float*>(src)[row * cols + c];
+    };
+    float mx = 0.0f;
+    for (int c = lane; c < cols; c += 32) mx = fmaxf(mx, fabsf(load(c)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float scale = mx > 0.0f ? __fdiv_rn(mx, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (lane == 0) scales[row] = scale;
+    for (int c = lane; c < cols; c += 32) {
+        const float r = roundf(__fmul_rn(load(c), inv));
+        const int v = max(-127, min(127, __float2int_rz(r)));  // saturating convert, NaN -> 0, like Rust's `as i32`
+        q[row * cols + c] = (int8_t)v;
+    }
+}
+
+int launch_pack_int8(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols, void* q, void* scales) {
+    if (rows == 0) return MOE_OK;
+    const int64_t blocks = (rows + 7) / 8;
+    MOE_REQUIRE(blocks < (1ll << 31), "pack_int8: too many rows");
+    if (src_dtype == MOE_DT_BF16)
+        pack_int8_kernel<true><<<(unsigned)blocks, 256, 0, e->stream>>>(src, rows, cols, (int8_t*)q, (float*)scales);
+    else
+        pack_int8_kernel<false><<<(unsigned)blocks, 256, 0, e->stream>>>(src, rows, cols, (int8_t*)q, (float*)scales);
+    e->launches++;
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
 }  // namespace moe

@@ -10,7 +10,8 @@ src/quantize.rs:150-291, src/quantize/qwen35_moe/common.rs:314-348):
                                      layer, MTP block = index num_hidden_layers
 
 dtype strings follow src/dtype.rs:34-43: "f32", "bf16", "u32" (= 4-bit words), "u8".
-Only the tensors the MoE path needs are read; attention tensors are ignored.
+Only the tensors of the MoE path and of the model head (embedding table, final norm, lm_head) are read;
+attention tensors are ignored.
 """
 from __future__ import annotations
 
@@ -115,6 +116,11 @@ class ModelDirWriter:
         self._put(base + ".weight", w.astype(np.uint32), "u32", w.shape)
         self._put(base + ".scales", s.astype(np.uint16), "bf16", s.shape)
         self._put(base + ".biases", b.astype(np.uint16), "bf16", b.shape)
+
+    def add_int8(self, base: str, q: np.ndarray, scales: np.ndarray) -> None:
+        # encode_int8 (reference src/dtype.rs:466-475): ".weight" as "u8" [out, in], ".scales" as "f32" [out]
+        self._put(base + ".weight", np.ascontiguousarray(q).view(np.uint8), "u8", q.shape)
+        self._put(base + ".scales", scales.astype(np.float32), "f32", scales.shape)
 
     def add_expert_layer(self, layer: int, blob: np.ndarray) -> None:
         with open(os.path.join(self.path, "packed_experts", f"layer_{layer:02d}.bin"), "wb") as f:

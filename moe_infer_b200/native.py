@@ -155,6 +155,15 @@ class NativeEngine:
         L.check(self.lib.moe_pack_int4_host(self.h, L.ptr(src), dt, rows, cols, L.ptr(w), L.ptr(s), L.ptr(b)))
         return w, s, b
 
+    def pack_int8(self, src: np.ndarray):
+        """f32 / bf16 [rows, cols] -> (int8 [rows, cols], f32 scales [rows]): the INT8 lm_head codec."""
+        src, dt = self._src(src)
+        rows, cols = src.shape
+        q = np.empty((rows, cols), np.int8)
+        s = np.empty(rows, np.float32)
+        L.check(self.lib.moe_pack_int8_host(self.h, L.ptr(src), dt, rows, cols, L.ptr(q), L.ptr(s)))
+        return q, s
+
     def pack_experts(self, gate_up: np.ndarray, down: np.ndarray) -> np.ndarray:
         gate_up, dt = self._src(gate_up)
         down, dt2 = self._src(down)
@@ -222,6 +231,46 @@ class NativeEngine:
         L.check(self.lib.moe_layer_forward_dev(self.h, layer, C.c_void_p(h_in), n, C.c_void_p(h_out),
                                                C.c_void_p(logit_bias or None), C.c_void_p(forced_idx or None),
                                                C.c_void_p(out_idx or None), C.c_void_p(out_w or None)))
+
+    # ── the model head ───────────────────────────────────────────────────
+    def load_embed(self, t: Q4) -> None:
+        w, s, b = (np.ascontiguousarray(t[0], np.uint32), np.ascontiguousarray(t[1], np.uint16),
+                   np.ascontiguousarray(t[2], np.uint16))
+        L.check(self.lib.moe_head_load_tensor(self.h, L.H_EMBED, L.ptr(w), L.ptr(s), L.ptr(b), L.DT_INT4))
+
+    def load_final_norm(self, w: np.ndarray) -> None:
+        w = np.ascontiguousarray(w, np.uint16)
+        L.check(self.lib.moe_head_load_tensor(self.h, L.H_FINAL_NORM, L.ptr(w), None, None, L.DT_BF16))
+
+    def load_lm_head_int8(self, q: np.ndarray, scales: np.ndarray) -> None:
+        q = np.ascontiguousarray(q).view(np.int8)
+        scales = np.ascontiguousarray(scales, np.float32)
+        L.check(self.lib.moe_head_load_tensor(self.h, L.H_LM_HEAD, L.ptr(q), L.ptr(scales), None, L.DT_INT8))
+
+    def load_lm_head_q4(self, t: Q4) -> None:
+        w, s, b = (np.ascontiguousarray(t[0], np.uint32), np.ascontiguousarray(t[1], np.uint16),
+                   np.ascontiguousarray(t[2], np.uint16))
+        L.check(self.lib.moe_head_load_tensor(self.h, L.H_LM_HEAD, L.ptr(w), L.ptr(s), L.ptr(b), L.DT_INT4))
+
+    def embed_lookup(self, ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.int64).reshape(-1)
+        out = np.empty((ids.size, self.dims.hidden), np.float32)
+        L.check(self.lib.moe_embed_lookup_host(self.h, L.ptr(ids), ids.size, L.ptr(out)))
+        return out
+
+    def logits(self, hidden: np.ndarray) -> np.ndarray:
+        hidden = np.ascontiguousarray(hidden, np.float32).reshape(-1, self.dims.hidden)
+        out = np.empty((hidden.shape[0], self.dims.vocab), np.float32)
+        L.check(self.lib.moe_logits_host(self.h, L.ptr(hidden), hidden.shape[0], L.ptr(out)))
+        return out
+
+    def forward(self, ids: np.ndarray, *, batched: bool = False, mtp: bool = False, check=None) -> np.ndarray:
+        """Token ids -> logits [n, vocab]: embedding rows, the layer stack, final norm, lm_head."""
+        ids = np.ascontiguousarray(ids, np.int64).reshape(-1)
+        out = np.empty((ids.size, self.dims.vocab), np.float32)
+        cb = L.CHECK_FN(lambda _ctx: 1 if check() else 0) if check else C.cast(None, L.CHECK_FN)
+        L.check(self.lib.moe_forward_host(self.h, L.ptr(ids), ids.size, int(batched), int(mtp), cb, None, L.ptr(out)))
+        return out
 
     def last_h_pre_norm(self) -> np.ndarray:
         out = np.empty(self.dims.hidden, np.float32)

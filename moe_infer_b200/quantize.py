@@ -1,4 +1,4 @@
-"""HF safetensors -> converted model directory, for the tensors of the MoE path.
+"""HF safetensors -> converted model directory, for the tensors of the MoE path and the model head.
 
 Follows the reference's quantize pipeline (src/quantize.rs:71-365 and
 src/quantize/qwen35_moe/{common,bq4,int4}.rs) for:
@@ -6,9 +6,13 @@ src/quantize/qwen35_moe/{common,bq4,int4}.rs) for:
     -> packed_experts/layer_NN.bin (common.rs:300-345), packed on the GPU;
   * `mlp.gate` (bf16 in the BQ4 scheme, 4-bit in INT4: bq4.rs:25-32, int4.rs:24-35),
     `mlp.shared_expert.{gate,up,down}_proj`, `mlp.shared_expert_gate` (4-bit);
-  * `post_attention_layernorm.weight` (bf16; +1 for Qwen3.6, bq4.rs:113-116).
-The 4-bit codec and the bf16 rounding are the GPU packer's (bit-exact with
-src/dtype.rs:85-135).  Attention, embedding, vision and lm_head tensors are skipped.
+  * `post_attention_layernorm.weight` (bf16; +1 for Qwen3.6, bq4.rs:113-116);
+  * the head: `embed_tokens` (4-bit in both schemes), the final `norm.weight` (bf16, +1 for Qwen3.6:
+    common.rs is_final_zc_norm) and `lm_head` (INT8 with one f32 scale per row in BQ4, bq4.rs:29; 4-bit in INT4).
+Tensor names in the manifest are the reference's (`language_model.model.layers.N...`, `language_model.lm_head`).
+A 4-bit tensor whose inner dimension is not a multiple of 64 is zero-padded to one (src/quantize.rs:230-249).
+The codecs and the bf16 rounding are the GPU packers' (bit-exact with src/dtype.rs:85-135, 164-179).
+Attention and vision tensors are skipped.
 """
 from __future__ import annotations
 
@@ -91,10 +95,20 @@ def quantize_moe_checkpoint(model_path: str, output_dir: str, *, version: str, s
                 return index[name]
         return None
 
+    def pack_q4(t: np.ndarray):
+        """4-bit triple of a 2-D tensor; the inner dimension is zero-padded to a multiple of 64 first."""
+        t = t if t.dtype == np.uint16 else _f32(t)
+        rows, cols = t.shape
+        if cols % 64:
+            padded = np.zeros((rows, (cols + 63) // 64 * 64), t.dtype)
+            padded[:, :cols] = t
+            t = padded
+        return eng.pack_int4(t)
+
     try:
         for l in range(n_layers + n_mtp):
             if l < n_layers:
-                pat, dst = r"^(?!mtp\.).*" + rf"layers\.{l}\.", f"model.layers.{l}"
+                pat, dst = r"^(?!mtp\.).*" + rf"layers\.{l}\.", f"language_model.model.layers.{l}"
             else:
                 pat, dst = rf"^mtp\.layers\.{l - n_layers}\.", f"mtp.layers.{l - n_layers}"
             gu, dn = find(pat, "mlp.experts.gate_up_proj"), find(pat, "mlp.experts.down_proj")
@@ -105,16 +119,34 @@ def quantize_moe_checkpoint(model_path: str, output_dir: str, *, version: str, s
             nv = _f32(_load(norm)).reshape(-1)
             if version == "3.6":
                 nv = nv + np.float32(1.0)
-            out.add_bf16(dst + ".post_attention_layernorm.weight", _ref_bf16(nv))
+            out.add_bf16(dst + ".post_attention_layernorm.weight", _ref_bf16(nv), flat=True)
             router = _load(find(pat, "mlp.gate.weight"))
             if scheme == "bq4":
                 out.add_bf16(dst + ".mlp.gate.weight", _ref_bf16(_f32(router)), flat=True)
             else:
-                out.add_q4(dst + ".mlp.gate", *eng.pack_int4(router if router.dtype == np.uint16 else _f32(router)))
+                out.add_q4(dst + ".mlp.gate", *pack_q4(router))
             for nm in ("shared_expert.gate_proj", "shared_expert.up_proj", "shared_expert.down_proj", "shared_expert_gate"):
                 t = _load(find(pat, f"mlp.{nm}.weight"))
                 t = t.reshape(t.shape[0], -1) if t.ndim == 2 else t.reshape(1, -1)
-                out.add_q4(dst + ".mlp." + nm, *eng.pack_int4(t if t.dtype == np.uint16 else _f32(t)))
+                out.add_q4(dst + ".mlp." + nm, *pack_q4(t))
+        # the head (optional in stripped test checkpoints)
+        emb = find(r"^(model\.language_model\.|model\.|language_model\.model\.)", "embed_tokens.weight")
+        if emb is not None:
+            out.add_q4("language_model.model.embed_tokens", *pack_q4(_load(emb)))
+        fnorm = find(r"^(model\.language_model\.|model\.|language_model\.model\.)", "norm.weight")
+        if fnorm is not None:
+            nv = _f32(_load(fnorm)).reshape(-1)
+            if version == "3.6":
+                nv = nv + np.float32(1.0)
+            out.add_bf16("language_model.model.norm.weight", _ref_bf16(nv), flat=True)
+        head = find(r"^(language_model\.)?", "lm_head.weight")
+        if head is not None:
+            t = _load(head)
+            if scheme == "bq4":
+                q, sc = eng.pack_int8(t if t.dtype == np.uint16 else _f32(t))
+                out.add_int8("language_model.lm_head", q, sc)
+            else:
+                out.add_q4("language_model.lm_head", *pack_q4(t))
     finally:
         out.close()
         eng.close()

@@ -260,3 +260,47 @@ def moe_stack(layers, h: np.ndarray, top_k: int, threads: int = 1) -> np.ndarray
     for lw in layers:
         h, _, _ = moe_layer(lw, h, top_k, threads=threads)
     return h
+
+
+# ─── the model head: embedding rows, final norm, lm_head ─────────────────────
+
+def quant_int8(vals: np.ndarray):
+    """f32 [out, in] -> (int8 [out, in], f32 scales [out]); reference src/dtype.rs:164-179."""
+    vals = _c(vals, np.float32)
+    out_dim, in_dim = vals.shape
+    q = np.empty((out_dim, in_dim), np.int8)
+    s = np.empty(out_dim, np.float32)
+    lib().orc_quant_int8(_p(vals), out_dim, in_dim, _p(q), _p(s))
+    return q, s
+
+
+def matvec_int8(w, scales, x, threads: int = 1) -> np.ndarray:
+    w = _c(w, np.int8)
+    scales = _c(scales, np.float32)
+    x = _c(x, np.float32)
+    out = np.empty(w.shape[0], np.float32)
+    lib().orc_matvec_int8(_p(w), _p(scales), _p(x), _p(out), w.shape[0], w.shape[1], threads)
+    return out
+
+
+def embed_lookup(w, s, b, token_ids) -> np.ndarray:
+    """Rows of a 4-bit table; reference src/math_util.rs:205-236."""
+    w = _c(w, np.uint32)
+    s = _c(s, np.uint16)
+    b = _c(b, np.uint16)
+    ids = np.ascontiguousarray(token_ids, np.int64).reshape(-1)
+    hidden = w.shape[1] * 8
+    out = np.empty((ids.size, hidden), np.float32)
+    for i, t in enumerate(ids):
+        lib().orc_embed_lookup(_p(w), _p(s), _p(b), C.c_int64(int(t)), hidden, _p(out[i]))
+    return out
+
+
+def final_norm(h, w_u16, eps: float = 1e-6) -> np.ndarray:
+    """Reference src/math_util.rs:240-247, on a copy."""
+    h = _c(h, np.float32).copy()
+    w_u16 = _c(w_u16, np.uint16)
+    flat = h.reshape(-1, w_u16.size)
+    for i in range(flat.shape[0]):
+        lib().orc_final_norm(_p(flat[i]), _p(w_u16), w_u16.size, C.c_float(eps))
+    return h

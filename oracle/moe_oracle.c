@@ -547,3 +547,74 @@ void orc_moe_layer_decode_mt(const orc_dims_t* d, const orc_layer_t* ly, const f
     free(post); free(scores); free(g); free(u); free(act); free(eout); free(sdown);
 }
 
+
+/* ─── the model head: embedding rows, final norm, lm_head ──────────────── */
+
+/* quant_f32_to_int8: src/dtype.rs:164-179.  Per-row symmetric: scale = max|v| / 127 (1/127 for an
+ * all-zero row), q = clamp(round(v * (1 / scale)), -127, 127); Rust's f32::round rounds half away
+ * from zero, like roundf. */
+void orc_quant_int8(const float* vals, int out_dim, int in_dim, int8_t* packed, float* scales) {
+    for (int row = 0; row < out_dim; ++row) {
+        const float* r = vals + (size_t)row * in_dim;
+        float max_abs = 0.0f;
+        for (int j = 0; j < in_dim; ++j) max_abs = rust_max(max_abs, fabsf(r[j]));
+        const float scale = max_abs > 0.0f ? max_abs / 127.0f : 1.0f / 127.0f;
+        scales[row] = scale;
+        const float inv_scale = 1.0f / scale;
+        int8_t* dst = packed + (size_t)row * in_dim;
+        for (int j = 0; j < in_dim; ++j) {
+            int32_t q = rust_f32_as_i32(roundf(r[j] * inv_scale));
+            if (q < -127) q = -127;
+            if (q > 127) q = 127;
+            dst[j] = (int8_t)q;
+        }
+    }
+}
+
+/* matvec_int8 (src/engine/shaders.metal:2435-2471): out[row] = sum_col float(w) * scale * x, stated as a
+ * sequential f32 sum in column order (the shader strides the columns over 32 lanes). */
+static void matvec_int8_rows(const int8_t* w, const float* scales, const float* x, float* out, int r0, int r1, int in_dim) {
+    for (int row = r0; row < r1; ++row) {
+        const int8_t* w_row = w + (size_t)row * in_dim;
+        const float scale = scales[row];
+        float acc = 0.0f;
+        for (int c = 0; c < in_dim; ++c) acc += (float)w_row[c] * scale * x[c];
+        out[row] = acc;
+    }
+}
+typedef struct { const int8_t* w; const float* scales; const float* x; float* out; int in_dim; } mv8_ctx;
+static void mv8_range(int r0, int r1, void* p) {
+    mv8_ctx* c = (mv8_ctx*)p;
+    matvec_int8_rows(c->w, c->scales, c->x, c->out, r0, r1, c->in_dim);
+}
+void orc_matvec_int8(const int8_t* w, const float* scales, const float* x, float* out, int out_dim, int in_dim, int threads) {
+    mv8_ctx c = {w, scales, x, out, in_dim};
+    orc_par_for(out_dim, mv8_range, &c, threads);
+}
+
+/* embed_lookup: src/math_util.rs:205-236.  One row of the 4-bit embedding table, (nibble as f32) * scale + bias. */
+void orc_embed_lookup(const uint32_t* w, const uint16_t* s, const uint16_t* b, int64_t token_id, int hidden, float* out) {
+    const int num_groups = hidden / ORC_GROUP, packed_cols = hidden / 8, packed_per_group = ORC_GROUP / 8;
+    const uint32_t* w_row = w + (size_t)token_id * packed_cols;
+    const uint16_t* s_row = s + (size_t)token_id * num_groups;
+    const uint16_t* b_row = b + (size_t)token_id * num_groups;
+    for (int g = 0; g < num_groups; ++g) {
+        const float scale = orc_bf16_to_f32(s_row[g]), bias = orc_bf16_to_f32(b_row[g]);
+        const int base = g * ORC_GROUP;
+        for (int p = 0; p < packed_per_group; ++p) {
+            const uint32_t packed = w_row[g * packed_per_group + p];
+            for (int n = 0; n < 8; ++n) {
+                const uint32_t nibble = (packed >> (n * 4)) & 0xF;
+                out[base + p * 8 + n] = (float)nibble * scale + bias;
+            }
+        }
+    }
+}
+
+/* final_norm: src/math_util.rs:240-247.  hidden[i] *= inv_rms * w[i], in place. */
+void orc_final_norm(float* hidden, const uint16_t* w, int dim, float eps) {
+    float sum_sq = 0.0f;
+    for (int i = 0; i < dim; ++i) sum_sq += hidden[i] * hidden[i];
+    const float inv_rms = 1.0f / sqrtf(sum_sq / (float)dim + eps);
+    for (int i = 0; i < dim; ++i) hidden[i] *= inv_rms * orc_bf16_to_f32(w[i]);
+}

@@ -13,7 +13,7 @@ from benchmarks import synth
 from tests.util import rel_l2
 
 pytestmark = pytest.mark.gpu
-E, K, H, I = 4, 4, 2048, 512
+E, K, H, I, V = 4, 4, 2048, 512, 100
 
 
 def _write_safetensors(path, tensors):
@@ -52,8 +52,24 @@ def _hf_checkpoint(tmp, layers, mtp):
                    p + "mlp.shared_expert.down_proj.weight": b(t["shared_down"]),
                    p + "mlp.shared_expert_gate.weight": b(t["shared_sgate"]),
                    p + "post_attention_layernorm.weight": b(t["post_norm"])})
+    rng = np.random.default_rng(99)
+    head = {"embed": synth.bf16_to_f32(synth.to_bf16_rne(synth.normal_weights(rng, (V, H)))),
+            "norm": synth.bf16_to_f32(synth.to_bf16_rne(rng.uniform(-0.1, 0.1, H).astype(np.float32))),
+            "lm_head": synth.bf16_to_f32(synth.to_bf16_rne(synth.normal_weights(rng, (V, H))))}
+    ts.update({"model.language_model.embed_tokens.weight": synth.to_bf16_rne(head["embed"]),
+               "model.language_model.norm.weight": synth.to_bf16_rne(head["norm"]),
+               "lm_head.weight": synth.to_bf16_rne(head["lm_head"])})
     _write_safetensors(os.path.join(tmp, "model-00001-of-00001.safetensors"), ts)
-    return raw
+    return raw, head
+
+
+def _oracle_logits(head, scheme, hidden):
+    x = oracle.final_norm(hidden, oracle.f32_to_bf16(head["norm"] + np.float32(1.0)))
+    if scheme == "bq4":
+        q, sc = oracle.quant_int8(head["lm_head"])
+        return np.stack([oracle.matvec_int8(q, sc, xi) for xi in x])
+    w, s, b = oracle.quant_int4(head["lm_head"])
+    return np.stack([oracle.matvec_int4(w, s, b, xi) for xi in x])
 
 
 def _oracle_layers(raw, scheme):
@@ -72,7 +88,7 @@ def _oracle_layers(raw, scheme):
 @pytest.mark.parametrize("scheme", ["bq4", "int4"])
 def test_quantize_load_forward(tmp_path, scheme):
     src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
-    raw = _hf_checkpoint(src, layers=2, mtp=1)
+    raw, head = _hf_checkpoint(src, layers=2, mtp=1)
     rs.qwen35_moe_quantize(src, dst, version="3.6", scheme=scheme)
     ref_layers = _oracle_layers(raw, scheme)
     for l, lw in enumerate(ref_layers):  # packed bytes identical to the reference packer's
@@ -82,20 +98,58 @@ def test_quantize_load_forward(tmp_path, scheme):
     cache = rs.Cache(model)
     emb = synth.hidden_states(3, 2, 5, H)
     rs.record_engine_telemetry(True)
-    out = eng.forward_hidden(emb, cache)
+    out = eng.forward_hidden_states(emb, cache)
     rs.record_engine_telemetry(False)
     ref = oracle.moe_stack(ref_layers[:2], emb, K)
     assert out.shape == (5, H) and rel_l2(out, ref) < 1e-2
     assert cache.pos == 5 and cache.gpu_dirty and eng.telemetry()["engine.total_ms"] > 0
     assert np.array_equal(eng.last_h_pre_norm(), out[-1])
-    out_b = eng.forward_batched(np.arange(3, dtype=np.int64), cache)       # no embedding table: zeros in, finite out
-    assert out_b.shape == (3, H) and cache.pos == 8
-    assert eng.forward(np.zeros(0, np.int64), cache).shape == (0, H)
+    # the reference surface: logits [n, vocab] from embeddings and from token ids
+    logits = eng.forward_hidden(emb, cache)
+    assert logits.shape == (5, V) and rel_l2(logits, _oracle_logits(head, scheme, ref)) < 1e-2
+    ids = np.array([3, 99, 0], np.int64)
+    ew, es, eb = oracle.quant_int4(head["embed"])
+    emb_ref = oracle.embed_lookup(ew, es, eb, ids)
+    assert np.array_equal(eng.embed_lookup(ids), emb_ref)                  # row dequantisation is exact
+    want = _oracle_logits(head, scheme, oracle.moe_stack(ref_layers[:2], emb_ref, K))
+    got = eng.forward(ids, cache)
+    assert got.shape == (3, V) and rel_l2(got, want) < 1e-2
+    got_b = eng.forward_batched(ids, cache)                                # grouped path: bf16 operands
+    assert got_b.shape == (3, V) and rel_l2(got_b, want) < 2e-2 and cache.pos == 16
+    assert np.array_equal(got.argmax(axis=1), want.argmax(axis=1))
+    assert eng.forward(np.zeros(0, np.int64), cache).shape == (0, V)
+    with pytest.raises(ValueError, match="token id"):
+        eng.forward(np.array([V], np.int64), cache)
     snap = eng.snapshot_state()
     m = eng.mtp_forward(0)                                                 # MoE half of the MTP block (layer index 2)
     ref_m, _, _ = oracle.moe_layer(ref_layers[2], eng.last_h_pre_norm(), K)
     assert rel_l2(m, ref_m[0]) < 1e-2
-    eng.forward_hidden(emb[:1], cache)
+    with pytest.raises(ValueError):
+        eng.mtp_forward(V)
+    eng.forward_hidden_states(emb[:1], cache)
     eng.restore_snapshot(snap)
-    assert eng.pos == 8
+    assert eng.pos == 16
     eng.native.close()
+
+
+def test_top_level_module_alias_runs_a_forward(tmp_path):
+    """The reference's Python does `import _moe_infer_rs as _rs` (moe_infer/_core.py:14, pipeline.py:16): with the mirror
+    registered under that name, the call sequence of pipeline.py:250-254 and :361-367 runs on the GPU."""
+    import sys
+    sys.modules["_moe_infer_rs"] = rs
+    import _moe_infer_rs as _rs
+    src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
+    _hf_checkpoint(src, layers=1, mtp=0)
+    _rs.qwen35_moe_quantize(src, dst, version="3.6", scheme="bq4")
+    model = _rs.Model(dst)
+    engine = _rs.Engine(model, "Qwen35MoEFusedExp2", 0, expert_cache_count=0)
+    cache = _rs.Cache(model)
+    ids = np.array([1, 2, 3], np.int64)
+    emb = engine.embed_lookup(ids)
+    logits = engine.forward_hidden(emb, cache)
+    assert logits.shape == (3, V) and np.isfinite(logits).all()
+    again = engine.forward(ids, cache)
+    assert np.allclose(again, logits, rtol=1e-5, atol=1e-6) and cache.pos == 6
+    cache.reset()
+    assert isinstance(engine.telemetry(), dict)
+    engine.native.close()
