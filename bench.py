@@ -273,6 +273,8 @@ def run_decode(args, rank, world, local, dist):
         parity["prefill_4096x40"] = {"rel_l2_vs_decode_path": secondary["prefill_4096x40"]["parity_rel_l2_vs_decode_path"],
                                      "rel_l2_vs_single_gpu": secondary["prefill_4096x40"]["parity_rel_l2_vs_single_gpu"]}
         secondary["pack"] = workloads.run_pack(args, rank, world, local, dist)
+        if world == 1:
+            secondary["lm_head_int8"] = workloads.run_lm_head(args, local, "int8")
 
     if rank == 0:
         line = {

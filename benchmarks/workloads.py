@@ -276,6 +276,44 @@ def run_pack(args, rank: int, world: int, local: int, dist) -> dict:
     return out
 
 
+# ─── lm_head: the largest single read of a decode step ────────────────────────
+
+def run_lm_head(args, local: int, kind: str = "int8", vocab: int = 248320) -> dict:
+    """final norm + lm_head for one token: vocab x 2048 INT8 rows (BQ4 scheme) or 4-bit rows (INT4 scheme)."""
+    import ctypes as C
+    dims = Dims(num_layers=1, num_experts=4, top_k=4, vocab=vocab)
+    eng = NativeEngine(dims, device=local)
+    H = dims.hidden
+    rng = np.random.default_rng(args.seed)
+    eng.load_final_norm(synth.to_bf16_rne(np.ones(H, np.float32)))
+    if kind == "int8":
+        q = rng.integers(-127, 128, size=(vocab, H), dtype=np.int8)
+        eng.load_lm_head_int8(q, np.full(vocab, 2e-4, np.float32))
+        by = vocab * H + vocab * 4
+    else:
+        w = rng.integers(0, 2**32, size=(vocab, H // 8), dtype=np.uint64).astype(np.uint32)
+        sb = np.full((vocab, H // 64), 0x3C00, np.uint16)
+        eng.load_lm_head_q4((w, sb, sb))
+        by = vocab * H // 2 + 2 * vocab * (H // 64) * 2
+    h = synth.hidden_states(args.seed, 2, 4, H)
+    d_h = eng.alloc(h.nbytes).upload(h)
+    d_l = eng.alloc(vocab * 4)
+
+    def step(i):
+        L.check(eng.lib.moe_logits_dev(eng.h, C.c_void_p(d_h.ptr + (i % 4) * H * 4), 1, C.c_void_p(d_l.ptr)))
+
+    t = timed_repeats(eng, step, max(3, min(args.warmup, 10)), max(1, min(args.steps, 20)))
+    out = {"workload": f"final norm + lm_head, 1 token: {vocab} x {H} {'INT8 rows, one f32 scale per row' if kind == 'int8' else '4-bit rows'} "
+                       f"({by / 1e6:.0f} MB per call, larger than L2)",
+           "us_per_call": t["ms_per_step"] * 1e3, "repeats": t["repeats"], "gpu_launches": t["launches"],
+           "roofline": hbm_roofline("matvec_int8_stream_kernel" if kind == "int8" else "matvec_int4_stream_kernel", by + vocab * 4,
+                                    t["ms_per_step"])}
+    d_h.free()
+    d_l.free()
+    eng.close()
+    return out
+
+
 # ─── config 1 on the GPU, and the matvec at HBM size ──────────────────────────
 
 def run_matvec(args, eng: NativeEngine, local: int, rows: int = 512, cols: int = 2048, copies: int = 512) -> dict:
@@ -306,7 +344,8 @@ def run_matvec(args, eng: NativeEngine, local: int, rows: int = 512, cols: int =
     out = {"workload": f"{rows} x {cols} 4-bit dequant-matvec per launch, rotating over {copies} distinct matrices "
                        f"({copies * (wb + 2 * sb) / 1e6:.0f} MB)",
            "us_per_call": t["ms_per_step"] * 1e3, "repeats": t["repeats"], "gpu_launches": t["launches"],
-           "roofline": hbm_roofline("matvec_int4_kernel", by, t["ms_per_step"])}
+           "roofline": hbm_roofline("matvec_int4_stream_kernel" if (cols == 2048 and rows >= 4096) else "matvec_int4_kernel", by,
+                                    t["ms_per_step"])}
     for buf in (w, s, b, src, dx, dy):
         buf.free()
     return out

@@ -165,6 +165,11 @@ struct moe_engine {
     unsigned long long* dec_h_ll = nullptr;    // fused decode kernel: tagged hidden state between layers
     long long* dec_prof = nullptr;         // per-phase clock stamps (off unless enabled)
     int dec_grid = 0;
+    // slot-grouped decode kernel (decode_slots.cu)
+    bool dec_sl_ok = false;                     // device and model shape fit it
+    unsigned long long* dec_sl_words = nullptr; // accumulators, tagged SwiGLU outputs, counters (one allocation)
+    unsigned long long dec_sl_hint_base = 0, dec_sl_act_base = 0;
+    unsigned int dec_sl_epoch = 0;
     bool matvec_attr_set = false;          // matvec kernel's shared-memory attribute set on this engine's device
     float* stage_host = nullptr;           // pinned staging [H] x 2
     std::vector<float> last_h;             // last_h_pre_norm

@@ -1286,7 +1286,7 @@ int decode_init(moe_engine* e) {
                                                            sizeof(DecodeSmem)));
     MOE_REQUIRE(per_sm >= 1, "decode kernel does not fit on an SM");
     e->dec_grid = e->sm_count;  // one CTA per SM, all co-resident (cooperative launch)
-    return MOE_OK;
+    return slots_decode_init(e);
 }
 
 // Turns the per-phase clock stamps on or off (a device buffer of
@@ -1313,6 +1313,7 @@ int decode_profile_read(moe_engine* e, long long* out, int max_layers, int* poin
 }
 
 void decode_destroy(moe_engine* e) {
+    slots_decode_destroy(e);
     if (e->dec_prof) cudaFree(e->dec_prof);
     cudaFree(e->dec_sync);
     cudaFree(e->dec_act_ll); cudaFree(e->dec_acc); cudaFree(e->dec_hint); cudaFree(e->dec_h_ll);
@@ -1327,6 +1328,8 @@ int decode_reset_after_error(moe_engine* e) {
     MOE_CUDA(cudaMemsetAsync(e->dec_hint, 0, 256, e->stream));
     MOE_CUDA(cudaMemsetAsync(e->dec_h_ll, 0, kH * sizeof(unsigned long long), e->stream));
     e->dec_hint_base = 0;
+    int rc = slots_decode_reset(e);
+    if (rc != MOE_OK) return rc;
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     e->dec_epoch = 0;
     return MOE_OK;
@@ -1361,7 +1364,10 @@ int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
     for (int a = l0; a < l1; a += kMaxDecLayers) {
         const int b = a + kMaxDecLayers < l1 ? a + kMaxDecLayers : l1;
-        int rc = launch_decode_chunk(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w);
+        // the slot-grouped kernel where the device and the model shape allow it, the grid-wide kernel otherwise
+        int rc = slots_decode_usable(e, a, b)
+                     ? launch_decode_slots(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w)
+                     : launch_decode_chunk(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w);
         if (rc != MOE_OK) return rc;
     }
     return MOE_OK;

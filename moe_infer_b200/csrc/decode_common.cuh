@@ -1,4 +1,4 @@
-// Device helpers of the decode kernels (decode.cu): model
+// Device helpers shared by the decode kernels (decode.cu, decode_slots.cu): model
 // constants, 16-byte asynchronous copies, the integer dot product of staged 4-bit rows,
 // and the on-device routing (softmax / top-k / renormalise of the reference's
 // route_experts, src/engine/qwen35_moe/cpu.rs:78-85).
@@ -171,5 +171,13 @@ __device__ __forceinline__ void route_weights(SM* sm, float v, int E, int K) {
     __syncthreads();
 }
 
+
+// Entry points of the slot-grouped decode kernel (decode_slots.cu).
+int slots_decode_init(moe_engine* e);
+void slots_decode_destroy(moe_engine* e);
+bool slots_decode_usable(const moe_engine* e, int l0, int l1);
+int slots_decode_reset(moe_engine* e);
+int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float* h_out, const float* logit_bias,
+                        const int32_t* forced_idx, int32_t* out_idx, float* out_w);
 
 }  // namespace moe
