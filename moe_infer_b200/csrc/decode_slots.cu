@@ -143,10 +143,9 @@ __device__ __forceinline__ int wait_count(const unsigned long long* ctr, unsigne
 }
 
 // x = rmsnorm(h) * w (rms_norm_bf16, reference src/math_util.rs:282-288, eps 1e-6) staged as digit planes;
-// h given as this thread's float4 (elements 4 tid ..), 1 / rms(h) already known.
-__device__ __forceinline__ void stage_x(SlotSmem* sm, const uint16_t* norm_w, const float4 v, float inv_rms) {
+// h given as this thread's float4 (elements 4 tid ..), its four norm weights as bf16 pairs, 1 / rms(h) already known.
+__device__ __forceinline__ void stage_x(SlotSmem* sm, const uint2 wb, const float4 v, float inv_rms) {
     const int tid = threadIdx.x;
-    const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + tid);
     float4 o;
     o.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
     o.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
@@ -300,6 +299,39 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         return __syncthreads_and(ok) != 0;
     };
 
+    // Requests this CTA's weight slices of a layer: every slice is one contiguous range of the slot's expert.  One copy
+    // per warp (lane 0): copies issued by several lanes of one warp would go out one after the other.
+    auto request_weights = [&](const LayerDev& ly) {
+        const uint8_t* ex = shared_slot ? ly.shared : ly.experts + (size_t)sm->topi[slot] * L.expert_size;
+        if (lane == 0 && warp < 12) {
+            const int b = warp / 6, a = warp - b * 6;  // batch, array
+            const bool is_w = a < 2;
+            const int64_t off = a == 0 ? L.gate_w : a == 1 ? L.up_w : a == 2 ? L.gate_s : a == 3 ? L.up_s : a == 4 ? L.gate_b : L.up_b;
+            const uint32_t row_bytes = is_w ? kH / 2 : (kH / kGroup) * 2;
+            const int j0 = b * kBatch;
+            void* dst = a == 0 ? (void*)sm->gu_w[0][j0] : a == 1 ? (void*)sm->gu_w[1][j0] : a == 2 ? (void*)sm->gu_s[0][j0]
+                      : a == 3 ? (void*)sm->gu_s[1][j0] : a == 4 ? (void*)sm->gu_b[0][j0] : (void*)sm->gu_b[1][j0];
+            const uint32_t bytes = kBatch * row_bytes;
+            mbar_expect_tx(&sm->bar_g[b], bytes);
+            bulk_g2s(dst, ex + off + (size_t)(item0 + j0) * row_bytes, bytes, &sm->bar_g[b]);
+        } else if (lane == 0 && warp < 15) {
+            const int q = warp - 12;
+            const int64_t off = q == 0 ? L.down_w : q == 1 ? L.down_s : L.down_b;
+            const uint32_t row_bytes = q == 0 ? kI / 2 : (kI / kGroup) * 2;
+            void* dst = q == 0 ? (void*)sm->dn_w : q == 1 ? (void*)sm->dn_s : (void*)sm->dn_b;
+            const uint32_t bytes = kDnRows * row_bytes;
+            mbar_expect_tx(&sm->bar_d, bytes);
+            bulk_g2s(dst, ex + off + (size_t)r0 * row_bytes, bytes, &sm->bar_d);
+        }
+        if (shared_slot && lane == 1 && warp < 3) {
+            const void* src = warp == 0 ? (const void*)ly.sgate.w : warp == 1 ? (const void*)ly.sgate.s : (const void*)ly.sgate.b;
+            void* dst = warp == 0 ? (void*)sm->sg_w : warp == 1 ? (void*)sm->sg_s : (void*)sm->sg_b;
+            const uint32_t bytes = warp == 0 ? kH / 2 : (kH / kGroup) * 2;
+            mbar_expect_tx(&sm->bar_g[1], bytes);
+            bulk_g2s(dst, src, bytes, &sm->bar_g[1]);
+        }
+    };
+
     // ── prologue: router logits of the first layer from h_in (the first group's rows cover all of h) ──
     {
         load_router_slice(rt, sm->tab[0].router_t, Ep, rt_row0, rt_e2);
@@ -327,6 +359,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         const bool has_next = rel + 1 < n_layers;
         const unsigned int epoch = p.epoch_base + (unsigned int)rel + 1u;
         SPROF(0);
+        // the shared expert's slices depend on nothing but the layer: requested before the layer's input is known
+        if (shared_slot) request_weights(ly);
+        // norm weights of this thread's elements (this layer) and of this CTA's output rows (next layer): requested now,
+        // used after the layer's input has arrived
+        const uint2 norm_wb = __ldg(reinterpret_cast<const uint2*>(ly.post_norm) + tid);
+        uint16_t nwn_bits = 0;
+        if (has_next && tid < kDnRows) nwn_bits = __ldg(sm->tab[rel + 1].post_norm + r0 + tid);
         // ── this layer's input: h (sums of the layer before) and the router logits ──
         long long lq = 0;
         if (!read_acc(rel + 1, rel > 0, (rel + 1) & 1, true, rel & 1, lq)) {
@@ -343,47 +382,15 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         }
         route_select(sm, v, p.forced_idx, E, K, p.err);
         SPROF(2);
-
-        // ── weight requests: every slice is one contiguous range of this slot's expert ──
-        {
-            const uint8_t* ex = shared_slot ? ly.shared : ly.experts + (size_t)sm->topi[slot] * L.expert_size;
-            if (warp == 0 && lane < 12) {
-                const int b = lane / 6, a = lane - b * 6;  // batch, array
-                const bool is_w = a < 2;
-                const int64_t off = a == 0 ? L.gate_w : a == 1 ? L.up_w : a == 2 ? L.gate_s : a == 3 ? L.up_s : a == 4 ? L.gate_b : L.up_b;
-                const uint32_t row_bytes = is_w ? kH / 2 : (kH / kGroup) * 2;
-                const int j0 = b * kBatch;
-                void* dst = a == 0 ? (void*)sm->gu_w[0][j0] : a == 1 ? (void*)sm->gu_w[1][j0] : a == 2 ? (void*)sm->gu_s[0][j0]
-                          : a == 3 ? (void*)sm->gu_s[1][j0] : a == 4 ? (void*)sm->gu_b[0][j0] : (void*)sm->gu_b[1][j0];
-                const uint32_t bytes = kBatch * row_bytes;
-                mbar_expect_tx(&sm->bar_g[b], bytes);
-                bulk_g2s(dst, ex + off + (size_t)(item0 + j0) * row_bytes, bytes, &sm->bar_g[b]);
-            } else if (warp == 1 && lane < 3) {
-                const int64_t off = lane == 0 ? L.down_w : lane == 1 ? L.down_s : L.down_b;
-                const uint32_t row_bytes = lane == 0 ? kI / 2 : (kI / kGroup) * 2;
-                void* dst = lane == 0 ? (void*)sm->dn_w : lane == 1 ? (void*)sm->dn_s : (void*)sm->dn_b;
-                const uint32_t bytes = kDnRows * row_bytes;
-                mbar_expect_tx(&sm->bar_d, bytes);
-                bulk_g2s(dst, ex + off + (size_t)r0 * row_bytes, bytes, &sm->bar_d);
-            } else if (shared_slot && warp == 2 && lane < 3) {
-                const void* src = lane == 0 ? (const void*)ly.sgate.w : lane == 1 ? (const void*)ly.sgate.s : (const void*)ly.sgate.b;
-                void* dst = lane == 0 ? (void*)sm->sg_w : lane == 1 ? (void*)sm->sg_s : (void*)sm->sg_b;
-                const uint32_t bytes = lane == 0 ? kH / 2 : (kH / kGroup) * 2;
-                mbar_expect_tx(&sm->bar_g[1], bytes);
-                bulk_g2s(dst, src, bytes, &sm->bar_g[1]);
-            }
-        }
+        // ── weight requests (the shared expert's group made them at the top of the layer) ──
+        if (!shared_slot) request_weights(ly);
         SPROF(3);
         // the copies are on their way: stage x, the softmax weights of the chosen experts, and what the end of
         // the layer needs from the layer's input
-        stage_x(sm, ly.post_norm, hv, inv_rms);
+        stage_x(sm, norm_wb, hv, inv_rms);
         if (warp == grank) reinterpret_cast<float4*>(sm->hrow)[lane] = (slot == 0) ? hv : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (has_next && tid < kDnRows) sm->nwn[tid] = __uint_as_float((uint32_t)__ldg(sm->tab[rel + 1].post_norm + r0 + tid) << 16);
-        route_weights(sm, v, E, K);  // ends with a CTA barrier: x is staged for every warp
-        if (blockIdx.x == 0 && warp == 0 && lane < K) {
-            if (p.out_idx) p.out_idx[lane] = sm->topi[lane];
-            if (p.out_w) p.out_w[lane] = sm->topw[lane];
-        }
+        if (tid < kDnRows) sm->nwn[tid] = __uint_as_float((uint32_t)nwn_bits << 16);
+        __syncthreads();  // x is staged for every warp
         SPROF(4);
 
         // ── gate/up + SwiGLU: two row pairs per warp (items warp and warp + 16); a lane holds the digits of one
@@ -391,7 +398,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         int ok = 1;
         {
             const bool sg_now = shared_slot && warp == kDecWarps - 1;  // the gate score: one more row for one warp
-            ok = (wait_bar(&sm->bar_g[0], ph, p.err) && wait_bar(&sm->bar_g[1], ph, p.err)) ? 1 : 0;
+            ok = wait_bar(&sm->bar_g[0], ph, p.err) ? 1 : 0;
+            SPROF(10);
+            ok = (ok && wait_bar(&sm->bar_g[1], ph, p.err)) ? 1 : 0;
+            SPROF(11);
             float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, sg = 0.0f;
             if (ok) {
 #pragma unroll
@@ -449,12 +459,18 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
                 asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(grp + item0 + lane), "l"(word) : "memory");
                 __syncwarp();
                 // not ordered against the stores above (no fence): readers use it only to decide when to start reading
-                if (lane == 0) {
+                if (lane == 0)
                     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.act_hint + slot * kHintStride), "l"(1ull) : "memory");
-                    sm->flag = wait_count(p.act_hint + slot * kHintStride,
-                                          p.act_hint_base + (unsigned long long)kGrpCtas * (unsigned long long)(rel + 1), p.err);
-                }
             }
+            // while the group's outputs arrive: the softmax weights of the chosen experts (needed from the down phase on)
+            route_weights(sm, v, E, K);  // ends with a CTA barrier
+            if (blockIdx.x == 0 && warp == 0 && lane < K) {
+                if (p.out_idx) p.out_idx[lane] = sm->topi[lane];
+                if (p.out_w) p.out_w[lane] = sm->topw[lane];
+            }
+            if (tid == 0)
+                sm->flag = wait_count(p.act_hint + slot * kHintStride,
+                                      p.act_hint_base + (unsigned long long)kGrpCtas * (unsigned long long)(rel + 1), p.err);
             __syncthreads();
             ok = sm->flag;
             if (tid < kI / 4) {  // four whole warps: thread t takes values 4 t .. 4 t + 3
