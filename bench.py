@@ -29,7 +29,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-NCU_DRAM_BYTES_PER_LAYER = 17.24e6  # (68.00 MB read + 0.97 MB written) / 4 layers: profiles/decode_fused_kernel_4layers.md
+NCU_DRAM_BYTES_PER_LAYER = 17.24e6  # (68.00 MB read + 0.97 MB written) / 4 layers: profiles/decode_slots_kernel_4layers.md
 N_ROTATE = 64  # distinct input tokens cycled through, so routing differs from step to step
 DECODE_DTYPE = "u4 weights x 24-bit fixed-point activations (three s8 digits), exact s32 dp4a sums, f32 scales"
 
@@ -236,7 +236,7 @@ def run_decode(args, rank, world, local, dist):
     bytes_per_launch = benchlib.layer_token_bytes(dims) * dims.num_layers
     default_shape = (dims.hidden, dims.inter, dims.num_experts, dims.top_k) == (2048, 512, 256, 8)
     traffic = NCU_DRAM_BYTES_PER_LAYER * dims.num_layers if default_shape else None
-    roof = workloads.hbm_roofline("decode_fused_kernel", bytes_per_launch, ms_region / K, traffic=traffic,
+    roof = workloads.hbm_roofline("decode_slots_kernel", bytes_per_launch, ms_region / K, traffic=traffic,
                                   traffic_source="ncu dram__bytes_read+write of a 4-layer launch, per layer, x layers"
                                   if default_shape else None)
     roof["bytes_per_launch"] = bytes_per_launch

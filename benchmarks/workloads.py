@@ -112,7 +112,7 @@ def run_layer(args, eng: NativeEngine, local: int) -> dict:
     out = {"workload": f"config 2: one MoE layer, batch-1 decode, {dims.num_experts} experts top-{dims.top_k}, BQ4; "
                        f"rotating over {n_copies} layer copies (L2 cannot hold them)",
            "us_per_layer": t["ms_per_step"] * 1e3, "repeats": t["repeats"], "gpu_launches": t["launches"],
-           "roofline": hbm_roofline("decode_fused_kernel (1 layer)", b, t["ms_per_step"])}
+           "roofline": hbm_roofline("decode_slots_kernel (1 layer)", b, t["ms_per_step"])}
     d_in.free()
     d_out.free()
     return out

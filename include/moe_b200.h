@@ -238,12 +238,17 @@ int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n);
 /* Fine-grained phase timing of the decode kernel, the device-side counterpart of
  * the reference's `phase.*` telemetry (src/engine/qwen35_moe/fused_exp5.rs:162-177).
  * With stamps == NULL: switches recording on (enable != 0) or off.  Otherwise
- * copies the SM-clock stamps of the last decode launch, [layer][*points_per_layer],
- * taken by CTA 0 at: layer start, norm staged and phase-A weights landed, router
- * and shared rows done, barrier 1 passed, next layer's phase-A copies issued,
- * top-k done, gate/up/down copies issued, gate/up weights landed, gate/up rows
- * done, barrier 2 passed, activations staged and down weights landed, down rows
- * and combine done. */
+ * copies the SM-clock stamps of the last decode launch, [layer][*points_per_layer]
+ * (12 per layer), taken by thread 0 of CTA 0.  The default (slot-grouped) kernel
+ * stamps: 0 layer start; 1 residual and router sums of the previous layer read,
+ * 1/rms known; 2 top-k done; 3 this CTA's weight slices requested; 4 input staged
+ * as digit planes; 10 / 11 first / second half of the gate/up slices landed;
+ * 5 gate/up rows and SwiGLU done; 6 the group's 512 SwiGLU values gathered and
+ * staged, down slices landed; 7 down rows added to the residual sums; 8 this CTA's
+ * share of the next layer's router logits added, layer counter bumped; 9 (last
+ * layer only) result written.  The grid-wide fallback kernel stamps its own
+ * twelve points in the same order of events (copies issued, landed, rows done,
+ * barrier passed) for its three phases. */
 int moe_decode_profile(moe_engine_t* e, int enable, int64_t* stamps, int max_layers, int* points_per_layer);
 
 /* ── expert parallelism over the GPUs of one box ─────────────────────────────

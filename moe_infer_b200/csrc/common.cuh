@@ -146,7 +146,7 @@ struct moe_engine {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
     moe_expert_layout_t lay{};         // routed experts
     moe_expert_layout_t shared_lay{};  // shared expert (hidden, shared_inter)
     std::vector<moe::LayerHost> layers;  // num_layers + num_mtp_layers

@@ -631,19 +631,6 @@ constexpr int kAccPitch = 1;  // distance between accumulators in words (spreadi
 constexpr int kAccStride = (kMaxE + 8) * kAccPitch;
 constexpr int kLLGroups = ((kMaxK + 1) * (kI / 4) + kDecThreads - 1) / kDecThreads;  // 4-value groups per thread
 
-#ifdef MOE_DEC_SKEW
-// build-time diagnostic: wall-clock stamps of every CTA at a few points of one layer
-__device__ long long g_dbg[8 * 1024];
-__device__ __forceinline__ long long gtime() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define DBG(k) do { if (p.prof && l == p.l0 + 4 && tid == 0) g_dbg[(k) * 1024 + cta] = gtime(); } while (0)
-#define RT(k) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_dbg[7 * 1024 + 512 + (k)] = clock64(); } while (0)
-#define DBGW(k) do { if (p.prof && l == p.l0 + 4 && lane == 0) atomicMax((unsigned long long*)&g_dbg[(k) * 1024 + cta], (unsigned long long)gtime()); } while (0)
-#else
-#define DBG(k) do { } while (0)
-#define DBGW(k) do { } while (0)
-#define RT(k) do { } while (0)
-#endif
-
 struct Decode3Params {
     const LayerDev* layers;
     int l0, l1;
@@ -747,7 +734,6 @@ __device__ __forceinline__ int router_t_stride(int E) { return (E + 7) & ~7; }  
 // (gate/up weights, scales, biases) is at most two contiguous byte ranges (one per slot
 // touched): twelve bulk copies, issued by twelve different threads, each announcing its own
 // bytes on the mbarrier (which counts kBCopies arrivals per phase).
-constexpr bool kBulk = true;    // gate/up slices by bulk copy
 constexpr int kBCopies = 12;
 
 __device__ __forceinline__ void bulk_B_copy(DecodeSmem3* sm, const LayerDev& ly, const moe_expert_layout_t& L,
@@ -943,7 +929,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
 
         // ── route (from the accumulators) while h is being staged ──────────
         PROF3(0);
-        DBG(4);
         float vlogit = -INFINITY;  // this thread's router logit (thread t owns expert t)
         {
             // every CTA has announced the end of the previous phase (a hint: the words below validate themselves)
@@ -983,14 +968,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             vlogit = v;
         }
         PROF3(1);
-        if (kBulk) {
-            // one copy per thread: gate/up slices first, then everything the down phase needs
-            if (lane == 0 && warp < kBCopies) bulk_B_copy(sm, ly, L, i0, nb, K, warp);
-            if (sg_here) prefetch_B3_warp(sm, ly, L, i0, 0, K, true, warp, lane);  // the gate-score row only
-            else cp_commit();
-        } else {
-            prefetch_B3_warp(sm, ly, L, i0, nb, K, sg_here, warp, lane);
-        }
+        // one bulk copy per thread: gate/up slices first, then everything the down phase needs
+        if (lane == 0 && warp < kBCopies) bulk_B_copy(sm, ly, L, i0, nb, K, warp);
+        if (sg_here) prefetch_B3_warp(sm, ly, L, i0, 0, K, true, warp, lane);  // the gate-score row only
+        else cp_commit();
         // the copies are on their way: now the softmax weights of the chosen experts
         route_weights(sm, vlogit, E, K);
         if (cta == 0 && warp == 0 && lane < K) {
@@ -1035,7 +1016,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
         PROF3(3);
         int landed = 1;
         cp_wait<0>();  // this warp's gate/up rows (and the gate-score row) landed
-        if (kBulk) landed = mbar_wait(&sm->bar_b, wpar) ? 1 : 0;
+        landed = mbar_wait(&sm->bar_b, wpar) ? 1 : 0;
         __syncwarp();
         PROF3(4);
         {
@@ -1066,7 +1047,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 if (lane == 0) st_ll(p.act_ll + n_items, epoch, o[0]);
             }
         }
-        DBGW(6);
         // Tell the others that this CTA's outputs are on their way.  Not ordered against the
         // stores above (no fence): readers use it only to decide when to start reading.
         __syncthreads();
@@ -1081,7 +1061,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             cp_commit();  // keep the group count per layer fixed
         }
         PROF3(5);
-        DBG(0);
 
         // ── gather every CTA's SwiGLU outputs: re-read until all tags are current ──
         {
@@ -1140,7 +1119,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 }
             }
             __syncwarp();
-            DBGW(7);
 #pragma unroll
             for (int t = 0; t < kLLGroups; ++t) {
                 const int i = gidx[t];
@@ -1162,7 +1140,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             }
             // sigmoid (reference src/math_util.rs:67-69) of the shared gate score
             if (sg_reader) sm->topw[K] = 1.0f / (1.0f + expf(-__uint_as_float((unsigned int)qs)));
-            DBG(1);
             PROF3(6);
             cp_wait<1>();  // this warp's down rows landed (the next router's slice may still be in flight)
             wpar ^= 1u;
@@ -1173,7 +1150,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
             }
         }
         PROF3(7);
-        DBG(5);
         {
             const int sub = lane >> 4, c = lane & 15;
             constexpr int kMats = (kMaxK + 2) / 2;
@@ -1213,9 +1189,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_fused_kernel(Decode3Par
                 push_partial_logits(sm, sm->tab[rel + 1].router_bf16 != nullptr, acc_nxt, nc, E, inv_rms, tid);
                 pscale = inv_rms;
                 PROF3(9);
-                DBG(2);
                 announce();
-                DBG(3);
                 PROF3(10);
             }
         }
@@ -1588,9 +1562,3 @@ extern "C" int moe_layer_decode_noalloc_status(int device, void* cuda_stream, un
     }
     return MOE_OK;
 }
-
-#ifdef MOE_DEC_SKEW
-extern "C" int moe_debug_read(long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, moe::g_dbg, (size_t)n * sizeof(long long));
-}
-#endif

@@ -8,6 +8,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <chrono>
 
 #include "common.cuh"
 
@@ -192,6 +193,20 @@ static void tel_add(moe_engine* e, const char* key, double v) {
     if (g_record_telemetry.load(std::memory_order_relaxed)) e->telemetry[key] += v;
 }
 
+// The reference's per-phase keys (src/engine/qwen35_moe/fused_exp5.rs:162-177, 249, 378, 401, 412), as they map onto
+// one call here: the host time spent enqueueing the stack (the reference's command-buffer encoding of the MoE half),
+// the host time spent waiting for the stream (its wait for the hidden state), and the device time of final norm +
+// lm_head.  The CPU routing and expert-read costs the reference also reports do not exist on this path: 0.
+using host_time_t = std::chrono::steady_clock::time_point;
+static void tel_phases(moe_engine_t* e, host_time_t t0, host_time_t t1, host_time_t t2, double lm_head_ms) {
+    tel_add(e, "phase.op2_encode_ms", std::chrono::duration<double, std::milli>(t1 - t0).count());
+    tel_add(e, "phase.hidden_wait_ms", std::chrono::duration<double, std::milli>(t2 - t1).count());
+    tel_add(e, "phase.lm_head_ms", lm_head_ms);
+    tel_add(e, "phase.route_cpu_ms", 0.0);
+    tel_add(e, "engine.expert_io_ms", 0.0);
+    tel_add(e, "engine.routing_cpu_ms", 0.0);
+}
+
 }  // namespace moe
 
 using namespace moe;
@@ -246,7 +261,7 @@ int moe_engine_create(const moe_dims_t* dims, int device, moe_engine_t** out) {
     int rc = MOE_OK;
     do {
         if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
-            cudaEventCreate(&e->ev0) != cudaSuccess || cudaEventCreate(&e->ev1) != cudaSuccess ||
+            cudaEventCreate(&e->ev0) != cudaSuccess || cudaEventCreate(&e->ev1) != cudaSuccess || cudaEventCreate(&e->ev2) != cudaSuccess ||
             cudaMalloc(&e->layers_dev, e->layers.size() * sizeof(LayerDev)) != cudaSuccess) {
             rc = cuda_fail(cudaGetLastError(), "engine resources", __FILE__, __LINE__);
             break;
@@ -279,6 +294,7 @@ void moe_engine_destroy(moe_engine_t* e) {
     if (e->io_dev) cudaFree(e->io_dev);
     if (e->ev0) cudaEventDestroy(e->ev0);
     if (e->ev1) cudaEventDestroy(e->ev1);
+    if (e->ev2) cudaEventDestroy(e->ev2);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -673,6 +689,7 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
     float* d_in = (float*)e->io_dev;
     float* d_out = (float*)(e->io_dev + align_up(hb, 256));
     do {
+        const auto host_t0 = std::chrono::steady_clock::now();
         if (rec) cudaEventRecord(t0, e->stream);
         cudaError_t ce = cudaMemcpyAsync(d_in, emb, hb, cudaMemcpyHostToDevice, e->stream);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward_hidden upload", __FILE__, __LINE__); break; }
@@ -680,7 +697,9 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
         if (rc) break;
         ce = cudaMemcpyAsync(out, d_out, hb, cudaMemcpyDeviceToHost, e->stream);
         if (rec && ce == cudaSuccess) ce = cudaEventRecord(t1, e->stream);
+        const auto host_t1 = std::chrono::steady_clock::now();
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+        const auto host_t2 = std::chrono::steady_clock::now();
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward_hidden download", __FILE__, __LINE__); break; }
         rc = poll_device_error(e);
         if (rc) break;
@@ -690,10 +709,7 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
             cudaEventElapsedTime(&ms, t0, t1);
             tel_add(e, "engine.total_ms", ms);
             tel_add(e, "engine.tokens", n);
-            // keys the reference fills with CPU-side costs that no longer exist here
-            tel_add(e, "engine.expert_io_ms", 0.0);
-            tel_add(e, "engine.routing_cpu_ms", 0.0);
-            tel_add(e, "phase.route_cpu_ms", 0.0);
+            tel_phases(e, host_t0, host_t1, host_t2, 0.0);
         }
     } while (0);
     if (rc == MOE_ERR_INTERRUPTED) cudaStreamSynchronize(e->stream);
@@ -773,6 +789,7 @@ int moe_forward_host(moe_engine_t* e, const int64_t* ids, int32_t n, int batched
     float* d_out = (float*)(e->io_dev + hb);
     float* d_l = (float*)(e->io_dev + 2 * hb);
     do {
+        const auto host_t0 = std::chrono::steady_clock::now();
         if (rec) cudaEventRecord(e->ev0, e->stream);
         cudaError_t ce = cudaMemcpyAsync(e->head.ids, ids, (size_t)n * 8, cudaMemcpyHostToDevice, e->stream);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward upload", __FILE__, __LINE__); break; }
@@ -780,25 +797,27 @@ int moe_forward_host(moe_engine_t* e, const int64_t* ids, int32_t n, int batched
         if (rc) break;
         rc = run_stack_checked(e, d_in, n, batched, check, check_ctx, d_out);
         if (rc) break;
+        if (rec) cudaEventRecord(e->ev2, e->stream);
         rc = launch_logits(e, d_out, n, d_l);
         if (rc) break;
+        if (rec) cudaEventRecord(e->ev1, e->stream);
         ce = cudaMemcpyAsync(logits, d_l, lb, cudaMemcpyDeviceToHost, e->stream);
         if (ce == cudaSuccess)
             ce = cudaMemcpyAsync(e->stage_host, d_out + (size_t)(n - 1) * d.hidden, (size_t)d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
-        if (rec && ce == cudaSuccess) ce = cudaEventRecord(e->ev1, e->stream);
+        const auto host_t1 = std::chrono::steady_clock::now();
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+        const auto host_t2 = std::chrono::steady_clock::now();
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward download", __FILE__, __LINE__); break; }
         rc = poll_device_error(e);
         if (rc) break;
         memcpy(e->last_h.data(), e->stage_host, (size_t)d.hidden * 4);
         if (rec) {
-            float ms = 0.0f;
+            float ms = 0.0f, head_ms = 0.0f;
             cudaEventElapsedTime(&ms, e->ev0, e->ev1);
+            cudaEventElapsedTime(&head_ms, e->ev2, e->ev1);
             tel_add(e, "engine.total_ms", ms);
             tel_add(e, "engine.tokens", n);
-            tel_add(e, "engine.expert_io_ms", 0.0);
-            tel_add(e, "engine.routing_cpu_ms", 0.0);
-            tel_add(e, "phase.route_cpu_ms", 0.0);
+            tel_phases(e, host_t0, host_t1, host_t2, head_ms);
         }
     } while (0);
     if (rc == MOE_ERR_INTERRUPTED) cudaStreamSynchronize(e->stream);

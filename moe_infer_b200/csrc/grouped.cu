@@ -45,14 +45,8 @@ constexpr int kNT = 256;   // tokens per tile (MMA N, padded to a multiple of 16
 constexpr int kProdWarps = 16;                  // operand producers / epilogue
 constexpr int kProdThreads = kProdWarps * 32;
 constexpr int kGemmThreads = kProdThreads + 32;  // + one MMA-issuing warp
-#ifndef MOE_AST
-#define MOE_AST 2
-#endif
-#ifndef MOE_BST
-#define MOE_BST 4
-#endif
-constexpr int kAStages = MOE_AST;   // dequantised weight tiles (produced locally: shallow ring)
-constexpr int kBStages = MOE_BST;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
+constexpr int kAStages = 2;   // dequantised weight tiles (produced locally: shallow ring)
+constexpr int kBStages = 4;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
 constexpr int kFullRing = 4;  // "operands in place" barriers (producers run at most kAStages steps ahead of the MMAs)
 constexpr int kMaxEPerLane = 16;
 
@@ -599,16 +593,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-#ifdef MOE_GEMM_PROF
-__device__ long long g_gprof[2][256][8];
-#define GP_DECL long long gp_t = clock64(), gp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long gp_t0 = gp_t
-#define GP(k) do { const long long n_ = clock64(); gp_acc[k] += n_ - gp_t; gp_t = n_; } while (0)
-#define GP_FLUSH(role) do { if (lane == 0) { gp_acc[7] = clock64() - gp_t0; for (int i_ = 0; i_ < 8; ++i_) g_gprof[role][blockIdx.x][i_] = gp_acc[i_]; } } while (0)
-#else
-#define GP_DECL
-#define GP(k) do { } while (0)
-#define GP_FLUSH(role) do { } while (0)
-#endif
 
 // Warp roles: warps 0..15 produce the operand tiles (dequantised weights, copied
 // activations) and run the epilogue; warp 16 only issues the MMAs, because a
@@ -667,7 +651,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
 
     if (warp == kProdWarps) {
         // ─── MMA issuer ───────────────────────────────────────────────────────
-        GP_DECL;
         for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
             const int tile = item / kRB;
             const int nt = p.tile_list[3 * tile + 2];
@@ -679,7 +662,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                 if (kc == 0 && n_done > 0) ok = wait_or_abort(&bar_tfree, (n_done - 1) & 1, s_abort) && ok;
                 alive = __all_sync(0xffffffffu, ok);
                 if (!alive) break;
-                GP(0);
                 if (lane == 0) {
                     umma::fence_after_sync();
                     const uint32_t a_addr = stages_addr + sa * kABytes, b_addr = b_ring_addr + sb * kBBytes;
@@ -695,14 +677,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                     if (kc == kKC - 1) umma::commit(&bar_acc);
                 }
                 __syncwarp();
-                GP(1);
             }
             ++n_done;
         }
-        GP_FLUSH(0);
     } else {
         // ─── producers + epilogue ─────────────────────────────────────────────
-        GP_DECL;
         for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
             const int tile = item / kRB, rb = item - tile * kRB;
             const int e = p.tile_list[3 * tile], s0 = p.tile_list[3 * tile + 1], nt = p.tile_list[3 * tile + 2];
@@ -763,7 +742,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             };
 
             bool ok = true;
-            GP(0);
             {   // prologue: weights of the first kWRing K steps, activations of the first kLook K steps
 #pragma unroll
                 for (int i = 0; i < kWRing; ++i) load_a(i, wq[i], sq[i], bq[i]);
@@ -777,14 +755,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             }
             auto k_step = [&](int kc, uint4& w, uint16_t& sc, uint16_t& bi) {
                 const uint32_t sa = it % kAStages;
-                GP(1);
                 // dequantise this K step's 64 columns of this thread's row half, once the MMAs that read
                 // this weight stage kAStages K steps ago are done
                 {
                     const uint32_t use = it / kAStages;
                     if (use > 0) ok = wait_or_abort(&bar_empty_a[sa], (use - 1) & 1, s_abort) && ok;
                 }
-                GP(2);
                 unsigned char* a_tile = stages + sa * kABytes;
                 const uint32_t s32 = (uint32_t)sc | ((uint32_t)sc << 16);
                 const uint32_t b32 = (uint32_t)bi | ((uint32_t)bi << 16);
@@ -795,9 +771,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                 for (int wi = 0; wi < 4; ++wi)
                     *reinterpret_cast<uint4*>(a_tile + aoff[wi]) = dequant_word(words[wi], s2, b2);
                 if (kc + kWRing < kKC) load_a(kc + kWRing, w, sc, bi);  // refill this register set
-                GP(3);
                 cp_wait_group<kLook - 1>();  // this K step's activation pieces have landed (later ones may be in flight)
-                GP(4);
                 umma::fence_smem_to_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_full[it % kFullRing]);
@@ -810,7 +784,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
                     issue_b(kc + kLook, sb);
                 }
                 cp_commit_group();
-                GP(5);
                 ++it;
             };
             for (int kc = 0; kc < kKC; kc += kWRing) {
@@ -861,10 +834,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(GemmParam
             umma::fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_tfree);  // this warp has read its part of the accumulators
-            GP(6);
         }
         cp_wait_group<0>();
-        if (warp == 0) GP_FLUSH(1);
     }
 
     if (!alive && lane == 0) atomicExch(p.err, 7u);
@@ -1368,43 +1339,24 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     for (int i = 0; i < P; ++i) peers.base[i] = ep.peer[i];
     const int32_t* counts_all = reinterpret_cast<const int32_t*>(ep.local + ep.sym.counts);
 
-    // optional timeline of one layer (environment variable MOE_EP_TRACE = layer index): an event after every
-    // launch, printed by rank 0 once the layer has finished
-    static const int trace_layer = getenv("MOE_EP_TRACE") ? atoi(getenv("MOE_EP_TRACE")) : -1;
-    const bool tracing = (layer == trace_layer);
-    std::vector<std::pair<const char*, cudaEvent_t>> marks;
-    auto ep_mark = [&](const char* name) {
-        if (!tracing) return;
-        cudaEvent_t ev;
-        cudaEventCreate(&ev);
-        cudaEventRecord(ev, st);
-        marks.emplace_back(name, ev);
-    };
-#define EP_MARK(name) ep_mark(name)
-    EP_MARK("start");
     batch_prep_kernel<<<n, 256, 0, st>>>(h_in, n, ly, bw.x, bw.x_mid, bw.x_lo, bw.sgate, bw.counts, E + 1);
-    EP_MARK("batch_prep_kernel");
     const int rsplit = router_split(n, E, ly.router_nplanes);
     MOE_REQUIRE((int64_t)rsplit * n <= bw.logit_rows, "router partial sums (%d x %d rows) exceed the logits work area (%lld rows)",
                 rsplit, n, (long long)bw.logit_rows);
     router_gemm_kernel<<<dim3((n + kRtTok - 1) / kRtTok, ly.router_nplanes == 1 ? (E + 255) / 256 : (E + 127) / 128, rsplit), 256, kRtSmem, st>>>(
         *reinterpret_cast<const CUtensorMap*>(e->layers[layer].planes_map), *reinterpret_cast<const CUtensorMap*>(bw.x_map), n, E,
         ly.router_nplanes, (E + 127) / 128 * 128, bw.capacity, bw.logits, err);
-    EP_MARK("router_gemm_kernel");
     // 1. histogram exchange: the last block of the route kernel pushes it and publishes the epoch; the plan waits for everybody's
     EpPush push{};
     push.peers = peers; push.counts_off = ep.sym.counts; push.flags_off = ep.sym.flags;
     push.me = me; push.world = P; push.epoch = ++ep.epoch; push.done = ep.done;
     if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push, err);
     else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, nullptr, nullptr, bw.topk_idx, bw.topk_w, bw.counts, rsplit, push, err);
-    EP_MARK("batch_route_kernel");
     ep_plan_kernel<<<1, 1024, 0, st>>>(counts_all, me, P, E, n, ep.base_send, ep.cursor, ep.tile_list, ep.n_tiles,
                                        ep.max_tiles, ep.total_recv, ep.local, ep.sym.flags, ep.epoch, err);
-    EP_MARK("ep_plan_kernel");
     // 2. dispatch (the last block of the scatter publishes the epoch)
     ep_scatter_kernel<<<(n + 7) / 8, 256, 0, st>>>(peers, ep.sym, me, P, E, K, n, bw.x, bw.topk_idx, bw.topk_w, ep.base_send,
                                                   ep.cursor, ep.total_recv, ep.lead_mask, ep.done, ++ep.epoch);
-    EP_MARK("ep_scatter_kernel");
     // 3. grouped GEMMs over the received rows (+ shared expert over the local ones); the first one waits for the rows
     GemmParams gp{};
     gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
@@ -1414,41 +1366,15 @@ int ep_layer(moe_engine* e, int layer, const float* h_in, int32_t n, float* h_ou
     gp.err = err;
     gp.ep_local = ep.local; gp.ep_flags = ep.sym.flags; gp.ep_world = P; gp.ep_epoch = ep.epoch;
     grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
-    EP_MARK("grouped_gemm_kernel<1>");
     gp.ep_world = 0;
     grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
-    EP_MARK("grouped_gemm_kernel<2>");
     // 4. return (the last block publishes the epoch), 5. combine (waits for everybody's rows)
     ep_return_kernel<<<e->sm_count * 2, 256, 0, st>>>(peers, ep.sym, me, P, ep.o, ep.total_recv, ep.done, ++ep.epoch);
-    EP_MARK("ep_return_kernel");
     ep_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, reinterpret_cast<const __nv_bfloat16*>(ep.local + ep.sym.oback),
                                          ep.o, ep.total_recv, ep.lead_mask, bw.sgate, ep.local, ep.sym.flags, P, ep.epoch, err);
-    EP_MARK("ep_combine_kernel");
-    if (tracing) {
-        cudaStreamSynchronize(st);
-        if (me == 0) {
-            fprintf(stderr, "[ep trace] layer %d, %d tokens on this rank, %d ranks\n", layer, n, P);
-            for (size_t i = 1; i < marks.size(); ++i) {
-                float ms = 0.0f;
-                cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
-                fprintf(stderr, "[ep trace] %-28s %8.1f us\n", marks[i].first, ms * 1e3f);
-            }
-            float tot = 0.0f;
-            cudaEventElapsedTime(&tot, marks.front().second, marks.back().second);
-            fprintf(stderr, "[ep trace] %-28s %8.1f us\n", "total", tot * 1e3f);
-        }
-        for (auto& m : marks) cudaEventDestroy(m.second);
-    }
-#undef EP_MARK
     e->launches += 9;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
 
 }  // namespace moe
-
-#ifdef MOE_GEMM_PROF
-extern "C" int moe_gemm_prof_read(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, moe::g_gprof, sizeof(long long) * 2 * 256 * 8);
-}
-#endif

@@ -216,3 +216,7 @@ def test_telemetry_keys(small_stack):
     eng.lib.moe_set_record_telemetry(0)
     assert tel["engine.total_ms"] > 0 and tel["engine.tokens"] >= 2
     assert "engine.expert_io_ms" in tel
+    # the reference's per-phase keys (src/engine/qwen35_moe/fused_exp5.rs:170-176, 249, 378, 401, 412)
+    for key in ("phase.op2_encode_ms", "phase.hidden_wait_ms", "phase.lm_head_ms", "phase.route_cpu_ms"):
+        assert key in tel and tel[key] >= 0.0
+    assert tel["phase.op2_encode_ms"] + tel["phase.hidden_wait_ms"] > 0.0
