@@ -5,11 +5,15 @@
 // src/quantize/qwen35_moe/common.rs:300-345).  HBM-bound: 2 B (bf16) or 4 B (f32)
 // read and 0.5625 B written per element.
 //
-// Mapping: eight consecutive lanes own one 64-column group; lane p of the eight
-// owns word p (columns p*8 .. p*8+7).  Min/max cross the eight lanes with three
-// xor-shuffles.  All f32 arithmetic uses the explicitly rounded intrinsics so the
-// compiler cannot contract a multiply-add: the reference computes
-// trunc((v - min) * (1 / scale) + 0.5) with separately rounded operations.
+// Mapping: one thread owns one 64-column group, so min, max, the two IEEE divisions
+// and the 64 quantisations need no cross-lane traffic.  A warp first copies its 32
+// consecutive groups (4 KB of bf16, 8 KB of f32) into shared memory with coalesced
+// 16-byte asynchronous copies; a pitch of one extra 16-byte unit per group makes
+// both the copy and each thread's reads of its own group bank-conflict free.  All
+// f32 arithmetic uses the explicitly rounded intrinsics so the compiler cannot
+// contract a multiply-add: the reference computes trunc((v - min) * (1 / scale) + 0.5)
+// with separately rounded operations.  bf16 sources take min and max on packed
+// pairs (exact: no rounding is involved in a comparison).
 #include "common.cuh"
 
 namespace moe {
@@ -42,122 +46,138 @@ struct PackJob {
     uint8_t* s_base[2];
     uint8_t* b_base[2];
     FastDiv div_gpr, div_unit, div_mat;  // by groups per row, rows per unit, rows per matrix (filled at launch)
+    int32_t w_aligned16;     // every word destination is 16-byte aligned (filled at launch)
 };
 
-constexpr int kPackUnroll = 4;  // groups per 8-lane team: their loads are all issued before the first use
+constexpr int kPackWarps = 8;            // warps per CTA
+constexpr int kPackGroupsPerWarp = 32;   // one group per lane
+
+template <bool kSrcBf16>
+constexpr int pack_smem_bytes() { return kPackWarps * kPackGroupsPerWarp * ((kSrcBf16 ? 8 : 16) + 1) * 16; }
+
+__device__ __forceinline__ void pack_cp16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// trunc((v - min) * inv + 0.5) as the reference rounds it, clamped to a nibble.  Rust's `as i32` truncates,
+// saturates and maps NaN to 0, then clamp(0, 15): the unsigned conversion already sends everything below zero
+// (and NaN) to 0, so one minimum remains.
+__device__ __forceinline__ uint32_t pack_quant(float v, float fbias, float inv_scale) {
+    const float t = __fadd_rn(__fmul_rn(__fsub_rn(v, fbias), inv_scale), 0.5f);
+    return min(__float2uint_rz(t), 15u);
+}
 
 template <bool kSrcBf16>
 __global__ void __launch_bounds__(256) pack_int4_kernel(PackJob job) {
+    constexpr int kUnits = kSrcBf16 ? 8 : 16;  // 16-byte units per group
+    constexpr int kPitch = kUnits + 1;
+    extern __shared__ uint4 pack_stage[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint4* stage = pack_stage + warp * (kPackGroupsPerWarp * kPitch);
     // 32-bit index arithmetic: the host splits jobs so that a launch covers fewer than 2^31 groups
     const uint32_t groups_per_row = (uint32_t)(job.cols / kGroup);
     const uint32_t total_groups = (uint32_t)job.n_rows * groups_per_row;
-    // a team of 8 lanes takes kPackUnroll consecutive groups: gi0 .. gi0 + kPackUnroll - 1
-    const uint32_t team = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-    const uint32_t gi0 = team * kPackUnroll;
-    const int p = threadIdx.x & 7;
-    // Lanes of one team are 8-aligned inside the warp and take the same branches,
-    // so the shuffle mask names just this team's lanes.
-    const unsigned gmask = 0xFFu << (threadIdx.x & 24);
-
-    uint4 raw[kPackUnroll][kSrcBf16 ? 1 : 2];
+    const uint32_t g_first = (blockIdx.x * kPackWarps + warp) * kPackGroupsPerWarp;
+    if (g_first >= total_groups) return;
+    const uint32_t n_here = min((uint32_t)kPackGroupsPerWarp, total_groups - g_first);
+    {
+        // source rows are contiguous, so group gi starts at element gi * 64: the warp's groups are one byte range
+        const uint4* src = reinterpret_cast<const uint4*>(job.src) + (size_t)g_first * kUnits;
+        const uint32_t n_units = n_here * kUnits;
 #pragma unroll
-    for (int u = 0; u < kPackUnroll; ++u) {
-        const uint32_t gi = gi0 + u;
-        if (gi < total_groups) {
-            // source rows are contiguous, so group gi starts at element gi * 64
-            if (kSrcBf16) {
-                raw[u][0] = ld_stream_u4(reinterpret_cast<const uint16_t*>(job.src) + (size_t)gi * kGroup + p * 8);
-            } else {
-                const float* sp = reinterpret_cast<const float*>(job.src) + (size_t)gi * kGroup + p * 8;
-                raw[u][0] = ld_stream_u4(sp);
-                raw[u][kSrcBf16 ? 0 : 1] = ld_stream_u4(sp + 4);
-            }
+        for (int i = 0; i < kUnits; ++i) {
+            const uint32_t c = i * 32 + lane;
+            if (c < n_units) pack_cp16(smem_u32(stage + c + c / kUnits), src + c);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
     }
-    // pass 1: widen, and reduce min / max over each group (8 lanes, three xor-shuffles)
-    float v[kPackUnroll][8], gmin[kPackUnroll], gmax[kPackUnroll];
+    if ((uint32_t)lane >= n_here) return;
+    const uint32_t gi = g_first + lane;
+    uint4 raw[kUnits];
 #pragma unroll
-    for (int u = 0; u < kPackUnroll; ++u) {
-        if (kSrcBf16) {
-            const uint32_t r[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+    for (int k = 0; k < kUnits; ++k) raw[k] = stage[lane * kPitch + k];
+
+    float gmin, gmax;
+    if (kSrcBf16) {
+        __nv_bfloat162 mn = *reinterpret_cast<const __nv_bfloat162*>(&raw[0].x), mx = mn;
+#pragma unroll
+        for (int k = 0; k < kUnits; ++k) {
+            const uint32_t r[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                v[u][2 * i] = __uint_as_float(r[i] << 16);            // bf16 -> f32 is exact
-                v[u][2 * i + 1] = __uint_as_float(r[i] & 0xFFFF0000u);
+                const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(&r[i]);
+                mn = __hmin2(mn, w);
+                mx = __hmax2(mx, w);
+            }
+        }
+        const uint32_t mnb = *reinterpret_cast<const uint32_t*>(&mn), mxb = *reinterpret_cast<const uint32_t*>(&mx);
+        gmin = fminf(__uint_as_float(mnb << 16), __uint_as_float(mnb & 0xFFFF0000u));  // bf16 -> f32 is exact
+        gmax = fmaxf(__uint_as_float(mxb << 16), __uint_as_float(mxb & 0xFFFF0000u));
+    } else {
+        gmin = gmax = __uint_as_float(raw[0].x);
+#pragma unroll
+        for (int k = 0; k < kUnits; ++k) {
+            const float f[4] = {__uint_as_float(raw[k].x), __uint_as_float(raw[k].y), __uint_as_float(raw[k].z), __uint_as_float(raw[k].w)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                gmin = fminf(gmin, f[i]);
+                gmax = fmaxf(gmax, f[i]);
+            }
+        }
+    }
+    if (gmax == gmin) gmax = __fadd_rn(gmin, 1.0f);
+    const float fscale = __fdiv_rn(__fsub_rn(gmax, gmin), 15.0f);
+    const float inv_scale = __fdiv_rn(1.0f, fscale);
+    const float fbias = gmin;
+
+    uint32_t words[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        uint32_t word = 0;
+        if (kSrcBf16) {
+            const uint32_t r[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // multiply-add nibble insert (the nibbles do not overlap): one instruction, off the ALU pipe
+                word = pack_quant(__uint_as_float(r[i] << 16), fbias, inv_scale) * (1u << (8 * i)) + word;
+                word = pack_quant(__uint_as_float(r[i] & 0xFFFF0000u), fbias, inv_scale) * (1u << (8 * i + 4)) + word;
             }
         } else {
-            const uint4 a = raw[u][0], b = raw[u][kSrcBf16 ? 0 : 1];
-            v[u][0] = __uint_as_float(a.x); v[u][1] = __uint_as_float(a.y); v[u][2] = __uint_as_float(a.z); v[u][3] = __uint_as_float(a.w);
-            v[u][4] = __uint_as_float(b.x); v[u][5] = __uint_as_float(b.y); v[u][6] = __uint_as_float(b.z); v[u][7] = __uint_as_float(b.w);
-        }
-        float vmin = v[u][0], vmax = v[u][0];
+            const uint4 a = raw[kSrcBf16 ? 0 : 2 * k], b = raw[kSrcBf16 ? 0 : 2 * k + 1];
+            const float f[8] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w),
+                                __uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w)};
 #pragma unroll
-        for (int i = 1; i < 8; ++i) {
-            vmin = fminf(vmin, v[u][i]);
-            vmax = fmaxf(vmax, v[u][i]);
+            for (int n = 0; n < 8; ++n) word = pack_quant(f[n], fbias, inv_scale) * (1u << (4 * n)) + word;
         }
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            vmin = fminf(vmin, __shfl_xor_sync(gmask, vmin, o));
-            vmax = fmaxf(vmax, __shfl_xor_sync(gmask, vmax, o));
-        }
-        gmin[u] = vmin;
-        gmax[u] = vmax;
+        words[k] = word;
     }
-    // pass 2: the two IEEE divisions of a group are done once, by lane u of its team (lane u takes group u),
-    // and handed to the other seven lanes by shuffle: a division costs a dozen instructions
-    static_assert(kPackUnroll <= 8, "one lane of the team per unrolled group");
-    float my_min = gmin[0], my_max = gmax[0];
+
+    // where this group goes: (row, group in row) -> (unit, matrix, row in matrix)
+    const uint32_t row = fdiv(gi, job.div_gpr);
+    const uint32_t g = gi - row * groups_per_row;
+    const uint32_t unit = fdiv(row, job.div_unit);
+    const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
+    const uint32_t m = fdiv(rr, job.div_mat);
+    const uint32_t r = rr - m * (uint32_t)job.rows_per_mat;
+    const int64_t uoff = (int64_t)unit * job.unit_stride;
+    // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
+    uint8_t* const wdst = (m ? job.w_base[1] : job.w_base[0]) + uoff;
+    uint8_t* const sdst = (m ? job.s_base[1] : job.s_base[0]) + uoff;
+    uint8_t* const bdst = (m ? job.b_base[1] : job.b_base[0]) + uoff;
+    const uint64_t gq = (uint64_t)r * groups_per_row + g;  // group index inside the destination matrix
+    if (job.w_aligned16) {
+        uint4* const wd = reinterpret_cast<uint4*>(wdst + gq * 32);
+        wd[0] = make_uint4(words[0], words[1], words[2], words[3]);
+        wd[1] = make_uint4(words[4], words[5], words[6], words[7]);
+    } else {
+        uint32_t* const wd = reinterpret_cast<uint32_t*>(wdst + gq * 32);
 #pragma unroll
-    for (int u = 1; u < kPackUnroll; ++u)
-        if (p == u) { my_min = gmin[u]; my_max = gmax[u]; }
-    if (my_max == my_min) my_max = __fadd_rn(my_min, 1.0f);
-    const float my_scale = __fdiv_rn(__fsub_rn(my_max, my_min), 15.0f);
-    const float my_inv = __fdiv_rn(1.0f, my_scale);
-    const int team_lane0 = threadIdx.x & 24;  // first lane of this team inside the warp
-    // pass 3: quantise and store.  (row, group in row) of the first group by division, of the others by stepping.
-    uint32_t row = fdiv(gi0, job.div_gpr);
-    uint32_t g = gi0 - row * groups_per_row;
-    // where a row's groups go: recomputed only when the row changes
-    uint8_t *wdst = nullptr, *sdst = nullptr, *bdst = nullptr;  // destination matrices of this row, at its unit
-    uint64_t gq0 = 0;                                            // index of the row's first group inside them
-    auto locate = [&]() {
-        const uint32_t unit = fdiv(row, job.div_unit);
-        const uint32_t rr = row - unit * (uint32_t)job.rows_per_unit;
-        const uint32_t m = fdiv(rr, job.div_mat);
-        const uint32_t r = rr - m * (uint32_t)job.rows_per_mat;
-        const int64_t uoff = (int64_t)unit * job.unit_stride;
-        // selects, not indexing: a dynamically indexed kernel parameter would be copied to local memory
-        wdst = (m ? job.w_base[1] : job.w_base[0]) + uoff;
-        sdst = (m ? job.s_base[1] : job.s_base[0]) + uoff;
-        bdst = (m ? job.b_base[1] : job.b_base[0]) + uoff;
-        gq0 = (uint64_t)r * groups_per_row;
-    };
-    locate();
-#pragma unroll
-    for (int u = 0; u < kPackUnroll; ++u) {
-        const float fscale = __shfl_sync(gmask, my_scale, team_lane0 + u);
-        const float inv_scale = __shfl_sync(gmask, my_inv, team_lane0 + u);
-        if (u > 0 && ++g == groups_per_row) { g = 0; ++row; locate(); }
-        const uint32_t gi = gi0 + u;
-        if (gi >= total_groups) continue;
-        const float fbias = gmin[u];
-        uint32_t word = 0;
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const float t = __fadd_rn(__fmul_rn(__fsub_rn(v[u][n], fbias), inv_scale), 0.5f);
-            // Rust `as i32` truncates, saturates and maps NaN to 0, then clamp(0, 15): the unsigned conversion
-            // already sends everything below zero (and NaN) to 0, so one minimum remains
-            const uint32_t q = min(__float2uint_rz(t), 15u);
-            word = q * (1u << (n * 4)) + word;  // multiply-add (the nibbles do not overlap): one instruction, off the ALU pipe
-        }
-        const uint64_t gq = gq0 + g;  // group index inside the destination matrix
-        reinterpret_cast<uint32_t*>(wdst)[gq * 8 + p] = word;
-        // lane 0 writes the scale, lane 1 the bias: one conversion and one store per lane
-        const float sv = p == 0 ? fscale : fbias;
-        uint8_t* const dst = p == 0 ? sdst : bdst;
-        if (p < 2) reinterpret_cast<uint16_t*>(dst)[gq] = f32_to_bf16_ref(sv);
+        for (int k = 0; k < 8; ++k) wd[k] = words[k];
     }
+    reinterpret_cast<uint16_t*>(sdst)[gq] = f32_to_bf16_ref(fscale);
+    reinterpret_cast<uint16_t*>(bdst)[gq] = f32_to_bf16_ref(fbias);
 }
 
 static int run_pack_one(moe_engine* e, const PackJob& job, int src_dtype);
@@ -211,13 +231,18 @@ static int run_pack_one(moe_engine* e, const PackJob& job_in, int src_dtype) {
     job.div_gpr = make_fastdiv((uint32_t)(job.cols / kGroup));
     job.div_unit = make_fastdiv((uint32_t)job.rows_per_unit);
     job.div_mat = make_fastdiv((uint32_t)job.rows_per_mat);
-    const int64_t threads = (total_groups + kPackUnroll - 1) / kPackUnroll * 8;
-    const int64_t blocks = (threads + 255) / 256;
+    MOE_REQUIRE(((uintptr_t)job.src & 15u) == 0, "pack: the source must be 16-byte aligned");
+    job.w_aligned16 = (((uintptr_t)job.w_base[0] | (uintptr_t)job.w_base[1] | (uintptr_t)job.unit_stride) & 15u) == 0;
+    const int64_t per_block = (int64_t)kPackWarps * kPackGroupsPerWarp;
+    const int64_t blocks = (total_groups + per_block - 1) / per_block;
     MOE_REQUIRE(blocks < (1ll << 31), "pack: too many rows for one launch (%lld blocks)", (long long)blocks);
-    if (src_dtype == MOE_DT_BF16)
-        pack_int4_kernel<true><<<(unsigned)blocks, 256, 0, e->stream>>>(job);
-    else
-        pack_int4_kernel<false><<<(unsigned)blocks, 256, 0, e->stream>>>(job);
+    if (src_dtype == MOE_DT_BF16) {
+        pack_int4_kernel<true><<<(unsigned)blocks, 256, pack_smem_bytes<true>(), e->stream>>>(job);
+    } else {
+        // above the default 48 KB of dynamic shared memory
+        MOE_CUDA(cudaFuncSetAttribute(pack_int4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, pack_smem_bytes<false>()));
+        pack_int4_kernel<false><<<(unsigned)blocks, 256, pack_smem_bytes<false>(), e->stream>>>(job);
+    }
     e->launches++;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
