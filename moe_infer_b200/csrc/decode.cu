@@ -348,6 +348,9 @@ __device__ __forceinline__ void route_cta(SM* sm, float v, const int32_t* forced
     const float pr = ex * inv;
     static_assert(kMaxE == kDecThreads, "one thread per expert slot");
     sm->prob[tid] = (tid < E) ? pr : -1.0f;
+    // default choice (experts 0..K-1): stands only when NaN logits leave fewer than K candidates, as the
+    // reference's heap keeps its first K entries then (src/math_util.rs:89-99); never an undefined index
+    if (tid < K) { sm->topi[tid] = tid; sm->topp[tid] = pr; }
     if (forced) {
         __syncthreads();
         if (tid < K) {

@@ -84,6 +84,10 @@ __device__ __forceinline__ void route_select(SM* sm, float v, const int32_t* for
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
     if (lane == 0) sm->red[warp] = m;  // per-warp maxima: kept for route_weights
     if (tid == 0) { sm->ncand = 0; sm->tau = -INFINITY; }
+    // Default choice: experts 0..K-1.  It stands only where the ranking below writes nothing, i.e. when logits are
+    // NaN (comparisons with NaN are false, so fewer than K candidates exist): the reference's heap keeps its first
+    // K entries in that case (src/math_util.rs:89-99), and an expert index must never be left undefined.
+    if (tid < K) { sm->topi[tid] = tid; sm->topp[tid] = v; }
     if (forced) sm->prob[tid] = v;
     __syncthreads();
     if (forced) {

@@ -407,8 +407,9 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
             if (lane == k) { myw = v; myi = e; }
         }
     } else {
+        uint32_t taken = 0;  // bit i: this lane's i-th expert has been chosen
         for (int k = 0; k < K; ++k) {
-            float bv = -2.0f;
+            float bv = -1.0f;  // chosen experts and lanes beyond E hold -1: never greater than this
             int be = 0x7fffffff;
 #pragma unroll
             for (int i = 0; i < NPER; ++i)
@@ -419,10 +420,23 @@ __global__ void __launch_bounds__(256) batch_route_kernel(const float* __restric
                 const int oe = __shfl_xor_sync(0xffffffffu, be, o);
                 if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
             }
+            if (be >= E) {
+                // Nothing compared greater: the remaining probabilities are NaN.  Take the lowest expert not
+                // chosen yet (all-NaN logits give experts 0..K-1, as the reference's heap does,
+                // src/math_util.rs:89-99); an index outside [0, E) must never reach the histogram.
+                int lo = 0x7fffffff;
+#pragma unroll
+                for (int i = NPER - 1; i >= 0; --i)
+                    if (lane + 32 * i < E && !((taken >> i) & 1u)) lo = lane + 32 * i;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+                be = lo;  // K <= E, so one exists
+                bv = NAN;
+            }
             if (lane == k) { myw = bv; myi = be; }
 #pragma unroll
             for (int i = 0; i < NPER; ++i)
-                if (lane + 32 * i == be) p[i] = -1.0f;
+                if (lane + 32 * i == be) { p[i] = -1.0f; taken |= 1u << i; }
         }
     }
     const float ws = warp_sum(lane < K ? myw : 0.0f);

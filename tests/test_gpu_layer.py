@@ -220,3 +220,30 @@ def test_telemetry_keys(small_stack):
     for key in ("phase.op2_encode_ms", "phase.hidden_wait_ms", "phase.lm_head_ms", "phase.route_cpu_ms"):
         assert key in tel and tel[key] >= 0.0
     assert tel["phase.op2_encode_ms"] + tel["phase.hidden_wait_ms"] > 0.0
+
+
+def test_nan_hidden_state_selects_valid_experts(full_layer):
+    """A NaN hidden state must never turn into an expert index outside [0, E).
+
+    With NaN logits every comparison is false; the reference's heap then keeps its first K entries
+    (src/math_util.rs:89-99: experts 0..K-1, NaN weights) and the output is NaN.  Here: the same expert set, an
+    output that still carries NaN, no error, and the other tokens of the batch are untouched.
+    """
+    eng, lw = full_layer
+    h = synth.hidden_states(12, 2, 6, 2048)
+    clean, idx_clean, _ = eng.layer_forward(0, h)
+    bad = h.copy()
+    bad[2, 100] = np.nan
+    # batched path: token 2 is NaN, the others must come out exactly as before
+    out, idx, wts = eng.layer_forward(0, bad)
+    assert idx.min() >= 0 and idx.max() < 256
+    assert np.array_equal(np.sort(idx[2]), np.arange(8))
+    assert np.isnan(out[2]).any()  # the caller can see that this token is invalid
+    keep = [0, 1, 3, 4, 5]
+    assert np.array_equal(out[keep], clean[keep]) and np.array_equal(idx[keep], idx_clean[keep])
+    # decode path, one token
+    out1, idx1, _ = eng.layer_forward(0, bad[2])
+    assert np.array_equal(np.sort(idx1[0]), np.arange(8)) and np.isnan(out1).any()
+    # the engine is still usable and still right
+    again, idx_again, _ = eng.layer_forward(0, h[0])
+    assert np.array_equal(again[0], eng.layer_forward(0, h[0])[0][0]) and np.isfinite(again).all()
