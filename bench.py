@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=None, help="untimed steps (default 20; 3 for --impl reference)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode",
-                    choices=["decode", "layer", "pack", "matvec", "matvec_hbm", "batched64", "prefill"])
+                    choices=["decode", "layer", "pack", "matvec", "matvec_hbm", "lm_head", "batched64", "prefill"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--tokens", type=int, default=0, help="tokens per step for the batched workloads")
     ap.add_argument("--seed", type=int, default=0)
@@ -311,6 +311,9 @@ def run_single(args, rank, world, local, dist):
     elif name == "pack":
         r = workloads.run_pack(args, rank, world, local, dist)
         metric, unit, value, ms = "quantize_GB_per_s", "GB/s", r["GB_per_s"], r["ms_per_checkpoint"]
+    elif name == "lm_head":
+        r = workloads.run_lm_head(args, local, "int8")
+        metric, unit, value, ms = "lm_head_GB_per_s", "GB/s", r["roofline"]["achieved"], r["us_per_call"] / 1e3
     else:
         small = name in ("matvec", "matvec_hbm")
         dims = Dims(num_layers=1, num_experts=4, top_k=4) if small else Dims(num_layers=min(args.layers, 12))

@@ -121,7 +121,9 @@ int moe_store_bytes(const moe_engine_t* e, size_t* resident_bytes);
 /* ── packer ──────────────────────────────────────────────────────────────────
  * quant_f32_to_int4 (src/dtype.rs:102-135) with the reference's bf16 rounding
  * (src/dtype.rs:85-89); bit-exact.  src is f32 or bf16 [rows, cols]; cols % 64
- * == 0.  Device pointers. */
+ * == 0.  Device pointers; src must be 16-byte aligned (MOE_ERR_INVALID otherwise),
+ * the outputs need only their element alignment (word stores are 16 bytes wide
+ * when the destination allows it). */
 int moe_pack_int4_dev(moe_engine_t* e, const void* src_dev, int src_dtype, int64_t rows, int32_t cols,
                       void* w_dev, void* s_dev, void* b_dev);
 /* Same through host buffers (copies in, packs on the GPU, copies out). */

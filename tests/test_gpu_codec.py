@@ -53,6 +53,31 @@ def test_packer_wide_dynamic_range_bit_exact(eng):
     assert _same(eng.pack_int4(v), oracle.quant_int4(v))
 
 
+def test_packer_device_pointers_any_word_alignment(eng):
+    """Device entry point: a destination that is only 4-byte aligned takes the narrow stores; a source that is
+    not 16-byte aligned is refused before any device work."""
+    from moe_infer_b200 import _lib
+    rng = np.random.default_rng(13)
+    rows, cols = 70, 192  # 210 groups: six full warps of 32 groups and a ragged one
+    v = synth.normal_weights(rng, (rows, cols), outlier_frac=0.001)
+    want = oracle.quant_int4(v)
+    d_src = eng.alloc(v.nbytes + 16).upload(v)
+    d_w = eng.alloc(rows * cols // 2 + 16)
+    d_s = eng.alloc(rows * cols // 64 * 2 + 16)
+    d_b = eng.alloc(rows * cols // 64 * 2 + 16)
+    for off in (0, 4):
+        eng.pack_int4_dev(d_src.ptr, _lib.DT_F32, rows, cols, d_w.ptr + off, d_s.ptr + 2, d_b.ptr + 2)
+        eng.sync()
+        w = d_w.download(np.uint8, (rows * cols // 2 + 16,))[off:off + rows * cols // 2].view(np.uint32).reshape(rows, cols // 8)
+        s = d_s.download(np.uint8, (rows * cols // 64 * 2 + 16,))[2:2 + rows * cols // 32].view(np.uint16).reshape(rows, cols // 64)
+        b = d_b.download(np.uint8, (rows * cols // 64 * 2 + 16,))[2:2 + rows * cols // 32].view(np.uint16).reshape(rows, cols // 64)
+        assert _same((w, s, b), want), off
+    with pytest.raises(ValueError, match="16-byte aligned"):
+        eng.pack_int4_dev(d_src.ptr + 4, _lib.DT_F32, rows, cols, d_w.ptr, d_s.ptr, d_b.ptr)
+    for d in (d_src, d_w, d_s, d_b):
+        d.free()
+
+
 def test_packer_empty_and_ragged(eng):
     w, s, b = eng.pack_int4(np.zeros((0, 64), np.float32))
     assert w.shape == (0, 8) and s.shape == (0, 1)
