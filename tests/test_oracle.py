@@ -111,6 +111,48 @@ def test_packer_roundtrip_property_of_reference_test():
                 assert np.abs(a - b).max() / rng_ < 0.1
 
 
+def _np_bf16_ref(v: np.ndarray) -> np.ndarray:
+    """The reference's f32 -> bf16 rounding (src/dtype.rs:85-89), in numpy integer arithmetic."""
+    bits = v.astype(np.float32).view(np.uint32).astype(np.uint64)
+    # the reference ANDs a one-bit value with an unnormalised word: only bit 0 of (low 15 bits | bit 16) counts
+    round_up = ((bits >> 15) & 1) & ((bits & 0x7FFF) | ((bits >> 16) & 1))
+    return (((bits + (round_up << 16)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def _np_quant_int4(v: np.ndarray):
+    """quant_f32_to_int4 (src/dtype.rs:102-135) written a second time, in numpy float32 arithmetic: every
+    numpy f32 operation rounds once, like the Rust expression it stands for."""
+    v = v.astype(np.float32)
+    rows, cols = v.shape
+    g = v.reshape(rows, cols // 64, 64)
+    vmin = g.min(axis=2)
+    vmax = g.max(axis=2)
+    vmax = np.where(vmax == vmin, vmin + np.float32(1.0), vmax).astype(np.float32)
+    scale = ((vmax - vmin) / np.float32(15.0)).astype(np.float32)
+    inv = (np.float32(1.0) / scale).astype(np.float32)
+    t = ((g - vmin[..., None]).astype(np.float32) * inv[..., None]).astype(np.float32) + np.float32(0.5)
+    q = np.clip(np.trunc(t.astype(np.float32)), 0, 15).astype(np.uint32).reshape(rows, cols // 8, 8)
+    w = np.zeros((rows, cols // 8), np.uint32)
+    for n in range(8):
+        w |= q[:, :, n] << np.uint32(4 * n)
+    return w, _np_bf16_ref(scale), _np_bf16_ref(vmin)
+
+
+@pytest.mark.parametrize("seed,shape,spread", [(3, (16, 256), 0.0), (4, (7, 128), 30.0), (5, (33, 2048), 0.0)])
+def test_packer_matches_numpy_restatement(seed, shape, spread):
+    """The C packer against a second, independent statement of the same arithmetic (numpy f32), bit for bit;
+    spread > 0 scales rows over many decades."""
+    rng = np.random.default_rng(seed)
+    v = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    if spread:
+        v = (v * np.exp(rng.uniform(-spread, spread, size=(shape[0], 1)))).astype(np.float32)
+    v[0, :64] = 0.25  # a constant group
+    got = oracle.quant_int4(v)
+    want = _np_quant_int4(v)
+    for a, b in zip(got, want):
+        assert np.array_equal(a, b)
+
+
 def test_bf16_source_equals_widened_f32():
     rng = np.random.default_rng(2)
     u = oracle.f32_to_bf16((rng.standard_normal((8, 128)) * 0.02).astype(np.float32))
