@@ -297,9 +297,9 @@ def _interrupt_pending() -> bool:
 def qwen35_moe_quantize(model_path: str, output_dir: str, *, version: str, scheme: str = "bq4", device: int = 0) -> None:
     """src/python_bindings.rs:327-387: HF safetensors -> model_weights.{bin,json} + packed_experts/.
 
-    Converts the tensors of the MoE path (experts, router, shared expert, shared gate,
-    post-attention norms) with the GPU packer; attention, embedding and lm_head tensors
-    are not converted yet.
+    Converts every tensor of the checkpoint the way the reference's pipeline does (manifest names,
+    storage type per scheme, norm shift, conv1d axes, padding, config block); vision tensors are
+    skipped.  Matrices are packed on the GPU.
     """
     if version not in ("3.5", "3.6"):
         raise ValueError(f"unknown Qwen version {version!r} (expected '3.5' or '3.6')")

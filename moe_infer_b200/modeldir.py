@@ -1,4 +1,4 @@
-"""Reader and writer of the reference's on-disk model directory (MoE tensors only).
+"""Reader and writer of the reference's on-disk model directory.
 
 Layout (reference src/model.rs:26-112, src/model/weights.rs:82-179,
 src/quantize.rs:150-291, src/quantize/qwen35_moe/common.rs:314-348):
@@ -10,8 +10,8 @@ src/quantize.rs:150-291, src/quantize/qwen35_moe/common.rs:314-348):
                                      layer, MTP block = index num_hidden_layers
 
 dtype strings follow src/dtype.rs:34-43: "f32", "bf16", "u32" (= 4-bit words), "u8".
-Only the tensors of the MoE path and of the model head (embedding table, final norm, lm_head) are read;
-attention tensors are ignored.
+The engine reads only the tensors of the MoE path and of the model head (embedding table, final norm, lm_head);
+the converter writes every tensor of the checkpoint, attention included.
 """
 from __future__ import annotations
 
@@ -111,6 +111,10 @@ class ModelDirWriter:
     def add_bf16(self, name: str, bits: np.ndarray, flat: bool = False) -> None:
         # encode_bf16 writes matrices with shape [len] (reference src/dtype.rs:456-460)
         self._put(name, bits.astype(np.uint16), "bf16", [bits.size] if flat else bits.shape)
+
+    def add_f32(self, name: str, vals: np.ndarray) -> None:
+        # encode_fp32 (reference src/dtype.rs:462-465): shape [len]
+        self._put(name, vals.astype(np.float32), "f32", [vals.size])
 
     def add_q4(self, base: str, w: np.ndarray, s: np.ndarray, b: np.ndarray) -> None:
         self._put(base + ".weight", w.astype(np.uint32), "u32", w.shape)

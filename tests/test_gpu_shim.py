@@ -20,7 +20,8 @@ def _write_safetensors(path, tensors):
     hdr, blobs, off = {}, [], 0
     for name, arr in tensors.items():
         raw = np.ascontiguousarray(arr).tobytes()
-        hdr[name] = {"dtype": "BF16", "shape": list(arr.shape), "data_offsets": [off, off + len(raw)]}
+        hdr[name] = {"dtype": "F32" if arr.dtype == np.float32 else "BF16", "shape": list(arr.shape),
+                     "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
         off += len(raw)
     h = json.dumps(hdr).encode()
@@ -130,6 +131,71 @@ def test_quantize_load_forward(tmp_path, scheme):
     eng.restore_snapshot(snap)
     assert eng.pos == 16
     eng.native.close()
+
+
+@pytest.mark.parametrize("scheme", ["bq4", "int4"])
+def test_quantize_whole_checkpoint_names_types_values(tmp_path, scheme):
+    """Every tensor of a checkpoint goes through the reference's pipeline (src/quantize.rs:171-291): manifest name,
+    storage type by scheme, +1 on zero-centred norms (Qwen3.6), conv1d axes, inner-dimension padding, config block."""
+    from moe_infer_b200.modeldir import ModelDir
+    src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
+    _hf_checkpoint(src, layers=1, mtp=0)
+    rng = np.random.default_rng(5)
+    bf = lambda a: synth.to_bf16_rne(a.astype(np.float32))
+    f = lambda bits: synth.bf16_to_f32(bits)
+    p = "model.language_model.layers.0."
+    extra = {
+        p + "input_layernorm.weight": bf(rng.uniform(-0.1, 0.1, H)),
+        p + "self_attn.q_proj.weight": bf(synth.normal_weights(rng, (64, H))),
+        p + "self_attn.q_norm.weight": bf(rng.uniform(-0.1, 0.1, 256)),
+        p + "linear_attn.conv1d.weight": bf(rng.standard_normal((8, 1, 4))),
+        p + "linear_attn.A_log": rng.standard_normal(16).astype(np.float32),
+        p + "linear_attn.dt_bias": bf(rng.standard_normal(16)),
+        p + "linear_attn.norm.weight": bf(rng.uniform(0.9, 1.1, 128)),
+        p + "linear_attn.in_proj_a.weight": bf(synth.normal_weights(rng, (16, H))),
+        p + "linear_attn.out_proj.weight": bf(synth.normal_weights(rng, (32, 96))),
+        "model.visual.blocks.0.attn.qkv.weight": bf(synth.normal_weights(rng, (8, 64))),
+    }
+    _write_safetensors(os.path.join(src, "model-00002-of-00002.safetensors"), extra)
+    from moe_infer_b200.quantize import quantize_moe_checkpoint
+    summary = quantize_moe_checkpoint(src, dst, version="3.6", scheme=scheme)
+    md = ModelDir(dst)
+    L0 = "language_model.model.layers.0."
+    assert not any(k.startswith("vision_tower") or "visual" in k for k in md.tensors)
+    # zero-centred norms are stored as w + 1; the gated norm of the linear-attention block is not
+    for name, shifted in (("input_layernorm.weight", True), ("self_attn.q_norm.weight", True), ("linear_attn.norm.weight", False)):
+        want = f(extra[p + name]) + (np.float32(1.0) if shifted else np.float32(0.0))
+        info = md.tensors[L0 + name]
+        assert info["dtype"] == "bf16" and info["shape"] == [want.size]
+        assert np.array_equal(md.tensor(L0 + name), oracle.f32_to_bf16(want))
+    # conv1d [C, K, S] -> [C, S, K], bf16, flat
+    conv = md.tensor(L0 + "linear_attn.conv1d.weight")
+    assert np.array_equal(conv, np.moveaxis(extra[p + "linear_attn.conv1d.weight"], 2, 1).reshape(-1))
+    assert md.tensors[L0 + "linear_attn.A_log"]["dtype"] == "f32"
+    assert np.array_equal(md.tensor(L0 + "linear_attn.A_log"), extra[p + "linear_attn.A_log"])
+    assert np.array_equal(md.tensor(L0 + "linear_attn.dt_bias"), extra[p + "linear_attn.dt_bias"])
+    # attention projections: bf16 in BQ4 (under their full name), 4-bit triple in INT4 (".weight" stripped from the base)
+    q = f(extra[p + "self_attn.q_proj.weight"])
+    if scheme == "bq4":
+        assert md.tensors[L0 + "self_attn.q_proj.weight"]["dtype"] == "bf16"
+        assert np.array_equal(md.tensor(L0 + "self_attn.q_proj.weight"), extra[p + "self_attn.q_proj.weight"].reshape(-1))
+    else:
+        got = md.q4(L0 + "self_attn.q_proj")
+        assert md.tensors[L0 + "self_attn.q_proj.weight"]["dtype"] == "u32"
+        assert all(np.array_equal(a, b) for a, b in zip(got, oracle.quant_int4(q)))
+    got = md.q4(L0 + "linear_attn.in_proj_a")
+    assert all(np.array_equal(a, b) for a, b in zip(got, oracle.quant_int4(f(extra[p + "linear_attn.in_proj_a.weight"]))))
+    # inner dimension 96 is zero-padded to 128 before packing
+    padded = np.zeros((32, 128), np.float32)
+    padded[:, :96] = f(extra[p + "linear_attn.out_proj.weight"])
+    got = md.q4(L0 + "linear_attn.out_proj")
+    assert got[0].shape == (32, 16) and all(np.array_equal(a, b) for a, b in zip(got, oracle.quant_int4(padded)))
+    # the manifest's config block
+    cfg = json.load(open(os.path.join(dst, "model_weights.json")))["config"]
+    assert cfg["hidden_size"] == H and cfg["num_hidden_layers"] == 1 and cfg["num_experts"] == E
+    assert cfg["layer_types"] == ["linear_attention"] and cfg["full_attention_interval"] == 4
+    assert cfg["rope_theta"] == 10_000_000.0 and cfg["partial_rotary_factor"] == 0.25 and cfg["linear_conv_kernel_dim"] == 4
+    assert summary["f32"] == 1 and summary.get("int8", 0) == (1 if scheme == "bq4" else 0)
 
 
 def test_top_level_module_alias_runs_a_forward(tmp_path):
