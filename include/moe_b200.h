@@ -228,6 +228,32 @@ int moe_mtp_reset(moe_engine_t* e);
 int moe_mtp_rollback(moe_engine_t* e, int64_t pos);
 int moe_mtp_pos(const moe_engine_t* e, int64_t* pos);
 
+/* ── MTP block, whole step ───────────────────────────────────────────────────
+ * mtp_step (src/engine/qwen35_moe/mtp.rs:58-225): (hidden state before the final norm, previous token) -> logits.
+ * embed the token; RMS-norm it and the hidden state with their own weights; concatenate (embedding first) and
+ * project with mtp.fc; one gated full-attention block (input norm; q/k/v projections, q carrying the output gate
+ * in its second half; per-head q/k RMS norm; interleaved RoPE on the first rotary_dim elements of every head; f32
+ * KV cache of the block's own; softmax attention; sigmoid gate; o projection; residual); the MoE half (layer index
+ * num_layers of the store: post-attention norm, router, experts, shared expert, residual); mtp.norm (or the model's
+ * final norm when mtp.norm was not loaded); lm_head.  The position is the one moe_mtp_reset / moe_mtp_rollback
+ * manage.  Norm weights are bf16; a projection is MOE_DT_BF16 ([out, in], BQ4 scheme, bq4.rs:25-32) or MOE_DT_INT4
+ * (triple); mtp.fc is always MOE_DT_INT4 [hidden, 2 * hidden].  Host pointers.
+ * moe_mtp_configure allocates the KV cache (max_seq positions; the reference's MAX_SEQ = 4096 is src/constants.rs:12)
+ * and must come before the tensors.  MOE_ERR_STATE when the block has no MTP layer, a tensor is missing or the
+ * cache is full. */
+typedef struct {
+    int32_t num_heads, num_kv_heads, head_dim, rotary_dim, max_seq;
+    float rope_theta;
+} moe_attn_dims_t;
+typedef enum {
+    MOE_M_PRE_FC_NORM_HIDDEN = 0, MOE_M_PRE_FC_NORM_EMBEDDING = 1, MOE_M_FC = 2, MOE_M_INPUT_NORM = 3,
+    MOE_M_Q_PROJ = 4, MOE_M_K_PROJ = 5, MOE_M_V_PROJ = 6, MOE_M_Q_NORM = 7, MOE_M_K_NORM = 8, MOE_M_O_PROJ = 9,
+    MOE_M_OUT_NORM = 10
+} moe_mtp_tensor_t;
+int moe_mtp_configure(moe_engine_t* e, const moe_attn_dims_t* attn);
+int moe_mtp_load_tensor(moe_engine_t* e, int which, const void* w_host, const void* s_host, const void* b_host, int dtype);
+int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, float* logits_host);
+
 /* ── telemetry ───────────────────────────────────────────────────────────────
  * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys
  * follow the reference (`engine.total_ms`, `phase.route_cpu_ms`, ...).  Fills up

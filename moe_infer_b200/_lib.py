@@ -20,6 +20,8 @@ ERR_INVALID, ERR_CUDA, ERR_STATE, ERR_INTERRUPTED, ERR_DEVICE_WAIT, ERR_UNSUPPOR
 SCHEME_BQ4, SCHEME_INT4 = 0, 1
 DT_F32, DT_BF16, DT_INT4, DT_INT8 = 0, 1, 2, 3
 H_EMBED, H_FINAL_NORM, H_LM_HEAD = 0, 1, 2
+(M_PRE_FC_NORM_HIDDEN, M_PRE_FC_NORM_EMBEDDING, M_FC, M_INPUT_NORM, M_Q_PROJ, M_K_PROJ, M_V_PROJ, M_Q_NORM, M_K_NORM,
+ M_O_PROJ, M_OUT_NORM) = range(11)
 T_POST_NORM, T_ROUTER, T_SHARED_GATE, T_SHARED_UP, T_SHARED_DOWN, T_SHARED_SGATE = range(6)
 EP_HANDLE_BYTES = 64
 
@@ -32,6 +34,11 @@ class MoeDims(C.Structure):
 class ExpertLayout(C.Structure):
     _fields_ = [(n, C.c_int64) for n in ("gate_w", "gate_s", "gate_b", "up_w", "up_s", "up_b",
                                          "down_w", "down_s", "down_b", "expert_size")]
+
+
+class AttnDims(C.Structure):
+    _fields_ = [("num_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("rotary_dim", C.c_int32),
+                ("max_seq", C.c_int32), ("rope_theta", C.c_float)]
 
 
 class LayerPtrs(C.Structure):
@@ -77,6 +84,9 @@ SIGNATURES = {
     "moe_logits_dev": (_i, [_vp, _vp, _i32, _vp]),
     "moe_forward_host": (_i, [_vp, _vp, _i32, _i, _i, CHECK_FN, _vp, _vp]),
     "moe_mtp_forward_host": (_i, [_vp, _vp, _vp]),
+    "moe_mtp_configure": (_i, [_vp, C.POINTER(AttnDims)]),
+    "moe_mtp_load_tensor": (_i, [_vp, _i, _vp, _vp, _vp, _i]),
+    "moe_mtp_step_host": (_i, [_vp, _vp, _i64, _vp]),
     "moe_mtp_reset": (_i, [_vp]),
     "moe_mtp_rollback": (_i, [_vp, _i64]),
     "moe_mtp_pos": (_i, [_vp, C.POINTER(_i64)]),

@@ -132,6 +132,7 @@ class Engine:
             for l in range(layers + mtp):
                 self._load_layer(l, f"model.layers.{l}" if l < layers else f"mtp.layers.{l - layers}")
             self._missing_head = self._load_head()
+            self._missing_mtp = self._load_mtp() if mtp else ["an MTP layer (mtp_num_hidden_layers == 0)"]
         except Exception:
             self.native.close()
             raise
@@ -158,6 +159,44 @@ class Engine:
         else:
             missing.append("lm_head")
         return missing
+
+    def _load_mtp(self):
+        """The attention half of the MTP block, when the directory has its tensors (src/engine/qwen35_moe/mtp.rs:85-216
+        names them); returns the names that are missing.  mtp.norm is optional: the model's final norm stands in."""
+        m, eng = self.model.inner, self.native
+        heads, kv_heads, head_dim = m.get("num_attention_heads"), m.get("num_key_value_heads"), m.get("head_dim")
+        if not heads or not kv_heads or not head_dim:
+            return ["num_attention_heads / num_key_value_heads / head_dim in config.json"]
+        rope = m.get("rope_parameters") or {}
+        factor = m.get("partial_rotary_factor", rope.get("partial_rotary_factor", 0.25))
+        theta = m.get("rope_theta", rope.get("rope_theta", 10_000_000.0))
+        norms = {L.M_PRE_FC_NORM_HIDDEN: "mtp.pre_fc_norm_hidden.weight", L.M_PRE_FC_NORM_EMBEDDING: "mtp.pre_fc_norm_embedding.weight",
+                 L.M_INPUT_NORM: "mtp.layers.0.input_layernorm.weight", L.M_Q_NORM: "mtp.layers.0.self_attn.q_norm.weight",
+                 L.M_K_NORM: "mtp.layers.0.self_attn.k_norm.weight"}
+        q_dim, kv_dim, H = int(heads) * int(head_dim), int(kv_heads) * int(head_dim), self.dims.hidden
+        projs = {L.M_FC: ("mtp.fc", H, 2 * H), L.M_Q_PROJ: ("mtp.layers.0.self_attn.q_proj", 2 * q_dim, H),
+                 L.M_K_PROJ: ("mtp.layers.0.self_attn.k_proj", kv_dim, H), L.M_V_PROJ: ("mtp.layers.0.self_attn.v_proj", kv_dim, H),
+                 L.M_O_PROJ: ("mtp.layers.0.self_attn.o_proj", H, q_dim)}
+        found_n = {k: m.tensor(n) for k, n in norms.items()}
+        found_p = {}
+        for k, (base, rows, cols) in projs.items():
+            w = m.tensor(base + ".weight")
+            if w is not None and w.dtype == np.uint16:            # bf16, stored flat (src/dtype.rs:456-460)
+                found_p[k] = w.reshape(rows, cols)
+            else:
+                found_p[k] = m.q4(base)
+        missing = [norms[k] for k, v in found_n.items() if v is None] + [projs[k][0] for k, v in found_p.items() if v is None]
+        if missing:
+            return missing
+        eng.mtp_configure(int(heads), int(kv_heads), int(head_dim), int(int(head_dim) * float(factor)), float(theta))
+        for k, v in found_n.items():
+            eng.mtp_load_norm(k, v)
+        out_norm = m.tensor("mtp.norm.weight")
+        if out_norm is not None:
+            eng.mtp_load_norm(L.M_OUT_NORM, out_norm)
+        for k, v in found_p.items():
+            eng.mtp_load_proj(k, v)
+        return []
 
     def _load_layer(self, layer: int, prefix: str) -> None:
         m, d, eng = self.model.inner, self.dims, self.native
@@ -268,7 +307,11 @@ class Engine:
             return np.zeros(0, np.float32)
         if not 0 <= int(token_id) < self.dims.vocab:
             raise ValueError(f"token id {token_id} outside [0, {self.dims.vocab})")
-        return self.native.mtp_forward(self._last_h)
+        if self._missing_mtp or self._missing_head:
+            # without the block's attention tensors or the head only the MoE half can run: hidden state [hidden]
+            return self.native.mtp_forward(self._last_h)
+        # the reference's mtp_forward (src/python_bindings.rs:283-291): logits [vocab] of the next-next token
+        return self.native.mtp_step(self._last_h, int(token_id))
 
     def mtp_reset(self) -> None:
         self.native.mtp_reset()

@@ -139,6 +139,25 @@ struct HeadState {
     int32_t cap = 0;
 };
 
+// The MTP block's attention half (attn.cu): tensors, KV cache and scratch.
+struct ProjTensor {
+    uint8_t* w = nullptr;          // bf16 [rows, cols], or 4-bit words followed by scales at s_off and biases at b_off
+    size_t s_off = 0, b_off = 0;
+    int dtype = 0, rows = 0, cols = 0;
+    bool loaded = false;
+};
+struct MtpAttnState {
+    moe_attn_dims_t ad{};
+    bool configured = false;
+    uint16_t* norms[11] = {};      // bf16 norm weights by moe_mtp_tensor_t (projection slots stay null)
+    ProjTensor proj[11];           // projections by moe_mtp_tensor_t (norm slots stay unloaded)
+    float* k_cache = nullptr;      // [max_seq, num_kv_heads * head_dim]
+    float* v_cache = nullptr;
+    float* work = nullptr;         // scratch vectors of one step
+    int64_t* id_dev = nullptr;
+    bool bf_attr_set = false;
+};
+
 }  // namespace moe
 
 struct moe_engine {
@@ -187,6 +206,7 @@ struct moe_engine {
     moe::EpState ep;
 
     moe::HeadState head;
+    moe::MtpAttnState mtp;
 };
 
 namespace moe {
@@ -218,6 +238,12 @@ int ep_alloc_work(moe_engine* e);
 int head_load_tensor(moe_engine* e, int which, const void* w, const void* s, const void* b, int dtype);
 int launch_embed(moe_engine* e, const int64_t* ids_dev, int32_t n, float* out_dev);
 int launch_logits(moe_engine* e, const float* hidden_dev, int32_t n, float* logits_dev);
+// the same with another norm weight (bf16 [hidden], device) in place of the model's final norm; null = the model's
+int launch_logits_norm(moe_engine* e, const float* hidden_dev, int32_t n, float* logits_dev, const uint16_t* norm_w);
+int mtp_configure(moe_engine* e, const moe_attn_dims_t* ad);
+int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, const void* b, int dtype);
+int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits_dev);
+void mtp_destroy(moe_engine* e);
 int head_reserve(moe_engine* e, int32_t n);
 void head_destroy(moe_engine* e);
 int refresh_layer_table(moe_engine* e);

@@ -290,6 +290,7 @@ void moe_engine_destroy(moe_engine_t* e) {
     decode_destroy(e);
     batch_destroy(e);
     head_destroy(e);
+    mtp_destroy(e);
     if (e->layers_dev) cudaFree(e->layers_dev);
     if (e->io_dev) cudaFree(e->io_dev);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -839,6 +840,34 @@ int moe_mtp_forward_host(moe_engine_t* e, const float* h_in, float* h_out) {
         return MOE_ERR_STATE;
     }
     int rc = moe_layer_forward_host(e, e->dims.num_layers, h_in, 1, h_out, nullptr, nullptr, nullptr, nullptr);
+    if (rc == MOE_OK) e->mtp_pos++;
+    return rc;
+}
+
+int moe_mtp_configure(moe_engine_t* e, const moe_attn_dims_t* attn) {
+    MOE_REQUIRE(e && attn, "null argument");
+    return mtp_configure(e, attn);
+}
+
+int moe_mtp_load_tensor(moe_engine_t* e, int which, const void* w, const void* s, const void* b, int dtype) {
+    MOE_REQUIRE(e, "null engine");
+    return mtp_load_tensor(e, which, w, s, b, dtype);
+}
+
+int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, float* logits_host) {
+    MOE_REQUIRE(e && h_host && logits_host, "null argument");
+    const size_t lb = (size_t)e->dims.vocab * 4;
+    int rc = io_reserve(e, align_up(lb, 256));
+    if (rc) return rc;
+    float* logits_dev = reinterpret_cast<float*>(e->io_dev);
+    rc = mtp_step(e, h_host, token_id, logits_dev);
+    if (rc) {
+        cudaStreamSynchronize(e->stream);  // the inputs are the caller's: nothing of theirs may still be in flight
+        return rc;
+    }
+    MOE_CUDA(cudaMemcpyAsync(logits_host, logits_dev, lb, cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    rc = poll_device_error(e);
     if (rc == MOE_OK) e->mtp_pos++;
     return rc;
 }

@@ -301,15 +301,19 @@ int launch_embed(moe_engine* e, const int64_t* ids_dev, int32_t n, float* out_de
 
 // logits[t] = lm_head . final_norm(hidden[t]) for n tokens; all device pointers
 int launch_logits(moe_engine* e, const float* hidden_dev, int32_t n, float* logits_dev) {
+    return launch_logits_norm(e, hidden_dev, n, logits_dev, nullptr);
+}
+
+int launch_logits_norm(moe_engine* e, const float* hidden_dev, int32_t n, float* logits_dev, const uint16_t* norm_w) {
     HeadState& hs = e->head;
     const moe_dims_t& d = e->dims;
-    if (!hs.norm_loaded || !hs.lm_loaded) {
-        set_error("the model head is not loaded (%s missing)", !hs.norm_loaded ? "model.norm.weight" : "lm_head");
+    if ((!norm_w && !hs.norm_loaded) || !hs.lm_loaded) {
+        set_error("the model head is not loaded (%s missing)", !hs.lm_loaded ? "lm_head" : "model.norm.weight");
         return MOE_ERR_STATE;
     }
     int rc = head_reserve(e, n);
     if (rc) return rc;
-    final_norm_kernel<<<n, 256, 0, e->stream>>>(hidden_dev, hs.final_norm, d.hidden, hs.x);
+    final_norm_kernel<<<n, 256, 0, e->stream>>>(hidden_dev, norm_w ? norm_w : hs.final_norm, d.hidden, hs.x);
     e->launches++;
     for (int t = 0; t < n; ++t) {
         const float* x = hs.x + (size_t)t * d.hidden;

@@ -283,6 +283,33 @@ class NativeEngine:
         L.check(self.lib.moe_mtp_forward_host(self.h, L.ptr(h_in), L.ptr(out)))
         return out
 
+    # ── MTP block, whole step (attention + MoE + head) ───────────────────
+    def mtp_configure(self, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, rope_theta: float,
+                      max_seq: int = 4096) -> None:
+        ad = L.AttnDims(num_heads, num_kv_heads, head_dim, rotary_dim, max_seq, rope_theta)
+        L.check(self.lib.moe_mtp_configure(self.h, C.byref(ad)))
+
+    def mtp_load_norm(self, which: int, w: np.ndarray) -> None:
+        w = np.ascontiguousarray(w, np.uint16)
+        L.check(self.lib.moe_mtp_load_tensor(self.h, which, L.ptr(w), None, None, L.DT_BF16))
+
+    def mtp_load_proj(self, which: int, t) -> None:
+        """A projection: bf16 bit patterns [out, in] or a 4-bit triple."""
+        if isinstance(t, tuple):
+            w, s, b = (np.ascontiguousarray(t[0], np.uint32), np.ascontiguousarray(t[1], np.uint16),
+                       np.ascontiguousarray(t[2], np.uint16))
+            L.check(self.lib.moe_mtp_load_tensor(self.h, which, L.ptr(w), L.ptr(s), L.ptr(b), L.DT_INT4))
+        else:
+            w = np.ascontiguousarray(t, np.uint16)
+            L.check(self.lib.moe_mtp_load_tensor(self.h, which, L.ptr(w), None, None, L.DT_BF16))
+
+    def mtp_step(self, h: np.ndarray, token_id: int) -> np.ndarray:
+        """(hidden state before the final norm, previous token) -> logits [vocab]; advances the block's position."""
+        h = np.ascontiguousarray(h, np.float32).reshape(self.dims.hidden)
+        out = np.empty(self.dims.vocab, np.float32)
+        L.check(self.lib.moe_mtp_step_host(self.h, L.ptr(h), int(token_id), L.ptr(out)))
+        return out
+
     def mtp_reset(self) -> None:
         L.check(self.lib.moe_mtp_reset(self.h))
 

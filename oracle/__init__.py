@@ -304,3 +304,64 @@ def final_norm(h, w_u16, eps: float = 1e-6) -> np.ndarray:
     for i in range(flat.shape[0]):
         lib().orc_final_norm(_p(flat[i]), _p(w_u16), w_u16.size, C.c_float(eps))
     return h
+
+
+# ── the MTP block (reference src/engine/qwen35_moe/mtp.rs:58-225) ─────────────
+
+def rope(x, num_heads: int, head_dim: int, rope_dim: int, pos: int, theta: float) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    lib().orc_rope(_p(x), _p(out), num_heads, head_dim, rope_dim, pos, C.c_float(theta))
+    return out
+
+
+def attention(q, k_cache, v_cache, num_heads: int, num_kv_heads: int, head_dim: int, seq_len: int) -> np.ndarray:
+    q = _c(q, np.float32)
+    k_cache = _c(k_cache, np.float32)
+    v_cache = _c(v_cache, np.float32)
+    out = np.empty(num_heads * head_dim, np.float32)
+    lib().orc_attention(_p(q), _p(k_cache), _p(v_cache), num_heads, num_kv_heads, head_dim, seq_len,
+                        C.c_float(1.0 / np.sqrt(np.float32(head_dim))), _p(out))
+    return out
+
+
+class MtpWeights:
+    """Tensors of the MTP block besides its MoE half.  Norm weights are bf16 bit patterns; a projection is either
+    bf16 bit patterns [out, in] or a 4-bit triple (w, s, b)."""
+
+    def __init__(self, *, hnorm, enorm, fc, attn_norm, q_proj, k_proj, v_proj, q_norm, k_norm, o_proj, out_norm,
+                 num_heads, num_kv_heads, head_dim, rope_dim, rope_theta):
+        self.__dict__.update(locals())
+
+
+def _project(w, x) -> np.ndarray:
+    return matvec_int4(*w, x) if isinstance(w, tuple) else matvec_bf16(w, x)
+
+
+def mtp_step(mw: "MtpWeights", moe: "LayerWeights", top_k: int, embed_q4, lm_head, h, token_id: int, pos: int,
+             k_cache: np.ndarray, v_cache: np.ndarray) -> np.ndarray:
+    """(h, token) -> logits; appends this position's K and V to the caches (mtp.rs:85-225)."""
+    H = h.size
+    tok = embed_lookup(*embed_q4, [token_id])[0]
+    concat = np.concatenate([final_norm(tok, mw.enorm), final_norm(h, mw.hnorm)])  # embedding first (mtp.rs:103-105)
+    cur = matvec_int4(*mw.fc, concat)
+    x = final_norm(cur, mw.attn_norm)
+    q_dim, kv_dim = mw.num_heads * mw.head_dim, mw.num_kv_heads * mw.head_dim
+    q = _project(mw.q_proj, x)
+    k = _project(mw.k_proj, x)
+    v = _project(mw.v_proj, x)
+    q_head, gate = q[:q_dim], q[q_dim:]
+    qn = final_norm(q_head.reshape(mw.num_heads, mw.head_dim), mw.q_norm).reshape(-1)   # per head (mtp.rs:268-276)
+    kn = final_norm(k.reshape(mw.num_kv_heads, mw.head_dim), mw.k_norm).reshape(-1)
+    qr = rope(qn, mw.num_heads, mw.head_dim, mw.rope_dim, pos, mw.rope_theta)
+    kr = rope(kn, mw.num_kv_heads, mw.head_dim, mw.rope_dim, pos, mw.rope_theta)
+    k_cache[pos] = kr
+    v_cache[pos] = v
+    att = attention(qr, k_cache, v_cache, mw.num_heads, mw.num_kv_heads, mw.head_dim, pos + 1)
+    gated = (att * (np.float32(1.0) / (np.float32(1.0) + np.exp(-gate)))).astype(np.float32)
+    cur = (_project(mw.o_proj, gated) + cur).astype(np.float32)
+    cur, _, _ = moe_layer(moe, cur, top_k)                                   # post-attention norm, MoE, residual
+    out = final_norm(cur[0], mw.out_norm)
+    if isinstance(lm_head, tuple) and len(lm_head) == 2:
+        return matvec_int8(lm_head[0], lm_head[1], out)
+    return matvec_int4(*lm_head, out)

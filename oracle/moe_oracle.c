@@ -618,3 +618,53 @@ void orc_final_norm(float* hidden, const uint16_t* w, int dim, float eps) {
     const float inv_rms = 1.0f / sqrtf(sum_sq / (float)dim + eps);
     for (int i = 0; i < dim; ++i) hidden[i] *= inv_rms * orc_bf16_to_f32(w[i]);
 }
+
+/* ─── MTP block: the attention half (reference src/engine/qwen35_moe/mtp.rs) ─── */
+
+/* apply_rope: mtp.rs:285-303.  Interleaved pairs (2i, 2i+1) of the first rope_dim elements of every head. */
+void orc_rope(const float* x, float* out, int num_heads, int head_dim, int rope_dim, int pos, float theta) {
+    const float pos_f = (float)pos;
+    for (int i = 0; i < num_heads * head_dim; ++i) out[i] = x[i];
+    for (int h = 0; h < num_heads; ++h) {
+        const int base = h * head_dim;
+        for (int i = 0; i < rope_dim / 2; ++i) {
+            const int idx = base + i * 2;
+            const float freq = powf(theta, -2.0f * (float)i / (float)rope_dim);
+            const float angle = pos_f * freq;
+            const float sin_a = sinf(angle), cos_a = cosf(angle);
+            const float x0 = x[idx], x1 = x[idx + 1];
+            out[idx] = x0 * cos_a - x1 * sin_a;
+            out[idx + 1] = x0 * sin_a + x1 * cos_a;
+        }
+    }
+}
+
+/* cpu_attention: mtp.rs:305-352.  q [num_heads * head_dim] against caches [seq_len, num_kv_heads * head_dim];
+ * scores scaled, max-subtracted, exponentiated; each output element adds score / sum * v over the positions. */
+void orc_attention(const float* q, const float* k_cache, const float* v_cache, int num_heads, int num_kv_heads,
+                   int head_dim, int seq_len, float kq_scale, float* out) {
+    const int kv_dim = num_kv_heads * head_dim, group_size = num_heads / num_kv_heads;
+    float* scores = (float*)malloc(sizeof(float) * (size_t)seq_len);
+    for (int h = 0; h < num_heads; ++h) {
+        const int kv_h = h / group_size, q_off = h * head_dim;
+        float max_score = -INFINITY;
+        for (int t = 0; t < seq_len; ++t) {
+            const float* kr = k_cache + (size_t)t * kv_dim + kv_h * head_dim;
+            float dot = 0.0f;
+            for (int d = 0; d < head_dim; ++d) dot += q[q_off + d] * kr[d];
+            scores[t] = dot * kq_scale;
+            max_score = rust_max(max_score, scores[t]);
+        }
+        float sum_exp = 0.0f;
+        for (int t = 0; t < seq_len; ++t) {
+            scores[t] = expf(scores[t] - max_score);
+            sum_exp += scores[t];
+        }
+        for (int d = 0; d < head_dim; ++d) {
+            float acc = 0.0f;
+            for (int t = 0; t < seq_len; ++t) acc += scores[t] / sum_exp * v_cache[(size_t)t * kv_dim + kv_h * head_dim + d];
+            out[q_off + d] = acc;
+        }
+    }
+    free(scores);
+}

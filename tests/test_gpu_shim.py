@@ -198,6 +198,57 @@ def test_quantize_whole_checkpoint_names_types_values(tmp_path, scheme):
     assert summary["f32"] == 1 and summary.get("int8", 0) == (1 if scheme == "bq4" else 0)
 
 
+@pytest.mark.parametrize("scheme", ["bq4", "int4"])
+def test_mtp_forward_returns_logits_when_the_block_is_complete(tmp_path, scheme):
+    """A checkpoint that carries the MTP block's attention tensors: quantise, load, and `mtp_forward(token)` is the
+    reference's draft step (src/python_bindings.rs:283-291, src/engine/qwen35_moe/mtp.rs:58-225): logits [vocab]."""
+    NH, NKV, HD = 4, 2, 64
+    src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
+    raw, head = _hf_checkpoint(src, layers=1, mtp=1)
+    cfg = json.load(open(os.path.join(src, "config.json")))
+    cfg["text_config"].update({"num_attention_heads": NH, "num_key_value_heads": NKV, "head_dim": HD})
+    json.dump(cfg, open(os.path.join(src, "config.json"), "w"))
+    rng = np.random.default_rng(17)
+    bf = lambda a: synth.to_bf16_rne(np.asarray(a, np.float32))
+    f = synth.bf16_to_f32
+    zc = lambda n: bf(rng.uniform(-0.2, 0.2, n))            # zero-centred norm weights, as stored by Qwen3.6
+    mat = lambda r, c: bf(synth.normal_weights(rng, (r, c)) * 2.0)
+    q_dim, kv_dim = NH * HD, NKV * HD
+    t = {"mtp.pre_fc_norm_hidden.weight": zc(H), "mtp.pre_fc_norm_embedding.weight": zc(H), "mtp.fc.weight": mat(H, 2 * H),
+         "mtp.layers.0.input_layernorm.weight": zc(H), "mtp.layers.0.self_attn.q_proj.weight": mat(2 * q_dim, H),
+         "mtp.layers.0.self_attn.k_proj.weight": mat(kv_dim, H), "mtp.layers.0.self_attn.v_proj.weight": mat(kv_dim, H),
+         "mtp.layers.0.self_attn.q_norm.weight": zc(HD), "mtp.layers.0.self_attn.k_norm.weight": zc(HD),
+         "mtp.layers.0.self_attn.o_proj.weight": mat(H, q_dim), "mtp.norm.weight": zc(H)}
+    _write_safetensors(os.path.join(src, "model-00002-of-00002.safetensors"), t)
+    rs.qwen35_moe_quantize(src, dst, version="3.6", scheme=scheme)
+    one = np.float32(1.0)
+    nw = lambda k: oracle.f32_to_bf16(f(t[k]) + one)
+    pj = lambda k: oracle.quant_int4(f(t[k])) if scheme == "int4" else t[k]
+    mw = oracle.MtpWeights(hnorm=nw("mtp.pre_fc_norm_hidden.weight"), enorm=nw("mtp.pre_fc_norm_embedding.weight"),
+                           fc=oracle.quant_int4(f(t["mtp.fc.weight"])), attn_norm=nw("mtp.layers.0.input_layernorm.weight"),
+                           q_proj=pj("mtp.layers.0.self_attn.q_proj.weight"), k_proj=pj("mtp.layers.0.self_attn.k_proj.weight"),
+                           v_proj=pj("mtp.layers.0.self_attn.v_proj.weight"), q_norm=nw("mtp.layers.0.self_attn.q_norm.weight"),
+                           k_norm=nw("mtp.layers.0.self_attn.k_norm.weight"), o_proj=pj("mtp.layers.0.self_attn.o_proj.weight"),
+                           out_norm=nw("mtp.norm.weight"), num_heads=NH, num_kv_heads=NKV, head_dim=HD, rope_dim=HD // 4,
+                           rope_theta=1.0e7)
+    layers = _oracle_layers(raw, scheme)
+    lm = oracle.quant_int8(head["lm_head"]) if scheme == "bq4" else oracle.quant_int4(head["lm_head"])
+    embed = oracle.quant_int4(head["embed"])
+    model = rs.Model(dst)
+    eng = rs.Engine(model, "Qwen35MoEFusedExp5")
+    cache = rs.Cache(model)
+    eng.forward(np.array([3, 9], np.int64), cache)       # leaves last_h_pre_norm behind
+    h = eng.last_h_pre_norm().copy()
+    kc = np.zeros((8, kv_dim), np.float32)
+    vc = np.zeros((8, kv_dim), np.float32)
+    for pos, tok in enumerate([11, 12]):
+        got = eng.mtp_forward(tok)
+        want = oracle.mtp_step(mw, layers[1], K, embed, lm, h, tok, pos, kc, vc)
+        assert got.shape == (V,) and rel_l2(got, want) < 1e-2
+    eng.mtp_reset()
+    eng.native.close()
+
+
 def test_top_level_module_alias_runs_a_forward(tmp_path):
     """The reference's Python does `import _moe_infer_rs as _rs` (moe_infer/_core.py:14, pipeline.py:16): with the mirror
     registered under that name, the call sequence of pipeline.py:250-254 and :361-367 runs on the GPU."""
