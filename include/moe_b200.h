@@ -254,6 +254,37 @@ int moe_mtp_configure(moe_engine_t* e, const moe_attn_dims_t* attn);
 int moe_mtp_load_tensor(moe_engine_t* e, int which, const void* w_host, const void* s_host, const void* b_host, int dtype);
 int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, float* logits_host);
 
+/* ── attention half of the 40 main layers, batch-1 decode ────────────────────
+ * pre_expert_full / pre_expert_linear up to the residual (src/engine/qwen35_moe/cpu.rs:87-183, 218-347; the
+ * Metal engines' op1, fused_exp1.rs:399-732): layer l is a gated full-attention layer when (l + 1) %
+ * full_attn_interval == 0 (input norm; q/k/v projections, q carrying [head, gate] per head; per-head q/k RMS
+ * norm; RoPE on the pairs (d, d + rotary_dim / 2); f32 KV cache; softmax attention; sigmoid gate; o projection;
+ * residual) and a Gated DeltaNet layer otherwise (input norm; in_proj_qkv / z / b / a; causal depthwise conv
+ * over the last conv_kernel inputs + SiLU; unweighted per-head q/k norm; decay and input gate from a, b, A_log,
+ * dt_bias; delta-rule recurrence on a [v_heads, value_dim, key_dim] f32 state; gated RMS norm; out_proj;
+ * residual).  Each attention half feeds the layer's MoE half (the decode kernel).  Token-serial: n tokens are
+ * n decode steps.  moe_attn_configure allocates every layer's cache / state and resets the position; tensors
+ * by role (norms, conv1d [channels, kernel], dt_bias: bf16; A_log: MOE_DT_F32; projections: MOE_DT_BF16 [out,
+ * in] or MOE_DT_INT4 triple).  moe_model_forward_hidden_host: embeddings [n, hidden] -> hidden states before
+ * the final norm [n, hidden] (then moe_logits_host); moe_model_forward_host: token ids -> logits [n, vocab].
+ * MOE_ERR_STATE when a tensor is missing or the position reaches max_seq.  Host pointers. */
+typedef struct {
+    moe_attn_dims_t full;
+    int32_t lin_num_k_heads, lin_num_v_heads, lin_key_dim, lin_value_dim, conv_kernel, full_attn_interval;
+} moe_model_attn_dims_t;
+typedef enum {
+    MOE_A_INPUT_NORM = 0, MOE_A_Q_PROJ = 1, MOE_A_K_PROJ = 2, MOE_A_V_PROJ = 3, MOE_A_Q_NORM = 4, MOE_A_K_NORM = 5,
+    MOE_A_O_PROJ = 6, MOE_A_IN_PROJ_QKV = 7, MOE_A_IN_PROJ_Z = 8, MOE_A_IN_PROJ_B = 9, MOE_A_IN_PROJ_A = 10,
+    MOE_A_CONV1D = 11, MOE_A_A_LOG = 12, MOE_A_DT_BIAS = 13, MOE_A_LIN_NORM = 14, MOE_A_OUT_PROJ = 15
+} moe_attn_tensor_t;
+int moe_attn_configure(moe_engine_t* e, const moe_model_attn_dims_t* dims);
+int moe_attn_load_tensor(moe_engine_t* e, int layer, int which, const void* w_host, const void* s_host,
+                         const void* b_host, int dtype);
+int moe_model_forward_hidden_host(moe_engine_t* e, const float* emb_host, int32_t n, float* out_host);
+int moe_model_forward_host(moe_engine_t* e, const int64_t* ids_host, int32_t n, float* logits_host);
+int moe_model_reset(moe_engine_t* e);
+int moe_model_pos(const moe_engine_t* e, int64_t* pos);
+
 /* ── telemetry ───────────────────────────────────────────────────────────────
  * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys
  * follow the reference (`engine.total_ms`, `phase.route_cpu_ms`, ...).  Fills up

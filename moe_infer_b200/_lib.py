@@ -41,6 +41,15 @@ class AttnDims(C.Structure):
                 ("max_seq", C.c_int32), ("rope_theta", C.c_float)]
 
 
+class ModelAttnDims(C.Structure):
+    _fields_ = [("full", AttnDims), ("lin_num_k_heads", C.c_int32), ("lin_num_v_heads", C.c_int32), ("lin_key_dim", C.c_int32),
+                ("lin_value_dim", C.c_int32), ("conv_kernel", C.c_int32), ("full_attn_interval", C.c_int32)]
+
+
+(A_INPUT_NORM, A_Q_PROJ, A_K_PROJ, A_V_PROJ, A_Q_NORM, A_K_NORM, A_O_PROJ, A_IN_PROJ_QKV, A_IN_PROJ_Z, A_IN_PROJ_B, A_IN_PROJ_A,
+ A_CONV1D, A_A_LOG, A_DT_BIAS, A_LIN_NORM, A_OUT_PROJ) = range(16)
+
+
 class LayerPtrs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("experts", "post_norm", "router_bf16", "router_w", "router_s", "router_b",
                                           "shared", "sgate_w", "sgate_s", "sgate_b")]
@@ -87,6 +96,12 @@ SIGNATURES = {
     "moe_mtp_configure": (_i, [_vp, C.POINTER(AttnDims)]),
     "moe_mtp_load_tensor": (_i, [_vp, _i, _vp, _vp, _vp, _i]),
     "moe_mtp_step_host": (_i, [_vp, _vp, _i64, _vp]),
+    "moe_attn_configure": (_i, [_vp, C.POINTER(ModelAttnDims)]),
+    "moe_attn_load_tensor": (_i, [_vp, _i, _i, _vp, _vp, _vp, _i]),
+    "moe_model_forward_hidden_host": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_model_forward_host": (_i, [_vp, _vp, _i32, _vp]),
+    "moe_model_reset": (_i, [_vp]),
+    "moe_model_pos": (_i, [_vp, C.POINTER(_i64)]),
     "moe_mtp_reset": (_i, [_vp]),
     "moe_mtp_rollback": (_i, [_vp, _i64]),
     "moe_mtp_pos": (_i, [_vp, C.POINTER(_i64)]),

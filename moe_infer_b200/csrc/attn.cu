@@ -65,10 +65,16 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float* __restr
     for (int i = tid; i < dim; i += 256) out[(size_t)blockIdx.x * dim + i] = row[i] * inv_rms * bf16_bits_to_f32(w[i]);
 }
 
-// ─── per-head norm + RoPE of q and k, K/V cache append (mtp.rs:137-157) ──────────────────────────────────────
+// ─── per-head norm + RoPE of q and k, K/V cache append ───────────────────────────────────────────────────────
 // Block h < num_heads: query head h -> q_out.  Block num_heads + j: key head j -> k_cache[pos], and value head j
-// is copied to v_cache[pos].  RoPE rotates the interleaved pairs (2i, 2i+1), i < rope_dim / 2, by pos * theta^(-2i/rope_dim).
-__global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict__ q, const float* __restrict__ k,
+// is copied to v_cache[pos].  Two conventions exist in the reference:
+//   * the MTP block (mtp.rs:137-157, 268-303): the q projection is [all heads | all gates] (q_stride = head_dim) and
+//     RoPE rotates the interleaved pairs (2i, 2i+1), i < rope_dim / 2;
+//   * the main model's full-attention layers (src/math_util.rs:501-597): the q projection is [head, gate] per head
+//     (q_stride = 2 * head_dim) and RoPE rotates the pairs (i, i + rope_dim / 2).
+// Either way the angle of pair i is pos * theta^(-2i / rope_dim).
+__global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict__ q, int q_stride, int rope_half_split,
+                                                        const float* __restrict__ k,
                                                         const float* __restrict__ v, const uint16_t* __restrict__ q_norm,
                                                         const uint16_t* __restrict__ k_norm, int num_heads, int num_kv_heads,
                                                         int head_dim, int rope_dim, int pos, float theta, float* __restrict__ q_out,
@@ -78,7 +84,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool is_q = (int)blockIdx.x < num_heads;
     const int h = is_q ? blockIdx.x : blockIdx.x - num_heads;
-    const float* src = (is_q ? q : k) + (size_t)h * head_dim;
+    const float* src = is_q ? q + (size_t)h * q_stride : k + (size_t)h * head_dim;
     const uint16_t* nw = is_q ? q_norm : k_norm;
     const size_t kv_dim = (size_t)num_kv_heads * head_dim;
     float* dst = is_q ? q_out + (size_t)h * head_dim : k_cache + (size_t)pos * kv_dim + (size_t)h * head_dim;
@@ -96,12 +102,14 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
     for (int i = tid; i < head_dim; i += 256) {
         float o = hv[i];
         if (i < rope_dim) {
-            const int p = i >> 1;
+            const int half = rope_dim >> 1;
+            const int p = rope_half_split ? (i < half ? i : i - half) : (i >> 1);
+            const bool second = rope_half_split ? (i >= half) : ((i & 1) != 0);
             const float freq = powf(theta, -2.0f * (float)p / (float)rope_dim);
             float sn, cs;
             sincosf((float)pos * freq, &sn, &cs);
-            const float x0 = hv[i & ~1], x1 = hv[i | 1];
-            o = (i & 1) ? x0 * sn + x1 * cs : x0 * cs - x1 * sn;
+            const float x0 = hv[rope_half_split ? p : 2 * p], x1 = hv[rope_half_split ? p + half : 2 * p + 1];
+            o = second ? x0 * sn + x1 * cs : x0 * cs - x1 * sn;
         }
         dst[i] = o;
     }
@@ -118,7 +126,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
 // across the head).  out = attention * sigmoid(gate).
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, const float* __restrict__ gate,
-                                                          int num_heads, int num_kv_heads, int head_dim, int seq_len,
+                                                          int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_len,
                                                           float kq_scale, float* __restrict__ out) {
     extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head
     __shared__ float red[8];
@@ -159,7 +167,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
         const float* vc = v_cache + (size_t)kv_h * head_dim + d;
         float acc = 0.0f;
         for (int t = 0; t < seq_len; ++t) acc = fmaf(sc[t] / tot, vc[(size_t)t * kv_dim], acc);
-        const float g = gate[(size_t)h * head_dim + d];
+        const float g = gate[(size_t)h * gate_stride + d];
         out[(size_t)h * head_dim + d] = acc * (1.0f / (1.0f + expf(-g)));
     }
 }
@@ -167,6 +175,102 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
 __global__ void __launch_bounds__(256) add_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, int n, float* __restrict__ out) {
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i < n) out[i] = a[i] + b[i];
+}
+
+// ─── Gated DeltaNet (linear attention) layer, one token (src/engine/qwen35_moe/cpu.rs:218-347) ───────────────
+// Causal depthwise conv over the last `ksize` inputs of every channel, then SiLU; the state keeps the previous
+// ksize - 1 inputs, oldest first, and is shifted here (conv1d_step, src/math_util.rs:149-168; cpu.rs:263-275).
+// Weights [channels][ksize] bf16.  A thread owns a channel, so the in-place shift is race-free.
+__global__ void __launch_bounds__(256) conv1d_step_kernel(float* __restrict__ conv_state, const float* __restrict__ x,
+                                                          const uint16_t* __restrict__ w, float* __restrict__ out, int channels,
+                                                          int ksize) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= channels) return;
+    float acc = 0.0f;
+    for (int k = 0; k < ksize - 1; ++k) acc += conv_state[(size_t)k * channels + c] * bf16_bits_to_f32(w[(size_t)c * ksize + k]);
+    const float xin = x[c];
+    acc += xin * bf16_bits_to_f32(w[(size_t)c * ksize + ksize - 1]);
+    out[c] = acc / (1.0f + expf(-acc));  // silu (src/math_util.rs:71-75)
+    for (int k = 0; k + 2 < ksize; ++k) conv_state[(size_t)k * channels + c] = conv_state[(size_t)(k + 1) * channels + c];
+    if (ksize >= 2) conv_state[(size_t)(ksize - 2) * channels + c] = xin;
+}
+
+// Per-head RMS norm of q and k without weights, q scaled by 1 / key_dim and k by 1 / sqrt(key_dim) (cpu.rs:277-299).
+// Block (h, which): which = 0 the query head h, 1 the key head h; in place on the conv output [q | k | v].
+__global__ void __launch_bounds__(128) lin_qk_norm_kernel(float* __restrict__ qkv, int total_key, int key_dim) {
+    __shared__ float red[4];
+    const int h = blockIdx.x >> 1, which = blockIdx.x & 1;
+    float* head = qkv + (size_t)which * total_key + (size_t)h * key_dim;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float ss = 0.0f;
+    for (int i = tid; i < key_dim; i += 128) ss = fmaf(head[i], head[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float tot = red[0] + red[1] + red[2] + red[3];
+    const float inv = 1.0f / sqrtf(tot / (float)key_dim + 1e-6f);
+    const float inv_scale = 1.0f / sqrtf((float)key_dim);
+    const float mul = which == 0 ? inv * inv_scale * inv_scale : inv * inv_scale;
+    for (int i = tid; i < key_dim; i += 128) head[i] *= mul;
+}
+
+// The recurrence (compute_decay_beta + gated_delta_net_step, src/math_util.rs:401-466): per value head h and value
+// row vi, the key_dim-long state row is decayed, read against k, corrected by the delta rule and read against q.
+// One warp per row: the 2 MB of state per layer are read and written once, coalesced.
+__global__ void __launch_bounds__(256) delta_step_kernel(float* __restrict__ state, const float* __restrict__ q,
+                                                         const float* __restrict__ k, const float* __restrict__ v,
+                                                         const float* __restrict__ alpha, const float* __restrict__ beta,
+                                                         const float* __restrict__ a_log, const uint16_t* __restrict__ dt_bias,
+                                                         float* __restrict__ out, int num_v_heads, int k_heads_per_v,
+                                                         int key_dim, int value_dim) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= num_v_heads * value_dim) return;
+    const int h = row / value_dim, vi = row - h * value_dim;
+    const int kh = h / k_heads_per_v;
+    // decay and input gate of this head
+    const float a = expf(a_log ? a_log[h] : 0.0f);
+    const float softplus = logf(1.0f + expf(alpha[h] + (dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f)));
+    const float g = expf(-a * softplus);
+    const float bgate = 1.0f / (1.0f + expf(-beta[h]));
+    float* srow = state + ((size_t)h * value_dim + vi) * key_dim;
+    const float* kk = k + (size_t)kh * key_dim;
+    const float* qq = q + (size_t)kh * key_dim;
+    float kv_mem = 0.0f;
+    for (int i = lane; i < key_dim; i += 32) kv_mem = fmaf(srow[i] * g, kk[i], kv_mem);
+    kv_mem = warp_sum(kv_mem);
+    const float delta = (v[(size_t)h * value_dim + vi] - kv_mem) * bgate;
+    float o = 0.0f;
+    for (int i = lane; i < key_dim; i += 32) {
+        const float sn = srow[i] * g + kk[i] * delta;
+        srow[i] = sn;
+        o = fmaf(sn, qq[i], o);
+    }
+    o = warp_sum(o);
+    if (lane == 0) out[(size_t)h * value_dim + vi] = o;
+}
+
+// Per value head: RMS norm of the recurrence output, SiLU gate from z, bf16 weight [value_dim]
+// (gated_rms_norm, src/math_util.rs:472-493; w == null leaves the values as they are, cpu.rs:329-336).
+__global__ void __launch_bounds__(128) gated_rms_norm_kernel(const float* __restrict__ vals, const float* __restrict__ z,
+                                                             const uint16_t* __restrict__ w, float* __restrict__ out, int value_dim) {
+    __shared__ float red[4];
+    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = vals + (size_t)h * value_dim;
+    if (!w) {
+        for (int i = tid; i < value_dim; i += 128) out[(size_t)h * value_dim + i] = x[i];
+        return;
+    }
+    float ss = 0.0f;
+    for (int i = tid; i < value_dim; i += 128) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)value_dim + 1e-6f);
+    for (int i = tid; i < value_dim; i += 128) {
+        const float zv = z[(size_t)h * value_dim + i];
+        out[(size_t)h * value_dim + i] = x[i] * inv * (zv / (1.0f + expf(-zv))) * bf16_bits_to_f32(w[i]);
+    }
 }
 
 // ─── host side ──────────────────────────────────────────────────────────────
@@ -348,10 +452,10 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     if ((rc = mtp_project(e, MOE_M_Q_PROJ, x, q))) return rc;
     if ((rc = mtp_project(e, MOE_M_K_PROJ, x, k))) return rc;
     if ((rc = mtp_project(e, MOE_M_V_PROJ, x, v))) return rc;
-    attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
+    attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
                                                           m.ad.rotary_dim, pos, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
     const int seq = pos + 1;
-    attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, nh, nkv, hd, seq,
+    attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq,
                                                                1.0f / sqrtf((float)hd), gated);
     e->launches += 2;
     if ((rc = mtp_project(e, MOE_M_O_PROJ, gated, o))) return rc;
@@ -361,6 +465,292 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     // the MoE half: post-attention norm, router, experts, shared expert, residual (layer index num_layers)
     if ((rc = launch_decode(e, d.num_layers, d.num_layers + 1, cur2, y, nullptr, nullptr, nullptr, nullptr))) return rc;
     if ((rc = launch_logits_norm(e, y, 1, logits_dev, m.norms[MOE_M_OUT_NORM]))) return rc;
+    return MOE_OK;
+}
+
+
+// ─── the main layers' attention halves ──────────────────────────────────────
+
+static const char* attn_tensor_name(int which) {
+    static const char* names[] = {"input_layernorm", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.q_norm",
+                                  "self_attn.k_norm", "self_attn.o_proj", "linear_attn.in_proj_qkv", "linear_attn.in_proj_z",
+                                  "linear_attn.in_proj_b", "linear_attn.in_proj_a", "linear_attn.conv1d", "linear_attn.A_log",
+                                  "linear_attn.dt_bias", "linear_attn.norm", "linear_attn.out_proj"};
+    return (which >= 0 && which <= MOE_A_OUT_PROJ) ? names[which] : "?";
+}
+static bool attn_is_proj(int which) {
+    return which == MOE_A_Q_PROJ || which == MOE_A_K_PROJ || which == MOE_A_V_PROJ || which == MOE_A_O_PROJ ||
+           which == MOE_A_IN_PROJ_QKV || which == MOE_A_IN_PROJ_Z || which == MOE_A_IN_PROJ_B || which == MOE_A_IN_PROJ_A ||
+           which == MOE_A_OUT_PROJ;
+}
+static bool attn_role_is_full(int which) { return which >= MOE_A_Q_PROJ && which <= MOE_A_O_PROJ; }
+
+void attn_destroy(moe_engine* e) {
+    ModelAttnState& a = e->attn;
+    for (AttnLayerState& ls : a.layers) {
+        for (int i = 0; i < 16; ++i) {
+            if (ls.vec[i]) cudaFree(ls.vec[i]);
+            if (ls.proj[i].w) cudaFree(ls.proj[i].w);
+        }
+        if (ls.k_cache) cudaFree(ls.k_cache);
+        if (ls.v_cache) cudaFree(ls.v_cache);
+        if (ls.conv_state) cudaFree(ls.conv_state);
+        if (ls.ssm_state) cudaFree(ls.ssm_state);
+    }
+    a.layers.clear();
+    if (a.work) cudaFree(a.work);
+    a.work = nullptr;
+    a.configured = false;
+    a.pos = 0;
+}
+
+struct AttnSizes {
+    size_t H, q_dim, kv_dim, total_key, total_value, conv_dim;
+};
+static AttnSizes attn_sizes(const moe_engine* e) {
+    const moe_model_attn_dims_t& d = e->attn.d;
+    AttnSizes z{};
+    z.H = (size_t)e->dims.hidden;
+    z.q_dim = (size_t)d.full.num_heads * d.full.head_dim;
+    z.kv_dim = (size_t)d.full.num_kv_heads * d.full.head_dim;
+    z.total_key = (size_t)d.lin_num_k_heads * d.lin_key_dim;
+    z.total_value = (size_t)d.lin_num_v_heads * d.lin_value_dim;
+    z.conv_dim = 2 * z.total_key + z.total_value;
+    return z;
+}
+
+int attn_reset(moe_engine* e) {
+    ModelAttnState& a = e->attn;
+    if (!a.configured) return MOE_OK;
+    const AttnSizes z = attn_sizes(e);
+    for (AttnLayerState& ls : a.layers) {
+        if (ls.full) continue;  // KV entries behind the position are never read
+        MOE_CUDA(cudaMemsetAsync(ls.conv_state, 0, (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4, e->stream));
+        MOE_CUDA(cudaMemsetAsync(ls.ssm_state, 0, z.total_value * a.d.lin_key_dim * 4, e->stream));
+    }
+    a.pos = 0;
+    return MOE_OK;
+}
+
+int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
+    const moe_attn_dims_t& f = dims->full;
+    MOE_REQUIRE(f.num_heads > 0 && f.num_kv_heads > 0 && f.num_heads % f.num_kv_heads == 0,
+                "attention heads (%d) must be a positive multiple of the key/value heads (%d)", f.num_heads, f.num_kv_heads);
+    MOE_REQUIRE(f.head_dim > 0 && f.head_dim % 8 == 0 && f.head_dim <= 1024, "head_dim (%d) must be a multiple of 8 up to 1024", f.head_dim);
+    MOE_REQUIRE(f.rotary_dim >= 0 && f.rotary_dim <= f.head_dim && f.rotary_dim % 2 == 0,
+                "rotary_dim (%d) must be even and at most head_dim (%d)", f.rotary_dim, f.head_dim);
+    MOE_REQUIRE(f.max_seq > 0 && f.max_seq <= 8192, "max_seq (%d) must be in 1..8192", f.max_seq);
+    MOE_REQUIRE(dims->lin_num_k_heads > 0 && dims->lin_num_v_heads > 0 && dims->lin_num_v_heads % dims->lin_num_k_heads == 0,
+                "linear-attention value heads (%d) must be a positive multiple of the key heads (%d)", dims->lin_num_v_heads,
+                dims->lin_num_k_heads);
+    MOE_REQUIRE(dims->lin_key_dim > 0 && dims->lin_value_dim > 0 && dims->conv_kernel >= 2 && dims->conv_kernel <= 16,
+                "linear-attention dimensions out of range");
+    MOE_REQUIRE(dims->full_attn_interval >= 1, "full_attention_interval must be at least 1");
+    attn_destroy(e);
+    ModelAttnState& a = e->attn;
+    a.d = *dims;
+    const AttnSizes z = attn_sizes(e);
+    MOE_REQUIRE(z.q_dim % 64 == 0 && z.total_value % 64 == 0 && z.q_dim <= 16384 && z.total_value <= 16384,
+                "attention widths must be multiples of 64 up to 16384");
+    a.layers.resize((size_t)e->dims.num_layers);
+    for (int l = 0; l < e->dims.num_layers; ++l) {
+        AttnLayerState& ls = a.layers[l];
+        ls.full = (l + 1) % dims->full_attn_interval == 0;
+        if (ls.full) {
+            MOE_CUDA(cudaMalloc(&ls.k_cache, (size_t)f.max_seq * z.kv_dim * 4));
+            MOE_CUDA(cudaMalloc(&ls.v_cache, (size_t)f.max_seq * z.kv_dim * 4));
+        } else {
+            MOE_CUDA(cudaMalloc(&ls.conv_state, (size_t)(dims->conv_kernel - 1) * z.conv_dim * 4));
+            MOE_CUDA(cudaMalloc(&ls.ssm_state, z.total_value * dims->lin_key_dim * 4));
+        }
+    }
+    // scratch of one step: x, o, h_mid, ping, pong [H]; wide = max(2 q_dim, conv_dim); conv_out [conv_dim];
+    // k, v [kv_dim]; z, vals, normed [max(q_dim, total_value)]; qr [q_dim]; a, b [v_heads]
+    const size_t wide = 2 * z.q_dim > z.conv_dim ? 2 * z.q_dim : z.conv_dim;
+    const size_t mid = z.q_dim > z.total_value ? z.q_dim : z.total_value;
+    size_t bytes = 5 * al256a(z.H * 4) + al256a(wide * 4) + al256a(z.conv_dim * 4) + 2 * al256a(z.kv_dim * 4) + 3 * al256a(mid * 4) +
+                   al256a(z.q_dim * 4) + 2 * al256a((size_t)dims->lin_num_v_heads * 4);
+    MOE_CUDA(cudaMalloc(&a.work, bytes));
+    a.configured = true;
+    return attn_reset(e);
+}
+
+int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const void* s, const void* b, int dtype) {
+    ModelAttnState& a = e->attn;
+    if (!a.configured) {
+        set_error("moe_attn_configure must come before the attention tensors");
+        return MOE_ERR_STATE;
+    }
+    MOE_REQUIRE(layer >= 0 && layer < e->dims.num_layers, "attention tensor: layer %d out of range", layer);
+    MOE_REQUIRE(which >= 0 && which <= MOE_A_OUT_PROJ, "unknown attention tensor %d", which);
+    MOE_REQUIRE(w, "%s: null weight pointer", attn_tensor_name(which));
+    AttnLayerState& ls = a.layers[layer];
+    MOE_REQUIRE(which == MOE_A_INPUT_NORM || attn_role_is_full(which) == ls.full, "layer %d is a %s layer: it has no %s", layer,
+                ls.full ? "full-attention" : "linear-attention", attn_tensor_name(which));
+    const AttnSizes z = attn_sizes(e);
+    const moe_model_attn_dims_t& d = a.d;
+    if (!attn_is_proj(which)) {
+        size_t bytes = 0;
+        int want = MOE_DT_BF16;
+        switch (which) {
+            case MOE_A_INPUT_NORM: bytes = z.H * 2; break;
+            case MOE_A_Q_NORM: case MOE_A_K_NORM: bytes = (size_t)d.full.head_dim * 2; break;
+            case MOE_A_CONV1D: bytes = z.conv_dim * d.conv_kernel * 2; break;
+            case MOE_A_A_LOG: bytes = (size_t)d.lin_num_v_heads * 4; want = MOE_DT_F32; break;
+            case MOE_A_DT_BIAS: bytes = (size_t)d.lin_num_v_heads * 2; break;
+            default: bytes = (size_t)d.lin_value_dim * 2; break;  // linear_attn.norm
+        }
+        MOE_REQUIRE(dtype == want, "%s must be %s", attn_tensor_name(which), want == MOE_DT_F32 ? "f32" : "bf16");
+        if (!ls.vec[which]) MOE_CUDA(cudaMalloc(&ls.vec[which], al256a(bytes)));
+        MOE_CUDA(cudaMemcpyAsync(ls.vec[which], w, bytes, cudaMemcpyHostToDevice, e->stream));
+        MOE_CUDA(cudaStreamSynchronize(e->stream));
+        return MOE_OK;
+    }
+    size_t rows = 0, cols = z.H;
+    switch (which) {
+        case MOE_A_Q_PROJ: rows = 2 * z.q_dim; break;
+        case MOE_A_K_PROJ: case MOE_A_V_PROJ: rows = z.kv_dim; break;
+        case MOE_A_O_PROJ: rows = z.H; cols = z.q_dim; break;
+        case MOE_A_IN_PROJ_QKV: rows = z.conv_dim; break;
+        case MOE_A_IN_PROJ_Z: rows = z.total_value; break;
+        case MOE_A_IN_PROJ_B: case MOE_A_IN_PROJ_A: rows = (size_t)d.lin_num_v_heads; break;
+        default: rows = z.H; cols = z.total_value; break;  // out_proj
+    }
+    MOE_REQUIRE(dtype == MOE_DT_INT4 || dtype == MOE_DT_BF16, "%s: dtype %d not supported", attn_tensor_name(which), dtype);
+    ProjTensor& t = ls.proj[which];
+    if (t.w) { cudaFree(t.w); t = ProjTensor{}; }
+    t.dtype = dtype; t.rows = (int)rows; t.cols = (int)cols;
+    if (dtype == MOE_DT_BF16) {
+        MOE_CUDA(cudaMalloc(&t.w, rows * cols * 2));
+        MOE_CUDA(cudaMemcpyAsync(t.w, w, rows * cols * 2, cudaMemcpyHostToDevice, e->stream));
+    } else {
+        MOE_REQUIRE(s && b, "%s: a 4-bit tensor needs scales and biases", attn_tensor_name(which));
+        const size_t wb = rows * cols / 2, sb = rows * (cols / 64) * 2;
+        t.s_off = al256a(wb);
+        t.b_off = t.s_off + al256a(sb);
+        MOE_CUDA(cudaMalloc(&t.w, t.b_off + al256a(sb)));
+        MOE_CUDA(cudaMemcpyAsync(t.w, w, wb, cudaMemcpyHostToDevice, e->stream));
+        MOE_CUDA(cudaMemcpyAsync(t.w + t.s_off, s, sb, cudaMemcpyHostToDevice, e->stream));
+        MOE_CUDA(cudaMemcpyAsync(t.w + t.b_off, b, sb, cudaMemcpyHostToDevice, e->stream));
+    }
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    t.loaded = true;
+    return MOE_OK;
+}
+
+static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y) {
+    if (t.dtype == MOE_DT_INT4) return launch_matvec(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols);
+    if (!e->mtp.bf_attr_set) {
+        MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
+        e->mtp.bf_attr_set = true;
+    }
+    int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
+    if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
+    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols);
+    e->launches++;
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
+// One layer's attention half on one token: h (device, [H]) -> h_mid (device, [H]) = attention(h) + h.
+static int attn_layer_step(moe_engine* e, int layer, int pos, const float* h, float* h_mid, float* scratch) {
+    ModelAttnState& a = e->attn;
+    AttnLayerState& ls = a.layers[layer];
+    const moe_model_attn_dims_t& d = a.d;
+    const AttnSizes z = attn_sizes(e);
+    const int H = (int)z.H;
+    cudaStream_t st = e->stream;
+    const size_t wide_n = 2 * z.q_dim > z.conv_dim ? 2 * z.q_dim : z.conv_dim;
+    const size_t mid_n = z.q_dim > z.total_value ? z.q_dim : z.total_value;
+    float* p = scratch;
+    auto take = [&](size_t n) { float* r = p; p += al256a(n * 4) / 4; return r; };
+    float* x = take(z.H); float* o = take(z.H);
+    float* wide = take(wide_n); float* conv_out = take(z.conv_dim);
+    float* kb = take(z.kv_dim); float* vb = take(z.kv_dim);
+    float* zb = take(mid_n); float* vals = take(mid_n); float* normed = take(mid_n);
+    float* qr = take(z.q_dim); float* ab = take((size_t)d.lin_num_v_heads); float* bb = take((size_t)d.lin_num_v_heads);
+    auto need = [&](int which) -> bool {
+        const bool ok = attn_is_proj(which) ? ls.proj[which].loaded : ls.vec[which] != nullptr;
+        if (!ok) set_error("layer %d: the attention half is not loaded (%s missing)", layer, attn_tensor_name(which));
+        return ok;
+    };
+    if (!need(MOE_A_INPUT_NORM)) return MOE_ERR_STATE;
+    rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x);
+    e->launches++;
+    int rc;
+    if (ls.full) {
+        for (int w : {MOE_A_Q_PROJ, MOE_A_K_PROJ, MOE_A_V_PROJ, MOE_A_Q_NORM, MOE_A_K_NORM, MOE_A_O_PROJ})
+            if (!need(w)) return MOE_ERR_STATE;
+        const int nh = d.full.num_heads, nkv = d.full.num_kv_heads, hd = d.full.head_dim;
+        if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, wide))) return rc;  // [head, gate] per head
+        if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb))) return rc;
+        attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(wide, 2 * hd, 1, kb, vb, (const uint16_t*)ls.vec[MOE_A_Q_NORM],
+                                                              (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd, d.full.rotary_dim, pos,
+                                                              d.full.rope_theta, qr, ls.k_cache, ls.v_cache);
+        const int seq = pos + 1;
+        attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, wide + hd, 2 * hd, nh, nkv, hd, seq,
+                                                                   1.0f / sqrtf((float)hd), vals);
+        e->launches += 2;
+        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, o))) return rc;
+    } else {
+        for (int w : {MOE_A_IN_PROJ_QKV, MOE_A_IN_PROJ_Z, MOE_A_IN_PROJ_B, MOE_A_IN_PROJ_A, MOE_A_OUT_PROJ})
+            if (!need(w)) return MOE_ERR_STATE;
+        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, wide))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab))) return rc;
+        const float* qkv = wide;
+        if (ls.vec[MOE_A_CONV1D]) {  // without a conv weight the projection passes through (cpu.rs:261-263)
+            conv1d_step_kernel<<<(int)((z.conv_dim + 255) / 256), 256, 0, st>>>(ls.conv_state, wide, (const uint16_t*)ls.vec[MOE_A_CONV1D],
+                                                                             conv_out, (int)z.conv_dim, d.conv_kernel);
+            e->launches++;
+            qkv = conv_out;
+        }
+        float* qkv_w = const_cast<float*>(qkv);
+        lin_qk_norm_kernel<<<2 * d.lin_num_k_heads, 128, 0, st>>>(qkv_w, (int)z.total_key, d.lin_key_dim);
+        const int rows = d.lin_num_v_heads * d.lin_value_dim;
+        delta_step_kernel<<<(rows + 7) / 8, 256, 0, st>>>(ls.ssm_state, qkv_w, qkv_w + z.total_key, qkv_w + 2 * z.total_key, ab, bb,
+                                                          (const float*)ls.vec[MOE_A_A_LOG], (const uint16_t*)ls.vec[MOE_A_DT_BIAS], vals,
+                                                          d.lin_num_v_heads, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim,
+                                                          d.lin_value_dim);
+        gated_rms_norm_kernel<<<d.lin_num_v_heads, 128, 0, st>>>(vals, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM], normed, d.lin_value_dim);
+        e->launches += 3;
+        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, o))) return rc;
+    }
+    add_rows_kernel<<<(H + 255) / 256, 256, 0, st>>>(o, h, H, h_mid);
+    e->launches++;
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
+int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev) {
+    ModelAttnState& a = e->attn;
+    if (!a.configured) {
+        set_error("the attention halves are not configured (moe_attn_configure)");
+        return MOE_ERR_STATE;
+    }
+    if (a.pos + n > a.d.full.max_seq) {
+        set_error("the KV caches hold %d positions: %lld + %d tokens do not fit", a.d.full.max_seq, (long long)a.pos, n);
+        return MOE_ERR_STATE;
+    }
+    const size_t H = (size_t)e->dims.hidden;
+    float* h_mid = a.work;
+    float* ping = a.work + al256a(H * 4) / 4;
+    float* pong = ping + al256a(H * 4) / 4;
+    float* scratch = pong + al256a(H * 4) / 4;
+    for (int t = 0; t < n; ++t) {
+        const float* cur = emb_dev + (size_t)t * H;
+        for (int l = 0; l < e->dims.num_layers; ++l) {
+            int rc = attn_layer_step(e, l, (int)a.pos, cur, h_mid, scratch);
+            if (rc) return rc;
+            float* nxt = (l == e->dims.num_layers - 1) ? out_dev + (size_t)t * H : ((l & 1) ? pong : ping);
+            rc = launch_decode(e, l, l + 1, h_mid, nxt, nullptr, nullptr, nullptr, nullptr);
+            if (rc) return rc;
+            cur = nxt;
+        }
+        a.pos++;
+    }
     return MOE_OK;
 }
 

@@ -158,6 +158,24 @@ struct MtpAttnState {
     bool bf_attr_set = false;
 };
 
+// The attention half of the main layers (attn.cu): per-layer tensors and caches, one scratch area.
+struct AttnLayerState {
+    bool full = false;
+    void* vec[16] = {};            // norm weights, conv1d, dt_bias (bf16) and A_log (f32) by moe_attn_tensor_t
+    ProjTensor proj[16];           // projections by moe_attn_tensor_t
+    float* k_cache = nullptr;      // full attention: [max_seq, kv_dim] each
+    float* v_cache = nullptr;
+    float* conv_state = nullptr;   // linear attention: [conv_kernel - 1, conv_dim]
+    float* ssm_state = nullptr;    // linear attention: [v_heads, value_dim, key_dim]
+};
+struct ModelAttnState {
+    moe_model_attn_dims_t d{};
+    bool configured = false;
+    std::vector<AttnLayerState> layers;
+    float* work = nullptr;
+    int64_t pos = 0;
+};
+
 }  // namespace moe
 
 struct moe_engine {
@@ -207,6 +225,7 @@ struct moe_engine {
 
     moe::HeadState head;
     moe::MtpAttnState mtp;
+    moe::ModelAttnState attn;
 };
 
 namespace moe {
@@ -244,6 +263,12 @@ int mtp_configure(moe_engine* e, const moe_attn_dims_t* ad);
 int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, const void* b, int dtype);
 int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits_dev);
 void mtp_destroy(moe_engine* e);
+int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims);
+int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const void* s, const void* b, int dtype);
+// n decode steps with attention, enqueued: emb_dev [n, hidden] -> out_dev [n, hidden]; advances the position
+int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev);
+int attn_reset(moe_engine* e);
+void attn_destroy(moe_engine* e);
 int head_reserve(moe_engine* e, int32_t n);
 void head_destroy(moe_engine* e);
 int refresh_layer_table(moe_engine* e);

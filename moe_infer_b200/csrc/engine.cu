@@ -291,6 +291,7 @@ void moe_engine_destroy(moe_engine_t* e) {
     batch_destroy(e);
     head_destroy(e);
     mtp_destroy(e);
+    attn_destroy(e);
     if (e->layers_dev) cudaFree(e->layers_dev);
     if (e->io_dev) cudaFree(e->io_dev);
     if (e->ev0) cudaEventDestroy(e->ev0);
@@ -870,6 +871,84 @@ int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, fl
     rc = poll_device_error(e);
     if (rc == MOE_OK) e->mtp_pos++;
     return rc;
+}
+
+int moe_attn_configure(moe_engine_t* e, const moe_model_attn_dims_t* dims) {
+    MOE_REQUIRE(e && dims, "null argument");
+    return attn_configure(e, dims);
+}
+
+int moe_attn_load_tensor(moe_engine_t* e, int layer, int which, const void* w, const void* s, const void* b, int dtype) {
+    MOE_REQUIRE(e, "null engine");
+    return attn_load_tensor(e, layer, which, w, s, b, dtype);
+}
+
+int moe_model_reset(moe_engine_t* e) {
+    MOE_REQUIRE(e, "null engine");
+    int rc = attn_reset(e);
+    if (rc) return rc;
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    return MOE_OK;
+}
+
+int moe_model_pos(const moe_engine_t* e, int64_t* pos) {
+    MOE_REQUIRE(e && pos, "null argument");
+    *pos = e->attn.pos;
+    return MOE_OK;
+}
+
+// n decode steps with attention; ids != null: embed first and return logits, else emb in and hidden states out
+static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, int32_t n, float* out, bool logits) {
+    MOE_REQUIRE(n >= 0, "negative token count");
+    if (n == 0) return MOE_OK;
+    const moe_dims_t& d = e->dims;
+    const size_t hb = align_up((size_t)n * d.hidden * 4, 256), lb = logits ? align_up((size_t)n * d.vocab * 4, 256) : 0;
+    int rc = io_reserve(e, 2 * hb + lb);
+    if (rc) return rc;
+    float* d_in = (float*)e->io_dev;
+    float* d_out = (float*)(e->io_dev + hb);
+    float* d_l = (float*)(e->io_dev + 2 * hb);
+    const int64_t pos0 = e->attn.pos;
+    do {
+        if (ids) {
+            if ((rc = head_reserve(e, n))) break;
+            cudaError_t ce = cudaMemcpyAsync(e->head.ids, ids, (size_t)n * 8, cudaMemcpyHostToDevice, e->stream);
+            if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward upload", __FILE__, __LINE__); break; }
+            if ((rc = launch_embed(e, e->head.ids, n, d_in))) break;
+        } else {
+            cudaError_t ce = cudaMemcpyAsync(d_in, emb, (size_t)n * d.hidden * 4, cudaMemcpyHostToDevice, e->stream);
+            if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward upload", __FILE__, __LINE__); break; }
+        }
+        if ((rc = attn_model_forward(e, d_in, n, d_out))) break;
+        cudaError_t ce;
+        if (logits) {
+            if ((rc = launch_logits(e, d_out, n, d_l))) break;
+            ce = cudaMemcpyAsync(out, d_l, (size_t)n * d.vocab * 4, cudaMemcpyDeviceToHost, e->stream);
+        } else {
+            ce = cudaMemcpyAsync(out, d_out, (size_t)n * d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
+        }
+        if (ce == cudaSuccess)
+            ce = cudaMemcpyAsync(e->stage_host, d_out + (size_t)(n - 1) * d.hidden, (size_t)d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+        if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward download", __FILE__, __LINE__); break; }
+        if ((rc = poll_device_error(e))) break;
+        memcpy(e->last_h.data(), e->stage_host, (size_t)d.hidden * 4);
+    } while (0);
+    if (rc) {
+        cudaStreamSynchronize(e->stream);
+        e->attn.pos = pos0;  // a failed call consumes no positions (the recurrence states may have moved: reset to reuse)
+    }
+    return rc;
+}
+
+int moe_model_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, float* out) {
+    MOE_REQUIRE(e && emb && out, "null argument");
+    return model_forward(e, nullptr, emb, n, out, false);
+}
+
+int moe_model_forward_host(moe_engine_t* e, const int64_t* ids, int32_t n, float* logits) {
+    MOE_REQUIRE(e && ids && logits, "null argument");
+    return model_forward(e, ids, nullptr, n, logits, true);
 }
 
 int moe_mtp_reset(moe_engine_t* e) {

@@ -283,6 +283,53 @@ class NativeEngine:
         L.check(self.lib.moe_mtp_forward_host(self.h, L.ptr(h_in), L.ptr(out)))
         return out
 
+    # ── attention halves of the main layers (batch-1 decode) ─────────────
+    def attn_configure(self, *, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, rope_theta: float,
+                       lin_num_k_heads: int, lin_num_v_heads: int, lin_key_dim: int, lin_value_dim: int, conv_kernel: int = 4,
+                       full_attn_interval: int = 4, max_seq: int = 4096) -> None:
+        d = L.ModelAttnDims(L.AttnDims(num_heads, num_kv_heads, head_dim, rotary_dim, max_seq, rope_theta), lin_num_k_heads,
+                            lin_num_v_heads, lin_key_dim, lin_value_dim, conv_kernel, full_attn_interval)
+        L.check(self.lib.moe_attn_configure(self.h, C.byref(d)))
+
+    def attn_load_vec(self, layer: int, which: int, w: np.ndarray) -> None:
+        """A norm weight, conv1d [channels, kernel] or dt_bias (bf16 bit patterns), or A_log (float32)."""
+        if which == L.A_A_LOG:
+            w = np.ascontiguousarray(w, np.float32)
+            L.check(self.lib.moe_attn_load_tensor(self.h, layer, which, L.ptr(w), None, None, L.DT_F32))
+        else:
+            w = np.ascontiguousarray(w, np.uint16)
+            L.check(self.lib.moe_attn_load_tensor(self.h, layer, which, L.ptr(w), None, None, L.DT_BF16))
+
+    def attn_load_proj(self, layer: int, which: int, t) -> None:
+        if isinstance(t, tuple):
+            w, s, b = (np.ascontiguousarray(t[0], np.uint32), np.ascontiguousarray(t[1], np.uint16),
+                       np.ascontiguousarray(t[2], np.uint16))
+            L.check(self.lib.moe_attn_load_tensor(self.h, layer, which, L.ptr(w), L.ptr(s), L.ptr(b), L.DT_INT4))
+        else:
+            w = np.ascontiguousarray(t, np.uint16)
+            L.check(self.lib.moe_attn_load_tensor(self.h, layer, which, L.ptr(w), None, None, L.DT_BF16))
+
+    def model_forward_hidden(self, emb: np.ndarray) -> np.ndarray:
+        """Embeddings [n, hidden] through attention + MoE of every layer, one decode step per token."""
+        emb = np.ascontiguousarray(emb, np.float32).reshape(-1, self.dims.hidden)
+        out = np.empty_like(emb)
+        L.check(self.lib.moe_model_forward_hidden_host(self.h, L.ptr(emb), emb.shape[0], L.ptr(out)))
+        return out
+
+    def model_forward(self, ids: np.ndarray) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.int64).reshape(-1)
+        out = np.empty((ids.size, self.dims.vocab), np.float32)
+        L.check(self.lib.moe_model_forward_host(self.h, L.ptr(ids), ids.size, L.ptr(out)))
+        return out
+
+    def model_reset(self) -> None:
+        L.check(self.lib.moe_model_reset(self.h))
+
+    def model_pos(self) -> int:
+        p = C.c_int64()
+        L.check(self.lib.moe_model_pos(self.h, C.byref(p)))
+        return p.value
+
     # ── MTP block, whole step (attention + MoE + head) ───────────────────
     def mtp_configure(self, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, rope_theta: float,
                       max_seq: int = 4096) -> None:

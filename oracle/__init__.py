@@ -365,3 +365,114 @@ def mtp_step(mw: "MtpWeights", moe: "LayerWeights", top_k: int, embed_q4, lm_hea
     if isinstance(lm_head, tuple) and len(lm_head) == 2:
         return matvec_int8(lm_head[0], lm_head[1], out)
     return matvec_int4(*lm_head, out)
+
+
+# ── the main model's attention layers (reference src/engine/qwen35_moe/cpu.rs:87-347) ──────────────────────────
+
+class AttnDims:
+    def __init__(self, *, num_heads, num_kv_heads, head_dim, rotary_dim, rope_theta, lin_num_k_heads, lin_num_v_heads,
+                 lin_key_dim, lin_value_dim, conv_kernel=4, full_attn_interval=4):
+        self.__dict__.update(locals())
+
+    @property
+    def total_key(self):
+        return self.lin_num_k_heads * self.lin_key_dim
+
+    @property
+    def total_value(self):
+        return self.lin_num_v_heads * self.lin_value_dim
+
+    @property
+    def conv_dim(self):
+        return 2 * self.total_key + self.total_value
+
+
+class FullAttnWeights:
+    """input_norm / q_norm / k_norm: bf16 bits; projections: bf16 bits [out, in] or 4-bit triples."""
+
+    def __init__(self, *, input_norm, q_proj, k_proj, v_proj, q_norm, k_norm, o_proj):
+        self.__dict__.update(locals())
+
+
+class LinAttnWeights:
+    """input_norm, dt_bias, norm: bf16 bits; conv1d: bf16 bits [channels, kernel]; a_log: f32; projections as above."""
+
+    def __init__(self, *, input_norm, in_proj_qkv, in_proj_z, in_proj_b, in_proj_a, conv1d, a_log, dt_bias, norm, out_proj):
+        self.__dict__.update(locals())
+
+
+def full_attn_block(w: FullAttnWeights, ad: AttnDims, hidden, pos: int, k_cache, v_cache) -> np.ndarray:
+    """pre_expert_full up to the residual (cpu.rs:87-183): returns h_mid = o_proj(...) + hidden."""
+    hidden = _c(hidden, np.float32)
+    nh, nkv, hd = ad.num_heads, ad.num_kv_heads, ad.head_dim
+    x = final_norm(hidden, w.input_norm)
+    q = _project(w.q_proj, x)          # [head, gate] per head
+    k = _project(w.k_proj, x)
+    v = _project(w.v_proj, x)
+    q_out = np.empty(nh * hd, np.float32)
+    k_out = np.empty(nkv * hd, np.float32)
+    lib().orc_head_norm_rope_split(_p(q), 2 * hd, _p(_c(w.q_norm, np.uint16)), _p(q_out), nh, hd, ad.rotary_dim,
+                                   C.c_float(ad.rope_theta), pos, C.c_float(1e-6))
+    lib().orc_head_norm_rope_split(_p(k), hd, _p(_c(w.k_norm, np.uint16)), _p(k_out), nkv, hd, ad.rotary_dim,
+                                   C.c_float(ad.rope_theta), pos, C.c_float(1e-6))
+    gate = q.reshape(nh, 2 * hd)[:, hd:].reshape(-1)
+    k_cache[pos] = k_out
+    v_cache[pos] = v
+    att = attention(q_out, k_cache, v_cache, nh, nkv, hd, pos + 1)
+    gated = (att * (np.float32(1.0) / (np.float32(1.0) + np.exp(-gate)))).astype(np.float32)
+    return (_project(w.o_proj, gated) + hidden).astype(np.float32)
+
+
+def linear_attn_block(w: LinAttnWeights, ad: AttnDims, hidden, conv_state, ssm_state) -> np.ndarray:
+    """pre_expert_linear up to the residual (cpu.rs:218-347); conv_state [kernel - 1, channels] and
+    ssm_state [v_heads, value_dim, key_dim] are updated in place."""
+    hidden = _c(hidden, np.float32)
+    x = final_norm(hidden, w.input_norm)
+    qkv = _project(w.in_proj_qkv, x)
+    z = _project(w.in_proj_z, x)
+    beta = _project(w.in_proj_b, x)
+    alpha = _project(w.in_proj_a, x)
+    conv_out = np.empty_like(qkv)
+    conv_w = _c(w.conv1d, np.uint16)
+    lib().orc_conv1d_step(_p(conv_state), _p(qkv), _p(conv_w), _p(conv_out), ad.conv_dim, ad.conv_kernel)
+    lib().orc_lin_qk_norm(_p(conv_out), ad.total_key, ad.lin_num_k_heads, ad.lin_key_dim)
+    out = np.empty(ad.total_value, np.float32)
+    a_log = _c(w.a_log, np.float32)
+    dt_bias = _c(w.dt_bias, np.uint16)
+    qn, kn, vv = conv_out[:ad.total_key], conv_out[ad.total_key:2 * ad.total_key], conv_out[2 * ad.total_key:]
+    lib().orc_delta_step(_p(ssm_state), _p(_c(qn, np.float32)), _p(_c(kn, np.float32)), _p(_c(vv, np.float32)), _p(alpha), _p(beta),
+                         _p(a_log), _p(dt_bias), _p(out), ad.lin_num_v_heads, ad.lin_num_v_heads // ad.lin_num_k_heads,
+                         ad.lin_key_dim, ad.lin_value_dim)
+    normed = np.empty_like(out)
+    lib().orc_gated_rms_norm(_p(out), _p(z), _p(_c(w.norm, np.uint16)), _p(normed), ad.lin_num_v_heads, ad.lin_value_dim,
+                             C.c_float(1e-6))
+    return (_project(w.out_proj, normed) + hidden).astype(np.float32)
+
+
+class ModelState:
+    """Per-layer caches of a decode: KV for the full-attention layers, conv + recurrence state for the others."""
+
+    def __init__(self, ad: AttnDims, num_layers: int, max_seq: int):
+        self.pos = 0
+        self.kv, self.lin = {}, {}
+        for l in range(num_layers):
+            if (l + 1) % ad.full_attn_interval == 0:
+                self.kv[l] = (np.zeros((max_seq, ad.num_kv_heads * ad.head_dim), np.float32),
+                              np.zeros((max_seq, ad.num_kv_heads * ad.head_dim), np.float32))
+            else:
+                self.lin[l] = (np.zeros((ad.conv_kernel - 1, ad.conv_dim), np.float32),
+                               np.zeros((ad.lin_num_v_heads, ad.lin_value_dim, ad.lin_key_dim), np.float32))
+
+
+def model_decode_token(attn_layers, moe_layers, ad: AttnDims, state: ModelState, h, top_k: int) -> np.ndarray:
+    """One token through every layer: attention half (full or linear by position in the stack), then the MoE half
+    (cpu.rs:398-483); advances the state's position."""
+    h = _c(h, np.float32)
+    for l, (aw, mw) in enumerate(zip(attn_layers, moe_layers)):
+        if l in state.kv:
+            h_mid = full_attn_block(aw, ad, h, state.pos, *state.kv[l])
+        else:
+            h_mid = linear_attn_block(aw, ad, h, *state.lin[l])
+        h = moe_layer(mw, h_mid, top_k)[0][0]
+    state.pos += 1
+    return h

@@ -668,3 +668,105 @@ void orc_attention(const float* q, const float* k_cache, const float* v_cache, i
     }
     free(scores);
 }
+
+/* ─── main-model attention layers (reference src/engine/qwen35_moe/cpu.rs:87-347, src/math_util.rs) ─── */
+
+/* q_head_norm_rope / k_head_norm_rope: src/math_util.rs:501-597.  Per-head RMS norm with a bf16 weight, then RoPE on
+ * the pairs (d, d + rotary_dim / 2).  src holds `num_heads` heads `stride` floats apart; out is dense. */
+void orc_head_norm_rope_split(const float* src, int stride, const uint16_t* norm_w, float* out, int num_heads,
+                              int head_dim, int rotary_dim, float rope_theta, int pos, float eps) {
+    const int rot_half = rotary_dim / 2;
+    for (int h = 0; h < num_heads; ++h) {
+        const float* x = src + (size_t)h * stride;
+        float* o = out + (size_t)h * head_dim;
+        float sum_sq = 0.0f;
+        for (int d = 0; d < head_dim; ++d) sum_sq += x[d] * x[d];
+        const float inv_rms = 1.0f / sqrtf(sum_sq / (float)head_dim + eps);
+        for (int d = 0; d < head_dim; ++d) {
+            const float val = x[d] * inv_rms * orc_bf16_to_f32(norm_w[d]);
+            if (d < rotary_dim) {
+                const int pair = d < rot_half ? d : d - rot_half;
+                const int other = d < rot_half ? d + rot_half : d - rot_half;
+                const float theta = (float)pos * powf(rope_theta, -2.0f * (float)pair / (float)rotary_dim);
+                const float pair_val = x[other] * inv_rms * orc_bf16_to_f32(norm_w[other]);
+                const float cos_t = cosf(theta), sin_t = sinf(theta);
+                o[d] = d < rot_half ? val * cos_t - pair_val * sin_t : pair_val * sin_t + val * cos_t;
+            } else {
+                o[d] = val;
+            }
+        }
+    }
+}
+
+/* conv1d_step + the state shift that follows it: src/math_util.rs:149-168, cpu.rs:263-275. */
+void orc_conv1d_step(float* conv_state, const float* x, const uint16_t* w, float* out, int channels, int ksize) {
+    for (int c = 0; c < channels; ++c) {
+        float acc = 0.0f;
+        for (int k = 0; k < ksize - 1; ++k) acc += conv_state[(size_t)k * channels + c] * orc_bf16_to_f32(w[(size_t)c * ksize + k]);
+        acc += x[c] * orc_bf16_to_f32(w[(size_t)c * ksize + ksize - 1]);
+        out[c] = acc;
+    }
+    for (int c = 0; c < channels; ++c) out[c] = out[c] / (1.0f + expf(-out[c]));
+    for (int k = 0; k + 2 < ksize; ++k) memcpy(conv_state + (size_t)k * channels, conv_state + (size_t)(k + 1) * channels, sizeof(float) * (size_t)channels);
+    if (ksize >= 2) memcpy(conv_state + (size_t)(ksize - 2) * channels, x, sizeof(float) * (size_t)channels);
+}
+
+/* cpu.rs:277-299: unweighted per-head RMS norm of q and k, q scaled by inv_scale^2 and k by inv_scale. */
+void orc_lin_qk_norm(float* qkv, int total_key, int num_k_heads, int key_dim) {
+    const float inv_scale = 1.0f / sqrtf((float)key_dim);
+    for (int h = 0; h < num_k_heads; ++h) {
+        float* q = qkv + (size_t)h * key_dim;
+        float* k = qkv + total_key + (size_t)h * key_dim;
+        float q_sq = 0.0f, k_sq = 0.0f;
+        for (int d = 0; d < key_dim; ++d) q_sq += q[d] * q[d];
+        for (int d = 0; d < key_dim; ++d) k_sq += k[d] * k[d];
+        const float q_inv = 1.0f / sqrtf(q_sq / (float)key_dim + 1e-6f), k_inv = 1.0f / sqrtf(k_sq / (float)key_dim + 1e-6f);
+        for (int d = 0; d < key_dim; ++d) {
+            q[d] = q[d] * q_inv * inv_scale * inv_scale;
+            k[d] = k[d] * k_inv * inv_scale;
+        }
+    }
+}
+
+/* compute_decay_beta + gated_delta_net_step: src/math_util.rs:401-466. */
+void orc_delta_step(float* state, const float* q, const float* k, const float* v, const float* alpha, const float* beta,
+                    const float* a_log, const uint16_t* dt_bias, float* out, int num_v_heads, int k_heads_per_v,
+                    int key_dim, int value_dim) {
+    for (int h = 0; h < num_v_heads; ++h) {
+        const float a = expf(a_log[h]);
+        const float softplus = logf(1.0f + expf(alpha[h] + orc_bf16_to_f32(dt_bias[h])));
+        const float g = expf(-a * softplus);
+        const float bgate = 1.0f / (1.0f + expf(-beta[h]));
+        const int kh = h / k_heads_per_v;
+        const float* kk = k + (size_t)kh * key_dim;
+        const float* qq = q + (size_t)kh * key_dim;
+        for (int vi = 0; vi < value_dim; ++vi) {
+            float* row = state + ((size_t)h * value_dim + vi) * key_dim;
+            float kv_mem = 0.0f;
+            for (int ki = 0; ki < key_dim; ++ki) {
+                const float s = row[ki] * g;
+                row[ki] = s;
+                kv_mem += s * kk[ki];
+            }
+            const float delta = (v[(size_t)h * value_dim + vi] - kv_mem) * bgate;
+            for (int ki = 0; ki < key_dim; ++ki) row[ki] += kk[ki] * delta;
+            float o = 0.0f;
+            for (int ki = 0; ki < key_dim; ++ki) o += row[ki] * qq[ki];
+            out[(size_t)h * value_dim + vi] = o;
+        }
+    }
+}
+
+/* gated_rms_norm: src/math_util.rs:472-493. */
+void orc_gated_rms_norm(const float* vals, const float* z, const uint16_t* w, float* out, int num_heads, int value_dim, float eps) {
+    for (int h = 0; h < num_heads; ++h) {
+        const float* x = vals + (size_t)h * value_dim;
+        float sum_sq = 0.0f;
+        for (int d = 0; d < value_dim; ++d) sum_sq += x[d] * x[d];
+        const float inv_rms = 1.0f / sqrtf(sum_sq / (float)value_dim + eps);
+        for (int d = 0; d < value_dim; ++d) {
+            const float zv = z[(size_t)h * value_dim + d];
+            out[(size_t)h * value_dim + d] = x[d] * inv_rms * (zv / (1.0f + expf(-zv))) * orc_bf16_to_f32(w[d]);
+        }
+    }
+}

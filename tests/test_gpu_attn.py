@@ -1,0 +1,114 @@
+"""GPU parity of the main layers' attention halves (gated full attention and Gated DeltaNet, batch-1 decode) with the
+MoE half behind each, against the CPU oracle's restatement of src/engine/qwen35_moe/cpu.rs:87-347 and
+src/math_util.rs:149-168, 401-597, through the C ABI.
+
+A 4-layer stack (three linear-attention layers and one full-attention layer, as the model's interval of 4 arranges
+them) is stepped over several tokens so that the KV cache, the conv state and the recurrence state all carry over;
+both storage variants of the projections; reset; error paths.  Tolerance 1e-2 relative L2 (achieved values printed).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from benchmarks import synth
+from moe_infer_b200 import _lib as L
+from moe_infer_b200.native import Dims, NativeEngine
+from tests.util import make_layer, rel_l2, upload_layer
+
+pytestmark = pytest.mark.gpu
+H, V, E, K = 2048, 200, 16, 8
+AD = dict(num_heads=4, num_kv_heads=2, head_dim=64, rotary_dim=16, rope_theta=1.0e7, lin_num_k_heads=2, lin_num_v_heads=4,
+          lin_key_dim=32, lin_value_dim=64, conv_kernel=4, full_attn_interval=4)
+
+
+def _attn_weights(seed, scheme, layers):
+    ad = oracle.AttnDims(**AD)
+    rng = np.random.default_rng(seed)
+    bf = lambda a: oracle.f32_to_bf16(np.asarray(a, np.float32))
+    f = oracle.bf16_to_f32
+    norm = lambda n: bf(rng.uniform(0.8, 1.2, n))
+    q4 = lambda r, c, gain=2.0: oracle.quant_int4(f(bf(synth.normal_weights(rng, (r, c)) * gain)))
+
+    def attn_proj(r, c):  # bf16 in the BQ4 scheme, 4-bit in the INT4 scheme (bq4.rs:25-32)
+        m = f(bf(synth.normal_weights(rng, (r, c)) * 2.0))
+        return oracle.quant_int4(m) if scheme == "int4" else bf(m)
+
+    q_dim, kv_dim = ad.num_heads * ad.head_dim, ad.num_kv_heads * ad.head_dim
+    out = []
+    for l in range(layers):
+        if (l + 1) % ad.full_attn_interval == 0:
+            out.append(oracle.FullAttnWeights(input_norm=norm(H), q_proj=attn_proj(2 * q_dim, H), k_proj=attn_proj(kv_dim, H),
+                                              v_proj=attn_proj(kv_dim, H), q_norm=norm(ad.head_dim), k_norm=norm(ad.head_dim),
+                                              o_proj=attn_proj(H, q_dim)))
+        else:
+            out.append(oracle.LinAttnWeights(
+                input_norm=norm(H), in_proj_qkv=q4(ad.conv_dim, H), in_proj_z=q4(ad.total_value, H), in_proj_b=q4(ad.lin_num_v_heads, H),
+                in_proj_a=q4(ad.lin_num_v_heads, H), conv1d=bf(rng.standard_normal((ad.conv_dim, ad.conv_kernel)) * 0.5),
+                a_log=rng.uniform(-1.0, 1.0, ad.lin_num_v_heads).astype(np.float32), dt_bias=bf(rng.uniform(-1.0, 1.0, ad.lin_num_v_heads)),
+                norm=norm(ad.lin_value_dim), out_proj=q4(H, ad.total_value)))
+    return ad, out
+
+
+def _upload_attn(eng, attn_layers, max_seq=16):
+    eng.attn_configure(max_seq=max_seq, **AD)
+    for l, w in enumerate(attn_layers):
+        eng.attn_load_vec(l, L.A_INPUT_NORM, w.input_norm)
+        if isinstance(w, oracle.FullAttnWeights):
+            eng.attn_load_vec(l, L.A_Q_NORM, w.q_norm)
+            eng.attn_load_vec(l, L.A_K_NORM, w.k_norm)
+            for which, t in ((L.A_Q_PROJ, w.q_proj), (L.A_K_PROJ, w.k_proj), (L.A_V_PROJ, w.v_proj), (L.A_O_PROJ, w.o_proj)):
+                eng.attn_load_proj(l, which, t)
+        else:
+            for which, v in ((L.A_CONV1D, w.conv1d), (L.A_A_LOG, w.a_log), (L.A_DT_BIAS, w.dt_bias), (L.A_LIN_NORM, w.norm)):
+                eng.attn_load_vec(l, which, v)
+            for which, t in ((L.A_IN_PROJ_QKV, w.in_proj_qkv), (L.A_IN_PROJ_Z, w.in_proj_z), (L.A_IN_PROJ_B, w.in_proj_b),
+                             (L.A_IN_PROJ_A, w.in_proj_a), (L.A_OUT_PROJ, w.out_proj)):
+                eng.attn_load_proj(l, which, t)
+
+
+@pytest.mark.parametrize("scheme", ["bq4", "int4"])
+def test_decode_with_attention_matches_oracle(scheme):
+    layers = 4
+    ad, attn = _attn_weights(51, scheme, layers)
+    moe = [make_layer(51, l, num_experts=E, scheme=scheme) for l in range(layers)]
+    eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=layers, vocab=V, scheme=L.SCHEME_INT4 if scheme == "int4" else L.SCHEME_BQ4))
+    for l in range(layers):
+        upload_layer(eng, l, moe[l])
+    _upload_attn(eng, attn)
+    emb = synth.hidden_states(51, 2, 6, H)
+    state = oracle.ModelState(ad, layers, 16)
+    want = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb[t], K) for t in range(6)])
+    got = np.concatenate([eng.model_forward_hidden(emb[:1]), eng.model_forward_hidden(emb[1:4]), eng.model_forward_hidden(emb[4:])])
+    errs = [rel_l2(got[t], want[t]) for t in range(6)]
+    print(f"decode with attention, {scheme}: rel-L2 per token {['%.1e' % x for x in errs]}")
+    assert max(errs) < 1e-2 and eng.model_pos() == 6
+    assert rel_l2(got - emb, want - emb) < 1e-2     # the layers' updates themselves, without the residual stream
+    # a new sequence: the caches and recurrence states start from zero again
+    eng.model_reset()
+    state = oracle.ModelState(ad, layers, 16)
+    again = eng.model_forward_hidden(emb[2:4])
+    want2 = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb[t], K) for t in (2, 3)])
+    assert rel_l2(again, want2) < 1e-2 and eng.model_pos() == 2
+    eng.close()
+
+
+def test_attention_error_paths():
+    layers = 4
+    ad, attn = _attn_weights(52, "bq4", layers)
+    eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=layers, vocab=V))
+    emb = synth.hidden_states(52, 2, 3, H)
+    with pytest.raises(L.MoeError, match="not configured"):
+        eng.model_forward_hidden(emb)
+    with pytest.raises(L.MoeError, match="must come before"):
+        eng.attn_load_vec(0, L.A_INPUT_NORM, attn[0].input_norm)
+    eng.attn_configure(max_seq=2, **AD)
+    with pytest.raises(ValueError, match="full-attention layer"):
+        eng.attn_load_vec(3, L.A_CONV1D, attn[0].conv1d)      # layer 3 is the full-attention one
+    with pytest.raises(ValueError, match="linear-attention layer"):
+        eng.attn_load_proj(0, L.A_Q_PROJ, attn[3].q_proj)
+    with pytest.raises(L.MoeError, match="input_layernorm missing"):
+        eng.model_forward_hidden(emb[:1])
+    assert eng.model_pos() == 0
+    with pytest.raises(L.MoeError, match="do not fit"):
+        eng.model_forward_hidden(emb)                           # three tokens, two positions
+    eng.close()
