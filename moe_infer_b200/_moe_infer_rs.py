@@ -133,6 +133,7 @@ class Engine:
                 self._load_layer(l, f"model.layers.{l}" if l < layers else f"mtp.layers.{l - layers}")
             self._missing_head = self._load_head()
             self._missing_mtp = self._load_mtp() if mtp else ["an MTP layer (mtp_num_hidden_layers == 0)"]
+            self._missing_attn = self._load_attn()
         except Exception:
             self.native.close()
             raise
@@ -159,6 +160,56 @@ class Engine:
         else:
             missing.append("lm_head")
         return missing
+
+    def _load_attn(self):
+        """The attention halves of the main layers, when the directory has the tensors of every layer
+        (src/engine/qwen35_moe/cpu.rs:87-347 names them); returns what is missing, and then attention is passed through."""
+        m, eng = self.model.inner, self.native
+        need = ("num_attention_heads", "num_key_value_heads", "head_dim")
+        if any(not m.get(k) for k in need):
+            return [" / ".join(need) + " in config.json"]
+        rope = m.get("rope_parameters") or {}
+        heads, kv_heads, head_dim = (int(m.get(k)) for k in need)
+        ad = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim,
+                  rotary_dim=int(head_dim * float(m.get("partial_rotary_factor", rope.get("partial_rotary_factor", 0.25)))),
+                  rope_theta=float(m.get("rope_theta", rope.get("rope_theta", 10_000_000.0))),
+                  lin_num_k_heads=int(m.get("linear_num_key_heads", 16)), lin_num_v_heads=int(m.get("linear_num_value_heads", 32)),
+                  lin_key_dim=int(m.get("linear_key_head_dim", 128)), lin_value_dim=int(m.get("linear_value_head_dim", 128)),
+                  conv_kernel=int(m.get("linear_conv_kernel_dim", 4)), full_attn_interval=int(m.get("full_attention_interval", 4)))
+        H = self.dims.hidden
+        q_dim, kv_dim = heads * head_dim, kv_heads * head_dim
+        total_key, total_value = ad["lin_num_k_heads"] * ad["lin_key_dim"], ad["lin_num_v_heads"] * ad["lin_value_dim"]
+        conv_dim = 2 * total_key + total_value
+        full_vecs = {L.A_Q_NORM: "self_attn.q_norm.weight", L.A_K_NORM: "self_attn.k_norm.weight"}
+        full_projs = {L.A_Q_PROJ: ("self_attn.q_proj", 2 * q_dim, H), L.A_K_PROJ: ("self_attn.k_proj", kv_dim, H),
+                      L.A_V_PROJ: ("self_attn.v_proj", kv_dim, H), L.A_O_PROJ: ("self_attn.o_proj", H, q_dim)}
+        lin_vecs = {L.A_CONV1D: "linear_attn.conv1d.weight", L.A_A_LOG: "linear_attn.A_log", L.A_DT_BIAS: "linear_attn.dt_bias",
+                    L.A_LIN_NORM: "linear_attn.norm.weight"}
+        lin_projs = {L.A_IN_PROJ_QKV: ("linear_attn.in_proj_qkv", conv_dim, H), L.A_IN_PROJ_Z: ("linear_attn.in_proj_z", total_value, H),
+                     L.A_IN_PROJ_B: ("linear_attn.in_proj_b", ad["lin_num_v_heads"], H),
+                     L.A_IN_PROJ_A: ("linear_attn.in_proj_a", ad["lin_num_v_heads"], H), L.A_OUT_PROJ: ("linear_attn.out_proj", H, total_value)}
+        plan, missing = [], []
+        for l in range(self.dims.num_layers):
+            pre = f"model.layers.{l}."
+            full = (l + 1) % ad["full_attn_interval"] == 0
+            vecs = {L.A_INPUT_NORM: "input_layernorm.weight", **(full_vecs if full else lin_vecs)}
+            for which, name in vecs.items():
+                t = m.tensor(pre + name)
+                if t is None:
+                    missing.append(pre + name)
+                plan.append((l, which, t, None))
+            for which, (base, rows, cols) in (full_projs if full else lin_projs).items():
+                w = m.tensor(pre + base + ".weight")
+                t = w.reshape(rows, cols) if (w is not None and w.dtype == np.uint16) else m.q4(pre + base)
+                if t is None:
+                    missing.append(pre + base)
+                plan.append((l, which, t, "proj"))
+        if missing:
+            return missing
+        eng.attn_configure(**ad)
+        for l, which, t, kind in plan:
+            (eng.attn_load_proj if kind else eng.attn_load_vec)(l, which, t)
+        return []
 
     def _load_mtp(self):
         """The attention half of the MTP block, when the directory has its tensors (src/engine/qwen35_moe/mtp.rs:85-216
@@ -238,6 +289,17 @@ class Engine:
         except L.MoeError as e:
             raise RuntimeError(str(e)) from e
 
+    def _sync_sequence(self, cache: Cache) -> None:
+        """The attention state lives on the device.  A cache at position 0 starts a new sequence; any other position
+        must be the one the device is at (the KV and recurrence states cannot be rebuilt from a position alone)."""
+        dev = self.native.model_pos()
+        if cache.pos == 0 and dev != 0:
+            self.native.model_reset()
+            self.pos = 0
+        elif cache.pos != dev:
+            raise RuntimeError(f"cache position {cache.pos} does not match the device state at position {dev}; "
+                               "attention state can only continue or restart")
+
     def _after(self, n: int, cache: Cache) -> None:
         self.pos += n
         cache.pos = self.pos
@@ -251,7 +313,12 @@ class Engine:
         if cache.cpu_dirty:
             self.upload_cache(cache)
         try:
-            out = self.native.forward_hidden(emb, batched=batched, mtp=mtp, check=_interrupt_pending)
+            if not self._missing_attn:
+                # the whole decoder block per layer; attention has no batched form: one decode step per token
+                self._sync_sequence(cache)
+                out = self.native.model_forward_hidden(emb)
+            else:
+                out = self.native.forward_hidden(emb, batched=batched, mtp=mtp, check=_interrupt_pending)
         except L.MoeError as e:
             raise RuntimeError(str(e)) from e
         self._after(emb.shape[0], cache)
@@ -274,7 +341,11 @@ class Engine:
         if cache.cpu_dirty:
             self.upload_cache(cache)
         try:
-            out = self.native.forward(toks, batched=batched, mtp=mtp, check=_interrupt_pending)
+            if not self._missing_attn:
+                self._sync_sequence(cache)
+                out = self.native.model_forward(toks)
+            else:
+                out = self.native.forward(toks, batched=batched, mtp=mtp, check=_interrupt_pending)
         except L.MoeError as e:
             raise RuntimeError(str(e)) from e
         self._after(toks.size, cache)
@@ -323,6 +394,8 @@ class Engine:
         return PyEngineSnapshot(self.pos, self.native.mtp_pos(), self._last_h)
 
     def restore_snapshot(self, snap: PyEngineSnapshot) -> None:
+        if not self._missing_attn and snap.pos != self.native.model_pos():
+            raise RuntimeError("the attention state on the device cannot be rolled back to an earlier position")
         self.pos = snap.pos
         self._last_h = snap.last_h_pre_norm.copy()
         self.native.mtp_rollback(snap.mtp_pos)

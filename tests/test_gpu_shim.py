@@ -249,6 +249,76 @@ def test_mtp_forward_returns_logits_when_the_block_is_complete(tmp_path, scheme)
     eng.native.close()
 
 
+@pytest.mark.parametrize("scheme", ["bq4", "int4"])
+def test_forward_runs_attention_when_the_checkpoint_has_it(tmp_path, scheme):
+    """A checkpoint with the attention tensors of every layer: quantise, load, and `forward(ids)` is the whole decoder
+    (attention half + MoE half per layer, final norm, lm_head), token by token, against the oracle."""
+    layers = 4
+    adk = dict(num_heads=4, num_kv_heads=2, head_dim=64, rotary_dim=16, rope_theta=1.0e7, lin_num_k_heads=2, lin_num_v_heads=4,
+               lin_key_dim=32, lin_value_dim=64, conv_kernel=4, full_attn_interval=4)
+    ad = oracle.AttnDims(**adk)
+    src, dst = str(tmp_path / "hf"), str(tmp_path / "out")
+    raw, head = _hf_checkpoint(src, layers=layers, mtp=0)
+    cfg = json.load(open(os.path.join(src, "config.json")))
+    cfg["text_config"].update({"num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "linear_num_key_heads": 2,
+                               "linear_num_value_heads": 4, "linear_key_head_dim": 32, "linear_value_head_dim": 64,
+                               "linear_conv_kernel_dim": 4, "full_attention_interval": 4})
+    json.dump(cfg, open(os.path.join(src, "config.json"), "w"))
+    rng = np.random.default_rng(23)
+    bf = lambda a: synth.to_bf16_rne(np.asarray(a, np.float32))
+    f = synth.bf16_to_f32
+    zc = lambda n: bf(rng.uniform(-0.2, 0.2, n))
+    mat = lambda r, c: bf(synth.normal_weights(rng, (r, c)) * 2.0)
+    q_dim, kv_dim = 256, 128
+    t, attn = {}, []
+    one = np.float32(1.0)
+    nw = lambda bits: oracle.f32_to_bf16(f(bits) + one)                       # zero-centred norms are stored as w + 1
+    q4 = lambda bits: oracle.quant_int4(f(bits))
+    pj = lambda bits: q4(bits) if scheme == "int4" else bits                  # attention projections: bf16 in BQ4
+    for l in range(layers):
+        p = f"model.language_model.layers.{l}."
+        t[p + "input_layernorm.weight"] = zc(H)
+        if l == 3:
+            w = {"q": mat(2 * q_dim, H), "k": mat(kv_dim, H), "v": mat(kv_dim, H), "o": mat(H, q_dim), "qn": zc(64), "kn": zc(64)}
+            t.update({p + "self_attn.q_proj.weight": w["q"], p + "self_attn.k_proj.weight": w["k"], p + "self_attn.v_proj.weight": w["v"],
+                      p + "self_attn.o_proj.weight": w["o"], p + "self_attn.q_norm.weight": w["qn"], p + "self_attn.k_norm.weight": w["kn"]})
+            attn.append(oracle.FullAttnWeights(input_norm=nw(t[p + "input_layernorm.weight"]), q_proj=pj(w["q"]), k_proj=pj(w["k"]),
+                                               v_proj=pj(w["v"]), q_norm=nw(w["qn"]), k_norm=nw(w["kn"]), o_proj=pj(w["o"])))
+        else:
+            w = {"qkv": mat(ad.conv_dim, H), "z": mat(ad.total_value, H), "b": mat(4, H), "a": mat(4, H),
+                 "conv": bf(rng.standard_normal((ad.conv_dim, 1, 4)) * 0.5), "alog": rng.uniform(-1, 1, 4).astype(np.float32),
+                 "dt": bf(rng.uniform(-1, 1, 4)), "norm": bf(rng.uniform(0.8, 1.2, 64)), "out": mat(H, ad.total_value)}
+            t.update({p + "linear_attn.in_proj_qkv.weight": w["qkv"], p + "linear_attn.in_proj_z.weight": w["z"],
+                      p + "linear_attn.in_proj_b.weight": w["b"], p + "linear_attn.in_proj_a.weight": w["a"],
+                      p + "linear_attn.conv1d.weight": w["conv"], p + "linear_attn.A_log": w["alog"], p + "linear_attn.dt_bias": w["dt"],
+                      p + "linear_attn.norm.weight": w["norm"], p + "linear_attn.out_proj.weight": w["out"]})
+            attn.append(oracle.LinAttnWeights(input_norm=nw(t[p + "input_layernorm.weight"]), in_proj_qkv=q4(w["qkv"]), in_proj_z=q4(w["z"]),
+                                              in_proj_b=q4(w["b"]), in_proj_a=q4(w["a"]), conv1d=w["conv"].reshape(ad.conv_dim, 4),
+                                              a_log=w["alog"], dt_bias=w["dt"], norm=w["norm"], out_proj=q4(w["out"])))
+    _write_safetensors(os.path.join(src, "model-00002-of-00002.safetensors"), t)
+    rs.qwen35_moe_quantize(src, dst, version="3.6", scheme=scheme)
+    moe = _oracle_layers(raw, scheme)
+    model = rs.Model(dst)
+    eng = rs.Engine(model, "Qwen35MoEFusedExp5")
+    cache = rs.Cache(model)
+    ids = np.array([5, 17, 3, 99, 42], np.int64)
+    got = np.concatenate([eng.forward(ids[:2], cache), eng.forward(ids[2:], cache)])
+    emb = oracle.embed_lookup(*oracle.quant_int4(head["embed"]), ids)
+    state = oracle.ModelState(ad, layers, 16)
+    hid = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb[i], K) for i in range(ids.size)])
+    want = _oracle_logits(head, scheme, hid)
+    assert got.shape == (5, V) and rel_l2(got, want) < 1e-2 and cache.pos == 5
+    assert np.array_equal(got.argmax(axis=1), want.argmax(axis=1))
+    # a fresh cache starts a new sequence on the device; a stale position is refused
+    again = eng.forward(ids[:1], rs.Cache(model))
+    assert rel_l2(again, want[:1]) < 1e-2
+    stale = rs.Cache(model)
+    stale.pos = 3
+    with pytest.raises(RuntimeError, match="does not match the device state"):
+        eng.forward(ids[:1], stale)
+    eng.native.close()
+
+
 def test_top_level_module_alias_runs_a_forward(tmp_path):
     """The reference's Python does `import _moe_infer_rs as _rs` (moe_infer/_core.py:14, pipeline.py:16): with the mirror
     registered under that name, the call sequence of pipeline.py:250-254 and :361-367 runs on the GPU."""
