@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=None, help="untimed steps (default 20; 3 for --impl reference)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode",
-                    choices=["decode", "layer", "pack", "matvec", "matvec_hbm", "lm_head", "batched64", "prefill"])
+                    choices=["decode", "layer", "pack", "matvec", "matvec_hbm", "lm_head", "full_decode", "batched64", "prefill"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--tokens", type=int, default=0, help="tokens per step for the batched workloads")
     ap.add_argument("--seed", type=int, default=0)
@@ -262,6 +262,7 @@ def run_decode(args, rank, world, local, dist):
             parity["batched64"] = {"rel_l2_vs_decode_path": secondary["batched64"]["parity_rel_l2_vs_decode_path"]}
             secondary["matvec_512x2048"] = workloads.run_matvec(args, eng, local)
             secondary["matvec_hbm"] = workloads.run_matvec(args, eng, local, rows=248320, cols=2048, copies=2)
+            secondary["full_decode"] = workloads.run_full_decode(args, eng, local)
     resident_gb = eng.resident_bytes() / 1e9
     for b in (emb_dev, out_dev):
         b.free()
@@ -316,11 +317,14 @@ def run_single(args, rank, world, local, dist):
         metric, unit, value, ms = "lm_head_GB_per_s", "GB/s", r["roofline"]["achieved"], r["us_per_call"] / 1e3
     else:
         small = name in ("matvec", "matvec_hbm")
-        dims = Dims(num_layers=1, num_experts=4, top_k=4) if small else Dims(num_layers=min(args.layers, 12))
+        dims = Dims(num_layers=1, num_experts=4, top_k=4) if small else Dims(num_layers=args.layers if name == "full_decode" else min(args.layers, 12))
         eng = NativeEngine(dims, device=local)
         if not small:
             benchlib.populate_synthetic(eng, base_seed=args.seed)
-        if name == "layer":
+        if name == "full_decode":
+            r = workloads.run_full_decode(args, eng, local)
+            metric, unit, value, ms = "decoder_decode_tokens_per_s", "tok/s", r["tok_per_s"], r["ms_per_token"]
+        elif name == "layer":
             r = workloads.run_layer(args, eng, local)
             metric, unit, value, ms = "moe_layer_decode_us", "us", r["us_per_layer"], r["us_per_layer"] / 1e3
         elif name == "batched64":

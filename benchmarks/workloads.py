@@ -314,6 +314,70 @@ def run_lm_head(args, local: int, kind: str = "int8", vocab: int = 248320) -> di
     return out
 
 
+# ─── the whole decoder: attention half + MoE half of every layer, one token ──
+
+QWEN36_ATTN = dict(num_heads=16, num_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1.0e7, lin_num_k_heads=16,
+                   lin_num_v_heads=32, lin_key_dim=128, lin_value_dim=128, conv_kernel=4, full_attn_interval=4)
+
+
+def run_full_decode(args, eng: NativeEngine, local: int) -> dict:
+    """One token through attention + MoE of every layer of `eng` (whose MoE store is populated): the model's own
+    attention shapes (10 gated full-attention layers with bf16 projections, 30 Gated DeltaNet layers with 4-bit
+    projections, as the BQ4 scheme stores them).  The same random projection values are uploaded to every layer of a
+    kind (each layer has its own device copy, so the traffic is real); context length stays below 64 positions."""
+    a = QWEN36_ATTN
+    H, n_layers = eng.dims.hidden, eng.dims.num_layers
+    rng = np.random.default_rng(args.seed + 77)
+    q_dim, kv_dim = a["num_heads"] * a["head_dim"], a["num_kv_heads"] * a["head_dim"]
+    total_key, total_value = a["lin_num_k_heads"] * a["lin_key_dim"], a["lin_num_v_heads"] * a["lin_value_dim"]
+    conv_dim = 2 * total_key + total_value
+    eng.attn_configure(max_seq=64, **a)
+    bfm = lambda r, c: synth.to_bf16_rne((rng.standard_normal((r, c)) * 0.02).astype(np.float32))
+    q4m = lambda r, c: (rng.integers(0, 2**32, size=(r, c // 8), dtype=np.uint64).astype(np.uint32),
+                        np.full((r, c // 64), 0x3B00, np.uint16), np.full((r, c // 64), 0xBC80, np.uint16))  # scale 2^-9, bias -2^-6
+    ones = lambda n: synth.to_bf16_rne(np.ones(n, np.float32))
+    full = {L.A_Q_PROJ: bfm(2 * q_dim, H), L.A_K_PROJ: bfm(kv_dim, H), L.A_V_PROJ: bfm(kv_dim, H), L.A_O_PROJ: bfm(H, q_dim)}
+    lin = {L.A_IN_PROJ_QKV: q4m(conv_dim, H), L.A_IN_PROJ_Z: q4m(total_value, H), L.A_IN_PROJ_B: q4m(a["lin_num_v_heads"], H),
+           L.A_IN_PROJ_A: q4m(a["lin_num_v_heads"], H), L.A_OUT_PROJ: q4m(H, total_value)}
+    conv = synth.to_bf16_rne((rng.standard_normal((conv_dim, a["conv_kernel"])) * 0.5).astype(np.float32))
+    attn_bytes = 0
+    for l in range(n_layers):
+        eng.attn_load_vec(l, L.A_INPUT_NORM, ones(H))
+        if (l + 1) % a["full_attn_interval"] == 0:
+            eng.attn_load_vec(l, L.A_Q_NORM, ones(a["head_dim"]))
+            eng.attn_load_vec(l, L.A_K_NORM, ones(a["head_dim"]))
+            for which, t in full.items():
+                eng.attn_load_proj(l, which, t)
+                attn_bytes += t.nbytes
+        else:
+            eng.attn_load_vec(l, L.A_CONV1D, conv)
+            eng.attn_load_vec(l, L.A_A_LOG, np.zeros(a["lin_num_v_heads"], np.float32))
+            eng.attn_load_vec(l, L.A_DT_BIAS, synth.to_bf16_rne(np.zeros(a["lin_num_v_heads"], np.float32)))
+            eng.attn_load_vec(l, L.A_LIN_NORM, ones(a["lin_value_dim"]))
+            for which, t in lin.items():
+                eng.attn_load_proj(l, which, t)
+                attn_bytes += sum(x.nbytes for x in t)
+            attn_bytes += 2 * total_value * a["lin_key_dim"] * 4  # the recurrence state is read and written
+    emb = synth.hidden_states(args.seed, 2, 8, H)
+    out = np.empty((1, H), np.float32)
+
+    def step(i):
+        if eng.model_pos() >= 60:
+            eng.model_reset()
+        L.check(eng.lib.moe_model_forward_hidden_host(eng.h, L.ptr(emb[i % 8:i % 8 + 1]), 1, L.ptr(out)))
+
+    t = timed_repeats(eng, step, max(3, min(args.warmup, 5)), max(1, min(args.steps, 10)))
+    moe_bytes = benchlib.layer_token_bytes(eng.dims) * n_layers
+    res = {"workload": f"whole decoder, 1 token x {n_layers} layers: attention half (10 full-attention layers with bf16 projections, "
+                       "30 Gated DeltaNet layers with 4-bit projections; Qwen3.6-35B-A3B head counts) + MoE half, host buffers, "
+                       "context below 64 positions",
+           "ms_per_token": t["ms_per_step"], "tok_per_s": 1e3 / t["ms_per_step"], "repeats": t["repeats"],
+           "gpu_launches": t["launches"], "finite": bool(np.isfinite(out).all()),
+           "attention_MB_per_token": attn_bytes / 1e6, "moe_MB_per_token": moe_bytes / 1e6,
+           "roofline": hbm_roofline("attention kernels + decode_slots_kernel per layer", attn_bytes + moe_bytes, t["ms_per_step"])}
+    return res
+
+
 # ─── config 1 on the GPU, and the matvec at HBM size ──────────────────────────
 
 def run_matvec(args, eng: NativeEngine, local: int, rows: int = 512, cols: int = 2048, copies: int = 512) -> dict:
