@@ -77,8 +77,10 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
                                                         const float* __restrict__ k,
                                                         const float* __restrict__ v, const uint16_t* __restrict__ q_norm,
                                                         const uint16_t* __restrict__ k_norm, int num_heads, int num_kv_heads,
-                                                        int head_dim, int rope_dim, int pos, float theta, float* __restrict__ q_out,
+                                                        int head_dim, int rope_dim, int pos_value, const int* __restrict__ pos_ptr,
+                                                        float theta, float* __restrict__ q_out,
                                                         float* __restrict__ k_cache, float* __restrict__ v_cache) {
+    const int pos = pos_ptr ? *pos_ptr : pos_value;  // a device-side position keeps the launch replayable (CUDA graph)
     extern __shared__ float hv[];  // the normed head
     __shared__ float red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -126,8 +128,9 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
 // across the head).  out = attention * sigmoid(gate).
 __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, const float* __restrict__ gate,
-                                                          int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_len,
-                                                          float kq_scale, float* __restrict__ out) {
+                                                          int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_value,
+                                                          const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out) {
+    const int seq_len = pos_ptr ? *pos_ptr + 1 : seq_value;
     extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head
     __shared__ float red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -453,9 +456,9 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     if ((rc = mtp_project(e, MOE_M_K_PROJ, x, k))) return rc;
     if ((rc = mtp_project(e, MOE_M_V_PROJ, x, v))) return rc;
     attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
-                                                          m.ad.rotary_dim, pos, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
+                                                          m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
     const int seq = pos + 1;
-    attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq,
+    attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
                                                                1.0f / sqrtf((float)hd), gated);
     e->launches += 2;
     if ((rc = mtp_project(e, MOE_M_O_PROJ, gated, o))) return rc;
@@ -485,8 +488,22 @@ static bool attn_is_proj(int which) {
 }
 static bool attn_role_is_full(int which) { return which >= MOE_A_Q_PROJ && which <= MOE_A_O_PROJ; }
 
+static void attn_drop_graphs(moe_engine* e) {
+    ModelAttnState& a = e->attn;
+    for (cudaGraphExec_t g : a.graphs)
+        if (g) cudaGraphExecDestroy(g);
+    a.graphs.clear();
+    a.graph_nodes.clear();
+    a.graphs_valid = false;
+}
+
+__global__ void set_pos_kernel(int* p, int v) { *p = v; }
+
 void attn_destroy(moe_engine* e) {
     ModelAttnState& a = e->attn;
+    attn_drop_graphs(e);
+    if (a.d_pos) cudaFree(a.d_pos);
+    a.d_pos = nullptr;
     for (AttnLayerState& ls : a.layers) {
         for (int i = 0; i < 16; ++i) {
             if (ls.vec[i]) cudaFree(ls.vec[i]);
@@ -571,6 +588,12 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
     size_t bytes = 5 * al256a(z.H * 4) + al256a(wide * 4) + al256a(z.conv_dim * 4) + 2 * al256a(z.kv_dim * 4) + 3 * al256a(mid * 4) +
                    al256a(z.q_dim * 4) + 2 * al256a((size_t)dims->lin_num_v_heads * 4);
     MOE_CUDA(cudaMalloc(&a.work, bytes));
+    MOE_CUDA(cudaMalloc(&a.d_pos, 256));
+    // function attributes are set here, never between the launches of a layer (those are captured into graphs)
+    MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
+    e->mtp.bf_attr_set = true;
+    int rc = matvec_prepare(e);
+    if (rc) return rc;
     a.configured = true;
     return attn_reset(e);
 }
@@ -585,6 +608,7 @@ int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const v
     MOE_REQUIRE(which >= 0 && which <= MOE_A_OUT_PROJ, "unknown attention tensor %d", which);
     MOE_REQUIRE(w, "%s: null weight pointer", attn_tensor_name(which));
     AttnLayerState& ls = a.layers[layer];
+    attn_drop_graphs(e);  // captured launches hold the old pointers
     MOE_REQUIRE(which == MOE_A_INPUT_NORM || attn_role_is_full(which) == ls.full, "layer %d is a %s layer: it has no %s", layer,
                 ls.full ? "full-attention" : "linear-attention", attn_tensor_name(which));
     const AttnSizes z = attn_sizes(e);
@@ -653,7 +677,7 @@ static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y
 }
 
 // One layer's attention half on one token: h (device, [H]) -> h_mid (device, [H]) = attention(h) + h.
-static int attn_layer_step(moe_engine* e, int layer, int pos, const float* h, float* h_mid, float* scratch) {
+static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch) {
     ModelAttnState& a = e->attn;
     AttnLayerState& ls = a.layers[layer];
     const moe_model_attn_dims_t& d = a.d;
@@ -686,11 +710,11 @@ static int attn_layer_step(moe_engine* e, int layer, int pos, const float* h, fl
         if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb))) return rc;
         if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb))) return rc;
         attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(wide, 2 * hd, 1, kb, vb, (const uint16_t*)ls.vec[MOE_A_Q_NORM],
-                                                              (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd, d.full.rotary_dim, pos,
-                                                              d.full.rope_theta, qr, ls.k_cache, ls.v_cache);
-        const int seq = pos + 1;
-        attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, wide + hd, 2 * hd, nh, nkv, hd, seq,
-                                                                   1.0f / sqrtf((float)hd), vals);
+                                                              (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd, d.full.rotary_dim, 0,
+                                                              a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache);
+        // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
+        attn_decode_kernel<<<nh, 256, (size_t)(d.full.max_seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, wide + hd, 2 * hd, nh, nkv, hd, 0,
+                                                                              a.d_pos, 1.0f / sqrtf((float)hd), vals);
         e->launches += 2;
         if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, o))) return rc;
     } else {
@@ -724,6 +748,51 @@ static int attn_layer_step(moe_engine* e, int layer, int pos, const float* h, fl
     return MOE_OK;
 }
 
+// Captures every layer's attention half (fixed pointers, position read on the device) into a CUDA graph: a token then
+// costs one graph launch + the MoE launch per layer instead of a dozen launches issued one by one from the host.
+// MOE_B200_ATTN_GRAPHS=0 keeps the eager launches.
+static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float* h_mid, float* scratch) {
+    ModelAttnState& a = e->attn;
+    attn_drop_graphs(e);
+    const char* env = getenv("MOE_B200_ATTN_GRAPHS");
+    const int L = e->dims.num_layers;
+    a.graphs.assign((size_t)L, nullptr);
+    a.graph_nodes.assign((size_t)L, 0);
+    a.graphs_valid = true;
+    if (env && atoi(env) == 0) return MOE_OK;
+    for (int l = 0; l < L; ++l) {
+        const int64_t before = e->launches;
+        if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            return MOE_OK;  // capture unavailable: eager launches
+        }
+        const int rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch);
+        cudaGraph_t g = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(e->stream, &g);
+        e->launches = before;  // nothing ran
+        if (rc) {
+            if (g) cudaGraphDestroy(g);
+            attn_drop_graphs(e);
+            return rc;  // a missing tensor: reported as in the eager path
+        }
+        if (ce != cudaSuccess || !g) {
+            cudaGetLastError();
+            continue;
+        }
+        size_t nodes = 0;
+        cudaGraphGetNodes(g, nullptr, &nodes);
+        cudaGraphExec_t ex = nullptr;
+        if (cudaGraphInstantiate(&ex, g, 0) == cudaSuccess) {
+            a.graphs[l] = ex;
+            a.graph_nodes[l] = (int)nodes;
+        } else {
+            cudaGetLastError();
+        }
+        cudaGraphDestroy(g);
+    }
+    return MOE_OK;
+}
+
 int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev) {
     ModelAttnState& a = e->attn;
     if (!a.configured) {
@@ -735,19 +804,39 @@ int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* ou
         return MOE_ERR_STATE;
     }
     const size_t H = (size_t)e->dims.hidden;
+    const int L = e->dims.num_layers;
     float* h_mid = a.work;
     float* ping = a.work + al256a(H * 4) / 4;
     float* pong = ping + al256a(H * 4) / 4;
     float* scratch = pong + al256a(H * 4) / 4;
+    // every layer reads from a fixed buffer: layer 0 from `pong` (the token's embedding is copied there), layer l > 0
+    // from where layer l - 1's MoE half wrote (ping / pong alternate); the last layer writes the caller's row
+    std::vector<const float*> layer_in((size_t)L);
+    std::vector<float*> layer_out((size_t)L);
+    for (int l = 0; l < L; ++l) {
+        layer_in[l] = (l == 0) ? pong : layer_out[l - 1];
+        layer_out[l] = (l & 1) ? pong : ping;
+    }
+    if (!a.graphs_valid) {
+        int rc = attn_build_graphs(e, layer_in.data(), h_mid, scratch);
+        if (rc) return rc;
+    }
     for (int t = 0; t < n; ++t) {
-        const float* cur = emb_dev + (size_t)t * H;
-        for (int l = 0; l < e->dims.num_layers; ++l) {
-            int rc = attn_layer_step(e, l, (int)a.pos, cur, h_mid, scratch);
+        set_pos_kernel<<<1, 1, 0, e->stream>>>(a.d_pos, (int)a.pos);
+        MOE_CUDA(cudaMemcpyAsync(pong, emb_dev + (size_t)t * H, H * 4, cudaMemcpyDeviceToDevice, e->stream));
+        e->launches++;
+        for (int l = 0; l < L; ++l) {
+            int rc = MOE_OK;
+            if (a.graphs[l]) {
+                MOE_CUDA(cudaGraphLaunch(a.graphs[l], e->stream));
+                e->launches += a.graph_nodes[l];
+            } else {
+                rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch);
+            }
             if (rc) return rc;
-            float* nxt = (l == e->dims.num_layers - 1) ? out_dev + (size_t)t * H : ((l & 1) ? pong : ping);
+            float* nxt = (l == L - 1) ? out_dev + (size_t)t * H : layer_out[l];
             rc = launch_decode(e, l, l + 1, h_mid, nxt, nullptr, nullptr, nullptr, nullptr);
             if (rc) return rc;
-            cur = nxt;
         }
         a.pos++;
     }

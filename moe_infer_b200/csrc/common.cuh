@@ -174,6 +174,10 @@ struct ModelAttnState {
     std::vector<AttnLayerState> layers;
     float* work = nullptr;
     int64_t pos = 0;
+    int* d_pos = nullptr;                    // the position as the kernels read it
+    std::vector<cudaGraphExec_t> graphs;     // one captured attention half per layer (null: launch eagerly)
+    std::vector<int> graph_nodes;            // kernels in each
+    bool graphs_valid = false;
 };
 
 }  // namespace moe
@@ -236,6 +240,8 @@ int launch_pack(moe_engine* e, const void* src, int src_dtype, int64_t rows, int
 int launch_pack_int8(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols, void* q, void* scales);
 int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, int src_dtype,
                         int32_t n_experts, void* blob);
+// sets the per-device function attributes of the matvec kernels (so that later launches can be captured into a graph)
+int matvec_prepare(moe_engine* e);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);

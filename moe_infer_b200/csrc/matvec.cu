@@ -188,6 +188,14 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
     }
 }
 
+int matvec_prepare(moe_engine* e) {
+    if (!e->matvec_attr_set) {  // a per-device function attribute: set once per engine
+        MOE_CUDA(cudaFuncSetAttribute(matvec_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8 + 2048));
+        e->matvec_attr_set = true;
+    }
+    return MOE_OK;
+}
+
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
@@ -205,10 +213,8 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
         return MOE_OK;
     }
     const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
-    if (!e->matvec_attr_set) {  // a per-device function attribute: set once per engine
-        MOE_CUDA(cudaFuncSetAttribute(matvec_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 8 + 2048));
-        e->matvec_attr_set = true;
-    }
+    int rc = matvec_prepare(e);
+    if (rc) return rc;
     int blocks = (rows + kMvWarps - 1) / kMvWarps;
     const int cap = e->sm_count * 8;
     if (blocks > cap) blocks = cap;
