@@ -14,7 +14,8 @@ namespace moe {
 constexpr int kBfWarps = 8;
 
 __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16_t* __restrict__ w, const float* __restrict__ x,
-                                                                   float* __restrict__ y, int rows, int cols) {
+                                                                   float* __restrict__ y, int rows, int cols,
+                                                                   const float* __restrict__ residual) {  // nullable: y = W x + residual
     extern __shared__ float xs[];
     for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = x[i];
     __syncthreads();
@@ -41,8 +42,8 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
         a0 = warp_sum(a0);
         a1 = warp_sum(a1);
         if (lane == 0) {
-            y[r0] = a0;
-            if (two) y[r0 + 1] = a1;
+            y[r0] = residual ? a0 + residual[r0] : a0;
+            if (two) y[r0 + 1] = residual ? a1 + residual[r0 + 1] : a1;
         }
     }
 }
@@ -399,7 +400,7 @@ static int mtp_project(moe_engine* e, int which, const float* x, float* y) {
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
     if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
-    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols);
+    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, nullptr);
     e->launches++;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
@@ -509,6 +510,7 @@ void attn_destroy(moe_engine* e) {
             if (ls.vec[i]) cudaFree(ls.vec[i]);
             if (ls.proj[i].w) cudaFree(ls.proj[i].w);
         }
+        if (ls.fused.w) cudaFree(ls.fused.w);
         if (ls.k_cache) cudaFree(ls.k_cache);
         if (ls.v_cache) cudaFree(ls.v_cache);
         if (ls.conv_state) cudaFree(ls.conv_state);
@@ -534,6 +536,12 @@ static AttnSizes attn_sizes(const moe_engine* e) {
     z.total_value = (size_t)d.lin_num_v_heads * d.lin_value_dim;
     z.conv_dim = 2 * z.total_key + z.total_value;
     return z;
+}
+
+// floats of the stacked input projections' output: q|k|v of a full layer or qkv|z|b|a of a linear one
+static size_t attn_proj_out_floats(const AttnSizes& z, size_t v_heads) {
+    const size_t full = 2 * z.q_dim + 2 * z.kv_dim, lin = z.conv_dim + z.total_value + 2 * v_heads;
+    return full > lin ? full : lin;
 }
 
 int attn_reset(moe_engine* e) {
@@ -581,12 +589,11 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
             MOE_CUDA(cudaMalloc(&ls.ssm_state, z.total_value * dims->lin_key_dim * 4));
         }
     }
-    // scratch of one step: x, o, h_mid, ping, pong [H]; wide = max(2 q_dim, conv_dim); conv_out [conv_dim];
-    // k, v [kv_dim]; z, vals, normed [max(q_dim, total_value)]; qr [q_dim]; a, b [v_heads]
-    const size_t wide = 2 * z.q_dim > z.conv_dim ? 2 * z.q_dim : z.conv_dim;
+    // scratch of one step: h_mid, ping, pong, x [H]; the stacked projections' output; conv_out [conv_dim];
+    // vals, normed [max(q_dim, total_value)]; qr [q_dim]
     const size_t mid = z.q_dim > z.total_value ? z.q_dim : z.total_value;
-    size_t bytes = 5 * al256a(z.H * 4) + al256a(wide * 4) + al256a(z.conv_dim * 4) + 2 * al256a(z.kv_dim * 4) + 3 * al256a(mid * 4) +
-                   al256a(z.q_dim * 4) + 2 * al256a((size_t)dims->lin_num_v_heads * 4);
+    size_t bytes = 4 * al256a(z.H * 4) + al256a(attn_proj_out_floats(z, (size_t)dims->lin_num_v_heads) * 4) + al256a(z.conv_dim * 4) +
+                   2 * al256a(mid * 4) + al256a(z.q_dim * 4);
     MOE_CUDA(cudaMalloc(&a.work, bytes));
     MOE_CUDA(cudaMalloc(&a.d_pos, 256));
     // function attributes are set here, never between the launches of a layer (those are captured into graphs)
@@ -662,17 +669,65 @@ int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const v
     return MOE_OK;
 }
 
-static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y) {
-    if (t.dtype == MOE_DT_INT4) return launch_matvec(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols);
+static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr) {
+    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual);
     if (!e->mtp.bf_attr_set) {
         MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
         e->mtp.bf_attr_set = true;
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
     if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
-    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols);
+    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual);
     e->launches++;
     MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+}
+
+// Stacks a layer's input projections row-wise into one tensor (same storage type and width required; otherwise the
+// layer keeps its separate launches).  The originals stay loaded.
+static int attn_fuse_layer(moe_engine* e, AttnLayerState& ls) {
+    if (ls.fused.w) { cudaFree(ls.fused.w); ls.fused = ProjTensor{}; }
+    const int full_parts[] = {MOE_A_Q_PROJ, MOE_A_K_PROJ, MOE_A_V_PROJ};
+    const int lin_parts[] = {MOE_A_IN_PROJ_QKV, MOE_A_IN_PROJ_Z, MOE_A_IN_PROJ_B, MOE_A_IN_PROJ_A};
+    const int* parts = ls.full ? full_parts : lin_parts;
+    const int np = ls.full ? 3 : 4;
+    size_t rows = 0;
+    for (int i = 0; i < np; ++i) {
+        const ProjTensor& t = ls.proj[parts[i]];
+        if (!t.loaded || t.dtype != ls.proj[parts[0]].dtype || t.cols != ls.proj[parts[0]].cols) return MOE_OK;
+        rows += (size_t)t.rows;
+    }
+    const int dtype = ls.proj[parts[0]].dtype;
+    const size_t cols = (size_t)ls.proj[parts[0]].cols;
+    ProjTensor f;
+    f.dtype = dtype; f.rows = (int)rows; f.cols = (int)cols;
+    if (dtype == MOE_DT_BF16) {
+        MOE_CUDA(cudaMalloc(&f.w, rows * cols * 2));
+        size_t off = 0;
+        for (int i = 0; i < np; ++i) {
+            const ProjTensor& t = ls.proj[parts[i]];
+            MOE_CUDA(cudaMemcpyAsync(f.w + off, t.w, (size_t)t.rows * cols * 2, cudaMemcpyDeviceToDevice, e->stream));
+            off += (size_t)t.rows * cols * 2;
+        }
+    } else {
+        const size_t wb = rows * cols / 2, sb = rows * (cols / 64) * 2;
+        f.s_off = al256a(wb);
+        f.b_off = f.s_off + al256a(sb);
+        MOE_CUDA(cudaMalloc(&f.w, f.b_off + al256a(sb)));
+        size_t wo = 0, so = 0;
+        for (int i = 0; i < np; ++i) {
+            const ProjTensor& t = ls.proj[parts[i]];
+            const size_t twb = (size_t)t.rows * cols / 2, tsb = (size_t)t.rows * (cols / 64) * 2;
+            MOE_CUDA(cudaMemcpyAsync(f.w + wo, t.w, twb, cudaMemcpyDeviceToDevice, e->stream));
+            MOE_CUDA(cudaMemcpyAsync(f.w + f.s_off + so, t.w + t.s_off, tsb, cudaMemcpyDeviceToDevice, e->stream));
+            MOE_CUDA(cudaMemcpyAsync(f.w + f.b_off + so, t.w + t.b_off, tsb, cudaMemcpyDeviceToDevice, e->stream));
+            wo += twb;
+            so += tsb;
+        }
+    }
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    f.loaded = true;
+    ls.fused = f;
     return MOE_OK;
 }
 
@@ -683,16 +738,16 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     const moe_model_attn_dims_t& d = a.d;
     const AttnSizes z = attn_sizes(e);
     const int H = (int)z.H;
+    const size_t Hv = (size_t)d.lin_num_v_heads;
     cudaStream_t st = e->stream;
-    const size_t wide_n = 2 * z.q_dim > z.conv_dim ? 2 * z.q_dim : z.conv_dim;
     const size_t mid_n = z.q_dim > z.total_value ? z.q_dim : z.total_value;
     float* p = scratch;
     auto take = [&](size_t n) { float* r = p; p += al256a(n * 4) / 4; return r; };
-    float* x = take(z.H); float* o = take(z.H);
-    float* wide = take(wide_n); float* conv_out = take(z.conv_dim);
-    float* kb = take(z.kv_dim); float* vb = take(z.kv_dim);
-    float* zb = take(mid_n); float* vals = take(mid_n); float* normed = take(mid_n);
-    float* qr = take(z.q_dim); float* ab = take((size_t)d.lin_num_v_heads); float* bb = take((size_t)d.lin_num_v_heads);
+    float* x = take(z.H);
+    float* proj_out = take(attn_proj_out_floats(z, Hv));  // the stacked projections' output
+    float* conv_out = take(z.conv_dim);
+    float* vals = take(mid_n); float* normed = take(mid_n);
+    float* qr = take(z.q_dim);
     auto need = [&](int which) -> bool {
         const bool ok = attn_is_proj(which) ? ls.proj[which].loaded : ls.vec[which] != nullptr;
         if (!ok) set_error("layer %d: the attention half is not loaded (%s missing)", layer, attn_tensor_name(which));
@@ -706,44 +761,56 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         for (int w : {MOE_A_Q_PROJ, MOE_A_K_PROJ, MOE_A_V_PROJ, MOE_A_Q_NORM, MOE_A_K_NORM, MOE_A_O_PROJ})
             if (!need(w)) return MOE_ERR_STATE;
         const int nh = d.full.num_heads, nkv = d.full.num_kv_heads, hd = d.full.head_dim;
-        if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, wide))) return rc;  // [head, gate] per head
-        if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb))) return rc;
-        if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb))) return rc;
-        attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(wide, 2 * hd, 1, kb, vb, (const uint16_t*)ls.vec[MOE_A_Q_NORM],
+        float* qb = proj_out;                  // [head, gate] per head
+        float* kb = qb + 2 * z.q_dim;
+        float* vb = kb + z.kv_dim;
+        if (ls.fused.loaded) {
+            if ((rc = proj_run(e, ls.fused, x, proj_out))) return rc;
+        } else {
+            if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, qb))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb))) return rc;
+        }
+        attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(qb, 2 * hd, 1, kb, vb, (const uint16_t*)ls.vec[MOE_A_Q_NORM],
                                                               (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd, d.full.rotary_dim, 0,
                                                               a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache);
         // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
-        attn_decode_kernel<<<nh, 256, (size_t)(d.full.max_seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, wide + hd, 2 * hd, nh, nkv, hd, 0,
+        attn_decode_kernel<<<nh, 256, (size_t)(d.full.max_seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0,
                                                                               a.d_pos, 1.0f / sqrtf((float)hd), vals);
         e->launches += 2;
-        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, o))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h))) return rc;  // + residual
     } else {
         for (int w : {MOE_A_IN_PROJ_QKV, MOE_A_IN_PROJ_Z, MOE_A_IN_PROJ_B, MOE_A_IN_PROJ_A, MOE_A_OUT_PROJ})
             if (!need(w)) return MOE_ERR_STATE;
-        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, wide))) return rc;
-        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb))) return rc;
-        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb))) return rc;
-        if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab))) return rc;
-        const float* qkv = wide;
+        float* qkv_raw = proj_out;
+        float* zb = qkv_raw + z.conv_dim;
+        float* bb = zb + z.total_value;
+        float* ab = bb + Hv;
+        if (ls.fused.loaded) {
+            if ((rc = proj_run(e, ls.fused, x, proj_out))) return rc;
+        } else {
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, qkv_raw))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab))) return rc;
+        }
+        float* qkv = qkv_raw;
         if (ls.vec[MOE_A_CONV1D]) {  // without a conv weight the projection passes through (cpu.rs:261-263)
-            conv1d_step_kernel<<<(int)((z.conv_dim + 255) / 256), 256, 0, st>>>(ls.conv_state, wide, (const uint16_t*)ls.vec[MOE_A_CONV1D],
+            conv1d_step_kernel<<<(int)((z.conv_dim + 255) / 256), 256, 0, st>>>(ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D],
                                                                              conv_out, (int)z.conv_dim, d.conv_kernel);
             e->launches++;
             qkv = conv_out;
         }
-        float* qkv_w = const_cast<float*>(qkv);
-        lin_qk_norm_kernel<<<2 * d.lin_num_k_heads, 128, 0, st>>>(qkv_w, (int)z.total_key, d.lin_key_dim);
+        lin_qk_norm_kernel<<<2 * d.lin_num_k_heads, 128, 0, st>>>(qkv, (int)z.total_key, d.lin_key_dim);
         const int rows = d.lin_num_v_heads * d.lin_value_dim;
-        delta_step_kernel<<<(rows + 7) / 8, 256, 0, st>>>(ls.ssm_state, qkv_w, qkv_w + z.total_key, qkv_w + 2 * z.total_key, ab, bb,
+        delta_step_kernel<<<(rows + 7) / 8, 256, 0, st>>>(ls.ssm_state, qkv, qkv + z.total_key, qkv + 2 * z.total_key, ab, bb,
                                                           (const float*)ls.vec[MOE_A_A_LOG], (const uint16_t*)ls.vec[MOE_A_DT_BIAS], vals,
                                                           d.lin_num_v_heads, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim,
                                                           d.lin_value_dim);
         gated_rms_norm_kernel<<<d.lin_num_v_heads, 128, 0, st>>>(vals, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM], normed, d.lin_value_dim);
         e->launches += 3;
-        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, o))) return rc;
+        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h))) return rc;  // + residual
     }
-    add_rows_kernel<<<(H + 255) / 256, 256, 0, st>>>(o, h, H, h_mid);
-    e->launches++;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
@@ -759,6 +826,10 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
     a.graphs.assign((size_t)L, nullptr);
     a.graph_nodes.assign((size_t)L, 0);
     a.graphs_valid = true;
+    for (AttnLayerState& ls : a.layers) {
+        const int rc = attn_fuse_layer(e, ls);
+        if (rc) return rc;
+    }
     if (env && atoi(env) == 0) return MOE_OK;
     for (int l = 0; l < L; ++l) {
         const int64_t before = e->launches;

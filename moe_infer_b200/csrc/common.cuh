@@ -167,6 +167,7 @@ struct AttnLayerState {
     float* v_cache = nullptr;
     float* conv_state = nullptr;   // linear attention: [conv_kernel - 1, conv_dim]
     float* ssm_state = nullptr;    // linear attention: [v_heads, value_dim, key_dim]
+    ProjTensor fused;              // the input projections stacked row-wise (q|k|v, or qkv|z|b|a): one launch instead of 3-4
 };
 struct ModelAttnState {
     moe_model_attn_dims_t d{};
@@ -242,6 +243,9 @@ int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, in
                         int32_t n_experts, void* blob);
 // sets the per-device function attributes of the matvec kernels (so that later launches can be captured into a graph)
 int matvec_prepare(moe_engine* e);
+// y = W x + residual (residual nullable; may not alias y)
+int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x, float* y, int32_t rows,
+                      int32_t cols, const float* residual);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);

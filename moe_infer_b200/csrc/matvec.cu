@@ -17,7 +17,8 @@ constexpr int kMvWarps = 8;
 __global__ void __launch_bounds__(kMvWarps * 32)
 matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s,
                    const uint16_t* __restrict__ b, const float* __restrict__ x,
-                   float* __restrict__ y, int rows, int cols, unsigned int* err_flag) {
+                   float* __restrict__ y, int rows, int cols, unsigned int* err_flag,
+                   const float* __restrict__ residual) {  // nullable: y = W x + residual
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nch = cols / 32;  // chunks per row
     float* raw = reinterpret_cast<float*>(smem_raw);                 // [cols]
@@ -98,7 +99,7 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
             }
         }
         acc = warp_sum(acc);
-        if (lane == 0) y[row] = acc;
+        if (lane == 0) y[row] = residual ? acc + residual[row] : acc;
     }
 }
 
@@ -114,7 +115,8 @@ constexpr int kSvUnroll = 4;
 
 __global__ void __launch_bounds__(kSvWarps * 32, 2)
 matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s, const uint16_t* __restrict__ b,
-                          const float* __restrict__ x, float* __restrict__ y, int rows, unsigned int* err_flag) {
+                          const float* __restrict__ x, float* __restrict__ y, int rows, unsigned int* err_flag,
+                          const float* __restrict__ residual) {
     constexpr int nch = kSvCols / 32;
     __shared__ __align__(128) float raw[kSvCols];
     __shared__ __align__(16) uint4 xq[6 * nch];
@@ -182,7 +184,7 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
                 const float d = fmaf(dl0, dot32_regs(q[u][0], xe[0], xo[0]), dl1 * dot32_regs(q[u][1], xe[1], xo[1]));
                 float acc = fmaf(bf16_bits_to_f32(sc[u]), d, bf16_bits_to_f32(bi[u]) * sx);
                 acc = warp_sum(acc);
-                if (lane == 0) y[row] = acc;
+                if (lane == 0) y[row] = residual ? acc + residual[row] : acc;
             }
         }
     }
@@ -198,6 +200,11 @@ int matvec_prepare(moe_engine* e) {
 
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols) {
+    return launch_matvec_res(e, w, s, b, x, y, rows, cols, nullptr);
+}
+
+int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
+                      float* y, int32_t rows, int32_t cols, const float* residual) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
@@ -207,7 +214,7 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
         const int cap = e->sm_count * 2;
         if (blocks > cap) blocks = cap;
         matvec_int4_stream_kernel<<<blocks, kSvWarps * 32, 0, e->stream>>>(
-            (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2);
+            (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual);
         e->launches++;
         MOE_CUDA(cudaGetLastError());
         return MOE_OK;
@@ -219,7 +226,7 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
     const int cap = e->sm_count * 8;
     if (blocks > cap) blocks = cap;
     matvec_int4_kernel<<<blocks, kMvWarps * 32, smem, e->stream>>>(
-        (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2);
+        (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual);
     e->launches++;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
