@@ -284,6 +284,14 @@ int moe_model_forward_hidden_host(moe_engine_t* e, const float* emb_host, int32_
 int moe_model_forward_host(moe_engine_t* e, const int64_t* ids_host, int32_t n, float* logits_host);
 int moe_model_reset(moe_engine_t* e);
 int moe_model_pos(const moe_engine_t* e, int64_t* pos);
+/* Engine::snapshot / restore (src/engine.rs:84-105): the state a speculative decode rolls back to, i.e. the position,
+ * the MTP position, last_h_pre_norm and the conv + recurrence state of every linear-attention layer (KV entries behind
+ * the position are simply overwritten later).  The copy lives in device memory owned by the snapshot; restoring is
+ * allowed any number of times, into the engine it was taken from, until moe_model_snapshot_free. */
+typedef struct moe_snapshot moe_snapshot_t;
+int moe_model_snapshot(moe_engine_t* e, moe_snapshot_t** out);
+int moe_model_restore(moe_engine_t* e, const moe_snapshot_t* snap);
+void moe_model_snapshot_free(moe_snapshot_t* snap);
 
 /* ── telemetry ───────────────────────────────────────────────────────────────
  * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys

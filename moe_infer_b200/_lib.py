@@ -102,6 +102,9 @@ SIGNATURES = {
     "moe_model_forward_host": (_i, [_vp, _vp, _i32, _vp]),
     "moe_model_reset": (_i, [_vp]),
     "moe_model_pos": (_i, [_vp, C.POINTER(_i64)]),
+    "moe_model_snapshot": (_i, [_vp, _pp]),
+    "moe_model_restore": (_i, [_vp, _vp]),
+    "moe_model_snapshot_free": (None, [_vp]),
     "moe_mtp_reset": (_i, [_vp]),
     "moe_mtp_rollback": (_i, [_vp, _i64]),
     "moe_mtp_pos": (_i, [_vp, C.POINTER(_i64)]),

@@ -97,8 +97,9 @@ class Cache:
 class PyEngineSnapshot:
     """src/python_bindings.rs:21-24, src/engine.rs:98-109"""
 
-    def __init__(self, pos: int, mtp_pos: int, last_h: np.ndarray):
+    def __init__(self, pos: int, mtp_pos: int, last_h: np.ndarray, device_state=None):
         self.pos, self.mtp_pos, self.last_h_pre_norm = pos, mtp_pos, last_h.copy()
+        self.device_state = device_state  # conv + recurrence states of the linear-attention layers, when attention runs
 
 
 class Engine:
@@ -391,11 +392,14 @@ class Engine:
         self.native.mtp_rollback(pos)
 
     def snapshot_state(self) -> PyEngineSnapshot:
-        return PyEngineSnapshot(self.pos, self.native.mtp_pos(), self._last_h)
+        dev = self.native.model_snapshot() if not self._missing_attn else None
+        return PyEngineSnapshot(self.pos, self.native.mtp_pos(), self._last_h, dev)
 
     def restore_snapshot(self, snap: PyEngineSnapshot) -> None:
-        if not self._missing_attn and snap.pos != self.native.model_pos():
-            raise RuntimeError("the attention state on the device cannot be rolled back to an earlier position")
+        if not self._missing_attn:
+            if snap.device_state is None:
+                raise RuntimeError("this snapshot carries no attention state")
+            self.native.model_restore(snap.device_state)
         self.pos = snap.pos
         self._last_h = snap.last_h_pre_norm.copy()
         self.native.mtp_rollback(snap.mtp_pos)

@@ -557,6 +557,35 @@ int attn_reset(moe_engine* e) {
     return MOE_OK;
 }
 
+size_t attn_state_bytes(const moe_engine* e) {
+    const ModelAttnState& a = e->attn;
+    if (!a.configured) return 0;
+    const AttnSizes z = attn_sizes(e);
+    const size_t per = (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4 + z.total_value * a.d.lin_key_dim * 4;
+    size_t n = 0;
+    for (const AttnLayerState& ls : a.layers) n += ls.full ? 0 : per;
+    return n;
+}
+
+int attn_state_copy(moe_engine* e, uint8_t* buf, bool save) {
+    ModelAttnState& a = e->attn;
+    const AttnSizes z = attn_sizes(e);
+    const size_t cb = (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4, sb = z.total_value * a.d.lin_key_dim * 4;
+    size_t off = 0;
+    for (AttnLayerState& ls : a.layers) {
+        if (ls.full) continue;
+        if (save) {
+            MOE_CUDA(cudaMemcpyAsync(buf + off, ls.conv_state, cb, cudaMemcpyDeviceToDevice, e->stream));
+            MOE_CUDA(cudaMemcpyAsync(buf + off + cb, ls.ssm_state, sb, cudaMemcpyDeviceToDevice, e->stream));
+        } else {
+            MOE_CUDA(cudaMemcpyAsync(ls.conv_state, buf + off, cb, cudaMemcpyDeviceToDevice, e->stream));
+            MOE_CUDA(cudaMemcpyAsync(ls.ssm_state, buf + off + cb, sb, cudaMemcpyDeviceToDevice, e->stream));
+        }
+        off += cb + sb;
+    }
+    return MOE_OK;
+}
+
 int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
     const moe_attn_dims_t& f = dims->full;
     MOE_REQUIRE(f.num_heads > 0 && f.num_kv_heads > 0 && f.num_heads % f.num_kv_heads == 0,

@@ -278,6 +278,10 @@ int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const v
 // n decode steps with attention, enqueued: emb_dev [n, hidden] -> out_dev [n, hidden]; advances the position
 int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev);
 int attn_reset(moe_engine* e);
+// bytes of the linear-attention layers' conv + recurrence states (0 when attention is not configured), and a copy of
+// them to (save) or from a device buffer of that size, enqueued on the engine's stream
+size_t attn_state_bytes(const moe_engine* e);
+int attn_state_copy(moe_engine* e, uint8_t* buf, bool save);
 void attn_destroy(moe_engine* e);
 int head_reserve(moe_engine* e, int32_t n);
 void head_destroy(moe_engine* e);

@@ -897,6 +897,54 @@ int moe_model_pos(const moe_engine_t* e, int64_t* pos) {
     return MOE_OK;
 }
 
+struct moe_snapshot {
+    moe_engine_t* owner = nullptr;
+    int64_t pos = 0, mtp_pos = 0;
+    std::vector<float> last_h;
+    uint8_t* dev = nullptr;   // conv + recurrence states of the linear-attention layers, back to back
+    size_t bytes = 0;
+};
+
+int moe_model_snapshot(moe_engine_t* e, moe_snapshot_t** out) {
+    MOE_REQUIRE(e && out, "null argument");
+    MOE_CUDA(cudaSetDevice(e->device));
+    moe_snapshot* s = new moe_snapshot();
+    s->owner = e;
+    s->pos = e->attn.pos;
+    s->mtp_pos = e->mtp_pos;
+    s->last_h = e->last_h;
+    s->bytes = attn_state_bytes(e);
+    if (s->bytes) {
+        cudaError_t ce = cudaMalloc(&s->dev, s->bytes);
+        if (ce != cudaSuccess) { delete s; return cuda_fail(ce, "snapshot allocation", __FILE__, __LINE__); }
+        int rc = attn_state_copy(e, s->dev, true);
+        if (rc == MOE_OK && cudaStreamSynchronize(e->stream) != cudaSuccess) rc = MOE_ERR_CUDA;
+        if (rc) { cudaFree(s->dev); delete s; return rc; }
+    }
+    *out = s;
+    return MOE_OK;
+}
+
+int moe_model_restore(moe_engine_t* e, const moe_snapshot_t* s) {
+    MOE_REQUIRE(e && s, "null argument");
+    MOE_REQUIRE(s->owner == e && s->bytes == attn_state_bytes(e), "the snapshot was taken from another engine or configuration");
+    if (s->bytes) {
+        int rc = attn_state_copy(e, s->dev, false);
+        if (rc) return rc;
+        MOE_CUDA(cudaStreamSynchronize(e->stream));
+    }
+    e->attn.pos = s->pos;
+    e->mtp_pos = s->mtp_pos;
+    e->last_h = s->last_h;
+    return MOE_OK;
+}
+
+void moe_model_snapshot_free(moe_snapshot_t* s) {
+    if (!s) return;
+    if (s->dev) cudaFree(s->dev);
+    delete s;
+}
+
 // n decode steps with attention; ids != null: embed first and return logits, else emb in and hidden states out
 static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, int32_t n, float* out, bool logits) {
     MOE_REQUIRE(n >= 0, "negative token count");

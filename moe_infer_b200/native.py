@@ -84,6 +84,24 @@ class PinnedArray:
 Q4 = Tuple[np.ndarray, np.ndarray, np.ndarray]
 
 
+class ModelSnapshot:
+    """Device-side copy of what a speculative decode rolls back to (moe_model_snapshot); freed with the object."""
+
+    def __init__(self, eng: "NativeEngine", handle):
+        self.eng, self.handle = eng, handle
+
+    def free(self) -> None:
+        if self.handle is not None and self.eng.h is not None:
+            self.eng.lib.moe_model_snapshot_free(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class NativeEngine:
     def __init__(self, dims: Dims, device: int = 0):
         self.lib = L.load()
@@ -321,6 +339,14 @@ class NativeEngine:
         out = np.empty((ids.size, self.dims.vocab), np.float32)
         L.check(self.lib.moe_model_forward_host(self.h, L.ptr(ids), ids.size, L.ptr(out)))
         return out
+
+    def model_snapshot(self) -> "ModelSnapshot":
+        h = C.c_void_p()
+        L.check(self.lib.moe_model_snapshot(self.h, C.byref(h)))
+        return ModelSnapshot(self, h)
+
+    def model_restore(self, snap: "ModelSnapshot") -> None:
+        L.check(self.lib.moe_model_restore(self.h, snap.handle))
 
     def model_reset(self) -> None:
         L.check(self.lib.moe_model_reset(self.h))

@@ -83,6 +83,13 @@ def test_decode_with_attention_matches_oracle(scheme):
     print(f"decode with attention, {scheme}: rel-L2 per token {['%.1e' % x for x in errs]}")
     assert max(errs) < 1e-2 and eng.model_pos() == 6
     assert rel_l2(got - emb, want - emb) < 1e-2     # the layers' updates themselves, without the residual stream
+    # snapshot, run ahead, roll back: the same tokens give the same result again (speculative decoding's reject path)
+    snap = eng.model_snapshot()
+    ahead = eng.model_forward_hidden(emb[:2])
+    eng.model_restore(snap)
+    assert eng.model_pos() == 6
+    assert np.array_equal(eng.model_forward_hidden(emb[:2]), ahead)
+    snap.free()
     # a new sequence: the caches and recurrence states start from zero again
     eng.model_reset()
     state = oracle.ModelState(ad, layers, 16)
