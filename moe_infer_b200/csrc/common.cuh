@@ -210,7 +210,7 @@ struct moe_engine {
     // slot-grouped decode kernel (decode_slots.cu)
     bool dec_sl_ok = false;                     // device and model shape fit it
     unsigned long long* dec_sl_words = nullptr; // accumulators, tagged SwiGLU outputs, counters (one allocation)
-    unsigned long long dec_sl_hint_base = 0, dec_sl_act_base = 0;
+    unsigned long long dec_sl_hint_base = 0;
     unsigned int dec_sl_epoch = 0;
     bool matvec_attr_set = false;          // matvec kernel's shared-memory attribute set on this engine's device
     float* stage_host = nullptr;           // pinned staging [H] x 2
