@@ -372,17 +372,31 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
             break;
         }
         SPROF(1);
-        const float inv_rms = block_inv_rms(sm, hv);
-        float v = -INFINITY;
-        if (tid < E) {
-            v = __ll2float_rn(lq) * (1.0f / kLFix) * (inv_rms / pscale);
-            if (p.logit_bias) v += p.logit_bias[tid];
+        float inv_rms, v = -INFINITY;
+        if (p.logit_bias == nullptr) {
+            // The logits are the accumulated sums times a positive factor (1 / rms of this layer's input over the
+            // factor they were pushed with): the selection needs only their order, so it runs on the raw sums and
+            // the weight requests go out before the norm's reduction; the factor is applied afterwards.
+            const float u = (tid < E) ? __ll2float_rn(lq) : -INFINITY;
+            route_select(sm, u, p.forced_idx, E, K, p.err);
+            SPROF(2);
+            if (!shared_slot) request_weights(ly);
+            SPROF(3);
+            inv_rms = block_inv_rms(sm, hv);
+            const float f1 = 1.0f / kLFix, f2 = inv_rms / pscale;
+            if (tid < E) v = u * f1 * f2;
+            // what route_weights reads later (behind the barrier that follows the staging): chosen logits, warp maxima
+            if (tid < K) sm->topp[tid] = sm->topp[tid] * f1 * f2;
+            if (tid >= 32 && tid < 32 + kDecWarps) sm->red[tid - 32] = sm->red[tid - 32] * f1 * f2;
+        } else {
+            inv_rms = block_inv_rms(sm, hv);
+            if (tid < E) v = __ll2float_rn(lq) * (1.0f / kLFix) * (inv_rms / pscale) + p.logit_bias[tid];
+            route_select(sm, v, p.forced_idx, E, K, p.err);
+            SPROF(2);
+            // ── weight requests (the shared expert's group made them at the top of the layer) ──
+            if (!shared_slot) request_weights(ly);
+            SPROF(3);
         }
-        route_select(sm, v, p.forced_idx, E, K, p.err);
-        SPROF(2);
-        // ── weight requests (the shared expert's group made them at the top of the layer) ──
-        if (!shared_slot) request_weights(ly);
-        SPROF(3);
         // the copies are on their way: stage x, the softmax weights of the chosen experts, and what the end of
         // the layer needs from the layer's input
         stage_x(sm, norm_wb, hv, inv_rms);
