@@ -251,6 +251,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
     // Waits until `n_done` pushes of every CTA are announced, then reads this thread's accumulator words until
     // they are complete: the hidden-state sums of the layer just finished (added to hv) when with_h, the router
     // logits of the layer about to run (returned through `logit`, in 2^-32 units times pscale) when with_l.
+    unsigned long long l_expect = (unsigned long long)kSG;  // contributions a finished logit sum carries
     auto read_acc = [&](int n_done, bool with_h, int hset, bool with_l, int lset, long long& logit) -> bool {
         if (tid == 0) sm->flag = wait_count(p.hint, p.hint_base + (unsigned long long)kSG * (unsigned long long)n_done, p.err);
         __syncthreads();
@@ -271,7 +272,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
 #pragma unroll
                 for (int i = 0; i < 4; ++i) done = done && (((q[i] - hprev_cur[i]) & kCntMask) == (unsigned long long)kNSlots);
             }
-            if (my_l) done = done && (((ql - lprev_cur) & kCntMask) == (unsigned long long)kSG);
+            if (my_l) done = done && (((ql - lprev_cur) & kCntMask) == l_expect);
             if (done) break;
             if ((it & 15u) == 15u) {
                 if (t0 == 0) t0 = clock64();
@@ -346,8 +347,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
             reinterpret_cast<float4*>(sm->hn)[lane] = o;
         }
         __syncthreads();
-        push_partial_logits(sm, rt, p.lacc, E, Ep, pscale);
-        __syncthreads();
+        // only the first group holds rows of h here: the other groups' shares would be zeros
+        if (slot == 0) {
+            push_partial_logits(sm, rt, p.lacc, E, Ep, pscale);
+            __syncthreads();
+        }
         if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p.hint), "l"(1ull) : "memory");
     }
 
@@ -366,6 +370,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         if (has_next && tid < kDnRows) nwn_bits = __ldg(sm->tab[rel + 1].post_norm + r0 + tid);
         // ── this layer's input: h (sums of the layer before) and the router logits ──
         long long lq = 0;
+        l_expect = (unsigned long long)(rel == 0 ? kGrpCtas : kSG);  // the first layer's sums come from the first group alone
         if (!read_acc(rel + 1, rel > 0, (rel + 1) & 1, true, rel & 1, lq)) {
             if (tid == 0) atomicExch(p.err, 3u);
             alive = false;
