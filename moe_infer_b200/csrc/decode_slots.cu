@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
                       : a == 3 ? (void*)sm->gu_s[1][j0] : a == 4 ? (void*)sm->gu_b[0][j0] : (void*)sm->gu_b[1][j0];
             const uint32_t bytes = kBatch * row_bytes;
             mbar_expect_tx(&sm->bar_g[b], bytes);
-            bulk_g2s(dst, ex + off + (size_t)(item0 + j0) * row_bytes, bytes, &sm->bar_g[b]);
+            bulk_g2s_stream(dst, ex + off + (size_t)(item0 + j0) * row_bytes, bytes, &sm->bar_g[b]);
         } else if (lane == 0 && warp < 15) {
             const int q = warp - 12;
             const int64_t off = q == 0 ? L.down_w : q == 1 ? L.down_s : L.down_b;
@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
             void* dst = q == 0 ? (void*)sm->dn_w : q == 1 ? (void*)sm->dn_s : (void*)sm->dn_b;
             const uint32_t bytes = kDnRows * row_bytes;
             mbar_expect_tx(&sm->bar_d, bytes);
-            bulk_g2s(dst, ex + off + (size_t)r0 * row_bytes, bytes, &sm->bar_d);
+            bulk_g2s_stream(dst, ex + off + (size_t)r0 * row_bytes, bytes, &sm->bar_d);
         }
         if (shared_slot && lane == 1 && warp < 3) {
             const void* src = warp == 0 ? (const void*)ly.sgate.w : warp == 1 ? (const void*)ly.sgate.s : (const void*)ly.sgate.b;

@@ -44,6 +44,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+// The same for bytes that are read once (streamed weights): the L2 is told to evict them first, which leaves its
+// capacity to the words that are exchanged between CTAs.
+__device__ __forceinline__ void bulk_g2s_stream(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
 // L2 prefetch of a byte range (16-byte aligned, multiple of 16).
 __device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
