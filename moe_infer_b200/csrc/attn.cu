@@ -182,98 +182,165 @@ __global__ void __launch_bounds__(256) add_rows_kernel(const float* __restrict__
 }
 
 // ─── Gated DeltaNet (linear attention) layer, one token (src/engine/qwen35_moe/cpu.rs:218-347) ───────────────
-// Causal depthwise conv over the last `ksize` inputs of every channel, then SiLU; the state keeps the previous
-// ksize - 1 inputs, oldest first, and is shifted here (conv1d_step, src/math_util.rs:149-168; cpu.rs:263-275).
-// Weights [channels][ksize] bf16.  A thread owns a channel, so the in-place shift is race-free.
-__global__ void __launch_bounds__(256) conv1d_step_kernel(float* __restrict__ conv_state, const float* __restrict__ x,
-                                                          const uint16_t* __restrict__ w, float* __restrict__ out, int channels,
-                                                          int ksize) {
-    const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= channels) return;
-    float acc = 0.0f;
-    for (int k = 0; k < ksize - 1; ++k) acc += conv_state[(size_t)k * channels + c] * bf16_bits_to_f32(w[(size_t)c * ksize + k]);
-    const float xin = x[c];
-    acc += xin * bf16_bits_to_f32(w[(size_t)c * ksize + ksize - 1]);
-    out[c] = acc / (1.0f + expf(-acc));  // silu (src/math_util.rs:71-75)
-    for (int k = 0; k + 2 < ksize; ++k) conv_state[(size_t)k * channels + c] = conv_state[(size_t)(k + 1) * channels + c];
-    if (ksize >= 2) conv_state[(size_t)(ksize - 2) * channels + c] = xin;
-}
+// One CTA per value head does everything between the input projections and the output projection:
+//   * causal depthwise conv over the last `ksize` inputs of its channels (its key head's q and k, its own v), then
+//     SiLU (conv1d_step, src/math_util.rs:149-168; weights [channels][ksize] bf16).  The state is a ring of `ksize`
+//     input rows indexed by position: tap k < ksize - 1 reads the input of step pos - (ksize - 1) + k, the new input
+//     goes to row pos % ksize, which nobody reads in this step, so the value heads that share a key head (and write
+//     the same values) do not race.  Rows never written hold zeros, as the reference's shifted state does at start;
+//   * unweighted per-head RMS norm of q and k, q scaled by 1 / key_dim and k by 1 / sqrt(key_dim) (cpu.rs:277-299);
+//   * decay exp(-exp(A_log) * softplus(a + dt_bias)) and input gate sigmoid(b) (compute_decay_beta, math_util.rs:401-416);
+//   * the delta rule on the head's [value_dim, key_dim] state, one warp per row at a time: decay, read against k,
+//     correct, read against q (gated_delta_net_step, math_util.rs:425-466); the state is read and written once;
+//   * RMS norm of the head's outputs, SiLU gate from z, bf16 weight (gated_rms_norm, math_util.rs:472-493; no weight:
+//     the outputs pass through, cpu.rs:329-336).
+// Shared memory: q, k [key_dim], v, vals [value_dim].
+constexpr int kLinThreads = 1024, kLinWarps = kLinThreads / 32;
+constexpr int kLinRows = 4;    // state rows a warp has in flight
+constexpr int kLinPerMax = 8; // state elements per lane and row: key_dim <= 256
 
-// Per-head RMS norm of q and k without weights, q scaled by 1 / key_dim and k by 1 / sqrt(key_dim) (cpu.rs:277-299).
-// Block (h, which): which = 0 the query head h, 1 the key head h; in place on the conv output [q | k | v].
-__global__ void __launch_bounds__(128) lin_qk_norm_kernel(float* __restrict__ qkv, int total_key, int key_dim) {
-    __shared__ float red[4];
-    const int h = blockIdx.x >> 1, which = blockIdx.x & 1;
-    float* head = qkv + (size_t)which * total_key + (size_t)h * key_dim;
+template <int kLinPer>  // 4: key_dim <= 128, 8: key_dim <= 256
+__global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict__ conv_ring, const float* __restrict__ qkv_in,
+                                                       const uint16_t* __restrict__ conv_w, const float* __restrict__ z,
+                                                       const float* __restrict__ alpha, const float* __restrict__ beta,
+                                                       const float* __restrict__ a_log, const uint16_t* __restrict__ dt_bias,
+                                                       const uint16_t* __restrict__ norm_w, float* __restrict__ state,
+                                                       float* __restrict__ out, const int* __restrict__ pos_ptr, int total_key,
+                                                       int conv_dim, int ksize, int k_heads_per_v, int key_dim, int value_dim) {
+    extern __shared__ float lsm[];
+    __shared__ float red[kLinWarps];
+    float* qs = lsm;
+    float* ks = qs + key_dim;
+    float* vs = ks + key_dim;
+    float* vals = vs + value_dim;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float ss = 0.0f;
-    for (int i = tid; i < key_dim; i += 128) ss = fmaf(head[i], head[i], ss);
-    ss = warp_sum(ss);
-    if (lane == 0) red[warp] = ss;
+    const int h = blockIdx.x, kh = h / k_heads_per_v;
+    const int pos = *pos_ptr;
+    // 1. conv + SiLU of this head's channels, and the ring update
+    const int n_ch = 2 * key_dim + value_dim;
+    for (int i = tid; i < n_ch; i += kLinThreads) {
+        const int c = i < key_dim ? kh * key_dim + i
+                    : i < 2 * key_dim ? total_key + kh * key_dim + (i - key_dim)
+                                      : 2 * total_key + h * value_dim + (i - 2 * key_dim);
+        const float xin = qkv_in[c];
+        float val = xin;
+        if (conv_w) {
+            float acc = 0.0f;
+            for (int k = 0; k < ksize - 1; ++k) {
+                const int step = pos - (ksize - 1) + k;                   // the input this tap multiplies
+                const int row = ((step % ksize) + ksize) % ksize;         // rows of steps before the start hold zeros
+                acc += conv_ring[(size_t)row * conv_dim + c] * bf16_bits_to_f32(conv_w[(size_t)c * ksize + k]);
+            }
+            acc += xin * bf16_bits_to_f32(conv_w[(size_t)c * ksize + ksize - 1]);
+            val = acc / (1.0f + expf(-acc));  // silu (src/math_util.rs:71-75)
+            conv_ring[(size_t)(pos % ksize) * conv_dim + c] = xin;
+        }
+        if (i < key_dim) qs[i] = val;
+        else if (i < 2 * key_dim) ks[i - key_dim] = val;
+        else vs[i - 2 * key_dim] = val;
+    }
     __syncthreads();
-    const float tot = red[0] + red[1] + red[2] + red[3];
-    const float inv = 1.0f / sqrtf(tot / (float)key_dim + 1e-6f);
+    // 2. q / k norms
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = tid; i < key_dim; i += kLinThreads) {
+        sq = fmaf(qs[i], qs[i], sq);
+        sk = fmaf(ks[i], ks[i], sk);
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    __shared__ float red2[kLinWarps];
+    if (lane == 0) { red[warp] = sq; red2[warp] = sk; }
+    __syncthreads();
+    float tq = 0.0f, tk = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLinWarps; ++i) { tq += red[i]; tk += red2[i]; }
     const float inv_scale = 1.0f / sqrtf((float)key_dim);
-    const float mul = which == 0 ? inv * inv_scale * inv_scale : inv * inv_scale;
-    for (int i = tid; i < key_dim; i += 128) head[i] *= mul;
-}
-
-// The recurrence (compute_decay_beta + gated_delta_net_step, src/math_util.rs:401-466): per value head h and value
-// row vi, the key_dim-long state row is decayed, read against k, corrected by the delta rule and read against q.
-// One warp per row: the 2 MB of state per layer are read and written once, coalesced.
-__global__ void __launch_bounds__(256) delta_step_kernel(float* __restrict__ state, const float* __restrict__ q,
-                                                         const float* __restrict__ k, const float* __restrict__ v,
-                                                         const float* __restrict__ alpha, const float* __restrict__ beta,
-                                                         const float* __restrict__ a_log, const uint16_t* __restrict__ dt_bias,
-                                                         float* __restrict__ out, int num_v_heads, int k_heads_per_v,
-                                                         int key_dim, int value_dim) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= num_v_heads * value_dim) return;
-    const int h = row / value_dim, vi = row - h * value_dim;
-    const int kh = h / k_heads_per_v;
-    // decay and input gate of this head
+    const float q_mul = (1.0f / sqrtf(tq / (float)key_dim + 1e-6f)) * inv_scale * inv_scale;
+    const float k_mul = (1.0f / sqrtf(tk / (float)key_dim + 1e-6f)) * inv_scale;
+    __syncthreads();  // red / red2 are reused below
+    for (int i = tid; i < key_dim; i += kLinThreads) {
+        qs[i] *= q_mul;
+        ks[i] *= k_mul;
+    }
+    // 3. decay and input gate of this head
     const float a = expf(a_log ? a_log[h] : 0.0f);
     const float softplus = logf(1.0f + expf(alpha[h] + (dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f)));
     const float g = expf(-a * softplus);
     const float bgate = 1.0f / (1.0f + expf(-beta[h]));
-    float* srow = state + ((size_t)h * value_dim + vi) * key_dim;
-    const float* kk = k + (size_t)kh * key_dim;
-    const float* qq = q + (size_t)kh * key_dim;
-    float kv_mem = 0.0f;
-    for (int i = lane; i < key_dim; i += 32) kv_mem = fmaf(srow[i] * g, kk[i], kv_mem);
-    kv_mem = warp_sum(kv_mem);
-    const float delta = (v[(size_t)h * value_dim + vi] - kv_mem) * bgate;
-    float o = 0.0f;
-    for (int i = lane; i < key_dim; i += 32) {
-        const float sn = srow[i] * g + kk[i] * delta;
-        srow[i] = sn;
-        o = fmaf(sn, qq[i], o);
+    __syncthreads();
+    // 4. the recurrence: a warp takes kLinRows consecutive rows at a time and requests all their state up front
+    for (int v0 = warp * kLinRows; v0 < value_dim; v0 += kLinWarps * kLinRows) {
+        float sreg[kLinRows][kLinPer];
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            const float* srow = state + ((size_t)h * value_dim + v0 + r) * key_dim;
+#pragma unroll
+            for (int j = 0; j < kLinPer; ++j) {
+                const int i = lane + 32 * j;
+                sreg[r][j] = (v0 + r < value_dim && i < key_dim) ? srow[i] : 0.0f;
+            }
+        }
+        float kv[kLinRows];
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kLinPer; ++j) {
+                const int i = lane + 32 * j;
+                sreg[r][j] *= g;
+                if (i < key_dim) acc = fmaf(sreg[r][j], ks[i], acc);
+            }
+            kv[r] = acc;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kLinRows; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+        float ov[kLinRows];
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            const float delta = ((v0 + r < value_dim ? vs[v0 + r] : 0.0f) - kv[r]) * bgate;
+            float* srow = state + ((size_t)h * value_dim + v0 + r) * key_dim;
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kLinPer; ++j) {
+                const int i = lane + 32 * j;
+                if (v0 + r < value_dim && i < key_dim) {
+                    const float sn = sreg[r][j] + ks[i] * delta;
+                    srow[i] = sn;
+                    acc = fmaf(sn, qs[i], acc);
+                }
+            }
+            ov[r] = acc;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kLinRows; ++r) ov[r] += __shfl_xor_sync(0xffffffffu, ov[r], o);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kLinRows; ++r)
+                if (v0 + r < value_dim) vals[v0 + r] = ov[r];
+        }
     }
-    o = warp_sum(o);
-    if (lane == 0) out[(size_t)h * value_dim + vi] = o;
-}
-
-// Per value head: RMS norm of the recurrence output, SiLU gate from z, bf16 weight [value_dim]
-// (gated_rms_norm, src/math_util.rs:472-493; w == null leaves the values as they are, cpu.rs:329-336).
-__global__ void __launch_bounds__(128) gated_rms_norm_kernel(const float* __restrict__ vals, const float* __restrict__ z,
-                                                             const uint16_t* __restrict__ w, float* __restrict__ out, int value_dim) {
-    __shared__ float red[4];
-    const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* x = vals + (size_t)h * value_dim;
-    if (!w) {
-        for (int i = tid; i < value_dim; i += 128) out[(size_t)h * value_dim + i] = x[i];
+    __syncthreads();
+    // 5. gated RMS norm
+    if (!norm_w) {
+        for (int i = tid; i < value_dim; i += kLinThreads) out[(size_t)h * value_dim + i] = vals[i];
         return;
     }
     float ss = 0.0f;
-    for (int i = tid; i < value_dim; i += 128) ss = fmaf(x[i], x[i], ss);
+    for (int i = tid; i < value_dim; i += kLinThreads) ss = fmaf(vals[i], vals[i], ss);
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
     __syncthreads();
-    const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)value_dim + 1e-6f);
-    for (int i = tid; i < value_dim; i += 128) {
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLinWarps; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)value_dim + 1e-6f);
+    for (int i = tid; i < value_dim; i += kLinThreads) {
         const float zv = z[(size_t)h * value_dim + i];
-        out[(size_t)h * value_dim + i] = x[i] * inv * (zv / (1.0f + expf(-zv))) * bf16_bits_to_f32(w[i]);
+        out[(size_t)h * value_dim + i] = vals[i] * inv * (zv / (1.0f + expf(-zv))) * bf16_bits_to_f32(norm_w[i]);
     }
 }
 
@@ -550,7 +617,7 @@ int attn_reset(moe_engine* e) {
     const AttnSizes z = attn_sizes(e);
     for (AttnLayerState& ls : a.layers) {
         if (ls.full) continue;  // KV entries behind the position are never read
-        MOE_CUDA(cudaMemsetAsync(ls.conv_state, 0, (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4, e->stream));
+        MOE_CUDA(cudaMemsetAsync(ls.conv_state, 0, (size_t)a.d.conv_kernel * z.conv_dim * 4, e->stream));
         MOE_CUDA(cudaMemsetAsync(ls.ssm_state, 0, z.total_value * a.d.lin_key_dim * 4, e->stream));
     }
     a.pos = 0;
@@ -561,7 +628,7 @@ size_t attn_state_bytes(const moe_engine* e) {
     const ModelAttnState& a = e->attn;
     if (!a.configured) return 0;
     const AttnSizes z = attn_sizes(e);
-    const size_t per = (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4 + z.total_value * a.d.lin_key_dim * 4;
+    const size_t per = (size_t)a.d.conv_kernel * z.conv_dim * 4 + z.total_value * a.d.lin_key_dim * 4;
     size_t n = 0;
     for (const AttnLayerState& ls : a.layers) n += ls.full ? 0 : per;
     return n;
@@ -570,7 +637,7 @@ size_t attn_state_bytes(const moe_engine* e) {
 int attn_state_copy(moe_engine* e, uint8_t* buf, bool save) {
     ModelAttnState& a = e->attn;
     const AttnSizes z = attn_sizes(e);
-    const size_t cb = (size_t)(a.d.conv_kernel - 1) * z.conv_dim * 4, sb = z.total_value * a.d.lin_key_dim * 4;
+    const size_t cb = (size_t)a.d.conv_kernel * z.conv_dim * 4, sb = z.total_value * a.d.lin_key_dim * 4;
     size_t off = 0;
     for (AttnLayerState& ls : a.layers) {
         if (ls.full) continue;
@@ -597,8 +664,9 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
     MOE_REQUIRE(dims->lin_num_k_heads > 0 && dims->lin_num_v_heads > 0 && dims->lin_num_v_heads % dims->lin_num_k_heads == 0,
                 "linear-attention value heads (%d) must be a positive multiple of the key heads (%d)", dims->lin_num_v_heads,
                 dims->lin_num_k_heads);
-    MOE_REQUIRE(dims->lin_key_dim > 0 && dims->lin_value_dim > 0 && dims->conv_kernel >= 2 && dims->conv_kernel <= 16,
-                "linear-attention dimensions out of range");
+    MOE_REQUIRE(dims->lin_key_dim > 0 && dims->lin_key_dim <= 32 * kLinPerMax && dims->lin_value_dim > 0 && dims->lin_value_dim <= 2048 &&
+                    dims->conv_kernel >= 2 && dims->conv_kernel <= 16,
+                "linear-attention dimensions out of range (key_dim <= %d, value_dim <= 2048, conv kernel 2..16)", 32 * kLinPerMax);
     MOE_REQUIRE(dims->full_attn_interval >= 1, "full_attention_interval must be at least 1");
     attn_destroy(e);
     ModelAttnState& a = e->attn;
@@ -614,14 +682,14 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
             MOE_CUDA(cudaMalloc(&ls.k_cache, (size_t)f.max_seq * z.kv_dim * 4));
             MOE_CUDA(cudaMalloc(&ls.v_cache, (size_t)f.max_seq * z.kv_dim * 4));
         } else {
-            MOE_CUDA(cudaMalloc(&ls.conv_state, (size_t)(dims->conv_kernel - 1) * z.conv_dim * 4));
+            MOE_CUDA(cudaMalloc(&ls.conv_state, (size_t)dims->conv_kernel * z.conv_dim * 4));
             MOE_CUDA(cudaMalloc(&ls.ssm_state, z.total_value * dims->lin_key_dim * 4));
         }
     }
-    // scratch of one step: h_mid, ping, pong, x [H]; the stacked projections' output; conv_out [conv_dim];
+    // scratch of one step: h_mid, ping, pong, x [H]; the stacked projections' output;
     // vals, normed [max(q_dim, total_value)]; qr [q_dim]
     const size_t mid = z.q_dim > z.total_value ? z.q_dim : z.total_value;
-    size_t bytes = 4 * al256a(z.H * 4) + al256a(attn_proj_out_floats(z, (size_t)dims->lin_num_v_heads) * 4) + al256a(z.conv_dim * 4) +
+    size_t bytes = 4 * al256a(z.H * 4) + al256a(attn_proj_out_floats(z, (size_t)dims->lin_num_v_heads) * 4) +
                    2 * al256a(mid * 4) + al256a(z.q_dim * 4);
     MOE_CUDA(cudaMalloc(&a.work, bytes));
     MOE_CUDA(cudaMalloc(&a.d_pos, 256));
@@ -774,7 +842,6 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     auto take = [&](size_t n) { float* r = p; p += al256a(n * 4) / 4; return r; };
     float* x = take(z.H);
     float* proj_out = take(attn_proj_out_floats(z, Hv));  // the stacked projections' output
-    float* conv_out = take(z.conv_dim);
     float* vals = take(mid_n); float* normed = take(mid_n);
     float* qr = take(z.q_dim);
     auto need = [&](int which) -> bool {
@@ -823,21 +890,18 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab))) return rc;
         }
-        float* qkv = qkv_raw;
-        if (ls.vec[MOE_A_CONV1D]) {  // without a conv weight the projection passes through (cpu.rs:261-263)
-            conv1d_step_kernel<<<(int)((z.conv_dim + 255) / 256), 256, 0, st>>>(ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D],
-                                                                             conv_out, (int)z.conv_dim, d.conv_kernel);
-            e->launches++;
-            qkv = conv_out;
-        }
-        lin_qk_norm_kernel<<<2 * d.lin_num_k_heads, 128, 0, st>>>(qkv, (int)z.total_key, d.lin_key_dim);
-        const int rows = d.lin_num_v_heads * d.lin_value_dim;
-        delta_step_kernel<<<(rows + 7) / 8, 256, 0, st>>>(ls.ssm_state, qkv, qkv + z.total_key, qkv + 2 * z.total_key, ab, bb,
-                                                          (const float*)ls.vec[MOE_A_A_LOG], (const uint16_t*)ls.vec[MOE_A_DT_BIAS], vals,
-                                                          d.lin_num_v_heads, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim,
-                                                          d.lin_value_dim);
-        gated_rms_norm_kernel<<<d.lin_num_v_heads, 128, 0, st>>>(vals, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM], normed, d.lin_value_dim);
-        e->launches += 3;
+        const size_t lin_smem = (size_t)(2 * d.lin_key_dim + 2 * d.lin_value_dim) * 4;
+        if (d.lin_key_dim <= 128)
+            lin_core_kernel<4><<<d.lin_num_v_heads, kLinThreads, lin_smem, st>>>(
+            ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
+            (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed, a.d_pos,
+            (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim);
+        else
+            lin_core_kernel<8><<<d.lin_num_v_heads, kLinThreads, lin_smem, st>>>(
+            ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
+            (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed, a.d_pos,
+            (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim);
+        e->launches++;
         if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h))) return rc;  // + residual
     }
     MOE_CUDA(cudaGetLastError());

@@ -165,7 +165,7 @@ struct AttnLayerState {
     ProjTensor proj[16];           // projections by moe_attn_tensor_t
     float* k_cache = nullptr;      // full attention: [max_seq, kv_dim] each
     float* v_cache = nullptr;
-    float* conv_state = nullptr;   // linear attention: [conv_kernel - 1, conv_dim]
+    float* conv_state = nullptr;   // linear attention: ring of the last conv_kernel inputs, [conv_kernel, conv_dim], row = position % conv_kernel
     float* ssm_state = nullptr;    // linear attention: [v_heads, value_dim, key_dim]
     ProjTensor fused;              // the input projections stacked row-wise (q|k|v, or qkv|z|b|a): one launch instead of 3-4
 };
