@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
         const uint16_t* wa = w + (size_t)r0 * cols;
         const uint16_t* wb = w + (size_t)(two ? r0 + 1 : r0) * cols;
         float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 4
         for (int c = lane * 8; c < cols; c += 256) {
             const uint4 qa = ld_stream_u4(wa + c), qb = ld_stream_u4(wb + c);
             const float4 x0 = *reinterpret_cast<const float4*>(xs + c), x1 = *reinterpret_cast<const float4*>(xs + c + 4);

@@ -223,7 +223,8 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
     int rc = matvec_prepare(e);
     if (rc) return rc;
     int blocks = (rows + kMvWarps - 1) / kMvWarps;
-    const int cap = e->sm_count * 8;
+    // every CTA stages the whole x: with long rows fewer CTAs, each taking several rows per warp, amortise that better
+    const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
     if (blocks > cap) blocks = cap;
     matvec_int4_kernel<<<blocks, kMvWarps * 32, smem, e->stream>>>(
         (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual);
