@@ -177,10 +177,6 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     }
 }
 
-__global__ void __launch_bounds__(256) add_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, int n, float* __restrict__ out) {
-    const int i = blockIdx.x * 256 + threadIdx.x;
-    if (i < n) out[i] = a[i] + b[i];
-}
 
 // ─── Gated DeltaNet (linear attention) layer, one token (src/engine/qwen35_moe/cpu.rs:218-347) ───────────────
 // One CTA per value head does everything between the input projections and the output projection:
@@ -458,17 +454,16 @@ int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, cons
     return MOE_OK;
 }
 
-static int mtp_project(moe_engine* e, int which, const float* x, float* y) {
-    MtpAttnState& m = e->mtp;
-    const ProjTensor& t = m.proj[which];
-    if (t.dtype == MOE_DT_INT4) return launch_matvec(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols);
-    if (!m.bf_attr_set) {
+// y = W x (+ residual) for a projection stored as bf16 rows or as a 4-bit triple
+static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr) {
+    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual);
+    if (!e->mtp.bf_attr_set) {
         MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
-        m.bf_attr_set = true;
+        e->mtp.bf_attr_set = true;
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
     if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
-    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, nullptr);
+    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual);
     e->launches++;
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
@@ -507,7 +502,7 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     auto take = [&](size_t n) { float* r = p; p += al256a(n * 4) / 4; return r; };
     float* h = take(H); float* tok = take(H); float* concat = take(2 * (size_t)H); float* cur = take(H); float* x = take(H);
     float* q = take(2 * q_dim); float* k = take(kv_dim); float* v = take(kv_dim); float* qr = take(q_dim); float* gated = take(q_dim);
-    float* o = take(H); float* cur2 = take(H); float* y = take(H);
+    float* cur2 = take(H); float* y = take(H);
     cudaStream_t st = e->stream;
     MOE_CUDA(cudaMemcpyAsync(h, h_host, (size_t)H * 4, cudaMemcpyHostToDevice, st));
     MOE_CUDA(cudaMemcpyAsync(m.id_dev, &token_id, 8, cudaMemcpyHostToDevice, st));
@@ -517,23 +512,20 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     rms_norm_rows_kernel<<<1, 256, 0, st>>>(tok, m.norms[MOE_M_PRE_FC_NORM_EMBEDDING], H, concat);
     rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, m.norms[MOE_M_PRE_FC_NORM_HIDDEN], H, concat + H);
     e->launches += 2;
-    rc = mtp_project(e, MOE_M_FC, concat, cur);
+    rc = proj_run(e, m.proj[MOE_M_FC], concat, cur);
     if (rc) return rc;
     rms_norm_rows_kernel<<<1, 256, 0, st>>>(cur, m.norms[MOE_M_INPUT_NORM], H, x);
     e->launches++;
-    if ((rc = mtp_project(e, MOE_M_Q_PROJ, x, q))) return rc;
-    if ((rc = mtp_project(e, MOE_M_K_PROJ, x, k))) return rc;
-    if ((rc = mtp_project(e, MOE_M_V_PROJ, x, v))) return rc;
+    if ((rc = proj_run(e, m.proj[MOE_M_Q_PROJ], x, q))) return rc;
+    if ((rc = proj_run(e, m.proj[MOE_M_K_PROJ], x, k))) return rc;
+    if ((rc = proj_run(e, m.proj[MOE_M_V_PROJ], x, v))) return rc;
     attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
                                                           m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
     const int seq = pos + 1;
     attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
                                                                1.0f / sqrtf((float)hd), gated);
     e->launches += 2;
-    if ((rc = mtp_project(e, MOE_M_O_PROJ, gated, o))) return rc;
-    add_rows_kernel<<<(H + 255) / 256, 256, 0, st>>>(o, cur, H, cur2);
-    e->launches++;
-    MOE_CUDA(cudaGetLastError());
+    if ((rc = proj_run(e, m.proj[MOE_M_O_PROJ], gated, cur2, cur))) return rc;  // + residual
     // the MoE half: post-attention norm, router, experts, shared expert, residual (layer index num_layers)
     if ((rc = launch_decode(e, d.num_layers, d.num_layers + 1, cur2, y, nullptr, nullptr, nullptr, nullptr))) return rc;
     if ((rc = launch_logits_norm(e, y, 1, logits_dev, m.norms[MOE_M_OUT_NORM]))) return rc;
@@ -764,20 +756,6 @@ int attn_load_tensor(moe_engine* e, int layer, int which, const void* w, const v
     }
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     t.loaded = true;
-    return MOE_OK;
-}
-
-static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr) {
-    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual);
-    if (!e->mtp.bf_attr_set) {
-        MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
-        e->mtp.bf_attr_set = true;
-    }
-    int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
-    if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
-    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual);
-    e->launches++;
-    MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
 

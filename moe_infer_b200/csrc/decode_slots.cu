@@ -573,6 +573,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         long long unused = 0;
         if (read_acc(n_layers + 1, true, (n_layers + 1) & 1, false, 0, unused)) {
             reinterpret_cast<float4*>(p.h_out)[tid] = hv;
+            // Leave the accumulators (hidden-state sets, then logit sets: one range) cleared for the next launch.  Nobody
+            // reads or adds to them any more: every CTA has passed its last read, the last layer pushes no logits, and
+            // the sums just read carried every contribution.  (A launch that fails leaves them to the host's reset.)
+            for (int i = tid; i < 2 * kH + 2 * kMaxE; i += kDecThreads) p.hacc[i] = 0ull;
         } else if (tid == 0) {
             atomicExch(p.err, 3u);
         }
@@ -660,8 +664,8 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
     p.prof = e->dec_prof;
     p.E = e->dims.num_experts;
     p.lay = e->lay;
-    // the accumulators are never cleared by the kernel (readers subtract what they saw before): start from zero
-    MOE_CUDA(cudaMemsetAsync(e->dec_sl_words, 0, kSlAccWords * sizeof(unsigned long long), e->stream));
+    // the accumulators start from zero: cleared at set-up and after an error by the host, at the end of every launch by
+    // the kernel's first CTA (a memset per launch cost a single-layer call about two microseconds of stream time)
     e->dec_sl_hint_base += (unsigned long long)kSG * (unsigned long long)(l1 - l0 + 1);  // one push per layer and the prologue's
     e->dec_sl_epoch += (unsigned int)(l1 - l0);
     void* args[] = {&p};
