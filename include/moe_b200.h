@@ -297,7 +297,11 @@ void moe_model_snapshot_free(moe_snapshot_t* snap);
  * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys
  * follow the reference (`engine.total_ms`, `phase.route_cpu_ms`, ...).  Fills up
  * to *n entries; on return *n is the number available.  Key pointers stay
- * valid until the next call on the same engine. */
+ * valid until the next call on the same engine.  With MOE_B200_DECODE_PREFETCH=1 in
+ * the environment when the engine is created, the decode kernel requests the next
+ * layer's copy of every chosen expert into L2 ahead of time (the reference's
+ * predictor, src/engine/qwen35_moe/expert_prefetch.rs:95-135) and the keys
+ * `prefetch.checks` / `prefetch.hits` count its predictions since creation. */
 void moe_set_record_telemetry(int on);
 int moe_get_record_telemetry(void);
 int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n);

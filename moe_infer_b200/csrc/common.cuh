@@ -211,6 +211,7 @@ struct moe_engine {
     bool dec_sl_ok = false;                     // device and model shape fit it
     unsigned long long* dec_sl_words = nullptr; // accumulators, tagged SwiGLU outputs, counters (one allocation)
     unsigned long long dec_sl_hint_base = 0;
+    bool dec_sl_prefetch = false;          // request the next layer's copy of a layer's experts into L2 (environment switch)
     unsigned int dec_sl_epoch = 0;
     bool matvec_attr_set = false;          // matvec kernel's shared-memory attribute set on this engine's device
     float* stage_host = nullptr;           // pinned staging [H] x 2

@@ -67,6 +67,8 @@ struct SlotParams {
     long long* prof;              // nullable: [layer][kSlProfPoints] SM-clock stamps taken by CTA 0
     int E;
     moe_expert_layout_t lay;
+    int prefetch_same;            // 1: request the next layer's copy of this layer's experts into L2 (the reference's predictor)
+    unsigned long long* pf_stats; // [2]: predictions checked, predictions that were among the next layer's experts
 };
 
 struct __align__(128) SlotSmem {
@@ -103,6 +105,7 @@ struct __align__(128) SlotSmem {
     float topw[kMaxK + 1];                   // combine weights; [K] = sigmoid(shared gate score)
     float topp[kMaxK];
     int topi[kMaxK];
+    int pred_prev;                           // the expert this CTA requested ahead for the layer now running (-1: none)
     int flag;
     uint64_t bar_g[2];                       // gate/up batches landed
     uint64_t bar_d;                          // down rows landed
@@ -331,6 +334,35 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         }
     };
 
+    // The reference hides expert fetches by assuming that layer L + 1 picks the experts layer L picked
+    // (src/engine/qwen35_moe/fused_exp6.rs:4-8, expert_prefetch.rs:95-135) and reading them ahead.  Here: once layer L is
+    // routed, a routed CTA asks for its own slices of the same expert in layer L + 1 to be brought into L2 (nine ranges, one
+    // per warp), and the first CTA of each group counts how often the expert it asked for was indeed chosen.  Off by default:
+    // with routers that are independent from layer to layer (the synthetic store) the guess is right 8 times in 256.
+    if (tid == 0) sm->pred_prev = -1;
+    auto prefetch_same_experts = [&](int rel) {
+        if (!p.prefetch_same || shared_slot) return;
+        if (tid == 0) {
+            if (sm->pred_prev >= 0 && grank == 0) {
+                bool hit = false;
+                for (int k = 0; k < K; ++k) hit = hit || sm->topi[k] == sm->pred_prev;
+                atomicAdd(p.pf_stats, 1ull);
+                if (hit) atomicAdd(p.pf_stats + 1, 1ull);
+            }
+            sm->pred_prev = (rel + 1 < n_layers) ? sm->topi[slot] : -1;
+        }
+        if (rel + 1 < n_layers && lane == 0 && warp < 9) {
+            const uint8_t* ex = sm->tab[rel + 1].experts + (size_t)sm->topi[slot] * L.expert_size;
+            const int a = warp;
+            const bool gu = a < 6;
+            const int64_t off = a == 0 ? L.gate_w : a == 1 ? L.up_w : a == 2 ? L.gate_s : a == 3 ? L.up_s : a == 4 ? L.gate_b : a == 5 ? L.up_b
+                              : a == 6 ? L.down_w : a == 7 ? L.down_s : L.down_b;
+            const uint32_t row_bytes = a < 2 ? kH / 2 : gu ? (kH / kGroup) * 2 : a == 6 ? kI / 2 : (kI / kGroup) * 2;
+            const int row = gu ? item0 : r0, rows = gu ? kItems : kDnRows;
+            prefetch_l2(ex + off + (size_t)row * row_bytes, (uint32_t)rows * row_bytes);
+        }
+    };
+
     // ── prologue: router logits of the first layer from h_in (the first group's rows cover all of h) ──
     {
         load_router_slice(rt, sm->tab[0].router_t, Ep, rt_row0, rt_e2);
@@ -387,6 +419,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
             SPROF(2);
             if (!shared_slot) request_weights(ly);
             SPROF(3);
+            prefetch_same_experts(rel);
             inv_rms = block_inv_rms(sm, hv);
             const float f1 = 1.0f / kLFix, f2 = inv_rms / pscale;
             if (tid < E) v = u * f1 * f2;
@@ -401,6 +434,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
             // ── weight requests (the shared expert's group made them at the top of the layer) ──
             if (!shared_slot) request_weights(ly);
             SPROF(3);
+            prefetch_same_experts(rel);
         }
         // the copies are on their way: stage x, the softmax weights of the chosen experts, and what the end of
         // the layer needs from the layer's input
@@ -588,7 +622,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
 
 constexpr size_t kSlAccWords = 2 * kH + 2 * kMaxE;          // hidden-state sets, then logit sets
 constexpr size_t kSlActWords = (size_t)kNSlots * kI;
-constexpr size_t kSlHintWords = (size_t)(kNSlots + 1) * kHintStride;  // per-group counters, then the layer counter
+constexpr size_t kSlHintWords = (size_t)(kNSlots + 2) * kHintStride;  // (unused group slots), the layer counter, the prefetch statistics
 
 // Decides once per engine whether this device and model shape can use the kernel; never fatal.
 int slots_decode_init(moe_engine* e) {
@@ -607,6 +641,10 @@ int slots_decode_init(moe_engine* e) {
     e->dec_sl_hint_base = 0;
     e->dec_sl_epoch = 0;
     e->dec_sl_ok = true;
+    {
+        const char* v = getenv("MOE_B200_DECODE_PREFETCH");
+        e->dec_sl_prefetch = v && atoi(v) != 0;
+    }
     return MOE_OK;
 }
 
@@ -629,6 +667,19 @@ int slots_decode_reset(moe_engine* e) {
     MOE_CUDA(cudaMemsetAsync(e->dec_sl_words, 0, (kSlAccWords + kSlActWords + kSlHintWords) * sizeof(unsigned long long), e->stream));
     e->dec_sl_hint_base = 0;
     e->dec_sl_epoch = 0;
+    return MOE_OK;
+}
+
+// predictions checked / predictions right since the engine was created (zero unless MOE_B200_DECODE_PREFETCH=1)
+int slots_decode_prefetch_stats(moe_engine* e, double* checks, double* hits) {
+    *checks = *hits = 0.0;
+    if (!e->dec_sl_ok || !e->dec_sl_prefetch) return MOE_OK;
+    unsigned long long v[2] = {0ull, 0ull};
+    const unsigned long long* src = e->dec_sl_words + kSlAccWords + kSlActWords + (size_t)kNSlots * kHintStride + kHintStride;
+    MOE_CUDA(cudaMemcpyAsync(v, src, sizeof(v), cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    *checks = (double)v[0];
+    *hits = (double)v[1];
     return MOE_OK;
 }
 
@@ -664,6 +715,8 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
     p.prof = e->dec_prof;
     p.E = e->dims.num_experts;
     p.lay = e->lay;
+    p.prefetch_same = e->dec_sl_prefetch ? 1 : 0;
+    p.pf_stats = e->dec_sl_words + kSlAccWords + kSlActWords + (size_t)kNSlots * kHintStride + kHintStride;
     // the accumulators start from zero: cleared at set-up and after an error by the host, at the end of every launch by
     // the kernel's first CTA (a memset per launch cost a single-layer call about two microseconds of stream time)
     e->dec_sl_hint_base += (unsigned long long)kSG * (unsigned long long)(l1 - l0 + 1);  // one push per layer and the prologue's

@@ -11,6 +11,7 @@
 #include <chrono>
 
 #include "common.cuh"
+#include "decode_common.cuh"
 
 namespace moe {
 
@@ -1026,6 +1027,14 @@ int moe_get_record_telemetry(void) { return g_record_telemetry.load(std::memory_
 int moe_telemetry_get(moe_engine_t* e, const char** keys, double* vals, int* n) {
     MOE_REQUIRE(e && n, "null argument");
     const int cap = *n;
+    if (e->dec_sl_prefetch) {
+        // the expert-prefetch predictor's record (the reference logs hits and misses of its own, expert_prefetch.rs:95-135)
+        double checks = 0.0, hits = 0.0;
+        int rc = slots_decode_prefetch_stats(e, &checks, &hits);
+        if (rc) return rc;
+        e->telemetry["prefetch.checks"] = checks;
+        e->telemetry["prefetch.hits"] = hits;
+    }
     e->tel_keys.clear();
     for (auto& kv : e->telemetry) e->tel_keys.push_back(kv.first);
     int i = 0;

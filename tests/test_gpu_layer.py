@@ -247,3 +247,32 @@ def test_nan_hidden_state_selects_valid_experts(full_layer):
     # the engine is still usable and still right
     again, idx_again, _ = eng.layer_forward(0, h[0])
     assert np.array_equal(again[0], eng.layer_forward(0, h[0])[0][0]) and np.isfinite(again).all()
+
+
+def test_same_expert_prefetch_option_changes_nothing_but_the_statistics(monkeypatch):
+    """MOE_B200_DECODE_PREFETCH=1: the decode kernel asks for the next layer's copy of each chosen expert ahead of time
+    (the reference's predictor, src/engine/qwen35_moe/expert_prefetch.rs:95-135).  A prefetch moves no data the kernel
+    computes with: results are bit-identical; the telemetry counts predictions and hits."""
+    layers = [make_layer(14, l, num_experts=16) for l in range(4)]
+    h = synth.hidden_states(14, 2, 3, 2048)
+
+    def run(flag):
+        if flag:
+            monkeypatch.setenv("MOE_B200_DECODE_PREFETCH", "1")
+        else:
+            monkeypatch.delenv("MOE_B200_DECODE_PREFETCH", raising=False)
+        eng = NativeEngine(Dims(num_experts=16, top_k=8, num_layers=4))
+        for l, lw in enumerate(layers):
+            upload_layer(eng, l, lw)
+        out = eng.forward_hidden(h)
+        tel = eng.telemetry()
+        eng.close()
+        return out, tel
+
+    base, tel0 = run(False)
+    pre, tel1 = run(True)
+    assert np.array_equal(base, pre)
+    assert "prefetch.checks" not in tel0
+    assert tel1["prefetch.checks"] == 3 * (4 - 1) * 8          # tokens x layer transitions x routed slots
+    assert 0 <= tel1["prefetch.hits"] <= tel1["prefetch.checks"]
+    print(f"same-expert predictor: {int(tel1['prefetch.hits'])} of {int(tel1['prefetch.checks'])} right (16 experts, top-8)")
