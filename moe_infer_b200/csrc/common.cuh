@@ -214,7 +214,8 @@ struct moe_engine {
     bool dec_sl_prefetch = false;          // request the next layer's copy of a layer's experts into L2 (environment switch)
     unsigned int dec_sl_epoch = 0;
     bool matvec_attr_set = false;          // matvec kernel's shared-memory attribute set on this engine's device
-    float* stage_host = nullptr;           // pinned staging [H] x 2
+    float* stage_host = nullptr;           // pinned staging [H] x 2, then 16 words (the device error word is read into the first)
+    bool err_read_pending = false;         // a read of the error word is enqueued behind the current call's work
     std::vector<float> last_h;             // last_h_pre_norm
     int64_t mtp_pos = 0;
 

@@ -1240,7 +1240,7 @@ int decode_init(moe_engine* e) {
     MOE_CUDA(cudaMalloc(&e->dec_sync, 16 * sizeof(unsigned int)));
     MOE_CUDA(cudaMemset(e->dec_sync, 0, 16 * sizeof(unsigned int)));
     e->dec_prof = nullptr;
-    MOE_CUDA(cudaMallocHost(&e->stage_host, (size_t)2 * d.hidden * sizeof(float)));
+    MOE_CUDA(cudaMallocHost(&e->stage_host, ((size_t)2 * d.hidden + 16) * sizeof(float)));  // + the error word's landing place
     MOE_CUDA(cudaMalloc(&e->dec_act_ll, kActLLWords * sizeof(unsigned long long)));
     MOE_CUDA(cudaMemset(e->dec_act_ll, 0, kActLLWords * sizeof(unsigned long long)));
     MOE_CUDA(cudaMalloc(&e->dec_hint, 256));  // two counters, a cache line apart

@@ -152,11 +152,25 @@ int check_layer_ready(moe_engine* e, int layer) {
     return MOE_OK;
 }
 
+// Enqueues the read of the device error word into pinned memory behind everything the call has launched, so that the
+// call's own synchronisation covers it (a separate copy + synchronise afterwards cost a host call about 10 us).
+static void error_read_enqueue(moe_engine* e) {
+    unsigned int* dst = reinterpret_cast<unsigned int*>(e->stage_host + 2 * (size_t)e->dims.hidden);
+    if (cudaMemcpyAsync(dst, e->dec_sync + 2, sizeof(unsigned int), cudaMemcpyDeviceToHost, e->stream) == cudaSuccess)
+        e->err_read_pending = true;
+}
+
 // Reads and clears the device error word; maps it to a status.
 static int poll_device_error(moe_engine* e) {
     unsigned int flag = 0;
-    MOE_CUDA(cudaMemcpyAsync(&flag, e->dec_sync + 2, sizeof(flag), cudaMemcpyDeviceToHost, e->stream));
-    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    if (e->err_read_pending) {
+        e->err_read_pending = false;
+        MOE_CUDA(cudaStreamSynchronize(e->stream));  // returns at once when the caller has synchronised already
+        flag = *reinterpret_cast<volatile unsigned int*>(e->stage_host + 2 * (size_t)e->dims.hidden);
+    } else {
+        MOE_CUDA(cudaMemcpyAsync(&flag, e->dec_sync + 2, sizeof(flag), cudaMemcpyDeviceToHost, e->stream));
+        MOE_CUDA(cudaStreamSynchronize(e->stream));
+    }
     if (flag != 0) {
         cudaMemsetAsync(e->dec_sync, 0, 16 * sizeof(unsigned int), e->stream);
         cudaStreamSynchronize(e->stream);
@@ -614,6 +628,7 @@ int moe_layer_forward_host(moe_engine_t* e, int layer, const float* h_in, int32_
             ce = cudaMemcpyAsync(out_idx, d_oi, (size_t)n * d.top_k * 4, cudaMemcpyDeviceToHost, e->stream);
         if (ce == cudaSuccess && out_w)
             ce = cudaMemcpyAsync(out_w, d_ow, (size_t)n * d.top_k * 4, cudaMemcpyDeviceToHost, e->stream);
+        if (ce == cudaSuccess) error_read_enqueue(e);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "layer_forward_host download", __FILE__, __LINE__); break; }
         rc = poll_device_error(e);
@@ -701,6 +716,7 @@ int moe_forward_hidden_host(moe_engine_t* e, const float* emb, int32_t n, int ba
         ce = cudaMemcpyAsync(out, d_out, hb, cudaMemcpyDeviceToHost, e->stream);
         if (rec && ce == cudaSuccess) ce = cudaEventRecord(t1, e->stream);
         const auto host_t1 = std::chrono::steady_clock::now();
+        if (ce == cudaSuccess) error_read_enqueue(e);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
         const auto host_t2 = std::chrono::steady_clock::now();
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward_hidden download", __FILE__, __LINE__); break; }
@@ -808,6 +824,7 @@ int moe_forward_host(moe_engine_t* e, const int64_t* ids, int32_t n, int batched
         if (ce == cudaSuccess)
             ce = cudaMemcpyAsync(e->stage_host, d_out + (size_t)(n - 1) * d.hidden, (size_t)d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
         const auto host_t1 = std::chrono::steady_clock::now();
+        if (ce == cudaSuccess) error_read_enqueue(e);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
         const auto host_t2 = std::chrono::steady_clock::now();
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "forward download", __FILE__, __LINE__); break; }
@@ -868,6 +885,7 @@ int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, fl
         return rc;
     }
     MOE_CUDA(cudaMemcpyAsync(logits_host, logits_dev, lb, cudaMemcpyDeviceToHost, e->stream));
+    error_read_enqueue(e);
     MOE_CUDA(cudaStreamSynchronize(e->stream));
     rc = poll_device_error(e);
     if (rc == MOE_OK) e->mtp_pos++;
@@ -978,6 +996,7 @@ static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, 
         }
         if (ce == cudaSuccess)
             ce = cudaMemcpyAsync(e->stage_host, d_out + (size_t)(n - 1) * d.hidden, (size_t)d.hidden * 4, cudaMemcpyDeviceToHost, e->stream);
+        if (ce == cudaSuccess) error_read_enqueue(e);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward download", __FILE__, __LINE__); break; }
         if ((rc = poll_device_error(e))) break;
