@@ -5,6 +5,7 @@
 // Everything here is a matrix-vector product or smaller: HBM-bound streaming kernels and a few tiny ones.
 // Projections are bf16 matrices in the BQ4 scheme (bq4.rs:25-32) and 4-bit triples in the INT4 scheme.
 #include "common.cuh"
+#include "stage.cuh"
 
 namespace moe {
 
@@ -17,10 +18,20 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
                                                                    float* __restrict__ y, int rows, int cols,
                                                                    const float* __restrict__ residual) {  // nullable: y = W x + residual
     extern __shared__ float xs[];
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = x[i];
-    __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int stride = gridDim.x * kBfWarps * 2;
+    pdl_trigger();
+    // the weights do not depend on x: ask for this warp's rows (L2) while the kernel that produces x still runs
+    if ((cols & 7) == 0) {
+        const int r = (blockIdx.x * kBfWarps + warp) * 2 + (lane >> 1) * stride + (lane & 1);
+        if (lane < 16 && r < rows) {
+            const unsigned char* wr = reinterpret_cast<const unsigned char*>(w + (size_t)r * cols);
+            for (int off = 0; off < cols * 2; off += 4096) prefetch_l2(wr + off, (uint32_t)min(4096, cols * 2 - off));
+        }
+    }
+    pdl_wait();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = x[i];
+    __syncthreads();
     for (int r0 = (blockIdx.x * kBfWarps + warp) * 2; r0 < rows; r0 += stride) {
         const bool two = r0 + 1 < rows;
         const uint16_t* wa = w + (size_t)r0 * cols;
@@ -55,6 +66,8 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float* __restr
     __shared__ float red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* row = x + (size_t)blockIdx.x * dim;
+    pdl_trigger();
+    pdl_wait();
     float ss = 0.0f;
     for (int i = tid; i < dim; i += 256) ss = fmaf(row[i], row[i], ss);
     ss = warp_sum(ss);
@@ -82,6 +95,8 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
                                                         int head_dim, int rope_dim, int pos_value, const int* __restrict__ pos_ptr,
                                                         float theta, float* __restrict__ q_out,
                                                         float* __restrict__ k_cache, float* __restrict__ v_cache) {
+    pdl_trigger();
+    pdl_wait();
     const int pos = pos_ptr ? *pos_ptr : pos_value;  // a device-side position keeps the launch replayable (CUDA graph)
     extern __shared__ float hv[];  // the normed head
     __shared__ float red[8];
@@ -132,6 +147,8 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
                                                           const float* __restrict__ v_cache, const float* __restrict__ gate,
                                                           int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_value,
                                                           const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int seq_len = pos_ptr ? *pos_ptr + 1 : seq_value;
     extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head
     __shared__ float red[8];
@@ -212,6 +229,16 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
     float* vals = vs + value_dim;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.x, kh = h / k_heads_per_v;
+    pdl_trigger();
+    // this head's recurrence state was last written a token ago: ask for it (L2) while the projections still run
+    {
+        const size_t bytes = (size_t)value_dim * key_dim * 4;
+        const unsigned char* sp = reinterpret_cast<const unsigned char*>(state + (size_t)h * value_dim * key_dim);
+        if ((bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0)
+            for (size_t off = (size_t)tid * 4096; off < bytes; off += (size_t)kLinThreads * 4096)
+                prefetch_l2(sp + off, (uint32_t)(bytes - off < 4096 ? bytes - off : 4096));
+    }
+    pdl_wait();
     const int pos = *pos_ptr;
     // 1. conv + SiLU of this head's channels, and the ring update
     const int n_ch = 2 * key_dim + value_dim;
@@ -455,17 +482,17 @@ int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, cons
 }
 
 // y = W x (+ residual) for a projection stored as bf16 rows or as a 4-bit triple
-static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr) {
-    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual);
+static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr, bool pdl = false) {
+    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual, pdl);
     if (!e->mtp.bf_attr_set) {
         MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
         e->mtp.bf_attr_set = true;
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
     if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
-    matvec_bf16_kernel<<<blocks, kBfWarps * 32, (size_t)t.cols * 4, e->stream>>>(reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual);
+    MOE_CUDA(launch_kernel(pdl, matvec_bf16_kernel, dim3(blocks), dim3(kBfWarps * 32), (size_t)t.cols * 4, e->stream,
+                           reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual));
     e->launches++;
-    MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
 
@@ -829,6 +856,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         return ok;
     };
     if (!need(MOE_A_INPUT_NORM)) return MOE_ERR_STATE;
+    const bool pdl = a.pdl;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
     rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x);
     e->launches++;
     int rc;
@@ -840,20 +868,20 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* kb = qb + 2 * z.q_dim;
         float* vb = kb + z.kv_dim;
         if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, x, proj_out))) return rc;
+            if ((rc = proj_run(e, ls.fused, x, proj_out, nullptr, pdl))) return rc;
         } else {
-            if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, qb))) return rc;
-            if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb))) return rc;
-            if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, qb, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb, nullptr, pdl))) return rc;
         }
-        attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(qb, 2 * hd, 1, kb, vb, (const uint16_t*)ls.vec[MOE_A_Q_NORM],
-                                                              (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd, d.full.rotary_dim, 0,
-                                                              a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache);
+        MOE_CUDA(launch_kernel(pdl, attn_prep_kernel, dim3(nh + nkv), dim3(256), (size_t)hd * 4, st, qb, 2 * hd, 1, kb, vb,
+                               (const uint16_t*)ls.vec[MOE_A_Q_NORM], (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd,
+                               d.full.rotary_dim, 0, a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache));
         // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
-        attn_decode_kernel<<<nh, 256, (size_t)(d.full.max_seq + hd) * 4, st>>>(qr, ls.k_cache, ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0,
-                                                                              a.d_pos, 1.0f / sqrtf((float)hd), vals);
+        MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(256), (size_t)(d.full.max_seq + hd) * 4, st, qr, ls.k_cache,
+                               ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, a.d_pos, 1.0f / sqrtf((float)hd), vals));
         e->launches += 2;
-        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h))) return rc;  // + residual
+        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h, pdl))) return rc;  // + residual
     } else {
         for (int w : {MOE_A_IN_PROJ_QKV, MOE_A_IN_PROJ_Z, MOE_A_IN_PROJ_B, MOE_A_IN_PROJ_A, MOE_A_OUT_PROJ})
             if (!need(w)) return MOE_ERR_STATE;
@@ -862,26 +890,22 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* bb = zb + z.total_value;
         float* ab = bb + Hv;
         if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, x, proj_out))) return rc;
+            if ((rc = proj_run(e, ls.fused, x, proj_out, nullptr, pdl))) return rc;
         } else {
-            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, qkv_raw))) return rc;
-            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb))) return rc;
-            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb))) return rc;
-            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, qkv_raw, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab, nullptr, pdl))) return rc;
         }
         const size_t lin_smem = (size_t)(2 * d.lin_key_dim + 2 * d.lin_value_dim) * 4;
-        if (d.lin_key_dim <= 128)
-            lin_core_kernel<4><<<d.lin_num_v_heads, kLinThreads, lin_smem, st>>>(
-            ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
-            (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed, a.d_pos,
-            (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim);
-        else
-            lin_core_kernel<8><<<d.lin_num_v_heads, kLinThreads, lin_smem, st>>>(
-            ls.conv_state, qkv_raw, (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
-            (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed, a.d_pos,
-            (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim);
+        auto* lin_kernel = d.lin_key_dim <= 128 ? lin_core_kernel<4> : lin_core_kernel<8>;
+        MOE_CUDA(launch_kernel(pdl, lin_kernel, dim3(d.lin_num_v_heads), dim3(kLinThreads), lin_smem, st, ls.conv_state, qkv_raw,
+                               (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
+                               (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed,
+                               a.d_pos, (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads,
+                               d.lin_key_dim, d.lin_value_dim));
         e->launches++;
-        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h))) return rc;  // + residual
+        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h, pdl))) return rc;  // + residual
     }
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
@@ -889,11 +913,16 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
 
 // Captures every layer's attention half (fixed pointers, position read on the device) into a CUDA graph: a token then
 // costs one graph launch + the MoE launch per layer instead of a dozen launches issued one by one from the host.
-// MOE_B200_ATTN_GRAPHS=0 keeps the eager launches.
+// Inside a graph (and in the eager path alike) every kernel after the first is a programmatic dependent of the one
+// before it: it becomes resident while its predecessor still runs, asks for its weights (L2 prefetch) and only then
+// waits for the predecessor's results.  MOE_B200_ATTN_GRAPHS=0 keeps the eager launches, MOE_B200_ATTN_PDL=0 the
+// ordinary dependencies.
 static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float* h_mid, float* scratch) {
     ModelAttnState& a = e->attn;
     attn_drop_graphs(e);
     const char* env = getenv("MOE_B200_ATTN_GRAPHS");
+    const char* env_pdl = getenv("MOE_B200_ATTN_PDL");
+    a.pdl = !(env_pdl && atoi(env_pdl) == 0);
     const int L = e->dims.num_layers;
     a.graphs.assign((size_t)L, nullptr);
     a.graph_nodes.assign((size_t)L, 0);

@@ -179,6 +179,7 @@ struct ModelAttnState {
     std::vector<cudaGraphExec_t> graphs;     // one captured attention half per layer (null: launch eagerly)
     std::vector<int> graph_nodes;            // kernels in each
     bool graphs_valid = false;
+    bool pdl = true;                         // kernels of a layer's attention half start ahead of their predecessor's end
 };
 
 }  // namespace moe
@@ -247,7 +248,7 @@ int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, in
 int matvec_prepare(moe_engine* e);
 // y = W x + residual (residual nullable; may not alias y)
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x, float* y, int32_t rows,
-                      int32_t cols, const float* residual);
+                      int32_t cols, const float* residual, bool pdl = false);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);
@@ -323,6 +324,31 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
+
+// Programmatic dependent launch.  A kernel launched with the attribute (launch_kernel below, pdl = true) may start
+// while the kernel before it in the stream is still running.  The rule every kernel of such a chain keeps: before
+// pdl_wait() it touches only bytes that no kernel writes (weights) and its own shared memory; pdl_wait() returns once
+// the preceding kernel has completed and its writes are visible, and since that kernel waited in the same way, so has
+// everything before it.  pdl_trigger() lets the next kernel of the chain become resident; both are no-ops in a
+// kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
+
+// Kernel launch with or without the programmatic-dependent-launch attribute (see pdl_wait above).
+template <typename... P, typename... A>
+inline cudaError_t launch_kernel(bool pdl, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
 
 }  // namespace moe

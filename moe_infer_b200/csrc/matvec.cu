@@ -27,18 +27,28 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
     __shared__ uint64_t bar;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
     if (tid == 0) {
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
+    // nothing about the weights depends on x: ask for this warp's rows (L2) while the kernel that produces x still runs
+    const int groups = cols / kGroup;
+    const int row_first = blockIdx.x * kMvWarps + warp;
+    {
+        const int row = row_first + lane * (int)gridDim.x * kMvWarps;
+        if (lane < 8 && row < rows) {
+            const unsigned char* wr = reinterpret_cast<const unsigned char*>(w + (size_t)row * (cols / 8));
+            for (int off = 0; off < cols / 2; off += 4096) prefetch_l2(wr + off, (uint32_t)min(4096, cols / 2 - off));
+        }
+    }
     __syncthreads();
+    pdl_wait();
     if (tid == 0) {
         mbar_expect_tx(&bar, (uint32_t)cols * 4u);
         bulk_g2s(raw, x, (uint32_t)cols * 4u, &bar);
     }
     // the first two chunks of this warp's first row do not depend on x: request them before waiting for it
-    const int groups = cols / kGroup;
-    const int row_first = blockIdx.x * kMvWarps + warp;
     uint4 pqa = make_uint4(0, 0, 0, 0), pqb = pqa;
     uint16_t psa = 0, pba = 0, psb = 0, pbb = 0;
     if (row_first < rows) {
@@ -124,11 +134,24 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
     __shared__ float sumx[nch];
     __shared__ uint64_t bar;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
     if (tid == 0) {
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
+    // the weights do not depend on x: ask for this warp's first rows (L2) while the kernel that produces x still runs
+    {
+        const int row = blockIdx.x * kSvWarps + warp + lane * (int)gridDim.x * kSvWarps;
+        if (lane < 16 && row < rows) {
+            prefetch_l2(w + (size_t)row * (kSvCols / 8), kSvCols / 2);
+            if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(b)) & 15) == 0) {
+                prefetch_l2(s + (size_t)row * (kSvCols / kGroup), kSvCols / kGroup * 2);
+                prefetch_l2(b + (size_t)row * (kSvCols / kGroup), kSvCols / kGroup * 2);
+            }
+        }
+    }
     __syncthreads();
+    pdl_wait();
     if (tid == 0) {
         mbar_expect_tx(&bar, kSvCols * 4u);
         bulk_g2s(raw, x, kSvCols * 4u, &bar);
@@ -204,7 +227,7 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
 }
 
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
-                      float* y, int32_t rows, int32_t cols, const float* residual) {
+                      float* y, int32_t rows, int32_t cols, const float* residual, bool pdl) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
@@ -213,10 +236,9 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
         int blocks = (rows + kSvWarps * kSvUnroll - 1) / (kSvWarps * kSvUnroll);
         const int cap = e->sm_count * 2;
         if (blocks > cap) blocks = cap;
-        matvec_int4_stream_kernel<<<blocks, kSvWarps * 32, 0, e->stream>>>(
-            (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual);
+        MOE_CUDA(launch_kernel(pdl, matvec_int4_stream_kernel, dim3(blocks), dim3(kSvWarps * 32), 0, e->stream, (const uint32_t*)w,
+                               (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual));
         e->launches++;
-        MOE_CUDA(cudaGetLastError());
         return MOE_OK;
     }
     const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
@@ -226,10 +248,9 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
     // every CTA stages the whole x: with long rows fewer CTAs, each taking several rows per warp, amortise that better
     const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
     if (blocks > cap) blocks = cap;
-    matvec_int4_kernel<<<blocks, kMvWarps * 32, smem, e->stream>>>(
-        (const uint32_t*)w, (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual);
+    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
+                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual));
     e->launches++;
-    MOE_CUDA(cudaGetLastError());
     return MOE_OK;
 }
 
