@@ -292,6 +292,19 @@ typedef struct moe_snapshot moe_snapshot_t;
 int moe_model_snapshot(moe_engine_t* e, moe_snapshot_t** out);
 int moe_model_restore(moe_engine_t* e, const moe_snapshot_t* snap);
 void moe_model_snapshot_free(moe_snapshot_t* snap);
+/* Engine::download_cache / upload_cache and what Cache::save / load put on disk (src/engine.rs:64-79,
+ * src/cache.rs:133-233): one state tensor of one layer, device -> host (to_device == 0) or host -> device.
+ *   MOE_ST_K_CACHE / MOE_ST_V_CACHE (full-attention layers): the first floats / kv_dim positions, [position, kv_dim];
+ *   MOE_ST_CONV (linear-attention layers): [conv_kernel, conv_dim], the input of step s in row s % conv_kernel (a ring;
+ *       the reference keeps the last conv_kernel - 1 inputs oldest first, src/math_util.rs:149-168: row k of that
+ *       layout is row (pos - (conv_kernel - 1) + k) mod conv_kernel here, zeros for steps before the start);
+ *   MOE_ST_SSM: the recurrence state [v_heads, value_dim, key_dim].
+ * `floats` must be the tensor's size (for the caches: a multiple of kv_dim, at most max_seq positions).  MOE_ERR_INVALID
+ * for a tensor the layer does not have.  moe_model_set_pos moves the position the next decode step runs at (after an
+ * upload; 0 <= pos <= max_seq). */
+typedef enum { MOE_ST_K_CACHE = 0, MOE_ST_V_CACHE = 1, MOE_ST_CONV = 2, MOE_ST_SSM = 3 } moe_state_tensor_t;
+int moe_model_state_host(moe_engine_t* e, int32_t layer, int32_t which, float* host, int64_t floats, int32_t to_device);
+int moe_model_set_pos(moe_engine_t* e, int64_t pos);
 
 /* ── telemetry ───────────────────────────────────────────────────────────────
  * set_record_telemetry / Engine::telemetry (src/engine.rs:13-23, 80-84); keys

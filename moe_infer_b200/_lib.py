@@ -48,6 +48,7 @@ class ModelAttnDims(C.Structure):
 
 (A_INPUT_NORM, A_Q_PROJ, A_K_PROJ, A_V_PROJ, A_Q_NORM, A_K_NORM, A_O_PROJ, A_IN_PROJ_QKV, A_IN_PROJ_Z, A_IN_PROJ_B, A_IN_PROJ_A,
  A_CONV1D, A_A_LOG, A_DT_BIAS, A_LIN_NORM, A_OUT_PROJ) = range(16)
+ST_K_CACHE, ST_V_CACHE, ST_CONV, ST_SSM = range(4)  # moe_state_tensor_t
 
 
 class LayerPtrs(C.Structure):
@@ -105,6 +106,8 @@ SIGNATURES = {
     "moe_model_snapshot": (_i, [_vp, _pp]),
     "moe_model_restore": (_i, [_vp, _vp]),
     "moe_model_snapshot_free": (None, [_vp]),
+    "moe_model_state_host": (_i, [_vp, _i32, _i32, _vp, _i64, _i32]),
+    "moe_model_set_pos": (_i, [_vp, _i64]),
     "moe_mtp_reset": (_i, [_vp]),
     "moe_mtp_rollback": (_i, [_vp, _i64]),
     "moe_mtp_pos": (_i, [_vp, C.POINTER(_i64)]),

@@ -7,17 +7,21 @@ reference binding: ``Model``, ``Cache``, ``Engine``, ``PyEngineSnapshot``,
 CUDA library; nothing here computes the MoE path on the CPU.
 
 Where this surface departs from the reference, and how the calls behave:
-  * attention / DeltaNet are passed through (each block is h <- h + moe(rmsnorm(h)));
+  * a model directory that has the attention tensors of every layer runs the whole decoder (gated full attention /
+    Gated DeltaNet half + MoE half per layer) on the GPU, one decode step per token, ``forward_batched`` included;
+    a directory with the MoE tensors only is still accepted and then each block is h <- h + moe(rmsnorm(h));
   * ``forward`` / ``forward_batched`` / ``forward_hidden`` return logits float32 [n, vocab] like the reference
     (embedding rows, stack, final norm and lm_head all on the GPU).  They raise ``RuntimeError`` naming the missing
     tensor when the model directory has no embedding table, final norm or lm_head, instead of returning zeros
     (the reference's ``embed_lookup`` silently fills zeros, src/math_util.rs:211-214);
   * ``forward_hidden_states`` (not in the reference) returns the hidden states before the final norm,
     float32 [n, hidden], and needs no head tensors;
-  * ``mtp_forward(token_id)`` runs the MoE half of the MTP block on ``last_h_pre_norm`` and returns
-    float32 [hidden], not logits: the block's embedding / fc / attention half is not built, so the token id is
-    only range-checked (an empty array when the model has no MTP block, like the reference);
-  * ``Cache.save`` writes an empty state file: the MoE path keeps no per-sequence state (only ``pos``).
+  * ``mtp_forward(token_id)`` is the reference's draft step (logits float32 [vocab]) when the directory has the MTP
+    block's tensors and the head; without them only the block's MoE half runs on ``last_h_pre_norm`` and the result
+    is float32 [hidden] (an empty array when the model has no MTP block, like the reference);
+  * ``Cache`` holds the per-sequence state in the reference's layout and file format (src/cache.rs:133-233); while a
+    sequence runs the state lives on the device and ``download_cache`` / ``upload_cache`` move it.  A cache whose
+    position is not 0 but which carries no state is refused (the reference would run on zeros).
 """
 from __future__ import annotations
 
@@ -53,41 +57,139 @@ class Model:
         return f"Model({self.inner.get('num_hidden_layers', 0)} layers, hidden={self.inner.get('hidden_size', 0)})"
 
 
+MAX_SEQ = 4096  # src/constants.rs:12: positions a KV cache holds, and the row count of the cache tensors on disk
+
+
+def _shifted_from_ring(ring: np.ndarray, pos: int) -> np.ndarray:
+    """The device keeps the last conv inputs as a ring (input of step s in row s % kernel); the reference keeps the
+    last kernel - 1 inputs oldest first (src/math_util.rs:149-168).  Row k of that layout is the input of step
+    pos - (kernel - 1) + k."""
+    ks = ring.shape[0]
+    return np.stack([ring[(pos - (ks - 1) + k) % ks] for k in range(ks - 1)]) if ks > 1 else ring[:0].copy()
+
+
+def _ring_from_shifted(shifted: np.ndarray, pos: int) -> np.ndarray:
+    ks = shifted.shape[0] + 1
+    ring = np.zeros((ks, shifted.shape[1]), np.float32)
+    for k in range(ks - 1):
+        ring[(pos - (ks - 1) + k) % ks] = shifted[k]
+    return ring
+
+
 class Cache:
-    """src/python_bindings.rs:64-100.  The MoE path is stateless; only the position and the
-    dirty flags of the reference's cache (src/cache.rs:32-42) are kept."""
+    """src/python_bindings.rs:64-100, src/cache.rs:32-233: the per-sequence state on the host side.  Full-attention
+    layers: K and V rows of the positions so far; linear-attention layers: the last conv inputs and the recurrence
+    state; and the position.  The state itself lives on the device while a sequence runs (``gpu_dirty``);
+    ``Engine.download_cache`` brings it here, ``save`` / ``load`` use the reference's file format (a flat binary of
+    float32 tensors plus a JSON manifest ``{"tensors": {name: {offset, size, shape, dtype}}}``), so a file written by
+    either implementation loads in the other.  ``states is None`` means the all-zero state of a new sequence.
+    A model directory without the attention keys in its config (MoE halves only) has no state beyond ``pos``."""
 
     def __init__(self, model: Model):
         self.pos = 0
-        self.cpu_dirty = False
+        self.cpu_dirty = True   # the device has nothing of this cache yet (src/cache.rs:75)
         self.gpu_dirty = False
+        self.states: Optional[list] = None
+        self.layout = self._layout_of(model.inner)
+
+    @staticmethod
+    def _layout_of(m) -> Optional[dict]:
+        need = ("num_hidden_layers", "num_key_value_heads", "head_dim")
+        if any(not m.get(k) for k in need):
+            return None
+        vh, kh = int(m.get("linear_num_value_heads", 0) or 0), int(m.get("linear_num_key_heads", 0) or 0)
+        kd, vd = int(m.get("linear_key_head_dim", 0) or 0), int(m.get("linear_value_head_dim", 0) or 0)
+        return dict(layers=int(m.get("num_hidden_layers")), kv_dim=int(m.get("num_key_value_heads")) * int(m.get("head_dim")),
+                    v_heads=vh, key_dim=kd, value_dim=vd, conv_dim=2 * kh * kd + vh * vd, has_linear=vh > 0 and kh > 0,
+                    conv_kernel=int(m.get("linear_conv_kernel_dim", 4)), interval=int(m.get("full_attention_interval", 4)))
+
+    def is_full(self, layer: int) -> bool:
+        lay = self.layout
+        return not lay["has_linear"] or (layer + 1) % lay["interval"] == 0   # src/cache.rs:63-65
 
     def reset(self) -> None:
+        """src/cache.rs:84-94: position 0, zero conv and recurrence states."""
         self.pos = 0
-        self.cpu_dirty = False
+        self.states = None
+        self.cpu_dirty = True
         self.gpu_dirty = False
 
+    def _zero_states(self) -> list:
+        lay, out = self.layout, []
+        for l in range(lay["layers"]):
+            if self.is_full(l):
+                out.append({"k_cache": np.zeros((0, lay["kv_dim"]), np.float32), "v_cache": np.zeros((0, lay["kv_dim"]), np.float32)})
+            else:
+                out.append({"conv_state": np.zeros((lay["conv_kernel"] - 1, lay["conv_dim"]), np.float32),
+                            "ssm_state": np.zeros(lay["v_heads"] * lay["value_dim"] * lay["key_dim"], np.float32)})
+        return out
+
     def save(self, bin_path: str, json_path: str) -> None:
+        """src/cache.rs:133-175.  K / V tensors are written with MAX_SEQ rows like the reference's."""
         if self.gpu_dirty:
             print("[cache] WARNING: saving cache with gpu_dirty=true", file=sys.stderr)
+        tensors, offset = {}, 0
         try:
-            with open(bin_path, "wb"):
-                pass
+            with open(bin_path, "wb") as f:
+                def put(name, arr, shape, dtype="float32"):
+                    nonlocal offset
+                    raw = arr.tobytes()
+                    f.write(raw)
+                    tensors[name] = {"offset": offset, "size": len(raw), "shape": list(shape), "dtype": dtype}
+                    offset += len(raw)
+
+                if self.layout is not None:
+                    states = self.states if self.states is not None else self._zero_states()
+                    kv_dim = self.layout["kv_dim"]
+                    for l, st in enumerate(states):
+                        if "k_cache" in st:
+                            for key in ("k_cache", "v_cache"):
+                                full = np.zeros((MAX_SEQ, kv_dim), np.float32)
+                                full[:st[key].shape[0]] = st[key]
+                                put(f"cache.layer_{l}.{key}", full, (MAX_SEQ, kv_dim))
+                            put(f"cache.layer_{l}.len", np.uint32(self.pos), (), "uint32")
+                        else:
+                            put(f"cache.layer_{l}.conv_state", st["conv_state"], st["conv_state"].shape)
+                            put(f"cache.layer_{l}.ssm_state", st["ssm_state"], (st["ssm_state"].size,))
+                put("cache.pos", np.uint32(self.pos), (), "uint32")
             with open(json_path, "w") as f:
-                json.dump({"pos": self.pos}, f)
+                json.dump({"tensors": tensors}, f, indent=2)
         except OSError as e:
             raise IOError(str(e)) from e
 
     @staticmethod
     def load(bin_path: str, json_path: str) -> "Cache":
+        """src/cache.rs:177-233: the layer kinds are read off the manifest's tensor names."""
         try:
             with open(json_path) as f:
-                meta = json.load(f)
-            os.stat(bin_path)
-        except (OSError, ValueError) as e:
+                tensors = json.load(f)["tensors"]
+            raw = np.fromfile(bin_path, np.uint8)
+        except (OSError, ValueError, KeyError) as e:
             raise IOError(str(e)) from e
+
+        def get(name, dtype):
+            if name not in tensors:
+                raise IOError(f"missing tensor: {name}")
+            t = tensors[name]
+            return raw[int(t["offset"]):int(t["offset"]) + int(t["size"])].view(dtype)
+
         c = Cache.__new__(Cache)
-        c.pos, c.cpu_dirty, c.gpu_dirty = int(meta.get("pos", 0)), True, False
+        c.pos = int(get("cache.pos", np.uint32)[0])
+        c.cpu_dirty, c.gpu_dirty, c.states, c.layout = True, False, None, None
+        states, l = [], 0
+        while f"cache.layer_{l}.k_cache" in tensors or f"cache.layer_{l}.conv_state" in tensors:
+            if f"cache.layer_{l}.k_cache" in tensors:
+                n = int(get(f"cache.layer_{l}.len", np.uint32)[0])
+                shape = tensors[f"cache.layer_{l}.k_cache"]["shape"]
+                states.append({key: get(f"cache.layer_{l}.{key}", np.float32).reshape(shape)[:n].copy() for key in ("k_cache", "v_cache")})
+            else:
+                shape = tensors[f"cache.layer_{l}.conv_state"]["shape"]
+                states.append({"conv_state": get(f"cache.layer_{l}.conv_state", np.float32).reshape(shape).copy(),
+                               "ssm_state": get(f"cache.layer_{l}.ssm_state", np.float32).copy()})
+            l += 1
+        if states:
+            c.states = states
+            c.layout = {"layers": len(states), "from_file": True}
         return c
 
     def __repr__(self) -> str:
@@ -361,10 +463,54 @@ class Engine:
         return self._forward_ids(tokens, cache, True, mtp)
 
     def upload_cache(self, cache: Cache) -> None:
+        """src/engine.rs:64-71: the cache's state becomes the device's (a cache without states: a new sequence)."""
+        if not self._missing_attn:
+            eng = self.native
+            try:
+                if cache.states is None:
+                    if cache.pos != 0:
+                        raise RuntimeError(f"the cache is at position {cache.pos} but carries no state: attention state cannot "
+                                           "be rebuilt from a position alone")
+                    eng.model_reset()
+                else:
+                    if len(cache.states) != self.dims.num_layers:
+                        raise RuntimeError(f"the cache holds {len(cache.states)} layers, the model {self.dims.num_layers}")
+                    for l, st in enumerate(cache.states):
+                        if "k_cache" in st:
+                            if st["k_cache"].shape[0] < cache.pos:
+                                raise RuntimeError(f"layer {l}: the cache holds {st['k_cache'].shape[0]} positions, pos is {cache.pos}")
+                            eng.model_state_upload(l, L.ST_K_CACHE, st["k_cache"][:cache.pos])
+                            eng.model_state_upload(l, L.ST_V_CACHE, st["v_cache"][:cache.pos])
+                        else:
+                            eng.model_state_upload(l, L.ST_CONV, _ring_from_shifted(st["conv_state"], cache.pos))
+                            eng.model_state_upload(l, L.ST_SSM, st["ssm_state"])
+                eng.model_set_pos(cache.pos)
+            except L.MoeError as e:
+                raise RuntimeError(str(e)) from e
         self.pos = cache.pos
         cache.cpu_dirty = False
 
     def download_cache(self, cache: Cache) -> None:
+        """src/engine.rs:72-79: the device's state becomes the cache's."""
+        if not self._missing_attn:
+            eng, pos = self.native, self.native.model_pos()
+            lay = Cache._layout_of(self.model.inner)
+            probe = Cache.__new__(Cache)
+            probe.layout = lay
+            states = []
+            try:
+                for l in range(self.dims.num_layers):
+                    if probe.is_full(l):
+                        states.append({"k_cache": eng.model_state_download(l, L.ST_K_CACHE, pos * lay["kv_dim"]).reshape(pos, lay["kv_dim"]),
+                                       "v_cache": eng.model_state_download(l, L.ST_V_CACHE, pos * lay["kv_dim"]).reshape(pos, lay["kv_dim"])})
+                    else:
+                        ring = eng.model_state_download(l, L.ST_CONV, lay["conv_kernel"] * lay["conv_dim"])
+                        states.append({"conv_state": _shifted_from_ring(ring.reshape(lay["conv_kernel"], lay["conv_dim"]), pos),
+                                       "ssm_state": eng.model_state_download(l, L.ST_SSM, lay["v_heads"] * lay["value_dim"] * lay["key_dim"])})
+            except L.MoeError as e:
+                raise RuntimeError(str(e)) from e
+            cache.states, cache.layout = states, lay
+            self.pos = pos
         cache.pos = self.pos
         cache.gpu_dirty = False
 

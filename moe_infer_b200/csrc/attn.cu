@@ -644,6 +644,46 @@ int attn_reset(moe_engine* e) {
     return MOE_OK;
 }
 
+// One state tensor of one layer between the device and host memory (which: moe_state_tensor_t).
+int attn_state_io(moe_engine* e, int layer, int which, float* host, int64_t floats, bool to_device) {
+    ModelAttnState& a = e->attn;
+    MOE_REQUIRE(a.configured, "the attention halves are not configured (moe_attn_configure)");
+    MOE_REQUIRE(layer >= 0 && layer < (int)a.layers.size(), "layer %d outside [0, %d)", layer, (int)a.layers.size());
+    const AttnSizes z = attn_sizes(e);
+    AttnLayerState& ls = a.layers[layer];
+    float* dev = nullptr;
+    int64_t want = 0;
+    switch (which) {
+    case MOE_ST_K_CACHE:
+    case MOE_ST_V_CACHE:
+        MOE_REQUIRE(ls.full, "layer %d is a linear-attention layer: it has no KV cache", layer);
+        MOE_REQUIRE(floats >= 0 && floats % (int64_t)z.kv_dim == 0 && floats <= (int64_t)a.d.full.max_seq * (int64_t)z.kv_dim,
+                    "KV cache: %lld floats is not a whole number of positions of %zu, at most %d", (long long)floats, z.kv_dim,
+                    a.d.full.max_seq);
+        dev = which == MOE_ST_K_CACHE ? ls.k_cache : ls.v_cache;
+        want = floats;
+        break;
+    case MOE_ST_CONV:
+    case MOE_ST_SSM:
+        MOE_REQUIRE(!ls.full, "layer %d is a full-attention layer: it has no conv / recurrence state", layer);
+        dev = which == MOE_ST_CONV ? ls.conv_state : ls.ssm_state;
+        want = which == MOE_ST_CONV ? (int64_t)a.d.conv_kernel * (int64_t)z.conv_dim : (int64_t)(z.total_value * a.d.lin_key_dim);
+        MOE_REQUIRE(floats == want, "state tensor %d of layer %d holds %lld floats, not %lld", which, layer, (long long)want,
+                    (long long)floats);
+        break;
+    default:
+        MOE_REQUIRE(false, "unknown state tensor %d", which);
+    }
+    if (want == 0) return MOE_OK;
+    MOE_REQUIRE(host != nullptr, "null host buffer");
+    if (to_device)
+        MOE_CUDA(cudaMemcpyAsync(dev, host, (size_t)want * 4, cudaMemcpyHostToDevice, e->stream));
+    else
+        MOE_CUDA(cudaMemcpyAsync(host, dev, (size_t)want * 4, cudaMemcpyDeviceToHost, e->stream));
+    MOE_CUDA(cudaStreamSynchronize(e->stream));
+    return MOE_OK;
+}
+
 size_t attn_state_bytes(const moe_engine* e) {
     const ModelAttnState& a = e->attn;
     if (!a.configured) return 0;

@@ -284,6 +284,7 @@ int attn_reset(moe_engine* e);
 // bytes of the linear-attention layers' conv + recurrence states (0 when attention is not configured), and a copy of
 // them to (save) or from a device buffer of that size, enqueued on the engine's stream
 size_t attn_state_bytes(const moe_engine* e);
+int attn_state_io(moe_engine* e, int layer, int which, float* host, int64_t floats, bool to_device);
 int attn_state_copy(moe_engine* e, uint8_t* buf, bool save);
 void attn_destroy(moe_engine* e);
 int head_reserve(moe_engine* e, int32_t n);

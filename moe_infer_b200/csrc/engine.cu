@@ -964,6 +964,20 @@ void moe_model_snapshot_free(moe_snapshot_t* s) {
     delete s;
 }
 
+int moe_model_state_host(moe_engine_t* e, int32_t layer, int32_t which, float* host, int64_t floats, int32_t to_device) {
+    MOE_REQUIRE(e, "null engine");
+    MOE_CUDA(cudaSetDevice(e->device));
+    return attn_state_io(e, layer, which, host, floats, to_device != 0);
+}
+
+int moe_model_set_pos(moe_engine_t* e, int64_t pos) {
+    MOE_REQUIRE(e, "null engine");
+    MOE_REQUIRE(e->attn.configured, "the attention halves are not configured (moe_attn_configure)");
+    MOE_REQUIRE(pos >= 0 && pos <= e->attn.d.full.max_seq, "position %lld outside [0, %d]", (long long)pos, e->attn.d.full.max_seq);
+    e->attn.pos = pos;
+    return MOE_OK;
+}
+
 // n decode steps with attention; ids != null: embed first and return logits, else emb in and hidden states out
 static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, int32_t n, float* out, bool logits) {
     MOE_REQUIRE(n >= 0, "negative token count");

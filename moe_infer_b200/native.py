@@ -356,6 +356,19 @@ class NativeEngine:
         L.check(self.lib.moe_model_pos(self.h, C.byref(p)))
         return p.value
 
+    def model_set_pos(self, pos: int) -> None:
+        L.check(self.lib.moe_model_set_pos(self.h, int(pos)))
+
+    def model_state_download(self, layer: int, which: int, floats: int) -> np.ndarray:
+        """One state tensor of one layer (L.ST_*) as float32 [floats]."""
+        out = np.empty(int(floats), np.float32)
+        L.check(self.lib.moe_model_state_host(self.h, layer, which, L.ptr(out) if out.size else None, out.size, 0))
+        return out
+
+    def model_state_upload(self, layer: int, which: int, data: np.ndarray) -> None:
+        data = np.ascontiguousarray(data, np.float32).reshape(-1)
+        L.check(self.lib.moe_model_state_host(self.h, layer, which, L.ptr(data) if data.size else None, data.size, 1))
+
     # ── MTP block, whole step (attention + MoE + head) ───────────────────
     def mtp_configure(self, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, rope_theta: float,
                       max_seq: int = 4096) -> None:

@@ -12,6 +12,7 @@ import pytest
 import oracle
 from benchmarks import synth
 from moe_infer_b200 import _lib as L
+from moe_infer_b200 import _moe_infer_rs as rs
 from moe_infer_b200.native import Dims, NativeEngine
 from tests.util import make_layer, rel_l2, upload_layer
 
@@ -83,6 +84,21 @@ def test_decode_with_attention_matches_oracle(scheme):
     print(f"decode with attention, {scheme}: rel-L2 per token {['%.1e' % x for x in errs]}")
     assert max(errs) < 1e-2 and eng.model_pos() == 6
     assert rel_l2(got - emb, want - emb) < 1e-2     # the layers' updates themselves, without the residual stream
+    # the state itself, tensor by tensor, in the layout the reference's cache file uses (src/cache.rs:140-160)
+    kv_dim = ad.num_kv_heads * ad.head_dim
+    for l in range(layers):
+        if l in state.kv:
+            for which, ref in ((L.ST_K_CACHE, state.kv[l][0]), (L.ST_V_CACHE, state.kv[l][1])):
+                assert rel_l2(eng.model_state_download(l, which, 6 * kv_dim).reshape(6, kv_dim), ref[:6]) < 1e-2
+        else:
+            ring = eng.model_state_download(l, L.ST_CONV, ad.conv_kernel * ad.conv_dim).reshape(ad.conv_kernel, ad.conv_dim)
+            assert rel_l2(rs._shifted_from_ring(ring, 6), state.lin[l][0]) < 1e-2
+            ssm = eng.model_state_download(l, L.ST_SSM, state.lin[l][1].size)
+            assert rel_l2(ssm, state.lin[l][1].ravel()) < 1e-2
+    with pytest.raises(ValueError, match="no KV cache"):
+        eng.model_state_download(0, L.ST_K_CACHE, kv_dim)
+    with pytest.raises(ValueError, match="holds"):
+        eng.model_state_download(0, L.ST_SSM, 5)
     # snapshot, run ahead, roll back: the same tokens give the same result again (speculative decoding's reject path)
     snap = eng.model_snapshot()
     ahead = eng.model_forward_hidden(emb[:2])

@@ -314,7 +314,7 @@ def test_forward_runs_attention_when_the_checkpoint_has_it(tmp_path, scheme):
     assert rel_l2(again, want[:1]) < 1e-2
     stale = rs.Cache(model)
     stale.pos = 3
-    with pytest.raises(RuntimeError, match="does not match the device state"):
+    with pytest.raises(RuntimeError, match="carries no state"):
         eng.forward(ids[:1], stale)
     eng.native.close()
 
