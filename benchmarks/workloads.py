@@ -367,12 +367,21 @@ def run_full_decode(args, eng: NativeEngine, local: int) -> dict:
         L.check(eng.lib.moe_model_forward_hidden_host(eng.h, L.ptr(emb[i % 8:i % 8 + 1]), 1, L.ptr(out)))
 
     t = timed_repeats(eng, step, max(3, min(args.warmup, 5)), max(1, min(args.steps, 10)))
+    # where the host's time goes, from the engine's own telemetry over a few more tokens (outside the timed region)
+    eng.lib.moe_set_record_telemetry(1)
+    t0 = eng.telemetry()
+    for i in range(8):
+        step(i)
+    t1 = eng.telemetry()
+    eng.lib.moe_set_record_telemetry(0)
+    host = {k: (t1.get(k, 0.0) - t0.get(k, 0.0)) / 8 for k in ("phase.op2_encode_ms", "phase.hidden_wait_ms")}
     moe_bytes = benchlib.layer_token_bytes(eng.dims) * n_layers
     res = {"workload": f"whole decoder, 1 token x {n_layers} layers: attention half (10 full-attention layers with bf16 projections, "
                        "30 Gated DeltaNet layers with 4-bit projections; Qwen3.6-35B-A3B head counts) + MoE half, host buffers, "
                        "context below 64 positions",
            "ms_per_token": t["ms_per_step"], "tok_per_s": 1e3 / t["ms_per_step"], "repeats": t["repeats"],
            "gpu_launches": t["launches"], "finite": bool(np.isfinite(out).all()),
+           "host_enqueue_ms_per_token": host["phase.op2_encode_ms"], "host_wait_ms_per_token": host["phase.hidden_wait_ms"],
            "attention_MB_per_token": attn_bytes / 1e6, "moe_MB_per_token": moe_bytes / 1e6,
            "roofline": hbm_roofline("attention kernels + decode_slots_kernel per layer", attn_bytes + moe_bytes, t["ms_per_step"])}
     return res

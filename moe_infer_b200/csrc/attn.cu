@@ -16,7 +16,8 @@ constexpr int kBfWarps = 8;
 
 __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16_t* __restrict__ w, const float* __restrict__ x,
                                                                    float* __restrict__ y, int rows, int cols,
-                                                                   const float* __restrict__ residual) {  // nullable: y = W x + residual
+                                                                   const float* __restrict__ residual,  // nullable: y = W x + residual
+                                                                   const uint16_t* __restrict__ norm_w) {  // nullable: x <- rmsnorm(x) * norm_w
     extern __shared__ float xs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int stride = gridDim.x * kBfWarps * 2;
@@ -29,17 +30,44 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
             for (int off = 0; off < cols * 2; off += 4096) prefetch_l2(wr + off, (uint32_t)min(4096, cols * 2 - off));
         }
     }
+    // ... and the first 16-byte steps of its first row pair go into registers before x is waited for
+    constexpr int kBfPre = 4;
+    const int r_first = (blockIdx.x * kBfWarps + warp) * 2;
+    uint4 pa[kBfPre], pb[kBfPre];
+#pragma unroll
+    for (int j = 0; j < kBfPre; ++j) {
+        const int c = lane * 8 + j * 256;
+        pa[j] = pb[j] = make_uint4(0, 0, 0, 0);
+        if (r_first < rows && c < cols) {
+            pa[j] = ld_stream_u4(w + (size_t)r_first * cols + c);
+            pb[j] = ld_stream_u4(w + (size_t)(r_first + 1 < rows ? r_first + 1 : r_first) * cols + c);
+        }
+    }
     pdl_wait();
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = x[i];
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = x[i];
+        xs[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (norm_w) {  // rms_norm_bf16 (reference src/math_util.rs:282-288) folded in: every CTA norms the input itself
+        __shared__ float red[kBfWarps];
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kBfWarps; ++i) tot += red[i];
+        const float inv_rms = 1.0f / sqrtf(tot / (float)cols + 1e-6f);
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = xs[i] * inv_rms * bf16_bits_to_f32(norm_w[i]);
+    }
     __syncthreads();
     for (int r0 = (blockIdx.x * kBfWarps + warp) * 2; r0 < rows; r0 += stride) {
         const bool two = r0 + 1 < rows;
         const uint16_t* wa = w + (size_t)r0 * cols;
         const uint16_t* wb = w + (size_t)(two ? r0 + 1 : r0) * cols;
         float a0 = 0.0f, a1 = 0.0f;
-#pragma unroll 4
-        for (int c = lane * 8; c < cols; c += 256) {
-            const uint4 qa = ld_stream_u4(wa + c), qb = ld_stream_u4(wb + c);
+        auto step = [&](int c, const uint4 qa, const uint4 qb) {
             const float4 x0 = *reinterpret_cast<const float4*>(xs + c), x1 = *reinterpret_cast<const float4*>(xs + c + 4);
             const uint32_t ra[4] = {qa.x, qa.y, qa.z, qa.w}, rb[4] = {qb.x, qb.y, qb.z, qb.w};
             const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
@@ -50,7 +78,15 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
                 a1 = fmaf(__uint_as_float(rb[i] << 16), xv[2 * i], a1);
                 a1 = fmaf(__uint_as_float(rb[i] & 0xFFFF0000u), xv[2 * i + 1], a1);
             }
+        };
+        int c = lane * 8;
+        if (r0 == r_first) {
+#pragma unroll
+            for (int j = 0; j < kBfPre; ++j, c += 256)
+                if (c < cols) step(c, pa[j], pb[j]);
         }
+#pragma unroll 8
+        for (; c < cols; c += 256) step(c, ld_stream_u4(wa + c), ld_stream_u4(wb + c));
         a0 = warp_sum(a0);
         a1 = warp_sum(a1);
         if (lane == 0) {
@@ -141,40 +177,63 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
 
 // ─── attention of one query position over the cache, output gate (cpu_attention + gate, mtp.rs:160-169, 305-352) ─
 // One CTA per query head.  Scores: a warp per cached position (lanes stride the head), scaled, max-subtracted,
-// exponentiated, summed; values: a thread per output element adds score / sum * v over the positions (coalesced
-// across the head).  out = attention * sigmoid(gate).
-__global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+// exponentiated, summed.  Values: the positions are dealt to the warps as well; a lane owns head elements lane, lane +
+// 32, ... (coalesced rows of V), keeps several positions' loads in flight, and the warps' partial sums meet in shared
+// memory.  out = attention * sigmoid(gate).
+constexpr int kAttnWarps = 8;
+constexpr int kAttnPerLane = 8;   // head_dim <= 256
+constexpr int kAttnInflight = 4;  // positions a warp has in flight in the value pass
+
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                           const float* __restrict__ v_cache, const float* __restrict__ gate,
                                                           int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_value,
                                                           const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const int seq_len = pos_ptr ? *pos_ptr + 1 : seq_value;
-    extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head
-    __shared__ float red[8];
+    extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head, then [warps][head_dim] partial outputs
+    __shared__ float red[kAttnWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.x, kv_h = h / (num_heads / num_kv_heads);
     const size_t kv_dim = (size_t)num_kv_heads * head_dim;
     float* qs = sc + seq_len;
-    for (int i = tid; i < head_dim; i += 256) qs[i] = q[(size_t)h * head_dim + i];
+    float* part = qs + head_dim;
+    for (int i = tid; i < head_dim; i += kAttnWarps * 32) qs[i] = q[(size_t)h * head_dim + i];
     __syncthreads();
+    float qreg[kAttnPerLane];
+#pragma unroll
+    for (int j = 0; j < kAttnPerLane; ++j) qreg[j] = lane + 32 * j < head_dim ? qs[lane + 32 * j] : 0.0f;
     float mx = -INFINITY;
-    for (int t = warp; t < seq_len; t += 8) {
-        const float* kr = k_cache + (size_t)t * kv_dim + (size_t)kv_h * head_dim;
-        float dot = 0.0f;
-        for (int d = lane; d < head_dim; d += 32) dot = fmaf(qs[d], kr[d], dot);
-        dot = warp_sum(dot) * kq_scale;
-        if (lane == 0) sc[t] = dot;
-        mx = fmaxf(mx, dot);
+    for (int t0 = warp; t0 < seq_len; t0 += kAttnWarps * kAttnInflight) {
+        float kr[kAttnInflight][kAttnPerLane];
+#pragma unroll
+        for (int u = 0; u < kAttnInflight; ++u) {
+            const int t = t0 + u * kAttnWarps;
+            const float* row = k_cache + (size_t)t * kv_dim + (size_t)kv_h * head_dim;
+#pragma unroll
+            for (int j = 0; j < kAttnPerLane; ++j) kr[u][j] = (t < seq_len && lane + 32 * j < head_dim) ? row[lane + 32 * j] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kAttnInflight; ++u) {
+            const int t = t0 + u * kAttnWarps;
+            float dot = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kAttnPerLane; ++j) dot = fmaf(qreg[j], kr[u][j], dot);
+            dot = warp_sum(dot) * kq_scale;
+            if (t < seq_len) {
+                if (lane == 0) sc[t] = dot;
+                mx = fmaxf(mx, dot);
+            }
+        }
     }
     if (lane == 0) red[warp] = mx;
     __syncthreads();
     mx = red[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+    for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, red[i]);
     __syncthreads();
     float sum = 0.0f;
-    for (int t = tid; t < seq_len; t += 256) {
+    for (int t = tid; t < seq_len; t += kAttnWarps * 32) {
         const float e = expf(sc[t] - mx);
         sc[t] = e;
         sum += e;
@@ -184,13 +243,38 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const float* __restric
     __syncthreads();
     float tot = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) tot += red[i];
-    for (int d = tid; d < head_dim; d += 256) {
-        const float* vc = v_cache + (size_t)kv_h * head_dim + d;
-        float acc = 0.0f;
-        for (int t = 0; t < seq_len; ++t) acc = fmaf(sc[t] / tot, vc[(size_t)t * kv_dim], acc);
+    for (int i = 0; i < kAttnWarps; ++i) tot += red[i];
+    // values: this warp's positions, kAttnInflight rows of V in flight
+    float acc[kAttnPerLane];
+#pragma unroll
+    for (int j = 0; j < kAttnPerLane; ++j) acc[j] = 0.0f;
+    for (int t0 = warp; t0 < seq_len; t0 += kAttnWarps * kAttnInflight) {
+        float vr[kAttnInflight][kAttnPerLane];
+#pragma unroll
+        for (int u = 0; u < kAttnInflight; ++u) {
+            const int t = t0 + u * kAttnWarps;
+            const float* row = v_cache + (size_t)t * kv_dim + (size_t)kv_h * head_dim;
+#pragma unroll
+            for (int j = 0; j < kAttnPerLane; ++j) vr[u][j] = (t < seq_len && lane + 32 * j < head_dim) ? row[lane + 32 * j] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kAttnInflight; ++u) {
+            const int t = t0 + u * kAttnWarps;
+            const float p = t < seq_len ? sc[t] / tot : 0.0f;
+#pragma unroll
+            for (int j = 0; j < kAttnPerLane; ++j) acc[j] = fmaf(p, vr[u][j], acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kAttnPerLane; ++j)
+        if (lane + 32 * j < head_dim) part[warp * head_dim + lane + 32 * j] = acc[j];
+    __syncthreads();
+    for (int d = tid; d < head_dim; d += kAttnWarps * 32) {
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) a += part[w * head_dim + d];
         const float g = gate[(size_t)h * gate_stride + d];
-        out[(size_t)h * head_dim + d] = acc * (1.0f / (1.0f + expf(-g)));
+        out[(size_t)h * head_dim + d] = a * (1.0f / (1.0f + expf(-g)));
     }
 }
 
@@ -238,24 +322,75 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
             for (size_t off = (size_t)tid * 4096; off < bytes; off += (size_t)kLinThreads * 4096)
                 prefetch_l2(sp + off, (uint32_t)(bytes - off < 4096 ? bytes - off : 4096));
     }
-    pdl_wait();
+    // ... and this warp's first group of state rows goes into registers right away: the loads are in flight through
+    // the conv and the norms.  (The state was last written by this kernel a token ago.)
+    float spre[kLinRows][kLinPer];
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        const int v = warp * kLinRows + r;
+        const float* srow = state + ((size_t)h * value_dim + v) * key_dim;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            spre[r][j] = (v < value_dim && i < key_dim) ? srow[i] : 0.0f;
+        }
+    }
+    // Everything else that does not come from the kernel before this one is requested now as well, so that after the
+    // wait only one round of loads (this thread's projection outputs) stands between the kernel and its arithmetic:
+    // the position, this thread's channel (conv taps and the ring rows they multiply: written in earlier steps), the
+    // head's decay parameters and this thread's norm weight.
     const int pos = *pos_ptr;
-    // 1. conv + SiLU of this head's channels, and the ring update
     const int n_ch = 2 * key_dim + value_dim;
+    auto channel_of = [&](int i) {
+        return i < key_dim ? kh * key_dim + i
+               : i < 2 * key_dim ? total_key + kh * key_dim + (i - key_dim)
+                                 : 2 * total_key + h * value_dim + (i - 2 * key_dim);
+    };
+    constexpr int kFastK = 4;  // conv kernel sizes up to this take the preloaded path for a thread's first channel
+    const bool fast_conv = conv_w != nullptr && ksize <= kFastK && tid < n_ch;
+    const int c_mine = tid < n_ch ? channel_of(tid) : 0;
+    float cw[kFastK], rv[kFastK];
+#pragma unroll
+    for (int k = 0; k < kFastK; ++k) {
+        cw[k] = rv[k] = 0.0f;
+        if (fast_conv && k < ksize) cw[k] = bf16_bits_to_f32(conv_w[(size_t)c_mine * ksize + k]);
+        if (fast_conv && k < ksize - 1) {
+            const int step = pos - (ksize - 1) + k;
+            const int row = ((step % ksize) + ksize) % ksize;
+            rv[k] = conv_ring[(size_t)row * conv_dim + c_mine];
+        }
+    }
+    const float a_log_h = a_log ? a_log[h] : 0.0f;
+    const float dt_bias_h = dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f;
+    const float nw_mine = (norm_w && tid < value_dim) ? bf16_bits_to_f32(norm_w[tid]) : 0.0f;
+    pdl_wait();
+    const float xin_mine = tid < n_ch ? qkv_in[c_mine] : 0.0f;
+    const float z_mine = (norm_w && tid < value_dim) ? z[(size_t)h * value_dim + tid] : 0.0f;
+    const float alpha_h = alpha[h], beta_h = beta[h];
+    // 1. conv + SiLU of this head's channels, and the ring update
     for (int i = tid; i < n_ch; i += kLinThreads) {
-        const int c = i < key_dim ? kh * key_dim + i
-                    : i < 2 * key_dim ? total_key + kh * key_dim + (i - key_dim)
-                                      : 2 * total_key + h * value_dim + (i - 2 * key_dim);
-        const float xin = qkv_in[c];
+        const int c = i == tid ? c_mine : channel_of(i);
+        const float xin = i == tid ? xin_mine : qkv_in[c];
         float val = xin;
         if (conv_w) {
             float acc = 0.0f;
-            for (int k = 0; k < ksize - 1; ++k) {
-                const int step = pos - (ksize - 1) + k;                   // the input this tap multiplies
-                const int row = ((step % ksize) + ksize) % ksize;         // rows of steps before the start hold zeros
-                acc += conv_ring[(size_t)row * conv_dim + c] * bf16_bits_to_f32(conv_w[(size_t)c * ksize + k]);
+            if (i == tid && fast_conv) {
+#pragma unroll
+                for (int k = 0; k < kFastK; ++k)
+                    if (k < ksize - 1) acc += rv[k] * cw[k];
+                float w_last = cw[0];
+#pragma unroll
+                for (int k = 1; k < kFastK; ++k)
+                    if (k == ksize - 1) w_last = cw[k];
+                acc += xin * w_last;
+            } else {
+                for (int k = 0; k < ksize - 1; ++k) {
+                    const int step = pos - (ksize - 1) + k;                   // the input this tap multiplies
+                    const int row = ((step % ksize) + ksize) % ksize;         // rows of steps before the start hold zeros
+                    acc += conv_ring[(size_t)row * conv_dim + c] * bf16_bits_to_f32(conv_w[(size_t)c * ksize + k]);
+                }
+                acc += xin * bf16_bits_to_f32(conv_w[(size_t)c * ksize + ksize - 1]);
             }
-            acc += xin * bf16_bits_to_f32(conv_w[(size_t)c * ksize + ksize - 1]);
             val = acc / (1.0f + expf(-acc));  // silu (src/math_util.rs:71-75)
             conv_ring[(size_t)(pos % ksize) * conv_dim + c] = xin;
         }
@@ -287,10 +422,10 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
         ks[i] *= k_mul;
     }
     // 3. decay and input gate of this head
-    const float a = expf(a_log ? a_log[h] : 0.0f);
-    const float softplus = logf(1.0f + expf(alpha[h] + (dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f)));
+    const float a = expf(a_log_h);
+    const float softplus = logf(1.0f + expf(alpha_h + dt_bias_h));
     const float g = expf(-a * softplus);
-    const float bgate = 1.0f / (1.0f + expf(-beta[h]));
+    const float bgate = 1.0f / (1.0f + expf(-beta_h));
     __syncthreads();
     // 4. the recurrence: a warp takes kLinRows consecutive rows at a time and requests all their state up front
     for (int v0 = warp * kLinRows; v0 < value_dim; v0 += kLinWarps * kLinRows) {
@@ -301,7 +436,8 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
 #pragma unroll
             for (int j = 0; j < kLinPer; ++j) {
                 const int i = lane + 32 * j;
-                sreg[r][j] = (v0 + r < value_dim && i < key_dim) ? srow[i] : 0.0f;
+                if (v0 == warp * kLinRows) sreg[r][j] = spre[r][j];  // the group requested at the top
+                else sreg[r][j] = (v0 + r < value_dim && i < key_dim) ? srow[i] : 0.0f;
             }
         }
         float kv[kLinRows];
@@ -363,8 +499,9 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
     for (int i = 0; i < kLinWarps; ++i) tot += red[i];
     const float inv = 1.0f / sqrtf(tot / (float)value_dim + 1e-6f);
     for (int i = tid; i < value_dim; i += kLinThreads) {
-        const float zv = z[(size_t)h * value_dim + i];
-        out[(size_t)h * value_dim + i] = vals[i] * inv * (zv / (1.0f + expf(-zv))) * bf16_bits_to_f32(norm_w[i]);
+        const float zv = i == tid ? z_mine : z[(size_t)h * value_dim + i];
+        const float nw = i == tid ? nw_mine : bf16_bits_to_f32(norm_w[i]);
+        out[(size_t)h * value_dim + i] = vals[i] * inv * (zv / (1.0f + expf(-zv))) * nw;
     }
 }
 
@@ -409,7 +546,7 @@ int mtp_configure(moe_engine* e, const moe_attn_dims_t* ad) {
     }
     MOE_REQUIRE(ad->num_heads > 0 && ad->num_kv_heads > 0 && ad->num_heads % ad->num_kv_heads == 0,
                 "attention heads (%d) must be a positive multiple of the key/value heads (%d)", ad->num_heads, ad->num_kv_heads);
-    MOE_REQUIRE(ad->head_dim > 0 && ad->head_dim % 8 == 0 && ad->head_dim <= 1024, "head_dim (%d) must be a multiple of 8 up to 1024", ad->head_dim);
+    MOE_REQUIRE(ad->head_dim > 0 && ad->head_dim % 8 == 0 && ad->head_dim <= 32 * kAttnPerLane, "head_dim (%d) must be a multiple of 8 up to 256", ad->head_dim);
     MOE_REQUIRE(ad->rotary_dim >= 0 && ad->rotary_dim <= ad->head_dim && ad->rotary_dim % 2 == 0,
                 "rotary_dim (%d) must be even and at most head_dim (%d)", ad->rotary_dim, ad->head_dim);
     MOE_REQUIRE(ad->max_seq > 0 && ad->max_seq <= 8192, "max_seq (%d) must be in 1..8192", ad->max_seq);
@@ -482,16 +619,20 @@ int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, cons
 }
 
 // y = W x (+ residual) for a projection stored as bf16 rows or as a 4-bit triple
-static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr, bool pdl = false) {
-    if (t.dtype == MOE_DT_INT4) return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual, pdl);
+// norm_w: the input is rmsnorm(x) * norm_w, applied inside the kernel (see proj_folds_norm)
+static bool proj_folds_norm(const ProjTensor& t) { return t.dtype != MOE_DT_INT4 || matvec_folds_norm(t.rows, t.cols); }
+static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr, bool pdl = false,
+                    const void* norm_w = nullptr) {
+    if (t.dtype == MOE_DT_INT4)
+        return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual, pdl, norm_w);
     if (!e->mtp.bf_attr_set) {
         MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
         e->mtp.bf_attr_set = true;
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
-    if (blocks > e->sm_count * 4) blocks = e->sm_count * 4;
+    if (blocks > e->sm_count * 2) blocks = e->sm_count * 2;  // one wave (two CTAs per SM): x is staged once per CTA
     MOE_CUDA(launch_kernel(pdl, matvec_bf16_kernel, dim3(blocks), dim3(kBfWarps * 32), (size_t)t.cols * 4, e->stream,
-                           reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual));
+                           reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual, (const uint16_t*)norm_w));
     e->launches++;
     return MOE_OK;
 }
@@ -549,7 +690,7 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
                                                           m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
     const int seq = pos + 1;
-    attn_decode_kernel<<<nh, 256, (size_t)(seq + hd) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
+    attn_decode_kernel<<<nh, kAttnWarps * 32, (size_t)(seq + hd * (1 + kAttnWarps)) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
                                                                1.0f / sqrtf((float)hd), gated);
     e->launches += 2;
     if ((rc = proj_run(e, m.proj[MOE_M_O_PROJ], gated, cur2, cur))) return rc;  // + residual
@@ -717,7 +858,7 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
     const moe_attn_dims_t& f = dims->full;
     MOE_REQUIRE(f.num_heads > 0 && f.num_kv_heads > 0 && f.num_heads % f.num_kv_heads == 0,
                 "attention heads (%d) must be a positive multiple of the key/value heads (%d)", f.num_heads, f.num_kv_heads);
-    MOE_REQUIRE(f.head_dim > 0 && f.head_dim % 8 == 0 && f.head_dim <= 1024, "head_dim (%d) must be a multiple of 8 up to 1024", f.head_dim);
+    MOE_REQUIRE(f.head_dim > 0 && f.head_dim % 8 == 0 && f.head_dim <= 32 * kAttnPerLane, "head_dim (%d) must be a multiple of 8 up to 256", f.head_dim);
     MOE_REQUIRE(f.rotary_dim >= 0 && f.rotary_dim <= f.head_dim && f.rotary_dim % 2 == 0,
                 "rotary_dim (%d) must be even and at most head_dim (%d)", f.rotary_dim, f.head_dim);
     MOE_REQUIRE(f.max_seq > 0 && f.max_seq <= 8192, "max_seq (%d) must be in 1..8192", f.max_seq);
@@ -896,9 +1037,16 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         return ok;
     };
     if (!need(MOE_A_INPUT_NORM)) return MOE_ERR_STATE;
-    const bool pdl = a.pdl;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
-    rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x);
-    e->launches++;
+    // the input norm is folded into the stacked projection where its kernel can do that; a kernel of its own otherwise
+    const bool fold = ls.fused.loaded && proj_folds_norm(ls.fused);
+    const void* fold_w = fold ? ls.vec[MOE_A_INPUT_NORM] : nullptr;
+    const float* proj_in = fold ? h : x;
+    bool pdl = false;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
+    if (!fold) {
+        rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x);
+        e->launches++;
+        pdl = a.pdl;
+    }
     int rc;
     if (ls.full) {
         for (int w : {MOE_A_Q_PROJ, MOE_A_K_PROJ, MOE_A_V_PROJ, MOE_A_Q_NORM, MOE_A_K_NORM, MOE_A_O_PROJ})
@@ -908,7 +1056,8 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* kb = qb + 2 * z.q_dim;
         float* vb = kb + z.kv_dim;
         if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, x, proj_out, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w))) return rc;
+            pdl = a.pdl;
         } else {
             if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, qb, nullptr, pdl))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb, nullptr, pdl))) return rc;
@@ -918,7 +1067,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
                                (const uint16_t*)ls.vec[MOE_A_Q_NORM], (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd,
                                d.full.rotary_dim, 0, a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache));
         // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
-        MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(256), (size_t)(d.full.max_seq + hd) * 4, st, qr, ls.k_cache,
+        MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(kAttnWarps * 32), (size_t)(d.full.max_seq + hd * (1 + kAttnWarps)) * 4, st, qr, ls.k_cache,
                                ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, a.d_pos, 1.0f / sqrtf((float)hd), vals));
         e->launches += 2;
         if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h, pdl))) return rc;  // + residual
@@ -930,7 +1079,8 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* bb = zb + z.total_value;
         float* ab = bb + Hv;
         if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, x, proj_out, nullptr, pdl))) return rc;
+            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w))) return rc;
+            pdl = a.pdl;
         } else {
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, qkv_raw, nullptr, pdl))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_Z], x, zb, nullptr, pdl))) return rc;

@@ -248,7 +248,9 @@ int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, in
 int matvec_prepare(moe_engine* e);
 // y = W x + residual (residual nullable; may not alias y)
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x, float* y, int32_t rows,
-                      int32_t cols, const float* residual, bool pdl = false);
+                      int32_t cols, const float* residual, bool pdl = false, const void* norm_w = nullptr);
+// whether launch_matvec_res can apply rmsnorm(x) * norm_w (bf16 weights) to its input itself for this shape
+bool matvec_folds_norm(int32_t rows, int32_t cols);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);

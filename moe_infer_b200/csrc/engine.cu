@@ -990,6 +990,9 @@ static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, 
     float* d_out = (float*)(e->io_dev + hb);
     float* d_l = (float*)(e->io_dev + 2 * hb);
     const int64_t pos0 = e->attn.pos;
+    const bool rec = g_record_telemetry.load(std::memory_order_relaxed) != 0;
+    host_time_t host_t0{}, host_t1{};
+    if (rec) host_t0 = std::chrono::steady_clock::now();
     do {
         if (ids) {
             if ((rc = head_reserve(e, n))) break;
@@ -1001,6 +1004,7 @@ static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, 
             if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward upload", __FILE__, __LINE__); break; }
         }
         if ((rc = attn_model_forward(e, d_in, n, d_out))) break;
+        if (rec) host_t1 = std::chrono::steady_clock::now();  // everything is enqueued; the copies below wait for the stream
         cudaError_t ce;
         if (logits) {
             if ((rc = launch_logits(e, d_out, n, d_l))) break;
@@ -1015,6 +1019,7 @@ static int model_forward(moe_engine_t* e, const int64_t* ids, const float* emb, 
         if (ce != cudaSuccess) { rc = cuda_fail(ce, "model forward download", __FILE__, __LINE__); break; }
         if ((rc = poll_device_error(e))) break;
         memcpy(e->last_h.data(), e->stage_host, (size_t)d.hidden * 4);
+        if (rec) tel_phases(e, host_t0, host_t1, std::chrono::steady_clock::now(), 0.0);  // enqueue time, then the wait for the stream
     } while (0);
     if (rc) {
         cudaStreamSynchronize(e->stream);

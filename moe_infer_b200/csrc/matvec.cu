@@ -32,11 +32,32 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
-    // nothing about the weights depends on x: ask for this warp's rows (L2) while the kernel that produces x still runs
+    // Nothing about the weights depends on x.  Before waiting for it (and for the kernel that produces it), this warp
+    // requests its first two rows' first 128 chunks into registers (rows of up to 4,096 columns: everything) and asks
+    // the L2 for its later rows.
     const int groups = cols / kGroup;
     const int row_first = blockIdx.x * kMvWarps + warp;
+    const int row_step = (int)gridDim.x * kMvWarps;
+    constexpr int kPreRows = 2, kPreSlots = 4;  // chunk slot j of a lane is chunk 32 j + lane
+    uint4 pq[kPreRows][kPreSlots];
+    uint16_t ps[kPreRows][kPreSlots], pb[kPreRows][kPreSlots];
+#pragma unroll
+    for (int r = 0; r < kPreRows; ++r) {
+        const int row = row_first + r * row_step;
+#pragma unroll
+        for (int j = 0; j < kPreSlots; ++j) {
+            const int c = 32 * j + lane;
+            pq[r][j] = make_uint4(0, 0, 0, 0);
+            ps[r][j] = pb[r][j] = 0;
+            if (row < rows && c < nch) {
+                pq[r][j] = ld_stream_u4(reinterpret_cast<const uint4*>(w + (size_t)row * (cols / 8)) + c);
+                ps[r][j] = s[(size_t)row * groups + (c >> 1)];
+                pb[r][j] = b[(size_t)row * groups + (c >> 1)];
+            }
+        }
+    }
     {
-        const int row = row_first + lane * (int)gridDim.x * kMvWarps;
+        const int row = row_first + (kPreRows + lane) * row_step;
         if (lane < 8 && row < rows) {
             const unsigned char* wr = reinterpret_cast<const unsigned char*>(w + (size_t)row * (cols / 8));
             for (int off = 0; off < cols / 2; off += 4096) prefetch_l2(wr + off, (uint32_t)min(4096, cols / 2 - off));
@@ -47,16 +68,6 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
     if (tid == 0) {
         mbar_expect_tx(&bar, (uint32_t)cols * 4u);
         bulk_g2s(raw, x, (uint32_t)cols * 4u, &bar);
-    }
-    // the first two chunks of this warp's first row do not depend on x: request them before waiting for it
-    uint4 pqa = make_uint4(0, 0, 0, 0), pqb = pqa;
-    uint16_t psa = 0, pba = 0, psb = 0, pbb = 0;
-    if (row_first < rows) {
-        const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row_first * (cols / 8));
-        const uint16_t* srow = s + (size_t)row_first * groups;
-        const uint16_t* brow = b + (size_t)row_first * groups;
-        if (lane < nch) { pqa = ld_stream_u4(wrow + lane); psa = srow[lane >> 1]; pba = brow[lane >> 1]; }
-        if (32 + lane < nch) { pqb = ld_stream_u4(wrow + 32 + lane); psb = srow[(32 + lane) >> 1]; pbb = brow[(32 + lane) >> 1]; }
     }
     // every thread observes the phase itself, so the copied bytes are visible to it
     const int ok = __syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0);
@@ -77,20 +88,28 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
     }
     __syncthreads();
 
-    for (int row = row_first; row < rows; row += gridDim.x * kMvWarps) {
+    int nrow = 0;
+    for (int row = row_first; row < rows; row += row_step, ++nrow) {
         const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (cols / 8));
         const uint16_t* srow = s + (size_t)row * groups;
         const uint16_t* brow = b + (size_t)row * groups;
         float acc = 0.0f;
+#pragma unroll 1
         for (int c0 = 0; c0 < nch; c0 += 64) {
             // two chunks per lane in flight
             const int ca = c0 + lane, cb = c0 + 32 + lane;
             const bool va = ca < nch, vb = cb < nch;
             uint4 qa = make_uint4(0, 0, 0, 0), qb = qa;
             uint16_t sa = 0, ba = 0, sb = 0, bb = 0;
-            if (row == row_first && c0 == 0) {
-                qa = pqa; sa = psa; ba = pba;
-                qb = pqb; sb = psb; bb = pbb;
+            if (nrow < kPreRows && c0 < 32 * kPreSlots) {
+                // (constant indices after unrolling the two cases, so the arrays stay in registers)
+                if (nrow == 0) {
+                    if (c0 == 0) { qa = pq[0][0]; sa = ps[0][0]; ba = pb[0][0]; qb = pq[0][1]; sb = ps[0][1]; bb = pb[0][1]; }
+                    else         { qa = pq[0][2]; sa = ps[0][2]; ba = pb[0][2]; qb = pq[0][3]; sb = ps[0][3]; bb = pb[0][3]; }
+                } else {
+                    if (c0 == 0) { qa = pq[1][0]; sa = ps[1][0]; ba = pb[1][0]; qb = pq[1][1]; sb = ps[1][1]; bb = pb[1][1]; }
+                    else         { qa = pq[1][2]; sa = ps[1][2]; ba = pb[1][2]; qb = pq[1][3]; sb = ps[1][3]; bb = pb[1][3]; }
+                }
             } else {
                 if (va) { qa = ld_stream_u4(wrow + ca); sa = srow[ca >> 1]; ba = brow[ca >> 1]; }
                 if (vb) { qb = ld_stream_u4(wrow + cb); sb = srow[cb >> 1]; bb = brow[cb >> 1]; }
@@ -126,7 +145,8 @@ constexpr int kSvUnroll = 4;
 __global__ void __launch_bounds__(kSvWarps * 32, 2)
 matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s, const uint16_t* __restrict__ b,
                           const float* __restrict__ x, float* __restrict__ y, int rows, unsigned int* err_flag,
-                          const float* __restrict__ residual) {
+                          const float* __restrict__ residual,
+                          const uint16_t* __restrict__ norm_w) {  // nullable: the input is rmsnorm(x) * norm_w (bf16), eps 1e-6
     constexpr int nch = kSvCols / 32;
     __shared__ __align__(128) float raw[kSvCols];
     __shared__ __align__(16) uint4 xq[6 * nch];
@@ -139,9 +159,28 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
         mbar_init(&bar, 1);
         mbar_fence_init();
     }
-    // the weights do not depend on x: ask for this warp's first rows (L2) while the kernel that produces x still runs
+    // The weights do not depend on x.  Before waiting for it (and for the kernel that produces it) this warp requests
+    // its first batch of rows into registers and asks the L2 for the rows after them.
+    const int stride = gridDim.x * kSvWarps;
+    const int row_first = blockIdx.x * kSvWarps + warp;
+    uint4 q[kSvUnroll][2] = {};
+    uint16_t sc[kSvUnroll] = {}, bi[kSvUnroll] = {};
+    auto load_batch = [&](int row0) {
+#pragma unroll
+        for (int u = 0; u < kSvUnroll; ++u) {
+            const int row = row0 + u * stride;
+            if (row < rows) {
+                const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (kSvCols / 8)) + 2 * lane;
+                q[u][0] = ld_stream_u4(wrow);
+                q[u][1] = ld_stream_u4(wrow + 1);
+                sc[u] = __ldg(s + (size_t)row * (kSvCols / kGroup) + lane);
+                bi[u] = __ldg(b + (size_t)row * (kSvCols / kGroup) + lane);
+            }
+        }
+    };
+    load_batch(row_first);
     {
-        const int row = blockIdx.x * kSvWarps + warp + lane * (int)gridDim.x * kSvWarps;
+        const int row = row_first + (kSvUnroll + lane) * stride;
         if (lane < 16 && row < rows) {
             prefetch_l2(w + (size_t)row * (kSvCols / 8), kSvCols / 2);
             if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(b)) & 15) == 0) {
@@ -161,10 +200,34 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
         if (tid == 0) atomicExch(err_flag, 1u);
         return;
     }
+    float inv_rms = 1.0f;
+    if (norm_w) {  // rms_norm_bf16 (reference src/math_util.rs:282-288) folded in: every CTA norms the 2,048 inputs itself
+        __shared__ float red[kSvWarps];
+        float ss = 0.0f;
+#pragma unroll
+        for (int it = 0; it < kSvCols / 4 / (kSvWarps * 32); ++it) {
+            const float4 v = reinterpret_cast<const float4*>(raw)[tid + it * kSvWarps * 32];
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kSvWarps; ++i) tot += red[i];
+        inv_rms = 1.0f / sqrtf(tot / (float)kSvCols + 1e-6f);
+    }
 #pragma unroll
     for (int it = 0; it < kSvCols / 4 / (kSvWarps * 32); ++it) {
         const int f = tid + it * kSvWarps * 32;  // float4 index: chunk f >> 3, part f & 7 (eight consecutive lanes per chunk)
-        const float4 v = reinterpret_cast<const float4*>(raw)[f];
+        float4 v = reinterpret_cast<const float4*>(raw)[f];
+        if (norm_w) {
+            const uint2 wb = __ldg(reinterpret_cast<const uint2*>(norm_w) + f);
+            v.x = v.x * inv_rms * __uint_as_float(wb.x << 16);
+            v.y = v.y * inv_rms * __uint_as_float(wb.x & 0xFFFF0000u);
+            v.z = v.z * inv_rms * __uint_as_float(wb.y << 16);
+            v.w = v.w * inv_rms * __uint_as_float(wb.y & 0xFFFF0000u);
+        }
         stage_digits(xq, xdl, nch, f >> 3, f & 7, v);
         float sv = (v.x + v.y) + (v.z + v.w);
         sv += __shfl_xor_sync(0xffffffffu, sv, 1);
@@ -185,29 +248,22 @@ matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __rest
     const float dl0 = xdl[2 * lane], dl1 = xdl[2 * lane + 1];
     const float sx = sumx[2 * lane] + sumx[2 * lane + 1];
 
-    const int stride = gridDim.x * kSvWarps;
-    for (int row0 = blockIdx.x * kSvWarps + warp; row0 < rows; row0 += stride * kSvUnroll) {
-        uint4 q[kSvUnroll][2];
-        uint16_t sc[kSvUnroll], bi[kSvUnroll];
+    for (int row0 = row_first; row0 < rows;) {
+        float acc[kSvUnroll];
 #pragma unroll
         for (int u = 0; u < kSvUnroll; ++u) {
-            const int row = row0 + u * stride;
-            if (row < rows) {
-                const uint4* wrow = reinterpret_cast<const uint4*>(w + (size_t)row * (kSvCols / 8)) + 2 * lane;
-                q[u][0] = ld_stream_u4(wrow);
-                q[u][1] = ld_stream_u4(wrow + 1);
-                sc[u] = __ldg(s + (size_t)row * (kSvCols / kGroup) + lane);
-                bi[u] = __ldg(b + (size_t)row * (kSvCols / kGroup) + lane);
-            }
+            const float d = fmaf(dl0, dot32_regs(q[u][0], xe[0], xo[0]), dl1 * dot32_regs(q[u][1], xe[1], xo[1]));
+            acc[u] = fmaf(bf16_bits_to_f32(sc[u]), d, bf16_bits_to_f32(bi[u]) * sx);
         }
+        const int done0 = row0;
+        row0 += stride * kSvUnroll;
+        if (row0 < rows) load_batch(row0);  // the next batch is on its way while this one is reduced and stored
 #pragma unroll
         for (int u = 0; u < kSvUnroll; ++u) {
-            const int row = row0 + u * stride;
+            const int row = done0 + u * stride;
             if (row < rows) {  // uniform per warp
-                const float d = fmaf(dl0, dot32_regs(q[u][0], xe[0], xo[0]), dl1 * dot32_regs(q[u][1], xe[1], xo[1]));
-                float acc = fmaf(bf16_bits_to_f32(sc[u]), d, bf16_bits_to_f32(bi[u]) * sx);
-                acc = warp_sum(acc);
-                if (lane == 0) y[row] = residual ? acc + residual[row] : acc;
+                const float a = warp_sum(acc[u]);
+                if (lane == 0) y[row] = residual ? a + residual[row] : a;
             }
         }
     }
@@ -226,18 +282,23 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
     return launch_matvec_res(e, w, s, b, x, y, rows, cols, nullptr);
 }
 
+bool matvec_folds_norm(int32_t rows, int32_t cols) { return cols == kSvCols && rows >= 4096; }
+
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
-                      float* y, int32_t rows, int32_t cols, const float* residual, bool pdl) {
+                      float* y, int32_t rows, int32_t cols, const float* residual, bool pdl, const void* norm_w) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
-    if (cols == kSvCols && rows >= 4096) {
+    MOE_REQUIRE(!norm_w || (matvec_folds_norm(rows, cols) && (((uintptr_t)norm_w) & 7) == 0),
+                "matvec: the input norm can only be folded into the streaming kernel (2048 columns, >= 4096 rows)");
+    if (matvec_folds_norm(rows, cols)) {
         // enough rows to stream: the register-resident variant
         int blocks = (rows + kSvWarps * kSvUnroll - 1) / (kSvWarps * kSvUnroll);
         const int cap = e->sm_count * 2;
         if (blocks > cap) blocks = cap;
         MOE_CUDA(launch_kernel(pdl, matvec_int4_stream_kernel, dim3(blocks), dim3(kSvWarps * 32), 0, e->stream, (const uint32_t*)w,
-                               (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual));
+                               (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual,
+                               (const uint16_t*)norm_w));
         e->launches++;
         return MOE_OK;
     }
