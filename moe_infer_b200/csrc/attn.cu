@@ -14,9 +14,9 @@ namespace moe {
 // 2 B per weight: bound by HBM bandwidth like the 4-bit matvec.
 constexpr int kBfWarps = 8;
 
-__global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16_t* __restrict__ w, const float* __restrict__ x,
+__global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16_t* __restrict__ w, const float* x,
                                                                    float* __restrict__ y, int rows, int cols,
-                                                                   const float* __restrict__ residual,  // nullable: y = W x + residual
+                                                                   const float* residual,  // nullable: y = W x + residual
                                                                    const uint16_t* __restrict__ norm_w) {  // nullable: x <- rmsnorm(x) * norm_w
     extern __shared__ float xs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16
 }
 
 // ─── RMS norm of `rows` vectors of `dim` elements with one bf16 weight vector (rms_norm, mtp.rs:261-266) ─────
-__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float* __restrict__ x, const uint16_t* __restrict__ w, int dim,
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float* x, const uint16_t* __restrict__ w, int dim,
                                                             float* __restrict__ out) {
     __shared__ float red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -124,9 +124,9 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(const float* __restr
 //   * the main model's full-attention layers (src/math_util.rs:501-597): the q projection is [head, gate] per head
 //     (q_stride = 2 * head_dim) and RoPE rotates the pairs (i, i + rope_dim / 2).
 // Either way the angle of pair i is pos * theta^(-2i / rope_dim).
-__global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict__ q, int q_stride, int rope_half_split,
-                                                        const float* __restrict__ k,
-                                                        const float* __restrict__ v, const uint16_t* __restrict__ q_norm,
+__global__ void __launch_bounds__(256) attn_prep_kernel(const float* q, int q_stride, int rope_half_split,
+                                                        const float* k,
+                                                        const float* v, const uint16_t* __restrict__ q_norm,
                                                         const uint16_t* __restrict__ k_norm, int num_heads, int num_kv_heads,
                                                         int head_dim, int rope_dim, int pos_value, const int* __restrict__ pos_ptr,
                                                         float theta, float* __restrict__ q_out,
@@ -184,8 +184,8 @@ constexpr int kAttnWarps = 8;
 constexpr int kAttnPerLane = 8;   // head_dim <= 256
 constexpr int kAttnInflight = 4;  // positions a warp has in flight in the value pass
 
-__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
-                                                          const float* __restrict__ v_cache, const float* __restrict__ gate,
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* q, const float* k_cache,
+                                                          const float* v_cache, const float* gate,
                                                           int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_value,
                                                           const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out) {
     pdl_trigger();
@@ -298,9 +298,9 @@ constexpr int kLinRows = 4;    // state rows a warp has in flight
 constexpr int kLinPerMax = 8; // state elements per lane and row: key_dim <= 256
 
 template <int kLinPer>  // 4: key_dim <= 128, 8: key_dim <= 256
-__global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict__ conv_ring, const float* __restrict__ qkv_in,
-                                                       const uint16_t* __restrict__ conv_w, const float* __restrict__ z,
-                                                       const float* __restrict__ alpha, const float* __restrict__ beta,
+__global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict__ conv_ring, const float* qkv_in,
+                                                       const uint16_t* __restrict__ conv_w, const float* z,
+                                                       const float* alpha, const float* beta,
                                                        const float* __restrict__ a_log, const uint16_t* __restrict__ dt_bias,
                                                        const uint16_t* __restrict__ norm_w, float* __restrict__ state,
                                                        float* __restrict__ out, const int* __restrict__ pos_ptr, int total_key,
@@ -502,6 +502,209 @@ __global__ void __launch_bounds__(kLinThreads) lin_core_kernel(float* __restrict
         const float zv = i == tid ? z_mine : z[(size_t)h * value_dim + i];
         const float nw = i == tid ? nw_mine : bf16_bits_to_f32(norm_w[i]);
         out[(size_t)h * value_dim + i] = vals[i] * inv * (zv / (1.0f + expf(-zv))) * nw;
+    }
+}
+
+// ─── the same layer with a head's state rows dealt to several small CTAs ────────────────────────────────────
+// One CTA of 256 threads per (value head, block of 32 state rows): conv + SiLU of the key head's q and k channels (every
+// CTA of the head repeats them; they write the same values into the ring) and of its own 32 v channels, the q / k
+// norms, decay and gate, and the delta rule on its rows.  The rows of a head are independent of one another given q
+// and k; only the gated RMS norm joins them (a sum over the head's outputs): every CTA applies the gate and the norm
+// weight to its outputs and leaves its sum of squares beside them, and the output projection's kernel multiplies by the
+// head's rsqrt(mean + eps) while it stages its input (launch_matvec_head_scaled).  Four times as many SMs work on the 2 MB of state, and a 256-thread CTA finds room on an SM
+// while the projection before it still runs, so what it requests ahead of its wait really is ahead.
+constexpr int kLpThreads = 256, kLpWarps = kLpThreads / 32;
+constexpr int kLpRows = kLpWarps * kLinRows;  // 32 state rows per CTA
+constexpr int kLpCh = 2;                      // channels a thread prepares ahead of the wait (the CTA's channels <= 512)
+constexpr int kLpK = 4;                       // conv kernel sizes up to this take the prepared path
+
+template <int kLinPer>  // 4: key_dim <= 128, 8: key_dim <= 256
+__global__ void __launch_bounds__(kLpThreads) lin_part_kernel(float* __restrict__ conv_ring, const float* qkv_in,
+                                                      const uint16_t* __restrict__ conv_w, const float* alpha,
+                                                      const float* beta, const float* __restrict__ a_log,
+                                                      const uint16_t* __restrict__ dt_bias, float* __restrict__ state,
+                                                      const float* z, const uint16_t* __restrict__ norm_w,
+                                                      float* __restrict__ out_gated, float* __restrict__ ss_part,
+                                                      const int* __restrict__ pos_ptr, int total_key,
+                                                      int conv_dim, int ksize, int k_heads_per_v, int key_dim, int value_dim,
+                                                      int parts) {
+    extern __shared__ float lsm[];
+    __shared__ float red[kLpWarps], red2[kLpWarps];
+    float* qs = lsm;
+    float* ks = qs + key_dim;
+    float* vs = ks + key_dim;  // [kLpRows]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.x / parts, part = blockIdx.x % parts, kh = h / k_heads_per_v;
+    const int v_begin = part * kLpRows;
+    const int nv = value_dim - v_begin < kLpRows ? value_dim - v_begin : kLpRows;
+    pdl_trigger();
+    // ahead of the wait: this warp's state rows, this thread's channels (taps and the ring rows they multiply), the
+    // head's decay parameters
+    float sreg[kLinRows][kLinPer];
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        const int v = warp * kLinRows + r;
+        const float* srow = state + ((size_t)h * value_dim + v_begin + v) * key_dim;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            sreg[r][j] = (v < nv && i < key_dim) ? srow[i] : 0.0f;
+        }
+    }
+    const int pos = *pos_ptr;
+    const int n_ch = 2 * key_dim + nv;
+    auto channel_of = [&](int i) {
+        return i < key_dim ? kh * key_dim + i
+               : i < 2 * key_dim ? total_key + kh * key_dim + (i - key_dim)
+                                 : 2 * total_key + h * value_dim + v_begin + (i - 2 * key_dim);
+    };
+    const bool prepared = conv_w != nullptr && ksize <= kLpK;
+    int c_mine[kLpCh];
+    float cw[kLpCh][kLpK], rv[kLpCh][kLpK];
+#pragma unroll
+    for (int u = 0; u < kLpCh; ++u) {
+        const int i = tid + u * kLpThreads;
+        c_mine[u] = i < n_ch ? channel_of(i) : 0;
+#pragma unroll
+        for (int k = 0; k < kLpK; ++k) {
+            cw[u][k] = rv[u][k] = 0.0f;
+            if (prepared && i < n_ch && k < ksize) cw[u][k] = bf16_bits_to_f32(conv_w[(size_t)c_mine[u] * ksize + k]);
+            if (prepared && i < n_ch && k < ksize - 1) {
+                const int step = pos - (ksize - 1) + k;                   // the input this tap multiplies
+                const int row = ((step % ksize) + ksize) % ksize;         // rows of steps before the start hold zeros
+                rv[u][k] = conv_ring[(size_t)row * conv_dim + c_mine[u]];
+            }
+        }
+    }
+    const float a_log_h = a_log ? a_log[h] : 0.0f;
+    const float dt_bias_h = dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f;
+    // lanes 0..3 of a warp finish one of its rows each: the row's norm weight now, its gate input after the wait
+    const int v_fin = warp * kLinRows + (lane & (kLinRows - 1));
+    const float nw_fin = (lane < kLinRows && v_fin < nv) ? bf16_bits_to_f32(norm_w[v_begin + v_fin]) : 0.0f;
+    pdl_wait();
+    const float z_fin = (lane < kLinRows && v_fin < nv) ? z[(size_t)h * value_dim + v_begin + v_fin] : 0.0f;
+    float xin_mine[kLpCh];
+#pragma unroll
+    for (int u = 0; u < kLpCh; ++u) xin_mine[u] = tid + u * kLpThreads < n_ch ? qkv_in[c_mine[u]] : 0.0f;
+    const float alpha_h = alpha[h], beta_h = beta[h];
+    // 1. conv + SiLU (conv1d_step, src/math_util.rs:149-168) and the ring update
+    for (int i = tid, u = 0; i < n_ch; i += kLpThreads, ++u) {
+        const bool mine = u < kLpCh;
+        int c = channel_of(i);
+        float xin, val;
+        if (mine) {
+            // (constant indices: the arrays stay in registers)
+            xin = u == 0 ? xin_mine[0] : xin_mine[1];
+        } else {
+            xin = qkv_in[c];
+        }
+        val = xin;
+        if (conv_w) {
+            float acc = 0.0f;
+            if (mine && prepared) {
+#pragma unroll
+                for (int k = 0; k < kLpK; ++k)
+                    if (k < ksize - 1) acc += (u == 0 ? rv[0][k] : rv[1][k]) * (u == 0 ? cw[0][k] : cw[1][k]);
+                float w_last = u == 0 ? cw[0][0] : cw[1][0];
+#pragma unroll
+                for (int k = 1; k < kLpK; ++k)
+                    if (k == ksize - 1) w_last = u == 0 ? cw[0][k] : cw[1][k];
+                acc += xin * w_last;
+            } else {
+                for (int k = 0; k < ksize - 1; ++k) {
+                    const int step = pos - (ksize - 1) + k;
+                    const int row = ((step % ksize) + ksize) % ksize;
+                    acc += conv_ring[(size_t)row * conv_dim + c] * bf16_bits_to_f32(conv_w[(size_t)c * ksize + k]);
+                }
+                acc += xin * bf16_bits_to_f32(conv_w[(size_t)c * ksize + ksize - 1]);
+            }
+            val = acc / (1.0f + expf(-acc));  // silu (src/math_util.rs:71-75)
+            conv_ring[(size_t)(pos % ksize) * conv_dim + c] = xin;
+        }
+        if (i < key_dim) qs[i] = val;
+        else if (i < 2 * key_dim) ks[i - key_dim] = val;
+        else vs[i - 2 * key_dim] = val;
+    }
+    __syncthreads();
+    // 2. q / k norms (cpu.rs:277-299)
+    float sq = 0.0f, sk = 0.0f;
+    for (int i = tid; i < key_dim; i += kLpThreads) {
+        sq = fmaf(qs[i], qs[i], sq);
+        sk = fmaf(ks[i], ks[i], sk);
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) { red[warp] = sq; red2[warp] = sk; }
+    __syncthreads();
+    float tq = 0.0f, tk = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kLpWarps; ++i) { tq += red[i]; tk += red2[i]; }
+    const float inv_scale = 1.0f / sqrtf((float)key_dim);
+    const float q_mul = (1.0f / sqrtf(tq / (float)key_dim + 1e-6f)) * inv_scale * inv_scale;
+    const float k_mul = (1.0f / sqrtf(tk / (float)key_dim + 1e-6f)) * inv_scale;
+    // 3. decay and input gate of this head (compute_decay_beta, math_util.rs:401-416)
+    const float a = expf(a_log_h);
+    const float softplus = logf(1.0f + expf(alpha_h + dt_bias_h));
+    const float g = expf(-a * softplus);
+    const float bgate = 1.0f / (1.0f + expf(-beta_h));
+    // 4. the delta rule on this warp's rows (gated_delta_net_step, math_util.rs:425-466); q and k are scaled as they are read
+    float kv[kLinRows];
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            sreg[r][j] *= g;
+            if (i < key_dim) acc = fmaf(sreg[r][j], ks[i] * k_mul, acc);
+        }
+        kv[r] = acc;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+    float ov[kLinRows];
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        const int v = warp * kLinRows + r;
+        const float delta = ((v < nv ? vs[v] : 0.0f) - kv[r]) * bgate;
+        float* srow = state + ((size_t)h * value_dim + v_begin + v) * key_dim;
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            if (v < nv && i < key_dim) {
+                const float sn = sreg[r][j] + (ks[i] * k_mul) * delta;
+                srow[i] = sn;
+                acc = fmaf(sn, qs[i] * q_mul, acc);
+            }
+        }
+        ov[r] = acc;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) ov[r] += __shfl_xor_sync(0xffffffffu, ov[r], o);
+    // 5. gated RMS norm (math_util.rs:472-493) up to the head's 1 / rms, which needs the other CTAs' rows: the outputs go
+    //    out times silu(z) and the norm weight, this CTA's sum of squares beside them, and the consumer scales by
+    //    rsqrt(mean + eps) while it stages its input.  Every lane holds the warp's sums; lane r finishes row r.
+    float mine = 0.0f, ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        if (lane == r) mine = ov[r];
+        if (warp * kLinRows + r < nv) ss = fmaf(ov[r], ov[r], ss);
+    }
+    if (lane < kLinRows && v_fin < nv)
+        out_gated[(size_t)h * value_dim + v_begin + v_fin] = mine * (z_fin / (1.0f + expf(-z_fin))) * nw_fin;
+    __syncthreads();  // red was read by every warp above
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (tid == 0) {
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kLpWarps; ++i) tot += red[i];
+        ss_part[blockIdx.x] = tot;
     }
 }
 
@@ -1087,6 +1290,29 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_B], x, bb, nullptr, pdl))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_A], x, ab, nullptr, pdl))) return rc;
         }
+        // a head's state rows dealt to several small CTAs, the gated norm folded into the output projection's kernel,
+        // where that kernel can do it; one large CTA per head doing everything otherwise
+        const ProjTensor& op = ls.proj[MOE_A_OUT_PROJ];
+        const int parts = (d.lin_value_dim + kLpRows - 1) / kLpRows;
+        const bool split = a.lin_split && op.dtype == MOE_DT_INT4 && ls.vec[MOE_A_LIN_NORM] != nullptr &&
+                           matvec_folds_head_scale(op.rows, op.cols, d.lin_value_dim) &&
+                           2 * d.lin_key_dim + kLpRows <= kLpCh * kLpThreads && (size_t)d.lin_num_v_heads * parts <= mid_n;
+        if (split) {
+            auto* part_kernel = d.lin_key_dim <= 128 ? lin_part_kernel<4> : lin_part_kernel<8>;
+            float* ss_part = normed;  // one sum of squares per CTA
+            MOE_CUDA(launch_kernel(pdl, part_kernel, dim3(d.lin_num_v_heads * parts), dim3(kLpThreads),
+                                   (size_t)(2 * d.lin_key_dim + kLpRows) * 4, st, ls.conv_state, qkv_raw,
+                                   (const uint16_t*)ls.vec[MOE_A_CONV1D], ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
+                                   (const uint16_t*)ls.vec[MOE_A_DT_BIAS], ls.ssm_state, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM],
+                                   vals, ss_part, a.d_pos, (int)z.total_key, (int)z.conv_dim, d.conv_kernel,
+                                   d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim, parts));
+            e->launches++;
+            if ((rc = launch_matvec_head_scaled(e, op.w, op.w + op.s_off, op.w + op.b_off, vals, ss_part, parts, d.lin_value_dim,
+                                                h_mid, op.rows, op.cols, h, pdl)))
+                return rc;
+            MOE_CUDA(cudaGetLastError());
+            return MOE_OK;
+        }
         const size_t lin_smem = (size_t)(2 * d.lin_key_dim + 2 * d.lin_value_dim) * 4;
         auto* lin_kernel = d.lin_key_dim <= 128 ? lin_core_kernel<4> : lin_core_kernel<8>;
         MOE_CUDA(launch_kernel(pdl, lin_kernel, dim3(d.lin_num_v_heads), dim3(kLinThreads), lin_smem, st, ls.conv_state, qkv_raw,
@@ -1113,6 +1339,8 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
     const char* env = getenv("MOE_B200_ATTN_GRAPHS");
     const char* env_pdl = getenv("MOE_B200_ATTN_PDL");
     a.pdl = !(env_pdl && atoi(env_pdl) == 0);
+    const char* env_split = getenv("MOE_B200_LIN_SPLIT");
+    a.lin_split = !(env_split && atoi(env_split) == 0);
     const int L = e->dims.num_layers;
     a.graphs.assign((size_t)L, nullptr);
     a.graph_nodes.assign((size_t)L, 0);

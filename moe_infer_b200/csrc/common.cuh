@@ -180,6 +180,7 @@ struct ModelAttnState {
     std::vector<int> graph_nodes;            // kernels in each
     bool graphs_valid = false;
     bool pdl = true;                         // kernels of a layer's attention half start ahead of their predecessor's end
+    bool lin_split = true;                   // DeltaNet core as 256-thread CTAs per block of state rows (gated norm in the out projection)
 };
 
 }  // namespace moe
@@ -251,6 +252,12 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
                       int32_t cols, const float* residual, bool pdl = false, const void* norm_w = nullptr);
 // whether launch_matvec_res can apply rmsnorm(x) * norm_w (bf16 weights) to its input itself for this shape
 bool matvec_folds_norm(int32_t rows, int32_t cols);
+// y = W (x scaled per head) + residual: the last step of a per-head RMS norm (sums of squares left in `ss` by the producer,
+// `parts` entries per head) folded into the kernel's staging
+bool matvec_folds_head_scale(int32_t rows, int32_t cols, int32_t head_dim);
+int launch_matvec_head_scaled(moe_engine* e, const void* w, const void* s, const void* b, const float* x, const float* ss,
+                              int32_t parts, int32_t head_dim, float* y, int32_t rows, int32_t cols, const float* residual,
+                              bool pdl);
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);
@@ -333,7 +340,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // pdl_wait() it touches only bytes that no kernel writes (weights) and its own shared memory; pdl_wait() returns once
 // the preceding kernel has completed and its writes are visible, and since that kernel waited in the same way, so has
 // everything before it.  pdl_trigger() lets the next kernel of the chain become resident; both are no-ops in a
-// kernel launched the ordinary way.
+// kernel launched the ordinary way.  A pointer to what an earlier kernel of the chain wrote must not be declared
+// `const __restrict__`: the compiler then treats it as read-only for the whole kernel and may move its loads above
+// the wait (seen: a kernel resident early read its predecessor's output buffer before that had been written).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif

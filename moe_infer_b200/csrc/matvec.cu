@@ -16,9 +16,13 @@ constexpr int kMvWarps = 8;
 
 __global__ void __launch_bounds__(kMvWarps * 32)
 matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s,
-                   const uint16_t* __restrict__ b, const float* __restrict__ x,
+                   const uint16_t* __restrict__ b, const float* x,
                    float* __restrict__ y, int rows, int cols, unsigned int* err_flag,
-                   const float* __restrict__ residual) {  // nullable: y = W x + residual
+                   const float* residual,  // nullable: y = W x + residual
+                   // nullable: every head of hs_dim inputs is scaled by rsqrt(sum / hs_dim + 1e-6), its sum of squares being
+                   // the total of the head's hs_parts entries of hs_ss (the RMS norm of a gated norm whose other factors the
+                   // producer has applied already; hs_dim % 32 == 0)
+                   const float* hs_ss, int hs_parts, int hs_dim) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nch = cols / 32;  // chunks per row
     float* raw = reinterpret_cast<float*>(smem_raw);                 // [cols]
@@ -69,22 +73,51 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
         mbar_expect_tx(&bar, (uint32_t)cols * 4u);
         bulk_g2s(raw, x, (uint32_t)cols * 4u, &bar);
     }
+    // the per-head scales of this thread's chunks (chunks tid and tid + 256: cols <= 16384), while x is on its way
+    float inv_mine[2] = {1.0f, 1.0f};
+    if (hs_ss) {
+        const int cph = hs_dim / 32;  // chunks per head
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = tid + u * kMvWarps * 32;
+            if (c < nch) {
+                float tot = 0.0f;
+                for (int k = 0; k < hs_parts; ++k) tot += hs_ss[(c / cph) * hs_parts + k];
+                inv_mine[u] = 1.0f / sqrtf(tot / (float)hs_dim + 1e-6f);
+            }
+        }
+    }
     // every thread observes the phase itself, so the copied bytes are visible to it
     const int ok = __syncthreads_and(mbar_wait(&bar, 0) ? 1 : 0);
     if (!ok) {
         if (tid == 0) atomicExch(err_flag, 1u);
         return;
     }
-    // chunk-transposed copy + per-chunk sums
-    for (int c = tid; c < nch; c += blockDim.x) {
-        float sum = 0.0f;
+    if (hs_ss) {
+        for (int c = tid, u = 0; c < nch; c += blockDim.x, ++u) {
+            const float inv = u == 0 ? inv_mine[0] : inv_mine[1];
+            float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float4 v = reinterpret_cast<const float4*>(raw)[c * 8 + j];
-            xs[j * nch + c] = v;
-            sum += (v.x + v.y) + (v.z + v.w);
+            for (int j = 0; j < 8; ++j) {
+                float4 v = reinterpret_cast<const float4*>(raw)[c * 8 + j];
+                v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+                xs[j * nch + c] = v;
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+            sumx[c] = sum;
         }
-        sumx[c] = sum;
+    } else {
+        // chunk-transposed copy + per-chunk sums
+        for (int c = tid; c < nch; c += blockDim.x) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 v = reinterpret_cast<const float4*>(raw)[c * 8 + j];
+                xs[j * nch + c] = v;
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+            sumx[c] = sum;
+        }
     }
     __syncthreads();
 
@@ -144,8 +177,8 @@ constexpr int kSvUnroll = 4;
 
 __global__ void __launch_bounds__(kSvWarps * 32, 2)
 matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s, const uint16_t* __restrict__ b,
-                          const float* __restrict__ x, float* __restrict__ y, int rows, unsigned int* err_flag,
-                          const float* __restrict__ residual,
+                          const float* x, float* __restrict__ y, int rows, unsigned int* err_flag,
+                          const float* residual,
                           const uint16_t* __restrict__ norm_w) {  // nullable: the input is rmsnorm(x) * norm_w (bf16), eps 1e-6
     constexpr int nch = kSvCols / 32;
     __shared__ __align__(128) float raw[kSvCols];
@@ -282,6 +315,29 @@ int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, co
     return launch_matvec_res(e, w, s, b, x, y, rows, cols, nullptr);
 }
 
+// y = W (x scaled per head) + residual: head h of head_dim inputs is multiplied by rsqrt(sum_h / head_dim + 1e-6), sum_h being
+// the total of ss[h * parts .. h * parts + parts): the last step of an RMS norm whose sums the producer left in `ss`
+bool matvec_folds_head_scale(int32_t rows, int32_t cols, int32_t head_dim) {
+    return !matvec_folds_norm(rows, cols) && head_dim > 0 && head_dim % 32 == 0 && cols % head_dim == 0 && cols <= 16384;
+}
+int launch_matvec_head_scaled(moe_engine* e, const void* w, const void* s, const void* b, const float* x, const float* ss,
+                              int32_t parts, int32_t head_dim, float* y, int32_t rows, int32_t cols, const float* residual,
+                              bool pdl) {
+    MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0 && parts > 0 && matvec_folds_head_scale(rows, cols, head_dim),
+                "matvec: cannot fold a norm of %d-element heads into a %d x %d product", head_dim, rows, cols);
+    MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
+    const size_t smem = (size_t)cols * 8 + (size_t)(cols / 32) * 4;
+    int rc = matvec_prepare(e);
+    if (rc) return rc;
+    int blocks = (rows + kMvWarps - 1) / kMvWarps;
+    const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
+    if (blocks > cap) blocks = cap;
+    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
+                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual, ss, parts, head_dim));
+    e->launches++;
+    return MOE_OK;
+}
+
 bool matvec_folds_norm(int32_t rows, int32_t cols) { return cols == kSvCols && rows >= 4096; }
 
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
@@ -310,7 +366,8 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
     const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
     if (blocks > cap) blocks = cap;
     MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
-                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual));
+                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual,
+                           (const float*)nullptr, 0, 0));
     e->launches++;
     return MOE_OK;
 }
