@@ -1219,7 +1219,8 @@ static int attn_fuse_layer(moe_engine* e, AttnLayerState& ls) {
 }
 
 // One layer's attention half on one token: h (device, [H]) -> h_mid (device, [H]) = attention(h) + h.
-static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch) {
+// first_pdl: the layer's first kernel is itself a programmatic dependent of the kernel before it in the stream
+static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch, bool first_pdl = false) {
     ModelAttnState& a = e->attn;
     AttnLayerState& ls = a.layers[layer];
     const moe_model_attn_dims_t& d = a.d;
@@ -1244,9 +1245,9 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     const bool fold = ls.fused.loaded && proj_folds_norm(ls.fused);
     const void* fold_w = fold ? ls.vec[MOE_A_INPUT_NORM] : nullptr;
     const float* proj_in = fold ? h : x;
-    bool pdl = false;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
+    bool pdl = first_pdl && a.pdl;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
     if (!fold) {
-        rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x);
+        MOE_CUDA(launch_kernel(pdl, rms_norm_rows_kernel, dim3(1), dim3(256), 0, st, h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x));
         e->launches++;
         pdl = a.pdl;
     }
@@ -1327,8 +1328,12 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     return MOE_OK;
 }
 
-// Captures every layer's attention half (fixed pointers, position read on the device) into a CUDA graph: a token then
-// costs one graph launch + the MoE launch per layer instead of a dozen launches issued one by one from the host.
+// Two ways to run a token's 160-odd kernels.  The default ("chain"): every kernel, the MoE kernels included, is launched
+// from the host as a programmatic dependent of the one before it, so each becomes resident, requests its weights and only
+// then waits for its input while its predecessor still runs (the host enqueues a token in about 0.4 ms, the device needs
+// four times that).  MOE_B200_ATTN_CHAIN=0 selects the other: every layer's attention half captured (fixed pointers,
+// position read on the device) into a CUDA graph, so a token costs one graph launch + the MoE launch per layer; the
+// graph's kernels are chained in the same way, but the graph and the MoE kernel meet at ordinary stream dependencies.
 // Inside a graph (and in the eager path alike) every kernel after the first is a programmatic dependent of the one
 // before it: it becomes resident while its predecessor still runs, asks for its weights (L2 prefetch) and only then
 // waits for the predecessor's results.  MOE_B200_ATTN_GRAPHS=0 keeps the eager launches, MOE_B200_ATTN_PDL=0 the
@@ -1339,6 +1344,8 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
     const char* env = getenv("MOE_B200_ATTN_GRAPHS");
     const char* env_pdl = getenv("MOE_B200_ATTN_PDL");
     a.pdl = !(env_pdl && atoi(env_pdl) == 0);
+    const char* env_chain = getenv("MOE_B200_ATTN_CHAIN");
+    a.chain = a.pdl && !(env_chain && atoi(env_chain) == 0);
     const char* env_split = getenv("MOE_B200_LIN_SPLIT");
     a.lin_split = !(env_split && atoi(env_split) == 0);
     const int L = e->dims.num_layers;
@@ -1349,7 +1356,7 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
         const int rc = attn_fuse_layer(e, ls);
         if (rc) return rc;
     }
-    if (env && atoi(env) == 0) return MOE_OK;
+    if ((env && atoi(env) == 0) || a.chain) return MOE_OK;
     for (int l = 0; l < L; ++l) {
         const int64_t before = e->launches;
         if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -1421,11 +1428,12 @@ int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* ou
                 MOE_CUDA(cudaGraphLaunch(a.graphs[l], e->stream));
                 e->launches += a.graph_nodes[l];
             } else {
-                rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch);
+                // chained: a layer's first kernel depends programmatically on the MoE kernel of the layer before it
+                rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch, a.chain && l > 0);
             }
             if (rc) return rc;
             float* nxt = (l == L - 1) ? out_dev + (size_t)t * H : layer_out[l];
-            rc = launch_decode(e, l, l + 1, h_mid, nxt, nullptr, nullptr, nullptr, nullptr);
+            rc = launch_decode(e, l, l + 1, h_mid, nxt, nullptr, nullptr, nullptr, nullptr, a.chain);
             if (rc) return rc;
         }
         a.pos++;

@@ -180,6 +180,7 @@ struct ModelAttnState {
     std::vector<int> graph_nodes;            // kernels in each
     bool graphs_valid = false;
     bool pdl = true;                         // kernels of a layer's attention half start ahead of their predecessor's end
+    bool chain = true;                       // no graphs: every kernel of a token, the MoE kernels included, is a programmatic dependent of the one before it
     bool lin_split = true;                   // DeltaNet core as 256-thread CTAs per block of state rows (gated norm in the out projection)
 };
 
@@ -266,7 +267,7 @@ int decode_reset_after_error(moe_engine* e);
 int ensure_router_t(moe_engine* e, int layer);
 // Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
-                  const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w);
+                  const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl = false);
 int decode_profile_enable(moe_engine* e, bool on);
 int decode_profile_read(moe_engine* e, long long* out, int max_layers, int* points);
 int batch_reserve(moe_engine* e, int32_t n_tokens);
@@ -344,6 +345,12 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // `const __restrict__`: the compiler then treats it as read-only for the whole kernel and may move its loads above
 // the wait (seen: a kernel resident early read its predecessor's output buffer before that had been written).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// 16 bytes of a predecessor's output, read where the code says (never moved above the wait)
+__device__ __forceinline__ float4 ld_dep_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 

@@ -1337,13 +1337,13 @@ static int launch_decode_chunk(moe_engine* e, int l0, int l1, const float* h_in,
 // layers; a later launch reads its input from h_out (a CTA writes its part of the output
 // only after every CTA has staged the input, so the two may be the same buffer).
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
-                  const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
+                  const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl) {
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size(), "decode: bad layer range [%d, %d)", l0, l1);
     for (int a = l0; a < l1; a += kMaxDecLayers) {
         const int b = a + kMaxDecLayers < l1 ? a + kMaxDecLayers : l1;
         // the slot-grouped kernel where the device and the model shape allow it, the grid-wide kernel otherwise
         int rc = slots_decode_usable(e, a, b)
-                     ? launch_decode_slots(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w)
+                     ? launch_decode_slots(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w, pdl && a == l0)
                      : launch_decode_chunk(e, a, b, a == l0 ? h_in : h_out, h_out, logit_bias, forced_idx, out_idx, out_w);
         if (rc != MOE_OK) return rc;
     }

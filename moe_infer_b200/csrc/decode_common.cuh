@@ -183,6 +183,6 @@ bool slots_decode_usable(const moe_engine* e, int l0, int l1);
 int slots_decode_reset(moe_engine* e);
 int slots_decode_prefetch_stats(moe_engine* e, double* checks, double* hits);
 int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float* h_out, const float* logit_bias,
-                        const int32_t* forced_idx, int32_t* out_idx, float* out_w);
+                        const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl = false);
 
 }  // namespace moe

@@ -224,12 +224,16 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
     const int n_layers = p.l1 - p.l0;
     const bool shared_slot = slot == K;
 
+    pdl_trigger();
     if (tid == 0) {
         mbar_init(&sm->bar_g[0], 6);
         mbar_init(&sm->bar_g[1], 6 + (shared_slot ? 3 : 0));
         mbar_init(&sm->bar_d, 3);
         mbar_fence_init();
     }
+    // launched as a programmatic dependent (the whole-decoder path), the kernel may be resident while the one that
+    // produces h_in still runs: nothing of global memory is touched before this wait
+    pdl_wait();
     {
         static_assert(sizeof(LayerDev) % 4 == 0, "table rows are copied as words");
         const uint32_t* src = reinterpret_cast<const uint32_t*>(p.layers + p.l0);
@@ -243,7 +247,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
     const int item0 = kItems * grank;     // this CTA's gate/up rows inside its slot's expert
     const int rt_e2 = tid & 127, rt_row0 = r0 + (tid >> 7) * kRtRows;  // this thread's part of the router slice
 
-    float4 hv = __ldg(reinterpret_cast<const float4*>(p.h_in) + tid);  // this thread's four elements of h
+    float4 hv = ld_dep_f4(reinterpret_cast<const float4*>(p.h_in) + tid);  // this thread's four elements of h
     // what this thread last read from its accumulator words: of the set about to be read / of the other set
     unsigned long long hprev_cur[4] = {0ull, 0ull, 0ull, 0ull}, hprev_oth[4] = {0ull, 0ull, 0ull, 0ull};
     unsigned long long lprev_cur = 0ull, lprev_oth = 0ull;
@@ -684,7 +688,7 @@ int slots_decode_prefetch_stats(moe_engine* e, double* checks, double* hits) {
 }
 
 int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float* h_out, const float* logit_bias,
-                        const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
+                        const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl) {
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size() && l1 - l0 <= kSlMaxLayers, "decode: bad layer range [%d, %d)", l0, l1);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
     for (int l = l0; l < l1; ++l) {
@@ -721,9 +725,20 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
     // the kernel's first CTA (a memset per launch cost a single-layer call about two microseconds of stream time)
     e->dec_sl_hint_base += (unsigned long long)kSG * (unsigned long long)(l1 - l0 + 1);  // one push per layer and the prologue's
     e->dec_sl_epoch += (unsigned int)(l1 - l0);
-    void* args[] = {&p};
-    MOE_CUDA(cudaLaunchCooperativeKernel((const void*)decode_slots_kernel, dim3(kSG), dim3(kDecThreads), args, sizeof(SlotSmem),
-                                         e->stream));
+    // a cooperative launch (every CTA resident), and on request a programmatic dependent of the kernel before it
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kSG);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = sizeof(SlotSmem);
+    cfg.stream = e->stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 2 : 1;
+    MOE_CUDA(cudaLaunchKernelEx(&cfg, decode_slots_kernel, p));
     e->launches++;
     return MOE_OK;
 }
