@@ -231,9 +231,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
         mbar_init(&sm->bar_d, 3);
         mbar_fence_init();
     }
-    // launched as a programmatic dependent (the whole-decoder path), the kernel may be resident while the one that
-    // produces h_in still runs: nothing of global memory is touched before this wait
-    pdl_wait();
+    // Launched as a programmatic dependent (the whole-decoder path), the kernel may be resident while the one that
+    // produces h_in still runs: until the wait below it reads only the layer table and the first layer's router slice,
+    // which no kernel of the chain writes (the host launches the ordinary way when it has just refreshed them).
     {
         static_assert(sizeof(LayerDev) % 4 == 0, "table rows are copied as words");
         const uint32_t* src = reinterpret_cast<const uint32_t*>(p.layers + p.l0);
@@ -247,11 +247,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
     const int item0 = kItems * grank;     // this CTA's gate/up rows inside its slot's expert
     const int rt_e2 = tid & 127, rt_row0 = r0 + (tid >> 7) * kRtRows;  // this thread's part of the router slice
 
+    uint32_t rt[kRtRows];
+    load_router_slice(rt, sm->tab[0].router_t, Ep, rt_row0, rt_e2);
+    pdl_wait();
     float4 hv = ld_dep_f4(reinterpret_cast<const float4*>(p.h_in) + tid);  // this thread's four elements of h
     // what this thread last read from its accumulator words: of the set about to be read / of the other set
     unsigned long long hprev_cur[4] = {0ull, 0ull, 0ull, 0ull}, hprev_oth[4] = {0ull, 0ull, 0ull, 0ull};
     unsigned long long lprev_cur = 0ull, lprev_oth = 0ull;
-    uint32_t rt[kRtRows];
     bool alive = true;
     float pscale = 1.0f;  // scale the pending logit accumulators were pushed with
 
@@ -369,7 +371,6 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_slots_kernel(SlotParams
 
     // ── prologue: router logits of the first layer from h_in (the first group's rows cover all of h) ──
     {
-        load_router_slice(rt, sm->tab[0].router_t, Ep, rt_row0, rt_e2);
         pscale = block_inv_rms(sm, hv);
         if (warp == grank) {
             const uint2 nw = __ldg(reinterpret_cast<const uint2*>(sm->tab[0].post_norm) + tid);
@@ -691,6 +692,8 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
                         const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl) {
     MOE_REQUIRE(l0 >= 0 && l1 > l0 && l1 <= (int)e->layers.size() && l1 - l0 <= kSlMaxLayers, "decode: bad layer range [%d, %d)", l0, l1);
     MOE_REQUIRE((((uintptr_t)h_in) & 15) == 0 && (((uintptr_t)h_out) & 15) == 0, "decode: h must be 16-byte aligned");
+    const int64_t launches_before = e->launches;
+    const bool table_was_dirty = e->table_dirty;
     for (int l = l0; l < l1; ++l) {
         int rc = check_layer_ready(e, l);
         if (rc != MOE_OK) return rc;
@@ -699,6 +702,8 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
     }
     int rc = refresh_layer_table(e);
     if (rc != MOE_OK) return rc;
+    // what the kernel reads ahead of its dependency wait was just rewritten on this stream: an ordinary launch this time
+    if (e->launches != launches_before || table_was_dirty || e->table_dirty) pdl = false;
     if (e->dec_sl_epoch > 0xFFFF0000u - (unsigned int)(l1 - l0)) {
         rc = slots_decode_reset(e);  // tags must never repeat: start the epochs over on cleared buffers
         if (rc != MOE_OK) return rc;
