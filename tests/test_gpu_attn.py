@@ -115,6 +115,37 @@ def test_decode_with_attention_matches_oracle(scheme):
     eng.close()
 
 
+def test_launch_modes_agree(monkeypatch):
+    """The ways of launching a token's kernels (every kernel a programmatic dependent of the one before it, the default;
+    one CUDA graph per attention half; plain launches; ordinary dependencies) change scheduling only: bit-identical
+    results.  The one-CTA-per-head DeltaNet kernel sums in another order than the split one: equal to rounding."""
+    layers = 4
+    ad, attn = _attn_weights(53, "bq4", layers)
+    moe = [make_layer(53, l, num_experts=E) for l in range(layers)]
+    emb = synth.hidden_states(53, 2, 5, H)
+
+    def run(env):
+        for k in ("MOE_B200_ATTN_CHAIN", "MOE_B200_ATTN_GRAPHS", "MOE_B200_ATTN_PDL", "MOE_B200_LIN_SPLIT"):
+            monkeypatch.delenv(k, raising=False)
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=layers, vocab=V))   # the switches are read at the first step
+        for l in range(layers):
+            upload_layer(eng, l, moe[l])
+        _upload_attn(eng, attn)
+        out = np.concatenate([eng.model_forward_hidden(emb[:2]), eng.model_forward_hidden(emb[2:])])
+        eng.close()
+        return out
+
+    base = run({})
+    for env in ({"MOE_B200_ATTN_CHAIN": "0"}, {"MOE_B200_ATTN_CHAIN": "0", "MOE_B200_ATTN_GRAPHS": "0"}, {"MOE_B200_ATTN_PDL": "0"},
+                {"MOE_B200_ATTN_PDL": "0", "MOE_B200_ATTN_GRAPHS": "0"}):
+        assert np.array_equal(run(env), base), env
+    other = run({"MOE_B200_LIN_SPLIT": "0"})
+    assert rel_l2(other, base) < 1e-5
+    assert np.array_equal(run({"MOE_B200_LIN_SPLIT": "0", "MOE_B200_ATTN_CHAIN": "0"}), other)
+
+
 def test_attention_error_paths():
     layers = 4
     ad, attn = _attn_weights(52, "bq4", layers)
