@@ -22,8 +22,8 @@ AD = dict(num_heads=4, num_kv_heads=2, head_dim=64, rotary_dim=16, rope_theta=1.
           lin_key_dim=32, lin_value_dim=64, conv_kernel=4, full_attn_interval=4)
 
 
-def _attn_weights(seed, scheme, layers):
-    ad = oracle.AttnDims(**AD)
+def _attn_weights(seed, scheme, layers, dims=None):
+    ad = oracle.AttnDims(**(dims or AD))
     rng = np.random.default_rng(seed)
     bf = lambda a: oracle.f32_to_bf16(np.asarray(a, np.float32))
     f = oracle.bf16_to_f32
@@ -50,8 +50,8 @@ def _attn_weights(seed, scheme, layers):
     return ad, out
 
 
-def _upload_attn(eng, attn_layers, max_seq=16):
-    eng.attn_configure(max_seq=max_seq, **AD)
+def _upload_attn(eng, attn_layers, max_seq=16, dims=None):
+    eng.attn_configure(max_seq=max_seq, **(dims or AD))
     for l, w in enumerate(attn_layers):
         eng.attn_load_vec(l, L.A_INPUT_NORM, w.input_norm)
         if isinstance(w, oracle.FullAttnWeights):
@@ -112,6 +112,33 @@ def test_decode_with_attention_matches_oracle(scheme):
     again = eng.model_forward_hidden(emb[2:4])
     want2 = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb[t], K) for t in (2, 3)])
     assert rel_l2(again, want2) < 1e-2 and eng.model_pos() == 2
+    eng.close()
+
+
+def test_decode_with_attention_at_the_model_own_head_counts():
+    """The shapes the kernels are tuned for (Qwen3.6-35B-A3B: 16 query / 2 KV heads of 256 with 64 rotary dimensions; 16 key
+    and 32 value heads of 128, conv over 8,192 channels): the streaming 4-bit matvec with the input norm folded in
+    (12,352 stacked rows), four CTAs per DeltaNet head with the norm's 1/rms folded into the 4,096-column output
+    projection, the bf16 projections of 9,216 and 2,048 rows, attention over 256-wide heads.  Four layers (three DeltaNet,
+    one full attention), five tokens so that the conv ring wraps and the cache is attended over."""
+    dims = dict(num_heads=16, num_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1.0e7, lin_num_k_heads=16, lin_num_v_heads=32,
+                lin_key_dim=128, lin_value_dim=128, conv_kernel=4, full_attn_interval=4)
+    layers = 4
+    ad, attn = _attn_weights(57, "bq4", layers, dims)
+    moe = [make_layer(57, l, num_experts=E) for l in range(layers)]
+    eng = NativeEngine(Dims(num_experts=E, top_k=K, num_layers=layers, vocab=V))
+    for l in range(layers):
+        upload_layer(eng, l, moe[l])
+    _upload_attn(eng, attn, dims=dims)
+    emb = synth.hidden_states(57, 2, 5, H)
+    state = oracle.ModelState(ad, layers, 16)
+    want = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb[t], K) for t in range(5)])
+    got = np.concatenate([eng.model_forward_hidden(emb[:2]), eng.model_forward_hidden(emb[2:])])
+    errs = [rel_l2(got[t], want[t]) for t in range(5)]
+    print(f"decode with attention at the model's head counts: rel-L2 per token {['%.1e' % x for x in errs]}")
+    assert max(errs) < 1e-2 and rel_l2(got - emb, want - emb) < 1e-2
+    ssm = eng.model_state_download(0, L.ST_SSM, state.lin[0][1].size)
+    assert rel_l2(ssm, state.lin[0][1].ravel()) < 1e-2
     eng.close()
 
 
