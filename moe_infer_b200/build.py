@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libmoe_b200.so")
-SOURCES = ["engine.cu", "pack.cu", "matvec.cu", "decode.cu", "decode_slots.cu", "head.cu", "attn.cu", "grouped.cu", "ep.cu", "synth.cu"]
+SOURCES = ["engine.cu", "pack.cu", "matvec.cu", "decode.cu", "decode_slots.cu", "head.cu", "attn.cu", "grouped.cu", "slots_ffn.cu", "ep.cu", "synth.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = os.environ.get("MOE_B200_NVCC_EXTRA", "").split()
 FLAGS = EXTRA + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -91,6 +91,8 @@ struct BatchWork {
     int32_t* slot_of = nullptr;    // [cap*K] slot of (token, k)
     __nv_bfloat16* act = nullptr;  // [cap*K + cap, I] SwiGLU outputs, expert-sorted, K-interleaved
     __nv_bfloat16* o = nullptr;    // [cap*K + cap, H] down-projection outputs, expert-sorted
+    int32_t* slot_expert = nullptr;  // [cap*K + cap] expert of each slot (E: the shared expert), written for small batches
+    float* act32 = nullptr;        // [small*K + small, I] f32 SwiGLU outputs of the slot-wise FFN (small batches)
     int32_t* tile_list = nullptr;  // (expert, first slot, slots) per token tile
     int32_t* n_tiles = nullptr;
     int32_t max_tiles = 0;
@@ -266,6 +268,8 @@ void decode_destroy(moe_engine* e);
 int decode_reset_after_error(moe_engine* e);
 int ensure_router_t(moe_engine* e, int layer);
 // Runs layers [l0, l1) on one token: h_in (device, [H]) -> h_out (device, [H]).
+int launch_slot_ffn(moe_engine* e, const moe::LayerDev& ly, const float* h_in, int slots, const int32_t* slot_token,
+                    const int32_t* slot_expert, float* act, void* o);
 int launch_decode(moe_engine* e, int l0, int l1, const float* h_in, float* h_out,
                   const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w, bool pdl = false);
 int decode_profile_enable(moe_engine* e, bool on);

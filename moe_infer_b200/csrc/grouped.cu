@@ -49,6 +49,9 @@ constexpr int kAStages = 2;   // dequantised weight tiles (produced locally: sha
 constexpr int kBStages = 4;   // activation tiles (copied from L2: deep ring, kBStages - 1 K steps of lookahead)
 constexpr int kFullRing = 4;  // "operands in place" barriers (producers run at most kAStages steps ahead of the MMAs)
 constexpr int kMaxEPerLane = 16;
+constexpr int kSlotPathMaxTokens = 256;  // the slot-wise expert FFN's work area is sized for this many tokens
+constexpr int kSlotPathDefault = 48;     // batches up to this size take it: 76 against 128 us at 8 tokens, 147 against 191 us
+                                         // at 32, level at 64 (L2-to-SM traffic grows with the slots), behind from there
 
 // position of logical column j (0..7) inside a K-interleaved 8-block
 __host__ __device__ __forceinline__ int ipos(int j) { return ((j & 3) << 1) | (j >> 2); }
@@ -518,7 +521,8 @@ __global__ void __launch_bounds__(1024) batch_plan_kernel(int32_t* counts, int32
 __global__ void __launch_bounds__(256) batch_scatter_kernel(const int32_t* __restrict__ topk_idx, int n, int K, int E,
                                                             const int32_t* __restrict__ offsets, int32_t* cursor,
                                                             int32_t* __restrict__ slot_token,
-                                                            int32_t* __restrict__ slot_of) {
+                                                            int32_t* __restrict__ slot_of,
+                                                            int32_t* __restrict__ slot_expert) {  // nullable
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n * K) {
         const int t = i / K;
@@ -526,8 +530,12 @@ __global__ void __launch_bounds__(256) batch_scatter_kernel(const int32_t* __res
         const int slot = offsets[e] + atomicAdd(&cursor[e], 1);
         slot_token[slot] = t;
         slot_of[i] = slot;
+        if (slot_expert) slot_expert[slot] = e;
     }
-    if (i < n) slot_token[offsets[E] + i] = i;
+    if (i < n) {
+        slot_token[offsets[E] + i] = i;
+        if (slot_expert) slot_expert[offsets[E] + i] = E;
+    }
 }
 
 // ─── grouped GEMM ───────────────────────────────────────────────────────────
@@ -1232,6 +1240,9 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     const size_t o_cnt = take((E + 1) * 4), o_off = take((E + 2) * 4), o_cur = take((E + 1) * 4);
     const size_t o_st = take(slots * 4), o_so = take(n * K * 4), o_act = take(slots * I * 2), o_o = take(slots * H * 2);
     const size_t o_tl = take((size_t)max_tiles * 3 * 4), o_nt = take(4);
+    // the slot-wise expert FFN of small batches: the expert of every slot, f32 SwiGLU outputs of up to kSlotPathMaxTokens tokens
+    const size_t small_n = n < (size_t)kSlotPathMaxTokens ? n : (size_t)kSlotPathMaxTokens;
+    const size_t o_se = take(slots * 4), o_a32 = take((small_n * K + small_n) * I * 4);
     MOE_CUDA(cudaMalloc(&bw.base, off));
     uint8_t* b = bw.base;
     bw.h_a = (float*)(b + o_ha); bw.h_b = (float*)(b + o_hb);
@@ -1242,6 +1253,7 @@ int batch_reserve(moe_engine* e, int32_t n_tokens) {
     bw.slot_token = (int32_t*)(b + o_st); bw.slot_of = (int32_t*)(b + o_so);
     bw.act = (__nv_bfloat16*)(b + o_act); bw.o = (__nv_bfloat16*)(b + o_o);
     bw.tile_list = (int32_t*)(b + o_tl); bw.n_tiles = (int32_t*)(b + o_nt);
+    bw.slot_expert = (int32_t*)(b + o_se); bw.act32 = (float*)(b + o_a32);
     bw.max_tiles = max_tiles;
     bw.capacity = n_tokens;
     bw.logit_rows = (int64_t)lg_rows;
@@ -1294,7 +1306,16 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     if (E <= 256) batch_route_kernel<8><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{}, e->dec_sync + 2);
     else batch_route_kernel<16><<<(n + 7) / 8, 256, 0, st>>>(bw.logits, n, E, K, logit_bias, forced_idx, idx, wts, bw.counts, rsplit, EpPush{}, e->dec_sync + 2);
     batch_plan_kernel<<<1, 1024, 0, st>>>(bw.counts, bw.offsets, bw.cursor, E, n, bw.tile_list, bw.n_tiles, bw.max_tiles);
-    batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of);
+    // Few tokens per expert: the slot-wise matvec form of the expert FFN (slots_ffn.cu); otherwise the grouped GEMMs.
+    static const int slot_max = [] { const char* v = getenv("MOE_B200_SLOT_FFN_MAX"); return v ? atoi(v) : kSlotPathDefault; }();
+    const bool by_slot = n <= slot_max && n <= kSlotPathMaxTokens;
+    batch_scatter_kernel<<<(n * K + 255) / 256, 256, 0, st>>>(idx, n, K, E, bw.offsets, bw.cursor, bw.slot_token, bw.slot_of,
+                                                               by_slot ? bw.slot_expert : nullptr);
+    if (by_slot) {
+        rc = launch_slot_ffn(e, ly, h_in, n * K + n, bw.slot_token, bw.slot_expert, bw.act32, bw.o);
+        if (rc) return rc;
+        e->launches -= 2;  // counted with the layer's eight below
+    } else {
     GemmParams gp{};
     gp.experts = ly.experts; gp.shared = ly.shared; gp.lay = e->lay; gp.E = E;
     gp.x = bw.x; gp.act = bw.act; gp.o = bw.o;
@@ -1302,6 +1323,7 @@ int launch_batched_layer(moe_engine* e, int layer, const float* h_in, int32_t n,
     gp.err = e->dec_sync + 2;
     grouped_gemm_kernel<1><<<e->sm_count, kGemmThreads, gemm_smem_bytes<1>(), st>>>(gp);
     grouped_gemm_kernel<2><<<e->sm_count, kGemmThreads, gemm_smem_bytes<2>(), st>>>(gp);
+    }
     batch_combine_kernel<<<n, 256, 0, st>>>(h_in, h_out, n, K, E, bw.o, bw.slot_of, wts, bw.sgate, bw.offsets);
     e->launches += 8;
     MOE_CUDA(cudaGetLastError());

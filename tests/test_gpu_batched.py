@@ -42,7 +42,7 @@ def small():
     eng.close()
 
 
-@pytest.mark.parametrize("n", [2, 5, 37, 128, 130, 300])
+@pytest.mark.parametrize("n", [2, 5, 37, 48, 49, 128, 130, 300])  # up to 48 tokens: the slot-wise expert FFN; beyond: the grouped GEMMs
 def test_batched_layer_small(small, n):
     eng, lw = small
     _check(eng, lw, synth.hidden_states(n, 3, n, 2048), 8)
@@ -79,6 +79,7 @@ def test_batched_all_tokens_one_expert_set():
     h = synth.hidden_states(6, 3, n, 2048)
     forced = np.tile(np.array([[5, 1]], np.int32), (n, 1))
     _check(eng, lw, h, 2, forced_idx=forced)
+    _check(eng, lw, h[:20], 2, forced_idx=forced[:20])  # the same skew through the slot-wise path: 20 slots per expert in a row
     eng.close()
 
 
