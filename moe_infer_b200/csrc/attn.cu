@@ -936,6 +936,11 @@ void attn_destroy(moe_engine* e) {
     attn_drop_graphs(e);
     if (a.d_pos) cudaFree(a.d_pos);
     a.d_pos = nullptr;
+    if (a.pos_table) cudaFree(a.pos_table);
+    a.pos_table = nullptr;
+    if (a.prefill_mid) cudaFree(a.prefill_mid);
+    a.prefill_mid = nullptr;
+    a.prefill_cap = 0;
     for (AttnLayerState& ls : a.layers) {
         for (int i = 0; i < 16; ++i) {
             if (ls.vec[i]) cudaFree(ls.vec[i]);
@@ -1097,6 +1102,13 @@ int attn_configure(moe_engine* e, const moe_model_attn_dims_t* dims) {
                    2 * al256a(mid * 4) + al256a(z.q_dim * 4);
     MOE_CUDA(cudaMalloc(&a.work, bytes));
     MOE_CUDA(cudaMalloc(&a.d_pos, 256));
+    {
+        // positions 0 .. max_seq - 1 as a device table: a launch that is not replayed takes its position from there
+        std::vector<int> tab((size_t)dims->full.max_seq);
+        for (int i = 0; i < dims->full.max_seq; ++i) tab[(size_t)i] = i;
+        MOE_CUDA(cudaMalloc(&a.pos_table, tab.size() * sizeof(int)));
+        MOE_CUDA(cudaMemcpy(a.pos_table, tab.data(), tab.size() * sizeof(int), cudaMemcpyHostToDevice));
+    }
     // function attributes are set here, never between the launches of a layer (those are captured into graphs)
     MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
     e->mtp.bf_attr_set = true;
@@ -1220,7 +1232,9 @@ static int attn_fuse_layer(moe_engine* e, AttnLayerState& ls) {
 
 // One layer's attention half on one token: h (device, [H]) -> h_mid (device, [H]) = attention(h) + h.
 // first_pdl: the layer's first kernel is itself a programmatic dependent of the kernel before it in the stream
-static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch, bool first_pdl = false) {
+// pos_ptr: where the kernels read the token's position (null: the engine's device-side position word)
+static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch, bool first_pdl = false,
+                           const int* pos_ptr = nullptr) {
     ModelAttnState& a = e->attn;
     AttnLayerState& ls = a.layers[layer];
     const moe_model_attn_dims_t& d = a.d;
@@ -1228,6 +1242,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     const int H = (int)z.H;
     const size_t Hv = (size_t)d.lin_num_v_heads;
     cudaStream_t st = e->stream;
+    const int* posp = pos_ptr ? pos_ptr : a.d_pos;
     const size_t mid_n = z.q_dim > z.total_value ? z.q_dim : z.total_value;
     float* p = scratch;
     auto take = [&](size_t n) { float* r = p; p += al256a(n * 4) / 4; return r; };
@@ -1269,10 +1284,10 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         }
         MOE_CUDA(launch_kernel(pdl, attn_prep_kernel, dim3(nh + nkv), dim3(256), (size_t)hd * 4, st, qb, 2 * hd, 1, kb, vb,
                                (const uint16_t*)ls.vec[MOE_A_Q_NORM], (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd,
-                               d.full.rotary_dim, 0, a.d_pos, d.full.rope_theta, qr, ls.k_cache, ls.v_cache));
+                               d.full.rotary_dim, 0, posp, d.full.rope_theta, qr, ls.k_cache, ls.v_cache));
         // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
         MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(kAttnWarps * 32), (size_t)(d.full.max_seq + hd * (1 + kAttnWarps)) * 4, st, qr, ls.k_cache,
-                               ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, a.d_pos, 1.0f / sqrtf((float)hd), vals));
+                               ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, posp, 1.0f / sqrtf((float)hd), vals));
         e->launches += 2;
         if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h, pdl))) return rc;  // + residual
     } else {
@@ -1305,7 +1320,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
                                    (size_t)(2 * d.lin_key_dim + kLpRows) * 4, st, ls.conv_state, qkv_raw,
                                    (const uint16_t*)ls.vec[MOE_A_CONV1D], ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
                                    (const uint16_t*)ls.vec[MOE_A_DT_BIAS], ls.ssm_state, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM],
-                                   vals, ss_part, a.d_pos, (int)z.total_key, (int)z.conv_dim, d.conv_kernel,
+                                   vals, ss_part, posp, (int)z.total_key, (int)z.conv_dim, d.conv_kernel,
                                    d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim, parts));
             e->launches++;
             if ((rc = launch_matvec_head_scaled(e, op.w, op.w + op.s_off, op.w + op.b_off, vals, ss_part, parts, d.lin_value_dim,
@@ -1319,7 +1334,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         MOE_CUDA(launch_kernel(pdl, lin_kernel, dim3(d.lin_num_v_heads), dim3(kLinThreads), lin_smem, st, ls.conv_state, qkv_raw,
                                (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
                                (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed,
-                               a.d_pos, (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads,
+                               posp, (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads,
                                d.lin_key_dim, d.lin_value_dim));
         e->launches++;
         if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h, pdl))) return rc;  // + residual
@@ -1346,6 +1361,9 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
     a.pdl = !(env_pdl && atoi(env_pdl) == 0);
     const char* env_chain = getenv("MOE_B200_ATTN_CHAIN");
     a.chain = a.pdl && !(env_chain && atoi(env_chain) == 0);
+    const char* env_pre = getenv("MOE_B200_PREFILL_MIN");
+    a.prefill_min = env_pre ? atoi(env_pre) : 8;
+    if (a.prefill_min < 2) a.prefill_min = 1 << 30;  // 0 or 1: token by token always
     const char* env_split = getenv("MOE_B200_LIN_SPLIT");
     a.lin_split = !(env_split && atoi(env_split) == 0);
     const int L = e->dims.num_layers;
@@ -1390,6 +1408,41 @@ static int attn_build_graphs(moe_engine* e, const float* const* layer_in, float*
     return MOE_OK;
 }
 
+// Several tokens at once (a prompt), layer by layer: the attention half of a layer runs token after token (its state
+// carries from one to the next) with the layer's projections staying in L2 from the first token on, and the layer's MoE
+// half then takes all the tokens in one batched call (launch_batched_layer: every expert's weights read once).  The same
+// arithmetic as token by token, except that the MoE half of a batch above 48 tokens computes on bf16 operands
+// (the grouped GEMMs) like any batched call.
+static int attn_model_prefill(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev, float* scratch) {
+    ModelAttnState& a = e->attn;
+    const size_t H = (size_t)e->dims.hidden;
+    const int L = e->dims.num_layers;
+    int rc = batch_reserve(e, n);   // its two [n, H] buffers hold the layers' outputs in turn
+    if (rc) return rc;
+    if (a.prefill_cap < n) {
+        MOE_CUDA(cudaStreamSynchronize(e->stream));
+        if (a.prefill_mid) cudaFree(a.prefill_mid);
+        a.prefill_mid = nullptr;
+        a.prefill_cap = 0;
+        MOE_CUDA(cudaMalloc(&a.prefill_mid, (size_t)n * H * 4));
+        a.prefill_cap = n;
+    }
+    const float* cur = emb_dev;
+    for (int l = 0; l < L; ++l) {
+        for (int t = 0; t < n; ++t) {
+            // a token's first kernel follows the previous token's output projection: a programmatic dependent of it
+            rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, t > 0, a.pos_table + a.pos + t);
+            if (rc) return rc;
+        }
+        float* nxt = (l == L - 1) ? out_dev : ((l & 1) ? e->bw.h_b : e->bw.h_a);
+        rc = launch_batched_layer(e, l, a.prefill_mid, n, nxt, nullptr, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+        cur = nxt;
+    }
+    a.pos += n;
+    return MOE_OK;
+}
+
 int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* out_dev) {
     ModelAttnState& a = e->attn;
     if (!a.configured) {
@@ -1418,6 +1471,7 @@ int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* ou
         int rc = attn_build_graphs(e, layer_in.data(), h_mid, scratch);
         if (rc) return rc;
     }
+    if (a.chain && n >= a.prefill_min) return attn_model_prefill(e, emb_dev, n, out_dev, scratch);
     for (int t = 0; t < n; ++t) {
         set_pos_kernel<<<1, 1, 0, e->stream>>>(a.d_pos, (int)a.pos);
         MOE_CUDA(cudaMemcpyAsync(pong, emb_dev + (size_t)t * H, H * 4, cudaMemcpyDeviceToDevice, e->stream));
