@@ -1473,9 +1473,13 @@ int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* ou
     }
     if (a.chain && n >= a.prefill_min) return attn_model_prefill(e, emb_dev, n, out_dev, scratch);
     for (int t = 0; t < n; ++t) {
-        set_pos_kernel<<<1, 1, 0, e->stream>>>(a.d_pos, (int)a.pos);
+        // graphs read the position from a fixed word (set per token); plain launches from the table entry of the position
+        const int* pos_ptr = a.chain ? a.pos_table + a.pos : nullptr;
+        if (!pos_ptr) {
+            set_pos_kernel<<<1, 1, 0, e->stream>>>(a.d_pos, (int)a.pos);
+            e->launches++;
+        }
         MOE_CUDA(cudaMemcpyAsync(pong, emb_dev + (size_t)t * H, H * 4, cudaMemcpyDeviceToDevice, e->stream));
-        e->launches++;
         for (int l = 0; l < L; ++l) {
             int rc = MOE_OK;
             if (a.graphs[l]) {
@@ -1483,7 +1487,7 @@ int attn_model_forward(moe_engine* e, const float* emb_dev, int32_t n, float* ou
                 e->launches += a.graph_nodes[l];
             } else {
                 // chained: a layer's first kernel depends programmatically on the MoE kernel of the layer before it
-                rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch, a.chain && l > 0);
+                rc = attn_layer_step(e, l, layer_in[l], h_mid, scratch, a.chain && l > 0, pos_ptr);
             }
             if (rc) return rc;
             float* nxt = (l == L - 1) ? out_dev + (size_t)t * H : layer_out[l];
