@@ -1430,8 +1430,10 @@ static int attn_model_prefill(moe_engine* e, const float* emb_dev, int32_t n, fl
     const float* cur = emb_dev;
     for (int l = 0; l < L; ++l) {
         for (int t = 0; t < n; ++t) {
-            // a token's first kernel follows the previous token's output projection: a programmatic dependent of it
-            rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, t > 0, a.pos_table + a.pos + t);
+            // A token's first kernel is launched the ordinary way: the DeltaNet kernel of this token reads the layer's conv
+            // ring and recurrence state ahead of its dependency wait, which is only safe once the previous token's kernels,
+            // which write them, have completed (token by token, a copy between two tokens separates them).
+            rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, false, a.pos_table + a.pos + t);
             if (rc) return rc;
         }
         float* nxt = (l == L - 1) ? out_dev : ((l & 1) ? e->bw.h_b : e->bw.h_a);
