@@ -17,8 +17,12 @@ constexpr int kBfWarps = 8;
 __global__ void __launch_bounds__(kBfWarps * 32) matvec_bf16_kernel(const uint16_t* __restrict__ w, const float* x,
                                                                    float* __restrict__ y, int rows, int cols,
                                                                    const float* residual,  // nullable: y = W x + residual
-                                                                   const uint16_t* __restrict__ norm_w) {  // nullable: x <- rmsnorm(x) * norm_w
+                                                                   const uint16_t* __restrict__ norm_w,  // nullable: x <- rmsnorm(x) * norm_w
+                                                                   int x_stride, int y_stride, int r_stride) {  // per vector (blockIdx.y)
     extern __shared__ float xs[];
+    x += (size_t)blockIdx.y * x_stride;
+    y += (size_t)blockIdx.y * y_stride;
+    if (residual) residual += (size_t)blockIdx.y * r_stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int stride = gridDim.x * kBfWarps * 2;
     pdl_trigger();
@@ -130,10 +134,15 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* q, int q_st
                                                         const uint16_t* __restrict__ k_norm, int num_heads, int num_kv_heads,
                                                         int head_dim, int rope_dim, int pos_value, const int* __restrict__ pos_ptr,
                                                         float theta, float* __restrict__ q_out,
-                                                        float* __restrict__ k_cache, float* __restrict__ v_cache) {
+                                                        float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                                        int tok_stride) {  // several tokens in one launch: blockIdx.y, consecutive positions
     pdl_trigger();
     pdl_wait();
-    const int pos = pos_ptr ? *pos_ptr : pos_value;  // a device-side position keeps the launch replayable (CUDA graph)
+    q += (size_t)blockIdx.y * tok_stride;
+    k += (size_t)blockIdx.y * tok_stride;
+    v += (size_t)blockIdx.y * tok_stride;
+    q_out += (size_t)blockIdx.y * tok_stride;
+    const int pos = (pos_ptr ? *pos_ptr : pos_value) + (int)blockIdx.y;  // a device-side position keeps the launch replayable (CUDA graph)
     extern __shared__ float hv[];  // the normed head
     __shared__ float red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -187,10 +196,14 @@ constexpr int kAttnInflight = 4;  // positions a warp has in flight in the value
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(const float* q, const float* k_cache,
                                                           const float* v_cache, const float* gate,
                                                           int gate_stride, int num_heads, int num_kv_heads, int head_dim, int seq_value,
-                                                          const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out) {
+                                                          const int* __restrict__ pos_ptr, float kq_scale, float* __restrict__ out,
+                                                          int tok_stride) {  // several tokens in one launch: blockIdx.y, each over its own prefix
     pdl_trigger();
     pdl_wait();
-    const int seq_len = pos_ptr ? *pos_ptr + 1 : seq_value;
+    q += (size_t)blockIdx.y * tok_stride;
+    gate += (size_t)blockIdx.y * tok_stride;
+    out += (size_t)blockIdx.y * tok_stride;
+    const int seq_len = (pos_ptr ? *pos_ptr + 1 : seq_value) + (int)blockIdx.y;
     extern __shared__ float sc[];  // [seq_len] scores, then [head_dim] the query head, then [warps][head_dim] partial outputs
     __shared__ float red[kAttnWarps];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -825,17 +838,19 @@ int mtp_load_tensor(moe_engine* e, int which, const void* w, const void* s, cons
 // norm_w: the input is rmsnorm(x) * norm_w, applied inside the kernel (see proj_folds_norm)
 static bool proj_folds_norm(const ProjTensor& t) { return t.dtype != MOE_DT_INT4 || matvec_folds_norm(t.rows, t.cols); }
 static int proj_run(moe_engine* e, const ProjTensor& t, const float* x, float* y, const float* residual = nullptr, bool pdl = false,
-                    const void* norm_w = nullptr) {
+                    const void* norm_w = nullptr, MvBatch mb = MvBatch{}) {
     if (t.dtype == MOE_DT_INT4)
-        return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual, pdl, norm_w);
+        return launch_matvec_res(e, t.w, t.w + t.s_off, t.w + t.b_off, x, y, t.rows, t.cols, residual, pdl, norm_w, mb);
     if (!e->mtp.bf_attr_set) {
         MOE_CUDA(cudaFuncSetAttribute(matvec_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * 4));
         e->mtp.bf_attr_set = true;
     }
     int blocks = (t.rows + kBfWarps * 2 - 1) / (kBfWarps * 2);
     if (blocks > e->sm_count * 2) blocks = e->sm_count * 2;  // one wave (two CTAs per SM): x is staged once per CTA
-    MOE_CUDA(launch_kernel(pdl, matvec_bf16_kernel, dim3(blocks), dim3(kBfWarps * 32), (size_t)t.cols * 4, e->stream,
-                           reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual, (const uint16_t*)norm_w));
+    blocks = matvec_batch_blocks(e, blocks, mb.n);
+    MOE_CUDA(launch_kernel(pdl, matvec_bf16_kernel, dim3(blocks, mb.n), dim3(kBfWarps * 32), (size_t)t.cols * 4, e->stream,
+                           reinterpret_cast<const uint16_t*>(t.w), x, y, t.rows, t.cols, residual, (const uint16_t*)norm_w,
+                           mb.x_stride, mb.y_stride, mb.r_stride));
     e->launches++;
     return MOE_OK;
 }
@@ -891,10 +906,10 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     if ((rc = proj_run(e, m.proj[MOE_M_K_PROJ], x, k))) return rc;
     if ((rc = proj_run(e, m.proj[MOE_M_V_PROJ], x, v))) return rc;
     attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
-                                                          m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache);
+                                                          m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache, 0);
     const int seq = pos + 1;
     attn_decode_kernel<<<nh, kAttnWarps * 32, (size_t)(seq + hd * (1 + kAttnWarps)) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
-                                                               1.0f / sqrtf((float)hd), gated);
+                                                               1.0f / sqrtf((float)hd), gated, 0);
     e->launches += 2;
     if ((rc = proj_run(e, m.proj[MOE_M_O_PROJ], gated, cur2, cur))) return rc;  // + residual
     // the MoE half: post-attention norm, router, experts, shared expert, residual (layer index num_layers)
@@ -1233,8 +1248,24 @@ static int attn_fuse_layer(moe_engine* e, AttnLayerState& ls) {
 // One layer's attention half on one token: h (device, [H]) -> h_mid (device, [H]) = attention(h) + h.
 // first_pdl: the layer's first kernel is itself a programmatic dependent of the kernel before it in the stream
 // pos_ptr: where the kernels read the token's position (null: the engine's device-side position word)
+// floats of one token's scratch as attn_layer_step carves it
+static size_t attn_scratch_floats(const moe_engine* e) {
+    const AttnSizes z = attn_sizes(e);
+    const size_t mid_n = z.q_dim > z.total_value ? z.q_dim : z.total_value;
+    return (al256a(z.H * 4) + al256a(attn_proj_out_floats(z, (size_t)e->attn.d.lin_num_v_heads) * 4) + 2 * al256a(mid_n * 4) +
+            al256a(z.q_dim * 4)) / 4;
+}
+// whether a layer's projections can run over several tokens in one launch (attn_layer_step with batch > 1): stacked
+// input projections with the input norm folded in
+static bool attn_layer_batchable(const AttnLayerState& ls) { return ls.fused.loaded && proj_folds_norm(ls.fused); }
+
+constexpr int kPhProj = 1, kPhCore = 2, kPhOut = 4;
+// phases: which of input projections / core (cache or state update, token-serial) / output projection + residual to run;
+// batch > 1 (projection phases only, batchable layers): that many tokens in one launch, token t's h and h_mid rows
+// hidden-size floats apart and its scratch tok_stride floats apart
 static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mid, float* scratch, bool first_pdl = false,
-                           const int* pos_ptr = nullptr) {
+                           const int* pos_ptr = nullptr, int phases = kPhProj | kPhCore | kPhOut, int batch = 1,
+                           size_t tok_stride = 0) {
     ModelAttnState& a = e->attn;
     AttnLayerState& ls = a.layers[layer];
     const moe_model_attn_dims_t& d = a.d;
@@ -1261,7 +1292,15 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     const void* fold_w = fold ? ls.vec[MOE_A_INPUT_NORM] : nullptr;
     const float* proj_in = fold ? h : x;
     bool pdl = first_pdl && a.pdl;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
-    if (!fold) {
+    MOE_REQUIRE(batch == 1 || (fold && (ls.full || !(phases & kPhCore))),
+                "layer %d: a batched step needs stacked projections, and a DeltaNet core runs one token at a time", layer);
+    const int core_n = batch;  // tokens of a full-attention core launch (the cache rows of all of them are written first)
+    MvBatch mb_in{}, mb_out{};
+    if (batch > 1) {
+        mb_in.n = batch; mb_in.x_stride = H; mb_in.y_stride = (int)tok_stride;
+        mb_out.n = batch; mb_out.x_stride = (int)tok_stride; mb_out.y_stride = H; mb_out.r_stride = H; mb_out.ss_stride = (int)tok_stride;
+    }
+    if (!fold && (phases & kPhProj)) {
         MOE_CUDA(launch_kernel(pdl, rms_norm_rows_kernel, dim3(1), dim3(256), 0, st, h, (const uint16_t*)ls.vec[MOE_A_INPUT_NORM], H, x));
         e->launches++;
         pdl = a.pdl;
@@ -1274,22 +1313,27 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* qb = proj_out;                  // [head, gate] per head
         float* kb = qb + 2 * z.q_dim;
         float* vb = kb + z.kv_dim;
-        if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w))) return rc;
+        if (!(phases & kPhProj)) {
+        } else if (ls.fused.loaded) {
+            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w, mb_in))) return rc;
             pdl = a.pdl;
         } else {
             if ((rc = proj_run(e, ls.proj[MOE_A_Q_PROJ], x, qb, nullptr, pdl))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_K_PROJ], x, kb, nullptr, pdl))) return rc;
             if ((rc = proj_run(e, ls.proj[MOE_A_V_PROJ], x, vb, nullptr, pdl))) return rc;
         }
-        MOE_CUDA(launch_kernel(pdl, attn_prep_kernel, dim3(nh + nkv), dim3(256), (size_t)hd * 4, st, qb, 2 * hd, 1, kb, vb,
+        if (phases & kPhCore) {
+        MOE_CUDA(launch_kernel(pdl, attn_prep_kernel, dim3(nh + nkv, core_n), dim3(256), (size_t)hd * 4, st, qb, 2 * hd, 1, kb, vb,
                                (const uint16_t*)ls.vec[MOE_A_Q_NORM], (const uint16_t*)ls.vec[MOE_A_K_NORM], nh, nkv, hd,
-                               d.full.rotary_dim, 0, posp, d.full.rope_theta, qr, ls.k_cache, ls.v_cache));
+                               d.full.rotary_dim, 0, posp, d.full.rope_theta, qr, ls.k_cache, ls.v_cache, (int)tok_stride));
+        pdl = a.pdl;
         // the position is read on the device and the score buffer is sized for the whole cache: the launch never changes
-        MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(kAttnWarps * 32), (size_t)(d.full.max_seq + hd * (1 + kAttnWarps)) * 4, st, qr, ls.k_cache,
-                               ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, posp, 1.0f / sqrtf((float)hd), vals));
+        MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh, core_n), dim3(kAttnWarps * 32), (size_t)(d.full.max_seq + hd * (1 + kAttnWarps)) * 4, st, qr, ls.k_cache,
+                               ls.v_cache, qb + hd, 2 * hd, nh, nkv, hd, 0, posp, 1.0f / sqrtf((float)hd), vals, (int)tok_stride));
         e->launches += 2;
-        if ((rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h, pdl))) return rc;  // + residual
+        pdl = a.pdl;
+        }
+        if ((phases & kPhOut) && (rc = proj_run(e, ls.proj[MOE_A_O_PROJ], vals, h_mid, h, pdl, nullptr, mb_out))) return rc;  // + residual
     } else {
         for (int w : {MOE_A_IN_PROJ_QKV, MOE_A_IN_PROJ_Z, MOE_A_IN_PROJ_B, MOE_A_IN_PROJ_A, MOE_A_OUT_PROJ})
             if (!need(w)) return MOE_ERR_STATE;
@@ -1297,8 +1341,9 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         float* zb = qkv_raw + z.conv_dim;
         float* bb = zb + z.total_value;
         float* ab = bb + Hv;
-        if (ls.fused.loaded) {
-            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w))) return rc;
+        if (!(phases & kPhProj)) {
+        } else if (ls.fused.loaded) {
+            if ((rc = proj_run(e, ls.fused, proj_in, proj_out, nullptr, pdl, fold_w, mb_in))) return rc;
             pdl = a.pdl;
         } else {
             if ((rc = proj_run(e, ls.proj[MOE_A_IN_PROJ_QKV], x, qkv_raw, nullptr, pdl))) return rc;
@@ -1316,6 +1361,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         if (split) {
             auto* part_kernel = d.lin_key_dim <= 128 ? lin_part_kernel<4> : lin_part_kernel<8>;
             float* ss_part = normed;  // one sum of squares per CTA
+            if (phases & kPhCore) {
             MOE_CUDA(launch_kernel(pdl, part_kernel, dim3(d.lin_num_v_heads * parts), dim3(kLpThreads),
                                    (size_t)(2 * d.lin_key_dim + kLpRows) * 4, st, ls.conv_state, qkv_raw,
                                    (const uint16_t*)ls.vec[MOE_A_CONV1D], ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
@@ -1323,21 +1369,26 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
                                    vals, ss_part, posp, (int)z.total_key, (int)z.conv_dim, d.conv_kernel,
                                    d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim, parts));
             e->launches++;
-            if ((rc = launch_matvec_head_scaled(e, op.w, op.w + op.s_off, op.w + op.b_off, vals, ss_part, parts, d.lin_value_dim,
-                                                h_mid, op.rows, op.cols, h, pdl)))
+            pdl = a.pdl;
+            }
+            if ((phases & kPhOut) && (rc = launch_matvec_head_scaled(e, op.w, op.w + op.s_off, op.w + op.b_off, vals, ss_part, parts,
+                                                                     d.lin_value_dim, h_mid, op.rows, op.cols, h, pdl, mb_out)))
                 return rc;
             MOE_CUDA(cudaGetLastError());
             return MOE_OK;
         }
         const size_t lin_smem = (size_t)(2 * d.lin_key_dim + 2 * d.lin_value_dim) * 4;
         auto* lin_kernel = d.lin_key_dim <= 128 ? lin_core_kernel<4> : lin_core_kernel<8>;
+        if (phases & kPhCore) {
         MOE_CUDA(launch_kernel(pdl, lin_kernel, dim3(d.lin_num_v_heads), dim3(kLinThreads), lin_smem, st, ls.conv_state, qkv_raw,
                                (const uint16_t*)ls.vec[MOE_A_CONV1D], zb, ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
                                (const uint16_t*)ls.vec[MOE_A_DT_BIAS], (const uint16_t*)ls.vec[MOE_A_LIN_NORM], ls.ssm_state, normed,
                                posp, (int)z.total_key, (int)z.conv_dim, d.conv_kernel, d.lin_num_v_heads / d.lin_num_k_heads,
                                d.lin_key_dim, d.lin_value_dim));
         e->launches++;
-        if ((rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h, pdl))) return rc;  // + residual
+        pdl = a.pdl;
+        }
+        if ((phases & kPhOut) && (rc = proj_run(e, ls.proj[MOE_A_OUT_PROJ], normed, h_mid, h, pdl, nullptr, mb_out))) return rc;  // + residual
     }
     MOE_CUDA(cudaGetLastError());
     return MOE_OK;
@@ -1424,17 +1475,34 @@ static int attn_model_prefill(moe_engine* e, const float* emb_dev, int32_t n, fl
         if (a.prefill_mid) cudaFree(a.prefill_mid);
         a.prefill_mid = nullptr;
         a.prefill_cap = 0;
-        MOE_CUDA(cudaMalloc(&a.prefill_mid, (size_t)n * H * 4));
+        MOE_CUDA(cudaMalloc(&a.prefill_mid, (size_t)n * (H + attn_scratch_floats(e)) * 4));
+        a.prefill_scratch = a.prefill_mid + (size_t)n * H;   // every token's own scratch (projection outputs, core outputs)
         a.prefill_cap = n;
     }
     const float* cur = emb_dev;
+    const size_t S = attn_scratch_floats(e);
     for (int l = 0; l < L; ++l) {
-        for (int t = 0; t < n; ++t) {
-            // A token's first kernel is launched the ordinary way: the DeltaNet kernel of this token reads the layer's conv
-            // ring and recurrence state ahead of its dependency wait, which is only safe once the previous token's kernels,
-            // which write them, have completed (token by token, a copy between two tokens separates them).
-            rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, false, a.pos_table + a.pos + t);
-            if (rc) return rc;
+        const AttnLayerState& ls = a.layers[l];
+        if (attn_layer_batchable(ls)) {
+            // the projections of all the tokens in one launch each (they depend on the layer's input only), the token-serial
+            // core in between.  The DeltaNet kernel reads the layer's conv ring and recurrence state ahead of its dependency
+            // wait, which is only safe once the previous token's kernel, which writes them, has completed: ordinary launches.
+            // (The two attention kernels of a full-attention layer could chain from token to token, but a chain of hundreds of
+            // tiny grids that all become resident and wait for one another ran at 26 us per kernel instead of 8.)
+            if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, nullptr, kPhProj, n, S))) return rc;
+            if (ls.full) {  // every token's K / V rows first, then every token's attention over its own prefix: two launches
+                if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, a.pos_table + a.pos, kPhCore, n, S))) return rc;
+            } else {
+                for (int t = 0; t < n; ++t)
+                    if ((rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, a.prefill_scratch + (size_t)t * S,
+                                              false, a.pos_table + a.pos + t, kPhCore)))
+                        return rc;
+            }
+            if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, nullptr, kPhOut, n, S))) return rc;
+        } else {
+            for (int t = 0; t < n; ++t)  // a token's first kernel the ordinary way, for the same reason
+                if ((rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, false, a.pos_table + a.pos + t)))
+                    return rc;
         }
         float* nxt = (l == L - 1) ? out_dev : ((l & 1) ? e->bw.h_b : e->bw.h_a);
         rc = launch_batched_layer(e, l, a.prefill_mid, n, nxt, nullptr, nullptr, nullptr, nullptr);

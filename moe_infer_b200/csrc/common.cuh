@@ -186,6 +186,7 @@ struct ModelAttnState {
     int prefill_min = 8;                     // calls of at least this many tokens run layer by layer (MoE halves batched)
     int* pos_table = nullptr;                // positions 0 .. max_seq - 1 on the device
     float* prefill_mid = nullptr;            // [prefill_cap, H] attention outputs of a layer, all tokens
+    float* prefill_scratch = nullptr;        // [prefill_cap] scratch areas, one per token (same allocation)
     int prefill_cap = 0;
     bool lin_split = true;                   // DeltaNet core as 256-thread CTAs per block of state rows (gated norm in the out projection)
 };
@@ -252,19 +253,26 @@ int launch_pack(moe_engine* e, const void* src, int src_dtype, int64_t rows, int
 int launch_pack_int8(moe_engine* e, const void* src, int src_dtype, int64_t rows, int32_t cols, void* q, void* scales);
 int launch_pack_experts(moe_engine* e, const void* gate_up, const void* down, int src_dtype,
                         int32_t n_experts, void* blob);
+// A matvec over several input vectors in one launch (grid.y = vector): element strides from one vector's buffers to the
+// next one's; the default is one vector.  The weights are read again for every vector (from L2 when they fit).
+struct MvBatch {
+    int n = 1;
+    int x_stride = 0, y_stride = 0, r_stride = 0, ss_stride = 0;  // input, output, residual, per-head sums
+};
 // sets the per-device function attributes of the matvec kernels (so that later launches can be captured into a graph)
 int matvec_prepare(moe_engine* e);
 // y = W x + residual (residual nullable; may not alias y)
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x, float* y, int32_t rows,
-                      int32_t cols, const float* residual, bool pdl = false, const void* norm_w = nullptr);
+                      int32_t cols, const float* residual, bool pdl = false, const void* norm_w = nullptr, MvBatch mb = MvBatch{});
 // whether launch_matvec_res can apply rmsnorm(x) * norm_w (bf16 weights) to its input itself for this shape
 bool matvec_folds_norm(int32_t rows, int32_t cols);
+int matvec_batch_blocks(const moe_engine* e, int blocks, int n);
 // y = W (x scaled per head) + residual: the last step of a per-head RMS norm (sums of squares left in `ss` by the producer,
 // `parts` entries per head) folded into the kernel's staging
 bool matvec_folds_head_scale(int32_t rows, int32_t cols, int32_t head_dim);
 int launch_matvec_head_scaled(moe_engine* e, const void* w, const void* s, const void* b, const float* x, const float* ss,
                               int32_t parts, int32_t head_dim, float* y, int32_t rows, int32_t cols, const float* residual,
-                              bool pdl);
+                              bool pdl, MvBatch mb = MvBatch{});
 int launch_matvec(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
                   float* y, int32_t rows, int32_t cols);
 int decode_init(moe_engine* e);

@@ -22,7 +22,12 @@ matvec_int4_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ 
                    // nullable: every head of hs_dim inputs is scaled by rsqrt(sum / hs_dim + 1e-6), its sum of squares being
                    // the total of the head's hs_parts entries of hs_ss (the RMS norm of a gated norm whose other factors the
                    // producer has applied already; hs_dim % 32 == 0)
-                   const float* hs_ss, int hs_parts, int hs_dim) {
+                   const float* hs_ss, int hs_parts, int hs_dim,
+                   int x_stride, int y_stride, int r_stride, int ss_stride) {  // per vector of a batched launch (blockIdx.y)
+    x += (size_t)blockIdx.y * x_stride;
+    y += (size_t)blockIdx.y * y_stride;
+    if (residual) residual += (size_t)blockIdx.y * r_stride;
+    if (hs_ss) hs_ss += (size_t)blockIdx.y * ss_stride;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nch = cols / 32;  // chunks per row
     float* raw = reinterpret_cast<float*>(smem_raw);                 // [cols]
@@ -179,7 +184,11 @@ __global__ void __launch_bounds__(kSvWarps * 32, 2)
 matvec_int4_stream_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ s, const uint16_t* __restrict__ b,
                           const float* x, float* __restrict__ y, int rows, unsigned int* err_flag,
                           const float* residual,
-                          const uint16_t* __restrict__ norm_w) {  // nullable: the input is rmsnorm(x) * norm_w (bf16), eps 1e-6
+                          const uint16_t* __restrict__ norm_w,  // nullable: the input is rmsnorm(x) * norm_w (bf16), eps 1e-6
+                          int x_stride, int y_stride, int r_stride) {  // per vector of a batched launch (blockIdx.y)
+    x += (size_t)blockIdx.y * x_stride;
+    y += (size_t)blockIdx.y * y_stride;
+    if (residual) residual += (size_t)blockIdx.y * r_stride;
     constexpr int nch = kSvCols / 32;
     __shared__ __align__(128) float raw[kSvCols];
     __shared__ __align__(16) uint4 xq[6 * nch];
@@ -322,7 +331,7 @@ bool matvec_folds_head_scale(int32_t rows, int32_t cols, int32_t head_dim) {
 }
 int launch_matvec_head_scaled(moe_engine* e, const void* w, const void* s, const void* b, const float* x, const float* ss,
                               int32_t parts, int32_t head_dim, float* y, int32_t rows, int32_t cols, const float* residual,
-                              bool pdl) {
+                              bool pdl, MvBatch mb) {
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0 && parts > 0 && matvec_folds_head_scale(rows, cols, head_dim),
                 "matvec: cannot fold a norm of %d-element heads into a %d x %d product", head_dim, rows, cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
@@ -332,16 +341,29 @@ int launch_matvec_head_scaled(moe_engine* e, const void* w, const void* s, const
     int blocks = (rows + kMvWarps - 1) / kMvWarps;
     const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
     if (blocks > cap) blocks = cap;
-    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
-                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual, ss, parts, head_dim));
+    MOE_REQUIRE(mb.n >= 1 && mb.n <= 65535, "matvec: %d vectors in one launch", mb.n);
+    blocks = matvec_batch_blocks(e, blocks, mb.n);
+    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks, mb.n), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
+                           (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual, ss, parts, head_dim,
+                           mb.x_stride, mb.y_stride, mb.r_stride, mb.ss_stride));
     e->launches++;
     return MOE_OK;
 }
 
 bool matvec_folds_norm(int32_t rows, int32_t cols) { return cols == kSvCols && rows >= 4096; }
 
+// CTAs per vector of a batched launch: every CTA stages its vector once, so with many vectors fewer CTAs, each with more
+// rows, spread that cost; about four CTAs per SM over the whole launch keep the device busy
+int matvec_batch_blocks(const moe_engine* e, int blocks, int n) {
+    if (n <= 1) return blocks;
+    int per = (4 * e->sm_count + n - 1) / n;
+    if (per < 8) per = 8;
+    return blocks < per ? blocks : per;
+}
+
 int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b, const float* x,
-                      float* y, int32_t rows, int32_t cols, const float* residual, bool pdl, const void* norm_w) {
+                      float* y, int32_t rows, int32_t cols, const float* residual, bool pdl, const void* norm_w, MvBatch mb) {
+    MOE_REQUIRE(mb.n >= 1 && mb.n <= 65535, "matvec: %d vectors in one launch", mb.n);
     MOE_REQUIRE(rows > 0 && cols > 0 && cols % kGroup == 0, "matvec: cols (%d) must be a positive multiple of 64", cols);
     MOE_REQUIRE(cols <= 16384, "matvec: cols (%d) above 16384 not supported", cols);
     MOE_REQUIRE((((uintptr_t)x) & 15) == 0 && (((uintptr_t)w) & 15) == 0, "matvec: x and w must be 16-byte aligned");
@@ -352,9 +374,10 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
         int blocks = (rows + kSvWarps * kSvUnroll - 1) / (kSvWarps * kSvUnroll);
         const int cap = e->sm_count * 2;
         if (blocks > cap) blocks = cap;
-        MOE_CUDA(launch_kernel(pdl, matvec_int4_stream_kernel, dim3(blocks), dim3(kSvWarps * 32), 0, e->stream, (const uint32_t*)w,
+        blocks = matvec_batch_blocks(e, blocks, mb.n);
+        MOE_CUDA(launch_kernel(pdl, matvec_int4_stream_kernel, dim3(blocks, mb.n), dim3(kSvWarps * 32), 0, e->stream, (const uint32_t*)w,
                                (const uint16_t*)s, (const uint16_t*)b, x, y, rows, e->dec_sync + 2, residual,
-                               (const uint16_t*)norm_w));
+                               (const uint16_t*)norm_w, mb.x_stride, mb.y_stride, mb.r_stride));
         e->launches++;
         return MOE_OK;
     }
@@ -365,9 +388,10 @@ int launch_matvec_res(moe_engine* e, const void* w, const void* s, const void* b
     // every CTA stages the whole x: with long rows fewer CTAs, each taking several rows per warp, amortise that better
     const int cap = e->sm_count * (cols >= 4096 ? 1 : 8);
     if (blocks > cap) blocks = cap;
-    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
+    blocks = matvec_batch_blocks(e, blocks, mb.n);
+    MOE_CUDA(launch_kernel(pdl, matvec_int4_kernel, dim3(blocks, mb.n), dim3(kMvWarps * 32), smem, e->stream, (const uint32_t*)w,
                            (const uint16_t*)s, (const uint16_t*)b, x, y, rows, cols, e->dec_sync + 2, residual,
-                           (const float*)nullptr, 0, 0));
+                           (const float*)nullptr, 0, 0, mb.x_stride, mb.y_stride, mb.r_stride, 0));
     e->launches++;
     return MOE_OK;
 }

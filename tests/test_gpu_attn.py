@@ -139,6 +139,14 @@ def test_decode_with_attention_at_the_model_own_head_counts():
     assert max(errs) < 1e-2 and rel_l2(got - emb, want - emb) < 1e-2
     ssm = eng.model_state_download(0, L.ST_SSM, state.lin[0][1].size)
     assert rel_l2(ssm, state.lin[0][1].ravel()) < 1e-2
+    # the same shapes as a prompt: nine tokens in one call run layer by layer, every projection over the nine tokens in one launch
+    eng.model_reset()
+    emb9 = synth.hidden_states(58, 2, 9, H)
+    state = oracle.ModelState(ad, layers, 16)
+    want9 = np.stack([oracle.model_decode_token(attn, moe, ad, state, emb9[t], K) for t in range(9)])
+    got9 = eng.model_forward_hidden(emb9)
+    print(f"the same as a 9-token prompt: rel-L2 {rel_l2(got9, want9):.1e}, on the updates {rel_l2(got9 - emb9, want9 - emb9):.1e}")
+    assert rel_l2(got9, want9) < 1e-2 and rel_l2(got9 - emb9, want9 - emb9) < 1e-2 and eng.model_pos() == 9
     eng.close()
 
 
