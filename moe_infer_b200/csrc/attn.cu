@@ -721,6 +721,211 @@ __global__ void __launch_bounds__(kLpThreads) lin_part_kernel(float* __restrict_
     }
 }
 
+// ─── the same for a run of tokens: one launch, the state in registers from the first token to the last ──────
+// A prompt's tokens go through a DeltaNet layer one after the other (each step needs the state the previous one left),
+// but not as one launch per token: here a CTA keeps its rows of the state, and every thread the last conv inputs of its
+// channels, in registers across the tokens; per token it reads the projection outputs (the next token's while this one
+// computes), writes the gated outputs and its sum of squares, and updates the conv ring; the state goes back to memory
+// once at the end.  Token t's buffers lie t * tok_stride floats after token 0's.  For conv kernels up to kLpK taps and at
+// most kLpCh channels per thread (the host checks).
+template <int kLinPer>
+__global__ void __launch_bounds__(kLpThreads) lin_seq_kernel(float* __restrict__ conv_ring, const float* qkv_in,
+                                                     const uint16_t* __restrict__ conv_w, const float* alpha,
+                                                     const float* beta, const float* __restrict__ a_log,
+                                                     const uint16_t* __restrict__ dt_bias, float* __restrict__ state,
+                                                     const float* z, const uint16_t* __restrict__ norm_w,
+                                                     float* __restrict__ out_gated, float* __restrict__ ss_part,
+                                                     const int* __restrict__ pos_ptr, int total_key,
+                                                     int conv_dim, int ksize, int k_heads_per_v, int key_dim, int value_dim,
+                                                     int parts, int n_tok, int tok_stride) {
+    extern __shared__ float lsm[];
+    __shared__ float red[kLpWarps], red2[kLpWarps];
+    float* qs = lsm;
+    float* ks = qs + key_dim;
+    float* vs = ks + key_dim;  // [kLpRows]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.x / parts, part = blockIdx.x % parts, kh = h / k_heads_per_v;
+    const int v_begin = part * kLpRows;
+    const int nv = value_dim - v_begin < kLpRows ? value_dim - v_begin : kLpRows;
+    pdl_trigger();
+    pdl_wait();
+    float sreg[kLinRows][kLinPer];
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        const int v = warp * kLinRows + r;
+        const float* srow = state + ((size_t)h * value_dim + v_begin + v) * key_dim;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            sreg[r][j] = (v < nv && i < key_dim) ? srow[i] : 0.0f;
+        }
+    }
+    const int pos0 = *pos_ptr;
+    const int n_ch = 2 * key_dim + nv;
+    auto channel_of = [&](int i) {
+        return i < key_dim ? kh * key_dim + i
+               : i < 2 * key_dim ? total_key + kh * key_dim + (i - key_dim)
+                                 : 2 * total_key + h * value_dim + v_begin + (i - 2 * key_dim);
+    };
+    int c_mine[kLpCh];
+    float cw[kLpCh][kLpK], rv[kLpCh][kLpK];  // taps; the last ksize - 1 inputs of the channel, oldest first
+    bool have[kLpCh];
+#pragma unroll
+    for (int u = 0; u < kLpCh; ++u) {
+        const int i = tid + u * kLpThreads;
+        have[u] = i < n_ch;
+        c_mine[u] = have[u] ? channel_of(i) : 0;
+#pragma unroll
+        for (int k = 0; k < kLpK; ++k) {
+            cw[u][k] = rv[u][k] = 0.0f;
+            if (have[u] && k < ksize) cw[u][k] = bf16_bits_to_f32(conv_w[(size_t)c_mine[u] * ksize + k]);
+            if (have[u] && k < ksize - 1) {
+                const int step = pos0 - (ksize - 1) + k;
+                const int row = ((step % ksize) + ksize) % ksize;
+                rv[u][k] = conv_ring[(size_t)row * conv_dim + c_mine[u]];
+            }
+        }
+    }
+    const float a_decay = expf(a_log ? a_log[h] : 0.0f);
+    const float dt_bias_h = dt_bias ? bf16_bits_to_f32(dt_bias[h]) : 0.0f;
+    const int v_fin = warp * kLinRows + (lane & (kLinRows - 1));
+    const bool fin = lane < kLinRows && v_fin < nv;
+    const float nw_fin = fin ? bf16_bits_to_f32(norm_w[v_begin + v_fin]) : 0.0f;
+    const float inv_scale = 1.0f / sqrtf((float)key_dim);
+    // the first token's inputs
+    float xin[kLpCh], xin_next[kLpCh] = {};
+    float alpha_t = alpha[h], beta_t = beta[h], z_t = fin ? z[(size_t)h * value_dim + v_begin + v_fin] : 0.0f;
+    float alpha_n = 0.0f, beta_n = 0.0f, z_n = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kLpCh; ++u) xin[u] = have[u] ? qkv_in[c_mine[u]] : 0.0f;
+    for (int t = 0; t < n_tok; ++t) {
+        const size_t off = (size_t)t * tok_stride;
+        if (t + 1 < n_tok) {  // the next token's inputs are on their way while this one computes
+            const size_t offn = off + tok_stride;
+#pragma unroll
+            for (int u = 0; u < kLpCh; ++u) xin_next[u] = have[u] ? qkv_in[offn + c_mine[u]] : 0.0f;
+            alpha_n = alpha[offn + h];
+            beta_n = beta[offn + h];
+            z_n = fin ? z[offn + (size_t)h * value_dim + v_begin + v_fin] : 0.0f;
+        }
+        const int pos = pos0 + t;
+        // 1. conv + SiLU, ring update, the channel's window moves on
+#pragma unroll
+        for (int u = 0; u < kLpCh; ++u) {
+            if (!have[u]) continue;
+            const int i = tid + u * kLpThreads;
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kLpK; ++k)
+                if (k < ksize - 1) acc += rv[u][k] * cw[u][k];
+            float w_last = cw[u][0];
+#pragma unroll
+            for (int k = 1; k < kLpK; ++k)
+                if (k == ksize - 1) w_last = cw[u][k];
+            acc += xin[u] * w_last;
+            const float val = acc / (1.0f + expf(-acc));
+            conv_ring[(size_t)(pos % ksize) * conv_dim + c_mine[u]] = xin[u];
+#pragma unroll
+            for (int k = 0; k < kLpK - 1; ++k)
+                if (k < ksize - 2) rv[u][k] = rv[u][k + 1];
+#pragma unroll
+            for (int k = 0; k < kLpK; ++k)
+                if (k == ksize - 2) rv[u][k] = xin[u];
+            if (i < key_dim) qs[i] = val;
+            else if (i < 2 * key_dim) ks[i - key_dim] = val;
+            else vs[i - 2 * key_dim] = val;
+        }
+        __syncthreads();
+        // 2. q / k norms
+        float sq = 0.0f, sk = 0.0f;
+        for (int i = tid; i < key_dim; i += kLpThreads) {
+            sq = fmaf(qs[i], qs[i], sq);
+            sk = fmaf(ks[i], ks[i], sk);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) { red[warp] = sq; red2[warp] = sk; }
+        __syncthreads();
+        float tq = 0.0f, tk = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kLpWarps; ++i) { tq += red[i]; tk += red2[i]; }
+        const float q_mul = (1.0f / sqrtf(tq / (float)key_dim + 1e-6f)) * inv_scale * inv_scale;
+        const float k_mul = (1.0f / sqrtf(tk / (float)key_dim + 1e-6f)) * inv_scale;
+        // 3. decay and input gate
+        const float softplus = logf(1.0f + expf(alpha_t + dt_bias_h));
+        const float g = expf(-a_decay * softplus);
+        const float bgate = 1.0f / (1.0f + expf(-beta_t));
+        // 4. the delta rule on this warp's rows
+        float kv[kLinRows];
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kLinPer; ++j) {
+                const int i = lane + 32 * j;
+                sreg[r][j] *= g;
+                if (i < key_dim) acc = fmaf(sreg[r][j], ks[i] * k_mul, acc);
+            }
+            kv[r] = acc;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kLinRows; ++r) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+        float ov[kLinRows];
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            const int v = warp * kLinRows + r;
+            const float delta = ((v < nv ? vs[v] : 0.0f) - kv[r]) * bgate;
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kLinPer; ++j) {
+                const int i = lane + 32 * j;
+                if (v < nv && i < key_dim) {
+                    sreg[r][j] = sreg[r][j] + (ks[i] * k_mul) * delta;
+                    acc = fmaf(sreg[r][j], qs[i] * q_mul, acc);
+                }
+            }
+            ov[r] = acc;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kLinRows; ++r) ov[r] += __shfl_xor_sync(0xffffffffu, ov[r], o);
+        // 5. gate and norm weight, this CTA's sum of squares
+        float mine = 0.0f, ss = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kLinRows; ++r) {
+            if (lane == r) mine = ov[r];
+            if (warp * kLinRows + r < nv) ss = fmaf(ov[r], ov[r], ss);
+        }
+        if (fin) out_gated[off + (size_t)h * value_dim + v_begin + v_fin] = mine * (z_t / (1.0f + expf(-z_t))) * nw_fin;
+        __syncthreads();  // red was read by every warp above; qs / ks / vs by the recurrence
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (tid == 0) {
+            float tot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kLpWarps; ++i) tot += red[i];
+            ss_part[off + blockIdx.x] = tot;
+        }
+        __syncthreads();  // before the next token overwrites red and the shared q / k / v
+#pragma unroll
+        for (int u = 0; u < kLpCh; ++u) xin[u] = xin_next[u];
+        alpha_t = alpha_n; beta_t = beta_n; z_t = z_n;
+    }
+#pragma unroll
+    for (int r = 0; r < kLinRows; ++r) {
+        const int v = warp * kLinRows + r;
+        float* srow = state + ((size_t)h * value_dim + v_begin + v) * key_dim;
+#pragma unroll
+        for (int j = 0; j < kLinPer; ++j) {
+            const int i = lane + 32 * j;
+            if (v < nv && i < key_dim) srow[i] = sreg[r][j];
+        }
+    }
+}
+
 // ─── host side ──────────────────────────────────────────────────────────────
 
 static size_t al256a(size_t v) { return (v + 255) / 256 * 256; }
@@ -1259,6 +1464,23 @@ static size_t attn_scratch_floats(const moe_engine* e) {
 // input projections with the input norm folded in
 static bool attn_layer_batchable(const AttnLayerState& ls) { return ls.fused.loaded && proj_folds_norm(ls.fused); }
 
+// whether a DeltaNet layer runs as 256-thread CTAs per block of state rows with the gated norm's 1/rms left to the output
+// projection (lin_part_kernel), and whether a run of tokens can then go through it in one launch (lin_seq_kernel)
+static bool attn_lin_split(const moe_engine* e, const AttnLayerState& ls) {
+    const ModelAttnState& a = e->attn;
+    const moe_model_attn_dims_t& d = a.d;
+    const AttnSizes z = attn_sizes(e);
+    const size_t mid_n = z.q_dim > z.total_value ? z.q_dim : z.total_value;
+    const ProjTensor& op = ls.proj[MOE_A_OUT_PROJ];
+    const int parts = (d.lin_value_dim + kLpRows - 1) / kLpRows;
+    return a.lin_split && !ls.full && op.loaded && op.dtype == MOE_DT_INT4 && ls.vec[MOE_A_LIN_NORM] != nullptr &&
+           matvec_folds_head_scale(op.rows, op.cols, d.lin_value_dim) && 2 * d.lin_key_dim + kLpRows <= kLpCh * kLpThreads &&
+           (size_t)d.lin_num_v_heads * parts <= mid_n;
+}
+static bool attn_lin_seq_ok(const moe_engine* e, const AttnLayerState& ls) {
+    return attn_lin_split(e, ls) && ls.vec[MOE_A_CONV1D] != nullptr && e->attn.d.conv_kernel <= kLpK && e->attn.d.conv_kernel >= 2;
+}
+
 constexpr int kPhProj = 1, kPhCore = 2, kPhOut = 4;
 // phases: which of input projections / core (cache or state update, token-serial) / output projection + residual to run;
 // batch > 1 (projection phases only, batchable layers): that many tokens in one launch, token t's h and h_mid rows
@@ -1292,8 +1514,7 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
     const void* fold_w = fold ? ls.vec[MOE_A_INPUT_NORM] : nullptr;
     const float* proj_in = fold ? h : x;
     bool pdl = first_pdl && a.pdl;  // every kernel after the first may start ahead of its predecessor's end (see pdl_wait)
-    MOE_REQUIRE(batch == 1 || (fold && (ls.full || !(phases & kPhCore))),
-                "layer %d: a batched step needs stacked projections, and a DeltaNet core runs one token at a time", layer);
+    MOE_REQUIRE(batch == 1 || fold, "layer %d: a batched step needs stacked projections", layer);
     const int core_n = batch;  // tokens of a full-attention core launch (the cache rows of all of them are written first)
     MvBatch mb_in{}, mb_out{};
     if (batch > 1) {
@@ -1355,13 +1576,23 @@ static int attn_layer_step(moe_engine* e, int layer, const float* h, float* h_mi
         // where that kernel can do it; one large CTA per head doing everything otherwise
         const ProjTensor& op = ls.proj[MOE_A_OUT_PROJ];
         const int parts = (d.lin_value_dim + kLpRows - 1) / kLpRows;
-        const bool split = a.lin_split && op.dtype == MOE_DT_INT4 && ls.vec[MOE_A_LIN_NORM] != nullptr &&
-                           matvec_folds_head_scale(op.rows, op.cols, d.lin_value_dim) &&
-                           2 * d.lin_key_dim + kLpRows <= kLpCh * kLpThreads && (size_t)d.lin_num_v_heads * parts <= mid_n;
+        const bool split = attn_lin_split(e, ls);
+        MOE_REQUIRE(batch == 1 || !(phases & kPhCore) || attn_lin_seq_ok(e, ls), "layer %d: its DeltaNet core runs one token at a time", layer);
         if (split) {
             auto* part_kernel = d.lin_key_dim <= 128 ? lin_part_kernel<4> : lin_part_kernel<8>;
             float* ss_part = normed;  // one sum of squares per CTA
-            if (phases & kPhCore) {
+            if ((phases & kPhCore) && batch > 1) {
+                auto* seq_kernel = d.lin_key_dim <= 128 ? lin_seq_kernel<4> : lin_seq_kernel<8>;
+                MOE_CUDA(launch_kernel(pdl, seq_kernel, dim3(d.lin_num_v_heads * parts), dim3(kLpThreads),
+                                       (size_t)(2 * d.lin_key_dim + kLpRows) * 4, st, ls.conv_state, qkv_raw,
+                                       (const uint16_t*)ls.vec[MOE_A_CONV1D], ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
+                                       (const uint16_t*)ls.vec[MOE_A_DT_BIAS], ls.ssm_state, zb, (const uint16_t*)ls.vec[MOE_A_LIN_NORM],
+                                       vals, ss_part, posp, (int)z.total_key, (int)z.conv_dim, d.conv_kernel,
+                                       d.lin_num_v_heads / d.lin_num_k_heads, d.lin_key_dim, d.lin_value_dim, parts, batch,
+                                       (int)tok_stride));
+                e->launches++;
+                pdl = a.pdl;
+            } else if (phases & kPhCore) {
             MOE_CUDA(launch_kernel(pdl, part_kernel, dim3(d.lin_num_v_heads * parts), dim3(kLpThreads),
                                    (size_t)(2 * d.lin_key_dim + kLpRows) * 4, st, ls.conv_state, qkv_raw,
                                    (const uint16_t*)ls.vec[MOE_A_CONV1D], ab, bb, (const float*)ls.vec[MOE_A_A_LOG],
@@ -1490,7 +1721,9 @@ static int attn_model_prefill(moe_engine* e, const float* emb_dev, int32_t n, fl
             // (The two attention kernels of a full-attention layer could chain from token to token, but a chain of hundreds of
             // tiny grids that all become resident and wait for one another ran at 26 us per kernel instead of 8.)
             if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, nullptr, kPhProj, n, S))) return rc;
-            if (ls.full) {  // every token's K / V rows first, then every token's attention over its own prefix: two launches
+            if (ls.full || attn_lin_seq_ok(e, ls)) {
+                // full attention: every token's K / V rows first, then every token's attention over its own prefix (two launches);
+                // DeltaNet: one launch that keeps the state in registers from the first token to the last
                 if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, a.pos_table + a.pos, kPhCore, n, S))) return rc;
             } else {
                 for (int t = 0; t < n; ++t)

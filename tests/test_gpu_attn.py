@@ -147,6 +147,14 @@ def test_decode_with_attention_at_the_model_own_head_counts():
     got9 = eng.model_forward_hidden(emb9)
     print(f"the same as a 9-token prompt: rel-L2 {rel_l2(got9, want9):.1e}, on the updates {rel_l2(got9 - emb9, want9 - emb9):.1e}")
     assert rel_l2(got9, want9) < 1e-2 and rel_l2(got9 - emb9, want9 - emb9) < 1e-2 and eng.model_pos() == 9
+    # what the prompt left behind: the recurrence state and conv inputs of a DeltaNet layer (kept in registers across the nine
+    # tokens by one launch), and a tenth token decoded from there
+    ssm = eng.model_state_download(1, L.ST_SSM, state.lin[1][1].size)
+    ring = eng.model_state_download(1, L.ST_CONV, ad.conv_kernel * ad.conv_dim).reshape(ad.conv_kernel, ad.conv_dim)
+    assert rel_l2(ssm, state.lin[1][1].ravel()) < 1e-2 and rel_l2(rs._shifted_from_ring(ring, 9), state.lin[1][0]) < 1e-2
+    nxt = synth.hidden_states(60, 2, 1, H)
+    want10 = oracle.model_decode_token(attn, moe, ad, state, nxt[0], K)
+    assert rel_l2(eng.model_forward_hidden(nxt)[0], want10) < 1e-2
     eng.close()
 
 
