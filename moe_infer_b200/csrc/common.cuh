@@ -183,7 +183,7 @@ struct ModelAttnState {
     bool graphs_valid = false;
     bool pdl = true;                         // kernels of a layer's attention half start ahead of their predecessor's end
     bool chain = true;                       // no graphs: every kernel of a token, the MoE kernels included, is a programmatic dependent of the one before it
-    int prefill_min = 8;                     // calls of at least this many tokens run layer by layer (MoE halves batched)
+    int prefill_min = 4;                     // calls of at least this many tokens run layer by layer (MoE halves batched)
     int* pos_table = nullptr;                // positions 0 .. max_seq - 1 on the device
     float* prefill_mid = nullptr;            // [prefill_cap, H] attention outputs of a layer, all tokens
     float* prefill_scratch = nullptr;        // [prefill_cap] scratch areas, one per token (same allocation)

@@ -160,7 +160,7 @@ def test_decode_with_attention_at_the_model_own_head_counts():
 
 @pytest.mark.parametrize("n", [8, 60])
 def test_prompt_runs_layer_by_layer_and_matches_the_oracle(n):
-    """A call of 8 tokens or more goes layer by layer: a layer's attention half token after token, its MoE half over all
+    """A call of 4 tokens or more goes layer by layer: a layer's attention half token after token, its MoE half over all
     the tokens in one batched call (the slot-wise FFN up to 48 tokens, the grouped GEMMs on bf16 operands beyond).
     Against the oracle's token-by-token decode, then the sequence goes on token by token from the state it left."""
     layers = 4
