@@ -375,6 +375,18 @@ def run_full_decode(args, eng: NativeEngine, local: int) -> dict:
     t1 = eng.telemetry()
     eng.lib.moe_set_record_telemetry(0)
     host = {k: (t1.get(k, 0.0) - t0.get(k, 0.0)) / 8 for k in ("phase.op2_encode_ms", "phase.hidden_wait_ms")}
+    # a prompt through the same path: 56 tokens in one call (layer by layer: projections, attention, DeltaNet recurrence and
+    # MoE halves each over all the tokens of the call)
+    n_prompt = 56
+    pe = synth.hidden_states(args.seed, 4, n_prompt, H)
+    po = np.empty((n_prompt, H), np.float32)
+
+    def prompt_step(i):
+        eng.model_reset()
+        L.check(eng.lib.moe_model_forward_hidden_host(eng.h, L.ptr(pe), n_prompt, L.ptr(po)))
+
+    tp = timed_repeats(eng, prompt_step, 1, 1, min_repeats=3)
+    eng.model_reset()
     moe_bytes = benchlib.layer_token_bytes(eng.dims) * n_layers
     res = {"workload": f"whole decoder, 1 token x {n_layers} layers: attention half (10 full-attention layers with bf16 projections, "
                        "30 Gated DeltaNet layers with 4-bit projections; Qwen3.6-35B-A3B head counts) + MoE half, host buffers, "
@@ -382,6 +394,9 @@ def run_full_decode(args, eng: NativeEngine, local: int) -> dict:
            "ms_per_token": t["ms_per_step"], "tok_per_s": 1e3 / t["ms_per_step"], "repeats": t["repeats"],
            "gpu_launches": t["launches"], "finite": bool(np.isfinite(out).all()),
            "host_enqueue_ms_per_token": host["phase.op2_encode_ms"], "host_wait_ms_per_token": host["phase.hidden_wait_ms"],
+           "prompt": {"tokens": n_prompt, "ms": tp["ms_per_step"], "ms_per_token": tp["ms_per_step"] / n_prompt,
+                      "tok_per_s": n_prompt / (tp["ms_per_step"] / 1e3), "finite": bool(np.isfinite(po).all()),
+                      "gpu_launches": tp["launches"]},
            "attention_MB_per_token": attn_bytes / 1e6, "moe_MB_per_token": moe_bytes / 1e6,
            "roofline": hbm_roofline("attention kernels + decode_slots_kernel per layer", attn_bytes + moe_bytes, t["ms_per_step"])}
     return res
