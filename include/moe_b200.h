@@ -262,8 +262,9 @@ int moe_mtp_step_host(moe_engine_t* e, const float* h_host, int64_t token_id, fl
  * residual) and a Gated DeltaNet layer otherwise (input norm; in_proj_qkv / z / b / a; causal depthwise conv
  * over the last conv_kernel inputs + SiLU; unweighted per-head q/k norm; decay and input gate from a, b, A_log,
  * dt_bias; delta-rule recurrence on a [v_heads, value_dim, key_dim] f32 state; gated RMS norm; out_proj;
- * residual).  Each attention half feeds the layer's MoE half (the decode kernel).  Token-serial: n tokens are
- * n decode steps.  moe_attn_configure allocates every layer's cache / state and resets the position; tensors
+ * residual).  Each attention half feeds the layer's MoE half (the decode kernel).  Up to three tokens run as that many
+ * decode steps; four and more run layer by layer (projections, cache update and attention, the DeltaNet recurrence and the MoE
+ * half each over all the tokens of the call; same results to the batched MoE path's accuracy).  moe_attn_configure allocates every layer's cache / state and resets the position; tensors
  * by role (norms, conv1d [channels, kernel], dt_bias: bf16; A_log: MOE_DT_F32; projections: MOE_DT_BF16 [out,
  * in] or MOE_DT_INT4 triple).  moe_model_forward_hidden_host: embeddings [n, hidden] -> hidden states before
  * the final norm [n, hidden] (then moe_logits_host); moe_model_forward_host: token ids -> logits [n, vocab].

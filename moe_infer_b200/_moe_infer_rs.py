@@ -8,7 +8,8 @@ CUDA library; nothing here computes the MoE path on the CPU.
 
 Where this surface departs from the reference, and how the calls behave:
   * a model directory that has the attention tensors of every layer runs the whole decoder (gated full attention /
-    Gated DeltaNet half + MoE half per layer) on the GPU, one decode step per token, ``forward_batched`` included;
+    Gated DeltaNet half + MoE half per layer) on the GPU: one decode step per token for calls of up to three tokens, layer
+    by layer with every stage batched over the call's tokens beyond (``forward`` and ``forward_batched`` alike);
     a directory with the MoE tensors only is still accepted and then each block is h <- h + moe(rmsnorm(h));
   * ``forward`` / ``forward_batched`` / ``forward_hidden`` return logits float32 [n, vocab] like the reference
     (embedding rows, stack, final norm and lm_head all on the GPU).  They raise ``RuntimeError`` naming the missing
@@ -417,7 +418,7 @@ class Engine:
             self.upload_cache(cache)
         try:
             if not self._missing_attn:
-                # the whole decoder block per layer; attention has no batched form: one decode step per token
+                # the whole decoder block per layer (token by token, or layer by layer for four tokens and more)
                 self._sync_sequence(cache)
                 out = self.native.model_forward_hidden(emb)
             else:

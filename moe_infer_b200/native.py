@@ -328,7 +328,8 @@ class NativeEngine:
             L.check(self.lib.moe_attn_load_tensor(self.h, layer, which, L.ptr(w), None, None, L.DT_BF16))
 
     def model_forward_hidden(self, emb: np.ndarray) -> np.ndarray:
-        """Embeddings [n, hidden] through attention + MoE of every layer, one decode step per token."""
+        """Embeddings [n, hidden] through attention + MoE of every layer: one decode step per token, or, from four tokens
+        on, layer by layer with projections, attention, recurrence and MoE halves batched over the tokens."""
         emb = np.ascontiguousarray(emb, np.float32).reshape(-1, self.dims.hidden)
         out = np.empty_like(emb)
         L.check(self.lib.moe_model_forward_hidden_host(self.h, L.ptr(emb), emb.shape[0], L.ptr(out)))
