@@ -1724,14 +1724,15 @@ static int attn_model_prefill(moe_engine* e, const float* emb_dev, int32_t n, fl
             if (ls.full || attn_lin_seq_ok(e, ls)) {
                 // full attention: every token's K / V rows first, then every token's attention over its own prefix (two launches);
                 // DeltaNet: one launch that keeps the state in registers from the first token to the last
-                if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, a.pos_table + a.pos, kPhCore, n, S))) return rc;
+                // (both wait for their predecessor before they touch anything: programmatic dependents of the projection)
+                if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, true, a.pos_table + a.pos, kPhCore, n, S))) return rc;
             } else {
                 for (int t = 0; t < n; ++t)
                     if ((rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, a.prefill_scratch + (size_t)t * S,
                                               false, a.pos_table + a.pos + t, kPhCore)))
                         return rc;
             }
-            if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, false, nullptr, kPhOut, n, S))) return rc;
+            if ((rc = attn_layer_step(e, l, cur, a.prefill_mid, a.prefill_scratch, true, nullptr, kPhOut, n, S))) return rc;
         } else {
             for (int t = 0; t < n; ++t)  // a token's first kernel the ordinary way, for the same reason
                 if ((rc = attn_layer_step(e, l, cur + (size_t)t * H, a.prefill_mid + (size_t)t * H, scratch, false, a.pos_table + a.pos + t)))
