@@ -1099,26 +1099,31 @@ int mtp_step(moe_engine* e, const float* h_host, int64_t token_id, float* logits
     MOE_CUDA(cudaMemcpyAsync(m.id_dev, &token_id, 8, cudaMemcpyHostToDevice, st));
     int rc = launch_embed(e, m.id_dev, 1, tok);
     if (rc) return rc;
+    // From here every kernel is a programmatic dependent of the one before it (see pdl_wait: each waits before it reads what
+    // an earlier kernel of the chain wrote, whichever that was); MOE_B200_ATTN_PDL=0 keeps the ordinary dependencies.
+    static const bool pdl = [] { const char* v = getenv("MOE_B200_ATTN_PDL"); return !(v && atoi(v) == 0); }();
     // embedding first, hidden state second (mtp.rs:103-105)
     rms_norm_rows_kernel<<<1, 256, 0, st>>>(tok, m.norms[MOE_M_PRE_FC_NORM_EMBEDDING], H, concat);
-    rms_norm_rows_kernel<<<1, 256, 0, st>>>(h, m.norms[MOE_M_PRE_FC_NORM_HIDDEN], H, concat + H);
+    MOE_CUDA(launch_kernel(pdl, rms_norm_rows_kernel, dim3(1), dim3(256), 0, st, (const float*)h, (const uint16_t*)m.norms[MOE_M_PRE_FC_NORM_HIDDEN], H, concat + H));
     e->launches += 2;
-    rc = proj_run(e, m.proj[MOE_M_FC], concat, cur);
+    rc = proj_run(e, m.proj[MOE_M_FC], concat, cur, nullptr, pdl);
     if (rc) return rc;
-    rms_norm_rows_kernel<<<1, 256, 0, st>>>(cur, m.norms[MOE_M_INPUT_NORM], H, x);
+    MOE_CUDA(launch_kernel(pdl, rms_norm_rows_kernel, dim3(1), dim3(256), 0, st, (const float*)cur, (const uint16_t*)m.norms[MOE_M_INPUT_NORM], H, x));
     e->launches++;
-    if ((rc = proj_run(e, m.proj[MOE_M_Q_PROJ], x, q))) return rc;
-    if ((rc = proj_run(e, m.proj[MOE_M_K_PROJ], x, k))) return rc;
-    if ((rc = proj_run(e, m.proj[MOE_M_V_PROJ], x, v))) return rc;
-    attn_prep_kernel<<<nh + nkv, 256, (size_t)hd * 4, st>>>(q, hd, 0, k, v, m.norms[MOE_M_Q_NORM], m.norms[MOE_M_K_NORM], nh, nkv, hd,
-                                                          m.ad.rotary_dim, pos, nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache, 0);
+    if ((rc = proj_run(e, m.proj[MOE_M_Q_PROJ], x, q, nullptr, pdl))) return rc;
+    if ((rc = proj_run(e, m.proj[MOE_M_K_PROJ], x, k, nullptr, pdl))) return rc;
+    if ((rc = proj_run(e, m.proj[MOE_M_V_PROJ], x, v, nullptr, pdl))) return rc;
+    MOE_CUDA(launch_kernel(pdl, attn_prep_kernel, dim3(nh + nkv), dim3(256), (size_t)hd * 4, st, (const float*)q, hd, 0, (const float*)k,
+                           (const float*)v, (const uint16_t*)m.norms[MOE_M_Q_NORM], (const uint16_t*)m.norms[MOE_M_K_NORM], nh, nkv, hd,
+                           m.ad.rotary_dim, pos, (const int*)nullptr, m.ad.rope_theta, qr, m.k_cache, m.v_cache, 0));
     const int seq = pos + 1;
-    attn_decode_kernel<<<nh, kAttnWarps * 32, (size_t)(seq + hd * (1 + kAttnWarps)) * 4, st>>>(qr, m.k_cache, m.v_cache, q + q_dim, hd, nh, nkv, hd, seq, nullptr,
-                                                               1.0f / sqrtf((float)hd), gated, 0);
+    MOE_CUDA(launch_kernel(pdl, attn_decode_kernel, dim3(nh), dim3(kAttnWarps * 32), (size_t)(seq + hd * (1 + kAttnWarps)) * 4, st,
+                           (const float*)qr, (const float*)m.k_cache, (const float*)m.v_cache, (const float*)(q + q_dim), hd, nh, nkv, hd,
+                           seq, (const int*)nullptr, 1.0f / sqrtf((float)hd), gated, 0));
     e->launches += 2;
-    if ((rc = proj_run(e, m.proj[MOE_M_O_PROJ], gated, cur2, cur))) return rc;  // + residual
+    if ((rc = proj_run(e, m.proj[MOE_M_O_PROJ], gated, cur2, cur, pdl))) return rc;  // + residual
     // the MoE half: post-attention norm, router, experts, shared expert, residual (layer index num_layers)
-    if ((rc = launch_decode(e, d.num_layers, d.num_layers + 1, cur2, y, nullptr, nullptr, nullptr, nullptr))) return rc;
+    if ((rc = launch_decode(e, d.num_layers, d.num_layers + 1, cur2, y, nullptr, nullptr, nullptr, nullptr, pdl))) return rc;
     if ((rc = launch_logits_norm(e, y, 1, logits_dev, m.norms[MOE_M_OUT_NORM]))) return rc;
     return MOE_OK;
 }
