@@ -581,12 +581,23 @@ int moe_matvec_int4_host(moe_engine_t* e, const void* w, const void* s, const vo
 
 // ── one MoE block ────────────────────────────────────────────────────────────
 
+// A single-layer decode call launches its kernel as a programmatic dependent of whatever kernel precedes it in the stream:
+// back-to-back layer calls overlap the next call's launch, layer table and router fetch with the tail of the one before
+// (16.5 -> 14.0 us per call; the kernel waits before it reads its input; a predecessor that never signals simply completes
+// first).  Such a launch is an ordinary one, not a cooperative one (a cooperative grid only starts on a drained device):
+// see launch_decode_slots for why its CTAs are co-resident all the same.  MOE_B200_DECODE_PDL=0: the cooperative launch.
+// The whole-stack launches stay cooperative: one launch per token gains nothing from starting early (445 against 448 us).
+static bool decode_pdl() {
+    static const bool on = [] { const char* v = getenv("MOE_B200_DECODE_PDL"); return !(v && atoi(v) == 0); }();
+    return on;
+}
+
 int moe_layer_forward_dev(moe_engine_t* e, int layer, const float* h_in, int32_t n, float* h_out,
                           const float* logit_bias, const int32_t* forced_idx, int32_t* out_idx, float* out_w) {
     MOE_REQUIRE(e && h_in && h_out, "null argument");
     MOE_REQUIRE(n >= 0, "negative token count");
     if (n == 0) return MOE_OK;
-    if (n == 1) return launch_decode(e, layer, layer + 1, h_in, h_out, logit_bias, forced_idx, out_idx, out_w);
+    if (n == 1) return launch_decode(e, layer, layer + 1, h_in, h_out, logit_bias, forced_idx, out_idx, out_w, decode_pdl());
     return launch_batched_layer(e, layer, h_in, n, h_out, logit_bias, forced_idx, out_idx, out_w);
 }
 
