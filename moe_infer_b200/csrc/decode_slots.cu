@@ -730,12 +730,13 @@ int launch_decode_slots(moe_engine* e, int l0, int l1, const float* h_in, float*
     // the kernel's first CTA (a memset per launch cost a single-layer call about two microseconds of stream time)
     e->dec_sl_hint_base += (unsigned long long)kSG * (unsigned long long)(l1 - l0 + 1);  // one push per layer and the prologue's
     e->dec_sl_epoch += (unsigned int)(l1 - l0);
-    // A cooperative launch: every CTA resident, or the launch fails.  As a programmatic dependent inside the whole-decoder
-    // chain the kernel is launched the ordinary way instead, so that its CTAs can take their SMs while the kernel before
-    // it drains (a cooperative grid waits for the whole device): its CTAs still all become resident, because the kernels
-    // before it never wait for it and the kernels after it are only launched once every CTA here has started (they are
-    // its programmatic dependents).  Another tenant holding SMs for good would end in the kernel's bounded waits and an
-    // error status, not in a hang.  MOE_B200_CHAIN_COOP=1 keeps the cooperative launch there too.
+    // A cooperative launch: every CTA resident, or the launch fails.  As a programmatic dependent (inside the whole-decoder
+    // chain, and in single-layer calls) the kernel is launched the ordinary way instead, so that its CTAs can take their
+    // SMs while the kernel before it drains (a cooperative grid waits for the whole device): its CTAs still all become
+    // resident, because the kernels before it never wait for it and the kernels after it either are its programmatic
+    // dependents, launched only once every CTA here has started, or ordinary launches that wait for its end.  Another
+    // tenant holding SMs for good would end in the kernel's bounded waits and an error status, not in a hang.
+    // MOE_B200_CHAIN_COOP=1 keeps the cooperative launch there too.
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(kSG);
     cfg.blockDim = dim3(kDecThreads);
