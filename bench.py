@@ -29,7 +29,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-NCU_DRAM_BYTES_PER_LAYER = 17.35e6  # (68.04 MB read + 1.36 MB written) / 4 layers: profiles/decode_slots_kernel_4layers.md
+NCU_DRAM_BYTES_PER_LAYER = 17.44e6  # (68.05 MB read + 1.70 MB written) / 4 layers: profiles/decode_slots_kernel_4layers.md
 N_ROTATE = 64  # distinct input tokens cycled through, so routing differs from step to step
 DECODE_DTYPE = "u4 weights x 24-bit fixed-point activations (three s8 digits), exact s32 dp4a sums, f32 scales"
 
