@@ -2,6 +2,7 @@
 kernel after them, from CUPTI activity records (``torch.profiler``; no replay, no clock control).
 
     python -m benchmarks.timeline [--layers 40] [--head 30]
+    python -m benchmarks.timeline --prompt 56        # one call of 56 tokens: per-kernel totals
 
 Timed figures belong to ``bench.py``; this only shows where a token's time goes.  A negative "gap after" is an overlap:
 the next kernel was resident (programmatic dependent launch) before this one ended.
@@ -19,6 +20,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--head", type=int, default=30, help="kernels of the token to list one by one")
+    ap.add_argument("--prompt", type=int, default=0, help="trace one call of this many tokens instead of single tokens")
     a = ap.parse_args()
     import torch
     from torch.profiler import ProfilerActivity, profile
@@ -34,6 +36,29 @@ def main() -> None:
     r = workloads.run_full_decode(types.SimpleNamespace(seed=0, warmup=3, steps=4), eng, 0)
     print(f"untraced: {r['ms_per_token']:.3f} ms per token, {r['gpu_launches'] // 4} kernels per token")
     H = eng.dims.hidden
+    if a.prompt:
+        n = a.prompt
+        emb = np.random.default_rng(0).standard_normal((n, H)).astype(np.float32)
+        out = np.empty((n, H), np.float32)
+        for _ in range(2):  # the first call sizes the work areas
+            eng.model_reset()
+            L.check(eng.lib.moe_model_forward_hidden_host(eng.h, L.ptr(emb), n, L.ptr(out)))
+        eng.model_reset()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            L.check(eng.lib.moe_model_forward_hidden_host(eng.h, L.ptr(emb), n, L.ptr(out)))
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+        tot = collections.defaultdict(lambda: [0, 0.0])
+        for e in evs:
+            name = e.name.split("(")[0].replace("moe::", "").replace("void ", "")[:44]
+            tot[name][0] += 1
+            tot[name][1] += e.time_range.end - e.time_range.start
+        span = evs[-1].time_range.end - evs[0].time_range.start
+        print(f"one call of {n} tokens: {span / 1e3:.2f} ms under the tracer = {span / 1e3 / n:.3f} ms per token, {len(evs)} kernels and copies")
+        print(f"{'kernel':<46}{'n':>6}{'total ms':>11}{'mean us':>10}")
+        for k, v in sorted(tot.items(), key=lambda kv: -kv[1][1]):
+            print(f"{k:<46}{v[0]:>6}{v[1] / 1e3:>11.2f}{v[1] / v[0]:>10.2f}")
+        eng.close()
+        return
     emb = np.random.default_rng(0).standard_normal((1, H)).astype(np.float32)
     out = np.empty((1, H), np.float32)
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
